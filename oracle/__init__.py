@@ -1,0 +1,337 @@
+"""ctypes bindings of the CPU checkers (TEST INFRASTRUCTURE ONLY).
+
+`Oracle` wraps oracle/librl_oracle.so (the C restatement, rl_oracle.c);
+`Reference` wraps oracle/_ref/librl_ref.so (the reference's own CPU operators
+behind ref_shim.cpp) when that library has been built.  Only tests, the smoke
+check and the bench's CPU-baseline / reference legs may import this package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "librl_oracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "librl_ref.so")
+
+
+def build(quiet: bool = True) -> None:
+    """Compile the restatement (and the reference library when its tree is there)."""
+    subprocess.run(["make", "-C", _HERE], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _ptr(a, ct):
+    return a.ctypes.data_as(C.POINTER(ct))
+
+
+class Oracle:
+    """numpy front-end of rl_oracle.c; every method names the C function it calls."""
+
+    def __init__(self):
+        if not os.path.exists(ORACLE_SO):
+            build()
+        self.lib = C.CDLL(ORACLE_SO)
+        self.lib.rlo_tq3_centroids.restype = C.POINTER(C.c_float)
+        self.lib.rlo_f16_to_f32.restype = C.c_float
+        self.lib.rlo_f32_to_f16.restype = C.c_uint16
+        self.lib.rlo_f32_to_f16.argtypes = [C.c_float]
+
+    # -- attention ---------------------------------------------------------
+    def attn_decode(self, q, k_cache, v_cache, pos=None):
+        """rlo_attn_decode: q [n_q,hd], caches [seq,n_kv,hd] fp32 -> o [n_q,hd]."""
+        q, qp = _f32(q)
+        k, kp = _f32(k_cache)
+        v, vp = _f32(v_cache)
+        n_q, hd = q.shape
+        n_kv = k.shape[1]
+        if pos is None:
+            pos = k.shape[0] - 1
+        o = np.empty_like(q)
+        self.lib.rlo_attn_decode(qp, kp, vp, _ptr(o, C.c_float), int(pos), n_q, n_kv, hd)
+        return o
+
+    def attn_prefill(self, q, k, v):
+        """rlo_attn_prefill: q [T,n_q,hd], k/v [T,n_kv,hd] -> o [T,n_q,hd]."""
+        q, qp = _f32(q)
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        T, n_q, hd = q.shape
+        o = np.empty_like(q)
+        self.lib.rlo_attn_prefill(qp, kp, vp, _ptr(o, C.c_float), T, n_q, k.shape[1], hd)
+        return o
+
+    def attn_prefill_rows(self, q_rows, k_cache, v_cache, row_pos):
+        """rlo_attn_prefill_rows: selected query rows at absolute positions row_pos."""
+        q, qp = _f32(q_rows)
+        k, kp = _f32(k_cache)
+        v, vp = _f32(v_cache)
+        rp = np.ascontiguousarray(row_pos, dtype=np.int32)
+        o = np.empty_like(q)
+        self.lib.rlo_attn_prefill_rows(qp, kp, vp, _ptr(o, C.c_float), _ptr(rp, C.c_int),
+                                       len(rp), q.shape[1], k.shape[1], q.shape[2])
+        return o
+
+    def sigmoid_gate(self, o, gate):
+        o = np.array(o, dtype=np.float32, order="C", copy=True)
+        g, gp = _f32(gate)
+        self.lib.rlo_sigmoid_gate(_ptr(o, C.c_float), gp, C.c_long(o.size))
+        return o
+
+    def gated_attn_decode(self, q, k_cache, v_cache, gate, pos=None):
+        return self.sigmoid_gate(self.attn_decode(q, k_cache, v_cache, pos), gate)
+
+    def attn_partial(self, qh, k_cache, v_cache, s0, s1, hkv):
+        qh, qp = _f32(qh)
+        k, kp = _f32(k_cache)
+        v, vp = _f32(v_cache)
+        hd = qh.shape[0]
+        m = C.c_float()
+        l = C.c_float()
+        acc = np.empty(hd, np.float32)
+        self.lib.rlo_attn_partial(qp, kp, vp, int(s0), int(s1), k.shape[1], int(hkv), hd,
+                                  C.byref(m), C.byref(l), _ptr(acc, C.c_float))
+        return m.value, l.value, acc
+
+    def lse_combine(self, m, l, acc):
+        m, mp = _f32(m)
+        l, lp = _f32(l)
+        acc, ap = _f32(acc)
+        o = np.empty(acc.shape[1], np.float32)
+        self.lib.rlo_lse_combine(mp, lp, ap, len(m), acc.shape[1], _ptr(o, C.c_float))
+        return o
+
+    # -- fp16 / paging -------------------------------------------------------
+    def to_f16(self, x):
+        x, xp = _f32(x)
+        y = np.empty(x.shape, np.uint16)
+        self.lib.rlo_f32_to_f16_n(xp, _ptr(y, C.c_uint16), C.c_long(x.size))
+        return y
+
+    def from_f16(self, x):
+        x = np.ascontiguousarray(x, dtype=np.uint16)
+        y = np.empty(x.shape, np.float32)
+        self.lib.rlo_f16_to_f32_n(_ptr(x, C.c_uint16), _ptr(y, C.c_float), C.c_long(x.size))
+        return y
+
+    def paged_gather(self, pool, table, seq_len):
+        """rlo_paged_gather_u16: pool [pages,n_kv,page_tokens,hd] u16 -> [seq,n_kv,hd]."""
+        pool = np.ascontiguousarray(pool, dtype=np.uint16)
+        table = np.ascontiguousarray(table, dtype=np.int32)
+        _, n_kv, pt, hd = pool.shape
+        out = np.empty((seq_len, n_kv, hd), np.uint16)
+        self.lib.rlo_paged_gather_u16(_ptr(pool, C.c_uint16), _ptr(table, C.c_int32), int(seq_len),
+                                      n_kv, pt, hd, _ptr(out, C.c_uint16))
+        return out
+
+    def paged_scatter(self, pool, table, s0, rows):
+        """rlo_paged_scatter_u16 (in place on pool): rows [n,n_kv,hd] -> tokens s0.."""
+        assert pool.dtype == np.uint16 and pool.flags.c_contiguous
+        table = np.ascontiguousarray(table, dtype=np.int32)
+        rows = np.ascontiguousarray(rows, dtype=np.uint16)
+        _, n_kv, pt, hd = pool.shape
+        self.lib.rlo_paged_scatter_u16(_ptr(pool, C.c_uint16), _ptr(table, C.c_int32), int(s0),
+                                       int(s0 + rows.shape[0]), n_kv, pt, hd,
+                                       _ptr(rows, C.c_uint16))
+
+    # -- DeltaNet --------------------------------------------------------------
+    def delta_step(self, S, q, k, v, beta, g_log, eps=1e-6):
+        """rlo_delta_step: S [n_v,dk,dv] updated in place; returns o [n_v,dv]."""
+        assert S.dtype == np.float32 and S.flags.c_contiguous
+        q, qp = _f32(q)
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        b, bp = _f32(beta)
+        g, gp = _f32(g_log)
+        n_v, dk, dv = S.shape
+        o = np.empty((n_v, dv), np.float32)
+        self.lib.rlo_delta_step(_ptr(S, C.c_float), qp, kp, vp, bp, gp, _ptr(o, C.c_float), n_v,
+                                dk, dv, C.c_float(eps))
+        return o
+
+    def delta_prefill_seq(self, S, q, k, v, beta, g_log, eps=1e-6):
+        """rlo_delta_prefill_seq: T sequential steps; q,k [T,n_v,dk] ..."""
+        assert S.dtype == np.float32 and S.flags.c_contiguous
+        q, qp = _f32(q)
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        b, bp = _f32(beta)
+        g, gp = _f32(g_log)
+        n_v, dk, dv = S.shape
+        T = q.shape[0]
+        o = np.empty((T, n_v, dv), np.float32)
+        self.lib.rlo_delta_prefill_seq(_ptr(S, C.c_float), qp, kp, vp, bp, gp, _ptr(o, C.c_float),
+                                       T, n_v, dk, dv, C.c_float(eps))
+        return o
+
+    def repeat_heads(self, x, n_v, tiled=False):
+        x, xp = _f32(x)
+        n_k, d = x.shape
+        y = np.empty((n_v, d), np.float32)
+        self.lib.rlo_repeat_heads(xp, _ptr(y, C.c_float), n_k, n_v, d, int(tiled))
+        return y
+
+    def delta_gates(self, a, b, A_log, dt_bias):
+        a, ap = _f32(a)
+        b, bp = _f32(b)
+        A, Ap = _f32(A_log)
+        d, dp = _f32(dt_bias)
+        beta = np.empty_like(a)
+        g = np.empty_like(a)
+        self.lib.rlo_delta_gates(ap, bp, Ap, dp, _ptr(beta, C.c_float), _ptr(g, C.c_float), a.size)
+        return beta, g
+
+    def l2norm(self, x, eps=1e-6):
+        x, xp = _f32(x)
+        y = np.empty_like(x)
+        self.lib.rlo_l2norm(xp, _ptr(y, C.c_float), x.size, C.c_float(eps))
+        return y
+
+    def conv1d_update(self, x_t, w, state):
+        """rlo_conv1d_update: state [dim,k] updated in place; returns y [dim]."""
+        assert state.dtype == np.float32 and state.flags.c_contiguous
+        x, xp = _f32(x_t)
+        w, wp = _f32(w)
+        dim, k = w.shape
+        y = np.empty(dim, np.float32)
+        self.lib.rlo_conv1d_update(xp, wp, _ptr(state, C.c_float), _ptr(y, C.c_float), dim, k)
+        return y
+
+    def conv1d_causal_prefill(self, x, w):
+        x, xp = _f32(x)
+        w, wp = _f32(w)
+        seq, dim = x.shape
+        y = np.empty_like(x)
+        self.lib.rlo_conv1d_causal_prefill(xp, wp, _ptr(y, C.c_float), seq, dim, w.shape[1])
+        return y
+
+    # -- compact KV ------------------------------------------------------------
+    def centroids(self):
+        return np.ctypeslib.as_array(self.lib.rlo_tq3_centroids(), shape=(8,)).copy()
+
+    def fwht(self, x):
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        self.lib.rlo_fwht(_ptr(x, C.c_float), x.size)
+        return x
+
+    def compact_store(self, k, v, wht_len=128, signs=None):
+        """rlo_compact_store: k,v [T,n_kv,hd] fp32 -> (k_q i8, k_sc u16, v_codes u8, v_sc u16)."""
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        T, n_kv, hd = k.shape
+        nblk = hd // wht_len
+        k_q = np.empty((T, n_kv, hd), np.int8)
+        k_sc = np.empty((T, n_kv), np.uint16)
+        v_codes = np.empty((T, n_kv, hd * 3 // 8), np.uint8)
+        v_sc = np.empty((T, n_kv, nblk), np.uint16)
+        sp = None
+        if signs is not None:
+            signs, sp = _f32(signs)
+        self.lib.rlo_compact_store(kp, vp, C.c_long(T), n_kv, hd, wht_len, sp, _ptr(k_q, C.c_int8),
+                                   _ptr(k_sc, C.c_uint16), _ptr(v_codes, C.c_uint8),
+                                   _ptr(v_sc, C.c_uint16))
+        return k_q, k_sc, v_codes, v_sc
+
+    def compact_dequant(self, k_q, k_sc, v_codes, v_sc, wht_len=128, signs=None):
+        k_q = np.ascontiguousarray(k_q, np.int8)
+        k_sc = np.ascontiguousarray(k_sc, np.uint16)
+        v_codes = np.ascontiguousarray(v_codes, np.uint8)
+        v_sc = np.ascontiguousarray(v_sc, np.uint16)
+        T, n_kv, hd = k_q.shape
+        k = np.empty((T, n_kv, hd), np.float32)
+        v = np.empty((T, n_kv, hd), np.float32)
+        sp = None
+        if signs is not None:
+            signs, sp = _f32(signs)
+        self.lib.rlo_compact_dequant(_ptr(k_q, C.c_int8), _ptr(k_sc, C.c_uint16),
+                                     _ptr(v_codes, C.c_uint8), _ptr(v_sc, C.c_uint16), C.c_long(T),
+                                     n_kv, hd, wht_len, sp, _ptr(k, C.c_float), _ptr(v, C.c_float))
+        return k, v
+
+
+class Reference:
+    """The reference's own CPU operators (oracle/_ref/librl_ref.so)."""
+
+    def __init__(self):
+        if not os.path.exists(REF_SO):
+            raise FileNotFoundError(REF_SO)
+        self.lib = C.CDLL(REF_SO)
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_SO)
+
+    def simd_name(self) -> str:
+        buf = C.create_string_buffer(128)
+        self.lib.ref_simd_name(buf, 128)
+        return buf.value.decode()
+
+    def num_threads(self) -> int:
+        return int(self.lib.ref_num_threads())
+
+    def set_threads(self, n: int) -> None:
+        self.lib.ref_set_threads(int(n))
+
+    def attn_decode(self, q, k_cache, v_cache, pos=None):
+        q, qp = _f32(q)
+        k, kp = _f32(k_cache)
+        v, vp = _f32(v_cache)
+        if pos is None:
+            pos = k.shape[0] - 1
+        o = np.empty_like(q)
+        self.lib.ref_attn_decode(qp, kp, vp, _ptr(o, C.c_float), int(pos), q.shape[0], k.shape[1],
+                                 q.shape[1])
+        return o
+
+    def attn_prefill(self, q, k, v):
+        q, qp = _f32(q)
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        o = np.empty_like(q)
+        self.lib.ref_attn_prefill(qp, kp, vp, _ptr(o, C.c_float), q.shape[0], q.shape[1],
+                                  k.shape[1], q.shape[2])
+        return o
+
+    def delta_step(self, S, q, k, v, beta, g_log, eps=1e-6, simd=False):
+        assert S.dtype == np.float32 and S.flags.c_contiguous
+        q, qp = _f32(q)
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        b, bp = _f32(beta)
+        g, gp = _f32(g_log)
+        n_v, dk, dv = S.shape
+        o = np.empty((n_v, dv), np.float32)
+        fn = self.lib.ref_delta_step_simd if simd else self.lib.ref_delta_step_scalar
+        fn(_ptr(S, C.c_float), qp, kp, vp, bp, gp, _ptr(o, C.c_float), n_v, dk, dv, C.c_float(eps))
+        return o
+
+    def conv1d_update(self, x_t, w, state):
+        assert state.dtype == np.float32 and state.flags.c_contiguous
+        x, xp = _f32(x_t)
+        w, wp = _f32(w)
+        dim, k = w.shape
+        y = np.empty(dim, np.float32)
+        self.lib.ref_conv1d_update(xp, wp, _ptr(state, C.c_float), _ptr(y, C.c_float), dim, k)
+        return y
+
+    def conv1d_causal_prefill(self, x, w):
+        x, xp = _f32(x)
+        w, wp = _f32(w)
+        y = np.empty_like(x)
+        self.lib.ref_conv1d_causal_prefill(xp, wp, _ptr(y, C.c_float), x.shape[0], x.shape[1],
+                                           w.shape[1])
+        return y
+
+    def l2norm(self, x, eps=1e-6):
+        x, xp = _f32(x)
+        y = np.empty_like(x)
+        self.lib.ref_l2norm(xp, _ptr(y, C.c_float), x.size, C.c_float(eps))
+        return y

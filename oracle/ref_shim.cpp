@@ -1,0 +1,60 @@
+// ref_shim.cpp -- C entry points onto the UNMODIFIED RapidLLM CPU operators.
+//
+// TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile together with the
+// reference's own source files, taken where they lie in the reference tree,
+// into oracle/_ref/librl_ref.so.  It pins the C restatement in rl_oracle.c
+// and serves as the timed CPU baseline.  Nothing here is copied from the
+// reference: this file only forwards arguments.
+#include "rapidllm/kernels/cpu_caps.h"
+#include "rapidllm/kernels/ops.h"
+#include "rapidllm/runtime/thread_pool.h"
+
+#include <cstring>
+
+using namespace rapidllm;
+
+extern "C" {
+
+void ref_attn_decode(const float* q, const float* k, const float* v, float* o, int pos, int n_q,
+                     int n_kv, int hd) {
+    ops::attn_decode(q, k, v, o, pos, n_q, n_kv, hd);
+}
+
+void ref_attn_prefill(const float* q, const float* k, const float* v, float* o, int seq, int n_q,
+                      int n_kv, int hd) {
+    ops::attn_prefill(q, k, v, o, seq, n_q, n_kv, hd);
+}
+
+void ref_delta_step_scalar(float* S, const float* q, const float* k, const float* v,
+                           const float* beta, const float* g, float* o, int n_v, int dk, int dv,
+                           float eps) {
+    ops::delta_recurrent_step_scalar(S, q, k, v, beta, g, o, n_v, dk, dv, eps);
+}
+
+void ref_delta_step_simd(float* S, const float* q, const float* k, const float* v,
+                         const float* beta, const float* g, float* o, int n_v, int dk, int dv,
+                         float eps) {
+    ops::delta_recurrent_step_simd(S, q, k, v, beta, g, o, n_v, dk, dv, eps);
+}
+
+void ref_conv1d_update(const float* x, const float* w, float* state, float* y, int dim, int k) {
+    ops::conv1d_update(x, w, state, y, dim, k);
+}
+
+void ref_conv1d_causal_prefill(const float* x, const float* w, float* y, int seq, int dim, int k) {
+    ops::conv1d_causal_prefill(x, w, y, seq, dim, k);
+}
+
+void ref_l2norm(const float* x, float* y, int n, float eps) { ops::l2norm(x, y, n, eps); }
+
+void ref_set_threads(int n) { set_num_threads(n); }
+int ref_num_threads(void) { return num_threads(); }
+
+int ref_simd_name(char* buf, int n) {
+    const char* s = ops::simd_isa_name();
+    std::strncpy(buf, s, n > 0 ? n - 1 : 0);
+    if (n > 0) buf[n - 1] = 0;
+    return static_cast<int>(std::strlen(s));
+}
+
+} // extern "C"

@@ -1,0 +1,175 @@
+"""The CPU restatement (oracle/rl_oracle.c) against the reference's own outputs.
+
+Golden vectors in tests/golden/ref_vectors.npz were produced by the reference's
+compiled CPU operators and by its python/goldens/tiny_hybrid.py (see
+tests/golden/make_golden.py).  Integer / same-order fp32 paths must match
+bit for bit; the AVX path and the double-precision Python model within a
+stated tolerance.
+"""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_attn_decode_bit_exact_vs_reference_golden(oracle, golden, tag):
+    q, k, v = (golden[f"attn_decode_{tag}_{n}"] for n in "qkv")
+    assert np.array_equal(oracle.attn_decode(q, k, v), golden[f"attn_decode_{tag}_o"])
+    assert np.array_equal(oracle.attn_decode(q, k, v, pos=k.shape[0] // 2),
+                          golden[f"attn_decode_{tag}_o_half"])
+
+
+def test_attn_prefill_bit_exact_vs_reference_golden(oracle, golden):
+    q, k, v = golden["attn_prefill_q"], golden["attn_prefill_k"], golden["attn_prefill_v"]
+    assert np.array_equal(oracle.attn_prefill(q, k, v), golden["attn_prefill_o"])
+    rows = np.array([0, 7, 18], np.int32)
+    o = oracle.attn_prefill_rows(q[rows], k, v, rows)
+    assert np.array_equal(o, golden["attn_prefill_o"][rows])
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_delta_step_vs_reference_golden(oracle, golden, tag):
+    S = golden[f"delta_{tag}_S0"].copy()
+    for t in range(3):
+        a = [golden[f"delta_{tag}_{n}{t}"] for n in ("q", "k", "v", "beta", "g")]
+        o = oracle.delta_step(S, *a)
+        assert np.array_equal(o, golden[f"delta_{tag}_o_scalar{t}"])
+        # the AVX-512/AVX2 path fuses multiply-adds: same maths, other rounding
+        assert rel_l2(o, golden[f"delta_{tag}_o_simd{t}"]) < 1e-5
+    assert np.array_equal(S, golden[f"delta_{tag}_S_scalar"])
+    assert rel_l2(S, golden[f"delta_{tag}_S_simd"]) < 1e-5
+
+
+def test_conv1d_vs_reference_golden(oracle, golden):
+    w, xs = golden["conv_w"], golden["conv_x"]
+    st = np.zeros_like(w)
+    ys = np.stack([oracle.conv1d_update(x, w, st) for x in xs])
+    assert np.array_equal(ys, golden["conv_y_update"])
+    assert np.array_equal(st, golden["conv_state_end"])
+    assert np.array_equal(oracle.conv1d_causal_prefill(xs, w), golden["conv_y_prefill"])
+    # decode form and prefill form are the same function of the inputs
+    assert np.array_equal(golden["conv_y_update"], golden["conv_y_prefill"])
+    assert np.array_equal(oracle.l2norm(golden["l2_x"]), golden["l2_y"])
+
+
+def test_tiny_hybrid_python_model(oracle, golden):
+    """python/goldens/tiny_hybrid.py delta_step (120-146) and decode attention
+    with the sigmoid gate (275-312), double precision, tiny dims."""
+    S = golden["tiny_delta_S0"].astype(np.float32)
+    eps = float(golden["tiny_delta_eps"])
+    for t in range(2):
+        a = [golden[f"tiny_delta_{n}{t}"] for n in ("q", "k", "v", "beta", "g")]
+        o = oracle.delta_step(S, *a, eps=eps)
+        assert np.allclose(o, golden[f"tiny_delta_o{t}"], rtol=1e-4, atol=1e-5)
+    assert np.allclose(S, golden["tiny_delta_S_end"], rtol=1e-4, atol=1e-5)
+    o = oracle.gated_attn_decode(golden["tiny_attn_q"], golden["tiny_attn_k"],
+                                 golden["tiny_attn_v"],
+                                 golden["tiny_attn_gate"].reshape(golden["tiny_attn_q"].shape))
+    assert np.allclose(o.ravel(), golden["tiny_attn_o"], rtol=1e-4, atol=1e-6)
+
+
+def test_live_reference_bit_exact(oracle, reference):
+    """Random shapes against the reference library built in this container."""
+    rng = np.random.default_rng(7)
+    for n_q, n_kv, hd, seq in [(24, 4, 256, 130), (4, 4, 16, 9), (12, 2, 128, 65)]:
+        q = rng.standard_normal((n_q, hd), dtype=np.float32)
+        k = rng.standard_normal((seq, n_kv, hd), dtype=np.float32)
+        v = rng.standard_normal((seq, n_kv, hd), dtype=np.float32)
+        assert np.array_equal(oracle.attn_decode(q, k, v), reference.attn_decode(q, k, v))
+    S1 = (rng.standard_normal((48, 128, 128), dtype=np.float32) * 0.02).astype(np.float32)
+    S2 = S1.copy()
+    for _ in range(4):
+        q = rng.standard_normal((48, 128), dtype=np.float32)
+        k = rng.standard_normal((48, 128), dtype=np.float32)
+        v = rng.standard_normal((48, 128), dtype=np.float32)
+        b = rng.random(48, dtype=np.float32)
+        g = -rng.random(48, dtype=np.float32)
+        assert np.array_equal(oracle.delta_step(S1, q, k, v, b, g),
+                              reference.delta_step(S2, q, k, v, b, g))
+    assert np.array_equal(S1, S2)
+    w = rng.standard_normal((10240, 4), dtype=np.float32)
+    s1 = rng.standard_normal((10240, 4), dtype=np.float32)
+    s2 = s1.copy()
+    x = rng.standard_normal(10240, dtype=np.float32)
+    assert np.array_equal(oracle.conv1d_update(x, w, s1), reference.conv1d_update(x, w, s2))
+    assert np.array_equal(s1, s2)
+
+
+def test_split_partials_combine_to_unsplit(oracle):
+    rng = np.random.default_rng(3)
+    n_kv, hd, seq = 2, 64, 300
+    q = rng.standard_normal((4, hd), dtype=np.float32)
+    k = rng.standard_normal((seq, n_kv, hd), dtype=np.float32)
+    v = rng.standard_normal((seq, n_kv, hd), dtype=np.float32)
+    full = oracle.attn_decode(q, k, v)
+    cuts = [0, 64, 128, 129, 300]
+    for hq in range(4):
+        parts = [oracle.attn_partial(q[hq], k, v, a, b, hq // 2) for a, b in zip(cuts, cuts[1:])]
+        o = oracle.lse_combine([p[0] for p in parts], [p[1] for p in parts],
+                               np.stack([p[2] for p in parts]))
+        assert rel_l2(o, full[hq]) < 1e-6
+    # an empty split (m = -1e30, l = 0) must not disturb the result
+    m, l, acc = oracle.attn_partial(q[0], k, v, 10, 10, 0)
+    assert l == 0.0 and m == np.float32(-1e30)
+
+
+def test_fp16_round_to_nearest_even(oracle):
+    x = np.array([1.0, 1.0 + 2 ** -11, 1.0 + 3 * 2 ** -11, 65504.0, 1e-8, -2.5, 6.1e-5],
+                 np.float32)
+    assert np.array_equal(oracle.to_f16(x), x.astype(np.float16).view(np.uint16))
+    r = np.random.default_rng(0).standard_normal(4096).astype(np.float32)
+    assert np.array_equal(oracle.to_f16(r), r.astype(np.float16).view(np.uint16))
+    assert np.array_equal(oracle.from_f16(oracle.to_f16(r)),
+                          r.astype(np.float16).astype(np.float32))
+
+
+def test_paged_gather_equals_contiguous(oracle):
+    rng = np.random.default_rng(5)
+    n_kv, pt, hd, n_pages = 4, 64, 256, 9
+    seq = 64 * 5 + 17
+    rows = rng.integers(0, 65535, size=(seq, n_kv, hd), dtype=np.uint16)
+    table = rng.permutation(n_pages)[:6].astype(np.int32)
+    pool = np.zeros((n_pages, n_kv, pt, hd), np.uint16)
+    oracle.paged_scatter(pool, table, 0, rows[:100])
+    oracle.paged_scatter(pool, table, 100, rows[100:])
+    assert np.array_equal(oracle.paged_gather(pool, table, seq), rows)
+
+
+@pytest.mark.parametrize("wht_len,use_signs", [(128, False), (256, True), (256, False)])
+def test_compact_kv_properties(oracle, wht_len, use_signs):
+    rng = np.random.default_rng(11)
+    T, n_kv, hd = 33, 4, 256
+    k = rng.standard_normal((T, n_kv, hd), dtype=np.float32)
+    v = rng.standard_normal((T, n_kv, hd), dtype=np.float32)
+    signs = (2.0 * rng.integers(0, 2, wht_len) - 1).astype(np.float32) if use_signs else None
+    k_q, k_sc, v_codes, v_sc = oracle.compact_store(k, v, wht_len, signs)
+    # q8: |q| <= 127, the row maximum maps to +-127, error below one step
+    assert np.abs(k_q.astype(np.int32)).max() == 127
+    amax = np.abs(k).max(-1)
+    s = amax / np.float32(127) + np.float32(1e-8)
+    assert np.array_equal(k_sc, s.astype(np.float16).view(np.uint16))
+    kd, vd = oracle.compact_dequant(k_q, k_sc, v_codes, v_sc, wht_len, signs)
+    assert np.abs(kd - k).max() <= 0.51 * s.max() + 2e-3 * amax.max()
+    # the transform is orthonormal and its own inverse
+    x = rng.standard_normal(wht_len).astype(np.float32)
+    y = oracle.fwht(x)
+    assert abs(np.linalg.norm(y) - np.linalg.norm(x)) < 1e-4
+    assert np.allclose(oracle.fwht(y), x, atol=1e-5)
+    # TQ3: scale is the RMS of the block, reconstruction error is that of an
+    # 8-level Lloyd-Max quantiser for N(0,1) (MSE 0.03454 -> rel error ~0.186)
+    rms = np.sqrt((v.reshape(T, n_kv, hd // wht_len, wht_len) ** 2).mean(-1))
+    assert np.allclose(oracle.from_f16(v_sc), rms, rtol=2e-3)
+    rel = rel_l2(vd, v)
+    assert 0.15 < rel < 0.22, rel
+    # codes are packed 8 per 3 bytes, LSB first
+    w = v_codes[0, 0, 0].astype(np.uint32) | (v_codes[0, 0, 1].astype(np.uint32) << 8) | \
+        (v_codes[0, 0, 2].astype(np.uint32) << 16)
+    cent = oracle.centroids()
+    xb = v[0, 0, :wht_len] * (signs if signs is not None else 1)
+    yb = oracle.fwht(xb)
+    r = np.float32(np.sqrt(np.float32((yb.astype(np.float64) ** 2).sum()) / wht_len))
+    for j in range(8):
+        idx = (w >> (3 * j)) & 7
+        assert idx == np.argmin(np.abs(yb[j] / r - cent)) or \
+            abs(abs(yb[j] / r - cent[idx]) - np.abs(yb[j] / r - cent).min()) < 1e-5
