@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the hybrid-attention hot path on B200.
+
+Workload (the "full 64-layer hybrid stack decode" configuration): 64 layers in
+the pattern 3 x Gated DeltaNet + 1 x Gated Attention, attention/DeltaNet
+operators only, batch 32 sequences with ragged contexts uniform in
+[8192, 32768] on a paged F16 KV cache (64-token pages, shuffled page table),
+24Q/4KV heads of 256, 16K/48V DeltaNet heads of 128x128 FP32 state, conv k=4 over
+10240 channels; seed 4; synthetic N(0,1) data.  One step = one decode step of
+every sequence through all 64 layers (KV append + attend + gate; conv update +
+delta rule).  Every step streams the whole KV cache and all recurrent state
+(~50 GB), far more than the 126 MB L2, so no explicit L2 flush is needed.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 (under torchrun, one rank per GPU): the batch is sharded by sequence --
+every rank owns 32 sequences of its own; there is no data-path collective.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_LAYERS, N_Q, N_KV, HD = 64, 24, 4, 256
+N_V, N_K, DK, DV, CONV_K = 48, 16, 128, 128, 4
+CONV_DIM = 2 * N_K * DK + N_V * DV
+PAGE = 64
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--ctx-min", type=int, default=8192)
+    ap.add_argument("--ctx-max", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--seed", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def contexts(args, rank):
+    import torch
+    g = torch.Generator().manual_seed(args.seed + 1000 * rank)
+    return torch.randint(args.ctx_min, args.ctx_max + 1, (args.batch,), generator=g).tolist()
+
+
+def workload_name(args):
+    return ("hybrid_stack_decode: %d layers (3 DeltaNet + 1 GatedAttn), batch %d, ragged ctx U[%d,%d], "
+            "paged F16 KV page 64" % (args.layers, args.batch, args.ctx_min, args.ctx_max))
+
+
+def algorithmic_bytes(args, ctx):
+    """Bytes one step must move, per kernel family (per layer-launch, and per step)."""
+    B = len(ctx)
+    n_attn = args.layers // 4
+    n_delta = args.layers - n_attn
+    attn_launch = sum(ctx) * N_KV * HD * 2 * 2 + B * N_Q * HD * 4 * 3
+    delta_launch = B * (2 * N_V * DK * DV * 4 + 2 * (N_K * DK * 4) + N_V * DV * 4 * 2 + N_V * 8)
+    conv_launch = B * (2 * CONV_DIM * CONV_K * 4 + 2 * CONV_DIM * 4) + CONV_DIM * CONV_K * 4
+    append_launch = B * N_KV * HD * (4 + 2) * 2
+    return {"attn_decode": attn_launch, "delta_rule": delta_launch, "conv1d_update": conv_launch,
+            "kv_append": append_launch,
+            "step": n_attn * (attn_launch + append_launch) + n_delta * (delta_launch + conv_launch)}
+
+
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------
+def cpu_reference_leg(args, ctx, seconds_budget=12.0, quiet=False):
+    """Time the reference's CPU implementation of one step's operators on host cores.
+
+    Attention: ops::attn_decode (scalar, one thread: the reference has no other CPU
+    attention) on whole sequences of the workload; DeltaNet: ops::conv1d_update +
+    ops::delta_recurrent_step_simd (AVX, WorkerPool threads) for the whole batch of one
+    layer.  The per-layer costs are scaled to the 16 + 48 layers of a step.
+    """
+    import numpy as np
+
+    import oracle as orc
+    kind = "reference" if orc.Reference.available() else "port"
+    impl = orc.Reference() if kind == "reference" else orc.Oracle()
+    rng = np.random.default_rng(args.seed)
+    # attention sample: the two shortest sequences of the batch, full context
+    order = sorted(range(len(ctx)), key=lambda b: ctx[b])[:2]
+    t_attn_tok = []
+    for b in order:
+        n = ctx[b]
+        k = rng.standard_normal((n, N_KV, HD), dtype=np.float32).astype(np.float16).astype(np.float32)
+        v = rng.standard_normal((n, N_KV, HD), dtype=np.float32).astype(np.float16).astype(np.float32)
+        q = rng.standard_normal((N_Q, HD), dtype=np.float32)
+        t0 = time.perf_counter()
+        reps = 0
+        while True:
+            impl.attn_decode(q, k, v)
+            reps += 1
+            if time.perf_counter() - t0 > seconds_budget / 4:
+                break
+        t_attn_tok.append((time.perf_counter() - t0) / reps / n)
+        del k, v
+    attn_s_per_tok = float(np.mean(t_attn_tok))
+    # DeltaNet sample: one layer, whole batch
+    B = len(ctx)
+    S = (rng.standard_normal((B, N_V, DK, DV), dtype=np.float32) * 0.02).astype(np.float32)
+    cst = np.zeros((B, CONV_DIM, CONV_K), np.float32)
+    w = (rng.standard_normal((CONV_DIM, CONV_K), dtype=np.float32) * 0.5).astype(np.float32)
+    x = rng.standard_normal((B, CONV_DIM), dtype=np.float32)
+    beta = rng.random((B, N_V), dtype=np.float32)
+    g = -rng.random((B, N_V), dtype=np.float32)
+    rep = N_V // N_K
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        for b in range(B):
+            mixed = impl.conv1d_update(x[b], w, cst[b])
+            qq = np.repeat(mixed[:N_K * DK].reshape(N_K, DK), rep, axis=0)
+            kk = np.repeat(mixed[N_K * DK:2 * N_K * DK].reshape(N_K, DK), rep, axis=0)
+            vv = mixed[2 * N_K * DK:].reshape(N_V, DV)
+            if kind == "reference":
+                impl.delta_step(S[b], qq, kk, vv, beta[b], g[b], simd=True)
+            else:
+                impl.delta_step(S[b], qq, kk, vv, beta[b], g[b])
+        reps += 1
+        if time.perf_counter() - t0 > seconds_budget / 4:
+            break
+    delta_layer_s = (time.perf_counter() - t0) / reps
+    n_attn = args.layers // 4
+    n_delta = args.layers - n_attn
+    step_s = n_attn * attn_s_per_tok * sum(ctx) + n_delta * delta_layer_s
+    cores = impl.num_threads() if kind == "reference" else 1
+    isa = impl.simd_name() if kind == "reference" else "scalar C"
+    return {"value": len(ctx) / step_s, "unit": "seq-steps/s", "cores": cores, "kind": kind,
+            "sample": ("ops::attn_decode (scalar, 1 thread) on the 2 shortest sequences (%d, %d tokens) of one "
+                       "layer, scaled by tokens to 32 seq x %d layers; conv1d_update + delta_recurrent_step_simd "
+                       "(%s, %d threads) on one whole layer x %d layers" %
+                       (ctx[order[0]], ctx[order[1]], n_attn, isa, cores, n_delta)),
+            "step_seconds": step_s, "attn_us_per_token_layer": attn_s_per_tok * 1e6,
+            "delta_ms_per_layer_batch": delta_layer_s * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ctx = contexts(args, 0)
+    steps = []
+    for _ in range(max(0, args.warmup)):
+        cpu_reference_leg(args, ctx, seconds_budget=2.0)
+    base = None
+    for _ in range(max(1, args.steps)):
+        base = cpu_reference_leg(args, ctx, seconds_budget=max(2.0, 60.0 / max(1, args.steps)))
+        steps.append(base["step_seconds"])
+    step_s = sum(steps) / len(steps)
+    value = len(ctx) * args.gpus / step_s
+    line = {"impl": "reference", "metric": "hybrid-layer decode steps/sec", "value": value,
+            "unit": "seq-steps/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(args), "l2": "inputs larger than L2",
+                       "note": "reference CPU operators on host cores; each step is a bounded sample scaled to the "
+                               "whole step; N ranks would each run the same CPU work, so value scales by n_gpus"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": value, "unit": "seq-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    line["cpu_baseline"]["value"] = value
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as ge
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if local == 0:
+        ge.build()
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.barrier()
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    if not _lib.lib().rl_b200_available():
+        raise SystemExit("no sm_100 device: the CUDA path is the only path")
+
+    ctx = contexts(args, rank)
+    B = args.batch
+    pages = [(c + PAGE - 1) // PAGE for c in ctx]
+    max_pages = max(pages)
+    n_pages = sum(pages)
+    types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
+    cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages,
+                        max_seq_len=max(ctx))
+    gen = torch.Generator(device="cuda").manual_seed(args.seed + 1000 * rank)
+    for a in range(cache.n_attn):
+        cache.k_pool(a).normal_(generator=gen)
+        cache.v_pool(a).normal_(generator=gen)
+    for d in range(cache.n_delta):
+        cache.state(d).normal_(0.0, 0.02, generator=gen)
+        cache.conv(d).normal_(generator=gen)
+    cg = torch.Generator().manual_seed(args.seed + 1000 * rank)
+    perm = torch.randperm(n_pages, generator=cg).int()
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    at = 0
+    for b, p in enumerate(pages):
+        table[b, :p] = perm[at:at + p]
+        at += p
+    sh = cache.io_shapes(B)
+    host = {}
+    for n in ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv"):
+        host[n] = torch.randn(sh[n], generator=cg).pin_memory()
+    host["delta_beta"] = torch.sigmoid(torch.randn(sh["delta_beta"], generator=cg)).pin_memory()
+    host["delta_g"] = (-torch.nn.functional.softplus(torch.randn(sh["delta_g"], generator=cg))).pin_memory()
+    host["attn_o"] = torch.zeros(sh["attn_o"]).pin_memory()
+    host["delta_o"] = torch.zeros(sh["delta_o"]).pin_memory()
+    host["page_table"] = table.pin_memory()
+    host["pos"] = torch.tensor([c - 1 for c in ctx], dtype=torch.int32).pin_memory()
+    conv_w = torch.randn(sh["conv_w"], generator=cg) * 0.5
+    cache.set_conv_w(conv_w)
+    dev = {n: x.cuda() for n, x in host.items()}
+    dev["conv_w"] = conv_w.cuda()
+    stream = torch.cuda.current_stream()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---------------- device-resident timing ----------------
+    cache.set_timing(True)
+    for _ in range(max(3, args.warmup)):
+        cache.decode(dev, B)
+    _lib.check_device()
+    sync_all()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fam = {}
+    e0.record(stream)
+    for _ in range(args.steps):
+        cache.decode(dev, B)
+        for k, v in cache.timing().items():      # waits for this step's last event
+            fam[k] = fam.get(k, 0.0) + v
+    e1.record(stream)
+    sync_all()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    _lib.check_device()
+    cache.set_timing(False)
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    ms_per_step = ms_max / args.steps
+    value = B * world / (ms_per_step * 1e-3)
+
+    # ---------------- end to end through the host-buffer entry point ----------------
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            cache.decode_host(host, B)
+        sync_all()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            cache.decode_host(host, B)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        t = torch.tensor([dt], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        h2d = sum(host[n].numel() * host[n].element_size() for n in
+                  ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv", "delta_beta", "delta_g",
+                   "page_table", "pos"))
+        d2h = sum(host[n].numel() * host[n].element_size() for n in ("attn_o", "delta_o"))
+        e2e = {"value": B * world / (dt / args.steps), "unit": "seq-steps/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": dt / args.steps * 1e3}
+        _lib.check_device()
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        ab = algorithmic_bytes(args, ctx)
+        n_attn = cache.n_attn
+        attn_ms_per_launch = fam["attn_decode"] / args.steps / max(1, n_attn)
+        achieved = ab["attn_decode"] / (attn_ms_per_launch * 1e-3) / 1e9
+        families = {}
+        for k, nl in (("attn_decode", n_attn), ("attn_combine", n_attn), ("kv_append", n_attn),
+                      ("delta_rule", cache.n_delta), ("conv1d_update", cache.n_delta)):
+            per = fam[k] / args.steps / max(1, nl)
+            families[k] = {"ms_per_launch": round(per, 5), "share": round(fam[k] / args.steps / ms_per_step, 4)}
+            if k in ab:
+                families[k]["gbs"] = round(ab[k] / (per * 1e-3) / 1e9, 1) if per > 0 else None
+        line = {
+            "metric": "hybrid-layer decode steps/sec", "value": value, "unit": "seq-steps/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 KV / f32 state",
+            "data": "synthetic",
+            "config": {"workload": workload_name(args), "l2": "inputs larger than L2 (%.1f GB streamed per step)"
+                       % (ab["step"] / 1e9), "parallelism": "sequence-sharded x%d, no collective" % world,
+                       "ctx_tokens_rank0": sum(ctx), "cache_bytes_rank0": cache.bytes},
+            "clocks": clocks,
+            "gpu_launches": cache.launches_per_step * args.steps,
+            "step_hbm_gbs": ab["step"] * world / (ms_per_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_f16_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
+                         "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "fallback 6650 (of fallback)",
+                         "bytes_per_launch": ab["attn_decode"], "ms_per_launch": attn_ms_per_launch,
+                         "traffic": None},
+            "kernel_families": families,
+        }
+        if e2e:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_reference_leg(args, ctx)
+            line["cpu_baseline"] = cb
+        print(json.dumps(line), flush=True)
+    cache.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

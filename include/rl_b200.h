@@ -1,0 +1,281 @@
+/*
+ * rl_b200.h -- C ABI of the B200 (sm_100a) hybrid-attention operators.
+ *
+ * Drop-in surface for the attention / DeltaNet hot path of RapidLLM's qwen3_5
+ * engine.  Each entry point names the reference interface it replaces
+ * (paths relative to the RapidLLM tree).  Conventions follow the reference's C
+ * API (include/rapidllm/api.h:11-25, src/api/rapidllm_c.cpp:46-50): nothing
+ * throws across this boundary, every call returns an rl_status, and
+ * rl_last_error() gives the message of the last failure on the calling thread.
+ *
+ * Unless a name ends in _host, every pointer is a DEVICE pointer owned by the
+ * caller and `stream` is a cudaStream_t passed as void* (NULL = default
+ * stream).  Work is enqueued asynchronously; bad device-side data (a page id
+ * outside the pool, a slot outside the cache, a length beyond the page table)
+ * never faults: the kernel skips the access and records a code that
+ * rl_device_error() returns.
+ */
+#ifndef RL_B200_H
+#define RL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define RL_B200_ABI_VERSION 1
+
+/* Same values as RapidStatus, include/rapidllm/api.h:11-20. */
+typedef enum rl_status {
+    RL_OK = 0,
+    RL_ERR_IO,
+    RL_ERR_FORMAT,
+    RL_ERR_NOMEM,
+    RL_ERR_UNSUPPORTED,
+    RL_ERR_DEVICE,
+    RL_ERR_RANGE,
+    RL_ERR_INTERNAL
+} rl_status;
+
+/* KV cache element formats (the reference's --kv-type f16 | q8k_tq3v,
+ * src/cli/main.cpp:137-155). */
+enum { RL_KV_F16 = 0, RL_KV_Q8K_TQ3V = 1 };
+/* layer_types[] entries (LayerKind, include/rapidllm/ir/model_desc.h). */
+enum { RL_LAYER_LINEAR_ATTENTION = 0, RL_LAYER_FULL_ATTENTION = 1 };
+/* How DeltaNet value head h finds its key/query head
+ * (src/kernels/ops_fused.cpp:117-119, cuda_engine.cu:78-89). */
+enum { RL_HEADS_PER_VALUE = 0, RL_HEADS_GROUPED = 1, RL_HEADS_TILED = 2 };
+
+/* cuda_gen::available(), include/rapidllm/runtime/cuda_engine.h:11:
+ * 1 when a CUDA device of compute capability 10.x is present, else 0. */
+int rl_b200_available(void);
+int rl_b200_abi_version(void);
+/* Message of the last failing call on this thread (RapidError.message). */
+const char* rl_last_error(void);
+/* Synchronises `stream`, returns the device error word (0 = none; see
+ * rl_device_error_string) and clears it. */
+int rl_device_error(void* stream);
+const char* rl_device_error_string(int code);
+
+/* ------------------------------------------------------------------------- */
+/* Gated attention, decode                                                    */
+/* ------------------------------------------------------------------------- */
+
+/* AttnDecodeParams {n_q, n_kv, head_dim, seq, pos, kv_dtype, rms_eps}
+ * (include/rapidllm/backend/params.h:17) extended to a ragged batch on a paged
+ * cache: `seq`/`pos` become the device arrays passed to the call. */
+typedef struct rl_attn_decode_params {
+    int n_q, n_kv, head_dim;     /* 24, 4, 256; n_q/n_kv <= 8, head_dim must be 256 */
+    int kv_dtype;                /* RL_KV_F16 or RL_KV_Q8K_TQ3V */
+    int batch;                   /* sequences in this call */
+    int page_tokens;             /* must be 64 */
+    int n_pages;                 /* pages in the pool */
+    int max_pages_per_seq;       /* row stride of page_table */
+    int max_seq_len;             /* host-side upper bound of every seq_lens[b] + len_add (sizing only) */
+    int len_add;                 /* tokens attended = seq_lens[b] + len_add (1 when seq_lens holds `pos`) */
+    int chunk_pages;             /* pages per split-KV work item; 0 = choose */
+    int wht_len;                 /* TQ3 transform length: 128 (reference layout) or 256 */
+} rl_attn_decode_params;
+
+/* Bytes of scratch rl_attn_decode needs for these parameters. */
+size_t rl_attn_decode_workspace_bytes(const rl_attn_decode_params* p);
+
+/* ops::attn_decode (include/rapidllm/kernels/ops.h:130-131,
+ * src/kernels/ops.cpp:575-605) for every sequence of a batch, followed by the
+ * sigmoid output gate o *= sigmoid(gate) (src/kernels/ops_fused.cpp:178) when
+ * gate != NULL.  Replaces qk_attn_decode_gqa_k / flash_attn_decode_f16_hd256
+ * (src/kernels/cuda/cuda_engine.cu:5802-5862, 303-375).
+ *   k_pool, v_pool  F16: fp16 pools [n_pages][n_kv] of 64x256 slices in the tile
+ *                   format written by rl_kv_append (opaque; read back with
+ *                   rl_kv_gather).  Q8K_TQ3V: see rl_kv_compact_* below.
+ *   page_table      int32 [batch][max_pages_per_seq]
+ *   seq_lens        int32 [batch], device resident so a step can be graph-captured
+ *   q, gate, o      fp32 [batch][n_q][head_dim]; softmax scale 1/sqrt(head_dim) */
+int rl_attn_decode(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                   const int32_t* seq_lens, const float* q, const float* gate, float* o,
+                   void* workspace, size_t workspace_bytes, const rl_attn_decode_params* p,
+                   void* stream);
+
+/* Merge n_parts split-KV partials per row and apply the gate: the grid-level
+ * (and cross-GPU) form of the warp merge at cuda_engine.cu:347-374.
+ *   part_o  fp32 [n_parts][rows][256] unnormalised sums
+ *   part_ml fp32 [n_parts][rows][2]   (running max of scaled scores, sum of exp)
+ *   gate    fp32 [rows][256] or NULL;  o fp32 [rows][256] */
+int rl_lse_combine(const float* part_o, const float* part_ml, const float* gate, float* o,
+                   int n_parts, int rows, int head_dim, void* stream);
+
+/* Same as rl_attn_decode but stops before the merge across sequences' chunks
+ * is normalised: writes one partial (unnormalised o, max, sum) per
+ * (sequence, query head) so that partials of several GPUs holding different
+ * token ranges can be merged with rl_lse_combine.
+ *   part_o fp32 [batch][n_q][256], part_ml fp32 [batch][n_q][2] */
+int rl_attn_decode_partial(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                           const int32_t* seq_lens, const float* q, float* part_o, float* part_ml,
+                           void* workspace, size_t workspace_bytes,
+                           const rl_attn_decode_params* p, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* KV cache maintenance                                                       */
+/* ------------------------------------------------------------------------- */
+
+typedef struct rl_kv_append_params {
+    int n_kv, head_dim;          /* 4, 256 */
+    int batch;                   /* sequences */
+    int n_tok;                   /* rows per sequence in this call (1 for decode) */
+    int page_tokens, n_pages, max_pages_per_seq;
+    int pos0;                    /* first position when pos == NULL */
+    int rows_fp16;               /* 1: rows are fp16; 0: fp32, rounded to nearest even */
+} rl_kv_append_params;
+
+/* DualCache::append_kv (src/runtime/dual_cache.cpp:74-79) / store_kv_batch_h_k
+ * (cuda_engine.cu:8216-8221): write K and V rows [batch][n_tok][n_kv][256] of
+ * each sequence at positions pos[b] (device int32, or pos0 when NULL) + 0..n_tok-1. */
+int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const int32_t* pos,
+                 const void* k_rows, const void* v_rows, const rl_kv_append_params* p,
+                 void* stream);
+
+/* Read tokens [0, n_tok) of one sequence (its page-table row) of one pool back as
+ * contiguous fp16 [n_tok][n_kv][256] -- the reference's cache layout
+ * (src/runtime/dual_cache.cpp:49-60). */
+int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16, int n_tok,
+                 int n_kv, int head_dim, int n_pages, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Gated DeltaNet                                                             */
+/* ------------------------------------------------------------------------- */
+
+/* DeltaRecurrentParams {n_v, dk, dv, eps_l2} (params.h:20) + batch/slot fields. */
+typedef struct rl_delta_recurrent_params {
+    int n_v, dk, dv;             /* 48, 128, 128 (dk = dv = 128 required) */
+    float eps_l2;                /* 1e-6 */
+    int batch;                   /* sequences in this call */
+    int n_slots;                 /* state slots in S */
+    int n_qk;                    /* heads present in q and k */
+    int head_map;                /* RL_HEADS_*; PER_VALUE requires n_qk == n_v */
+    long long q_stride, k_stride, v_stride; /* floats between sequences; 0 = dense */
+} rl_delta_recurrent_params;
+
+/* ops::delta_recurrent_step (ops.h:126-128, src/kernels/ops.cpp:495-540) for a
+ * batch: S fp32 [n_slots][n_v][128][128] updated in place (FP32 in HBM, as
+ * DualCache keeps it, src/runtime/dual_cache.cpp:29-33); sequence b uses slot
+ * slot_ids[b] (or b when NULL).  q,k fp32 [batch][n_qk][128] are L2-normalised
+ * inside (q also scaled by 1/sqrt(dk)), v [batch][n_v][128], beta/g_log
+ * [batch][n_v], o [batch][n_v][128].  Replaces gdn_decode_t1_k
+ * (cuda_engine.cu:5166-5286). */
+int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const float* k,
+                       const float* v, const float* beta, const float* g_log, float* o,
+                       const rl_delta_recurrent_params* p, void* stream);
+
+/* Conv1dParams {dim, k, silu} (params.h:19) + batch/slot fields. */
+typedef struct rl_conv1d_params {
+    int dim, k, silu;            /* 10240, 4, 1 (silu must be 1) */
+    int batch, n_slots;
+} rl_conv1d_params;
+
+/* ops::conv1d_update (ops.h:121, src/kernels/ops.cpp:458-468): shift the
+ * [dim][k] window of each sequence's slot, append x, dot with w, SiLU.
+ * x,y fp32 [batch][dim]; w [dim][k]; state [n_slots][dim][k]. */
+int rl_conv1d_update(const float* x, const float* w, float* state, const int32_t* slot_ids,
+                     float* y, const rl_conv1d_params* p, void* stream);
+
+/* ops::conv1d_causal_prefill (ops.h:120, src/kernels/ops.cpp:443-456) over
+ * x,y fp32 [seq][dim].  state_io (NULL or [dim][k]) receives the window after
+ * the last row; when use_state_in != 0 it also supplies the rows before row 0
+ * (a later chunk of a chunked prefill). */
+int rl_conv1d_causal(const float* x, const float* w, float* y, float* state_io, int seq,
+                     const rl_conv1d_params* p, int use_state_in, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Caches and the layer_types[] dispatch                                      */
+/* ------------------------------------------------------------------------- */
+
+/* Device-side replacement of DualCache (include/rapidllm/runtime/dual_cache.h:
+ * 11-39): a paged KV pool per full-attention layer and, per linear-attention
+ * layer, the FP32 recurrent state and conv window of every sequence slot. */
+typedef struct rl_cache rl_cache;
+
+typedef struct rl_cache_config {
+    int n_layers;                /* length of layer_types */
+    const int* layer_types;      /* RL_LAYER_* per layer (ModelDesc.layers[i].kind) */
+    int n_q, n_kv, head_dim;     /* attention: 24, 4, 256 */
+    int kv_dtype;                /* RL_KV_F16 */
+    int page_tokens, n_pages;    /* 64, pool size shared by all attention layers */
+    int n_v, n_k, dk, dv;        /* DeltaNet: 48, 16, 128, 128 */
+    int conv_k;                  /* 4; conv_dim = 2*n_k*dk + n_v*dv */
+    int head_map;                /* RL_HEADS_GROUPED (HF) or RL_HEADS_TILED (GGUF) */
+    int n_slots;                 /* sequences that can hold DeltaNet state */
+    int max_batch, max_pages_per_seq, max_seq_len;
+} rl_cache_config;
+
+/* DualCache::DualCache (src/runtime/dual_cache.cpp:7-41): allocates and zeroes. */
+int rl_cache_create(const rl_cache_config* cfg, rl_cache** out);
+void rl_cache_destroy(rl_cache* c);
+size_t rl_cache_bytes(const rl_cache* c);
+/* DualCache::k_ptr / v_ptr / state_ptr / conv_ptr (dual_cache.cpp:49-70), by
+ * the index among layers of the same kind (ModelDesc::mixer_slot,
+ * src/ir/model_desc.cpp:12-22). */
+void* rl_cache_k_pool(rl_cache* c, int attn_index);
+void* rl_cache_v_pool(rl_cache* c, int attn_index);
+float* rl_cache_state(rl_cache* c, int delta_index);
+float* rl_cache_conv(rl_cache* c, int delta_index);
+/* DualCache::zero (dual_cache.cpp:43-47). */
+int rl_cache_zero(rl_cache* c, void* stream);
+
+/* Inputs of one decode step of the attention/DeltaNet-only stack.  Arrays are
+ * indexed by the layer's index among its kind, then by sequence. */
+typedef struct rl_stack_io {
+    const float* attn_q;         /* [n_attn][batch][n_q][256] */
+    const float* attn_gate;      /* [n_attn][batch][n_q][256] pre-activation */
+    const float* attn_k;         /* [n_attn][batch][n_kv][256] new K row (norm + RoPE applied) */
+    const float* attn_v;         /* [n_attn][batch][n_kv][256] */
+    float* attn_o;               /* [n_attn][batch][n_q][256] */
+    const float* delta_qkv;      /* [n_delta][batch][conv_dim] pre-conv q|k|v channels */
+    const float* delta_beta;     /* [n_delta][batch][n_v] */
+    const float* delta_g;        /* [n_delta][batch][n_v]  log decay */
+    float* delta_o;              /* [n_delta][batch][n_v][dv] */
+    const float* conv_w;         /* [n_delta][conv_dim][conv_k] (weights, read only) */
+    const int32_t* page_table;   /* [batch][max_pages_per_seq] */
+    const int32_t* pos;          /* [batch] position of the token being decoded */
+    const int32_t* slot_ids;     /* [batch] DeltaNet slot per sequence or NULL */
+    int batch;
+} rl_stack_io;
+
+/* One decode step over layer_types[]: the scheduler loop of
+ * Session::forward_hidden (src/runtime/session.cpp:325-411) / launch_decode_batch
+ * (cuda_engine.cu:18999-19106) restricted to the mixer operators.  Per
+ * full-attention layer: append K,V at pos, attend over pos+1 tokens, gate.
+ * Per linear-attention layer: conv1d_update on the q|k|v channels, then the
+ * delta rule.  All pointers in io are device pointers. */
+int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream);
+
+/* The same step for a caller that keeps its tensors in HOST memory (pinned for
+ * full speed): copies every input of io (host pointers) to staging buffers on
+ * the device, runs the step and copies attn_o / delta_o back, overlapping the
+ * copies with the layers on internal streams.  conv_w is taken from the last
+ * rl_stack_set_conv_w call.  Returns after the outputs are in host memory. */
+int rl_stack_decode_host(rl_cache* c, const rl_stack_io* host_io);
+/* Upload the conv weights [n_delta][conv_dim][conv_k] (host pointer) once. */
+int rl_stack_set_conv_w(rl_cache* c, const float* host_conv_w);
+/* Number of kernels rl_stack_decode enqueues for a batch of this cache's shape. */
+int rl_stack_launches_per_step(const rl_cache* c);
+/* Phase timing with CUDA events on the launching stream, the counterpart of the
+ * reference's RAPIDLLM_PF_PROFILE brackets (cuda_engine.cu:18362-18380,
+ * 18581-18589).  While enabled every rl_stack_decode[_host] records events
+ * between its kernels; rl_stack_timing waits for the last step and returns the
+ * summed milliseconds over the layers in ms[5]: [0] KV append, [1] split-KV
+ * decode kernel, [2] merge + gate, [3] conv1d update, [4] delta rule. */
+int rl_stack_set_timing(rl_cache* c, int enable);
+int rl_stack_timing(rl_cache* c, float* ms);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* RL_B200_H */

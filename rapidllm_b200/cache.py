@@ -1,0 +1,131 @@
+"""HybridCache: the device-side DualCache (paged F16 KV + FP32 DeltaNet state +
+conv windows) and the decode step over layer_types[], through rl_cache_* /
+rl_stack_* of the C ABI.  Mirrors rapidllm::DualCache
+(include/rapidllm/runtime/dual_cache.h:11-39) and the scheduler loop of
+Session::forward_hidden (src/runtime/session.cpp:325-411).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import CacheConfig, StackIO, check, lib
+
+QWEN35_LAYER_TYPES = [_lib.RL_LAYER_LINEAR_ATTENTION] * 3 + [_lib.RL_LAYER_FULL_ATTENTION]
+
+
+class _DevView:
+    """Zero-copy torch view of library-owned device memory."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr,
+                                         "data": (int(ptr), False), "version": 2}
+
+
+def _view(ptr, shape, dtype):
+    typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.int32: "<i4"}[dtype]
+    return torch.as_tensor(_DevView(ptr, shape, typestr), device="cuda")
+
+
+class HybridCache:
+    def __init__(self, layer_types, n_pages, n_slots, max_batch, max_pages_per_seq,
+                 max_seq_len=None, n_q=24, n_kv=4, head_dim=256, n_v=48, n_k=16, dk=128, dv=128,
+                 conv_k=4, head_map=_lib.RL_HEADS_GROUPED):
+        self.layer_types = list(layer_types)
+        self.n_attn = sum(1 for t in self.layer_types if t == _lib.RL_LAYER_FULL_ATTENTION)
+        self.n_delta = len(self.layer_types) - self.n_attn
+        self.n_q, self.n_kv, self.head_dim = n_q, n_kv, head_dim
+        self.n_v, self.n_k, self.dk, self.dv, self.conv_k = n_v, n_k, dk, dv, conv_k
+        self.conv_dim = 2 * n_k * dk + n_v * dv
+        self.n_pages, self.n_slots, self.max_batch = n_pages, n_slots, max_batch
+        self.max_pages_per_seq = max_pages_per_seq
+        self.max_seq_len = max_seq_len or max_pages_per_seq * 64
+        arr = (C.c_int * len(self.layer_types))(*self.layer_types)
+        cfg = CacheConfig(n_layers=len(self.layer_types), layer_types=arr, n_q=n_q, n_kv=n_kv,
+                          head_dim=head_dim, kv_dtype=_lib.RL_KV_F16, page_tokens=64,
+                          n_pages=n_pages, n_v=n_v, n_k=n_k, dk=dk, dv=dv, conv_k=conv_k,
+                          head_map=head_map, n_slots=n_slots, max_batch=max_batch,
+                          max_pages_per_seq=max_pages_per_seq, max_seq_len=self.max_seq_len)
+        h = C.c_void_p()
+        check(lib().rl_cache_create(C.byref(cfg), C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().rl_cache_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    @property
+    def bytes(self):
+        return lib().rl_cache_bytes(self._h)
+
+    def k_pool(self, i):
+        return _view(lib().rl_cache_k_pool(self._h, i), (self.n_pages, self.n_kv, 64 * 256), torch.float16)
+
+    def v_pool(self, i):
+        return _view(lib().rl_cache_v_pool(self._h, i), (self.n_pages, self.n_kv, 64 * 256), torch.float16)
+
+    def state(self, i):
+        return _view(lib().rl_cache_state(self._h, i), (self.n_slots, self.n_v, self.dk, self.dv), torch.float32)
+
+    def conv(self, i):
+        return _view(lib().rl_cache_conv(self._h, i), (self.n_slots, self.conv_dim, self.conv_k), torch.float32)
+
+    def zero(self):
+        check(lib().rl_cache_zero(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    @property
+    def launches_per_step(self):
+        return lib().rl_stack_launches_per_step(self._h)
+
+    def set_timing(self, enable: bool):
+        check(lib().rl_stack_set_timing(self._h, int(enable)))
+
+    def timing(self):
+        """ms of the last step per kernel family, summed over the layers."""
+        ms = (C.c_float * 5)()
+        check(lib().rl_stack_timing(self._h, ms))
+        return dict(zip(("kv_append", "attn_decode", "attn_combine", "conv1d_update", "delta_rule"),
+                        list(ms)))
+
+    def io_shapes(self, batch):
+        """Tensor name -> shape of one decode step's inputs and outputs."""
+        A, D, B = self.n_attn, self.n_delta, batch
+        return {"attn_q": (A, B, self.n_q, 256), "attn_gate": (A, B, self.n_q, 256),
+                "attn_k": (A, B, self.n_kv, 256), "attn_v": (A, B, self.n_kv, 256),
+                "attn_o": (A, B, self.n_q, 256), "delta_qkv": (D, B, self.conv_dim),
+                "delta_beta": (D, B, self.n_v), "delta_g": (D, B, self.n_v),
+                "delta_o": (D, B, self.n_v, self.dv), "conv_w": (D, self.conv_dim, self.conv_k),
+                "page_table": (B, self.max_pages_per_seq), "pos": (B,), "slot_ids": (B,)}
+
+    def _io(self, t, batch, cuda):
+        io = StackIO(batch=batch)
+        for name in ("attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta",
+                     "delta_g", "delta_o", "conv_w", "page_table", "pos", "slot_ids"):
+            x = t.get(name)
+            if x is None:
+                continue
+            if x.is_cuda != cuda or not x.is_contiguous():
+                raise _lib.RlError(6, f"{name}: need a contiguous {'CUDA' if cuda else 'host'} tensor")
+            want = torch.int32 if name in ("page_table", "pos", "slot_ids") else torch.float32
+            if x.dtype != want:
+                raise _lib.RlError(6, f"{name}: need dtype {want}")
+            setattr(io, name, x.data_ptr())
+        return io
+
+    def decode(self, tensors: dict, batch: int):
+        """One step over layer_types[] with device tensors (rl_stack_decode)."""
+        io = self._io(tensors, batch, True)
+        check(lib().rl_stack_decode(self._h, C.byref(io), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def set_conv_w(self, host_w: torch.Tensor):
+        check(lib().rl_stack_set_conv_w(self._h, C.c_void_p(host_w.data_ptr())))
+
+    def decode_host(self, tensors: dict, batch: int):
+        """One step with HOST tensors (pinned for speed): H2D, step, D2H (rl_stack_decode_host)."""
+        io = self._io(tensors, batch, False)
+        check(lib().rl_stack_decode_host(self._h, C.byref(io)))

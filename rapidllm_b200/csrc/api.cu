@@ -1,0 +1,766 @@
+// C ABI of the library (include/rl_b200.h): argument checks, launches, the
+// device-side cache object and the layer_types[] dispatch.  No exception and no
+// C++ type crosses this boundary.
+#include "../../include/rl_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(rl_status st, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return st;
+}
+
+#define RL_CUDA(call)                                                                    \
+    do {                                                                                 \
+        cudaError_t e_ = (call);                                                         \
+        if (e_ != cudaSuccess)                                                           \
+            return fail(e_ == cudaErrorMemoryAllocation ? RL_ERR_NOMEM : RL_ERR_DEVICE,  \
+                        "%s: %s", #call, cudaGetErrorString(e_));                        \
+    } while (0)
+
+__device__ int g_dev_err;   // device error word (one per device that loads the library)
+
+struct DevInfo {
+    bool ready = false;
+    int sms = 0;
+    int cc_major = 0;
+    int* err_ptr = nullptr;
+    bool attn_attr = false;
+};
+std::mutex g_mu;
+DevInfo g_dev[64];
+
+int dev_info(DevInfo** out) {
+    int dev = 0;
+    RL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RL_ERR_RANGE, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    DevInfo& d = g_dev[dev];
+    if (!d.ready) {
+        cudaDeviceProp prop;
+        RL_CUDA(cudaGetDeviceProperties(&prop, dev));
+        d.sms = prop.multiProcessorCount;
+        d.cc_major = prop.major;
+        if (prop.major != 10)
+            return fail(RL_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                        dev, prop.major, prop.minor);
+        RL_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.err_ptr), g_dev_err));
+        RL_CUDA(cudaMemset(d.err_ptr, 0, sizeof(int)));
+        RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::attn_decode_f16_smem_bytes())));
+        d.ready = true;
+    }
+    *out = &d;
+    return RL_OK;
+}
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- split-KV plan: a pure function of the parameters ----------------------------
+struct AttnPlan {
+    int chunk_pages, max_chunks, G;
+    size_t part_o_bytes, part_ml_bytes, total_bytes;
+};
+
+int attn_check(const rl_attn_decode_params* p) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->head_dim != rl::kHeadDim) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 256", p->head_dim);
+    if (p->page_tokens != rl::kPageTokens) return fail(RL_ERR_UNSUPPORTED, "page_tokens %d: only 64", p->page_tokens);
+    if (p->n_kv <= 0 || p->n_q <= 0 || p->n_q % p->n_kv != 0 || p->n_q / p->n_kv > 8)
+        return fail(RL_ERR_UNSUPPORTED, "n_q %d / n_kv %d: group must divide and be <= 8", p->n_q, p->n_kv);
+    if (p->batch < 0 || p->batch > rl::attn_decode_max_batch())
+        return fail(RL_ERR_RANGE, "batch %d outside [0, %d]", p->batch, rl::attn_decode_max_batch());
+    if (p->n_pages <= 0 || p->max_pages_per_seq <= 0) return fail(RL_ERR_RANGE, "empty page pool or table");
+    if (p->max_seq_len <= 0 || p->max_seq_len > p->max_pages_per_seq * p->page_tokens)
+        return fail(RL_ERR_RANGE, "max_seq_len %d outside (0, max_pages_per_seq*page_tokens]", p->max_seq_len);
+    if (p->kv_dtype != RL_KV_F16) return fail(RL_ERR_UNSUPPORTED, "kv_dtype %d not supported by this call", p->kv_dtype);
+    return RL_OK;
+}
+
+AttnPlan attn_plan(const rl_attn_decode_params* p, int sms) {
+    AttnPlan pl;
+    pl.G = p->n_q / p->n_kv;
+    const int pages_per_seq = ceil_div(p->max_seq_len, p->page_tokens);
+    int chunk = p->chunk_pages;
+    if (chunk <= 0) {
+        const long long page_heads = 1LL * (p->batch > 0 ? p->batch : 1) * pages_per_seq * p->n_kv;
+        const long long target = 24LL * (sms > 0 ? sms : 148);
+        chunk = int((page_heads + target - 1) / target);
+        if (chunk < 1) chunk = 1;
+        if (chunk > 64) chunk = 64;
+    }
+    pl.chunk_pages = chunk;
+    pl.max_chunks = (p->batch > 0 ? p->batch : 1) * ceil_div(pages_per_seq, chunk);
+    pl.part_o_bytes = align_up(size_t(pl.max_chunks) * p->n_kv * pl.G * rl::kHeadDim * sizeof(float), 256);
+    pl.part_ml_bytes = align_up(size_t(pl.max_chunks) * p->n_kv * pl.G * 2 * sizeof(float), 256);
+    pl.total_bytes = pl.part_o_bytes + pl.part_ml_bytes;
+    return pl;
+}
+
+int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                     const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
+                     void* workspace, size_t workspace_bytes, const rl_attn_decode_params* p, void* stream,
+                     cudaEvent_t after_main = nullptr) {
+    if (int st = attn_check(p)) return st;
+    if (p->batch == 0) return RL_OK;
+    if (!k_pool || !v_pool || !page_table || !seq_lens || !q || !o || !workspace)
+        return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    const AttnPlan pl = attn_plan(p, d->sms);
+    if (workspace_bytes < pl.total_bytes)
+        return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, pl.total_bytes);
+    if (reinterpret_cast<uintptr_t>(k_pool) % 128 || reinterpret_cast<uintptr_t>(v_pool) % 128 ||
+        reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(workspace) % 16)
+        return fail(RL_ERR_RANGE, "pools must be 128-byte aligned, q and workspace 16-byte aligned");
+    rl::AttnDecodeArgs a;
+    a.k_pool = static_cast<const __half*>(k_pool);
+    a.v_pool = static_cast<const __half*>(v_pool);
+    a.page_table = page_table;
+    a.seq_lens = seq_lens;
+    a.q = q;
+    a.part_o = static_cast<float*>(workspace);
+    a.part_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.part_o_bytes);
+    a.err = d->err_ptr;
+    a.batch = p->batch;
+    a.n_q = p->n_q;
+    a.n_kv = p->n_kv;
+    a.n_pages = p->n_pages;
+    a.max_pages_per_seq = p->max_pages_per_seq;
+    a.chunk_pages = pl.chunk_pages;
+    a.max_chunks = pl.max_chunks;
+    a.len_add = p->len_add;
+    a.scale = 1.f / sqrtf(float(p->head_dim));
+    const long long max_items = 1LL * pl.max_chunks * p->n_kv;
+    const int grid = int(max_items < d->sms ? max_items : d->sms);
+    rl::attn_decode_f16_kernel<<<grid, rl::attn_decode_f16_threads(), rl::attn_decode_f16_smem_bytes(),
+                                 as_stream(stream)>>>(a);
+    if (after_main) cudaEventRecord(after_main, as_stream(stream));
+    rl::AttnCombineArgs c;
+    c.part_o = a.part_o;
+    c.part_ml = a.part_ml;
+    c.seq_lens = seq_lens;
+    c.gate = gate;
+    c.o = o;
+    c.out_ml = out_ml;
+    c.batch = p->batch;
+    c.n_q = p->n_q;
+    c.n_kv = p->n_kv;
+    c.chunk_pages = pl.chunk_pages;
+    c.max_chunks = pl.max_chunks;
+    c.page_tokens = p->page_tokens;
+    c.len_add = p->len_add;
+    c.max_len = p->max_pages_per_seq * p->page_tokens;
+    rl::attn_combine_kernel<<<dim3(p->n_q, p->batch), 256, 0, as_stream(stream)>>>(c);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+}  // namespace
+
+// ======================================================================================
+struct rl_cache {
+    rl_cache_config cfg;
+    std::vector<int> types;
+    int n_attn = 0, n_delta = 0, conv_dim = 0;
+    size_t pool_elems = 0;          // halves per (layer, K or V) pool
+    __half* kv = nullptr;           // [n_attn][2][pool_elems]
+    float* S = nullptr;             // [n_delta][n_slots][n_v][dk][dv]
+    float* conv = nullptr;          // [n_delta][n_slots][conv_dim][conv_k]
+    float* mixed = nullptr;         // [max_batch][conv_dim] conv output of the layer in flight
+    void* attn_ws = nullptr;
+    size_t attn_ws_bytes = 0;
+    size_t bytes = 0;
+    // host-call staging
+    bool staging = false;
+    float *d_attn_q = nullptr, *d_attn_gate = nullptr, *d_attn_k = nullptr, *d_attn_v = nullptr,
+          *d_attn_o = nullptr, *d_delta_qkv = nullptr, *d_delta_beta = nullptr, *d_delta_g = nullptr,
+          *d_delta_o = nullptr, *d_conv_w = nullptr;
+    int32_t *d_page_table = nullptr, *d_pos = nullptr, *d_slot_ids = nullptr;
+    cudaStream_t s_h2d = nullptr, s_run = nullptr, s_d2h = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_out;
+    // optional per-kernel timing of the last step (rl_stack_set_timing)
+    bool timing = false;
+    std::vector<cudaEvent_t> tev;   // 4 per layer: boundaries between the layer's kernels
+    int tev_used = 0;
+    rl_attn_decode_params attn_params(int batch) const {
+        rl_attn_decode_params p;
+        std::memset(&p, 0, sizeof p);
+        p.n_q = cfg.n_q;
+        p.n_kv = cfg.n_kv;
+        p.head_dim = cfg.head_dim;
+        p.kv_dtype = cfg.kv_dtype;
+        p.batch = batch;
+        p.page_tokens = cfg.page_tokens;
+        p.n_pages = cfg.n_pages;
+        p.max_pages_per_seq = cfg.max_pages_per_seq;
+        p.max_seq_len = cfg.max_seq_len;
+        p.len_add = 1;
+        p.chunk_pages = 0;
+        return p;
+    }
+};
+
+namespace {
+
+template <class T>
+int dev_alloc(T** p, size_t n, size_t* total) {
+    *p = nullptr;
+    if (n == 0) return RL_OK;
+    RL_CUDA(cudaMalloc(reinterpret_cast<void**>(p), n * sizeof(T)));
+    *total += n * sizeof(T);
+    return RL_OK;
+}
+
+int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bool host_mode) {
+    const rl_cache_config& f = c->cfg;
+    const int B = io->batch;
+    const size_t q_sz = size_t(B) * f.n_q * f.head_dim, kv_sz = size_t(B) * f.n_kv * f.head_dim;
+    const size_t qkv_sz = size_t(B) * c->conv_dim, hv_sz = size_t(B) * f.n_v, do_sz = size_t(B) * f.n_v * f.dv;
+    const size_t st_elems = size_t(f.n_slots) * f.n_v * f.dk * f.dv;
+    const size_t cv_elems = size_t(f.n_slots) * c->conv_dim * f.conv_k;
+    int ai = 0, di = 0;
+    const bool tm = c->timing && !c->tev.empty();
+    auto mark = [&](int L, int i) {
+        if (tm) cudaEventRecord(c->tev[size_t(L) * 4 + i], run);
+    };
+    for (int L = 0; L < f.n_layers; ++L) {
+        if (host_mode) RL_CUDA(cudaStreamWaitEvent(run, c->ev_in[L], 0));
+        mark(L, 0);
+        if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
+            rl_kv_append_params ap;
+            ap.n_kv = f.n_kv;
+            ap.head_dim = f.head_dim;
+            ap.batch = B;
+            ap.n_tok = 1;
+            ap.page_tokens = f.page_tokens;
+            ap.n_pages = f.n_pages;
+            ap.max_pages_per_seq = f.max_pages_per_seq;
+            ap.pos0 = 0;
+            ap.rows_fp16 = 0;
+            void* kp = rl_cache_k_pool(c, ai);
+            void* vp = rl_cache_v_pool(c, ai);
+            if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
+                                      io->attn_v + ai * kv_sz, &ap, run))
+                return st;
+            mark(L, 1);
+            const rl_attn_decode_params dp = c->attn_params(B);
+            if (int st = attn_decode_impl(kp, vp, io->page_table, io->pos, io->attn_q + ai * q_sz,
+                                          io->attn_gate ? io->attn_gate + ai * q_sz : nullptr,
+                                          io->attn_o + ai * q_sz, nullptr, c->attn_ws, c->attn_ws_bytes, &dp,
+                                          run, tm ? c->tev[size_t(L) * 4 + 3] : nullptr))
+                return st;
+            mark(L, 2);
+            ++ai;
+        } else {
+            rl_conv1d_params cp;
+            cp.dim = c->conv_dim;
+            cp.k = f.conv_k;
+            cp.silu = 1;
+            cp.batch = B;
+            cp.n_slots = f.n_slots;
+            if (int st = rl_conv1d_update(io->delta_qkv + di * qkv_sz,
+                                          io->conv_w + size_t(di) * c->conv_dim * f.conv_k,
+                                          c->conv + di * cv_elems, io->slot_ids, c->mixed, &cp, run))
+                return st;
+            mark(L, 1);
+            rl_delta_recurrent_params rp;
+            rp.n_v = f.n_v;
+            rp.dk = f.dk;
+            rp.dv = f.dv;
+            rp.eps_l2 = 1e-6f;
+            rp.batch = B;
+            rp.n_slots = f.n_slots;
+            rp.n_qk = f.n_k;
+            rp.head_map = f.head_map;
+            rp.q_stride = rp.k_stride = rp.v_stride = c->conv_dim;
+            const float* mq = c->mixed;
+            const float* mk = c->mixed + size_t(f.n_k) * f.dk;
+            const float* mv = c->mixed + 2 * size_t(f.n_k) * f.dk;
+            if (int st = rl_delta_recurrent(c->S + di * st_elems, io->slot_ids, mq, mk, mv,
+                                            io->delta_beta + di * hv_sz, io->delta_g + di * hv_sz,
+                                            io->delta_o + di * do_sz, &rp, run))
+                return st;
+            mark(L, 2);
+            ++di;
+        }
+        if (host_mode) RL_CUDA(cudaEventRecord(c->ev_out[L], run));
+    }
+    return RL_OK;
+}
+
+}  // namespace
+
+// ======================================================================================
+extern "C" {
+
+int rl_b200_abi_version(void) { return RL_B200_ABI_VERSION; }
+
+int rl_b200_available(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return 0;
+    }
+    int dev = 0;
+    cudaDeviceProp prop;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return 0;
+    return prop.major == 10 ? 1 : 0;
+}
+
+const char* rl_last_error(void) { return g_err; }
+
+const char* rl_device_error_string(int code) {
+    switch (code) {
+        case rl::DEV_OK: return "ok";
+        case rl::DEV_ERR_BAD_PAGE: return "page-table entry outside the pool";
+        case rl::DEV_ERR_WAIT_TIMEOUT: return "a bounded barrier wait gave up";
+        case rl::DEV_ERR_WORKSPACE: return "more split-KV chunks than the workspace holds";
+        case rl::DEV_ERR_BAD_SLOT: return "state slot outside the cache";
+        case rl::DEV_ERR_BAD_LEN: return "sequence length or position outside the page table";
+        default: return "unknown device error";
+    }
+}
+
+int rl_device_error(void* stream) {
+    DevInfo* d;
+    if (dev_info(&d)) return -1;
+    int code = 0;
+    if (cudaStreamSynchronize(as_stream(stream)) != cudaSuccess ||
+        cudaMemcpy(&code, d->err_ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        fail(RL_ERR_DEVICE, "reading the device error word: %s", cudaGetErrorString(cudaGetLastError()));
+        return -1;
+    }
+    if (code) cudaMemset(d->err_ptr, 0, sizeof(int));
+    return code;
+}
+
+size_t rl_attn_decode_workspace_bytes(const rl_attn_decode_params* p) {
+    if (attn_check(p)) return 0;
+    DevInfo* d;
+    int sms = 148;
+    if (dev_info(&d) == RL_OK) sms = d->sms;
+    return attn_plan(p, sms).total_bytes;
+}
+
+int rl_attn_decode(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                   const int32_t* seq_lens, const float* q, const float* gate, float* o, void* workspace,
+                   size_t workspace_bytes, const rl_attn_decode_params* p, void* stream) {
+    return attn_decode_impl(k_pool, v_pool, page_table, seq_lens, q, gate, o, nullptr, workspace,
+                            workspace_bytes, p, stream);
+}
+
+int rl_attn_decode_partial(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                           const int32_t* seq_lens, const float* q, float* part_o, float* part_ml,
+                           void* workspace, size_t workspace_bytes, const rl_attn_decode_params* p,
+                           void* stream) {
+    if (!part_ml) return fail(RL_ERR_RANGE, "part_ml is NULL");
+    return attn_decode_impl(k_pool, v_pool, page_table, seq_lens, q, nullptr, part_o, part_ml, workspace,
+                            workspace_bytes, p, stream);
+}
+
+int rl_lse_combine(const float* part_o, const float* part_ml, const float* gate, float* o, int n_parts,
+                   int rows, int head_dim, void* stream) {
+    if (head_dim != rl::kHeadDim) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 256", head_dim);
+    if (n_parts <= 0 || rows < 0) return fail(RL_ERR_RANGE, "n_parts %d rows %d", n_parts, rows);
+    if (rows == 0) return RL_OK;
+    if (!part_o || !part_ml || !o) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    rl::lse_combine_kernel<<<rows, 256, 0, as_stream(stream)>>>(part_o, part_ml, gate, o, n_parts, rows);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const int32_t* pos,
+                 const void* k_rows, const void* v_rows, const rl_kv_append_params* p, void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->head_dim != rl::kHeadDim || p->page_tokens != rl::kPageTokens)
+        return fail(RL_ERR_UNSUPPORTED, "head_dim %d / page_tokens %d: only 256 / 64", p->head_dim, p->page_tokens);
+    if (p->batch < 0 || p->n_tok < 0 || p->n_kv <= 0 || p->n_kv > 65535 || p->batch > 65535)
+        return fail(RL_ERR_RANGE, "batch %d n_tok %d n_kv %d", p->batch, p->n_tok, p->n_kv);
+    if (p->batch == 0 || p->n_tok == 0) return RL_OK;
+    if (!k_pool || !v_pool || !page_table || !k_rows || !v_rows) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::KvWriteArgs a;
+    a.k_pool = static_cast<__half*>(k_pool);
+    a.v_pool = static_cast<__half*>(v_pool);
+    a.page_table = page_table;
+    a.pos = pos;
+    a.k_rows = k_rows;
+    a.v_rows = v_rows;
+    a.err = d->err_ptr;
+    a.batch = p->batch;
+    a.n_tok = p->n_tok;
+    a.n_kv = p->n_kv;
+    a.n_pages = p->n_pages;
+    a.max_pages_per_seq = p->max_pages_per_seq;
+    a.pos0 = p->pos0;
+    a.rows_fp16 = p->rows_fp16;
+    rl::kv_write_kernel<<<dim3(p->n_tok, p->n_kv, p->batch), 32, 0, as_stream(stream)>>>(a);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16, int n_tok, int n_kv,
+                 int head_dim, int n_pages, void* stream) {
+    if (head_dim != rl::kHeadDim) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 256", head_dim);
+    if (n_tok < 0 || n_kv <= 0 || n_kv > 65535) return fail(RL_ERR_RANGE, "n_tok %d n_kv %d", n_tok, n_kv);
+    if (n_tok == 0) return RL_OK;
+    if (!pool || !page_table_row || !out_f16) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::kv_gather_kernel<<<dim3(n_tok, n_kv), 32, 0, as_stream(stream)>>>(
+        static_cast<const __half*>(pool), page_table_row, static_cast<__half*>(out_f16), n_tok, n_kv, n_pages,
+        d->err_ptr);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const float* k, const float* v,
+                       const float* beta, const float* g_log, float* o, const rl_delta_recurrent_params* p,
+                       void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->dk != 128 || p->dv != 128) return fail(RL_ERR_UNSUPPORTED, "dk %d dv %d: only 128 x 128", p->dk, p->dv);
+    if (p->n_v <= 0 || p->n_v > 65535 || p->batch < 0 || p->batch > 65535 || p->n_slots <= 0)
+        return fail(RL_ERR_RANGE, "n_v %d batch %d n_slots %d", p->n_v, p->batch, p->n_slots);
+    if (p->head_map == RL_HEADS_PER_VALUE ? p->n_qk != p->n_v
+                                          : (p->n_qk <= 0 || p->n_v % p->n_qk != 0 || p->head_map > RL_HEADS_TILED))
+        return fail(RL_ERR_RANGE, "n_qk %d does not fit n_v %d with head_map %d", p->n_qk, p->n_v, p->head_map);
+    if (p->batch == 0) return RL_OK;
+    if (!S || !q || !k || !v || !beta || !g_log || !o) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::DeltaDecodeArgs a;
+    a.S = S;
+    a.slot_ids = slot_ids;
+    a.q = q;
+    a.k = k;
+    a.v = v;
+    a.beta = beta;
+    a.g_log = g_log;
+    a.o = o;
+    a.err = d->err_ptr;
+    a.batch = p->batch;
+    a.n_v = p->n_v;
+    a.n_qk = p->n_qk;
+    a.n_slots = p->n_slots;
+    a.head_map = p->head_map;
+    a.eps_l2 = p->eps_l2;
+    a.q_stride = p->q_stride ? p->q_stride : 1LL * p->n_qk * p->dk;
+    a.k_stride = p->k_stride ? p->k_stride : 1LL * p->n_qk * p->dk;
+    a.v_stride = p->v_stride ? p->v_stride : 1LL * p->n_v * p->dv;
+    if ((a.q_stride | a.k_stride | a.v_stride) % 4 || reinterpret_cast<uintptr_t>(q) % 16 ||
+        reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16 ||
+        reinterpret_cast<uintptr_t>(S) % 16)
+        return fail(RL_ERR_RANGE, "S, q, k, v must be 16-byte aligned with strides a multiple of 4 floats");
+    rl::launch_delta_decode(a, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_conv1d_update(const float* x, const float* w, float* state, const int32_t* slot_ids, float* y,
+                     const rl_conv1d_params* p, void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (!p->silu) return fail(RL_ERR_UNSUPPORTED, "conv1d without SiLU is not on this path");
+    if (p->dim <= 0 || p->k < 1 || p->k > 8 || p->batch < 0 || p->batch > 65535 || p->n_slots <= 0)
+        return fail(RL_ERR_RANGE, "dim %d k %d batch %d n_slots %d", p->dim, p->k, p->batch, p->n_slots);
+    if (p->batch == 0) return RL_OK;
+    if (!x || !w || !state || !y) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::ConvUpdateArgs a;
+    a.x = x;
+    a.w = w;
+    a.state = state;
+    a.slot_ids = slot_ids;
+    a.y = y;
+    a.err = d->err_ptr;
+    a.batch = p->batch;
+    a.dim = p->dim;
+    a.k = p->k;
+    a.n_slots = p->n_slots;
+    if (p->k == 4 && (reinterpret_cast<uintptr_t>(w) % 16 || reinterpret_cast<uintptr_t>(state) % 16))
+        return fail(RL_ERR_RANGE, "w and state must be 16-byte aligned");
+    rl::launch_conv1d_update(a, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_conv1d_causal(const float* x, const float* w, float* y, float* state_io, int seq,
+                     const rl_conv1d_params* p, int use_state_in, void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (!p->silu) return fail(RL_ERR_UNSUPPORTED, "conv1d without SiLU is not on this path");
+    if (p->dim <= 0 || p->k < 1 || p->k > 8 || seq < 0) return fail(RL_ERR_RANGE, "dim %d k %d seq %d", p->dim, p->k, seq);
+    if (seq == 0) return RL_OK;
+    if (!x || !w || !y) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    rl::launch_conv1d_prefill(x, w, y, state_io, seq, p->dim, p->k, use_state_in, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+// ------------------------------------------------------------------------------------
+int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
+    if (!cfg || !out) return fail(RL_ERR_RANGE, "NULL argument");
+    *out = nullptr;
+    if (cfg->n_layers <= 0 || !cfg->layer_types) return fail(RL_ERR_RANGE, "no layers");
+    if (cfg->head_dim != rl::kHeadDim || cfg->page_tokens != rl::kPageTokens || cfg->dk != 128 || cfg->dv != 128)
+        return fail(RL_ERR_UNSUPPORTED, "shapes: head_dim 256, page_tokens 64, dk = dv = 128 only");
+    if (cfg->kv_dtype != RL_KV_F16) return fail(RL_ERR_UNSUPPORTED, "rl_cache holds F16 KV only");
+    if (cfg->n_slots <= 0 || cfg->max_batch <= 0 || cfg->n_pages <= 0 || cfg->max_pages_per_seq <= 0 ||
+        cfg->n_k <= 0 || cfg->n_v % cfg->n_k)
+        return fail(RL_ERR_RANGE, "bad cache sizes");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl_cache* c = new (std::nothrow) rl_cache();
+    if (!c) return fail(RL_ERR_NOMEM, "host allocation failed");
+    c->cfg = *cfg;
+    c->types.assign(cfg->layer_types, cfg->layer_types + cfg->n_layers);
+    c->cfg.layer_types = c->types.data();
+    for (int t : c->types) (t == RL_LAYER_FULL_ATTENTION ? c->n_attn : c->n_delta)++;
+    c->conv_dim = 2 * cfg->n_k * cfg->dk + cfg->n_v * cfg->dv;
+    c->pool_elems = size_t(cfg->n_pages) * cfg->n_kv * rl::kv_slice_elems();
+    const rl_attn_decode_params ap = c->attn_params(cfg->max_batch);
+    if (int st = attn_check(&ap)) {
+        delete c;
+        return st;
+    }
+    c->attn_ws_bytes = attn_plan(&ap, d->sms).total_bytes;
+    int st = RL_OK;
+    if (!st) st = dev_alloc(&c->kv, size_t(c->n_attn) * 2 * c->pool_elems, &c->bytes);
+    if (!st) st = dev_alloc(&c->S, size_t(c->n_delta) * cfg->n_slots * cfg->n_v * cfg->dk * cfg->dv, &c->bytes);
+    if (!st) st = dev_alloc(&c->conv, size_t(c->n_delta) * cfg->n_slots * c->conv_dim * cfg->conv_k, &c->bytes);
+    if (!st) st = dev_alloc(&c->mixed, size_t(cfg->max_batch) * c->conv_dim, &c->bytes);
+    if (!st) {
+        char* ws = nullptr;
+        st = dev_alloc(&ws, c->attn_ws_bytes, &c->bytes);
+        c->attn_ws = ws;
+    }
+    if (!st) st = rl_cache_zero(c, nullptr);
+    if (!st && cudaDeviceSynchronize() != cudaSuccess) st = fail(RL_ERR_DEVICE, "zeroing the cache failed");
+    if (st) {
+        rl_cache_destroy(c);
+        return st;
+    }
+    *out = c;
+    return RL_OK;
+}
+
+void rl_cache_destroy(rl_cache* c) {
+    if (!c) return;
+    void* ptrs[] = {c->kv, c->S, c->conv, c->mixed, c->attn_ws, c->d_attn_q, c->d_attn_gate, c->d_attn_k,
+                    c->d_attn_v, c->d_attn_o, c->d_delta_qkv, c->d_delta_beta, c->d_delta_g, c->d_delta_o,
+                    c->d_conv_w, c->d_page_table, c->d_pos, c->d_slot_ids};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    for (cudaEvent_t e : c->ev_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : c->ev_out) cudaEventDestroy(e);
+    for (cudaEvent_t e : c->tev) cudaEventDestroy(e);
+    if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
+    if (c->s_run) cudaStreamDestroy(c->s_run);
+    if (c->s_d2h) cudaStreamDestroy(c->s_d2h);
+    delete c;
+}
+
+size_t rl_cache_bytes(const rl_cache* c) { return c ? c->bytes : 0; }
+void* rl_cache_k_pool(rl_cache* c, int i) {
+    return (c && i >= 0 && i < c->n_attn) ? c->kv + (size_t(i) * 2) * c->pool_elems : nullptr;
+}
+void* rl_cache_v_pool(rl_cache* c, int i) {
+    return (c && i >= 0 && i < c->n_attn) ? c->kv + (size_t(i) * 2 + 1) * c->pool_elems : nullptr;
+}
+float* rl_cache_state(rl_cache* c, int i) {
+    return (c && i >= 0 && i < c->n_delta)
+               ? c->S + size_t(i) * c->cfg.n_slots * c->cfg.n_v * c->cfg.dk * c->cfg.dv : nullptr;
+}
+float* rl_cache_conv(rl_cache* c, int i) {
+    return (c && i >= 0 && i < c->n_delta)
+               ? c->conv + size_t(i) * c->cfg.n_slots * c->conv_dim * c->cfg.conv_k : nullptr;
+}
+
+int rl_cache_zero(rl_cache* c, void* stream) {
+    if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
+    const rl_cache_config& f = c->cfg;
+    if (c->kv) RL_CUDA(cudaMemsetAsync(c->kv, 0, size_t(c->n_attn) * 2 * c->pool_elems * sizeof(__half), as_stream(stream)));
+    if (c->S) RL_CUDA(cudaMemsetAsync(c->S, 0, size_t(c->n_delta) * f.n_slots * f.n_v * f.dk * f.dv * sizeof(float), as_stream(stream)));
+    if (c->conv) RL_CUDA(cudaMemsetAsync(c->conv, 0, size_t(c->n_delta) * f.n_slots * c->conv_dim * f.conv_k * sizeof(float), as_stream(stream)));
+    return RL_OK;
+}
+
+int rl_stack_set_timing(rl_cache* c, int enable) {
+    if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
+    if (enable && c->tev.empty()) {
+        c->tev.resize(size_t(c->cfg.n_layers) * 4);
+        for (auto& e : c->tev) RL_CUDA(cudaEventCreate(&e));
+    }
+    c->timing = enable != 0;
+    return RL_OK;
+}
+
+int rl_stack_timing(rl_cache* c, float* ms) {
+    if (!c || !ms) return fail(RL_ERR_RANGE, "NULL argument");
+    if (c->tev.empty()) return fail(RL_ERR_RANGE, "timing was never enabled");
+    for (int i = 0; i < 5; ++i) ms[i] = 0.f;
+    RL_CUDA(cudaEventSynchronize(c->tev[size_t(c->cfg.n_layers - 1) * 4 + 2]));
+    for (int L = 0; L < c->cfg.n_layers; ++L) {
+        float a = 0.f, b = 0.f;
+        RL_CUDA(cudaEventElapsedTime(&a, c->tev[size_t(L) * 4], c->tev[size_t(L) * 4 + 1]));
+        RL_CUDA(cudaEventElapsedTime(&b, c->tev[size_t(L) * 4 + 1], c->tev[size_t(L) * 4 + 2]));
+        if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
+            float m = 0.f;
+            RL_CUDA(cudaEventElapsedTime(&m, c->tev[size_t(L) * 4 + 1], c->tev[size_t(L) * 4 + 3]));
+            ms[0] += a;       // KV append
+            ms[1] += m;       // split-KV decode kernel
+            ms[2] += b - m;   // merge + gate
+        } else {
+            ms[3] += a;       // conv1d update
+            ms[4] += b;       // delta rule
+        }
+    }
+    return RL_OK;
+}
+
+int rl_stack_launches_per_step(const rl_cache* c) { return c ? c->n_attn * 3 + c->n_delta * 2 : 0; }
+
+int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
+    if (!c || !io) return fail(RL_ERR_RANGE, "NULL argument");
+    if (io->batch < 0 || io->batch > c->cfg.max_batch)
+        return fail(RL_ERR_RANGE, "batch %d outside [0, max_batch %d]", io->batch, c->cfg.max_batch);
+    if (io->batch == 0) return RL_OK;
+    if ((c->n_attn && (!io->attn_q || !io->attn_k || !io->attn_v || !io->attn_o || !io->page_table || !io->pos)) ||
+        (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
+        return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    return stack_decode_layers(c, io, as_stream(stream), false);
+}
+
+static int ensure_staging(rl_cache* c) {
+    if (c->staging) return RL_OK;
+    const rl_cache_config& f = c->cfg;
+    const size_t B = f.max_batch;
+    size_t unused = 0;
+    int st = RL_OK;
+    const size_t q_sz = size_t(c->n_attn) * B * f.n_q * f.head_dim, kv_sz = size_t(c->n_attn) * B * f.n_kv * f.head_dim;
+    if (!st) st = dev_alloc(&c->d_attn_q, q_sz, &unused);
+    if (!st) st = dev_alloc(&c->d_attn_gate, q_sz, &unused);
+    if (!st) st = dev_alloc(&c->d_attn_o, q_sz, &unused);
+    if (!st) st = dev_alloc(&c->d_attn_k, kv_sz, &unused);
+    if (!st) st = dev_alloc(&c->d_attn_v, kv_sz, &unused);
+    if (!st) st = dev_alloc(&c->d_delta_qkv, size_t(c->n_delta) * B * c->conv_dim, &unused);
+    if (!st) st = dev_alloc(&c->d_delta_beta, size_t(c->n_delta) * B * f.n_v, &unused);
+    if (!st) st = dev_alloc(&c->d_delta_g, size_t(c->n_delta) * B * f.n_v, &unused);
+    if (!st) st = dev_alloc(&c->d_delta_o, size_t(c->n_delta) * B * f.n_v * f.dv, &unused);
+    if (!st && !c->d_conv_w) st = dev_alloc(&c->d_conv_w, size_t(c->n_delta) * c->conv_dim * f.conv_k, &unused);
+    if (!st) st = dev_alloc(&c->d_page_table, B * f.max_pages_per_seq, &unused);
+    if (!st) st = dev_alloc(&c->d_pos, B, &unused);
+    if (!st) st = dev_alloc(&c->d_slot_ids, B, &unused);
+    if (st) return st;
+    c->bytes += unused;
+    RL_CUDA(cudaStreamCreateWithFlags(&c->s_h2d, cudaStreamNonBlocking));
+    RL_CUDA(cudaStreamCreateWithFlags(&c->s_run, cudaStreamNonBlocking));
+    RL_CUDA(cudaStreamCreateWithFlags(&c->s_d2h, cudaStreamNonBlocking));
+    c->ev_in.resize(f.n_layers);
+    c->ev_out.resize(f.n_layers);
+    for (int i = 0; i < f.n_layers; ++i) {
+        RL_CUDA(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming));
+        RL_CUDA(cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming));
+    }
+    c->staging = true;
+    return RL_OK;
+}
+
+int rl_stack_set_conv_w(rl_cache* c, const float* host_conv_w) {
+    if (!c || !host_conv_w) return fail(RL_ERR_RANGE, "NULL argument");
+    const size_t n = size_t(c->n_delta) * c->conv_dim * c->cfg.conv_k;
+    if (!c->d_conv_w) {
+        size_t t = 0;
+        if (int st = dev_alloc(&c->d_conv_w, n, &t)) return st;
+        c->bytes += t;
+    }
+    RL_CUDA(cudaMemcpy(c->d_conv_w, host_conv_w, n * sizeof(float), cudaMemcpyHostToDevice));
+    return RL_OK;
+}
+
+int rl_stack_decode_host(rl_cache* c, const rl_stack_io* h) {
+    if (!c || !h) return fail(RL_ERR_RANGE, "NULL argument");
+    if (h->batch < 0 || h->batch > c->cfg.max_batch)
+        return fail(RL_ERR_RANGE, "batch %d outside [0, max_batch %d]", h->batch, c->cfg.max_batch);
+    if (h->batch == 0) return RL_OK;
+    if ((c->n_attn && (!h->attn_q || !h->attn_k || !h->attn_v || !h->attn_o || !h->page_table || !h->pos)) ||
+        (c->n_delta && (!h->delta_qkv || !h->delta_beta || !h->delta_g || !h->delta_o)))
+        return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    if (c->n_delta && !c->d_conv_w) return fail(RL_ERR_RANGE, "call rl_stack_set_conv_w first");
+    if (int st = ensure_staging(c)) return st;
+    const rl_cache_config& f = c->cfg;
+    const size_t B = h->batch;
+    const size_t q_sz = B * f.n_q * f.head_dim, kv_sz = B * f.n_kv * f.head_dim;
+    const size_t qkv_sz = B * c->conv_dim, hv_sz = B * f.n_v, do_sz = B * f.n_v * f.dv;
+    const cudaMemcpyKind H2D = cudaMemcpyHostToDevice, D2H = cudaMemcpyDeviceToHost;
+    RL_CUDA(cudaMemcpyAsync(c->d_page_table, h->page_table, B * f.max_pages_per_seq * sizeof(int32_t), H2D, c->s_h2d));
+    RL_CUDA(cudaMemcpyAsync(c->d_pos, h->pos, B * sizeof(int32_t), H2D, c->s_h2d));
+    if (h->slot_ids) RL_CUDA(cudaMemcpyAsync(c->d_slot_ids, h->slot_ids, B * sizeof(int32_t), H2D, c->s_h2d));
+    int ai = 0, di = 0;
+    for (int L = 0; L < f.n_layers; ++L) {
+        if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
+            RL_CUDA(cudaMemcpyAsync(c->d_attn_q + ai * q_sz, h->attn_q + ai * q_sz, q_sz * 4, H2D, c->s_h2d));
+            if (h->attn_gate)
+                RL_CUDA(cudaMemcpyAsync(c->d_attn_gate + ai * q_sz, h->attn_gate + ai * q_sz, q_sz * 4, H2D, c->s_h2d));
+            RL_CUDA(cudaMemcpyAsync(c->d_attn_k + ai * kv_sz, h->attn_k + ai * kv_sz, kv_sz * 4, H2D, c->s_h2d));
+            RL_CUDA(cudaMemcpyAsync(c->d_attn_v + ai * kv_sz, h->attn_v + ai * kv_sz, kv_sz * 4, H2D, c->s_h2d));
+            ++ai;
+        } else {
+            RL_CUDA(cudaMemcpyAsync(c->d_delta_qkv + di * qkv_sz, h->delta_qkv + di * qkv_sz, qkv_sz * 4, H2D, c->s_h2d));
+            RL_CUDA(cudaMemcpyAsync(c->d_delta_beta + di * hv_sz, h->delta_beta + di * hv_sz, hv_sz * 4, H2D, c->s_h2d));
+            RL_CUDA(cudaMemcpyAsync(c->d_delta_g + di * hv_sz, h->delta_g + di * hv_sz, hv_sz * 4, H2D, c->s_h2d));
+            ++di;
+        }
+        RL_CUDA(cudaEventRecord(c->ev_in[L], c->s_h2d));
+    }
+    rl_stack_io d = *h;
+    d.attn_q = c->d_attn_q;
+    d.attn_gate = h->attn_gate ? c->d_attn_gate : nullptr;
+    d.attn_k = c->d_attn_k;
+    d.attn_v = c->d_attn_v;
+    d.attn_o = c->d_attn_o;
+    d.delta_qkv = c->d_delta_qkv;
+    d.delta_beta = c->d_delta_beta;
+    d.delta_g = c->d_delta_g;
+    d.delta_o = c->d_delta_o;
+    d.conv_w = c->d_conv_w;
+    d.page_table = c->d_page_table;
+    d.pos = c->d_pos;
+    d.slot_ids = h->slot_ids ? c->d_slot_ids : nullptr;
+    if (int st = stack_decode_layers(c, &d, c->s_run, true)) return st;
+    ai = di = 0;
+    for (int L = 0; L < f.n_layers; ++L) {
+        RL_CUDA(cudaStreamWaitEvent(c->s_d2h, c->ev_out[L], 0));
+        if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
+            RL_CUDA(cudaMemcpyAsync(h->attn_o + ai * q_sz, c->d_attn_o + ai * q_sz, q_sz * 4, D2H, c->s_d2h));
+            ++ai;
+        } else {
+            RL_CUDA(cudaMemcpyAsync(h->delta_o + di * do_sz, c->d_delta_o + di * do_sz, do_sz * 4, D2H, c->s_d2h));
+            ++di;
+        }
+    }
+    RL_CUDA(cudaStreamSynchronize(c->s_d2h));
+    RL_CUDA(cudaStreamSynchronize(c->s_run));
+    return RL_OK;
+}
+
+}  // extern "C"

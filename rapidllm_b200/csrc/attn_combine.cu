@@ -1,0 +1,90 @@
+// Log-sum-exp merge of split-KV partials, fused with the sigmoid output gate.
+//
+// Generalises the reference's merge of its 8 warp partials
+// (src/kernels/cuda/cuda_engine.cu:347-374) to grid-level chunks and, through
+// lse_combine_kernel, to partials gathered from other GPUs.  The gate is
+// o *= sigmoid(gate) (src/kernels/ops_fused.cpp:178, cuda_engine.cu:6229-6232).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rl {
+
+__global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
+    const int hq = blockIdx.x;
+    const int b = blockIdx.y;
+    const int G = a.n_q / a.n_kv;
+    const int h = hq / G, gi = hq - h * G;
+    const int d = threadIdx.x;
+    __shared__ int red[8];
+    __shared__ int s_prefix;
+    // chunks of the sequences before b
+    int mine = 0;
+    for (int bb = d; bb < b; bb += 256) {
+        int len = a.seq_lens[bb] + a.len_add;
+        if (len < 0 || len > a.max_len) len = 0;
+        const int pages = (len + a.page_tokens - 1) / a.page_tokens;
+        mine += (pages + a.chunk_pages - 1) / a.chunk_pages;
+    }
+    for (int off = 16; off > 0; off >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, off);
+    if ((d & 31) == 0) red[d >> 5] = mine;
+    __syncthreads();
+    if (d == 0) {
+        int t = 0;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        s_prefix = t;
+    }
+    __syncthreads();
+    const int prefix = s_prefix;
+    int len = a.seq_lens[b] + a.len_add;
+    if (len < 0 || len > a.max_len) len = 0;
+    const int pages = (len + a.page_tokens - 1) / a.page_tokens;
+    int n_chunks = (pages + a.chunk_pages - 1) / a.chunk_pages;
+    if (prefix + n_chunks > a.max_chunks) n_chunks = max(0, a.max_chunks - prefix);
+
+    float mm = -1e30f;
+    for (int c = 0; c < n_chunks; ++c) {
+        const size_t row = (size_t(prefix + c) * a.n_kv + h) * G + gi;
+        mm = fmaxf(mm, a.part_ml[row * 2]);
+    }
+    float acc = 0.f, l = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        const size_t row = (size_t(prefix + c) * a.n_kv + h) * G + gi;
+        const float al = expf(a.part_ml[row * 2] - mm);
+        l += a.part_ml[row * 2 + 1] * al;
+        acc += a.part_o[row * kHeadDim + d] * al;
+    }
+    const size_t oi = (size_t(b) * a.n_q + hq) * kHeadDim + d;
+    if (a.out_ml) {
+        a.o[oi] = acc;
+        if (d == 0) {
+            a.out_ml[(size_t(b) * a.n_q + hq) * 2] = mm;
+            a.out_ml[(size_t(b) * a.n_q + hq) * 2 + 1] = l;
+        }
+        return;
+    }
+    float out = l > 0.f ? acc / l : 0.f;
+    if (a.gate) out *= 1.f / (1.f + expf(-a.gate[oi]));
+    a.o[oi] = out;
+}
+
+__global__ void __launch_bounds__(256)
+lse_combine_kernel(const float* part_o, const float* part_ml, const float* gate, float* o,
+                   int n_parts, int rows) {
+    const int row = blockIdx.x;
+    const int d = threadIdx.x;
+    float mm = -1e30f;
+    for (int p = 0; p < n_parts; ++p) mm = fmaxf(mm, part_ml[(size_t(p) * rows + row) * 2]);
+    float acc = 0.f, l = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+        const size_t r = size_t(p) * rows + row;
+        const float al = expf(part_ml[r * 2] - mm);
+        l += part_ml[r * 2 + 1] * al;
+        acc += part_o[r * kHeadDim + d] * al;
+    }
+    float out = l > 0.f ? acc / l : 0.f;
+    const size_t oi = size_t(row) * kHeadDim + d;
+    if (gate) out *= 1.f / (1.f + expf(-gate[oi]));
+    o[oi] = out;
+}
+
+}  // namespace rl

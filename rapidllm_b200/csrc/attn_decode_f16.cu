@@ -1,0 +1,375 @@
+// Split-KV GQA decode attention over the paged F16 KV cache (sm_100a).
+//
+// Replaces the reference's one-block-per-head context walk
+// (src/kernels/cuda/cuda_engine.cu:303-375 flash_attn_decode_f16_hd256, called
+// from qk_attn_decode_gqa_k 5802-5862) and computes what ops::attn_decode
+// (src/kernels/ops.cpp:575-605) computes, for a batch of ragged sequences.
+//
+// Structure: a persistent grid (one CTA per SM).  Work items are
+// (sequence, chunk of pages, KV head), all the same size, dealt round-robin.
+// One producer warp streams half pages (32 tokens of K and of V, 32 KiB) into a
+// ring of shared-memory stages with TMA bulk copies that complete on
+// mbarriers; it runs ahead across item boundaries so the HBM stream never
+// drains.  Six consumer warps (three pairs, one pair per stage in flight) each
+// own 16 tokens of a stage: scores for the whole GQA group (<= 8 query heads)
+// come from m16n8k16 tensor-core MMAs with the fp32 query split into an fp16
+// high part (MMA rows 0-7) and its fp16 residual (rows 8-15, otherwise idle), the
+// online softmax runs in registers, and P.V accumulates transposed (dims x
+// heads) so that P feeds the second MMA straight from the score registers.  At
+// the end of an item the warps' (m, l, acc) merge in shared memory into one
+// partial per (item, head); attn_combine.cu merges the items and applies the
+// sigmoid gate.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rl {
+
+namespace {
+
+constexpr int kStageTokens = 32;                 // half a page
+constexpr int kStages = 6;
+constexpr int kSlots = 3;                        // consumer warp pairs
+constexpr int kConsumerWarps = kSlots * 2;
+// 6 consumer warps + 1 producer warp + 1 idle warp: 256 threads lets every thread have 255 registers
+constexpr int kThreads = 256;
+constexpr int kSubTiles = kHeadDim / 64;         // 4
+constexpr int kStageKBytes = kStageTokens * kHeadDim * 2;  // 16 KiB
+constexpr int kStageBytes = 2 * kStageKBytes;              // K + V
+constexpr int kSubTileStageBytes = kStageTokens * 128;     // 4 KiB
+constexpr int kSubTilePageBytes = kPageTokens * 128;       // 8 KiB
+constexpr int kMaxBatch = 1024;
+constexpr float kNegBig = -1e30f;
+constexpr int kMergeStride = kHeadDim + 1;
+
+struct Smem {
+    alignas(128) unsigned char stage[kStages][kStageBytes];
+    float o[8][kMergeStride];       // item merge buffer (row stride 257: conflict-free adds)
+    float m[kConsumerWarps][8];
+    float l[kConsumerWarps][8];
+    int prefix[kMaxBatch + 1];      // chunks before sequence b
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+};
+
+struct Item {
+    int b, h, first_tok, n_tok;     // tokens [first_tok, first_tok+n_tok) of sequence b
+    int page0;                      // first page index (in the sequence's table)
+};
+
+__device__ __forceinline__ Item decode_item(const Smem& s, int item, int batch, int n_kv,
+                                            int chunk_pages, const int32_t* seq_lens, int len_add) {
+    Item it;
+    const int ci = item / n_kv;
+    it.h = item - ci * n_kv;
+    int lo = 0, hi = batch;         // largest b with prefix[b] <= ci
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s.prefix[mid] <= ci) lo = mid; else hi = mid;
+    }
+    it.b = lo;
+    const int c = ci - s.prefix[lo];
+    it.page0 = c * chunk_pages;
+    it.first_tok = it.page0 * kPageTokens;
+    const int len = seq_lens[lo] + len_add;
+    int end = it.first_tok + chunk_pages * kPageTokens;
+    if (end > len) end = len;
+    it.n_tok = end - it.first_tok;
+    return it;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_decode_f16_kernel(AttnDecodeArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int G = a.n_q / a.n_kv;
+
+    // chunk prefix over the batch (every CTA computes the same table)
+    if (warp == 0) {
+        int run = 0;
+        for (int b0 = 0; b0 < a.batch; b0 += 32) {
+            const int b = b0 + lane;
+            int n = 0;
+            if (b < a.batch) {
+                int len = a.seq_lens[b] + a.len_add;
+                if (len < 0 || len > a.max_pages_per_seq * kPageTokens) {
+                    set_err(a.err, DEV_ERR_BAD_LEN);
+                    len = 0;
+                }
+                const int pages = (len + kPageTokens - 1) / kPageTokens;
+                n = (pages + a.chunk_pages - 1) / a.chunk_pages;
+            }
+            int inc = n;
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += t;
+            }
+            if (b < a.batch) s.prefix[b] = run + inc - n;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) {
+            s.prefix[a.batch] = run;
+            if (run > a.max_chunks) set_err(a.err, DEV_ERR_WORKSPACE);
+        }
+    }
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], 2);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    int total_chunks = s.prefix[a.batch];
+    if (total_chunks > a.max_chunks) total_chunks = a.max_chunks;
+    const int total_items = total_chunks * a.n_kv;
+
+    if (warp > kConsumerWarps) return;
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer ------------------------------
+        if (lane != 0) return;
+        uint32_t it = 0;
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            const Item w = decode_item(s, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
+            const int n_half = (w.n_tok + kStageTokens - 1) / kStageTokens;
+            for (int hp = 0; hp < n_half; ++hp, ++it) {
+                const int st = it % kStages;
+                const uint32_t ph = (it / kStages) & 1;
+                if (!mbar_wait(&s.empty[st], ph ^ 1)) {
+                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                    return;
+                }
+                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + w.page0 + (hp >> 1)];
+                if (page < 0 || page >= a.n_pages) {
+                    set_err(a.err, DEV_ERR_BAD_PAGE);
+                    page = 0;
+                }
+                const size_t slice = (size_t(page) * a.n_kv + w.h) * kv_slice_elems();
+                const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(a.k_pool + slice) +
+                                            (hp & 1) * kSubTileStageBytes;
+                const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(a.v_pool + slice) +
+                                            (hp & 1) * kSubTileStageBytes;
+                unsigned char* dst = s.stage[st];
+                mbar_arrive_expect_tx(&s.full[st], kStageBytes);
+#pragma unroll
+                for (int sub = 0; sub < kSubTiles; ++sub) {
+                    bulk_g2s(dst + sub * kSubTileStageBytes, ksrc + sub * kSubTilePageBytes,
+                             kSubTileStageBytes, &s.full[st]);
+                    bulk_g2s(dst + kStageKBytes + sub * kSubTileStageBytes,
+                             vsrc + sub * kSubTilePageBytes, kSubTileStageBytes, &s.full[st]);
+                }
+            }
+        }
+        return;
+    }
+
+    // -------------------------------- consumers --------------------------------
+    const int g = lane >> 2;                       // MMA group id: query head / token column
+    const int c = lane & 3;
+    const int pg = ((g & 1) << 2) | (g >> 1);      // bank-conflict-free permutation of 0..7
+    const int slot = warp >> 1;
+    const int tb = (warp & 1) * 16;                // this warp's tokens inside a stage
+    const float scale_log2 = a.scale * 1.4426950408889634f;
+
+    uint32_t it = 0;
+    bool alive = true;   // false after a wait gave up: keep arriving at barriers, touch no data
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        const Item w = decode_item(s, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
+        const int n_half = (w.n_tok + kStageTokens - 1) / kStageTokens;
+
+        // query fragments: rows 0-7 fp16(q), rows 8-15 fp16(q - fp16(q))
+        uint32_t qhi[8][4], qlo[8][4];
+        {
+            const bool live = g < G;
+            const float* qp = a.q + (size_t(w.b) * a.n_q + w.h * G + (live ? g : 0)) * kHeadDim;
+#pragma unroll
+            for (int L = 0; L < 8; ++L) {
+                float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+                if (live) {
+                    x0 = *reinterpret_cast<const float4*>(qp + 32 * L + 8 * c);
+                    x1 = *reinterpret_cast<const float4*>(qp + 32 * L + 8 * c + 4);
+                }
+                const float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __half h0 = __float2half_rn(v[2 * e]);
+                    const __half h1 = __float2half_rn(v[2 * e + 1]);
+                    const __half2 hh = __halves2half2(h0, h1);
+                    qhi[L][e] = *reinterpret_cast<const uint32_t*>(&hh);
+                    qlo[L][e] = pack_h2(v[2 * e] - __half2float(h0), v[2 * e + 1] - __half2float(h1));
+                }
+            }
+        }
+
+        float acc[4][4][4];                          // [sub-tile j][pair i][c0..c3]
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[j][i][e] = 0.f;
+        float m_run = kNegBig;                       // log2 domain, head g
+        float l_run = 0.f;                           // this lane's share of the row sum
+
+        for (int hp = 0; hp < n_half; ++hp, ++it) {
+            if (int(it % kSlots) != slot) continue;
+            const int st = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            if (alive && !mbar_wait(&s.full[st], ph)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                alive = false;
+            }
+            const int n_valid = min(kStageTokens, w.n_tok - hp * kStageTokens) - tb;  // in this warp's 16
+            if (alive && n_valid > 0) {
+                const unsigned char* kst = s.stage[st];
+                unsigned char* vst = s.stage[st] + kStageKBytes;
+                if (n_valid < 16) {
+                    // rows past the end of the sequence may hold anything: clear V
+                    for (int r = tb + n_valid; r < tb + 16; ++r)
+                        for (int x = lane; x < kSubTiles * 8; x += 32)
+                            *reinterpret_cast<uint4*>(vst + (x >> 3) * kSubTileStageBytes + r * 128 +
+                                                      (x & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                }
+                // ---- scores: S[heads][16 tokens], two n-tiles, two chains each ----
+                float sc[2][2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int z = 0; z < 2; ++z)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sc[nt][z][e] = 0.f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int r = tb + 8 * nt + pg;
+                    const unsigned char* rowp = kst + r * 128;
+#pragma unroll
+                    for (int L = 0; L < 8; ++L) {
+                        const int chunk = (4 * (L & 1) + c) ^ (r & 7);
+                        const uint4 kk = *reinterpret_cast<const uint4*>(
+                            rowp + (L >> 1) * kSubTileStageBytes + chunk * 16);
+                        mma_f16(sc[nt][0], qhi[L][0], qlo[L][0], qhi[L][1], qlo[L][1], kk.x, kk.y);
+                        mma_f16(sc[nt][1], qhi[L][2], qlo[L][2], qhi[L][3], qlo[L][3], kk.z, kk.w);
+                    }
+                }
+                // ---- online softmax (columns: tokens tb+c, tb+4+c, tb+8+c, tb+12+c) ----
+                float p[4];
+                float mx = kNegBig;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float sv = (sc[nt][0][e] + sc[nt][1][e]) + (sc[nt][0][e + 2] + sc[nt][1][e + 2]);
+                        const int tok = 8 * nt + 4 * e + c;
+                        p[nt * 2 + e] = tok < n_valid ? sv * scale_log2 : kNegBig;
+                        mx = fmaxf(mx, p[nt * 2 + e]);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run, mx);
+                if (__any_sync(0xffffffffu, m_new > m_run)) {
+                    const float alpha = fast_exp2(m_run - m_new);
+                    l_run *= alpha;
+                    const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * c);
+                    const float a1 = __shfl_sync(0xffffffffu, alpha, 8 * c + 4);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            acc[j][i][0] *= a0;
+                            acc[j][i][1] *= a1;
+                            acc[j][i][2] *= a0;
+                            acc[j][i][3] *= a1;
+                        }
+                    m_run = m_new;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = p[e] > 0.5f * kNegBig ? fast_exp2(p[e] - m_run) : 0.f;
+                    l_run += p[e];
+                }
+                const uint32_t pb0 = pack_h2(p[0], p[1]);   // tokens tb+c, tb+4+c
+                const uint32_t pb1 = pack_h2(p[2], p[3]);   // tokens tb+8+c, tb+12+c
+                // ---- acc[dims][heads] += V^T P^T ----
+                const int r0 = tb + c, r1 = tb + 4 + c, r8 = tb + 8 + c, r9 = tb + 12 + c;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned char* sub = vst + j * kSubTileStageBytes;
+                    const uint4 v0 = *reinterpret_cast<const uint4*>(sub + r0 * 128 + ((pg ^ (r0 & 7)) << 4));
+                    const uint4 v1 = *reinterpret_cast<const uint4*>(sub + r1 * 128 + ((pg ^ (r1 & 7)) << 4));
+                    const uint4 v8 = *reinterpret_cast<const uint4*>(sub + r8 * 128 + ((pg ^ (r8 & 7)) << 4));
+                    const uint4 v9 = *reinterpret_cast<const uint4*>(sub + r9 * 128 + ((pg ^ (r9 & 7)) << 4));
+                    const uint32_t x0[4] = {v0.x, v0.y, v0.z, v0.w};
+                    const uint32_t x1[4] = {v1.x, v1.y, v1.z, v1.w};
+                    const uint32_t x8[4] = {v8.x, v8.y, v8.z, v8.w};
+                    const uint32_t x9[4] = {v9.x, v9.y, v9.z, v9.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        mma_f16(acc[j][i], __byte_perm(x0[i], x1[i], 0x5410),
+                                __byte_perm(x0[i], x1[i], 0x7632), __byte_perm(x8[i], x9[i], 0x5410),
+                                __byte_perm(x8[i], x9[i], 0x7632), pb0, pb1);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.empty[st]);
+        }
+
+        // ------------------------ merge the warps of this item ------------------------
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        if (c == 0) {
+            s.m[warp][g] = m_run;
+            s.l[warp][g] = l_run;
+        }
+        for (int x = tid; x < 8 * kMergeStride; x += kConsumerWarps * 32) (&s.o[0][0])[x] = 0.f;
+        named_bar_sync(1, kConsumerWarps * 32);
+        float f[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float mm = kNegBig;
+#pragma unroll
+            for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
+            f[e] = fast_exp2(s.m[warp][2 * c + e] - mm);
+        }
+        if (__any_sync(0xffffffffu, l_run > 0.f)) {
+            // lanes with pg >= 4 add the odd dim first so that a warp's 32 adds hit 32 banks
+            const int odd = pg >> 2;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int d = 64 * j + 8 * pg + 2 * i;
+                    atomicAdd(&s.o[2 * c][d + odd], (odd ? acc[j][i][2] : acc[j][i][0]) * f[0]);
+                    atomicAdd(&s.o[2 * c][d + 1 - odd], (odd ? acc[j][i][0] : acc[j][i][2]) * f[0]);
+                    atomicAdd(&s.o[2 * c + 1][d + odd], (odd ? acc[j][i][3] : acc[j][i][1]) * f[1]);
+                    atomicAdd(&s.o[2 * c + 1][d + 1 - odd], (odd ? acc[j][i][1] : acc[j][i][3]) * f[1]);
+                }
+        }
+        named_bar_sync(1, kConsumerWarps * 32);
+        {
+            float* po = a.part_o + size_t(item) * G * kHeadDim;
+            for (int x = tid; x < G * kHeadDim; x += kConsumerWarps * 32)
+                po[x] = s.o[x >> 8][x & (kHeadDim - 1)];
+            if (tid < G) {
+                float mm = kNegBig;
+                for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][tid]);
+                float ll = 0.f;
+                for (int ww = 0; ww < kConsumerWarps; ++ww) ll += s.l[ww][tid] * fast_exp2(s.m[ww][tid] - mm);
+                a.part_ml[(size_t(item) * G + tid) * 2 + 0] = mm * 0.6931471805599453f;  // natural-log units
+                a.part_ml[(size_t(item) * G + tid) * 2 + 1] = ll;
+            }
+        }
+        named_bar_sync(1, kConsumerWarps * 32);
+    }
+}
+
+size_t attn_decode_f16_smem_bytes() { return sizeof(Smem) + 128; }
+int attn_decode_f16_threads() { return kThreads; }
+int attn_decode_max_batch() { return kMaxBatch; }
+
+}  // namespace rl

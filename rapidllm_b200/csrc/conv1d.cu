@@ -1,0 +1,120 @@
+// Depthwise causal conv1d (k taps, oldest first) + SiLU for the DeltaNet q/k/v
+// channels: the decode form keeps a [dim][k] fp32 window per sequence
+// (ops::conv1d_update, src/kernels/ops.cpp:458-468) and the prefill form walks
+// a [seq][dim] block (ops::conv1d_causal_prefill, 443-456).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rl {
+
+namespace {
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
+
+// k == 4: one channel per thread, window as one float4.
+__global__ void __launch_bounds__(256) conv1d_update4_kernel(ConvUpdateArgs a) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= a.dim) return;
+    const int slot = a.slot_ids ? a.slot_ids[b] : b;
+    if (slot < 0 || slot >= a.n_slots) {
+        set_err(a.err, DEV_ERR_BAD_SLOT);
+        return;
+    }
+    float4* st = reinterpret_cast<float4*>(a.state + (size_t(slot) * a.dim + c) * 4);
+    const float4 old = *st;
+    const float4 w = *reinterpret_cast<const float4*>(a.w + size_t(c) * 4);
+    const float4 nw = make_float4(old.y, old.z, old.w, a.x[size_t(b) * a.dim + c]);
+    *st = nw;
+    // double accumulator, taps in order, as the reference does
+    double acc = double(w.x) * nw.x;
+    acc += double(w.y) * nw.y;
+    acc += double(w.z) * nw.z;
+    acc += double(w.w) * nw.w;
+    a.y[size_t(b) * a.dim + c] = silu(float(acc));
+}
+
+__global__ void __launch_bounds__(256) conv1d_update_generic_kernel(ConvUpdateArgs a) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= a.dim) return;
+    const int slot = a.slot_ids ? a.slot_ids[b] : b;
+    if (slot < 0 || slot >= a.n_slots) {
+        set_err(a.err, DEV_ERR_BAD_SLOT);
+        return;
+    }
+    float* st = a.state + (size_t(slot) * a.dim + c) * a.k;
+    double acc = 0.0;
+    for (int p = 0; p < a.k - 1; ++p) {
+        const float t = st[p + 1];
+        st[p] = t;
+        acc += double(a.w[size_t(c) * a.k + p]) * t;
+    }
+    const float xn = a.x[size_t(b) * a.dim + c];
+    st[a.k - 1] = xn;
+    acc += double(a.w[size_t(c) * a.k + a.k - 1]) * xn;
+    a.y[size_t(b) * a.dim + c] = silu(float(acc));
+}
+
+// Prefill: thread = channel, walks a tile of time steps with the window in
+// registers (k <= 8).  grid (ceil(dim/256), ceil(seq/tile)).
+constexpr int kMaxTaps = 8;
+__global__ void __launch_bounds__(256)
+conv1d_prefill_kernel(const float* x, const float* w, float* y, const float* state_in, int seq,
+                      int dim, int k, int tile) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= dim) return;
+    const int t0 = blockIdx.y * tile;
+    const int t1 = min(seq, t0 + tile);
+    float win[kMaxTaps], wt[kMaxTaps];
+    for (int p = 0; p < k; ++p) wt[p] = w[size_t(c) * k + p];
+    // window before t0: inputs t0-k+1 .. t0-1 (index p = 0..k-2), from x, state_in or zero
+    for (int p = 0; p < k - 1; ++p) {
+        const int src = t0 - (k - 1) + p;
+        float v = 0.f;
+        if (src >= 0) v = x[size_t(src) * dim + c];
+        else if (state_in) v = state_in[size_t(c) * k + (k + src)];   // src = -1 -> newest tap k-1
+        win[p + 1] = v;
+    }
+    for (int t = t0; t < t1; ++t) {
+        for (int p = 0; p < k - 1; ++p) win[p] = win[p + 1];
+        win[k - 1] = x[size_t(t) * dim + c];
+        double acc = 0.0;
+        for (int p = 0; p < k; ++p) acc += double(wt[p]) * win[p];
+        y[size_t(t) * dim + c] = silu(float(acc));
+    }
+}
+
+__global__ void __launch_bounds__(256)
+conv1d_state_tail_kernel(const float* x, float* state_io, int seq, int dim, int k, int use_state_in) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= dim) return;
+    float old[kMaxTaps];
+    for (int p = 0; p < k; ++p) old[p] = use_state_in ? state_io[size_t(c) * k + p] : 0.f;
+    for (int p = 0; p < k; ++p) {
+        const int src = seq - k + p;   // input index that ends at tap p
+        state_io[size_t(c) * k + p] = src >= 0 ? x[size_t(src) * dim + c] : old[p + seq < k ? p + seq : k - 1];
+    }
+}
+
+}  // namespace
+
+void launch_conv1d_update(const ConvUpdateArgs& a, cudaStream_t st) {
+    if (a.batch <= 0 || a.dim <= 0) return;
+    dim3 grid((a.dim + 255) / 256, a.batch);
+    if (a.k == 4) conv1d_update4_kernel<<<grid, 256, 0, st>>>(a);
+    else conv1d_update_generic_kernel<<<grid, 256, 0, st>>>(a);
+}
+
+void launch_conv1d_prefill(const float* x, const float* w, float* y, float* state_io, int seq,
+                           int dim, int k, int use_state_in, cudaStream_t st) {
+    if (seq <= 0 || dim <= 0) return;
+    const int tile = 64;
+    dim3 grid((dim + 255) / 256, (seq + tile - 1) / tile);
+    conv1d_prefill_kernel<<<grid, 256, 0, st>>>(x, w, y, (use_state_in && state_io) ? state_io : nullptr,
+                                                seq, dim, k, tile);
+    if (state_io)
+        conv1d_state_tail_kernel<<<(dim + 255) / 256, 256, 0, st>>>(x, state_io, seq, dim, k, use_state_in);
+}
+
+}  // namespace rl

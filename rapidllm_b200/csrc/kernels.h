@@ -1,0 +1,101 @@
+// Launch-side declarations shared by the kernels and the C ABI (api.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace rl {
+
+// ---- decode attention over the paged F16 cache ------------------------------
+struct AttnDecodeArgs {
+    const __half* k_pool;        // [n_pages][n_kv] slices, see kv_slice_offset()
+    const __half* v_pool;
+    const int32_t* page_table;   // [batch][max_pages_per_seq]
+    const int32_t* seq_lens;     // [batch] device resident; tokens attended = seq_lens[b] + len_add
+    const float* q;              // [batch][n_q][256]
+    float* part_o;               // [max_chunks*n_kv][G][256] unnormalised partial outputs
+    float* part_ml;              // [max_chunks*n_kv][G][2]   (max in natural-log units, sum)
+    int* err;                    // device error word
+    int batch, n_q, n_kv, n_pages, max_pages_per_seq;
+    int chunk_pages;             // pages per work item
+    int max_chunks;              // workspace capacity in chunks (all sequences together)
+    int len_add;
+    float scale;                 // 1/sqrt(head_dim)
+};
+__global__ void attn_decode_f16_kernel(AttnDecodeArgs a);
+size_t attn_decode_f16_smem_bytes();
+int attn_decode_f16_threads();
+int attn_decode_max_batch();
+
+// ---- merge of split-KV partials + sigmoid gate -----------------------------------
+struct AttnCombineArgs {
+    const float* part_o;
+    const float* part_ml;
+    const int32_t* seq_lens;
+    const float* gate;           // [batch][n_q][256] pre-activation, may be null
+    float* o;                    // [batch][n_q][256]; unnormalised when out_ml != null
+    float* out_ml;               // null, or [batch][n_q][2] (max, sum): emit one partial per row
+    int batch, n_q, n_kv, chunk_pages, max_chunks, page_tokens, len_add;
+    int max_len;                 // lengths outside [0, max_len] count as 0, as in the decode kernel
+};
+__global__ void attn_combine_kernel(AttnCombineArgs a);
+
+// Generic merge of n_parts partials per row (used across GPUs):
+// part_o [n_parts][rows][256], part_ml [n_parts][rows][2]
+__global__ void lse_combine_kernel(const float* part_o, const float* part_ml, const float* gate,
+                                   float* o, int n_parts, int rows);
+
+// ---- KV cache maintenance ------------------------------------------------------------
+// Write rows [n_tok][n_kv][256] (fp32 or fp16) of sequence b at positions pos0.. into the pool.
+struct KvWriteArgs {
+    __half* k_pool;
+    __half* v_pool;
+    const int32_t* page_table;   // [batch][max_pages_per_seq]
+    const int32_t* pos;          // [batch] device positions (decode append) or null
+    const void* k_rows;          // [batch][n_tok][n_kv][256]
+    const void* v_rows;
+    int* err;
+    int batch, n_tok, n_kv, n_pages, max_pages_per_seq;
+    int pos0;                    // used when pos == null
+    int rows_fp16;               // 1: rows are fp16, 0: fp32 (rounded to nearest even)
+};
+__global__ void kv_write_kernel(KvWriteArgs a);
+// Read tokens [0, n_tok) of one sequence back as contiguous fp16 [n_tok][n_kv][256].
+__global__ void kv_gather_kernel(const __half* pool, const int32_t* table, __half* out, int n_tok,
+                                 int n_kv, int n_pages, int* err);
+
+// ---- Gated DeltaNet decode step ----------------------------------------------------
+struct DeltaDecodeArgs {
+    float* S;                    // [n_slots][n_v][128][128] fp32 recurrent state
+    const int32_t* slot_ids;     // [batch] state slot of each sequence, or null (slot = b)
+    const float* q;              // [batch][n_qk][128]
+    const float* k;              // [batch][n_qk][128]
+    const float* v;              // [batch][n_v][128]
+    const float* beta;           // [batch][n_v]
+    const float* g_log;          // [batch][n_v]
+    float* o;                    // [batch][n_v][128]
+    int* err;
+    int batch, n_v, n_qk, n_slots;
+    int head_map;                // 0: q/k given per value head; 1: grouped h/(n_v/n_qk); 2: tiled h%n_qk
+    float eps_l2;
+    long long q_stride, k_stride, v_stride;   // floats between sequences
+};
+void launch_delta_decode(const DeltaDecodeArgs& a, cudaStream_t st);
+
+// ---- causal depthwise conv1d + SiLU ------------------------------------------------
+struct ConvUpdateArgs {
+    const float* x;              // [batch][dim]
+    const float* w;              // [dim][k]
+    float* state;                // [n_slots][dim][k]
+    const int32_t* slot_ids;     // may be null
+    float* y;                    // [batch][dim]
+    int* err;
+    int batch, dim, k, n_slots;
+};
+void launch_conv1d_update(const ConvUpdateArgs& a, cudaStream_t st);
+// x,y [seq][dim]; state_out (may be null) receives the last k inputs [dim][k]
+void launch_conv1d_prefill(const float* x, const float* w, float* y, float* state_io, int seq,
+                           int dim, int k, int use_state_in, cudaStream_t st);
+
+}  // namespace rl

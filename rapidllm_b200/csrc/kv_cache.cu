@@ -1,0 +1,62 @@
+// Paged F16 KV cache maintenance: append / bulk write of K,V rows and gather back.
+//
+// The reference appends rows into a contiguous [pos][n_kv][hd] cache
+// (src/runtime/dual_cache.cpp:74-79; CUDA store_kv_batch_h_k,
+// src/kernels/cuda/cuda_engine.cu:8216-8221, __float2half = round to nearest
+// even).  Here token s of a sequence lives in page table[s / 64], row s % 64 of
+// the (page, head) slice, in the swizzled tile format of kv_slice_offset().
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rl {
+
+// grid (n_tok, n_kv, batch), 32 threads: one 16-byte chunk (8 dims) per thread.
+__global__ void __launch_bounds__(32) kv_write_kernel(KvWriteArgs a) {
+    const int t = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x;
+    const int pos = (a.pos ? a.pos[b] : a.pos0) + t;
+    const int pi = pos / kPageTokens;
+    if (pos < 0 || pi >= a.max_pages_per_seq) {
+        if (lane == 0) set_err(a.err, DEV_ERR_BAD_LEN);
+        return;
+    }
+    const int page = a.page_table[size_t(b) * a.max_pages_per_seq + pi];
+    if (page < 0 || page >= a.n_pages) {
+        if (lane == 0) set_err(a.err, DEV_ERR_BAD_PAGE);
+        return;
+    }
+    const int row = pos % kPageTokens;
+    const size_t src = ((size_t(b) * a.n_tok + t) * a.n_kv + h) * kHeadDim + lane * 8;
+    const size_t dst = (size_t(page) * a.n_kv + h) * kv_slice_elems() + kv_slice_offset(row, lane * 8);
+    uint4 kk, vv;
+    if (a.rows_fp16) {
+        kk = *reinterpret_cast<const uint4*>(static_cast<const __half*>(a.k_rows) + src);
+        vv = *reinterpret_cast<const uint4*>(static_cast<const __half*>(a.v_rows) + src);
+    } else {
+        const float* kf = static_cast<const float*>(a.k_rows) + src;
+        const float* vf = static_cast<const float*>(a.v_rows) + src;
+        const float4 k0 = *reinterpret_cast<const float4*>(kf), k1 = *reinterpret_cast<const float4*>(kf + 4);
+        const float4 v0 = *reinterpret_cast<const float4*>(vf), v1 = *reinterpret_cast<const float4*>(vf + 4);
+        kk = make_uint4(pack_h2(k0.x, k0.y), pack_h2(k0.z, k0.w), pack_h2(k1.x, k1.y), pack_h2(k1.z, k1.w));
+        vv = make_uint4(pack_h2(v0.x, v0.y), pack_h2(v0.z, v0.w), pack_h2(v1.x, v1.y), pack_h2(v1.z, v1.w));
+    }
+    *reinterpret_cast<uint4*>(a.k_pool + dst) = kk;
+    *reinterpret_cast<uint4*>(a.v_pool + dst) = vv;
+}
+
+// grid (n_tok, n_kv), 32 threads.
+__global__ void __launch_bounds__(32)
+kv_gather_kernel(const __half* pool, const int32_t* table, __half* out, int n_tok, int n_kv,
+                 int n_pages, int* err) {
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+    const int page = table[t / kPageTokens];
+    if (page < 0 || page >= n_pages) {
+        if (lane == 0) set_err(err, DEV_ERR_BAD_PAGE);
+        return;
+    }
+    const size_t src = (size_t(page) * n_kv + h) * kv_slice_elems() + kv_slice_offset(t % kPageTokens, lane * 8);
+    *reinterpret_cast<uint4*>(out + (size_t(t) * n_kv + h) * kHeadDim + lane * 8) =
+        *reinterpret_cast<const uint4*>(pool + src);
+}
+
+}  // namespace rl

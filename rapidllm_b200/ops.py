@@ -1,0 +1,182 @@
+"""Operator-level mirror of rapidllm::ops for torch CUDA tensors.
+
+Same names and argument meaning as include/rapidllm/kernels/ops.h:118-131;
+every function enqueues on the current torch stream through the C ABI and
+raises RlError on a bad argument.  No CPU path exists here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import (AttnDecodeParams, Conv1dParams, DeltaRecurrentParams, KvAppendParams, check,
+                   lib)
+
+PAGE_TOKENS = 64
+HEAD_DIM = 256
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _need(t, dtype, name):
+    if t is None:
+        return
+    if not (t.is_cuda and t.dtype == dtype and t.is_contiguous()):
+        raise _lib.RlError(6, f"{name}: need a contiguous CUDA tensor of {dtype}")
+
+
+def kv_slice_index(tok: torch.Tensor, d: torch.Tensor) -> torch.Tensor:
+    """Offset (in halves) of element (tok, d) inside one (page, head) slice."""
+    sub = d >> 6
+    chunk = ((d & 63) >> 3) ^ (tok & 7)
+    return sub * (PAGE_TOKENS * 64) + tok * 64 + chunk * 8 + (d & 7)
+
+
+def new_pool(n_pages: int, n_kv: int, device="cuda") -> torch.Tensor:
+    """A zeroed fp16 pool [n_pages][n_kv][64*256] for K or V."""
+    return torch.zeros(n_pages, n_kv, PAGE_TOKENS * HEAD_DIM, dtype=torch.float16, device=device)
+
+
+def kv_append(k_pool, v_pool, page_table, k_rows, v_rows, pos=None, pos0=0):
+    """Write rows [batch][n_tok][n_kv][256] (fp32 -> fp16 RNE, or fp16) at pos[b] (+0..n_tok-1)."""
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    if k_rows.dim() == 3:
+        k_rows, v_rows = k_rows.unsqueeze(0), v_rows.unsqueeze(0)
+    if page_table.dim() == 1:
+        page_table = page_table.unsqueeze(0)
+    fp16 = k_rows.dtype == torch.float16
+    _need(k_rows, torch.float16 if fp16 else torch.float32, "k_rows")
+    _need(v_rows, k_rows.dtype, "v_rows")
+    _need(page_table, torch.int32, "page_table")
+    _need(pos, torch.int32, "pos")
+    p = KvAppendParams(n_kv=n_kv, head_dim=HEAD_DIM, batch=k_rows.shape[0], n_tok=k_rows.shape[1],
+                       page_tokens=PAGE_TOKENS, n_pages=n_pages,
+                       max_pages_per_seq=page_table.shape[1], pos0=pos0, rows_fp16=int(fp16))
+    check(lib().rl_kv_append(_p(k_pool), _p(v_pool), _p(page_table), _p(pos), _p(k_rows),
+                             _p(v_rows), C.byref(p), _stream()))
+
+
+def kv_gather(pool, page_table_row, n_tok):
+    """Tokens [0, n_tok) of one sequence as contiguous fp16 [n_tok][n_kv][256]."""
+    n_pages, n_kv = pool.shape[0], pool.shape[1]
+    _need(page_table_row, torch.int32, "page_table_row")
+    out = torch.empty(n_tok, n_kv, HEAD_DIM, dtype=torch.float16, device=pool.device)
+    check(lib().rl_kv_gather(_p(pool), _p(page_table_row), _p(out), n_tok, n_kv, HEAD_DIM, n_pages,
+                             _stream()))
+    return out
+
+
+def attn_params(n_q, n_kv, batch, n_pages, max_pages_per_seq, max_seq_len, len_add=0,
+                chunk_pages=0):
+    return AttnDecodeParams(n_q=n_q, n_kv=n_kv, head_dim=HEAD_DIM, kv_dtype=_lib.RL_KV_F16,
+                            batch=batch, page_tokens=PAGE_TOKENS, n_pages=n_pages,
+                            max_pages_per_seq=max_pages_per_seq, max_seq_len=max_seq_len,
+                            len_add=len_add, chunk_pages=chunk_pages, wht_len=128)
+
+
+def attn_decode(q, k_pool, v_pool, page_table, seq_lens, gate=None, max_seq_len=None,
+                chunk_pages=0, workspace=None, out=None, partial=False):
+    """ops::attn_decode for a ragged batch over the paged F16 cache, then o *= sigmoid(gate).
+
+    q, gate [batch][n_q][256] fp32; page_table int32 [batch][max_pages]; seq_lens int32
+    [batch] on the device.  With partial=True returns (part_o, part_ml) per (sequence,
+    head) for a cross-GPU merge with lse_combine.
+    """
+    _need(q, torch.float32, "q")
+    _need(gate, torch.float32, "gate")
+    _need(page_table, torch.int32, "page_table")
+    _need(seq_lens, torch.int32, "seq_lens")
+    batch, n_q, _ = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    if max_seq_len is None:
+        max_seq_len = page_table.shape[1] * PAGE_TOKENS
+    p = attn_params(n_q, n_kv, batch, n_pages, page_table.shape[1], max_seq_len, 0, chunk_pages)
+    need = lib().rl_attn_decode_workspace_bytes(C.byref(p))
+    if need == 0 and batch > 0:
+        raise _lib.RlError(6, lib().rl_last_error().decode())
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    o = out if out is not None else torch.empty_like(q)
+    if partial:
+        ml = torch.empty(batch, n_q, 2, dtype=torch.float32, device=q.device)
+        check(lib().rl_attn_decode_partial(_p(k_pool), _p(v_pool), _p(page_table), _p(seq_lens),
+                                           _p(q), _p(o), _p(ml), _p(workspace), workspace.numel(),
+                                           C.byref(p), _stream()))
+        return o, ml
+    check(lib().rl_attn_decode(_p(k_pool), _p(v_pool), _p(page_table), _p(seq_lens), _p(q),
+                               _p(gate), _p(o), _p(workspace), workspace.numel(), C.byref(p),
+                               _stream()))
+    return o
+
+
+def lse_combine(part_o, part_ml, gate=None):
+    """Merge partials [n_parts][rows][256] / [n_parts][rows][2] -> o [rows][256]."""
+    _need(part_o, torch.float32, "part_o")
+    _need(part_ml, torch.float32, "part_ml")
+    n_parts, rows, hd = part_o.shape
+    o = torch.empty(rows, hd, dtype=torch.float32, device=part_o.device)
+    check(lib().rl_lse_combine(_p(part_o), _p(part_ml), _p(gate), _p(o), n_parts, rows, hd,
+                               _stream()))
+    return o
+
+
+def delta_recurrent_step(S, q, k, v, beta, g_log, eps_l2=1e-6, slot_ids=None, head_map=None,
+                         out=None):
+    """ops::delta_recurrent_step for a batch; S [n_slots][n_v][128][128] fp32 in place.
+
+    q,k [batch][n_qk][128]; v [batch][n_v][128]; beta,g_log [batch][n_v]; returns o.
+    A 3-D S / 2-D q,k,v (the reference's single-sequence shapes) are accepted.
+    """
+    single = S.dim() == 3
+    if single:
+        S, q, k, v = S.unsqueeze(0), q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+        beta, g_log = beta.unsqueeze(0), g_log.unsqueeze(0)
+    for t, n in ((S, "S"), (q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (g_log, "g_log")):
+        _need(t, torch.float32, n)
+    _need(slot_ids, torch.int32, "slot_ids")
+    n_slots, n_v, dk, dv = S.shape
+    batch, n_qk = q.shape[0], q.shape[1]
+    if head_map is None:
+        head_map = _lib.RL_HEADS_PER_VALUE if n_qk == n_v else _lib.RL_HEADS_GROUPED
+    o = out if out is not None else torch.empty(batch, n_v, dv, dtype=torch.float32, device=S.device)
+    p = DeltaRecurrentParams(n_v=n_v, dk=dk, dv=dv, eps_l2=eps_l2, batch=batch, n_slots=n_slots,
+                             n_qk=n_qk, head_map=head_map, q_stride=0, k_stride=0, v_stride=0)
+    check(lib().rl_delta_recurrent(_p(S), _p(slot_ids), _p(q), _p(k), _p(v), _p(beta), _p(g_log),
+                                   _p(o), C.byref(p), _stream()))
+    return o[0] if single else o
+
+
+def conv1d_update(x_t, w, state, slot_ids=None):
+    """ops::conv1d_update: state [n_slots][dim][k] (or [dim][k]) in place; x_t [batch][dim]."""
+    single = x_t.dim() == 1
+    if single:
+        x_t, state = x_t.unsqueeze(0), state.unsqueeze(0)
+    for t, n in ((x_t, "x_t"), (w, "w"), (state, "state")):
+        _need(t, torch.float32, n)
+    batch, dim = x_t.shape
+    y = torch.empty_like(x_t)
+    p = Conv1dParams(dim=dim, k=w.shape[1], silu=1, batch=batch, n_slots=state.shape[0])
+    check(lib().rl_conv1d_update(_p(x_t), _p(w), _p(state), _p(slot_ids), _p(y), C.byref(p),
+                                 _stream()))
+    return y[0] if single else y
+
+
+def conv1d_causal_prefill(x, w, state=None, use_state_in=False):
+    """ops::conv1d_causal_prefill over x [seq][dim]; optional [dim][k] window in/out."""
+    _need(x, torch.float32, "x")
+    _need(w, torch.float32, "w")
+    _need(state, torch.float32, "state")
+    seq, dim = x.shape
+    y = torch.empty_like(x)
+    p = Conv1dParams(dim=dim, k=w.shape[1], silu=1, batch=1, n_slots=1)
+    check(lib().rl_conv1d_causal(_p(x), _p(w), _p(y), _p(state), seq, C.byref(p),
+                                 int(use_state_in), _stream()))
+    return y

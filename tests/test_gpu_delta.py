@@ -1,0 +1,149 @@
+"""Gated DeltaNet decode step and causal conv1d (CUDA, through the C ABI) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import STATE_REL_L2, rel_l2, softplus
+
+pytestmark = pytest.mark.gpu
+
+N_V, N_K, DK, DV, CONV_DIM, CONV_K = 48, 16, 128, 128, 10240, 4
+
+
+def test_config1_1024_steps_with_conv(oracle):
+    """16 K / 48 V heads, FP32 S ~ N(0, 0.02), conv k=4 over 10240 channels, 1024
+    consecutive steps from seed 1: state rel-L2 <= 1e-5, outputs max-abs <= 1e-4."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(1)
+    S0 = torch.randn(N_V, DK, DV, generator=gen) * 0.02
+    w = torch.randn(CONV_DIM, CONV_K, generator=gen) * 0.5
+    steps = 1024
+    xs = torch.randn(steps, CONV_DIM, generator=gen)
+    beta = torch.sigmoid(torch.randn(steps, N_V, generator=gen))
+    g = -softplus(torch.randn(steps, N_V, generator=gen))
+    S = S0.cuda().unsqueeze(0).clone()
+    cst = torch.zeros(1, CONV_DIM, CONV_K, device="cuda")
+    wd, xd, bd, gd = w.cuda(), xs.cuda(), beta.cuda(), g.cuda()
+    outs = []
+    for t in range(steps):
+        mixed = ops.conv1d_update(xd[t:t + 1], wd, cst)
+        qk = mixed[:, :2 * N_K * DK].reshape(1, 2, N_K, DK)
+        v = mixed[:, 2 * N_K * DK:].reshape(1, N_V, DV).contiguous()
+        outs.append(ops.delta_recurrent_step(S, qk[:, 0].contiguous(), qk[:, 1].contiguous(), v,
+                                             bd[t:t + 1], gd[t:t + 1]))
+    _lib.check_device()
+    o_gpu = torch.cat(outs).cpu().numpy()
+    Sr = S0.numpy().copy()
+    cr = np.zeros((CONV_DIM, CONV_K), np.float32)
+    o_ref = np.empty_like(o_gpu)
+    for t in range(steps):
+        mixed = oracle.conv1d_update(xs[t].numpy(), w.numpy(), cr)
+        q = oracle.repeat_heads(mixed[:N_K * DK].reshape(N_K, DK), N_V)
+        k = oracle.repeat_heads(mixed[N_K * DK:2 * N_K * DK].reshape(N_K, DK), N_V)
+        v = mixed[2 * N_K * DK:].reshape(N_V, DV)
+        o_ref[t] = oracle.delta_step(Sr, q, k, v, beta[t].numpy(), g[t].numpy())
+    s_err = rel_l2(S[0].cpu().numpy(), Sr)
+    o_err = np.abs(o_gpu - o_ref).max()
+    print("cfg1 state rel-l2 %.3e, o max-abs %.3e, conv state max-abs %.3e" %
+          (s_err, o_err, np.abs(cst[0].cpu().numpy() - cr).max()))
+    assert s_err <= STATE_REL_L2
+    assert o_err <= 1e-4
+    assert np.array_equal(cst[0].cpu().numpy(), cr)          # the window is a pure shift
+
+
+def test_l2_normalised_inputs_per_value_heads(oracle):
+    """q, k already L2-normalised and repeated per value head (the op normalises again)."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(11)
+    S0 = torch.randn(N_V, DK, DV, generator=gen) * 0.02
+    q = torch.nn.functional.normalize(torch.randn(N_V, DK, generator=gen), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(N_V, DK, generator=gen), dim=-1)
+    v = torch.randn(N_V, DV, generator=gen)
+    beta = torch.sigmoid(torch.randn(N_V, generator=gen))
+    g = -softplus(torch.randn(N_V, generator=gen))
+    S = S0.cuda().clone()
+    o = ops.delta_recurrent_step(S, q.cuda(), k.cuda(), v.cuda(), beta.cuda(), g.cuda())
+    _lib.check_device()
+    Sr = S0.numpy().copy()
+    oref = oracle.delta_step(Sr, q.numpy(), k.numpy(), v.numpy(), beta.numpy(), g.numpy())
+    assert np.abs(o.cpu().numpy() - oref).max() < 1e-5
+    assert rel_l2(S.cpu().numpy(), Sr) < 1e-6
+
+
+def test_reference_golden_vectors(golden):
+    """The reference's own scalar outputs (tests/golden, 4 heads of 128x128, 3 steps)."""
+    from rapidllm_b200 import _lib, ops
+    S = torch.from_numpy(golden["delta_a_S0"].copy()).cuda()
+    for t in range(3):
+        a = [torch.from_numpy(golden[f"delta_a_{n}{t}"]).cuda() for n in ("q", "k", "v", "beta", "g")]
+        o = ops.delta_recurrent_step(S, *a)
+        assert np.abs(o.cpu().numpy() - golden[f"delta_a_o_scalar{t}"]).max() < 2e-5
+    _lib.check_device()
+    assert rel_l2(S.cpu().numpy(), golden["delta_a_S_scalar"]) < 1e-6
+
+
+@pytest.mark.parametrize("head_map", [1, 2])
+def test_batch_slots_and_head_maps(oracle, head_map):
+    """Batch of 5 sequences on shuffled state slots; grouped (h // 3) and tiled (h % 16) maps."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(20 + head_map)
+    B, n_slots = 5, 8
+    S0 = torch.randn(n_slots, N_V, DK, DV, generator=gen) * 0.02
+    slots = torch.randperm(n_slots, generator=gen)[:B].int()
+    q = torch.randn(B, N_K, DK, generator=gen)
+    k = torch.randn(B, N_K, DK, generator=gen)
+    v = torch.randn(B, N_V, DV, generator=gen)
+    beta = torch.sigmoid(torch.randn(B, N_V, generator=gen))
+    g = -softplus(torch.randn(B, N_V, generator=gen))
+    S = S0.cuda().clone()
+    o = ops.delta_recurrent_step(S, q.cuda(), k.cuda(), v.cuda(), beta.cuda(), g.cuda(),
+                                 slot_ids=slots.cuda(), head_map=head_map)
+    _lib.check_device()
+    Sr = S0.numpy().copy()
+    for b in range(B):
+        sl = int(slots[b])
+        qq = oracle.repeat_heads(q[b].numpy(), N_V, tiled=(head_map == 2))
+        kk = oracle.repeat_heads(k[b].numpy(), N_V, tiled=(head_map == 2))
+        oref = oracle.delta_step(Sr[sl], qq, kk, v[b].numpy(), beta[b].numpy(), g[b].numpy())
+        assert np.abs(o[b].cpu().numpy() - oref).max() < 2e-5
+    assert rel_l2(S.cpu().numpy(), Sr) < 1e-6           # untouched slots stay bit-identical too
+    untouched = [s for s in range(n_slots) if s not in slots.tolist()]
+    assert np.array_equal(S[untouched].cpu().numpy(), S0[untouched].numpy())
+    bad = torch.tensor([0, 1, 2, 3, 99], dtype=torch.int32, device="cuda")
+    ops.delta_recurrent_step(S, q.cuda(), k.cuda(), v.cuda(), beta.cuda(), g.cuda(), slot_ids=bad,
+                             head_map=head_map)
+    assert _lib.device_error() == 4
+
+
+def test_conv1d_update_and_prefill(oracle, golden):
+    from rapidllm_b200 import _lib, ops
+    w, xs = golden["conv_w"], golden["conv_x"]
+    wd = torch.from_numpy(w).cuda()
+    st = torch.zeros(1, *w.shape, device="cuda")
+    ys = torch.cat([ops.conv1d_update(torch.from_numpy(x).cuda().unsqueeze(0), wd, st) for x in xs])
+    assert np.abs(ys.cpu().numpy() - golden["conv_y_update"]).max() < 2e-6
+    assert np.array_equal(st[0].cpu().numpy(), golden["conv_state_end"])
+    # prefill form, whole and in two chunks carrying the window
+    xd = torch.from_numpy(xs).cuda()
+    st2 = torch.zeros(*w.shape, device="cuda")
+    y = ops.conv1d_causal_prefill(xd, wd, st2)
+    assert np.abs(y.cpu().numpy() - golden["conv_y_prefill"]).max() < 2e-6
+    assert np.array_equal(st2.cpu().numpy(), golden["conv_state_end"])
+    st3 = torch.zeros(*w.shape, device="cuda")
+    ya = ops.conv1d_causal_prefill(xd[:2].contiguous(), wd, st3)
+    yb = ops.conv1d_causal_prefill(xd[2:].contiguous(), wd, st3, use_state_in=True)
+    assert torch.equal(torch.cat([ya, yb]), y)
+    assert np.array_equal(st3.cpu().numpy(), golden["conv_state_end"])
+    # other tap counts and a ragged channel count
+    gen = torch.Generator().manual_seed(2)
+    for dim, k in [(1000, 3), (77, 4), (300, 2)]:
+        ww = torch.randn(dim, k, generator=gen)
+        x = torch.randn(9, dim, generator=gen)
+        s = np.zeros((dim, k), np.float32)
+        ref = np.stack([oracle.conv1d_update(x[t].numpy(), ww.numpy(), s) for t in range(9)])
+        sd = torch.zeros(1, dim, k, device="cuda")
+        got = torch.cat([ops.conv1d_update(x[t:t + 1].cuda(), ww.cuda(), sd) for t in range(9)])
+        assert np.abs(got.cpu().numpy() - ref).max() < 2e-6
+        assert np.array_equal(sd[0].cpu().numpy(), s)
+        assert np.abs(ops.conv1d_causal_prefill(x.cuda(), ww.cuda()).cpu().numpy() - ref).max() < 2e-6
+    _lib.check_device()

@@ -1,0 +1,99 @@
+"""The layer_types[] decode step (rl_stack_decode / rl_stack_decode_host) against the
+oracle run layer by layer, on a small hybrid stack with ragged paged contexts."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import ATTN_MAX_ABS, ATTN_REL_L2, rel_l2, softplus
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(cache, B, gen, lens):
+    sh = cache.io_shapes(B)
+    t = {n: torch.randn(sh[n], generator=gen) for n in
+         ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv")}
+    t["conv_w"] = torch.randn(sh["conv_w"], generator=gen) * 0.5
+    t["delta_beta"] = torch.sigmoid(torch.randn(sh["delta_beta"], generator=gen))
+    t["delta_g"] = -softplus(torch.randn(sh["delta_g"], generator=gen))
+    t["attn_o"] = torch.zeros(sh["attn_o"])
+    t["delta_o"] = torch.zeros(sh["delta_o"])
+    t["pos"] = torch.tensor(lens, dtype=torch.int32)
+    return t
+
+
+def test_stack_decode_matches_oracle_layer_by_layer(oracle):
+    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    gen = torch.Generator().manual_seed(4)
+    types = QWEN35_LAYER_TYPES * 2
+    lens = [100, 63, 257]                        # tokens already cached per sequence
+    B, n_slots, max_pages = 3, 4, 6
+    n_pages = 16
+    cache = HybridCache(types, n_pages=n_pages, n_slots=n_slots, max_batch=4,
+                        max_pages_per_seq=max_pages)
+    assert cache.n_attn == 2 and cache.n_delta == 6 and cache.launches_per_step == 2 * 3 + 6 * 2
+    # page table: disjoint shuffled pages
+    perm = torch.randperm(n_pages, generator=gen).int()
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        p = (n + 1 + 63) // 64
+        table[b, :p] = perm[at:at + p]
+        at += p
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32)
+    # fill the caches
+    k_hist = [[torch.randn(n, 4, 256, generator=gen).half() for n in lens] for _ in range(2)]
+    v_hist = [[torch.randn(n, 4, 256, generator=gen).half() for n in lens] for _ in range(2)]
+    for a in range(2):
+        for b in range(B):
+            ops.kv_append(cache.k_pool(a), cache.v_pool(a), table[b].cuda(), k_hist[a][b].cuda(),
+                          v_hist[a][b].cuda(), pos0=0)
+    S0 = [torch.randn(n_slots, 48, 128, 128, generator=gen) * 0.02 for _ in range(6)]
+    C0 = [torch.randn(n_slots, cache.conv_dim, 4, generator=gen) for _ in range(6)]
+    for d in range(6):
+        cache.state(d).copy_(S0[d])
+        cache.conv(d).copy_(C0[d])
+    t = _inputs(cache, B, gen, lens)
+    t["page_table"], t["slot_ids"] = table, slots
+    dev = {n: x.cuda() for n, x in t.items()}
+    cache.decode(dev, B)
+    _lib.check_device()
+    attn_o = dev["attn_o"].cpu().numpy()
+    delta_o = dev["delta_o"].cpu().numpy()
+    # oracle, layer by layer
+    for a in range(2):
+        for b in range(B):
+            k = torch.cat([k_hist[a][b], t["attn_k"][a, b:b + 1].half()]).float().numpy()
+            v = torch.cat([v_hist[a][b], t["attn_v"][a, b:b + 1].half()]).float().numpy()
+            ref = oracle.gated_attn_decode(t["attn_q"][a, b].numpy(), k, v, t["attn_gate"][a, b].numpy())
+            assert np.abs(attn_o[a, b] - ref).max() <= ATTN_MAX_ABS
+            assert rel_l2(attn_o[a, b], ref) <= ATTN_REL_L2
+    nk = 16 * 128
+    for d in range(6):
+        Sr = S0[d].numpy().copy()
+        Cr = C0[d].numpy().copy()
+        for b in range(B):
+            sl = int(slots[b])
+            mixed = oracle.conv1d_update(t["delta_qkv"][d, b].numpy(), t["conv_w"][d].numpy(), Cr[sl])
+            q = oracle.repeat_heads(mixed[:nk].reshape(16, 128), 48)
+            k = oracle.repeat_heads(mixed[nk:2 * nk].reshape(16, 128), 48)
+            ref = oracle.delta_step(Sr[sl], q, k, mixed[2 * nk:].reshape(48, 128),
+                                    t["delta_beta"][d, b].numpy(), t["delta_g"][d, b].numpy())
+            assert np.abs(delta_o[d, b] - ref).max() < 1e-4
+        assert rel_l2(cache.state(d).cpu().numpy(), Sr) < 1e-6
+        assert np.array_equal(cache.conv(d).cpu().numpy(), Cr)
+
+    # the host-buffer entry point gives the same bits
+    for d in range(6):
+        cache.state(d).copy_(S0[d])
+        cache.conv(d).copy_(C0[d])
+    host = {n: (x.pin_memory() if n != "conv_w" else x) for n, x in t.items()}
+    host["attn_o"].zero_()
+    host["delta_o"].zero_()
+    cache.set_conv_w(host["conv_w"])
+    cache.decode_host(host, B)
+    _lib.check_device()
+    assert np.array_equal(host["attn_o"].numpy(), attn_o)
+    assert np.array_equal(host["delta_o"].numpy(), delta_o)
+    cache.close()
