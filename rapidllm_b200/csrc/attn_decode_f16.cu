@@ -40,10 +40,11 @@ constexpr int kSubTilePageBytes = kPageTokens * 128;       // 8 KiB
 constexpr int kMaxBatch = 1024;
 constexpr float kNegBig = -1e30f;
 constexpr int kMergeStride = kHeadDim + 1;
+static_assert(kConsumerWarps == 6, "the item merge below is a fixed tree over six warps");
 
 struct Smem {
     alignas(128) unsigned char stage[kStages][kStageBytes];
-    float o[8][kMergeStride];       // item merge buffer (row stride 257: conflict-free adds)
+    float o[3][8][kMergeStride];    // item merge buffers (row stride 257: conflict-free)
     float m[kConsumerWarps][8];
     float l[kConsumerWarps][8];
     int prefix[kMaxBatch + 1];      // chunks before sequence b
@@ -326,35 +327,74 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
             s.m[warp][g] = m_run;
             s.l[warp][g] = l_run;
         }
-        for (int x = tid; x < 8 * kMergeStride; x += kConsumerWarps * 32) (&s.o[0][0])[x] = 0.f;
         named_bar_sync(1, kConsumerWarps * 32);
-        float f[2];
+        // scale this warp's accumulators to the item-wide maximum
+        {
+            float f[2];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            float mm = kNegBig;
+            for (int e = 0; e < 2; ++e) {
+                float mm = kNegBig;
 #pragma unroll
-            for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
-            f[e] = fast_exp2(s.m[warp][2 * c + e] - mm);
+                for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
+                f[e] = fast_exp2(s.m[warp][2 * c + e] - mm);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[j][i][0] *= f[0];
+                    acc[j][i][2] *= f[0];
+                    acc[j][i][1] *= f[1];
+                    acc[j][i][3] *= f[1];
+                }
         }
-        if (__any_sync(0xffffffffu, l_run > 0.f)) {
-            // lanes with pg >= 4 add the odd dim first so that a warp's 32 adds hit 32 banks
-            const int odd = pg >> 2;
+        // Fixed-order tree over the six warps (bit-reproducible, unlike atomics):
+        // warps 3,4,5 -> buffers 0,1,2; warps 0,1,2 add; warps 1,2 -> buffers 0,1; warp 0 adds
+        // them in order and leaves the item's total in buffer 2.  Lanes with pg >= 4 touch
+        // the odd dim first so that a warp's 32 accesses hit 32 banks (row stride 257).
+        const int odd = pg >> 2;
+        auto put = [&](float (*buf)[kMergeStride]) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int d = 64 * j + 8 * pg + 2 * i;
-                    atomicAdd(&s.o[2 * c][d + odd], (odd ? acc[j][i][2] : acc[j][i][0]) * f[0]);
-                    atomicAdd(&s.o[2 * c][d + 1 - odd], (odd ? acc[j][i][0] : acc[j][i][2]) * f[0]);
-                    atomicAdd(&s.o[2 * c + 1][d + odd], (odd ? acc[j][i][3] : acc[j][i][1]) * f[1]);
-                    atomicAdd(&s.o[2 * c + 1][d + 1 - odd], (odd ? acc[j][i][1] : acc[j][i][3]) * f[1]);
+                    buf[2 * c][d + odd] = odd ? acc[j][i][2] : acc[j][i][0];
+                    buf[2 * c][d + 1 - odd] = odd ? acc[j][i][0] : acc[j][i][2];
+                    buf[2 * c + 1][d + odd] = odd ? acc[j][i][3] : acc[j][i][1];
+                    buf[2 * c + 1][d + 1 - odd] = odd ? acc[j][i][1] : acc[j][i][3];
                 }
+        };
+        auto add = [&](const float (*buf)[kMergeStride]) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int d = 64 * j + 8 * pg + 2 * i;
+                    const float x0 = buf[2 * c][d + odd], x1 = buf[2 * c][d + 1 - odd];
+                    const float y0 = buf[2 * c + 1][d + odd], y1 = buf[2 * c + 1][d + 1 - odd];
+                    acc[j][i][0] += odd ? x1 : x0;
+                    acc[j][i][2] += odd ? x0 : x1;
+                    acc[j][i][1] += odd ? y1 : y0;
+                    acc[j][i][3] += odd ? y0 : y1;
+                }
+        };
+        if (warp >= 3) put(s.o[warp - 3]);
+        named_bar_sync(1, kConsumerWarps * 32);
+        if (warp < 3) add(s.o[warp]);
+        named_bar_sync(1, kConsumerWarps * 32);
+        if (warp == 1 || warp == 2) put(s.o[warp - 1]);
+        named_bar_sync(1, kConsumerWarps * 32);
+        if (warp == 0) {
+            add(s.o[0]);
+            add(s.o[1]);
+            put(s.o[2]);
         }
         named_bar_sync(1, kConsumerWarps * 32);
         {
             float* po = a.part_o + size_t(item) * G * kHeadDim;
             for (int x = tid; x < G * kHeadDim; x += kConsumerWarps * 32)
-                po[x] = s.o[x >> 8][x & (kHeadDim - 1)];
+                po[x] = s.o[2][x >> 8][x & (kHeadDim - 1)];
             if (tid < G) {
                 float mm = kNegBig;
                 for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][tid]);

@@ -32,6 +32,7 @@ def _oracle(oracle, q, gate, ks, vs):
 def _check(o, ref):
     o = o.cpu().numpy()
     assert np.isfinite(o).all()
+    print("attn max-abs %.3e rel-l2 %.3e" % (np.abs(o - ref).max(), rel_l2(o, ref)))
     assert np.abs(o - ref).max() <= ATTN_MAX_ABS, np.abs(o - ref).max()
     assert rel_l2(o, ref) <= ATTN_REL_L2, rel_l2(o, ref)
 
@@ -161,8 +162,12 @@ def test_long_ragged_contexts_split_invariance(oracle):
     o2 = ops.attn_decode(q.cuda(), kp, vp, table, lens, gate.cuda(), chunk_pages=64)
     o3 = ops.attn_decode(q.cuda(), kp, vp, table, lens, gate.cuda(), chunk_pages=5)
     _lib.check_device()
-    assert rel_l2(o2.cpu().numpy(), o1.cpu().numpy()) < 2e-4
-    assert rel_l2(o3.cpu().numpy(), o1.cpu().numpy()) < 2e-4
+    d2, d3 = rel_l2(o2.cpu().numpy(), o1.cpu().numpy()), rel_l2(o3.cpu().numpy(), o1.cpu().numpy())
+    print("split plans differ by rel-l2 %.3e %.3e" % (d2, d3))
+    assert d2 <= ATTN_REL_L2 and d3 <= ATTN_REL_L2
+    # the same call twice gives the same bits (fixed-order merges)
+    o1b = ops.attn_decode(q.cuda(), kp, vp, table, lens, gate.cuda())
+    assert torch.equal(o1, o1b)
     for b in (1, 3):
         ref = oracle.gated_attn_decode(q[b].numpy(), ks[b].float().numpy(), vs[b].float().numpy(),
                                        gate[b].numpy())
