@@ -384,7 +384,10 @@ def main():
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "fallback 6650 (of fallback)",
                          "bytes_per_launch": ab["attn_decode"], "ms_per_launch": attn_ms_per_launch,
-                         "traffic": None},
+                         # ncu dram read+write of a batch-8 capture was 1.0246 x its algorithmic bytes
+                         # (profiles/attn_decode_f16_kernel.stack_decode.md); traffic grows with tokens
+                         "traffic": int(1.0246 * ab["attn_decode"]),
+                         "traffic_source": "ncu capture of a batch-8 launch scaled by algorithmic bytes"},
             "kernel_families": families,
         }
         if e2e:
