@@ -80,6 +80,7 @@ typedef struct rl_attn_decode_params {
     int len_add;                 /* tokens attended = seq_lens[b] + len_add (1 when seq_lens holds `pos`) */
     int chunk_pages;             /* pages per split-KV work item; 0 = choose */
     int wht_len;                 /* TQ3 transform length: 128 (reference layout) or 256 */
+    const float* tq_signs;       /* device [256] +-1 sign vector of the 256 layout, or NULL */
 } rl_attn_decode_params;
 
 /* Bytes of scratch rl_attn_decode needs for these parameters. */
@@ -92,7 +93,9 @@ size_t rl_attn_decode_workspace_bytes(const rl_attn_decode_params* p);
  * (src/kernels/cuda/cuda_engine.cu:5802-5862, 303-375).
  *   k_pool, v_pool  F16: fp16 pools [n_pages][n_kv] of 64x256 slices in the tile
  *                   format written by rl_kv_append (opaque; read back with
- *                   rl_kv_gather).  Q8K_TQ3V: see rl_kv_compact_* below.
+ *                   rl_kv_gather).  Q8K_TQ3V: k_pool is the record pool written by
+ *                   rl_kv_compact_append, v_pool is ignored; replaces
+ *                   qk_attn_decode_tq_gqa_k (cuda_engine.cu:8382-8454).
  *   page_table      int32 [batch][max_pages_per_seq]
  *   seq_lens        int32 [batch], device resident so a step can be graph-captured
  *   q, gate, o      fp32 [batch][n_q][head_dim]; softmax scale 1/sqrt(head_dim) */
@@ -105,9 +108,12 @@ int rl_attn_decode(const void* k_pool, const void* v_pool, const int32_t* page_t
  * (and cross-GPU) form of the warp merge at cuda_engine.cu:347-374.
  *   part_o  fp32 [n_parts][rows][256] unnormalised sums
  *   part_ml fp32 [n_parts][rows][2]   (running max of scaled scores, sum of exp)
- *   gate    fp32 [rows][256] or NULL;  o fp32 [rows][256] */
+ *   gate    fp32 [rows][256] or NULL;  o fp32 [rows][256]
+ *   wht_len 0 for F16 partials; 128 / 256 (+ tq_signs) when the partials come from the
+ *           compact cache and are still in the rotated domain of the V transform */
 int rl_lse_combine(const float* part_o, const float* part_ml, const float* gate, float* o,
-                   int n_parts, int rows, int head_dim, void* stream);
+                   int n_parts, int rows, int head_dim, int wht_len, const float* tq_signs,
+                   void* stream);
 
 /* Same as rl_attn_decode but stops before the merge across sequences' chunks
  * is normalised: writes one partial (unnormalised o, max, sum) per
@@ -130,6 +136,7 @@ typedef struct rl_kv_append_params {
     int page_tokens, n_pages, max_pages_per_seq;
     int pos0;                    /* first position when pos == NULL */
     int rows_fp16;               /* 1: rows are fp16; 0: fp32, rounded to nearest even */
+    int wht_len;                 /* compact cache only: 128 or 256 */
 } rl_kv_append_params;
 
 /* DualCache::append_kv (src/runtime/dual_cache.cpp:74-79) / store_kv_batch_h_k
@@ -144,6 +151,22 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
  * (src/runtime/dual_cache.cpp:49-60). */
 int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16, int n_tok,
                  int n_kv, int head_dim, int n_pages, void* stream);
+
+/* Compact cache (--kv-type q8k_tq3v): K int8 + fp16 scale per row, V Walsh-Hadamard
+ * rotated + 3-bit Lloyd-Max codes + fp16 RMS scale per block of wht_len.  Codes and
+ * scales are those of store_k_q8_th_k / store_v_tq3_th_k (cuda_engine.cu:8224-8284)
+ * evaluated in IEEE fp32.  The pool is n_pages * n_kv * rl_kv_compact_page_bytes()
+ * bytes, 358 bytes per token and head as in the reference (cuda_engine.cu:18305-18318). */
+size_t rl_kv_compact_page_bytes(void);
+/* k_rows, v_rows fp32 [batch][n_tok][n_kv][256]; tq_signs device [256] or NULL. */
+int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* pos,
+                         const float* k_rows, const float* v_rows, const float* tq_signs,
+                         const rl_kv_append_params* p, void* stream);
+/* Tokens [0, n_tok) of one sequence in the reference's packing: k_q int8 [n_tok][n_kv][256],
+ * k_sc fp16 [n_tok][n_kv], v_codes u8 [n_tok][n_kv][96], v_sc fp16 [n_tok][n_kv][256/wht_len]. */
+int rl_kv_compact_gather(const void* pool, const int32_t* page_table_row, void* k_q, void* k_sc,
+                         void* v_codes, void* v_sc, int n_tok, int n_kv, int n_pages, int wht_len,
+                         void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Gated DeltaNet                                                             */

@@ -29,13 +29,14 @@ class RlError(RuntimeError):
 class AttnDecodeParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "n_q", "n_kv", "head_dim", "kv_dtype", "batch", "page_tokens", "n_pages",
-        "max_pages_per_seq", "max_seq_len", "len_add", "chunk_pages", "wht_len")]
+        "max_pages_per_seq", "max_seq_len", "len_add", "chunk_pages", "wht_len")] + [
+        ("tq_signs", C.c_void_p)]
 
 
 class KvAppendParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "n_kv", "head_dim", "batch", "n_tok", "page_tokens", "n_pages", "max_pages_per_seq",
-        "pos0", "rows_fp16")]
+        "pos0", "rows_fp16", "wht_len")]
 
 
 class DeltaRecurrentParams(C.Structure):
@@ -76,7 +77,10 @@ SYMBOLS = {
                             C.POINTER(AttnDecodeParams), _vp]),
     "rl_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz,
                                     C.POINTER(AttnDecodeParams), _vp]),
-    "rl_lse_combine": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "rl_lse_combine": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "rl_kv_compact_page_bytes": (_sz, []),
+    "rl_kv_compact_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(KvAppendParams), _vp]),
+    "rl_kv_compact_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(KvAppendParams), _vp]),
     "rl_kv_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_delta_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

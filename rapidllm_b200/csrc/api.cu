@@ -64,6 +64,8 @@ int dev_info(DevInfo** out) {
         RL_CUDA(cudaMemset(d.err_ptr, 0, sizeof(int)));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_f16_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_tq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::attn_decode_tq_smem_bytes())));
         d.ready = true;
     }
     *out = &d;
@@ -91,7 +93,10 @@ int attn_check(const rl_attn_decode_params* p) {
     if (p->n_pages <= 0 || p->max_pages_per_seq <= 0) return fail(RL_ERR_RANGE, "empty page pool or table");
     if (p->max_seq_len <= 0 || p->max_seq_len > p->max_pages_per_seq * p->page_tokens)
         return fail(RL_ERR_RANGE, "max_seq_len %d outside (0, max_pages_per_seq*page_tokens]", p->max_seq_len);
-    if (p->kv_dtype != RL_KV_F16) return fail(RL_ERR_UNSUPPORTED, "kv_dtype %d not supported by this call", p->kv_dtype);
+    if (p->kv_dtype != RL_KV_F16 && p->kv_dtype != RL_KV_Q8K_TQ3V)
+        return fail(RL_ERR_UNSUPPORTED, "kv_dtype %d unknown", p->kv_dtype);
+    if (p->kv_dtype == RL_KV_Q8K_TQ3V && p->wht_len != 128 && p->wht_len != 256)
+        return fail(RL_ERR_UNSUPPORTED, "wht_len %d: only 128 or 256", p->wht_len);
     return RL_OK;
 }
 
@@ -121,14 +126,15 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
                      cudaEvent_t after_main = nullptr) {
     if (int st = attn_check(p)) return st;
     if (p->batch == 0) return RL_OK;
-    if (!k_pool || !v_pool || !page_table || !seq_lens || !q || !o || !workspace)
+    const bool tq = p->kv_dtype == RL_KV_Q8K_TQ3V;
+    if (!k_pool || (!v_pool && !tq) || !page_table || !seq_lens || !q || !o || !workspace)
         return fail(RL_ERR_RANGE, "NULL pointer argument");
     DevInfo* d;
     if (int st = dev_info(&d)) return st;
     const AttnPlan pl = attn_plan(p, d->sms);
     if (workspace_bytes < pl.total_bytes)
         return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, pl.total_bytes);
-    if (reinterpret_cast<uintptr_t>(k_pool) % 128 || reinterpret_cast<uintptr_t>(v_pool) % 128 ||
+    if (reinterpret_cast<uintptr_t>(k_pool) % 128 || (!tq && reinterpret_cast<uintptr_t>(v_pool) % 128) ||
         reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(workspace) % 16)
         return fail(RL_ERR_RANGE, "pools must be 128-byte aligned, q and workspace 16-byte aligned");
     rl::AttnDecodeArgs a;
@@ -151,8 +157,12 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     a.scale = 1.f / sqrtf(float(p->head_dim));
     const long long max_items = 1LL * pl.max_chunks * p->n_kv;
     const int grid = int(max_items < d->sms ? max_items : d->sms);
-    rl::attn_decode_f16_kernel<<<grid, rl::attn_decode_f16_threads(), rl::attn_decode_f16_smem_bytes(),
-                                 as_stream(stream)>>>(a);
+    if (tq)
+        rl::attn_decode_tq_kernel<<<grid, rl::attn_decode_tq_threads(), rl::attn_decode_tq_smem_bytes(),
+                                    as_stream(stream)>>>(a);
+    else
+        rl::attn_decode_f16_kernel<<<grid, rl::attn_decode_f16_threads(), rl::attn_decode_f16_smem_bytes(),
+                                     as_stream(stream)>>>(a);
     if (after_main) cudaEventRecord(after_main, as_stream(stream));
     rl::AttnCombineArgs c;
     c.part_o = a.part_o;
@@ -169,6 +179,8 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     c.page_tokens = p->page_tokens;
     c.len_add = p->len_add;
     c.max_len = p->max_pages_per_seq * p->page_tokens;
+    c.wht_len = (tq && !out_ml) ? p->wht_len : 0;      // partial outputs stay in the rotated domain
+    c.signs = (tq && p->wht_len == 256) ? p->tq_signs : nullptr;
     rl::attn_combine_kernel<<<dim3(p->n_q, p->batch), 256, 0, as_stream(stream)>>>(c);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
@@ -256,6 +268,7 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             ap.max_pages_per_seq = f.max_pages_per_seq;
             ap.pos0 = 0;
             ap.rows_fp16 = 0;
+            ap.wht_len = 0;
             void* kp = rl_cache_k_pool(c, ai);
             void* vp = rl_cache_v_pool(c, ai);
             if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
@@ -378,12 +391,15 @@ int rl_attn_decode_partial(const void* k_pool, const void* v_pool, const int32_t
 }
 
 int rl_lse_combine(const float* part_o, const float* part_ml, const float* gate, float* o, int n_parts,
-                   int rows, int head_dim, void* stream) {
+                   int rows, int head_dim, int wht_len, const float* tq_signs, void* stream) {
     if (head_dim != rl::kHeadDim) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 256", head_dim);
+    if (wht_len != 0 && wht_len != 128 && wht_len != 256)
+        return fail(RL_ERR_UNSUPPORTED, "wht_len %d: only 0, 128 or 256", wht_len);
     if (n_parts <= 0 || rows < 0) return fail(RL_ERR_RANGE, "n_parts %d rows %d", n_parts, rows);
     if (rows == 0) return RL_OK;
     if (!part_o || !part_ml || !o) return fail(RL_ERR_RANGE, "NULL pointer argument");
-    rl::lse_combine_kernel<<<rows, 256, 0, as_stream(stream)>>>(part_o, part_ml, gate, o, n_parts, rows);
+    rl::lse_combine_kernel<<<rows, 256, 0, as_stream(stream)>>>(part_o, part_ml, gate, o, n_parts, rows, wht_len,
+                                                                wht_len == 256 ? tq_signs : nullptr);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -430,6 +446,59 @@ int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16,
     rl::kv_gather_kernel<<<dim3(n_tok, n_kv), 32, 0, as_stream(stream)>>>(
         static_cast<const __half*>(pool), page_table_row, static_cast<__half*>(out_f16), n_tok, n_kv, n_pages,
         d->err_ptr);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+size_t rl_kv_compact_page_bytes(void) { return 2 * size_t(rl::kCompactRecordBytes); }
+
+int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* pos, const float* k_rows,
+                         const float* v_rows, const float* tq_signs, const rl_kv_append_params* p,
+                         void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->head_dim != rl::kHeadDim || p->page_tokens != rl::kPageTokens)
+        return fail(RL_ERR_UNSUPPORTED, "head_dim %d / page_tokens %d: only 256 / 64", p->head_dim, p->page_tokens);
+    if (p->wht_len != 128 && p->wht_len != 256) return fail(RL_ERR_UNSUPPORTED, "wht_len %d: only 128 or 256", p->wht_len);
+    if (p->rows_fp16) return fail(RL_ERR_UNSUPPORTED, "the compact cache quantises fp32 rows");
+    if (p->batch < 0 || p->n_tok < 0 || p->n_kv <= 0 || p->n_kv > 65535 || p->batch > 65535)
+        return fail(RL_ERR_RANGE, "batch %d n_tok %d n_kv %d", p->batch, p->n_tok, p->n_kv);
+    if (p->batch == 0 || p->n_tok == 0) return RL_OK;
+    if (!pool || !page_table || !k_rows || !v_rows) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    if (reinterpret_cast<uintptr_t>(pool) % 16) return fail(RL_ERR_RANGE, "pool must be 16-byte aligned");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::KvCompactWriteArgs a;
+    a.pool = static_cast<unsigned char*>(pool);
+    a.page_table = page_table;
+    a.pos = pos;
+    a.k_rows = k_rows;
+    a.v_rows = v_rows;
+    a.signs = tq_signs;
+    a.err = d->err_ptr;
+    a.batch = p->batch;
+    a.n_tok = p->n_tok;
+    a.n_kv = p->n_kv;
+    a.n_pages = p->n_pages;
+    a.max_pages_per_seq = p->max_pages_per_seq;
+    a.pos0 = p->pos0;
+    a.wht_len = p->wht_len;
+    rl::kv_compact_write_kernel<<<dim3(p->n_tok, p->n_kv, p->batch), 256, 0, as_stream(stream)>>>(a);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_kv_compact_gather(const void* pool, const int32_t* page_table_row, void* k_q, void* k_sc, void* v_codes,
+                         void* v_sc, int n_tok, int n_kv, int n_pages, int wht_len, void* stream) {
+    if (wht_len != 128 && wht_len != 256) return fail(RL_ERR_UNSUPPORTED, "wht_len %d: only 128 or 256", wht_len);
+    if (n_tok < 0 || n_kv <= 0 || n_kv > 65535) return fail(RL_ERR_RANGE, "n_tok %d n_kv %d", n_tok, n_kv);
+    if (n_tok == 0) return RL_OK;
+    if (!pool || !page_table_row || !k_q || !k_sc || !v_codes || !v_sc) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::kv_compact_gather_kernel<<<dim3(n_tok, n_kv), 256, 0, as_stream(stream)>>>(
+        static_cast<const unsigned char*>(pool), page_table_row, static_cast<signed char*>(k_q),
+        static_cast<__half*>(k_sc), static_cast<unsigned char*>(v_codes), static_cast<__half*>(v_sc), n_tok, n_kv,
+        n_pages, wht_len, d->err_ptr);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

@@ -9,6 +9,33 @@
 
 namespace rl {
 
+namespace {
+
+// Orthonormal Walsh-Hadamard transform of the 256 values held one per thread (blocks of
+// wht_len = 128 or 256), same stage order as the store kernel; then the +-1 signs.
+__device__ __forceinline__ float block_wht(float v, int wht_len, const float* signs, float* xs) {
+    const int tid = threadIdx.x, lane = tid & 31;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, s);
+        v = ((lane & s) == 0) ? (v + o) : (o - v);
+    }
+    xs[tid] = v;
+    __syncthreads();
+    for (int s = 32; s < wht_len; s <<= 1) {
+        const int j = tid ^ s;
+        const float x0 = xs[tid], x1 = xs[j];
+        __syncthreads();
+        xs[tid] = (tid < j) ? (x0 + x1) : (x1 - x0);
+        __syncthreads();
+    }
+    v = xs[tid] * (wht_len == 128 ? 0.08838834764831845f : 0.0625f);
+    if (signs) v *= signs[tid];
+    return v;
+}
+
+}  // namespace
+
 __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     const int hq = blockIdx.x;
     const int b = blockIdx.y;
@@ -17,6 +44,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     const int d = threadIdx.x;
     __shared__ int red[8];
     __shared__ int s_prefix;
+    __shared__ float xs[256];
     // chunks of the sequences before b
     int mine = 0;
     for (int bb = d; bb < b; bb += 256) {
@@ -63,13 +91,15 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
         return;
     }
     float out = l > 0.f ? acc / l : 0.f;
+    if (a.wht_len) out = block_wht(out, a.wht_len, a.signs, xs);
     if (a.gate) out *= 1.f / (1.f + expf(-a.gate[oi]));
     a.o[oi] = out;
 }
 
 __global__ void __launch_bounds__(256)
 lse_combine_kernel(const float* part_o, const float* part_ml, const float* gate, float* o,
-                   int n_parts, int rows) {
+                   int n_parts, int rows, int wht_len, const float* signs) {
+    __shared__ float xs[256];
     const int row = blockIdx.x;
     const int d = threadIdx.x;
     float mm = -1e30f;
@@ -82,6 +112,7 @@ lse_combine_kernel(const float* part_o, const float* part_ml, const float* gate,
         acc += part_o[r * kHeadDim + d] * al;
     }
     float out = l > 0.f ? acc / l : 0.f;
+    if (wht_len) out = block_wht(out, wht_len, signs, xs);
     const size_t oi = size_t(row) * kHeadDim + d;
     if (gate) out *= 1.f / (1.f + expf(-gate[oi]));
     o[oi] = out;

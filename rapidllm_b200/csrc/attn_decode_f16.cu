@@ -19,7 +19,7 @@
 // the end of an item the warps' (m, l, acc) merge in shared memory into one
 // partial per (item, head); attn_combine.cu merges the items and applies the
 // sigmoid gate.
-#include "common.cuh"
+#include "attn_split.cuh"
 #include "kernels.h"
 
 namespace rl {
@@ -29,7 +29,8 @@ namespace {
 constexpr int kStageTokens = 32;                 // half a page
 constexpr int kStages = 6;
 constexpr int kSlots = 3;                        // consumer warp pairs
-constexpr int kConsumerWarps = kSlots * 2;
+constexpr int kConsumerWarps = split::kConsumerWarps;
+static_assert(kConsumerWarps == 2 * kSlots, "two warps per stage in flight");
 // 6 consumer warps + 1 producer warp + 1 idle warp: 256 threads lets every thread have 255 registers
 constexpr int kThreads = 256;
 constexpr int kSubTiles = kHeadDim / 64;         // 4
@@ -37,46 +38,16 @@ constexpr int kStageKBytes = kStageTokens * kHeadDim * 2;  // 16 KiB
 constexpr int kStageBytes = 2 * kStageKBytes;              // K + V
 constexpr int kSubTileStageBytes = kStageTokens * 128;     // 4 KiB
 constexpr int kSubTilePageBytes = kPageTokens * 128;       // 8 KiB
-constexpr int kMaxBatch = 1024;
-constexpr float kNegBig = -1e30f;
-constexpr int kMergeStride = kHeadDim + 1;
-static_assert(kConsumerWarps == 6, "the item merge below is a fixed tree over six warps");
+using split::kNegBig;
+using split::Item;
+using split::decode_item;
 
 struct Smem {
     alignas(128) unsigned char stage[kStages][kStageBytes];
-    float o[3][8][kMergeStride];    // item merge buffers (row stride 257: conflict-free)
-    float m[kConsumerWarps][8];
-    float l[kConsumerWarps][8];
-    int prefix[kMaxBatch + 1];      // chunks before sequence b
+    split::Shared sp;
     uint64_t full[kStages];
     uint64_t empty[kStages];
 };
-
-struct Item {
-    int b, h, first_tok, n_tok;     // tokens [first_tok, first_tok+n_tok) of sequence b
-    int page0;                      // first page index (in the sequence's table)
-};
-
-__device__ __forceinline__ Item decode_item(const Smem& s, int item, int batch, int n_kv,
-                                            int chunk_pages, const int32_t* seq_lens, int len_add) {
-    Item it;
-    const int ci = item / n_kv;
-    it.h = item - ci * n_kv;
-    int lo = 0, hi = batch;         // largest b with prefix[b] <= ci
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (s.prefix[mid] <= ci) lo = mid; else hi = mid;
-    }
-    it.b = lo;
-    const int c = ci - s.prefix[lo];
-    it.page0 = c * chunk_pages;
-    it.first_tok = it.page0 * kPageTokens;
-    const int len = seq_lens[lo] + len_add;
-    int end = it.first_tok + chunk_pages * kPageTokens;
-    if (end > len) end = len;
-    it.n_tok = end - it.first_tok;
-    return it;
-}
 
 }  // namespace
 
@@ -90,33 +61,9 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     const int G = a.n_q / a.n_kv;
 
     // chunk prefix over the batch (every CTA computes the same table)
-    if (warp == 0) {
-        int run = 0;
-        for (int b0 = 0; b0 < a.batch; b0 += 32) {
-            const int b = b0 + lane;
-            int n = 0;
-            if (b < a.batch) {
-                int len = a.seq_lens[b] + a.len_add;
-                if (len < 0 || len > a.max_pages_per_seq * kPageTokens) {
-                    set_err(a.err, DEV_ERR_BAD_LEN);
-                    len = 0;
-                }
-                const int pages = (len + kPageTokens - 1) / kPageTokens;
-                n = (pages + a.chunk_pages - 1) / a.chunk_pages;
-            }
-            int inc = n;
-            for (int off = 1; off < 32; off <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, inc, off);
-                if (lane >= off) inc += t;
-            }
-            if (b < a.batch) s.prefix[b] = run + inc - n;
-            run += __shfl_sync(0xffffffffu, inc, 31);
-        }
-        if (lane == 0) {
-            s.prefix[a.batch] = run;
-            if (run > a.max_chunks) set_err(a.err, DEV_ERR_WORKSPACE);
-        }
-    }
+    if (warp == 0)
+        split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.chunk_pages,
+                            a.max_chunks, a.err, lane);
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
@@ -125,7 +72,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
         mbar_fence_init();
     }
     __syncthreads();
-    int total_chunks = s.prefix[a.batch];
+    int total_chunks = s.sp.prefix[a.batch];
     if (total_chunks > a.max_chunks) total_chunks = a.max_chunks;
     const int total_items = total_chunks * a.n_kv;
 
@@ -135,7 +82,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
         if (lane != 0) return;
         uint32_t it = 0;
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-            const Item w = decode_item(s, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
+            const Item w = decode_item(s.sp, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
             const int n_half = (w.n_tok + kStageTokens - 1) / kStageTokens;
             for (int hp = 0; hp < n_half; ++hp, ++it) {
                 const int st = it % kStages;
@@ -179,7 +126,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     uint32_t it = 0;
     bool alive = true;   // false after a wait gave up: keep arriving at barriers, touch no data
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-        const Item w = decode_item(s, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
+        const Item w = decode_item(s.sp, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
         const int n_half = (w.n_tok + kStageTokens - 1) / kStageTokens;
 
         // query fragments: rows 0-7 fp16(q), rows 8-15 fp16(q - fp16(q))
@@ -320,96 +267,12 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
             if (lane == 0) mbar_arrive(&s.empty[st]);
         }
 
-        // ------------------------ merge the warps of this item ------------------------
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-        if (c == 0) {
-            s.m[warp][g] = m_run;
-            s.l[warp][g] = l_run;
-        }
-        named_bar_sync(1, kConsumerWarps * 32);
-        // scale this warp's accumulators to the item-wide maximum
-        {
-            float f[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                float mm = kNegBig;
-#pragma unroll
-                for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
-                f[e] = fast_exp2(s.m[warp][2 * c + e] - mm);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    acc[j][i][0] *= f[0];
-                    acc[j][i][2] *= f[0];
-                    acc[j][i][1] *= f[1];
-                    acc[j][i][3] *= f[1];
-                }
-        }
-        // Fixed-order tree over the six warps (bit-reproducible, unlike atomics):
-        // warps 3,4,5 -> buffers 0,1,2; warps 0,1,2 add; warps 1,2 -> buffers 0,1; warp 0 adds
-        // them in order and leaves the item's total in buffer 2.  Lanes with pg >= 4 touch
-        // the odd dim first so that a warp's 32 accesses hit 32 banks (row stride 257).
-        const int odd = pg >> 2;
-        auto put = [&](float (*buf)[kMergeStride]) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int d = 64 * j + 8 * pg + 2 * i;
-                    buf[2 * c][d + odd] = odd ? acc[j][i][2] : acc[j][i][0];
-                    buf[2 * c][d + 1 - odd] = odd ? acc[j][i][0] : acc[j][i][2];
-                    buf[2 * c + 1][d + odd] = odd ? acc[j][i][3] : acc[j][i][1];
-                    buf[2 * c + 1][d + 1 - odd] = odd ? acc[j][i][1] : acc[j][i][3];
-                }
-        };
-        auto add = [&](const float (*buf)[kMergeStride]) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int d = 64 * j + 8 * pg + 2 * i;
-                    const float x0 = buf[2 * c][d + odd], x1 = buf[2 * c][d + 1 - odd];
-                    const float y0 = buf[2 * c + 1][d + odd], y1 = buf[2 * c + 1][d + 1 - odd];
-                    acc[j][i][0] += odd ? x1 : x0;
-                    acc[j][i][2] += odd ? x0 : x1;
-                    acc[j][i][1] += odd ? y1 : y0;
-                    acc[j][i][3] += odd ? y0 : y1;
-                }
-        };
-        if (warp >= 3) put(s.o[warp - 3]);
-        named_bar_sync(1, kConsumerWarps * 32);
-        if (warp < 3) add(s.o[warp]);
-        named_bar_sync(1, kConsumerWarps * 32);
-        if (warp == 1 || warp == 2) put(s.o[warp - 1]);
-        named_bar_sync(1, kConsumerWarps * 32);
-        if (warp == 0) {
-            add(s.o[0]);
-            add(s.o[1]);
-            put(s.o[2]);
-        }
-        named_bar_sync(1, kConsumerWarps * 32);
-        {
-            float* po = a.part_o + size_t(item) * G * kHeadDim;
-            for (int x = tid; x < G * kHeadDim; x += kConsumerWarps * 32)
-                po[x] = s.o[2][x >> 8][x & (kHeadDim - 1)];
-            if (tid < G) {
-                float mm = kNegBig;
-                for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][tid]);
-                float ll = 0.f;
-                for (int ww = 0; ww < kConsumerWarps; ++ww) ll += s.l[ww][tid] * fast_exp2(s.m[ww][tid] - mm);
-                a.part_ml[(size_t(item) * G + tid) * 2 + 0] = mm * 0.6931471805599453f;  // natural-log units
-                a.part_ml[(size_t(item) * G + tid) * 2 + 1] = ll;
-            }
-        }
-        named_bar_sync(1, kConsumerWarps * 32);
+        split::merge_item(s.sp, acc, m_run, l_run, warp, lane, pg, G, a.part_o, a.part_ml, size_t(item));
     }
 }
 
 size_t attn_decode_f16_smem_bytes() { return sizeof(Smem) + 128; }
 int attn_decode_f16_threads() { return kThreads; }
-int attn_decode_max_batch() { return kMaxBatch; }
+int attn_decode_max_batch() { return split::kMaxBatch; }
 
 }  // namespace rl

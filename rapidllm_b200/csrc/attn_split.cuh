@@ -1,0 +1,171 @@
+// Pieces shared by the split-KV decode kernels (F16 and compact KV): the work
+// item table, and the fixed-order merge of the six consumer warps of a CTA.
+#pragma once
+#include "common.cuh"
+
+namespace rl {
+namespace split {
+
+constexpr int kConsumerWarps = 6;            // three pairs; the merge below is a tree over six
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kMaxBatch = 1024;
+constexpr float kNegBig = -1e30f;
+constexpr int kMergeStride = kHeadDim + 1;   // row stride 257 floats: conflict-free
+
+struct Shared {
+    float o[3][8][kMergeStride];    // item merge buffers
+    float m[kConsumerWarps][8];
+    float l[kConsumerWarps][8];
+    int prefix[kMaxBatch + 1];      // chunks before sequence b
+};
+
+struct Item {
+    int b, h;
+    int page0;                      // first page index in the sequence's table row
+    int n_tok;                      // tokens of this item: [page0 * 64, page0 * 64 + n_tok)
+};
+
+// Warp 0 fills s.prefix: a work item is (sequence, chunk of chunk_pages pages, KV head);
+// lengths outside [0, max_pages_per_seq * 64] count as 0 and are reported.
+__device__ __forceinline__ void build_prefix(Shared& s, const int32_t* seq_lens, int len_add, int batch,
+                                             int max_pages_per_seq, int chunk_pages, int max_chunks, int* err,
+                                             int lane) {
+    int run = 0;
+    for (int b0 = 0; b0 < batch; b0 += 32) {
+        const int b = b0 + lane;
+        int n = 0;
+        if (b < batch) {
+            int len = seq_lens[b] + len_add;
+            if (len < 0 || len > max_pages_per_seq * kPageTokens) {
+                set_err(err, DEV_ERR_BAD_LEN);
+                len = 0;
+            }
+            const int pages = (len + kPageTokens - 1) / kPageTokens;
+            n = (pages + chunk_pages - 1) / chunk_pages;
+        }
+        int inc = n;
+        for (int off = 1; off < 32; off <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) inc += t;
+        }
+        if (b < batch) s.prefix[b] = run + inc - n;
+        run += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) {
+        s.prefix[batch] = run;
+        if (run > max_chunks) set_err(err, DEV_ERR_WORKSPACE);
+    }
+}
+
+__device__ __forceinline__ Item decode_item(const Shared& s, int item, int batch, int n_kv, int chunk_pages,
+                                            const int32_t* seq_lens, int len_add) {
+    Item it;
+    const int ci = item / n_kv;
+    it.h = item - ci * n_kv;
+    int lo = 0, hi = batch;         // largest b with prefix[b] <= ci
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s.prefix[mid] <= ci) lo = mid; else hi = mid;
+    }
+    it.b = lo;
+    it.page0 = (ci - s.prefix[lo]) * chunk_pages;
+    const int first = it.page0 * kPageTokens;
+    int end = first + chunk_pages * kPageTokens;
+    const int len = seq_lens[lo] + len_add;
+    if (end > len) end = len;
+    it.n_tok = end - first;
+    return it;
+}
+
+// Merge the consumer warps' partial results of one item and write the item's partial.
+// acc[j][i][0..3] of lane (g, c) holds dims d = 64j + 8*dsel + 2i (+1 for [2],[3]) of heads
+// 2c ([0],[2]) and 2c+1 ([1],[3]); m_run is the running maximum (log2 domain) of head g and
+// l_run this lane's share of the row sum.  All consumer threads must call this.
+__device__ __forceinline__ void merge_item(Shared& s, float (&acc)[4][4][4], float m_run, float l_run, int warp,
+                                           int lane, int dsel, int G, float* part_o, float* part_ml,
+                                           size_t item) {
+    const int g = lane >> 2, c = lane & 3;
+    const int tid = warp * 32 + lane;
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (c == 0) {
+        s.m[warp][g] = m_run;
+        s.l[warp][g] = l_run;
+    }
+    named_bar_sync(1, kConsumerThreads);
+    {   // scale this warp's accumulators to the item-wide maximum
+        float f[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float mm = kNegBig;
+#pragma unroll
+            for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
+            f[e] = fast_exp2(s.m[warp][2 * c + e] - mm);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[j][i][0] *= f[0];
+                acc[j][i][2] *= f[0];
+                acc[j][i][1] *= f[1];
+                acc[j][i][3] *= f[1];
+            }
+    }
+    // Fixed-order tree (bit-reproducible, unlike atomics): warps 3,4,5 -> buffers 0,1,2; warps
+    // 0,1,2 add; warps 1,2 -> buffers 0,1; warp 0 adds them in order and leaves the total in
+    // buffer 2.  Lanes with dsel >= 4 touch the odd dim first so a warp's 32 accesses hit 32 banks.
+    const int odd = dsel >> 2;
+    auto put = [&](float (*buf)[kMergeStride]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int d = 64 * j + 8 * dsel + 2 * i;
+                buf[2 * c][d + odd] = odd ? acc[j][i][2] : acc[j][i][0];
+                buf[2 * c][d + 1 - odd] = odd ? acc[j][i][0] : acc[j][i][2];
+                buf[2 * c + 1][d + odd] = odd ? acc[j][i][3] : acc[j][i][1];
+                buf[2 * c + 1][d + 1 - odd] = odd ? acc[j][i][1] : acc[j][i][3];
+            }
+    };
+    auto add = [&](const float (*buf)[kMergeStride]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int d = 64 * j + 8 * dsel + 2 * i;
+                const float x0 = buf[2 * c][d + odd], x1 = buf[2 * c][d + 1 - odd];
+                const float y0 = buf[2 * c + 1][d + odd], y1 = buf[2 * c + 1][d + 1 - odd];
+                acc[j][i][0] += odd ? x1 : x0;
+                acc[j][i][2] += odd ? x0 : x1;
+                acc[j][i][1] += odd ? y1 : y0;
+                acc[j][i][3] += odd ? y0 : y1;
+            }
+    };
+    if (warp >= 3) put(s.o[warp - 3]);
+    named_bar_sync(1, kConsumerThreads);
+    if (warp < 3) add(s.o[warp]);
+    named_bar_sync(1, kConsumerThreads);
+    if (warp == 1 || warp == 2) put(s.o[warp - 1]);
+    named_bar_sync(1, kConsumerThreads);
+    if (warp == 0) {
+        add(s.o[0]);
+        add(s.o[1]);
+        put(s.o[2]);
+    }
+    named_bar_sync(1, kConsumerThreads);
+    float* po = part_o + item * G * kHeadDim;
+    for (int x = tid; x < G * kHeadDim; x += kConsumerThreads) po[x] = s.o[2][x >> 8][x & (kHeadDim - 1)];
+    if (tid < G) {
+        float mm = kNegBig;
+        for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][tid]);
+        float ll = 0.f;
+        for (int ww = 0; ww < kConsumerWarps; ++ww) ll += s.l[ww][tid] * fast_exp2(s.m[ww][tid] - mm);
+        part_ml[(item * G + tid) * 2 + 0] = mm * 0.6931471805599453f;   // natural-log units
+        part_ml[(item * G + tid) * 2 + 1] = ll;
+    }
+    named_bar_sync(1, kConsumerThreads);
+}
+
+}  // namespace split
+}  // namespace rl

@@ -112,4 +112,20 @@ __host__ __device__ __forceinline__ int kv_slice_offset(int tok, int d) {
     return sub * (kPageTokens * 64) + tok * 64 + chunk * 8 + (d & 7);
 }
 
+
+// ---- compact KV records (q8 K + TQ3 V), one per (page, head, half page) -----------
+constexpr int kCompactHalfTokens = 32;
+constexpr int kCompactVOff = 8192;
+constexpr int kCompactKScaleOff = 11264;
+constexpr int kCompactVScaleOff = 11328;
+constexpr int kCompactRecordBytes = 11456;
+// Byte offset, inside a record, of the 6 bytes holding the codes of dims 64j + 8g .. +7 for
+// the token pair that contains row `row` (0..31): V codes are grouped per 16-token block as
+// [pair half AB = 0,1][g = 0..7][c = 0..3][24 B] so that the 16 lanes (g, c) of a half warp read
+// 16 consecutive 24-byte groups (conflict-free 8-byte loads).
+__host__ __device__ __forceinline__ int compact_v_offset(int row, int g, int j) {
+    const int q = (row & 15) >> 1;
+    return kCompactVOff + (row >> 4) * 1536 + (q >> 2) * 768 + g * 96 + (q & 3) * 24 + j * 6;
+}
+
 }  // namespace rl

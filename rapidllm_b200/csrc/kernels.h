@@ -24,6 +24,10 @@ struct AttnDecodeArgs {
     float scale;                 // 1/sqrt(head_dim)
 };
 __global__ void attn_decode_f16_kernel(AttnDecodeArgs a);
+// same arguments over the compact cache: k_pool = record pool (kv_compact.cu), v_pool unused
+__global__ void attn_decode_tq_kernel(AttnDecodeArgs a);
+size_t attn_decode_tq_smem_bytes();
+int attn_decode_tq_threads();
 size_t attn_decode_f16_smem_bytes();
 int attn_decode_f16_threads();
 int attn_decode_max_batch();
@@ -38,13 +42,15 @@ struct AttnCombineArgs {
     float* out_ml;               // null, or [batch][n_q][2] (max, sum): emit one partial per row
     int batch, n_q, n_kv, chunk_pages, max_chunks, page_tokens, len_add;
     int max_len;                 // lengths outside [0, max_len] count as 0, as in the decode kernel
+    int wht_len;                 // 0, or 128 / 256: the partials are in the rotated domain of TQ3 V
+    const float* signs;          // [256] +-1 applied after the inverse transform, or null
 };
 __global__ void attn_combine_kernel(AttnCombineArgs a);
 
 // Generic merge of n_parts partials per row (used across GPUs):
 // part_o [n_parts][rows][256], part_ml [n_parts][rows][2]
 __global__ void lse_combine_kernel(const float* part_o, const float* part_ml, const float* gate,
-                                   float* o, int n_parts, int rows);
+                                   float* o, int n_parts, int rows, int wht_len, const float* signs);
 
 // ---- KV cache maintenance ------------------------------------------------------------
 // Write rows [n_tok][n_kv][256] (fp32 or fp16) of sequence b at positions pos0.. into the pool.
@@ -64,6 +70,22 @@ __global__ void kv_write_kernel(KvWriteArgs a);
 // Read tokens [0, n_tok) of one sequence back as contiguous fp16 [n_tok][n_kv][256].
 __global__ void kv_gather_kernel(const __half* pool, const int32_t* table, __half* out, int n_tok,
                                  int n_kv, int n_pages, int* err);
+
+// ---- compact KV (q8 K + TQ3 V) ---------------------------------------------------------
+struct KvCompactWriteArgs {
+    unsigned char* pool;         // [n_pages][n_kv][2] records of kCompactRecordBytes
+    const int32_t* page_table;
+    const int32_t* pos;          // [batch] or null
+    const float* k_rows;         // [batch][n_tok][n_kv][256] fp32
+    const float* v_rows;
+    const float* signs;          // [256] +-1 (wht_len 256) or null
+    int* err;
+    int batch, n_tok, n_kv, n_pages, max_pages_per_seq, pos0, wht_len;
+};
+__global__ void kv_compact_write_kernel(KvCompactWriteArgs a);
+__global__ void kv_compact_gather_kernel(const unsigned char* pool, const int32_t* table, signed char* k_q,
+                                         __half* k_sc, unsigned char* v_codes, __half* v_sc, int n_tok,
+                                         int n_kv, int n_pages, int wht_len, int* err);
 
 // ---- Gated DeltaNet decode step ----------------------------------------------------
 struct DeltaDecodeArgs {

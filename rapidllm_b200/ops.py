@@ -74,21 +74,60 @@ def kv_gather(pool, page_table_row, n_tok):
     return out
 
 
+def new_compact_pool(n_pages: int, n_kv: int, device="cuda") -> torch.Tensor:
+    """A zeroed byte pool [n_pages][n_kv][page bytes] for the q8-K / TQ3-V cache."""
+    return torch.zeros(n_pages, n_kv, lib().rl_kv_compact_page_bytes(), dtype=torch.uint8, device=device)
+
+
+def kv_compact_append(pool, page_table, k_rows, v_rows, wht_len=128, signs=None, pos=None, pos0=0):
+    """Quantise fp32 rows [batch][n_tok][n_kv][256] into the compact cache at pos[b] (+0..n_tok-1)."""
+    n_pages, n_kv = pool.shape[0], pool.shape[1]
+    if k_rows.dim() == 3:
+        k_rows, v_rows = k_rows.unsqueeze(0), v_rows.unsqueeze(0)
+    if page_table.dim() == 1:
+        page_table = page_table.unsqueeze(0)
+    for t, n in ((k_rows, "k_rows"), (v_rows, "v_rows"), (signs, "signs")):
+        _need(t, torch.float32, n)
+    _need(page_table, torch.int32, "page_table")
+    _need(pos, torch.int32, "pos")
+    p = KvAppendParams(n_kv=n_kv, head_dim=HEAD_DIM, batch=k_rows.shape[0], n_tok=k_rows.shape[1],
+                       page_tokens=PAGE_TOKENS, n_pages=n_pages,
+                       max_pages_per_seq=page_table.shape[1], pos0=pos0, rows_fp16=0, wht_len=wht_len)
+    check(lib().rl_kv_compact_append(_p(pool), _p(page_table), _p(pos), _p(k_rows), _p(v_rows),
+                                     _p(signs), C.byref(p), _stream()))
+
+
+def kv_compact_gather(pool, page_table_row, n_tok, wht_len=128):
+    """Codes and scales of tokens [0, n_tok) in the reference's packing:
+    (k_q int8 [n,n_kv,256], k_sc fp16 [n,n_kv], v_codes u8 [n,n_kv,96], v_sc fp16 [n,n_kv,256/wht])."""
+    n_pages, n_kv = pool.shape[0], pool.shape[1]
+    dev = pool.device
+    k_q = torch.empty(n_tok, n_kv, HEAD_DIM, dtype=torch.int8, device=dev)
+    k_sc = torch.empty(n_tok, n_kv, dtype=torch.float16, device=dev)
+    v_codes = torch.empty(n_tok, n_kv, 96, dtype=torch.uint8, device=dev)
+    v_sc = torch.empty(n_tok, n_kv, HEAD_DIM // wht_len, dtype=torch.float16, device=dev)
+    check(lib().rl_kv_compact_gather(_p(pool), _p(page_table_row), _p(k_q), _p(k_sc), _p(v_codes),
+                                     _p(v_sc), n_tok, n_kv, n_pages, wht_len, _stream()))
+    return k_q, k_sc, v_codes, v_sc
+
+
 def attn_params(n_q, n_kv, batch, n_pages, max_pages_per_seq, max_seq_len, len_add=0,
-                chunk_pages=0):
-    return AttnDecodeParams(n_q=n_q, n_kv=n_kv, head_dim=HEAD_DIM, kv_dtype=_lib.RL_KV_F16,
+                chunk_pages=0, kv_dtype=_lib.RL_KV_F16, wht_len=128, signs=None):
+    return AttnDecodeParams(n_q=n_q, n_kv=n_kv, head_dim=HEAD_DIM, kv_dtype=kv_dtype,
                             batch=batch, page_tokens=PAGE_TOKENS, n_pages=n_pages,
                             max_pages_per_seq=max_pages_per_seq, max_seq_len=max_seq_len,
-                            len_add=len_add, chunk_pages=chunk_pages, wht_len=128)
+                            len_add=len_add, chunk_pages=chunk_pages, wht_len=wht_len,
+                            tq_signs=None if signs is None else signs.data_ptr())
 
 
 def attn_decode(q, k_pool, v_pool, page_table, seq_lens, gate=None, max_seq_len=None,
-                chunk_pages=0, workspace=None, out=None, partial=False):
+                chunk_pages=0, workspace=None, out=None, partial=False, wht_len=128, signs=None):
     """ops::attn_decode for a ragged batch over the paged F16 cache, then o *= sigmoid(gate).
 
     q, gate [batch][n_q][256] fp32; page_table int32 [batch][max_pages]; seq_lens int32
     [batch] on the device.  With partial=True returns (part_o, part_ml) per (sequence,
-    head) for a cross-GPU merge with lse_combine.
+    head) for a cross-GPU merge with lse_combine.  A uint8 k_pool (new_compact_pool) selects
+    the q8-K / TQ3-V cache (v_pool is then ignored; wht_len 128 or 256, signs for 256).
     """
     _need(q, torch.float32, "q")
     _need(gate, torch.float32, "gate")
@@ -98,7 +137,10 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, gate=None, max_seq_len=
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
     if max_seq_len is None:
         max_seq_len = page_table.shape[1] * PAGE_TOKENS
-    p = attn_params(n_q, n_kv, batch, n_pages, page_table.shape[1], max_seq_len, 0, chunk_pages)
+    compact = k_pool.dtype == torch.uint8
+    _need(signs, torch.float32, "signs")
+    p = attn_params(n_q, n_kv, batch, n_pages, page_table.shape[1], max_seq_len, 0, chunk_pages,
+                    _lib.RL_KV_Q8K_TQ3V if compact else _lib.RL_KV_F16, wht_len, signs)
     need = lib().rl_attn_decode_workspace_bytes(C.byref(p))
     if need == 0 and batch > 0:
         raise _lib.RlError(6, lib().rl_last_error().decode())
@@ -117,14 +159,15 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, gate=None, max_seq_len=
     return o
 
 
-def lse_combine(part_o, part_ml, gate=None):
-    """Merge partials [n_parts][rows][256] / [n_parts][rows][2] -> o [rows][256]."""
+def lse_combine(part_o, part_ml, gate=None, wht_len=0, signs=None):
+    """Merge partials [n_parts][rows][256] / [n_parts][rows][2] -> o [rows][256]
+    (wht_len 128/256: partials of the compact cache, still in the rotated domain)."""
     _need(part_o, torch.float32, "part_o")
     _need(part_ml, torch.float32, "part_ml")
     n_parts, rows, hd = part_o.shape
     o = torch.empty(rows, hd, dtype=torch.float32, device=part_o.device)
     check(lib().rl_lse_combine(_p(part_o), _p(part_ml), _p(gate), _p(o), n_parts, rows, hd,
-                               _stream()))
+                               wht_len, _p(signs), _stream()))
     return o
 
 

@@ -46,5 +46,7 @@ def test_argument_errors_follow_reference_status_codes():
     assert L.rl_delta_recurrent(None, None, None, None, None, None, None, None, C.byref(d), None) == 6
     c = _lib.Conv1dParams(dim=10240, k=4, silu=0, batch=1, n_slots=1)
     assert L.rl_conv1d_update(None, None, None, None, None, C.byref(c), None) == 4
-    assert L.rl_lse_combine(None, None, None, None, 0, 4, 256, None) == 6
+    assert L.rl_lse_combine(None, None, None, None, 0, 4, 256, 0, None, None) == 6
+    assert L.rl_lse_combine(None, None, None, None, 2, 4, 256, 64, None, None) == 4
+    assert L.rl_kv_compact_page_bytes() == 2 * 11456
     assert L.rl_device_error_string(1).startswith(b"page-table")

@@ -1,0 +1,124 @@
+"""q8-K + TurboQuant-3-V compact cache: bit-exact codes and decode attention vs the oracle
+(the CPU restatement of the reference's CUDA store/dequant math; no reference test pins it)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import ATTN_MAX_ABS, ATTN_REL_L2, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+N_Q, N_KV, HD = 24, 4, 256
+
+
+def _signs(gen):
+    return (2.0 * torch.bernoulli(torch.full((256,), 0.5), generator=gen) - 1.0).float()
+
+
+def _table(lens, gen, extra=2):
+    pages = [(n + 63) // 64 for n in lens]
+    n_pages = sum(pages) + extra
+    perm = torch.randperm(n_pages, generator=gen).int()
+    table = torch.zeros(len(lens), max(1, max(pages)), dtype=torch.int32)
+    at = 0
+    for b, p in enumerate(pages):
+        table[b, :p] = perm[at:at + p]
+        at += p
+    return table.cuda(), n_pages
+
+
+@pytest.mark.parametrize("wht_len,use_signs", [(128, False), (256, True)])
+def test_codes_are_bit_exact(oracle, wht_len, use_signs):
+    """Store (prefill rows, then single-token appends) -> gather == oracle codes and scales."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(2)
+    n = 64 * 2 + 37
+    k = torch.randn(n, N_KV, HD, generator=gen)
+    v = torch.randn(n, N_KV, HD, generator=gen)
+    k[3] *= 1e-3                                   # small rows, a zero row, an outlier
+    v[5] = 0.0
+    k[7, 1, 11] = 40.0
+    signs = _signs(gen) if use_signs else None
+    sd = signs.cuda() if use_signs else None
+    table, n_pages = _table([n], gen)
+    pool = ops.new_compact_pool(n_pages, N_KV)
+    ops.kv_compact_append(pool, table, k[:101].cuda(), v[:101].cuda(), wht_len, sd, pos0=0)
+    for t in range(101, n):                        # decode-style appends, device-resident position
+        pos = torch.tensor([t], dtype=torch.int32, device="cuda")
+        ops.kv_compact_append(pool, table, k[t:t + 1].cuda(), v[t:t + 1].cuda(), wht_len, sd, pos=pos)
+    _lib.check_device()
+    k_q, k_sc, v_codes, v_sc = ops.kv_compact_gather(pool, table[0], n, wht_len)
+    rk_q, rk_sc, rv_codes, rv_sc = oracle.compact_store(k.numpy(), v.numpy(), wht_len,
+                                                        None if signs is None else signs.numpy())
+    assert np.array_equal(k_q.cpu().numpy(), rk_q)
+    assert np.array_equal(k_sc.cpu().numpy().view(np.uint16), rk_sc)
+    assert np.array_equal(v_sc.cpu().numpy().view(np.uint16), rv_sc)
+    assert np.array_equal(v_codes.cpu().numpy(), rv_codes)
+    # overwriting a token leaves its pair partner untouched
+    ops.kv_compact_append(pool, table, k[10:11].cuda(), v[10:11].cuda(), wht_len, sd, pos0=10)
+    again = ops.kv_compact_gather(pool, table[0], n, wht_len)
+    assert torch.equal(again[2], v_codes) and torch.equal(again[0], k_q)
+
+
+@pytest.mark.parametrize("wht_len,use_signs", [(128, False), (256, True)])
+def test_decode_over_compact_cache(oracle, wht_len, use_signs):
+    """Ragged batch; oracle = dequantise (per-token inverse transform) -> ops::attn_decode -> gate."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(22)
+    lens = [1, 31, 32, 33, 64, 65, 700, 0, 1000]
+    signs = _signs(gen) if use_signs else None
+    sd = signs.cuda() if use_signs else None
+    q = torch.randn(len(lens), N_Q, HD, generator=gen)
+    gate = torch.randn(len(lens), N_Q, HD, generator=gen)
+    ks = [torch.randn(n, N_KV, HD, generator=gen) for n in lens]
+    vs = [torch.randn(n, N_KV, HD, generator=gen) for n in lens]
+    table, n_pages = _table(lens, gen)
+    pool = ops.new_compact_pool(n_pages, N_KV)
+    pool.fill_(0xFF)                               # unused rows hold NaN scales / arbitrary codes
+    for b, n in enumerate(lens):
+        if n:
+            ops.kv_compact_append(pool, table[b], ks[b].cuda(), vs[b].cuda(), wht_len, sd, pos0=0)
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    outs = [ops.attn_decode(q.cuda(), pool, None, table, sl, gate.cuda(), wht_len=wht_len, signs=sd,
+                            chunk_pages=cp) for cp in (0, 1, 4)]
+    _lib.check_device()
+    sn = None if signs is None else signs.numpy()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert not outs[0][b].any()
+            continue
+        kd, vd = oracle.compact_dequant(*oracle.compact_store(ks[b].numpy(), vs[b].numpy(), wht_len, sn),
+                                        wht_len, sn)
+        ref = oracle.gated_attn_decode(q[b].numpy(), kd, vd, gate[b].numpy())
+        for o in outs:
+            ob = o[b].cpu().numpy()
+            assert np.isfinite(ob).all()
+            assert np.abs(ob - ref).max() <= ATTN_MAX_ABS, (b, np.abs(ob - ref).max())
+            assert rel_l2(ob, ref) <= ATTN_REL_L2, (b, rel_l2(ob, ref))
+        print("compact decode wht%d len %d: max-abs %.3e rel-l2 %.3e" %
+              (wht_len, n, np.abs(outs[0][b].cpu().numpy() - ref).max(), rel_l2(outs[0][b].cpu().numpy(), ref)))
+
+
+def test_compact_partials_merge_across_token_ranges(oracle):
+    """Split-KV across two 'GPUs': rotated-domain partials merged by lse_combine(wht_len)."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(23)
+    n, cut = 500, 256
+    q = torch.randn(1, N_Q, HD, generator=gen)
+    gate = torch.randn(1, N_Q, HD, generator=gen)
+    k = torch.randn(n, N_KV, HD, generator=gen)
+    v = torch.randn(n, N_KV, HD, generator=gen)
+    parts = []
+    for a, b in ((0, cut), (cut, n)):
+        table, n_pages = _table([b - a], gen)
+        pool = ops.new_compact_pool(n_pages, N_KV)
+        ops.kv_compact_append(pool, table[0], k[a:b].cuda(), v[a:b].cuda(), 128, None, pos0=0)
+        parts.append(ops.attn_decode(q.cuda(), pool, None, table,
+                                     torch.tensor([b - a], dtype=torch.int32, device="cuda"), partial=True))
+    po = torch.stack([p[0].reshape(-1, HD) for p in parts])
+    pml = torch.stack([p[1].reshape(-1, 2) for p in parts])
+    o = ops.lse_combine(po, pml, gate.cuda().reshape(-1, HD), wht_len=128).cpu().numpy()
+    _lib.check_device()
+    kd, vd = oracle.compact_dequant(*oracle.compact_store(k.numpy(), v.numpy(), 128), 128)
+    ref = oracle.gated_attn_decode(q[0].numpy(), kd, vd, gate[0].numpy())
+    assert np.abs(o - ref).max() <= ATTN_MAX_ABS and rel_l2(o, ref) <= ATTN_REL_L2
