@@ -46,6 +46,13 @@ def parse():
     ap.add_argument("--ctx-max", type=int, default=32768)
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--seed", type=int, default=4)
+    ap.add_argument("--workload", default="stack",
+                    choices=["stack", "compact_decode", "f16_decode", "delta_step"],
+                    help="stack = the headline workload; the others time one operator at the shapes of "
+                         "BASELINE configs 2, 0 and 1 (secondary lines, N=1 only)")
+    ap.add_argument("--wht-len", type=int, default=128)
+    ap.add_argument("--op-batch", type=int, default=0, help="operator workloads: override the batch")
+    ap.add_argument("--op-ctx", type=int, default=0, help="operator workloads: override the context")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -232,10 +239,123 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------------------
+def run_operator(args):
+    """Secondary lines: one operator at the shapes of BASELINE configs 0, 1, 2 (single GPU)."""
+    import torch
+
+    import __graft_entry__ as ge
+    ge.build()
+    from rapidllm_b200 import _lib, ops
+    torch.cuda.set_device(0)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    gen = torch.Generator(device="cuda").manual_seed(args.seed)
+    wl = args.workload
+    if wl in ("compact_decode", "f16_decode"):
+        if wl == "compact_decode":
+            B, ctx = 4, 131072
+        else:
+            B, ctx = 1, 4096
+        B, ctx = args.op_batch or B, args.op_ctx or ctx
+        pages = ctx // PAGE
+        n_pages = B * pages
+        cg = torch.Generator().manual_seed(args.seed)
+        table = torch.randperm(n_pages, generator=cg).int().reshape(B, pages).cuda()
+        lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, N_Q, HD, device="cuda", generator=gen)
+        gate = torch.randn(B, N_Q, HD, device="cuda", generator=gen)
+        if wl == "compact_decode":
+            signs = None
+            if args.wht_len == 256:
+                signs = (2.0 * torch.bernoulli(torch.full((256,), 0.5, device="cuda"), generator=gen) - 1.0)
+            pool = ops.new_compact_pool(n_pages, N_KV)
+            step = 8192
+            for b in range(B):
+                for t0 in range(0, ctx, step):
+                    k = torch.randn(step, N_KV, HD, device="cuda", generator=gen)
+                    v = torch.randn(step, N_KV, HD, device="cuda", generator=gen)
+                    ops.kv_compact_append(pool, table[b], k, v, args.wht_len, signs, pos0=t0)
+            per_tok = _lib.lib().rl_kv_compact_page_bytes() // PAGE
+            call = lambda: ops.attn_decode(q, pool, None, table, lens, gate, wht_len=args.wht_len, signs=signs,
+                                           workspace=ws, out=out)
+            kernel = "attn_decode_tq_kernel"
+            name = "gated attention decode over q8k_tq3v cache, batch %d, ctx %d, 24Q/4KV hd256, wht %d" % (
+                B, ctx, args.wht_len)
+        else:
+            kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+            kp.normal_(generator=gen)
+            vp.normal_(generator=gen)
+            per_tok = HD * 2 * 2
+            call = lambda: ops.attn_decode(q, kp, vp, table, lens, gate, workspace=ws, out=out)
+            kernel = "attn_decode_f16_kernel"
+            name = "gated attention decode over F16 cache, batch %d, ctx %d, 24Q/4KV hd256" % (B, ctx)
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+        out = torch.empty_like(q)
+        bytes_per_step = B * ctx * N_KV * per_tok + B * N_Q * HD * 4 * 3
+        unit_per_step = B
+    else:
+        B = 1
+        S = torch.randn(B, N_V, DK, DV, device="cuda", generator=gen) * 0.02
+        cst = torch.zeros(B, CONV_DIM, CONV_K, device="cuda")
+        w = torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5
+        x = torch.randn(B, CONV_DIM, device="cuda", generator=gen)
+        beta = torch.sigmoid(torch.randn(B, N_V, device="cuda", generator=gen))
+        gl = -torch.nn.functional.softplus(torch.randn(B, N_V, device="cuda", generator=gen))
+        od = torch.empty(B, N_V, DV, device="cuda")
+
+        def call():
+            mixed = ops.conv1d_update(x, w, cst)
+            qk = mixed[:, :2 * N_K * DK].view(B, 2, N_K, DK)
+            ops.delta_recurrent_step(S, qk[:, 0].contiguous(), qk[:, 1].contiguous(),
+                                     mixed[:, 2 * N_K * DK:].reshape(B, N_V, DV).contiguous(), beta, gl, out=od)
+        kernel = "delta_decode_kernel (+ conv1d_update4_kernel)"
+        name = "gated DeltaNet decode step, batch 1, 16K/48V heads 128x128 FP32 state + conv k4 x 10240 (state stays in L2)"
+        bytes_per_step = algorithmic_bytes(args, [1])["delta_rule"] + algorithmic_bytes(args, [1])["conv1d_update"]
+        unit_per_step = 1
+    for _ in range(max(3, args.warmup)):
+        call()
+    _lib.check_device()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if bytes_per_step < (512 << 20) else None
+    sampler = ClockSampler(0)
+    sampler.start()
+    tot = 0.0
+    for _ in range(args.steps):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        call()
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    _lib.check_device()
+    ms = tot / args.steps
+    achieved = bytes_per_step / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "hybrid-layer decode steps/sec", "value": unit_per_step / (ms * 1e-3), "unit": "seq-steps/s (one layer)",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+        "dtype": "q8 K / tq3 V" if wl == "compact_decode" else ("f16 KV" if wl == "f16_decode" else "f32 state"),
+        "config": {"workload": name, "l2": "256 MB buffer written between iterations" if flush is not None
+                   else "inputs larger than L2", "timed": "operator call incl. its merge kernel"},
+        "clocks": clocks, "gpu_launches": args.steps * 2,
+        "roofline": {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
+                     "bytes_per_launch": bytes_per_step, "traffic": None}}), flush=True)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload != "stack":
+        run_operator(args)
         return
     import torch
     import torch.distributed as dist

@@ -78,7 +78,7 @@ typedef struct rl_attn_decode_params {
     int max_pages_per_seq;       /* row stride of page_table */
     int max_seq_len;             /* host-side upper bound of every seq_lens[b] + len_add (sizing only) */
     int len_add;                 /* tokens attended = seq_lens[b] + len_add (1 when seq_lens holds `pos`) */
-    int chunk_pages;             /* pages per split-KV work item; 0 = choose */
+    int chunk_pages;             /* least pages a persistent CTA should own (bounds the grid); 0 = 1 */
     int wht_len;                 /* TQ3 transform length: 128 (reference layout) or 256 */
     const float* tq_signs;       /* device [256] +-1 sign vector of the 256 layout, or NULL */
 } rl_attn_decode_params;

@@ -78,7 +78,7 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // ---- split-KV plan: a pure function of the parameters ----------------------------
 struct AttnPlan {
-    int chunk_pages, max_chunks, G;
+    int grid, G;
     size_t part_o_bytes, part_ml_bytes, total_bytes;
 };
 
@@ -100,22 +100,21 @@ int attn_check(const rl_attn_decode_params* p) {
     return RL_OK;
 }
 
+// One persistent CTA per SM; fewer when the work is small (a CTA should own at least
+// chunk_pages pages, default 1).  One partial slot per CTA plus one per (sequence, KV head).
 AttnPlan attn_plan(const rl_attn_decode_params* p, int sms) {
     AttnPlan pl;
     pl.G = p->n_q / p->n_kv;
-    const int pages_per_seq = ceil_div(p->max_seq_len, p->page_tokens);
-    int chunk = p->chunk_pages;
-    if (chunk <= 0) {
-        const long long page_heads = 1LL * (p->batch > 0 ? p->batch : 1) * pages_per_seq * p->n_kv;
-        const long long target = 24LL * (sms > 0 ? sms : 148);
-        chunk = int((page_heads + target - 1) / target);
-        if (chunk < 1) chunk = 1;
-        if (chunk > 64) chunk = 64;
-    }
-    pl.chunk_pages = chunk;
-    pl.max_chunks = (p->batch > 0 ? p->batch : 1) * ceil_div(pages_per_seq, chunk);
-    pl.part_o_bytes = align_up(size_t(pl.max_chunks) * p->n_kv * pl.G * rl::kHeadDim * sizeof(float), 256);
-    pl.part_ml_bytes = align_up(size_t(pl.max_chunks) * p->n_kv * pl.G * 2 * sizeof(float), 256);
+    const int batch = p->batch > 0 ? p->batch : 1;
+    const long long page_heads = 1LL * batch * ceil_div(p->max_seq_len, p->page_tokens) * p->n_kv;
+    const int per_cta = p->chunk_pages > 0 ? p->chunk_pages : 1;
+    long long grid = (page_heads + per_cta - 1) / per_cta;
+    if (grid > sms) grid = sms;
+    if (grid < 1) grid = 1;
+    pl.grid = int(grid);
+    const size_t slots = size_t(pl.grid) + size_t(batch) * p->n_kv;
+    pl.part_o_bytes = align_up(slots * pl.G * rl::kHeadDim * sizeof(float), 256);
+    pl.part_ml_bytes = align_up(slots * pl.G * 2 * sizeof(float), 256);
     pl.total_bytes = pl.part_o_bytes + pl.part_ml_bytes;
     return pl;
 }
@@ -151,12 +150,9 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     a.n_kv = p->n_kv;
     a.n_pages = p->n_pages;
     a.max_pages_per_seq = p->max_pages_per_seq;
-    a.chunk_pages = pl.chunk_pages;
-    a.max_chunks = pl.max_chunks;
     a.len_add = p->len_add;
     a.scale = 1.f / sqrtf(float(p->head_dim));
-    const long long max_items = 1LL * pl.max_chunks * p->n_kv;
-    const int grid = int(max_items < d->sms ? max_items : d->sms);
+    const int grid = pl.grid;
     if (tq)
         rl::attn_decode_tq_kernel<<<grid, rl::attn_decode_tq_threads(), rl::attn_decode_tq_smem_bytes(),
                                     as_stream(stream)>>>(a);
@@ -174,10 +170,8 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     c.batch = p->batch;
     c.n_q = p->n_q;
     c.n_kv = p->n_kv;
-    c.chunk_pages = pl.chunk_pages;
-    c.max_chunks = pl.max_chunks;
-    c.page_tokens = p->page_tokens;
     c.len_add = p->len_add;
+    c.n_ctas = grid;
     c.max_len = p->max_pages_per_seq * p->page_tokens;
     c.wht_len = (tq && !out_ml) ? p->wht_len : 0;      // partial outputs stay in the rotated domain
     c.signs = (tq && p->wht_len == 256) ? p->tq_signs : nullptr;

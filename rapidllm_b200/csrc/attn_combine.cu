@@ -42,41 +42,46 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     const int G = a.n_q / a.n_kv;
     const int h = hq / G, gi = hq - h * G;
     const int d = threadIdx.x;
-    __shared__ int red[8];
-    __shared__ int s_prefix;
+    __shared__ int red[2][8];
     __shared__ float xs[256];
-    // chunks of the sequences before b
-    int mine = 0;
-    for (int bb = d; bb < b; bb += 256) {
+    // half pages of the sequences before b, and of all sequences (the unit list of attn_split.cuh)
+    int before = 0, total = 0;
+    for (int bb = d; bb < a.batch; bb += 256) {
         int len = a.seq_lens[bb] + a.len_add;
         if (len < 0 || len > a.max_len) len = 0;
-        const int pages = (len + a.page_tokens - 1) / a.page_tokens;
-        mine += (pages + a.chunk_pages - 1) / a.chunk_pages;
+        const int n = (len + 31) >> 5;
+        total += n;
+        if (bb < b) before += n;
     }
-    for (int off = 16; off > 0; off >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, off);
-    if ((d & 31) == 0) red[d >> 5] = mine;
-    __syncthreads();
-    if (d == 0) {
-        int t = 0;
-        for (int w = 0; w < 8; ++w) t += red[w];
-        s_prefix = t;
+    for (int off = 16; off > 0; off >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, off);
+        total += __shfl_xor_sync(0xffffffffu, total, off);
+    }
+    if ((d & 31) == 0) {
+        red[0][d >> 5] = before;
+        red[1][d >> 5] = total;
     }
     __syncthreads();
-    const int prefix = s_prefix;
+    before = total = 0;
+    for (int w = 0; w < 8; ++w) {
+        before += red[0][w];
+        total += red[1][w];
+    }
     int len = a.seq_lens[b] + a.len_add;
     if (len < 0 || len > a.max_len) len = 0;
-    const int pages = (len + a.page_tokens - 1) / a.page_tokens;
-    int n_chunks = (pages + a.chunk_pages - 1) / a.chunk_pages;
-    if (prefix + n_chunks > a.max_chunks) n_chunks = max(0, a.max_chunks - prefix);
+    const int hpb = (len + 31) >> 5;
+    // this head's units are [u0, u0 + hpb); CTA k of the decode kernel owned [k*q, (k+1)*q)
+    const int u0 = before * a.n_kv + h * hpb;
+    const int q = max(1, (total * a.n_kv + a.n_ctas - 1) / a.n_ctas);
+    const int k0 = u0 / q;
+    const int k1 = hpb > 0 ? (u0 + hpb - 1) / q : k0 - 1;
+    const size_t unit = size_t(b) * a.n_kv + h;
 
     float mm = -1e30f;
-    for (int c = 0; c < n_chunks; ++c) {
-        const size_t row = (size_t(prefix + c) * a.n_kv + h) * G + gi;
-        mm = fmaxf(mm, a.part_ml[row * 2]);
-    }
+    for (int k = k0; k <= k1; ++k) mm = fmaxf(mm, a.part_ml[((k + unit) * G + gi) * 2]);
     float acc = 0.f, l = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
-        const size_t row = (size_t(prefix + c) * a.n_kv + h) * G + gi;
+    for (int k = k0; k <= k1; ++k) {
+        const size_t row = (k + unit) * G + gi;
         const float al = expf(a.part_ml[row * 2] - mm);
         l += a.part_ml[row * 2 + 1] * al;
         acc += a.part_o[row * kHeadDim + d] * al;

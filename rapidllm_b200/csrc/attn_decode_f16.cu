@@ -5,20 +5,21 @@
 // from qk_attn_decode_gqa_k 5802-5862) and computes what ops::attn_decode
 // (src/kernels/ops.cpp:575-605) computes, for a batch of ragged sequences.
 //
-// Structure: a persistent grid (one CTA per SM).  Work items are
-// (sequence, chunk of pages, KV head), all the same size, dealt round-robin.
-// One producer warp streams half pages (32 tokens of K and of V, 32 KiB) into a
-// ring of shared-memory stages with TMA bulk copies that complete on
-// mbarriers; it runs ahead across item boundaries so the HBM stream never
+// Structure: a persistent grid (one CTA per SM).  The (sequence, KV head, half
+// page) units of the whole batch form one list and every CTA owns an equal
+// contiguous share of it (attn_split.cuh), cut into segments at (sequence, head)
+// boundaries.  One producer thread streams half pages (32 tokens of K and of V,
+// 32 KiB) into a ring of shared-memory stages with TMA bulk copies that complete
+// on mbarriers; it runs ahead across segment boundaries so the HBM stream never
 // drains.  Six consumer warps (three pairs, one pair per stage in flight) each
 // own 16 tokens of a stage: scores for the whole GQA group (<= 8 query heads)
 // come from m16n8k16 tensor-core MMAs with the fp32 query split into an fp16
 // high part (MMA rows 0-7) and its fp16 residual (rows 8-15, otherwise idle), the
 // online softmax runs in registers, and P.V accumulates transposed (dims x
 // heads) so that P feeds the second MMA straight from the score registers.  At
-// the end of an item the warps' (m, l, acc) merge in shared memory into one
-// partial per (item, head); attn_combine.cu merges the items and applies the
-// sigmoid gate.
+// the end of a segment the warps' (m, l, acc) merge in shared memory into one
+// partial per (segment, head); attn_combine.cu merges the few partials of a
+// (sequence, head) and applies the sigmoid gate.
 #include "attn_split.cuh"
 #include "kernels.h"
 
@@ -39,8 +40,7 @@ constexpr int kStageBytes = 2 * kStageKBytes;              // K + V
 constexpr int kSubTileStageBytes = kStageTokens * 128;     // 4 KiB
 constexpr int kSubTilePageBytes = kPageTokens * 128;       // 8 KiB
 using split::kNegBig;
-using split::Item;
-using split::decode_item;
+using split::Segment;
 
 struct Smem {
     alignas(128) unsigned char stage[kStages][kStageBytes];
@@ -62,8 +62,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
 
     // chunk prefix over the batch (every CTA computes the same table)
     if (warp == 0)
-        split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.chunk_pages,
-                            a.max_chunks, a.err, lane);
+        split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.err, lane);
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
@@ -72,26 +71,25 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
         mbar_fence_init();
     }
     __syncthreads();
-    int total_chunks = s.sp.prefix[a.batch];
-    if (total_chunks > a.max_chunks) total_chunks = a.max_chunks;
-    const int total_items = total_chunks * a.n_kv;
+    int u_begin, u_end;
+    split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end);
 
     if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
         if (lane != 0) return;
         uint32_t it = 0;
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-            const Item w = decode_item(s.sp, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
-            const int n_half = (w.n_tok + kStageTokens - 1) / kStageTokens;
-            for (int hp = 0; hp < n_half; ++hp, ++it) {
+        for (int pos = u_begin; pos < u_end;) {
+            const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
+            pos += w.hp1 - w.hp0;
+            for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
                 const int st = it % kStages;
                 const uint32_t ph = (it / kStages) & 1;
                 if (!mbar_wait(&s.empty[st], ph ^ 1)) {
                     set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                     return;
                 }
-                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + w.page0 + (hp >> 1)];
+                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + (hp >> 1)];
                 if (page < 0 || page >= a.n_pages) {
                     set_err(a.err, DEV_ERR_BAD_PAGE);
                     page = 0;
@@ -125,9 +123,9 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
 
     uint32_t it = 0;
     bool alive = true;   // false after a wait gave up: keep arriving at barriers, touch no data
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-        const Item w = decode_item(s.sp, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
-        const int n_half = (w.n_tok + kStageTokens - 1) / kStageTokens;
+    for (int pos = u_begin; pos < u_end;) {
+        const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
+        pos += w.hp1 - w.hp0;
 
         // query fragments: rows 0-7 fp16(q), rows 8-15 fp16(q - fp16(q))
         uint32_t qhi[8][4], qlo[8][4];
@@ -163,7 +161,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
         float m_run = kNegBig;                       // log2 domain, head g
         float l_run = 0.f;                           // this lane's share of the row sum
 
-        for (int hp = 0; hp < n_half; ++hp, ++it) {
+        for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
             if (int(it % kSlots) != slot) continue;
             const int st = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
@@ -171,7 +169,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 alive = false;
             }
-            const int n_valid = min(kStageTokens, w.n_tok - hp * kStageTokens) - tb;  // in this warp's 16
+            const int n_valid = min(kStageTokens, w.len - hp * kStageTokens) - tb;  // in this warp's 16
             if (alive && n_valid > 0) {
                 const unsigned char* kst = s.stage[st];
                 unsigned char* vst = s.stage[st] + kStageKBytes;
@@ -267,7 +265,8 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
             if (lane == 0) mbar_arrive(&s.empty[st]);
         }
 
-        split::merge_item(s.sp, acc, m_run, l_run, warp, lane, pg, G, a.part_o, a.part_ml, size_t(item));
+        split::merge_segment(s.sp, acc, m_run, l_run, warp, lane, pg, G, a.part_o, a.part_ml,
+                             size_t(blockIdx.x) + size_t(w.b) * a.n_kv + w.h);
     }
 }
 

@@ -4,7 +4,7 @@
 // walks the whole context with four thread blocks, dequantising every V row with two
 // Walsh-Hadamard transforms (dequant_v_tq3_256, 293-299).  Two identities remove the
 // per-token work:
-//   * q . (s_k * k_int8) = s_k * (q . k_int8): the query is quantised once per item to two
+//   * q . (s_k * k_int8) = s_k * (q . k_int8): the query is quantised once per segment to two
 //     int8 levels (q ~ s1*q1 + s2*q2, 16-bit effective precision) and the scores come from
 //     int8 tensor-core MMAs (m16n8k32) straight off the stored bytes, level 1 in MMA rows
 //     0-7 and level 2 in rows 8-15;
@@ -13,7 +13,7 @@
 //     table (two tokens x two dims per 12-bit field -> two fp16x2 MMA operand registers),
 //     the per-token scale is folded into P -- and ONE inverse transform per output head is
 //     applied by the merge kernel.
-// The persistent producer/consumer structure, the work items and the item merge are those
+// The persistent producer/consumer structure, the work division and the segment merge are those
 // of attn_decode_f16.cu; a stage is one 32-token record (11 456 B, see kv_compact.cu).
 #include "attn_split.cuh"
 #include "kernels.h"
@@ -28,8 +28,7 @@ constexpr int kConsumerWarps = split::kConsumerWarps;
 static_assert(kConsumerWarps == 2 * kSlots, "two warps per stage in flight");
 constexpr int kThreads = 256;                      // 6 consumer + 1 producer + 1 idle warp
 using split::kNegBig;
-using split::Item;
-using split::decode_item;
+using split::Segment;
 
 struct Smem {
     alignas(128) unsigned char stage[kStages][kCompactRecordBytes];
@@ -74,8 +73,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     const int G = a.n_q / a.n_kv;
 
     if (warp == 0)
-        split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.chunk_pages,
-                            a.max_chunks, a.err, lane);
+        split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.err, lane);
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
@@ -93,26 +91,25 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
         }
     }
     __syncthreads();
-    int total_chunks = s.sp.prefix[a.batch];
-    if (total_chunks > a.max_chunks) total_chunks = a.max_chunks;
-    const int total_items = total_chunks * a.n_kv;
+    int u_begin, u_end;
+    split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end);
 
     if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
         if (lane != 0) return;
         uint32_t it = 0;
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-            const Item w = decode_item(s.sp, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
-            const int n_half = (w.n_tok + kCompactHalfTokens - 1) / kCompactHalfTokens;
-            for (int hp = 0; hp < n_half; ++hp, ++it) {
+        for (int pos = u_begin; pos < u_end;) {
+            const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
+            pos += w.hp1 - w.hp0;
+            for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
                 const int st = it % kStages;
                 const uint32_t ph = (it / kStages) & 1;
                 if (!mbar_wait(&s.empty[st], ph ^ 1)) {
                     set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                     return;
                 }
-                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + w.page0 + (hp >> 1)];
+                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + (hp >> 1)];
                 if (page < 0 || page >= a.n_pages) {
                     set_err(a.err, DEV_ERR_BAD_PAGE);
                     page = 0;
@@ -136,9 +133,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
 
     uint32_t it = 0;
     bool alive = true;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-        const Item w = decode_item(s.sp, item, a.batch, a.n_kv, a.chunk_pages, a.seq_lens, a.len_add);
-        const int n_half = (w.n_tok + kCompactHalfTokens - 1) / kCompactHalfTokens;
+    for (int pos = u_begin; pos < u_end;) {
+        const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
+        pos += w.hp1 - w.hp0;
 
         // Query of head g in two int8 levels.  MMA (L, z) contracts dims 64L + 16c + 8z + 0..7
         // of this lane: qa[L][z][0] level 1 dims +0..3, [1] level 2 dims +0..3, [2] level 1 dims
@@ -199,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
         float m_run = kNegBig;
         float l_run = 0.f;
 
-        for (int hp = 0; hp < n_half; ++hp, ++it) {
+        for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
             if (int(it % kSlots) != slot) continue;
             const int st = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
@@ -207,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 alive = false;
             }
-            const int n_valid = min(kCompactHalfTokens, w.n_tok - hp * kCompactHalfTokens) - tb;
+            const int n_valid = min(kCompactHalfTokens, w.len - hp * kCompactHalfTokens) - tb;
             if (alive && n_valid > 0) {
                 const unsigned char* rec = s.stage[st];
                 // ---- scores from the stored int8 rows ----
@@ -311,7 +308,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.empty[st]);
         }
-        split::merge_item(s.sp, acc, m_run, l_run, warp, lane, g, G, a.part_o, a.part_ml, size_t(item));
+        split::merge_segment(s.sp, acc, m_run, l_run, warp, lane, g, G, a.part_o, a.part_ml,
+                             size_t(blockIdx.x) + size_t(w.b) * a.n_kv + w.h);
     }
 }
 

@@ -1,5 +1,6 @@
-// Pieces shared by the split-KV decode kernels (F16 and compact KV): the work
-// item table, and the fixed-order merge of the six consumer warps of a CTA.
+// Pieces shared by the split-KV decode kernels (F16 and compact KV): the division of
+// the work among the persistent CTAs, and the fixed-order merge of the six consumer
+// warps of a CTA.
 #pragma once
 #include "common.cuh"
 
@@ -13,23 +14,30 @@ constexpr float kNegBig = -1e30f;
 constexpr int kMergeStride = kHeadDim + 1;   // row stride 257 floats: conflict-free
 
 struct Shared {
-    float o[3][8][kMergeStride];    // item merge buffers
+    float o[3][8][kMergeStride];    // segment merge buffers
     float m[kConsumerWarps][8];
     float l[kConsumerWarps][8];
-    int prefix[kMaxBatch + 1];      // chunks before sequence b
+    int prefix[kMaxBatch + 1];      // half pages (32 tokens) before sequence b, per KV head
 };
 
-struct Item {
+// The work of a launch is the list of all (sequence b, KV head h, half page hp) units in the
+// order b, h, hp.  CTA k of a grid of n CTAs owns the contiguous units [k*Q, (k+1)*Q), Q =
+// ceil(total / n): equal work per CTA, and a CTA streams consecutive half pages of one head.
+// A CTA's range is cut into segments at (b, h) boundaries; each segment yields one partial
+// (unnormalised output, max, sum) in workspace slot k + (b * n_kv + h).  Along the unit list
+// either k or the (b, h) index grows from one segment to the next, so the slots are distinct
+// and there are fewer than n + batch * n_kv of them.
+struct Segment {
     int b, h;
-    int page0;                      // first page index in the sequence's table row
-    int n_tok;                      // tokens of this item: [page0 * 64, page0 * 64 + n_tok)
+    int hp0, hp1;                   // half pages [hp0, hp1) of sequence b
+    int len;                        // tokens of sequence b
 };
 
-// Warp 0 fills s.prefix: a work item is (sequence, chunk of chunk_pages pages, KV head);
-// lengths outside [0, max_pages_per_seq * 64] count as 0 and are reported.
+__device__ __forceinline__ int half_pages(int len) { return (len + 31) >> 5; }
+
+// Warp 0 fills s.prefix; lengths outside [0, max_pages_per_seq * 64] count as 0 and are reported.
 __device__ __forceinline__ void build_prefix(Shared& s, const int32_t* seq_lens, int len_add, int batch,
-                                             int max_pages_per_seq, int chunk_pages, int max_chunks, int* err,
-                                             int lane) {
+                                             int max_pages_per_seq, int* err, int lane) {
     int run = 0;
     for (int b0 = 0; b0 < batch; b0 += 32) {
         const int b = b0 + lane;
@@ -40,8 +48,7 @@ __device__ __forceinline__ void build_prefix(Shared& s, const int32_t* seq_lens,
                 set_err(err, DEV_ERR_BAD_LEN);
                 len = 0;
             }
-            const int pages = (len + kPageTokens - 1) / kPageTokens;
-            n = (pages + chunk_pages - 1) / chunk_pages;
+            n = half_pages(len);
         }
         int inc = n;
         for (int off = 1; off < 32; off <<= 1) {
@@ -51,39 +58,42 @@ __device__ __forceinline__ void build_prefix(Shared& s, const int32_t* seq_lens,
         if (b < batch) s.prefix[b] = run + inc - n;
         run += __shfl_sync(0xffffffffu, inc, 31);
     }
-    if (lane == 0) {
-        s.prefix[batch] = run;
-        if (run > max_chunks) set_err(err, DEV_ERR_WORKSPACE);
-    }
+    if (lane == 0) s.prefix[batch] = run;
 }
 
-__device__ __forceinline__ Item decode_item(const Shared& s, int item, int batch, int n_kv, int chunk_pages,
-                                            const int32_t* seq_lens, int len_add) {
-    Item it;
-    const int ci = item / n_kv;
-    it.h = item - ci * n_kv;
-    int lo = 0, hi = batch;         // largest b with prefix[b] <= ci
+__device__ __forceinline__ void cta_range(const Shared& s, int batch, int n_kv, int& begin, int& end) {
+    const int total = s.prefix[batch] * n_kv;
+    const int q = (total + int(gridDim.x) - 1) / int(gridDim.x);
+    begin = min(int(blockIdx.x) * q, total);
+    end = min(begin + q, total);
+}
+
+// The segment that starts at unit `pos` (pos < end <= total).
+__device__ __forceinline__ Segment segment_at(const Shared& s, int pos, int end, int batch, int n_kv,
+                                              const int32_t* seq_lens, int len_add) {
+    Segment g;
+    int lo = 0, hi = batch;         // largest b with prefix[b] * n_kv <= pos
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (s.prefix[mid] <= ci) lo = mid; else hi = mid;
+        if (s.prefix[mid] * n_kv <= pos) lo = mid; else hi = mid;
     }
-    it.b = lo;
-    it.page0 = (ci - s.prefix[lo]) * chunk_pages;
-    const int first = it.page0 * kPageTokens;
-    int end = first + chunk_pages * kPageTokens;
-    const int len = seq_lens[lo] + len_add;
-    if (end > len) end = len;
-    it.n_tok = end - first;
-    return it;
+    g.b = lo;
+    const int hpb = s.prefix[lo + 1] - s.prefix[lo];
+    const int rem = pos - s.prefix[lo] * n_kv;
+    g.h = rem / hpb;
+    g.hp0 = rem - g.h * hpb;
+    g.hp1 = min(hpb, g.hp0 + (end - pos));
+    g.len = seq_lens[lo] + len_add;
+    return g;
 }
 
-// Merge the consumer warps' partial results of one item and write the item's partial.
+// Merge the consumer warps' partial results of one segment and write its partial to `slot`.
 // acc[j][i][0..3] of lane (g, c) holds dims d = 64j + 8*dsel + 2i (+1 for [2],[3]) of heads
 // 2c ([0],[2]) and 2c+1 ([1],[3]); m_run is the running maximum (log2 domain) of head g and
 // l_run this lane's share of the row sum.  All consumer threads must call this.
-__device__ __forceinline__ void merge_item(Shared& s, float (&acc)[4][4][4], float m_run, float l_run, int warp,
-                                           int lane, int dsel, int G, float* part_o, float* part_ml,
-                                           size_t item) {
+__device__ __forceinline__ void merge_segment(Shared& s, float (&acc)[4][4][4], float m_run, float l_run,
+                                              int warp, int lane, int dsel, int G, float* part_o,
+                                              float* part_ml, size_t item) {
     const int g = lane >> 2, c = lane & 3;
     const int tid = warp * 32 + lane;
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);

@@ -14,12 +14,10 @@ struct AttnDecodeArgs {
     const int32_t* page_table;   // [batch][max_pages_per_seq]
     const int32_t* seq_lens;     // [batch] device resident; tokens attended = seq_lens[b] + len_add
     const float* q;              // [batch][n_q][256]
-    float* part_o;               // [max_chunks*n_kv][G][256] unnormalised partial outputs
-    float* part_ml;              // [max_chunks*n_kv][G][2]   (max in natural-log units, sum)
+    float* part_o;               // [grid + batch*n_kv][G][256] unnormalised partial outputs
+    float* part_ml;              // [grid + batch*n_kv][G][2]   (max in natural-log units, sum)
     int* err;                    // device error word
     int batch, n_q, n_kv, n_pages, max_pages_per_seq;
-    int chunk_pages;             // pages per work item
-    int max_chunks;              // workspace capacity in chunks (all sequences together)
     int len_add;
     float scale;                 // 1/sqrt(head_dim)
 };
@@ -40,7 +38,8 @@ struct AttnCombineArgs {
     const float* gate;           // [batch][n_q][256] pre-activation, may be null
     float* o;                    // [batch][n_q][256]; unnormalised when out_ml != null
     float* out_ml;               // null, or [batch][n_q][2] (max, sum): emit one partial per row
-    int batch, n_q, n_kv, chunk_pages, max_chunks, page_tokens, len_add;
+    int batch, n_q, n_kv, len_add;
+    int n_ctas;                  // grid size of the decode kernel that wrote the partials
     int max_len;                 // lengths outside [0, max_len] count as 0, as in the decode kernel
     int wht_len;                 // 0, or 128 / 256: the partials are in the rotated domain of TQ3 V
     const float* signs;          // [256] +-1 applied after the inverse transform, or null
