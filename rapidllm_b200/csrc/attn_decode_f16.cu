@@ -77,36 +77,48 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
-        if (lane != 0) return;
+        // The warp reads 32 page ids at a time (one per lane), so that the page-table latency is
+        // paid once per 16 pages; lane 0 waits for free stages and issues the copies.
         uint32_t it = 0;
+        bool ok = true;
         for (int pos = u_begin; pos < u_end;) {
             const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
             pos += w.hp1 - w.hp0;
-            for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
-                const int st = it % kStages;
-                const uint32_t ph = (it / kStages) & 1;
-                if (!mbar_wait(&s.empty[st], ph ^ 1)) {
-                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
-                    return;
+            for (int hp_base = w.hp0; hp_base < w.hp1; hp_base += 32) {
+                int my_page = 0;
+                if (hp_base + lane < w.hp1) {
+                    my_page = a.page_table[size_t(w.b) * a.max_pages_per_seq + ((hp_base + lane) >> 1)];
+                    if (my_page < 0 || my_page >= a.n_pages) {
+                        set_err(a.err, DEV_ERR_BAD_PAGE);
+                        my_page = 0;
+                    }
                 }
-                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + (hp >> 1)];
-                if (page < 0 || page >= a.n_pages) {
-                    set_err(a.err, DEV_ERR_BAD_PAGE);
-                    page = 0;
-                }
-                const size_t slice = (size_t(page) * a.n_kv + w.h) * kv_slice_elems();
-                const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(a.k_pool + slice) +
-                                            (hp & 1) * kSubTileStageBytes;
-                const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(a.v_pool + slice) +
-                                            (hp & 1) * kSubTileStageBytes;
-                unsigned char* dst = s.stage[st];
-                mbar_arrive_expect_tx(&s.full[st], kStageBytes);
+                const int n = min(32, w.hp1 - hp_base);
+                for (int j = 0; j < n; ++j, ++it) {
+                    const int page = __shfl_sync(0xffffffffu, my_page, j);
+                    if (lane != 0 || !ok) continue;
+                    const int hp = hp_base + j;
+                    const int st = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!mbar_wait(&s.empty[st], ph ^ 1)) {
+                        set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                        ok = false;
+                        continue;
+                    }
+                    const size_t slice = (size_t(page) * a.n_kv + w.h) * kv_slice_elems();
+                    const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(a.k_pool + slice) +
+                                                (hp & 1) * kSubTileStageBytes;
+                    const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(a.v_pool + slice) +
+                                                (hp & 1) * kSubTileStageBytes;
+                    unsigned char* dst = s.stage[st];
+                    mbar_arrive_expect_tx(&s.full[st], kStageBytes);
 #pragma unroll
-                for (int sub = 0; sub < kSubTiles; ++sub) {
-                    bulk_g2s(dst + sub * kSubTileStageBytes, ksrc + sub * kSubTilePageBytes,
-                             kSubTileStageBytes, &s.full[st]);
-                    bulk_g2s(dst + kStageKBytes + sub * kSubTileStageBytes,
-                             vsrc + sub * kSubTilePageBytes, kSubTileStageBytes, &s.full[st]);
+                    for (int sub = 0; sub < kSubTiles; ++sub) {
+                        bulk_g2s(dst + sub * kSubTileStageBytes, ksrc + sub * kSubTilePageBytes,
+                                 kSubTileStageBytes, &s.full[st]);
+                        bulk_g2s(dst + kStageKBytes + sub * kSubTileStageBytes,
+                                 vsrc + sub * kSubTilePageBytes, kSubTileStageBytes, &s.full[st]);
+                    }
                 }
             }
         }
@@ -171,7 +183,8 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
             }
             const int n_valid = min(kStageTokens, w.len - hp * kStageTokens) - tb;  // in this warp's 16
             if (alive && n_valid > 0) {
-                const unsigned char* kst = s.stage[st];
+                const uint32_t kst = smem_u32(s.stage[st]);
+                const uint32_t vsa = kst + kStageKBytes;
                 unsigned char* vst = s.stage[st] + kStageKBytes;
                 if (n_valid < 16) {
                     // rows past the end of the sequence may hold anything: clear V
@@ -193,12 +206,11 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     const int r = tb + 8 * nt + pg;
-                    const unsigned char* rowp = kst + r * 128;
+                    const uint32_t rowp = kst + r * 128;
 #pragma unroll
                     for (int L = 0; L < 8; ++L) {
                         const int chunk = (4 * (L & 1) + c) ^ (r & 7);
-                        const uint4 kk = *reinterpret_cast<const uint4*>(
-                            rowp + (L >> 1) * kSubTileStageBytes + chunk * 16);
+                        const uint4 kk = lds128(rowp + (L >> 1) * kSubTileStageBytes + chunk * 16);
                         mma_f16(sc[nt][0], qhi[L][0], qlo[L][0], qhi[L][1], qlo[L][1], kk.x, kk.y);
                         mma_f16(sc[nt][1], qhi[L][2], qlo[L][2], qhi[L][3], qlo[L][3], kk.z, kk.w);
                     }
@@ -245,11 +257,11 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
                 const int r0 = tb + c, r1 = tb + 4 + c, r8 = tb + 8 + c, r9 = tb + 12 + c;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const unsigned char* sub = vst + j * kSubTileStageBytes;
-                    const uint4 v0 = *reinterpret_cast<const uint4*>(sub + r0 * 128 + ((pg ^ (r0 & 7)) << 4));
-                    const uint4 v1 = *reinterpret_cast<const uint4*>(sub + r1 * 128 + ((pg ^ (r1 & 7)) << 4));
-                    const uint4 v8 = *reinterpret_cast<const uint4*>(sub + r8 * 128 + ((pg ^ (r8 & 7)) << 4));
-                    const uint4 v9 = *reinterpret_cast<const uint4*>(sub + r9 * 128 + ((pg ^ (r9 & 7)) << 4));
+                    const uint32_t sub = vsa + j * kSubTileStageBytes;
+                    const uint4 v0 = lds128(sub + r0 * 128 + ((pg ^ (r0 & 7)) << 4));
+                    const uint4 v1 = lds128(sub + r1 * 128 + ((pg ^ (r1 & 7)) << 4));
+                    const uint4 v8 = lds128(sub + r8 * 128 + ((pg ^ (r8 & 7)) << 4));
+                    const uint4 v9 = lds128(sub + r9 * 128 + ((pg ^ (r9 & 7)) << 4));
                     const uint32_t x0[4] = {v0.x, v0.y, v0.z, v0.w};
                     const uint32_t x1[4] = {v1.x, v1.y, v1.z, v1.w};
                     const uint32_t x8[4] = {v8.x, v8.y, v8.z, v8.w};

@@ -9,10 +9,10 @@
 //     int8 tensor-core MMAs (m16n8k32) straight off the stored bytes, level 1 in MMA rows
 //     0-7 and level 2 in rows 8-15;
 //   * the transform is linear and orthonormal: sum_t p_t H(s_t c_t) = H(sum_t p_t s_t c_t), so
-//     P.V accumulates in the rotated domain -- codes go through a 4096-entry shared-memory
-//     table (two tokens x two dims per 12-bit field -> two fp16x2 MMA operand registers),
-//     the per-token scale is folded into P -- and ONE inverse transform per output head is
-//     applied by the merge kernel.
+//     P.V accumulates in the rotated domain -- the codes of a token pair are stored
+//     interleaved, so 6 bits index a lane-private shared-memory table that returns one
+//     fp16x2 MMA operand register; the per-token scale is folded into P -- and ONE inverse
+//     transform per output head is applied by the merge kernel.
 // The persistent producer/consumer structure, the work division and the segment merge are those
 // of attn_decode_f16.cu; a stage is one 32-token record (11 456 B, see kv_compact.cu).
 #include "attn_split.cuh"
@@ -32,7 +32,9 @@ using split::Segment;
 
 struct Smem {
     alignas(128) unsigned char stage[kStages][kCompactRecordBytes];
-    alignas(16) uint2 lut[4096];                   // 12-bit field -> (dim d: even|odd token, dim d+1: even|odd)
+    // 6-bit index (code of the even token | code of the odd token << 3) -> fp16x2 centroids;
+    // one copy per lane ([index][lane]) so that a warp's 32 lookups never share a bank
+    alignas(128) uint32_t lut[64][32];
     split::Shared sp;
     uint64_t full[kStages];
     uint64_t empty[kStages];
@@ -52,14 +54,19 @@ __device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
            ((uint32_t(d) & 0xffu) << 24);
 }
 
-// 12-bit field k (0..15) of a 24-byte group held in six words, as a byte offset into the table
-template <int K>
-__device__ __forceinline__ uint32_t field_offset(const uint32_t (&w)[6]) {
-    constexpr int bit = 12 * K, word = bit >> 5, sh = bit & 31;
+// The 6 bits starting at bit BIT of a 24-byte group held in six words, times 128 (the byte
+// stride between table indices).
+template <int BIT>
+__device__ __forceinline__ uint32_t index_offset(const uint32_t (&w)[6]) {
+    constexpr int word = BIT >> 5, sh = BIT & 31;
     uint32_t x;
-    if constexpr (sh <= 20) x = w[word] >> sh;
-    else x = __funnelshift_r(w[word], w[word + 1], sh);
-    return (x & 0xfffu) << 3;
+    if constexpr (sh + 6 <= 32) {
+        if constexpr (sh >= 7) x = w[word] >> (sh - 7);
+        else x = w[word] << (7 - sh);
+    } else {
+        x = __funnelshift_r(w[word], w[word + 1], sh - 7);
+    }
+    return x & 0x1f80u;
 }
 
 }  // namespace
@@ -83,12 +90,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     }
     {   // centroid table (3-bit Lloyd-Max for N(0,1), cuda_engine.cu:205-209), fp16
         const float cent[8] = {-2.152f, -1.344f, -0.756f, -0.245f, 0.245f, 0.756f, 1.344f, 2.152f};
-        for (int f = tid; f < 4096; f += kThreads) {
-            uint2 e;
-            e.x = pack_h2(cent[f & 7], cent[(f >> 3) & 7]);
-            e.y = pack_h2(cent[(f >> 6) & 7], cent[(f >> 9) & 7]);
-            s.lut[f] = e;
-        }
+        for (int x = tid; x < 64 * 32; x += kThreads) s.lut[x >> 5][x & 31] = pack_h2(cent[(x >> 5) & 7], cent[x >> 8]);
     }
     __syncthreads();
     int u_begin, u_end;
@@ -97,27 +99,39 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
-        if (lane != 0) return;
+        // The warp reads 32 page ids at a time (one per lane), so that the page-table latency is
+        // paid once per 16 pages; lane 0 waits for free stages and issues the copies.
         uint32_t it = 0;
+        bool ok = true;
         for (int pos = u_begin; pos < u_end;) {
             const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
             pos += w.hp1 - w.hp0;
-            for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
-                const int st = it % kStages;
-                const uint32_t ph = (it / kStages) & 1;
-                if (!mbar_wait(&s.empty[st], ph ^ 1)) {
-                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
-                    return;
+            for (int hp_base = w.hp0; hp_base < w.hp1; hp_base += 32) {
+                int my_page = 0;
+                if (hp_base + lane < w.hp1) {
+                    my_page = a.page_table[size_t(w.b) * a.max_pages_per_seq + ((hp_base + lane) >> 1)];
+                    if (my_page < 0 || my_page >= a.n_pages) {
+                        set_err(a.err, DEV_ERR_BAD_PAGE);
+                        my_page = 0;
+                    }
                 }
-                int page = a.page_table[size_t(w.b) * a.max_pages_per_seq + (hp >> 1)];
-                if (page < 0 || page >= a.n_pages) {
-                    set_err(a.err, DEV_ERR_BAD_PAGE);
-                    page = 0;
+                const int n = min(32, w.hp1 - hp_base);
+                for (int j = 0; j < n; ++j, ++it) {
+                    const int page = __shfl_sync(0xffffffffu, my_page, j);
+                    if (lane != 0 || !ok) continue;
+                    const int hp = hp_base + j;
+                    const int st = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!mbar_wait(&s.empty[st], ph ^ 1)) {
+                        set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                        ok = false;
+                        continue;
+                    }
+                    const unsigned char* src = reinterpret_cast<const unsigned char*>(a.k_pool) +
+                                               ((size_t(page) * a.n_kv + w.h) * 2 + (hp & 1)) * kCompactRecordBytes;
+                    mbar_arrive_expect_tx(&s.full[st], kCompactRecordBytes);
+                    bulk_g2s(s.stage[st], src, kCompactRecordBytes, &s.full[st]);
                 }
-                const unsigned char* src = reinterpret_cast<const unsigned char*>(a.k_pool) +
-                                           ((size_t(page) * a.n_kv + w.h) * 2 + (hp & 1)) * kCompactRecordBytes;
-                mbar_arrive_expect_tx(&s.full[st], kCompactRecordBytes);
-                bulk_g2s(s.stage[st], src, kCompactRecordBytes, &s.full[st]);
             }
         }
         return;
@@ -129,7 +143,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     const int slot = warp >> 1;
     const int tb = (warp & 1) * 16;                // this warp's tokens inside a record
     const float scale_log2 = a.scale * 1.4426950408889634f;
-    const unsigned char* lut = reinterpret_cast<const unsigned char*>(s.lut);
+    const uint32_t lut = smem_u32(&s.lut[0][lane]);
+    const uint32_t stage0 = smem_u32(s.stage[0]);
 
     uint32_t it = 0;
     bool alive = true;
@@ -206,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
             }
             const int n_valid = min(kCompactHalfTokens, w.len - hp * kCompactHalfTokens) - tb;
             if (alive && n_valid > 0) {
-                const unsigned char* rec = s.stage[st];
+                const uint32_t rec = stage0 + st * kCompactRecordBytes;
                 // ---- scores from the stored int8 rows ----
                 int sc[2][4];
 #pragma unroll
@@ -214,11 +229,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
 #pragma unroll
                     for (int e = 0; e < 4; ++e) sc[nt][e] = 0;
                     const int r = tb + 8 * nt + g;
-                    const unsigned char* rowp = rec + r * 256;
+                    const uint32_t rowp = rec + r * 256;
 #pragma unroll
                     for (int L = 0; L < 4; ++L) {
                         const int chunk = (4 * L + c) ^ ((r & 1) << 2);
-                        const uint4 kk = *reinterpret_cast<const uint4*>(rowp + chunk * 16);
+                        const uint4 kk = lds128(rowp + chunk * 16);
                         mma_s8(sc[nt], qa[L][0][0], qa[L][0][1], qa[L][0][2], qa[L][0][3], kk.x, kk.y);
                         mma_s8(sc[nt], qa[L][1][0], qa[L][1][1], qa[L][1][2], qa[L][1][3], kk.z, kk.w);
                     }
@@ -228,9 +243,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
                 float mx = kNegBig;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    const __half2 ks2 = *reinterpret_cast<const __half2*>(rec + kCompactKScaleOff +
-                                                                          (tb + 8 * nt + 2 * c) * 2);
-                    const float2 ks = __half22float2(ks2);
+                    const uint32_t ks_raw = lds32(rec + kCompactKScaleOff + (tb + 8 * nt + 2 * c) * 2);
+                    const float2 ks = __half22float2(*reinterpret_cast<const __half2*>(&ks_raw));
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float sv = (e ? ks.y : ks.x) * (s1 * float(sc[nt][e]) + s2 * float(sc[nt][e + 2]));
@@ -267,8 +281,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
                 uint32_t pb[2][2];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(rec + kCompactVScaleOff +
-                                                                      (tb + 8 * nt + 2 * c) * 4);
+                    const uint2 raw = lds64(rec + kCompactVScaleOff + (tb + 8 * nt + 2 * c) * 4);
                     const float2 t0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));  // even token
                     const float2 t1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));  // odd token
                     // rows beyond the sequence may hold anything: their p is 0, keep the product 0
@@ -279,31 +292,25 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
                 // ---- acc[dims][heads] += centroids(V codes)^T (P * scale)^T, rotated domain ----
                 uint32_t wa[6], wb[6];
                 {
-                    const unsigned char* va = rec + kCompactVOff + (tb >> 4) * 1536 + g * 96 + c * 24;
-                    const uint2 a0 = *reinterpret_cast<const uint2*>(va);
-                    const uint2 a1 = *reinterpret_cast<const uint2*>(va + 8);
-                    const uint2 a2 = *reinterpret_cast<const uint2*>(va + 16);
-                    const uint2 b0 = *reinterpret_cast<const uint2*>(va + 768);
-                    const uint2 b1 = *reinterpret_cast<const uint2*>(va + 776);
-                    const uint2 b2 = *reinterpret_cast<const uint2*>(va + 784);
+                    const uint32_t va = rec + kCompactVOff + (tb >> 4) * 1536 + g * 96 + c * 24;
+                    const uint2 a0 = lds64(va), a1 = lds64(va + 8), a2 = lds64(va + 16);
+                    const uint2 b0 = lds64(va + 768), b1 = lds64(va + 776), b2 = lds64(va + 784);
                     wa[0] = a0.x; wa[1] = a0.y; wa[2] = a1.x; wa[3] = a1.y; wa[4] = a2.x; wa[5] = a2.y;
                     wb[0] = b0.x; wb[1] = b0.y; wb[2] = b1.x; wb[3] = b1.y; wb[4] = b2.x; wb[5] = b2.y;
                 }
-                if (n_valid < 16) {
-                    // codes of rows past the end are arbitrary but finite table entries; with p = 0
-                    // they contribute exactly 0, nothing to clear
-                }
+                // codes of rows past the end are arbitrary but finite table entries; with p = 0
+                // they contribute exactly 0, nothing to clear
+#define RL_TQ_LUT(W, BIT) lds32(lut + index_offset<(BIT)>(W))
 #define RL_TQ_MMA(J, I)                                                                              \
-    {                                                                                                \
-        const uint2 ea = *reinterpret_cast<const uint2*>(lut + field_offset<4 * (J) + (I)>(wa));     \
-        const uint2 eb = *reinterpret_cast<const uint2*>(lut + field_offset<4 * (J) + (I)>(wb));     \
-        mma_f16(acc[J][I], ea.x, ea.y, eb.x, eb.y, pb[(J) >> 1][0], pb[(J) >> 1][1]);                \
-    }
+    mma_f16(acc[J][I], RL_TQ_LUT(wa, 12 * (4 * (J) + (I))), RL_TQ_LUT(wa, 12 * (4 * (J) + (I)) + 6), \
+            RL_TQ_LUT(wb, 12 * (4 * (J) + (I))), RL_TQ_LUT(wb, 12 * (4 * (J) + (I)) + 6),            \
+            pb[(J) >> 1][0], pb[(J) >> 1][1]);
                 RL_TQ_MMA(0, 0) RL_TQ_MMA(0, 1) RL_TQ_MMA(0, 2) RL_TQ_MMA(0, 3)
                 RL_TQ_MMA(1, 0) RL_TQ_MMA(1, 1) RL_TQ_MMA(1, 2) RL_TQ_MMA(1, 3)
                 RL_TQ_MMA(2, 0) RL_TQ_MMA(2, 1) RL_TQ_MMA(2, 2) RL_TQ_MMA(2, 3)
                 RL_TQ_MMA(3, 0) RL_TQ_MMA(3, 1) RL_TQ_MMA(3, 2) RL_TQ_MMA(3, 3)
 #undef RL_TQ_MMA
+#undef RL_TQ_LUT
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.empty[st]);
