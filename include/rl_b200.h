@@ -126,6 +126,32 @@ int rl_attn_decode_partial(const void* k_pool, const void* v_pool, const int32_t
                            const rl_attn_decode_params* p, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Gated attention, chunked prefill                                           */
+/* ------------------------------------------------------------------------- */
+
+/* AttnPrefillParams {n_q, n_kv, head_dim, seq, br, bc} (params.h:18) + chunk position and
+ * paging.  br / bc are the row / column tile sizes; this kernel uses 128 / 64 and ignores
+ * other requests. */
+typedef struct rl_attn_prefill_params {
+    int n_q, n_kv, head_dim;     /* 24, 4, 256 */
+    int seq;                     /* T: query rows in this chunk */
+    int br, bc;
+    int pos0;                    /* position of the first row; the cache holds [0, pos0) already */
+    int page_tokens, n_pages;    /* 64, pages in the pool */
+    int n_table;                 /* entries in page_table_row (>= ceil((pos0 + seq) / 64)) */
+} rl_attn_prefill_params;
+
+/* ops::attn_prefill (ops.h:128-129, src/kernels/ops.cpp:542-573) for one chunk of one
+ * sequence, the way launch_prefill_chunk drives it (cuda_engine.cu:18338-18590): first the
+ * chunk's K,V rows (bf16 [seq][n_kv][256], norm and RoPE applied) are appended to the F16
+ * cache at pos0.. (skipped when k_rows is NULL), then row t attends to cache rows
+ * [0, pos0 + t] and the result is multiplied by sigmoid(gate) when gate != NULL.
+ *   q bf16 [seq][n_q][256];  gate, o fp32 [seq][n_q][256] */
+int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
+                    const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o,
+                    const rl_attn_prefill_params* p, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* KV cache maintenance                                                       */
 /* ------------------------------------------------------------------------- */
 
@@ -135,7 +161,7 @@ typedef struct rl_kv_append_params {
     int n_tok;                   /* rows per sequence in this call (1 for decode) */
     int page_tokens, n_pages, max_pages_per_seq;
     int pos0;                    /* first position when pos == NULL */
-    int rows_fp16;               /* 1: rows are fp16; 0: fp32, rounded to nearest even */
+    int rows_fp16;               /* row element type: 0 fp32 (rounded to nearest even), 1 fp16, 2 bf16 */
     int wht_len;                 /* compact cache only: 128 or 256 */
 } rl_kv_append_params;
 

@@ -33,6 +33,11 @@ class AttnDecodeParams(C.Structure):
         ("tq_signs", C.c_void_p)]
 
 
+class AttnPrefillParams(C.Structure):
+    _fields_ = [(n, C.c_int) for n in (
+        "n_q", "n_kv", "head_dim", "seq", "br", "bc", "pos0", "page_tokens", "n_pages", "n_table")]
+
+
 class KvAppendParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "n_kv", "head_dim", "batch", "n_tok", "page_tokens", "n_pages", "max_pages_per_seq",
@@ -77,6 +82,7 @@ SYMBOLS = {
                             C.POINTER(AttnDecodeParams), _vp]),
     "rl_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz,
                                     C.POINTER(AttnDecodeParams), _vp]),
+    "rl_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnPrefillParams), _vp]),
     "rl_lse_combine": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "rl_kv_compact_page_bytes": (_sz, []),
     "rl_kv_compact_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(KvAppendParams), _vp]),

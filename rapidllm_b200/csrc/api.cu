@@ -64,6 +64,8 @@ int dev_info(DevInfo** out) {
         RL_CUDA(cudaMemset(d.err_ptr, 0, sizeof(int)));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_f16_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::attn_prefill_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_tq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_tq_smem_bytes())));
         d.ready = true;
@@ -425,6 +427,62 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     a.pos0 = p->pos0;
     a.rows_fp16 = p->rows_fp16;
     rl::kv_write_kernel<<<dim3(p->n_tok, p->n_kv, p->batch), 32, 0, as_stream(stream)>>>(a);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
+                    const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o,
+                    const rl_attn_prefill_params* p, void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->head_dim != rl::kHeadDim || p->page_tokens != rl::kPageTokens)
+        return fail(RL_ERR_UNSUPPORTED, "head_dim %d / page_tokens %d: only 256 / 64", p->head_dim, p->page_tokens);
+    if (p->n_kv <= 0 || p->n_q <= 0 || p->n_q % p->n_kv != 0 || p->n_q > 65535)
+        return fail(RL_ERR_UNSUPPORTED, "n_q %d / n_kv %d", p->n_q, p->n_kv);
+    if (p->seq < 0 || p->pos0 < 0 || p->n_pages <= 0) return fail(RL_ERR_RANGE, "seq %d pos0 %d n_pages %d", p->seq, p->pos0, p->n_pages);
+    if ((long long)p->pos0 + p->seq > (long long)p->n_table * p->page_tokens)
+        return fail(RL_ERR_RANGE, "pos0 %d + seq %d exceeds the %d pages of the table row", p->pos0, p->seq, p->n_table);
+    if (p->seq == 0) return RL_OK;
+    if (!k_pool || !v_pool || !page_table_row || !q_bf16 || !o) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    if ((k_rows_bf16 == nullptr) != (v_rows_bf16 == nullptr)) return fail(RL_ERR_RANGE, "k_rows and v_rows go together");
+    if (reinterpret_cast<uintptr_t>(k_pool) % 128 || reinterpret_cast<uintptr_t>(v_pool) % 128 ||
+        reinterpret_cast<uintptr_t>(q_bf16) % 16 || reinterpret_cast<uintptr_t>(o) % 16 ||
+        reinterpret_cast<uintptr_t>(gate) % 16)
+        return fail(RL_ERR_RANGE, "pools must be 128-byte aligned, q, gate and o 16-byte aligned");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    if (k_rows_bf16) {
+        rl_kv_append_params ap;
+        ap.n_kv = p->n_kv;
+        ap.head_dim = p->head_dim;
+        ap.batch = 1;
+        ap.n_tok = p->seq;
+        ap.page_tokens = p->page_tokens;
+        ap.n_pages = p->n_pages;
+        ap.max_pages_per_seq = p->n_table;
+        ap.pos0 = p->pos0;
+        ap.rows_fp16 = 2;
+        ap.wht_len = 0;
+        if (int st = rl_kv_append(k_pool, v_pool, page_table_row, nullptr, k_rows_bf16, v_rows_bf16, &ap, stream))
+            return st;
+    }
+    rl::AttnPrefillArgs a;
+    a.k_pool = static_cast<const __half*>(k_pool);
+    a.v_pool = static_cast<const __half*>(v_pool);
+    a.page_table = page_table_row;
+    a.q = static_cast<const __nv_bfloat16*>(q_bf16);
+    a.gate = gate;
+    a.o = o;
+    a.err = d->err_ptr;
+    a.T = p->seq;
+    a.pos0 = p->pos0;
+    a.n_q = p->n_q;
+    a.n_kv = p->n_kv;
+    a.n_pages = p->n_pages;
+    a.scale = 1.f / sqrtf(float(p->head_dim));
+    const int n_qtiles = (p->seq + rl::attn_prefill_q_rows() - 1) / rl::attn_prefill_q_rows();
+    rl::attn_prefill_kernel<<<dim3(n_qtiles, p->n_q), rl::attn_prefill_threads(), rl::attn_prefill_smem_bytes(),
+                              as_stream(stream)>>>(a);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

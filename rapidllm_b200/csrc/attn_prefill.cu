@@ -1,0 +1,284 @@
+// Chunked causal attention prefill over the paged F16 KV cache on tcgen05 / TMEM (sm_100a).
+//
+// Computes what ops::attn_prefill (src/kernels/ops.cpp:542-573) computes for the query rows
+// of one chunk -- T rows at positions pos0 .. pos0+T-1 attending to cache rows [0, pos] with
+// the causal offset of the reference's chunk driver (src/kernels/cuda/cuda_engine.cu:
+// 8963-8975, launch_prefill_chunk 18338-18590) -- followed by the sigmoid output gate.  It
+// replaces the reference's CUDA-core prefill kernels and its cuBLAS TF32 path
+// (launch_attn_gqa_gemm, 9038-9125).
+//
+// One CTA = 128 query rows of one query head.  Q (bf16 -> fp16) sits in shared memory as a
+// K-major 128-byte-swizzled operand.  KV tiles are whole pages: a (page, head) slice is
+// stored in HBM in exactly the tensor-core tile format (kv_slice_offset), so a tile moves
+// with linear TMA bulk copies and is consumed in place: K as the K-major B operand of
+// S = Q K^T (M 128, N 64, 16 MMAs of K 16), V as the MN-major B operand of O += P V (M 128,
+// N 256, 4 MMAs).  S (64 columns) and O (256 columns) live in tensor memory.  Four softmax
+// warps own one query row per thread (TMEM lane = row): scores are read with tcgen05.ld,
+// the running maximum is only raised when it grows by more than 2^8 (then O is rescaled in
+// TMEM), and P goes back to shared memory as the fp16 A operand of the second MMA.  Warp 4
+// streams pages, one thread of warp 5 issues all MMAs and signals completion through
+// tcgen05.commit on mbarriers.  All waits are bounded.
+#include "kernels.h"
+#include "tcgen05.cuh"
+
+namespace rl {
+
+namespace {
+
+constexpr int kQRows = 128;
+constexpr int kKvTile = kPageTokens;              // 64
+constexpr int kStages = 2;
+constexpr int kSliceBytes = kPageTokens * kHeadDim * 2;   // 32 KiB
+constexpr int kThreads = 192;                     // 4 softmax warps + loader warp + MMA warp
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 64;
+constexpr float kRescaleThreshold = 8.f;          // log2 units
+
+struct Smem {
+    alignas(1024) unsigned char q[4][kQRows * 128];           // 64 KiB, 4 sub-tiles of 64 dims
+    alignas(1024) unsigned char kv[kStages][2][kSliceBytes];  // K, V page slices
+    alignas(1024) unsigned char p[kQRows * 128];              // 16 KiB, P tile (128 x 64 fp16)
+    uint64_t full[kStages], empty[kStages];
+    uint64_t bar_s, bar_p, bar_done;
+    uint32_t tmem_base;
+    int failed;
+};
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_qtiles = (a.T + kQRows - 1) / kQRows;
+    const int qt = n_qtiles - 1 - int(blockIdx.x);            // heaviest tiles first
+    const int hq = blockIdx.y;
+    const int G = a.n_q / a.n_kv;
+    const int hkv = hq / G;
+    const int q0 = qt * kQRows;                               // first query row of this CTA
+    const int rows = min(kQRows, a.T - q0);
+    const int last_pos = a.pos0 + q0 + rows - 1;              // position of the last query row
+    const int n_tiles = last_pos / kKvTile + 1;               // KV tiles [0, n_tiles)
+
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], 1);
+        }
+        mbar_init(&s.bar_s, 1);
+        mbar_init(&s.bar_p, 128);
+        mbar_init(&s.bar_done, 1);
+        s.failed = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tc::tmem_alloc(&s.tmem_base, kTmemCols);
+    // Q rows -> shared memory (bf16 -> fp16 is exact for normal-range values)
+    if (tid < kQRows) {
+        const int r = tid;
+        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim;
+#pragma unroll 4
+        for (int ch = 0; ch < 32; ++ch) {
+            uint4 out = make_uint4(0, 0, 0, 0);
+            if (r < rows) {
+                const uint4 in = *reinterpret_cast<const uint4*>(src + ch * 8);
+                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in);
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(b2[e]);
+                    o[e] = pack_h2(f.x, f.y);
+                }
+                out = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            *reinterpret_cast<uint4*>(s.q[ch >> 3] + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = out;
+        }
+        tc::fence_async_smem();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = s.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------ page loader ------------------------------
+        if (lane == 0) {
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kStages;
+                if (!mbar_wait(&s.empty[st], ((j / kStages) & 1) ^ 1)) {
+                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                    s.failed = 1;
+                    break;
+                }
+                int page = a.page_table[j];
+                if (page < 0 || page >= a.n_pages) {
+                    set_err(a.err, DEV_ERR_BAD_PAGE);
+                    page = 0;
+                }
+                const size_t slice = (size_t(page) * a.n_kv + hkv) * kv_slice_elems();
+                mbar_arrive_expect_tx(&s.full[st], 2 * kSliceBytes);
+                bulk_g2s(s.kv[st][0], a.k_pool + slice, kSliceBytes, &s.full[st]);
+                bulk_g2s(s.kv[st][1], a.v_pool + slice, kSliceBytes, &s.full[st]);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = tc::idesc_f16(kQRows, kKvTile, false, false);
+            constexpr uint32_t idesc_pv = tc::idesc_f16(kQRows, kHeadDim, false, true);
+            const uint32_t q_addr = smem_u32(s.q[0]);
+            const uint32_t p_addr = smem_u32(s.p);
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int st = j % kStages;
+                if (!mbar_wait(&s.full[st], (j / kStages) & 1)) { ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t k_addr = smem_u32(s.kv[st][0]);
+                const uint32_t v_addr = smem_u32(s.kv[st][1]);
+                // S = Q K^T : 4 sub-tiles of 64 dims x 4 K-steps of 16 dims (32 bytes)
+#pragma unroll
+                for (int kk = 0; kk < 16; ++kk) {
+                    const uint64_t da = tc::smem_desc(q_addr + (kk >> 2) * (kQRows * 128) + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = tc::smem_desc(k_addr + (kk >> 2) * (kKvTile * 128) + (kk & 3) * 32, 16, 1024);
+                    tc::mma_ss(tmem + kColS, da, db, idesc_qk, kk > 0);
+                }
+                tc::commit(&s.bar_s);
+                // O += P V once the softmax warps have written P
+                if (!mbar_wait(&s.bar_p, j & 1)) { ok = false; break; }
+                tc::fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t da = tc::smem_desc(p_addr + kk * 32, 16, 1024);
+                    const uint64_t db = tc::smem_desc(v_addr + kk * (16 * 128), kKvTile * 128, 1024);
+                    tc::mma_ss(tmem + kColO, da, db, idesc_pv, (j > 0) || (kk > 0));
+                }
+                tc::commit(&s.empty[st]);             // the stage is free when these MMAs are done
+            }
+            if (!ok) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                s.failed = 1;
+            }
+            tc::commit(&s.bar_done);
+        }
+    } else {
+        // ------------------------------ softmax warps ------------------------------
+        const int r = tid;                                    // query row = TMEM lane
+        const int pos = a.pos0 + q0 + r;                      // its position (rows >= `rows` are padding)
+        const uint32_t lane_addr = tmem + (uint32_t(warp * 32) << 16);
+        const float scale_log2 = a.scale * 1.4426950408889634f;
+        float m_run = -1e30f, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (ok && !mbar_wait(&s.bar_s, j & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
+            }
+            tc::fence_after_sync();
+            uint32_t raw[2][32];
+            if (ok) {
+                tc::tmem_ld32(lane_addr + kColS, raw[0]);
+                tc::tmem_ld32(lane_addr + kColS + 32, raw[1]);
+                tc::tmem_wait_ld();
+            }
+            const int tok0 = j * kKvTile;
+            if (j == n_tiles - 1 && last_pos + 1 - tok0 < kKvTile) {
+                // V rows past the last position may hold anything (0 * NaN would poison O): clear them
+                const int first = last_pos + 1 - tok0;
+                unsigned char* vt = s.kv[j % kStages][1];
+                for (int idx = tid; idx < (kKvTile - first) * 32; idx += 128) {
+                    const int row = first + (idx >> 5), c16 = idx & 31;
+                    *reinterpret_cast<uint4*>(vt + (c16 >> 3) * (kKvTile * 128) + row * 128 + (c16 & 7) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            float x[64];
+            float mx = -1e30f;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const float v = __uint_as_float(raw[i >> 5][i & 31]) * scale_log2;
+                x[i] = (tok0 + i <= pos) ? v : -1e30f;
+                mx = fmaxf(mx, x[i]);
+            }
+            // raise the running maximum only when it grew by more than the threshold
+            float alpha = 1.f;
+            if (mx > m_run + kRescaleThreshold) {
+                alpha = fast_exp2(m_run - mx);                // 0 on the first tile
+                m_run = mx;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // S_j complete implies O += P V of tile j-1 is complete (MMAs finish in issue order)
+                if (ok) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                        uint32_t o[32];
+                        tc::tmem_ld32(lane_addr + kColO + c0, o);
+                        tc::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tc::tmem_st32(lane_addr + kColO + c0, o);
+                    }
+                    tc::tmem_wait_st();
+                }
+            }
+            l_run *= alpha;
+            uint32_t ph[32];
+            float lsum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = x[2 * i] > -1e29f ? fast_exp2(x[2 * i] - m_run) : 0.f;
+                const float p1 = x[2 * i + 1] > -1e29f ? fast_exp2(x[2 * i + 1] - m_run) : 0.f;
+                lsum += p0 + p1;
+                ph[i] = pack_h2(p0, p1);
+            }
+            l_run += lsum;
+            // P row -> shared memory, K-major swizzled: chunk c of row r at (c ^ (r & 7)) * 16
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(s.p + r * 128 + ((ch ^ (r & 7)) << 4)) =
+                    make_uint4(ph[4 * ch], ph[4 * ch + 1], ph[4 * ch + 2], ph[4 * ch + 3]);
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+            mbar_arrive(&s.bar_p);
+        }
+        // ------------------------------ epilogue ------------------------------
+        if (ok && !mbar_wait(&s.bar_done, 0)) {
+            set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+            ok = false;
+        }
+        tc::fence_after_sync();
+        if (ok && !s.failed) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            float* dst = a.o + (size_t(q0 + r) * a.n_q + hq) * kHeadDim;
+            const float* gp = a.gate ? a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim : nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                uint32_t o[32];
+                tc::tmem_ld32(lane_addr + kColO + c0, o);
+                tc::tmem_wait_ld();
+                if (r < rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 v = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                               __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                        if (gp) {
+                            const float4 gq = *reinterpret_cast<const float4*>(gp + c0 + i);
+                            v.x *= 1.f / (1.f + expf(-gq.x));
+                            v.y *= 1.f / (1.f + expf(-gq.y));
+                            v.z *= 1.f / (1.f + expf(-gq.z));
+                            v.w *= 1.f / (1.f + expf(-gq.w));
+                        }
+                        *reinterpret_cast<float4*>(dst + c0 + i) = v;
+                    }
+                }
+            }
+        }
+        tc::fence_before_sync();
+    }
+    __syncthreads();
+    if (warp == 5) tc::tmem_dealloc(tmem, kTmemCols);
+}
+
+size_t attn_prefill_smem_bytes() { return sizeof(Smem) + 1024; }
+int attn_prefill_threads() { return kThreads; }
+int attn_prefill_q_rows() { return kQRows; }
+
+}  // namespace rl

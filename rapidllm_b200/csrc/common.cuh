@@ -51,13 +51,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kWaitLimit polls (each poll may itself suspend
+// Bounded wait: gives up after kWaitLimitNs of wall time (each poll may itself suspend
 // for a hardware-defined time), so a lost arrival can never hang the GPU.
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+        if (global_ns() - t0 > kWaitLimitNs) return false;
+    }
 }
 
 // ---- TMA (untiled bulk copy global -> shared, completes on an mbarrier) ----

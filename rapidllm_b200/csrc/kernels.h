@@ -1,5 +1,6 @@
 // Launch-side declarations shared by the kernels and the C ABI (api.cu).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -29,6 +30,23 @@ int attn_decode_tq_threads();
 size_t attn_decode_f16_smem_bytes();
 int attn_decode_f16_threads();
 int attn_decode_max_batch();
+
+// ---- chunked causal attention prefill (tcgen05) ------------------------------------------
+struct AttnPrefillArgs {
+    const __half* k_pool;
+    const __half* v_pool;
+    const int32_t* page_table;   // this sequence's row
+    const __nv_bfloat16* q;      // [T][n_q][256]
+    const float* gate;           // [T][n_q][256] or null
+    float* o;                    // [T][n_q][256]
+    int* err;
+    int T, pos0, n_q, n_kv, n_pages;
+    float scale;
+};
+__global__ void attn_prefill_kernel(AttnPrefillArgs a);
+size_t attn_prefill_smem_bytes();
+int attn_prefill_threads();
+int attn_prefill_q_rows();
 
 // ---- merge of split-KV partials + sigmoid gate -----------------------------------
 struct AttnCombineArgs {
@@ -63,7 +81,7 @@ struct KvWriteArgs {
     int* err;
     int batch, n_tok, n_kv, n_pages, max_pages_per_seq;
     int pos0;                    // used when pos == null
-    int rows_fp16;               // 1: rows are fp16, 0: fp32 (rounded to nearest even)
+    int rows_fp16;               // row element type: 0 fp32 (rounded to nearest even), 1 fp16, 2 bf16
 };
 __global__ void kv_write_kernel(KvWriteArgs a);
 // Read tokens [0, n_tok) of one sequence back as contiguous fp16 [n_tok][n_kv][256].

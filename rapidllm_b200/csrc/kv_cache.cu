@@ -29,9 +29,23 @@ __global__ void __launch_bounds__(32) kv_write_kernel(KvWriteArgs a) {
     const size_t src = ((size_t(b) * a.n_tok + t) * a.n_kv + h) * kHeadDim + lane * 8;
     const size_t dst = (size_t(page) * a.n_kv + h) * kv_slice_elems() + kv_slice_offset(row, lane * 8);
     uint4 kk, vv;
-    if (a.rows_fp16) {
+    if (a.rows_fp16 == 1) {
         kk = *reinterpret_cast<const uint4*>(static_cast<const __half*>(a.k_rows) + src);
         vv = *reinterpret_cast<const uint4*>(static_cast<const __half*>(a.v_rows) + src);
+    } else if (a.rows_fp16 == 2) {
+        const uint4 kb = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.k_rows) + src);
+        const uint4 vb = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.v_rows) + src);
+        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kb);
+        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vb);
+        uint32_t ko[4], vo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 kf = __bfloat1622float2(k2[e]), vf = __bfloat1622float2(v2[e]);
+            ko[e] = pack_h2(kf.x, kf.y);
+            vo[e] = pack_h2(vf.x, vf.y);
+        }
+        kk = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+        vv = make_uint4(vo[0], vo[1], vo[2], vo[3]);
     } else {
         const float* kf = static_cast<const float*>(a.k_rows) + src;
         const float* vf = static_cast<const float*>(a.v_rows) + src;

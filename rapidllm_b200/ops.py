@@ -11,8 +11,8 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import (AttnDecodeParams, Conv1dParams, DeltaRecurrentParams, KvAppendParams, check,
-                   lib)
+from ._lib import (AttnDecodeParams, AttnPrefillParams, Conv1dParams, DeltaRecurrentParams,
+                   KvAppendParams, check, lib)
 
 PAGE_TOKENS = 64
 HEAD_DIM = 256
@@ -52,14 +52,16 @@ def kv_append(k_pool, v_pool, page_table, k_rows, v_rows, pos=None, pos0=0):
         k_rows, v_rows = k_rows.unsqueeze(0), v_rows.unsqueeze(0)
     if page_table.dim() == 1:
         page_table = page_table.unsqueeze(0)
-    fp16 = k_rows.dtype == torch.float16
-    _need(k_rows, torch.float16 if fp16 else torch.float32, "k_rows")
+    kind = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}.get(k_rows.dtype)
+    if kind is None:
+        raise _lib.RlError(6, "k_rows: need fp32, fp16 or bf16")
+    _need(k_rows, k_rows.dtype, "k_rows")
     _need(v_rows, k_rows.dtype, "v_rows")
     _need(page_table, torch.int32, "page_table")
     _need(pos, torch.int32, "pos")
     p = KvAppendParams(n_kv=n_kv, head_dim=HEAD_DIM, batch=k_rows.shape[0], n_tok=k_rows.shape[1],
                        page_tokens=PAGE_TOKENS, n_pages=n_pages,
-                       max_pages_per_seq=page_table.shape[1], pos0=pos0, rows_fp16=int(fp16))
+                       max_pages_per_seq=page_table.shape[1], pos0=pos0, rows_fp16=kind)
     check(lib().rl_kv_append(_p(k_pool), _p(v_pool), _p(page_table), _p(pos), _p(k_rows),
                              _p(v_rows), C.byref(p), _stream()))
 
@@ -156,6 +158,27 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, gate=None, max_seq_len=
     check(lib().rl_attn_decode(_p(k_pool), _p(v_pool), _p(page_table), _p(seq_lens), _p(q),
                                _p(gate), _p(o), _p(workspace), workspace.numel(), C.byref(p),
                                _stream()))
+    return o
+
+
+def attn_prefill(q, k_pool, v_pool, page_table_row, pos0=0, k_rows=None, v_rows=None, gate=None):
+    """ops::attn_prefill for one chunk of one sequence over the paged F16 cache.
+
+    q bf16 [T][n_q][256]; k_rows, v_rows bf16 [T][n_kv][256] are appended at pos0 first (or the
+    cache already holds them); row t attends to cache rows [0, pos0 + t]; o *= sigmoid(gate).
+    """
+    _need(q, torch.bfloat16, "q")
+    _need(k_rows, torch.bfloat16, "k_rows")
+    _need(v_rows, torch.bfloat16, "v_rows")
+    _need(gate, torch.float32, "gate")
+    _need(page_table_row, torch.int32, "page_table_row")
+    T, n_q, _ = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    o = torch.empty(T, n_q, HEAD_DIM, dtype=torch.float32, device=q.device)
+    p = AttnPrefillParams(n_q=n_q, n_kv=n_kv, head_dim=HEAD_DIM, seq=T, br=128, bc=64, pos0=pos0,
+                          page_tokens=PAGE_TOKENS, n_pages=n_pages, n_table=page_table_row.numel())
+    check(lib().rl_attn_prefill(_p(k_pool), _p(v_pool), _p(page_table_row), _p(q), _p(k_rows),
+                                _p(v_rows), _p(gate), _p(o), C.byref(p), _stream()))
     return o
 
 

@@ -1,0 +1,94 @@
+"""Chunked causal attention prefill (tcgen05 kernel, through the C ABI) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import ATTN_MAX_ABS, ATTN_REL_L2, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+N_Q, N_KV, HD = 24, 4, 256
+
+
+def _inputs(gen, T):
+    q = torch.randn(T, N_Q, HD, generator=gen).bfloat16()
+    k = torch.randn(T, N_KV, HD, generator=gen).bfloat16()
+    v = torch.randn(T, N_KV, HD, generator=gen).bfloat16()
+    gate = torch.randn(T, N_Q, HD, generator=gen)
+    return q, k, v, gate
+
+
+def _check(o, ref, what=""):
+    o = o.cpu().numpy() if hasattr(o, "cpu") else o
+    assert np.isfinite(o).all()
+    e, r = np.abs(o - ref).max(), rel_l2(o, ref)
+    print("prefill %s max-abs %.3e rel-l2 %.3e" % (what, e, r))
+    assert e <= ATTN_MAX_ABS and r <= ATTN_REL_L2, (what, e, r)
+
+
+@pytest.mark.parametrize("T", [1, 64, 129, 200])
+def test_whole_sequence_small(oracle, T):
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(30 + T)
+    q, k, v, gate = _inputs(gen, T)
+    n_pages = (T + 63) // 64 + 2
+    table = torch.randperm(n_pages, generator=gen)[:(T + 63) // 64].int().cuda()
+    kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+    kp.fill_(float("nan"))                      # rows past the end hold NaN
+    vp.fill_(float("nan"))
+    o = ops.attn_prefill(q.cuda(), kp, vp, table, 0, k.cuda(), v.cuda(), gate.cuda())
+    _lib.check_device()
+    ref = oracle.attn_prefill(q.float().numpy(), k.float().numpy(), v.float().numpy())
+    ref = oracle.sigmoid_gate(ref, gate.numpy())
+    _check(o, ref, "T=%d" % T)
+    # the cache now holds the chunk's rows: bf16 -> fp16, round to nearest even (exact unless
+    # the value is below the fp16 normal range)
+    kg = ops.kv_gather(kp, table, T).cpu()
+    assert torch.equal(kg, k.float().half())
+
+
+def test_chunks_over_an_existing_cache(oracle):
+    """Three chunks (300 + 150 + 77 rows): each attends to everything cached before it."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(31)
+    T = 527
+    q, k, v, gate = _inputs(gen, T)
+    n_pages = 12
+    table = torch.randperm(n_pages, generator=gen)[:9].int().cuda()
+    kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+    outs, pos = [], 0
+    for n in (300, 150, 77):
+        sl = slice(pos, pos + n)
+        outs.append(ops.attn_prefill(q[sl].cuda(), kp, vp, table, pos, k[sl].cuda(), v[sl].cuda(),
+                                     gate[sl].cuda()))
+        pos += n
+    _lib.check_device()
+    o = torch.cat(outs).cpu().numpy()
+    ref = oracle.sigmoid_gate(oracle.attn_prefill(q.float().numpy(), k.float().numpy(), v.float().numpy()),
+                              gate.numpy())
+    _check(o, ref, "3 chunks")
+    # decode over the same cache agrees with the last prefill row
+    lens = torch.tensor([T], dtype=torch.int32, device="cuda")
+    od = ops.attn_decode(q[-1:].float().cuda(), kp, vp, table.unsqueeze(0), lens, gate[-1:].cuda())
+    assert rel_l2(od[0].cpu().numpy(), o[-1]) < ATTN_REL_L2
+
+
+def test_config3_8192_tokens_sampled_rows(oracle):
+    """8192-token prefill in 1024-row chunks; a strided sample of rows against the oracle."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(3)
+    T = 8192
+    q, k, v, gate = _inputs(gen, T)
+    n_pages = T // 64
+    table = torch.randperm(n_pages, generator=gen).int().cuda()
+    kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+    outs = []
+    for p0 in range(0, T, 1024):
+        sl = slice(p0, p0 + 1024)
+        outs.append(ops.attn_prefill(q[sl].cuda(), kp, vp, table, p0, k[sl].cuda(), v[sl].cuda(), gate[sl].cuda()))
+    _lib.check_device()
+    o = torch.cat(outs).cpu().numpy()
+    rows = np.array([0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 4095, 5000, 8191], np.int32)
+    ref = oracle.attn_prefill_rows(q[rows].float().numpy(), k.float().numpy(), v.float().numpy(), rows)
+    ref = oracle.sigmoid_gate(ref, gate[rows].numpy())
+    _check(o[rows], ref, "cfg3 rows")
