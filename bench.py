@@ -47,12 +47,13 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--seed", type=int, default=4)
     ap.add_argument("--workload", default="stack",
-                    choices=["stack", "compact_decode", "f16_decode", "delta_step"],
+                    choices=["stack", "compact_decode", "f16_decode", "delta_step", "attn_prefill"],
                     help="stack = the headline workload; the others time one operator at the shapes of "
                          "BASELINE configs 2, 0 and 1 (secondary lines, N=1 only)")
     ap.add_argument("--wht-len", type=int, default=128)
     ap.add_argument("--op-batch", type=int, default=0, help="operator workloads: override the batch")
     ap.add_argument("--op-ctx", type=int, default=0, help="operator workloads: override the context")
+    ap.add_argument("--chunk", type=int, default=8192, help="attn_prefill: query rows per call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -255,6 +256,50 @@ def run_operator(args):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     gen = torch.Generator(device="cuda").manual_seed(args.seed)
     wl = args.workload
+    if wl == "attn_prefill":
+        T = args.op_ctx or 8192
+        n_pages = (T + PAGE - 1) // PAGE
+        cg = torch.Generator().manual_seed(args.seed)
+        table = torch.randperm(n_pages, generator=cg).int().cuda()
+        q = torch.randn(T, N_Q, HD, device="cuda", generator=gen).bfloat16()
+        k = torch.randn(T, N_KV, HD, device="cuda", generator=gen).bfloat16()
+        v = torch.randn(T, N_KV, HD, device="cuda", generator=gen).bfloat16()
+        gate = torch.randn(T, N_Q, HD, device="cuda", generator=gen)
+        kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+
+        def call():
+            for p0 in range(0, T, args.chunk):
+                sl = slice(p0, min(T, p0 + args.chunk))
+                ops.attn_prefill(q[sl], kp, vp, table, p0, k[sl], v[sl], gate[sl])
+        for _ in range(max(3, args.warmup)):
+            call()
+        _lib.check_device()
+        sampler = ClockSampler(0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        _lib.check_device()
+        ms = e0.elapsed_time(e1) / args.steps
+        flops = 4.0 * N_Q * HD * T * (T + 1) / 2
+        tpeak = float(peaks.get("bf16_tflops", 1590.0))
+        achieved = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "attention prefill tokens/sec (one layer)", "value": T / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic", "dtype": "f16 (bf16 in)",
+            "config": {"workload": "gated attention chunked prefill, T %d in chunks of %d, 24Q/4KV hd256, causal, "
+                       "writes F16 KV" % (T, args.chunk), "l2": "K/V of one layer fit L2 by design (32 MB)"},
+            "clocks": clocks, "gpu_launches": args.steps * 2 * ((T + args.chunk - 1) // args.chunk),
+            "roofline": {"bound": "tensor", "kernel": "attn_prefill_kernel", "achieved": achieved, "peak": tpeak,
+                         "unit": "TFLOP/s", "frac": achieved / tpeak, "flops_per_step": flops, "traffic": None}}),
+            flush=True)
+        return
     if wl in ("compact_decode", "f16_decode"):
         if wl == "compact_decode":
             B, ctx = 4, 131072

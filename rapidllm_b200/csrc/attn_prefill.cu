@@ -12,7 +12,9 @@
 // stored in HBM in exactly the tensor-core tile format (kv_slice_offset), so a tile moves
 // with linear TMA bulk copies and is consumed in place: K as the K-major B operand of
 // S = Q K^T (M 128, N 64, 16 MMAs of K 16), V as the MN-major B operand of O += P V (M 128,
-// N 256, 4 MMAs).  S (64 columns) and O (256 columns) live in tensor memory.  Four softmax
+// N 256, 4 MMAs).  S (two buffers of 64 columns) and O (256 columns) live in tensor memory;
+// S of the next tile is issued before P.V of the current one, so the softmax of a tile
+// overlaps tensor-core work.  Four softmax
 // warps own one query row per thread (TMEM lane = row): scores are read with tcgen05.ld,
 // the running maximum is only raised when it grows by more than 2^8 (then O is rescaled in
 // TMEM), and P goes back to shared memory as the fp16 A operand of the second MMA.  Warp 4
@@ -27,19 +29,20 @@ namespace {
 
 constexpr int kQRows = 128;
 constexpr int kKvTile = kPageTokens;              // 64
-constexpr int kStages = 2;
+constexpr int kStages = 2;                        // per ring: K tiles and V tiles are staged separately
 constexpr int kSliceBytes = kPageTokens * kHeadDim * 2;   // 32 KiB
 constexpr int kThreads = 192;                     // 4 softmax warps + loader warp + MMA warp
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 64;
+constexpr uint32_t kColS = 0, kColO = 128;        // S double-buffered in columns [0,64) and [64,128)
 constexpr float kRescaleThreshold = 8.f;          // log2 units
 
 struct Smem {
     alignas(1024) unsigned char q[4][kQRows * 128];           // 64 KiB, 4 sub-tiles of 64 dims
-    alignas(1024) unsigned char kv[kStages][2][kSliceBytes];  // K, V page slices
-    alignas(1024) unsigned char p[kQRows * 128];              // 16 KiB, P tile (128 x 64 fp16)
-    uint64_t full[kStages], empty[kStages];
-    uint64_t bar_s, bar_p, bar_done;
+    alignas(1024) unsigned char k[kStages][kSliceBytes];      // K page slices
+    alignas(1024) unsigned char v[kStages][kSliceBytes];      // V page slices
+    alignas(1024) unsigned char p[2][kQRows * 128];           // 2 x 16 KiB, P tiles (128 x 64 fp16)
+    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t bar_s[2], bar_p, bar_pv[2], bar_done;
     uint32_t tmem_base;
     int failed;
 };
@@ -62,11 +65,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&s.full[i], 1);
-            mbar_init(&s.empty[i], 1);
+            mbar_init(&s.k_full[i], 1);
+            mbar_init(&s.k_empty[i], 1);
+            mbar_init(&s.v_full[i], 1);
+            mbar_init(&s.v_empty[i], 1);
         }
-        mbar_init(&s.bar_s, 1);
+        mbar_init(&s.bar_s[0], 1);
+        mbar_init(&s.bar_s[1], 1);
         mbar_init(&s.bar_p, 128);
+        mbar_init(&s.bar_pv[0], 1);
+        mbar_init(&s.bar_pv[1], 1);
         mbar_init(&s.bar_done, 1);
         s.failed = 0;
         mbar_fence_init();
@@ -101,57 +109,71 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
 
     if (warp == 4) {
         // ------------------------------ page loader ------------------------------
+        // K_j is needed early (S_j = Q K_j^T is issued one tile ahead), V_j late (O += P_j V_j):
+        // two rings, each freed by the MMA that last read it.
         if (lane == 0) {
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j % kStages;
-                if (!mbar_wait(&s.empty[st], ((j / kStages) & 1) ^ 1)) {
-                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
-                    s.failed = 1;
-                    break;
-                }
+                const uint32_t ph = ((j / kStages) & 1) ^ 1;
                 int page = a.page_table[j];
                 if (page < 0 || page >= a.n_pages) {
                     set_err(a.err, DEV_ERR_BAD_PAGE);
                     page = 0;
                 }
                 const size_t slice = (size_t(page) * a.n_kv + hkv) * kv_slice_elems();
-                mbar_arrive_expect_tx(&s.full[st], 2 * kSliceBytes);
-                bulk_g2s(s.kv[st][0], a.k_pool + slice, kSliceBytes, &s.full[st]);
-                bulk_g2s(s.kv[st][1], a.v_pool + slice, kSliceBytes, &s.full[st]);
+                if (!mbar_wait(&s.k_empty[st], ph)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.k_full[st], kSliceBytes);
+                bulk_g2s(s.k[st], a.k_pool + slice, kSliceBytes, &s.k_full[st]);
+                if (!mbar_wait(&s.v_empty[st], ph)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.v_full[st], kSliceBytes);
+                bulk_g2s(s.v[st], a.v_pool + slice, kSliceBytes, &s.v_full[st]);
             }
+            if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
+        // Order on the tensor pipe: S_0, S_1, PV_0, S_2, PV_1, ... so that the softmax of tile j
+        // overlaps S_{j+1} and PV_{j-1}.
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::idesc_f16(kQRows, kKvTile, false, false);
             constexpr uint32_t idesc_pv = tc::idesc_f16(kQRows, kHeadDim, false, true);
             const uint32_t q_addr = smem_u32(s.q[0]);
-            const uint32_t p_addr = smem_u32(s.p);
+            const uint32_t p_addr0 = smem_u32(s.p[0]);
             bool ok = true;
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            auto issue_qk = [&](int j) {
                 const int st = j % kStages;
-                if (!mbar_wait(&s.full[st], (j / kStages) & 1)) { ok = false; break; }
+                if (!mbar_wait(&s.k_full[st], (j / kStages) & 1)) { ok = false; return; }
                 tc::fence_after_sync();
-                const uint32_t k_addr = smem_u32(s.kv[st][0]);
-                const uint32_t v_addr = smem_u32(s.kv[st][1]);
-                // S = Q K^T : 4 sub-tiles of 64 dims x 4 K-steps of 16 dims (32 bytes)
+                const uint32_t k_addr = smem_u32(s.k[st]);
+                // 4 sub-tiles of 64 dims x 4 K-steps of 16 dims (32 bytes)
 #pragma unroll
                 for (int kk = 0; kk < 16; ++kk) {
                     const uint64_t da = tc::smem_desc(q_addr + (kk >> 2) * (kQRows * 128) + (kk & 3) * 32, 16, 1024);
                     const uint64_t db = tc::smem_desc(k_addr + (kk >> 2) * (kKvTile * 128) + (kk & 3) * 32, 16, 1024);
-                    tc::mma_ss(tmem + kColS, da, db, idesc_qk, kk > 0);
+                    tc::mma_ss(tmem + kColS + (j & 1) * 64, da, db, idesc_qk, kk > 0);
                 }
-                tc::commit(&s.bar_s);
-                // O += P V once the softmax warps have written P
+                tc::commit(&s.k_empty[st]);           // K stage free once S_j is done
+                tc::commit(&s.bar_s[j & 1]);
+            };
+            issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                // S buffer (j+1)&1 was last read by the softmax of tile j-1, which finished before
+                // it signalled P_{j-1} (awaited in the previous iteration)
+                if (j + 1 < n_tiles) issue_qk(j + 1);
+                if (!ok) break;
+                const int st = j % kStages;
+                if (!mbar_wait(&s.v_full[st], (j / kStages) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_p, j & 1)) { ok = false; break; }
                 tc::fence_after_sync();
+                const uint32_t v_addr = smem_u32(s.v[st]);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t da = tc::smem_desc(p_addr + kk * 32, 16, 1024);
+                    const uint64_t da = tc::smem_desc(p_addr0 + (j & 1) * (kQRows * 128) + kk * 32, 16, 1024);
                     const uint64_t db = tc::smem_desc(v_addr + kk * (16 * 128), kKvTile * 128, 1024);
                     tc::mma_ss(tmem + kColO, da, db, idesc_pv, (j > 0) || (kk > 0));
                 }
-                tc::commit(&s.empty[st]);             // the stage is free when these MMAs are done
+                tc::commit(&s.v_empty[st]);           // V stage free
+                tc::commit(&s.bar_pv[j & 1]);         // this P buffer free, O consistent
             }
             if (!ok) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -168,36 +190,47 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         float m_run = -1e30f, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            if (ok && !mbar_wait(&s.bar_s, j & 1)) {
+            if (ok && !mbar_wait(&s.bar_s[j & 1], (j >> 1) & 1)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
             }
             tc::fence_after_sync();
             uint32_t raw[2][32];
             if (ok) {
-                tc::tmem_ld32(lane_addr + kColS, raw[0]);
-                tc::tmem_ld32(lane_addr + kColS + 32, raw[1]);
+                tc::tmem_ld32(lane_addr + kColS + (j & 1) * 64, raw[0]);
+                tc::tmem_ld32(lane_addr + kColS + (j & 1) * 64 + 32, raw[1]);
                 tc::tmem_wait_ld();
             }
             const int tok0 = j * kKvTile;
             if (j == n_tiles - 1 && last_pos + 1 - tok0 < kKvTile) {
                 // V rows past the last position may hold anything (0 * NaN would poison O): clear them
+                if (ok && !mbar_wait(&s.v_full[j % kStages], (j / kStages) & 1)) {
+                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                    ok = false;
+                }
                 const int first = last_pos + 1 - tok0;
-                unsigned char* vt = s.kv[j % kStages][1];
+                unsigned char* vt = s.v[j % kStages];
                 for (int idx = tid; idx < (kKvTile - first) * 32; idx += 128) {
                     const int row = first + (idx >> 5), c16 = idx & 31;
                     *reinterpret_cast<uint4*>(vt + (c16 >> 3) * (kKvTile * 128) + row * 128 + (c16 & 7) * 16) =
                         make_uint4(0, 0, 0, 0);
                 }
             }
-            float x[64];
+            // raw scores -> maximum (scale > 0, so the maximum can be taken before scaling);
+            // only tiles that reach past the first row's position need the causal mask
+            const bool masked = tok0 + kKvTile - 1 > a.pos0 + q0;
             float mx = -1e30f;
+            if (masked) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float v = __uint_as_float(raw[i >> 5][i & 31]) * scale_log2;
-                x[i] = (tok0 + i <= pos) ? v : -1e30f;
-                mx = fmaxf(mx, x[i]);
+                for (int i = 0; i < 64; ++i) {
+                    if (tok0 + i > pos) raw[i >> 5][i & 31] = 0xff800000u;     // -inf
+                    mx = fmaxf(mx, __uint_as_float(raw[i >> 5][i & 31]));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(raw[i >> 5][i & 31]));
             }
+            mx = fmaxf(mx * scale_log2, -1e30f);
             // raise the running maximum only when it grew by more than the threshold
             float alpha = 1.f;
             if (mx > m_run + kRescaleThreshold) {
@@ -205,7 +238,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 m_run = mx;
             }
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // S_j complete implies O += P V of tile j-1 is complete (MMAs finish in issue order)
+                // O must not be in use by the tensor core: wait for P.V of tile j-1
+                if (ok && !mbar_wait(&s.bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1)) {
+                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                    ok = false;
+                }
+                tc::fence_after_sync();
                 if (ok) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
@@ -220,20 +258,29 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 }
             }
             l_run *= alpha;
+            // p = 2^(s * scale - m): one FFMA + one EX2 per score (-inf gives exactly 0)
             uint32_t ph[32];
-            float lsum = 0.f;
+            float lsum0 = 0.f, lsum1 = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                const float p0 = x[2 * i] > -1e29f ? fast_exp2(x[2 * i] - m_run) : 0.f;
-                const float p1 = x[2 * i + 1] > -1e29f ? fast_exp2(x[2 * i + 1] - m_run) : 0.f;
-                lsum += p0 + p1;
+                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[i >> 4][(2 * i) & 31]), scale_log2, -m_run));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[i >> 4][(2 * i + 1) & 31]), scale_log2, -m_run));
+                lsum0 += p0;
+                lsum1 += p1;
                 ph[i] = pack_h2(p0, p1);
             }
-            l_run += lsum;
+            l_run += lsum0 + lsum1;
+            // the P buffer of this parity was last read by P.V of tile j-2 (a barrier per buffer:
+            // a parity wait can only tell the current phase from the one before it)
+            if (j > 1 && ok && !mbar_wait(&s.bar_pv[j & 1], ((j >> 1) & 1) ^ 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
+            }
             // P row -> shared memory, K-major swizzled: chunk c of row r at (c ^ (r & 7)) * 16
+            unsigned char* pdst = s.p[j & 1] + r * 128;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(s.p + r * 128 + ((ch ^ (r & 7)) << 4)) =
+                *reinterpret_cast<uint4*>(pdst + ((ch ^ (r & 7)) << 4)) =
                     make_uint4(ph[4 * ch], ph[4 * ch + 1], ph[4 * ch + 2], ph[4 * ch + 3]);
             tc::fence_async_smem();
             tc::fence_before_sync();
