@@ -29,18 +29,19 @@ namespace {
 
 constexpr int kQRows = 128;
 constexpr int kKvTile = kPageTokens;              // 64
-constexpr int kStages = 2;                        // per ring: K tiles and V tiles are staged separately
+constexpr int kStages = 3;                        // per ring: K tiles and V tiles are staged separately
 constexpr int kSliceBytes = kPageTokens * kHeadDim * 2;   // 32 KiB
 constexpr int kThreads = 192;                     // 4 softmax warps + loader warp + MMA warp
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 128;        // S double-buffered in columns [0,64) and [64,128)
+// Tensor memory map (512 columns x 128 lanes, lane = query row): S double-buffered in columns
+// [0,64) and [64,128) -- P (fp16 pairs, 32 columns) overwrites the start of its S buffer --,
+// O in [128,384), Q (fp16 pairs) in [384,512).
+constexpr uint32_t kColS = 0, kColO = 128, kColQ = 384;
 constexpr float kRescaleThreshold = 8.f;          // log2 units
 
 struct Smem {
-    alignas(1024) unsigned char q[4][kQRows * 128];           // 64 KiB, 4 sub-tiles of 64 dims
     alignas(1024) unsigned char k[kStages][kSliceBytes];      // K page slices
     alignas(1024) unsigned char v[kStages][kSliceBytes];      // V page slices
-    alignas(1024) unsigned char p[2][kQRows * 128];           // 2 x 16 KiB, P tiles (128 x 64 fp16)
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
     uint64_t bar_s[2], bar_p, bar_pv[2], bar_done;
     uint32_t tmem_base;
@@ -80,32 +81,37 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         mbar_fence_init();
     }
     if (warp == 5) tc::tmem_alloc(&s.tmem_base, kTmemCols);
-    // Q rows -> shared memory (bf16 -> fp16 is exact for normal-range values)
-    if (tid < kQRows) {
-        const int r = tid;
-        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim;
-#pragma unroll 4
-        for (int ch = 0; ch < 32; ++ch) {
-            uint4 out = make_uint4(0, 0, 0, 0);
-            if (r < rows) {
-                const uint4 in = *reinterpret_cast<const uint4*>(src + ch * 8);
-                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in);
-                uint32_t o[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = __bfloat1622float2(b2[e]);
-                    o[e] = pack_h2(f.x, f.y);
-                }
-                out = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-            *reinterpret_cast<uint4*>(s.q[ch >> 3] + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = out;
-        }
-        tc::fence_async_smem();
-    }
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
+    // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
+    // normal-range values): thread r owns lane r, column c holds dims 2c, 2c+1
+    if (tid < kQRows) {
+        const int r = tid;
+        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim;
+        const uint32_t lane_addr = tmem + (uint32_t(warp * 32) << 16);
+#pragma unroll 1
+        for (int part = 0; part < 4; ++part) {
+            uint32_t regs[32];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                uint4 in = make_uint4(0, 0, 0, 0);
+                if (r < rows) in = *reinterpret_cast<const uint4*>(src + part * 64 + ch * 8);
+                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(b2[e]);
+                    regs[ch * 4 + e] = pack_h2(f.x, f.y);
+                }
+            }
+            tc::tmem_st32(lane_addr + kColQ + part * 32, regs);
+        }
+        tc::tmem_wait_st();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
 
     if (warp == 4) {
         // ------------------------------ page loader ------------------------------
@@ -137,20 +143,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::idesc_f16(kQRows, kKvTile, false, false);
             constexpr uint32_t idesc_pv = tc::idesc_f16(kQRows, kHeadDim, false, true);
-            const uint32_t q_addr = smem_u32(s.q[0]);
-            const uint32_t p_addr0 = smem_u32(s.p[0]);
             bool ok = true;
             auto issue_qk = [&](int j) {
                 const int st = j % kStages;
                 if (!mbar_wait(&s.k_full[st], (j / kStages) & 1)) { ok = false; return; }
                 tc::fence_after_sync();
                 const uint32_t k_addr = smem_u32(s.k[st]);
-                // 4 sub-tiles of 64 dims x 4 K-steps of 16 dims (32 bytes)
+                // 16 K-steps of 16 dims: A = 8 columns of Q in tensor memory, B = 32 bytes further
+                // into the 64-dim sub-tile of the K slice
 #pragma unroll
                 for (int kk = 0; kk < 16; ++kk) {
-                    const uint64_t da = tc::smem_desc(q_addr + (kk >> 2) * (kQRows * 128) + (kk & 3) * 32, 16, 1024);
                     const uint64_t db = tc::smem_desc(k_addr + (kk >> 2) * (kKvTile * 128) + (kk & 3) * 32, 16, 1024);
-                    tc::mma_ss(tmem + kColS + (j & 1) * 64, da, db, idesc_qk, kk > 0);
+                    tc::mma_ts(tmem + kColS + (j & 1) * 64, tmem + kColQ + kk * 8, db, idesc_qk, kk > 0);
                 }
                 tc::commit(&s.k_empty[st]);           // K stage free once S_j is done
                 tc::commit(&s.bar_s[j & 1]);
@@ -168,9 +172,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 const uint32_t v_addr = smem_u32(s.v[st]);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t da = tc::smem_desc(p_addr0 + (j & 1) * (kQRows * 128) + kk * 32, 16, 1024);
                     const uint64_t db = tc::smem_desc(v_addr + kk * (16 * 128), kKvTile * 128, 1024);
-                    tc::mma_ss(tmem + kColO, da, db, idesc_pv, (j > 0) || (kk > 0));
+                    tc::mma_ts(tmem + kColO, tmem + kColS + (j & 1) * 64 + kk * 8, db, idesc_pv, (j > 0) || (kk > 0));
                 }
                 tc::commit(&s.v_empty[st]);           // V stage free
                 tc::commit(&s.bar_pv[j & 1]);         // this P buffer free, O consistent
@@ -270,19 +273,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 ph[i] = pack_h2(p0, p1);
             }
             l_run += lsum0 + lsum1;
-            // the P buffer of this parity was last read by P.V of tile j-2 (a barrier per buffer:
-            // a parity wait can only tell the current phase from the one before it)
-            if (j > 1 && ok && !mbar_wait(&s.bar_pv[j & 1], ((j >> 1) & 1) ^ 1)) {
-                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
-                ok = false;
+            // P row -> tensor memory over the start of this tile's S buffer (which every thread of
+            // this warp has finished reading): the A operand of O += P V
+            if (ok) {
+                tc::tmem_st32(lane_addr + kColS + (j & 1) * 64, ph);
+                tc::tmem_wait_st();
             }
-            // P row -> shared memory, K-major swizzled: chunk c of row r at (c ^ (r & 7)) * 16
-            unsigned char* pdst = s.p[j & 1] + r * 128;
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(pdst + ((ch ^ (r & 7)) << 4)) =
-                    make_uint4(ph[4 * ch], ph[4 * ch + 1], ph[4 * ch + 2], ph[4 * ch + 3]);
-            tc::fence_async_smem();
             tc::fence_before_sync();
             mbar_arrive(&s.bar_p);
         }
