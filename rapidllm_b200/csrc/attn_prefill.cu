@@ -14,11 +14,12 @@
 // S = Q K^T (M 128, N 64, 16 MMAs of K 16), V as the MN-major B operand of O += P V (M 128,
 // N 256, 4 MMAs).  S (two buffers of 64 columns) and O (256 columns) live in tensor memory;
 // S of the next tile is issued before P.V of the current one, so the softmax of a tile
-// overlaps tensor-core work.  Four softmax
-// warps own one query row per thread (TMEM lane = row): scores are read with tcgen05.ld,
-// the running maximum is only raised when it grows by more than 2^8 (then O is rescaled in
-// TMEM), and P goes back to shared memory as the fp16 A operand of the second MMA.  Warp 4
-// streams pages, one thread of warp 5 issues all MMAs and signals completion through
+// overlaps tensor-core work.  Q and P are A operands read from tensor memory.  Eight softmax
+// warps: TMEM lane = query row, and the two warps that share a lane quadrant split a row's
+// 64 scores (and the columns of O) between them, exchanging the row maximum through shared
+// memory.  Scores are read with tcgen05.ld, the running maximum is only raised when it grows
+// by more than 2^8 (then O is rescaled in TMEM), and P overwrites the start of its S buffer.
+// Warp 8 streams pages, one thread of warp 9 issues all MMAs and signals completion through
 // tcgen05.commit on mbarriers.  All waits are bounded.
 #include "kernels.h"
 #include "tcgen05.cuh"
@@ -31,7 +32,8 @@ constexpr int kQRows = 128;
 constexpr int kKvTile = kPageTokens;              // 64
 constexpr int kStages = 3;                        // per ring: K tiles and V tiles are staged separately
 constexpr int kSliceBytes = kPageTokens * kHeadDim * 2;   // 32 KiB
-constexpr int kThreads = 192;                     // 4 softmax warps + loader warp + MMA warp
+constexpr int kSoftmaxThreads = 256;              // 8 softmax warps
+constexpr int kThreads = 320;                     // + loader warp + MMA warp
 constexpr uint32_t kTmemCols = 512;
 // Tensor memory map (512 columns x 128 lanes, lane = query row): S double-buffered in columns
 // [0,64) and [64,128) -- P (fp16 pairs, 32 columns) overwrites the start of its S buffer --,
@@ -44,6 +46,8 @@ struct Smem {
     alignas(1024) unsigned char v[kStages][kSliceBytes];      // V page slices
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
     uint64_t bar_s[2], bar_p, bar_pv[2], bar_done;
+    float xch[2][kQRows][2];                          // row maxima of the two column halves
+    float lsum[kQRows][2];
     uint32_t tmem_base;
     int failed;
 };
@@ -73,26 +77,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         }
         mbar_init(&s.bar_s[0], 1);
         mbar_init(&s.bar_s[1], 1);
-        mbar_init(&s.bar_p, 128);
+        mbar_init(&s.bar_p, kSoftmaxThreads);
         mbar_init(&s.bar_pv[0], 1);
         mbar_init(&s.bar_pv[1], 1);
         mbar_init(&s.bar_done, 1);
         s.failed = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tc::tmem_alloc(&s.tmem_base, kTmemCols);
+    if (warp == 9) tc::tmem_alloc(&s.tmem_base, kTmemCols);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
-    // normal-range values): thread r owns lane r, column c holds dims 2c, 2c+1
-    if (tid < kQRows) {
-        const int r = tid;
-        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim;
-        const uint32_t lane_addr = tmem + (uint32_t(warp * 32) << 16);
+    // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the two threads
+    // of a row stores 128 dims
+    if (tid < kSoftmaxThreads) {
+        const int half = warp >> 2, r = (warp & 3) * 32 + lane;
+        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + half * 128;
+        const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
 #pragma unroll 1
-        for (int part = 0; part < 4; ++part) {
+        for (int part = 0; part < 2; ++part) {
             uint32_t regs[32];
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
@@ -105,7 +110,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                     regs[ch * 4 + e] = pack_h2(f.x, f.y);
                 }
             }
-            tc::tmem_st32(lane_addr + kColQ + part * 32, regs);
+            tc::tmem_st32(lane_addr + kColQ + half * 64 + part * 32, regs);
         }
         tc::tmem_wait_st();
     }
@@ -113,7 +118,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     __syncthreads();
     tc::fence_after_sync();
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ page loader ------------------------------
         // K_j is needed early (S_j = Q K_j^T is issued one tile ahead), V_j late (O += P_j V_j):
         // two rings, each freed by the MMA that last read it.
@@ -136,7 +141,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             }
             if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
         // Order on the tensor pipe: S_0, S_1, PV_0, S_2, PV_1, ... so that the softmax of tile j
         // overlaps S_{j+1} and PV_{j-1}.
@@ -186,9 +191,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         }
     } else {
         // ------------------------------ softmax warps ------------------------------
-        const int r = tid;                                    // query row = TMEM lane
+        const int half = warp >> 2, quad = warp & 3;          // column half, TMEM lane quadrant
+        const int r = quad * 32 + lane;                       // query row = TMEM lane
         const int pos = a.pos0 + q0 + r;                      // its position (rows >= `rows` are padding)
-        const uint32_t lane_addr = tmem + (uint32_t(warp * 32) << 16);
+        const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
         const float scale_log2 = a.scale * 1.4426950408889634f;
         float m_run = -1e30f, l_run = 0.f;
         bool ok = true;
@@ -198,10 +204,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 ok = false;
             }
             tc::fence_after_sync();
-            uint32_t raw[2][32];
+            const uint32_t s_addr = lane_addr + kColS + (j & 1) * 64;
+            uint32_t raw[32];
             if (ok) {
-                tc::tmem_ld32(lane_addr + kColS + (j & 1) * 64, raw[0]);
-                tc::tmem_ld32(lane_addr + kColS + (j & 1) * 64 + 32, raw[1]);
+                tc::tmem_ld32(s_addr + half * 32, raw);
                 tc::tmem_wait_ld();
             }
             const int tok0 = j * kKvTile;
@@ -213,11 +219,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 }
                 const int first = last_pos + 1 - tok0;
                 unsigned char* vt = s.v[j % kStages];
-                for (int idx = tid; idx < (kKvTile - first) * 32; idx += 128) {
+                for (int idx = tid; idx < (kKvTile - first) * 32; idx += kSoftmaxThreads) {
                     const int row = first + (idx >> 5), c16 = idx & 31;
                     *reinterpret_cast<uint4*>(vt + (c16 >> 3) * (kKvTile * 128) + row * 128 + (c16 & 7) * 16) =
                         make_uint4(0, 0, 0, 0);
                 }
+                tc::fence_async_smem();
             }
             // raw scores -> maximum (scale > 0, so the maximum can be taken before scaling);
             // only tiles that reach past the first row's position need the causal mask
@@ -225,14 +232,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             float mx = -1e30f;
             if (masked) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    if (tok0 + i > pos) raw[i >> 5][i & 31] = 0xff800000u;     // -inf
-                    mx = fmaxf(mx, __uint_as_float(raw[i >> 5][i & 31]));
+                for (int i = 0; i < 32; ++i) {
+                    if (tok0 + half * 32 + i > pos) raw[i] = 0xff800000u;      // -inf
+                    mx = fmaxf(mx, __uint_as_float(raw[i]));
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(raw[i >> 5][i & 31]));
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
             }
+            // the row maximum over both halves: exchange with the partner warp of this quadrant
+            s.xch[j & 1][r][half] = mx;
+            named_bar_sync(1 + quad, 64);
+            mx = fmaxf(mx, s.xch[j & 1][r][half ^ 1]);
             mx = fmaxf(mx * scale_log2, -1e30f);
             // raise the running maximum only when it grew by more than the threshold
             float alpha = 1.f;
@@ -249,40 +260,44 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 tc::fence_after_sync();
                 if (ok) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+                    for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
                         uint32_t o[32];
-                        tc::tmem_ld32(lane_addr + kColO + c0, o);
+                        tc::tmem_ld32(lane_addr + kColO + half * 128 + c0, o);
                         tc::tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tc::tmem_st32(lane_addr + kColO + c0, o);
+                        tc::tmem_st32(lane_addr + kColO + half * 128 + c0, o);
                     }
                     tc::tmem_wait_st();
                 }
             }
             l_run *= alpha;
             // p = 2^(s * scale - m): one FFMA + one EX2 per score (-inf gives exactly 0)
-            uint32_t ph[32];
+            uint32_t ph[16];
             float lsum0 = 0.f, lsum1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[i >> 4][(2 * i) & 31]), scale_log2, -m_run));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[i >> 4][(2 * i + 1) & 31]), scale_log2, -m_run));
+            for (int i = 0; i < 16; ++i) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * i]), scale_log2, -m_run));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), scale_log2, -m_run));
                 lsum0 += p0;
                 lsum1 += p1;
                 ph[i] = pack_h2(p0, p1);
             }
             l_run += lsum0 + lsum1;
-            // P row -> tensor memory over the start of this tile's S buffer (which every thread of
-            // this warp has finished reading): the A operand of O += P V
+            // P row -> tensor memory over the start of this tile's S buffer (both warps of the
+            // quadrant are past their tcgen05.ld: the exchange barrier above): the A operand of
+            // O += P V; this thread's 32 tokens are fp16 columns [16 half, 16 half + 16)
             if (ok) {
-                tc::tmem_st32(lane_addr + kColS + (j & 1) * 64, ph);
+                tc::tmem_st16(s_addr + half * 16, ph);
                 tc::tmem_wait_st();
             }
             tc::fence_before_sync();
             mbar_arrive(&s.bar_p);
         }
         // ------------------------------ epilogue ------------------------------
+        s.lsum[r][half] = l_run;
+        named_bar_sync(1 + quad, 64);
+        l_run += s.lsum[r][half ^ 1];
         if (ok && !mbar_wait(&s.bar_done, 0)) {
             set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
             ok = false;
@@ -290,12 +305,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         tc::fence_after_sync();
         if (ok && !s.failed) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            float* dst = a.o + (size_t(q0 + r) * a.n_q + hq) * kHeadDim;
-            const float* gp = a.gate ? a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim : nullptr;
+            float* dst = a.o + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + half * 128;
+            const float* gp = a.gate ? a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + half * 128 : nullptr;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+            for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
                 uint32_t o[32];
-                tc::tmem_ld32(lane_addr + kColO + c0, o);
+                tc::tmem_ld32(lane_addr + kColO + half * 128 + c0, o);
                 tc::tmem_wait_ld();
                 if (r < rows) {
 #pragma unroll
@@ -317,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         tc::fence_before_sync();
     }
     __syncthreads();
-    if (warp == 5) tc::tmem_dealloc(tmem, kTmemCols);
+    if (warp == 9) tc::tmem_dealloc(tmem, kTmemCols);
 }
 
 size_t attn_prefill_smem_bytes() { return sizeof(Smem) + 1024; }
