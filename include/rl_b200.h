@@ -104,6 +104,27 @@ int rl_attn_decode(const void* k_pool, const void* v_pool, const int32_t* page_t
                    void* workspace, size_t workspace_bytes, const rl_attn_decode_params* p,
                    void* stream);
 
+/* rl_attn_decode for callers that must not allocate device memory and have none to lend:
+ * code running inside a memory-pool-managed or fixed-budget process where every cudaMalloc
+ * is forbidden or already spoken for (a serving engine that sized its pools at start-up,
+ * a plug-in loaded into someone else's allocator regime).  This entry point has no
+ * counterpart in the reference.  The split-KV partials go to a 4 MiB array that lives in
+ * the library's own device image (every GPU that loads the library holds it until exit)
+ * instead of a caller workspace; inputs and outputs are still the caller's.  Limits and rules:
+ *   - the call needs (SM count + batch * n_kv) * (n_q / n_kv) * 1032 bytes of that array,
+ *     rounded up to 512; anything beyond 4 MiB (for 24Q/4KV heads on a 148-SM part:
+ *     batch > 132) is refused with RL_ERR_RANGE and a message, nothing is launched;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - the first call on a device looks up the array's device address (and does the
+ *     library's one-time per-device set-up); make that first call outside any stream capture;
+ *   - all calls on a device share the array, which keeps the previous call's contents.
+ *     Nothing in it has to start at zero (every slot a call reads, that call wrote first),
+ *     but two calls that overlap on the GPU (different streams, or a graph replayed while
+ *     another call runs) race on it: serialise them. */
+int rl_attn_decode_noalloc(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                           const int32_t* seq_lens, const float* q, const float* gate, float* o,
+                           const rl_attn_decode_params* p, void* stream);
+
 /* Merge n_parts split-KV partials per row and apply the gate: the grid-level
  * (and cross-GPU) form of the warp merge at cuda_engine.cu:347-374.
  *   part_o  fp32 [n_parts][rows][256] unnormalised sums

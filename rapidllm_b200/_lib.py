@@ -80,6 +80,7 @@ SYMBOLS = {
     "rl_attn_decode_workspace_bytes": (_sz, [C.POINTER(AttnDecodeParams)]),
     "rl_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz,
                             C.POINTER(AttnDecodeParams), _vp]),
+    "rl_attn_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnDecodeParams), _vp]),
     "rl_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz,
                                     C.POINTER(AttnDecodeParams), _vp]),
     "rl_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnPrefillParams), _vp]),

@@ -386,6 +386,55 @@ int rl_attn_decode_partial(const void* k_pool, const void* v_pool, const int32_t
                             workspace_bytes, p, stream);
 }
 
+// ---- rl_attn_decode without any allocation: scratch in the library's device image -------------
+namespace {
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+// Split-KV partials of rl_attn_decode_noalloc.  One copy per GPU that loads this library.
+static __device__ __align__(256) unsigned char g_attn_scratch[kStaticScratchBytes];
+struct StaticScratch {
+    bool ready = false;
+    void* ptr = nullptr;
+};
+StaticScratch g_static_scratch[64];
+
+// The array's name is only a host-side handle: the kernels need its device address, looked
+// up once per device with that device current.
+int static_scratch(void** out) {
+    int dev = 0;
+    RL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RL_ERR_RANGE, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    StaticScratch& sc = g_static_scratch[dev];
+    if (!sc.ready) {
+        void* ptr = nullptr;
+        RL_CUDA(cudaGetSymbolAddress(&ptr, g_attn_scratch));
+        if (!ptr) return fail(RL_ERR_DEVICE, "cudaGetSymbolAddress returned a null address for the scratch array");
+        sc.ptr = ptr;
+        sc.ready = true;
+    }
+    *out = sc.ptr;
+    return RL_OK;
+}
+}  // namespace
+
+int rl_attn_decode_noalloc(const void* k_pool, const void* v_pool, const int32_t* page_table,
+                           const int32_t* seq_lens, const float* q, const float* gate, float* o,
+                           const rl_attn_decode_params* p, void* stream) {
+    if (int st = attn_check(p)) return st;
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    const size_t need = attn_plan(p, d->sms).total_bytes;
+    if (need > kStaticScratchBytes)
+        return fail(RL_ERR_RANGE,
+                    "rl_attn_decode_noalloc: batch %d x %d KV heads needs %zu bytes of split-KV scratch, the "
+                    "built-in array holds %zu; use rl_attn_decode with a caller workspace",
+                    p->batch, p->n_kv, need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (int st = static_scratch(&scratch)) return st;
+    return attn_decode_impl(k_pool, v_pool, page_table, seq_lens, q, gate, o, nullptr, scratch, kStaticScratchBytes,
+                            p, stream);
+}
+
 int rl_lse_combine(const float* part_o, const float* part_ml, const float* gate, float* o, int n_parts,
                    int rows, int head_dim, int wht_len, const float* tq_signs, void* stream) {
     if (head_dim != rl::kHeadDim) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 256", head_dim);
