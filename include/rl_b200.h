@@ -241,6 +241,28 @@ int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const 
                        const float* v, const float* beta, const float* g_log, float* o,
                        const rl_delta_recurrent_params* p, void* stream);
 
+/* DeltaChunkParams {n_v, dk, dv, seq, chunk, eps_l2} (params.h:21; declared but never
+ * implemented in the reference) + the key/query head layout. */
+typedef struct rl_delta_chunk_params {
+    int n_v, dk, dv;             /* 48, 128, 128 */
+    int seq;                     /* T tokens of this call */
+    int chunk;                   /* must be 64 */
+    float eps_l2;                /* 1e-6 */
+    int n_qk, head_map;          /* as in rl_delta_recurrent_params */
+} rl_delta_chunk_params;
+
+size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p);
+
+/* T consecutive delta-rule steps of ONE sequence in chunked (WY) form on the tensor cores:
+ * the result of calling ops::delta_recurrent_step (src/kernels/ops.cpp:495-540) T times, which
+ * is the reference's only prefill form (src/runtime/session.cpp:232-248; CUDA
+ * gdn_prefill_split2_k, cuda_engine.cu:4911-4974).  S fp32 [n_v][128][128] (one slot of the state
+ * cache) is read as the initial state and overwritten with the final one; q,k fp32
+ * [seq][n_qk][128], v [seq][n_v][128], beta/g_log [seq][n_v], o [seq][n_v][128]. */
+int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float* v, const float* beta,
+                           const float* g_log, float* o, void* workspace, size_t workspace_bytes,
+                           const rl_delta_chunk_params* p, void* stream);
+
 /* Conv1dParams {dim, k, silu} (params.h:19) + batch/slot fields. */
 typedef struct rl_conv1d_params {
     int dim, k, silu;            /* 10240, 4, 1 (silu must be 1) */

@@ -50,6 +50,11 @@ class DeltaRecurrentParams(C.Structure):
                 ("q_stride", C.c_longlong), ("k_stride", C.c_longlong), ("v_stride", C.c_longlong)]
 
 
+class DeltaChunkParams(C.Structure):
+    _fields_ = [("n_v", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("seq", C.c_int), ("chunk", C.c_int),
+                ("eps_l2", C.c_float), ("n_qk", C.c_int), ("head_map", C.c_int)]
+
+
 class Conv1dParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dim", "k", "silu", "batch", "n_slots")]
 
@@ -92,6 +97,8 @@ SYMBOLS = {
     "rl_kv_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_delta_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                 C.POINTER(DeltaRecurrentParams), _vp]),
+    "rl_delta_chunk_workspace_bytes": (_sz, [C.POINTER(DeltaChunkParams)]),
+    "rl_delta_chunk_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(DeltaChunkParams), _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),
     "rl_conv1d_causal": (_i, [_vp, _vp, _vp, _vp, _i, C.POINTER(Conv1dParams), _i, _vp]),
     "rl_cache_create": (_i, [C.POINTER(CacheConfig), C.POINTER(_vp)]),

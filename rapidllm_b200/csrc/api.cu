@@ -64,6 +64,10 @@ int dev_info(DevInfo** out) {
         RL_CUDA(cudaMemset(d.err_ptr, 0, sizeof(int)));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_f16_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::delta_chunk_prepare_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::delta_chunk_scan_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_prefill_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_tq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -642,6 +646,61 @@ int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const 
         reinterpret_cast<uintptr_t>(S) % 16)
         return fail(RL_ERR_RANGE, "S, q, k, v must be 16-byte aligned with strides a multiple of 4 floats");
     rl::launch_delta_decode(a, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+static int delta_chunk_check(const rl_delta_chunk_params* p) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->dk != 128 || p->dv != 128 || p->chunk != 64)
+        return fail(RL_ERR_UNSUPPORTED, "dk %d dv %d chunk %d: only 128 x 128, chunk 64", p->dk, p->dv, p->chunk);
+    if (p->n_v <= 0 || p->n_v > 65535 || p->seq < 0) return fail(RL_ERR_RANGE, "n_v %d seq %d", p->n_v, p->seq);
+    if (p->head_map == RL_HEADS_PER_VALUE ? p->n_qk != p->n_v
+                                          : (p->n_qk <= 0 || p->n_v % p->n_qk != 0 || p->head_map > RL_HEADS_TILED))
+        return fail(RL_ERR_RANGE, "n_qk %d does not fit n_v %d with head_map %d", p->n_qk, p->n_v, p->head_map);
+    return RL_OK;
+}
+
+size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p) {
+    if (delta_chunk_check(p)) return 0;
+    const size_t n_chunks = (size_t(p->seq) + 63) / 64;
+    return align_up(n_chunks * p->n_v * rl::delta_chunk_record_bytes(), 256) + align_up(n_chunks * p->n_v * sizeof(float), 256);
+}
+
+int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float* v, const float* beta,
+                           const float* g_log, float* o, void* workspace, size_t workspace_bytes,
+                           const rl_delta_chunk_params* p, void* stream) {
+    if (int st = delta_chunk_check(p)) return st;
+    if (p->seq == 0) return RL_OK;
+    if (!S || !q || !k || !v || !beta || !g_log || !o || !workspace) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    const size_t need = rl_delta_chunk_workspace_bytes(p);
+    if (workspace_bytes < need) return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, need);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 || reinterpret_cast<uintptr_t>(q) % 16 ||
+        reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16)
+        return fail(RL_ERR_RANGE, "workspace must be 256-byte aligned, q, k, v 16-byte aligned");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    const int n_chunks = (p->seq + 63) / 64;
+    rl::DeltaChunkArgs a;
+    a.S = S;
+    a.q = q;
+    a.k = k;
+    a.v = v;
+    a.beta = beta;
+    a.g_log = g_log;
+    a.o = o;
+    a.work = static_cast<unsigned char*>(workspace);
+    a.chunk_decay = reinterpret_cast<float*>(a.work + align_up(size_t(n_chunks) * p->n_v * rl::delta_chunk_record_bytes(), 256));
+    a.err = d->err_ptr;
+    a.T = p->seq;
+    a.n_v = p->n_v;
+    a.n_qk = p->n_qk;
+    a.head_map = p->head_map;
+    a.eps_l2 = p->eps_l2;
+    rl::delta_chunk_prepare_kernel<<<dim3(n_chunks, p->n_v), rl::delta_chunk_prepare_threads(),
+                                     rl::delta_chunk_prepare_smem_bytes(), as_stream(stream)>>>(a);
+    rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(),
+                                  as_stream(stream)>>>(a);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

@@ -122,6 +122,29 @@ struct DeltaDecodeArgs {
 };
 void launch_delta_decode(const DeltaDecodeArgs& a, cudaStream_t st);
 
+// ---- chunked (WY-form) DeltaNet prefill (tcgen05) --------------------------------------------
+struct DeltaChunkArgs {
+    float* S;                    // [n_v][128][128] fp32 state of one sequence, in place
+    const float* q;              // [T][n_qk][128]
+    const float* k;              // [T][n_qk][128]
+    const float* v;              // [T][n_v][128]
+    const float* beta;           // [T][n_v]
+    const float* g_log;          // [T][n_v]
+    float* o;                    // [T][n_v][128]
+    unsigned char* work;         // [n_chunks][n_v] records of delta_chunk_record_bytes()
+    float* chunk_decay;          // [n_chunks][n_v]
+    int* err;
+    int T, n_v, n_qk, head_map;
+    float eps_l2;
+};
+__global__ void delta_chunk_prepare_kernel(DeltaChunkArgs a);
+__global__ void delta_chunk_scan_kernel(DeltaChunkArgs a);
+size_t delta_chunk_record_bytes();
+size_t delta_chunk_prepare_smem_bytes();
+int delta_chunk_prepare_threads();
+size_t delta_chunk_scan_smem_bytes();
+int delta_chunk_scan_threads();
+
 // ---- causal depthwise conv1d + SiLU ------------------------------------------------
 struct ConvUpdateArgs {
     const float* x;              // [batch][dim]

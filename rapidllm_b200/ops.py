@@ -11,8 +11,8 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import (AttnDecodeParams, AttnPrefillParams, Conv1dParams, DeltaRecurrentParams,
-                   KvAppendParams, check, lib)
+from ._lib import (AttnDecodeParams, AttnPrefillParams, Conv1dParams, DeltaChunkParams,
+                   DeltaRecurrentParams, KvAppendParams, check, lib)
 
 PAGE_TOKENS = 64
 HEAD_DIM = 256
@@ -218,6 +218,28 @@ def delta_recurrent_step(S, q, k, v, beta, g_log, eps_l2=1e-6, slot_ids=None, he
     check(lib().rl_delta_recurrent(_p(S), _p(slot_ids), _p(q), _p(k), _p(v), _p(beta), _p(g_log),
                                    _p(o), C.byref(p), _stream()))
     return o[0] if single else o
+
+
+def delta_chunk_prefill(S, q, k, v, beta, g_log, eps_l2=1e-6, head_map=None, workspace=None):
+    """T delta-rule steps of one sequence in chunked (WY) form: the result of T calls of
+    ops::delta_recurrent_step.  S [n_v][128][128] fp32 in place; q,k [T][n_qk][128];
+    v [T][n_v][128]; beta,g_log [T][n_v]; returns o [T][n_v][128]."""
+    for t, n in ((S, "S"), (q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (g_log, "g_log")):
+        _need(t, torch.float32, n)
+    n_v, dk, dv = S.shape
+    T, n_qk = q.shape[0], q.shape[1]
+    if head_map is None:
+        head_map = _lib.RL_HEADS_PER_VALUE if n_qk == n_v else _lib.RL_HEADS_GROUPED
+    p = DeltaChunkParams(n_v=n_v, dk=dk, dv=dv, seq=T, chunk=64, eps_l2=eps_l2, n_qk=n_qk, head_map=head_map)
+    need = lib().rl_delta_chunk_workspace_bytes(C.byref(p))
+    if need == 0 and T > 0:
+        raise _lib.RlError(6, lib().rl_last_error().decode())
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=S.device)
+    o = torch.empty(T, n_v, dv, dtype=torch.float32, device=S.device)
+    check(lib().rl_delta_chunk_prefill(_p(S), _p(q), _p(k), _p(v), _p(beta), _p(g_log), _p(o), _p(workspace),
+                                       workspace.numel(), C.byref(p), _stream()))
+    return o
 
 
 def conv1d_update(x_t, w, state, slot_ids=None):
