@@ -1,0 +1,89 @@
+"""World-size-2 (gloo, CPU) checks of the multi-GPU division: the shard plan, the all_gather
+of head slices, and the split-KV exchange of (o, max, sum) partials merged like rl_lse_combine
+does -- with the oracle standing in for the kernels."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+from rapidllm_b200.shard import pages_of_part, plan_heads, plan_sequences
+
+
+def test_shard_plans():
+    for world in (1, 2, 4, 8):
+        shards = [plan_heads(r, world) for r in range(world)]
+        assert sorted(h for s in shards for h in s.v_heads) == list(range(48))
+        assert all(set(range(s.k_heads.start * 3, s.k_heads.stop * 3)) == set(s.v_heads) for s in shards)
+        cover = {}
+        for s in shards:
+            for h in s.kv_heads:
+                cover.setdefault(h, []).append(s.kv_part)
+            assert list(s.q_heads) == [6 * h + i for h in s.kv_heads for i in range(6)]
+            assert s.rank in s.peers and len(s.peers) == s.kv_split
+        assert sorted(cover) == [0, 1, 2, 3]
+        assert all(sorted(p) == list(range(max(1, world // 4))) for p in cover.values())
+    s = plan_heads(5, 8)
+    assert list(s.kv_heads) == [1] and s.kv_split == 2 and s.kv_part == 1 and s.peers == [1, 5]
+    assert pages_of_part(7, 2, 0) == [0, 2, 4, 6] and pages_of_part(7, 2, 1) == [1, 3, 5]
+    assert [len(plan_sequences(r, 4, 30)) for r in range(4)] == [8, 8, 7, 7]
+    with pytest.raises(ValueError):
+        plan_heads(0, 3)
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import Oracle
+    orc = Oracle()
+    rng = np.random.default_rng(0)                      # same inputs on every rank
+    n_q, n_kv, hd, seq = 12, 2, 64, 64 * 5 + 20
+    q = rng.standard_normal((n_q, hd), dtype=np.float32)
+    k = rng.standard_normal((seq, n_kv, hd), dtype=np.float32)
+    v = rng.standard_normal((seq, n_kv, hd), dtype=np.float32)
+    full = orc.attn_decode(q, k, v)
+    # (1) head sharding: every rank computes its KV head's query heads, one all_gather
+    sh = plan_heads(rank, world, n_q=n_q, n_kv=n_kv, n_v=4, n_k=2)
+    mine = orc.attn_decode(q[sh.q_heads.start:sh.q_heads.stop], k[:, sh.kv_heads.start:sh.kv_heads.stop],
+                           v[:, sh.kv_heads.start:sh.kv_heads.stop])
+    parts = [torch.empty(mine.shape) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(mine))
+    ok_heads = np.array_equal(torch.cat(parts).numpy(), full)
+    # (2) split-KV: rank holds alternating pages of every head; exchange (o, max, sum)
+    n_pages = (seq + 63) // 64
+    tok = np.concatenate([np.arange(p * 64, min(seq, p * 64 + 64)) for p in pages_of_part(n_pages, world, rank)])
+    po = np.empty((n_q, hd), np.float32)
+    pml = np.empty((n_q, 2), np.float32)
+    for h in range(n_q):
+        m, l, acc = orc.attn_partial(q[h], k[tok], v[tok], 0, len(tok), h // (n_q // n_kv))
+        po[h], pml[h] = acc, (m, l)
+    go = [torch.empty(n_q, hd) for _ in range(world)]
+    gml = [torch.empty(n_q, 2) for _ in range(world)]
+    dist.all_gather(go, torch.from_numpy(po))
+    dist.all_gather(gml, torch.from_numpy(pml))
+    merged = np.stack([orc.lse_combine([x[h, 0].item() for x in gml], [x[h, 1].item() for x in gml],
+                                       np.stack([x[h].numpy() for x in go])) for h in range(n_q)])
+    err = float(np.abs(merged - full).max())
+    # (3) a rank that fails is seen by the others on the host, not by a hung collective
+    flag = torch.tensor([1 if rank == 1 else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    ret[rank] = (ok_heads, err, int(flag.item()))
+    dist.destroy_process_group()
+
+
+def test_two_ranks_gloo():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    for r in range(world):
+        ok_heads, err, flag = ret[r]
+        assert ok_heads
+        assert err < 1e-5
+        assert flag == 1
