@@ -64,6 +64,8 @@ int dev_info(DevInfo** out) {
         RL_CUDA(cudaMemset(d.err_ptr, 0, sizeof(int)));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_f16_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::delta_decode_stream_kernel_ptr(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::delta_decode_stream_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::delta_chunk_prepare_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -645,7 +647,7 @@ int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const 
         reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16 ||
         reinterpret_cast<uintptr_t>(S) % 16)
         return fail(RL_ERR_RANGE, "S, q, k, v must be 16-byte aligned with strides a multiple of 4 floats");
-    rl::launch_delta_decode(a, as_stream(stream));
+    rl::launch_delta_decode(a, d->sms, as_stream(stream));
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

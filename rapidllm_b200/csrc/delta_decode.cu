@@ -118,10 +118,157 @@ __global__ void __launch_bounds__(256) delta_decode_kernel(DeltaDecodeArgs a) {
     }
 }
 
+// ---- large batches: persistent CTAs streaming whole heads through shared memory with TMA ----
+// One work item = one (sequence, value head): its 64 KiB of S is contiguous in HBM.  A producer
+// thread bulk-loads items into a 3-stage ring; 256 consumer threads decay, reduce S^T k, then
+// apply the rank-1 update, reduce S^T q and stream the new state straight back to HBM.  While
+// one item is computed two more are in flight, independent of registers or occupancy.
+constexpr int kStreamStages = 3;
+constexpr int kStreamThreads = 288;            // 8 consumer warps + producer warp
+constexpr int kHeadBytes = kDk * kDv * 4;      // 64 KiB
+
+struct StreamSmem {
+    alignas(128) float S[kStreamStages][kDk * kDv];
+    float q[2][kDk], k[2][kDk];
+    float red[8][kDv], red2[8][kDv];
+    uint64_t full[kStreamStages], empty[kStreamStages];
+};
+
+__global__ void __launch_bounds__(kStreamThreads, 1) delta_decode_stream_kernel(DeltaDecodeArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    StreamSmem& s = *reinterpret_cast<StreamSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_items = a.batch * a.n_v;
+    if (tid == 0) {
+        for (int i = 0; i < kStreamStages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], 1);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    auto slot_of = [&](int b) {
+        int slot = a.slot_ids ? a.slot_ids[b] : b;
+        if (slot < 0 || slot >= a.n_slots) {
+            set_err(a.err, DEV_ERR_BAD_SLOT);
+            slot = -1;
+        }
+        return slot;
+    };
+
+    if (warp == 8) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+                const int st = it % kStreamStages;
+                if (!mbar_wait(&s.empty[st], ((it / kStreamStages) & 1) ^ 1)) {
+                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                    break;
+                }
+                const int b = item / a.n_v, h = item - b * a.n_v;
+                const int slot = slot_of(b);
+                const float* src = a.S + (size_t(slot < 0 ? 0 : slot) * a.n_v + h) * (kDk * kDv);
+                mbar_arrive_expect_tx(&s.full[st], kHeadBytes);
+                bulk_g2s(s.S[st], src, kHeadBytes, &s.full[st]);
+            }
+        }
+        return;
+    }
+    // ------------------------------ consumers ------------------------------
+    const int rep = a.n_v / a.n_qk;
+    const int cg = tid & 31;                  // columns 4cg .. 4cg+3
+    const int rg = tid >> 5;                  // rows 16rg .. 16rg+15 (= warp)
+    uint32_t it = 0;
+    bool alive = true;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+        const int st = it % kStreamStages;
+        const int b = item / a.n_v, h = item - b * a.n_v;
+        const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
+        const int slot = slot_of(b);
+        // l2 norms of q (warp 0) and k (warp 1) into buffer it & 1
+        if (warp < 2) {
+            const float* src = warp == 0 ? a.q + size_t(b) * a.q_stride + size_t(hs) * kDk
+                                         : a.k + size_t(b) * a.k_stride + size_t(hs) * kDk;
+            const float4 x = *reinterpret_cast<const float4*>(src + lane * 4);
+            double ss = double(x.x) * x.x + double(x.y) * x.y + double(x.z) * x.z + double(x.w) * x.w;
+            for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+            float inv = 1.f / sqrtf(float(ss) + a.eps_l2);
+            if (warp == 0) inv *= 1.f / sqrtf(float(kDk));
+            float* dst = warp == 0 ? s.q[it & 1] : s.k[it & 1];
+            *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(x.x * inv, x.y * inv, x.z * inv, x.w * inv);
+        }
+        const float g = expf(a.g_log[size_t(b) * a.n_v + h]);
+        const float beta = a.beta[size_t(b) * a.n_v + h];
+        const float4 vv = *reinterpret_cast<const float4*>(a.v + size_t(b) * a.v_stride + size_t(h) * kDv + cg * 4);
+        if (alive && !mbar_wait(&s.full[st], (it / kStreamStages) & 1)) {
+            set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+            alive = false;
+        }
+        named_bar_sync(1, 256);               // q, k of this item visible
+        const float* Sp = s.S[st];
+        float* Sg = a.S + (size_t(slot < 0 ? 0 : slot) * a.n_v + h) * (kDk * kDv);
+        const float* kq = s.k[it & 1];
+        const float* qq = s.q[it & 1];
+        // pass 1: kv = (g S)^T k over this warp's 16 rows
+        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (alive) {
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const int i = 16 * rg + r;
+                const float4 x = *reinterpret_cast<const float4*>(Sp + i * kDv + cg * 4);
+                const float ki = kq[i] * g;
+                kv.x += x.x * ki; kv.y += x.y * ki; kv.z += x.z * ki; kv.w += x.w * ki;
+            }
+        }
+        *reinterpret_cast<float4*>(&s.red[rg][cg * 4]) = kv;
+        named_bar_sync(1, 256);
+        float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 t = *reinterpret_cast<const float4*>(&s.red[w][cg * 4]);
+            tot.x += t.x; tot.y += t.y; tot.z += t.z; tot.w += t.w;
+        }
+        const float4 dl = make_float4((vv.x - tot.x) * beta, (vv.y - tot.y) * beta, (vv.z - tot.z) * beta,
+                                      (vv.w - tot.w) * beta);
+        // pass 2: S = g S + k (x) delta written back to HBM, o = S^T q
+        float4 oo = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (alive) {
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const int i = 16 * rg + r;
+                float4 x = *reinterpret_cast<const float4*>(Sp + i * kDv + cg * 4);
+                const float ki = kq[i], qi = qq[i];
+                x.x = x.x * g + ki * dl.x; x.y = x.y * g + ki * dl.y; x.z = x.z * g + ki * dl.z; x.w = x.w * g + ki * dl.w;
+                oo.x += x.x * qi; oo.y += x.y * qi; oo.z += x.z * qi; oo.w += x.w * qi;
+                if (slot >= 0) __stcs(reinterpret_cast<float4*>(Sg + i * kDv + cg * 4), x);
+            }
+        }
+        *reinterpret_cast<float4*>(&s.red2[rg][cg * 4]) = oo;
+        named_bar_sync(1, 256);               // every thread is done reading this stage
+        if (tid < kDv) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += s.red2[w][tid];
+            if (slot >= 0) a.o[(size_t(b) * a.n_v + h) * kDv + tid] = t;
+        }
+        if (tid == 0) mbar_arrive(&s.empty[st]);
+    }
+}
+
 }  // namespace
 
-void launch_delta_decode(const DeltaDecodeArgs& a, cudaStream_t st) {
+size_t delta_decode_stream_smem_bytes() { return sizeof(StreamSmem) + 128; }
+const void* delta_decode_stream_kernel_ptr() { return reinterpret_cast<const void*>(&delta_decode_stream_kernel); }
+
+void launch_delta_decode(const DeltaDecodeArgs& a, int sms, cudaStream_t st) {
     if (a.batch <= 0) return;
+    const int items = a.batch * a.n_v;
+    if (sms > 0 && items >= 4 * sms) {
+        // enough heads to keep every SM streaming: one persistent CTA per SM
+        delta_decode_stream_kernel<<<sms, kStreamThreads, delta_decode_stream_smem_bytes(), st>>>(a);
+        return;
+    }
     dim3 grid(kSlices, a.n_v, a.batch);
     delta_decode_kernel<<<grid, 256, 0, st>>>(a);
 }

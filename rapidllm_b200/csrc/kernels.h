@@ -120,7 +120,9 @@ struct DeltaDecodeArgs {
     float eps_l2;
     long long q_stride, k_stride, v_stride;   // floats between sequences
 };
-void launch_delta_decode(const DeltaDecodeArgs& a, cudaStream_t st);
+void launch_delta_decode(const DeltaDecodeArgs& a, int sms, cudaStream_t st);
+size_t delta_decode_stream_smem_bytes();
+const void* delta_decode_stream_kernel_ptr();
 
 // ---- chunked (WY-form) DeltaNet prefill (tcgen05) --------------------------------------------
 struct DeltaChunkArgs {

@@ -147,3 +147,32 @@ def test_conv1d_update_and_prefill(oracle, golden):
         assert np.array_equal(sd[0].cpu().numpy(), s)
         assert np.abs(ops.conv1d_causal_prefill(x.cuda(), ww.cuda()).cpu().numpy() - ref).max() < 2e-6
     _lib.check_device()
+
+
+def test_large_batch_streaming_path(oracle):
+    """Batch 16 x 48 heads takes the persistent TMA-streamed kernel; two steps, shuffled slots."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(33)
+    B, n_slots = 16, 20
+    S0 = torch.randn(n_slots, N_V, DK, DV, generator=gen) * 0.02
+    slots = torch.randperm(n_slots, generator=gen)[:B].int()
+    S = S0.cuda().clone()
+    Sr = S0.numpy().copy()
+    for step in range(2):
+        q = torch.randn(B, N_K, DK, generator=gen)
+        k = torch.randn(B, N_K, DK, generator=gen)
+        v = torch.randn(B, N_V, DV, generator=gen)
+        beta = torch.sigmoid(torch.randn(B, N_V, generator=gen))
+        g = -softplus(torch.randn(B, N_V, generator=gen))
+        o = ops.delta_recurrent_step(S, q.cuda(), k.cuda(), v.cuda(), beta.cuda(), g.cuda(),
+                                     slot_ids=slots.cuda(), head_map=1)
+        _lib.check_device()
+        for b in range(B):
+            sl = int(slots[b])
+            oref = oracle.delta_step(Sr[sl], oracle.repeat_heads(q[b].numpy(), N_V),
+                                     oracle.repeat_heads(k[b].numpy(), N_V), v[b].numpy(), beta[b].numpy(),
+                                     g[b].numpy())
+            assert np.abs(o[b].cpu().numpy() - oref).max() < 2e-5
+    assert rel_l2(S.cpu().numpy(), Sr) < 1e-6
+    untouched = [s for s in range(n_slots) if s not in slots.tolist()]
+    assert np.array_equal(S[untouched].cpu().numpy(), S0[untouched].numpy())
