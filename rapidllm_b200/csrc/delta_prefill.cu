@@ -48,13 +48,16 @@ __device__ __forceinline__ int tile_off(int row, int x) {
 
 constexpr int kPrepThreads = 256;
 constexpr int kPad = kD + 1;
+constexpr int kB = 16;                    // block size of the triangular inverse
 
 struct PrepSmem {
     float kn[kC][kPad];       // k^
     float qn[kC][kPad];       // q^
-    float a[kC][kC + 1];      // k^.k^ -> A
-    float p[kC][kC + 1];      // q^.k^ -> P
-    float t[kC][kC + 1];      // (I + A)^-1
+    float kk[kC][kC + 1];     // k^_t . k^_i   (shared by the value heads of this key head)
+    float qk[kC][kC + 1];     // q^_t . k^_i
+    float l[kC][kC + 1];      // A (strictly lower part of I + A)
+    float m[kC][kC + 1];      // (I + A)^-1
+    float tmp[kC][kC + 1];
     float G[kC], beta[kC], eg[kC];
 };
 
@@ -62,17 +65,16 @@ struct PrepSmem {
 
 size_t delta_chunk_record_bytes() { return kRecordBytes; }
 
-// grid (n_chunks, n_v), 256 threads
+// grid (n_chunks, n_qk), 256 threads: one CTA per chunk and key/query head; the dot products
+// k^.k^ and q^.k^ are computed once and reused by every value head that maps to this key head.
 __global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
-    const int chunk = blockIdx.x, h = blockIdx.y;
+    const int chunk = blockIdx.x, hs = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rep = a.n_v / a.n_qk;
-    const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
+    const int rep = a.head_map == 0 ? 1 : a.n_v / a.n_qk;
     const int t0 = chunk * kC;
     const int n_tok = min(kC, a.T - t0);
-    unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
 
     // ---- l2 norms (double accumulators as ops::l2norm); padded tokens are all zero ----
     for (int t = warp; t < kC; t += kPrepThreads / 32) {
@@ -95,28 +97,12 @@ __global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(Delta
         s.qn[t][lane * 4 + 0] = qx.x * qi; s.qn[t][lane * 4 + 1] = qx.y * qi;
         s.qn[t][lane * 4 + 2] = qx.z * qi; s.qn[t][lane * 4 + 3] = qx.w * qi;
     }
-    // ---- cumulative log decay, beta ----
-    if (tid < kC) {
-        const bool live = tid < n_tok;
-        s.beta[tid] = live ? a.beta[size_t(t0 + tid) * a.n_v + h] : 0.f;
-        s.G[tid] = live ? a.g_log[size_t(t0 + tid) * a.n_v + h] : 0.f;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        float run = 0.f;
-        for (int t = 0; t < kC; ++t) {
-            run += s.G[t];
-            s.G[t] = run;
-            s.eg[t] = expf(run);
-        }
-        a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(run);
-    }
     __syncthreads();
     // ---- k^.k^ and q^.k^ (lower triangle), 4 x 4 outputs per thread ----
     {
         const int tb = (tid >> 4) * 4, ib = (tid & 15) * 4;
+        float kk[4][4] = {}, qk[4][4] = {};
         if (ib <= tb + 3) {
-            float kk[4][4] = {}, qk[4][4] = {};
             for (int d = 0; d < kD; ++d) {
                 float kt[4], qt[4], ki[4];
 #pragma unroll
@@ -133,64 +119,123 @@ __global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(Delta
                         qk[x][y] += qt[x] * ki[y];
                     }
             }
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                for (int y = 0; y < 4; ++y) {
-                    const int t = tb + x, i = ib + y;
-                    const float dec = i <= t ? expf(s.G[t] - s.G[i]) : 0.f;
-                    s.a[t][i] = i < t ? s.beta[t] * dec * kk[x][y] : 0.f;
-                    s.p[t][i] = dec * qk[x][y];
-                }
-        } else {
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                for (int y = 0; y < 4; ++y) {
-                    s.a[tb + x][ib + y] = 0.f;
-                    s.p[tb + x][ib + y] = 0.f;
-                }
         }
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) {
+                s.kk[tb + x][ib + y] = kk[x][y];
+                s.qk[tb + x][ib + y] = qk[x][y];
+            }
     }
     __syncthreads();
-    // ---- T = (I + A)^-1 by forward substitution; thread c owns column c ----
-    if (tid < kC) {
-        const int c = tid;
-        for (int t = 0; t < kC; ++t) {
-            float acc = t == c ? 1.f : 0.f;
-            for (int i = c; i < t; ++i) acc -= s.a[t][i] * s.t[i][c];   // T is lower triangular: T[i][c] = 0 for i < c
-            s.t[t][c] = t >= c ? acc : 0.f;
+
+    for (int r = 0; r < rep; ++r) {
+        const int h = a.head_map == 0 ? hs : (a.head_map == 1 ? hs * rep + r : hs + r * a.n_qk);
+        unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
+        // ---- cumulative log decay, beta ----
+        if (tid < kC) {
+            const bool live = tid < n_tok;
+            s.beta[tid] = live ? a.beta[size_t(t0 + tid) * a.n_v + h] : 0.f;
+            float gl = live ? a.g_log[size_t(t0 + tid) * a.n_v + h] : 0.f;
+            // inclusive scan over 64 values held by two warps
+            for (int off = 1; off < 32; off <<= 1) {
+                const float o = __shfl_up_sync(0xffffffffu, gl, off);
+                if (lane >= off) gl += o;
+            }
+            s.G[tid] = gl;
         }
-    }
-    __syncthreads();
-    // ---- tiles: T diag(beta), P (64 x 64); W, Qg, Kt, V (64 x 128), fp16, swizzled ----
-    const float gC = s.G[kC - 1];
-    for (int idx = tid; idx < kC * kC / 2; idx += kPrepThreads) {
-        const int t = idx >> 5, i = (idx & 31) * 2;
-        *reinterpret_cast<uint32_t*>(rec + kOffT + tile_off(t, i)) = pack_h2(s.t[t][i] * s.beta[i], s.t[t][i + 1] * s.beta[i + 1]);
-        *reinterpret_cast<uint32_t*>(rec + kOffP + tile_off(t, i)) = pack_h2(s.p[t][i], s.p[t][i + 1]);
-    }
-    for (int idx = tid; idx < kC * kD / 2; idx += kPrepThreads) {
-        const int t = idx >> 6, d = (idx & 63) * 2;
-        // W[t][d] = sum_{i<=t} T[t][i] beta_i exp(G_i) k^[i][d]
-        float w0 = 0.f, w1 = 0.f;
-        for (int i = 0; i <= t; ++i) {
-            const float c = s.t[t][i] * s.beta[i] * s.eg[i];
-            w0 += c * s.kn[i][d];
-            w1 += c * s.kn[i][d + 1];
+        __syncthreads();
+        if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
+        __syncthreads();
+        if (tid < kC) s.eg[tid] = expf(s.G[tid]);
+        if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
+        // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t ----
+        for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
+            const int t = idx >> 6, i = idx & 63;
+            s.l[t][i] = i < t ? s.beta[t] * expf(s.G[t] - s.G[i]) * s.kk[t][i] : 0.f;
+            s.m[t][i] = t == i ? 1.f : 0.f;
         }
-        const int o = tile_off(t, d);
-        *reinterpret_cast<uint32_t*>(rec + kOffW + o) = pack_h2(w0, w1);
-        *reinterpret_cast<uint32_t*>(rec + kOffQg + o) = pack_h2(s.eg[t] * s.qn[t][d], s.eg[t] * s.qn[t][d + 1]);
-        const float kt = expf(gC - s.G[t]);
-        *reinterpret_cast<uint32_t*>(rec + kOffKt + o) = pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]);
-        float v0 = 0.f, v1 = 0.f;
-        if (t < n_tok) {
-            const float2 vv = *reinterpret_cast<const float2*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
-            v0 = vv.x;
-            v1 = vv.y;
+        __syncthreads();
+        // ---- M = (I + A)^-1, blocked: 16 x 16 diagonal blocks by forward substitution ... ----
+        if (tid < kC) {
+            const int bb = (tid >> 4) * kB, c = tid & 15;           // thread owns column c of block bb
+            for (int t = c + 1; t < kB; ++t) {
+                float acc = 0.f;
+                for (int i = c; i < t; ++i) acc -= s.l[bb + t][bb + i] * s.m[bb + i][bb + c];
+                s.m[bb + t][bb + c] = acc;
+            }
         }
-        *reinterpret_cast<uint32_t*>(rec + kOffV + o) = pack_h2(v0, v1);
+        __syncthreads();
+        // ... then block row by block row: M_ij = -M_ii (sum_{j<=k<i} A_ik M_kj), j < i
+        for (int bi = 1; bi < kC / kB; ++bi) {
+            for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
+                const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
+                float acc = 0.f;
+                for (int kx = bj * kB; kx < bi * kB; ++kx) acc += s.l[bi * kB + x][kx] * s.m[kx][bj * kB + y];
+                s.tmp[bi * kB + x][bj * kB + y] = acc;
+            }
+            __syncthreads();
+            for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
+                const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
+                float acc = 0.f;
+                for (int kx = 0; kx <= x; ++kx) acc -= s.m[bi * kB + x][bi * kB + kx] * s.tmp[bi * kB + kx][bj * kB + y];
+                s.m[bi * kB + x][bj * kB + y] = acc;
+            }
+            __syncthreads();
+        }
+        // ---- tiles: T = M diag(beta), P (64 x 64); W, Qg, Kt, V (64 x 128), fp16, swizzled ----
+        const float gC = s.G[kC - 1];
+        for (int idx = tid; idx < kC * kC / 2; idx += kPrepThreads) {
+            const int t = idx >> 5, i = (idx & 31) * 2;
+            *reinterpret_cast<uint32_t*>(rec + kOffT + tile_off(t, i)) =
+                pack_h2(s.m[t][i] * s.beta[i], s.m[t][i + 1] * s.beta[i + 1]);
+            const float p0 = i <= t ? expf(s.G[t] - s.G[i]) * s.qk[t][i] : 0.f;
+            const float p1 = i + 1 <= t ? expf(s.G[t] - s.G[i + 1]) * s.qk[t][i + 1] : 0.f;
+            *reinterpret_cast<uint32_t*>(rec + kOffP + tile_off(t, i)) = pack_h2(p0, p1);
+        }
+        // fold beta_i exp(G_i) into M once: tmp[t][i] = M[t][i] beta_i exp(G_i)
+        for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
+            const int t = idx >> 6, i = idx & 63;
+            s.tmp[t][i] = s.m[t][i] * s.beta[i] * s.eg[i];
+        }
+        __syncthreads();
+        // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] (tmp is zero above the diagonal).  Warp w owns rows
+        // w, w+8, ..., in two groups of four that share the k^ loads; lane owns dims 2l, 2l+1 (+64).
+        for (int grp = 0; grp < 2; ++grp) {
+            const int tr0 = warp + 8 * (4 * grp);
+            float acc[4][4] = {};
+            const int i_max = tr0 + 24;
+            for (int i = 0; i <= i_max; ++i) {
+                const float k0 = s.kn[i][2 * lane], k1 = s.kn[i][2 * lane + 1];
+                const float k2 = s.kn[i][2 * lane + 64], k3 = s.kn[i][2 * lane + 65];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float c = s.tmp[tr0 + 8 * r][i];
+                    acc[r][0] += c * k0; acc[r][1] += c * k1; acc[r][2] += c * k2; acc[r][3] += c * k3;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int t = tr0 + 8 * r;
+                *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane)) = pack_h2(acc[r][0], acc[r][1]);
+                *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane + 64)) = pack_h2(acc[r][2], acc[r][3]);
+            }
+        }
+        for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
+            const int t = idx >> 5, d = (idx & 31) * 4;
+            const int o = tile_off(t, d);
+            const float e = s.eg[t];
+            *reinterpret_cast<uint2*>(rec + kOffQg + o) =
+                make_uint2(pack_h2(e * s.qn[t][d], e * s.qn[t][d + 1]), pack_h2(e * s.qn[t][d + 2], e * s.qn[t][d + 3]));
+            const float kt = expf(gC - s.G[t]);
+            *reinterpret_cast<uint2*>(rec + kOffKt + o) =
+                make_uint2(pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]), pack_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3]));
+            float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < n_tok) vv = *reinterpret_cast<const float4*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
+            *reinterpret_cast<uint2*>(rec + kOffV + o) = make_uint2(pack_h2(vv.x, vv.y), pack_h2(vv.z, vv.w));
+        }
+        __syncthreads();
     }
 }
 
