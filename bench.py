@@ -50,6 +50,10 @@ def parse():
                     choices=["stack", "compact_decode", "f16_decode", "delta_step", "attn_prefill", "delta_prefill"],
                     help="stack = the headline workload; the others time one operator at the shapes of "
                          "BASELINE configs 2, 0 and 1 (secondary lines, N=1 only)")
+    ap.add_argument("--shard", default="seq", choices=["seq", "heads"],
+                    help="N > 1: seq = every rank owns 32 sequences of its own (weak scaling, no collective); "
+                         "heads = ONE batch of 32 divided by KV / value heads (up to 4 ways) and then by sequence, "
+                         "head outputs all-gathered over NCCL every step (strong scaling)")
     ap.add_argument("--wht-len", type=int, default=128)
     ap.add_argument("--op-batch", type=int, default=0, help="operator workloads: override the batch")
     ap.add_argument("--op-ctx", type=int, default=0, help="operator workloads: override the context")
@@ -467,14 +471,25 @@ def main():
     if not _lib.lib().rl_b200_available():
         raise SystemExit("no sm_100 device: the CUDA path is the only path")
 
-    ctx = contexts(args, rank)
-    B = args.batch
+    heads_mode = args.shard == "heads" and world > 1
+    head_ways = 1
+    if heads_mode:
+        # head shards first (at most one KV head per rank), then sequence shards
+        from rapidllm_b200.shard import plan_heads, plan_sequences
+        head_ways = min(world, N_KV)
+        hshard = plan_heads(rank % head_ways, head_ways)
+        seqs = plan_sequences(rank // head_ways, world // head_ways, args.batch)
+        ctx = [contexts(args, 0)[b] for b in seqs]
+    else:
+        ctx = contexts(args, rank)
+    B = len(ctx)
     pages = [(c + PAGE - 1) // PAGE for c in ctx]
     max_pages = max(pages)
     n_pages = sum(pages)
     types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
     cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages,
-                        max_seq_len=max(ctx))
+                        max_seq_len=max(ctx), n_q=N_Q // head_ways, n_kv=N_KV // head_ways,
+                        n_v=N_V // head_ways, n_k=N_K // head_ways)
     gen = torch.Generator(device="cuda").manual_seed(args.seed + 1000 * rank)
     for a in range(cache.n_attn):
         cache.k_pool(a).normal_(generator=gen)
@@ -505,6 +520,17 @@ def main():
     dev["conv_w"] = conv_w.cuda()
     stream = torch.cuda.current_stream()
 
+    gathered = None
+    if heads_mode:
+        gathered = (torch.empty((world,) + tuple(dev["attn_o"].shape), device="cuda"),
+                    torch.empty((world,) + tuple(dev["delta_o"].shape), device="cuda"))
+
+    def exchange():
+        # what a tensor-parallel model does with the mixer outputs: every rank gets every head slice
+        if heads_mode:
+            dist.all_gather_into_tensor(gathered[0], dev["attn_o"])
+            dist.all_gather_into_tensor(gathered[1], dev["delta_o"])
+
     def sync_all():
         torch.cuda.synchronize()
         if world > 1:
@@ -515,6 +541,7 @@ def main():
     cache.set_timing(True)
     for _ in range(max(3, args.warmup)):
         cache.decode(dev, B)
+        exchange()
     _lib.check_device()
     sync_all()
     sampler = ClockSampler(local)
@@ -524,6 +551,7 @@ def main():
     e0.record(stream)
     for _ in range(args.steps):
         cache.decode(dev, B)
+        exchange()
         for k, v in cache.timing().items():      # waits for this step's last event
             fam[k] = fam.get(k, 0.0) + v
     e1.record(stream)
@@ -537,11 +565,12 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
     ms_per_step = ms_max / args.steps
-    value = B * world / (ms_per_step * 1e-3)
+    total_seqs = args.batch if heads_mode else B * world
+    value = total_seqs / (ms_per_step * 1e-3)
 
     # ---------------- end to end through the host-buffer entry point ----------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not heads_mode:
         for _ in range(2):
             cache.decode_host(host, B)
         sync_all()
@@ -571,6 +600,8 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         ab = algorithmic_bytes(args, ctx)
+        if heads_mode:
+            ab = {k: v / head_ways for k, v in ab.items()}
         n_attn = cache.n_attn
         attn_ms_per_launch = fam["attn_decode"] / args.steps / max(1, n_attn)
         achieved = ab["attn_decode"] / (attn_ms_per_launch * 1e-3) / 1e9
@@ -584,14 +615,17 @@ def main():
         line = {
             "metric": "hybrid-layer decode steps/sec", "value": value, "unit": "seq-steps/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 KV / f32 state",
-            "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if heads_mode else "weak", "vs_baseline": None,
+            "dtype": "f16 KV / f32 state", "data": "synthetic",
             "config": {"workload": workload_name(args), "l2": "inputs larger than L2 (%.1f GB streamed per step)"
-                       % (ab["step"] / 1e9), "parallelism": "sequence-sharded x%d, no collective" % world,
+                       % (ab["step"] / 1e9),
+                       "parallelism": ("heads x%d then sequences x%d, NCCL all_gather of head outputs"
+                                       % (head_ways, world // head_ways)) if heads_mode
+                       else "sequence-sharded x%d, no collective" % world,
                        "ctx_tokens_rank0": sum(ctx), "cache_bytes_rank0": cache.bytes},
             "clocks": clocks,
             "gpu_launches": cache.launches_per_step * args.steps,
-            "step_hbm_gbs": ab["step"] * world / (ms_per_step * 1e-3) / 1e9,
+            "step_hbm_gbs": ab["step"] * world / (ms_per_step * 1e-3) / 1e9,   # rank 0's bytes x ranks
             "roofline": {"bound": "hbm", "kernel": "attn_decode_f16_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "fallback 6650 (of fallback)",
