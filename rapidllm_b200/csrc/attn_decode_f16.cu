@@ -30,7 +30,7 @@ namespace {
 constexpr int kStageTokens = 32;                 // half a page
 constexpr int kStages = 6;
 constexpr int kSlots = 3;                        // consumer warp pairs
-constexpr int kConsumerWarps = split::kConsumerWarps;
+constexpr int kConsumerWarps = 6;
 static_assert(kConsumerWarps == 2 * kSlots, "two warps per stage in flight");
 // 6 consumer warps + 1 producer warp + 1 idle warp: 256 threads lets every thread have 255 registers
 constexpr int kThreads = 256;
@@ -44,7 +44,7 @@ using split::Segment;
 
 struct Smem {
     alignas(128) unsigned char stage[kStages][kStageBytes];
-    split::Shared sp;
+    split::Shared<kConsumerWarps> sp;
     uint64_t full[kStages];
     uint64_t empty[kStages];
 };

@@ -22,11 +22,9 @@ namespace rl {
 
 namespace {
 
-constexpr int kStages = 12;
-constexpr int kSlots = 3;
-constexpr int kConsumerWarps = split::kConsumerWarps;
-static_assert(kConsumerWarps == 2 * kSlots, "two warps per stage in flight");
-constexpr int kThreads = 256;                      // 6 consumer + 1 producer + 1 idle warp
+constexpr int kStages = 14;
+constexpr int kConsumerWarps = 7;                  // each consumes whole records, round-robin
+constexpr int kThreads = 256;                      // 7 consumer warps + 1 producer warp
 using split::kNegBig;
 using split::Segment;
 
@@ -35,7 +33,7 @@ struct Smem {
     // 6-bit index (code of the even token | code of the odd token << 3) -> fp16x2 centroids;
     // one copy per lane ([index][lane]) so that a warp's 32 lookups never share a bank
     alignas(128) uint32_t lut[64][32];
-    split::Shared sp;
+    split::Shared<kConsumerWarps> sp;
     uint64_t full[kStages];
     uint64_t empty[kStages];
 };
@@ -84,7 +82,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&s.full[i], 1);
-            mbar_init(&s.empty[i], 2);
+            mbar_init(&s.empty[i], 1);
         }
         mbar_fence_init();
     }
@@ -96,7 +94,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     int u_begin, u_end;
     split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end);
 
-    if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
         // The warp reads 32 page ids at a time (one per lane), so that the page-table latency is
@@ -138,10 +135,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     }
 
     // -------------------------------- consumers --------------------------------
+    // A warp takes every 7th record (32 tokens): scores for all 32 tokens first (four independent
+    // int8 MMA chains), one online-softmax update, then the two 16-token halves of P.V.
     const int g = lane >> 2;
     const int c = lane & 3;
-    const int slot = warp >> 1;
-    const int tb = (warp & 1) * 16;                // this warp's tokens inside a record
     const float scale_log2 = a.scale * 1.4426950408889634f;
     const uint32_t lut = smem_u32(&s.lut[0][lane]);
     const uint32_t stage0 = smem_u32(s.stage[0]);
@@ -212,38 +209,39 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
         float l_run = 0.f;
 
         for (int hp = w.hp0; hp < w.hp1; ++hp, ++it) {
-            if (int(it % kSlots) != slot) continue;
+            if (int(it % kConsumerWarps) != warp) continue;
             const int st = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
             if (alive && !mbar_wait(&s.full[st], ph)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 alive = false;
             }
-            const int n_valid = min(kCompactHalfTokens, w.len - hp * kCompactHalfTokens) - tb;
-            if (alive && n_valid > 0) {
+            const int n_valid = min(kCompactHalfTokens, w.len - hp * kCompactHalfTokens);
+            if (alive) {
                 const uint32_t rec = stage0 + st * kCompactRecordBytes;
-                // ---- scores from the stored int8 rows ----
-                int sc[2][4];
+                // ---- scores from the stored int8 rows: n-tile nt = tokens 8nt .. 8nt+7 ----
+                int sc[4][4];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+                for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) sc[nt][e] = 0;
-                    const int r = tb + 8 * nt + g;
-                    const uint32_t rowp = rec + r * 256;
 #pragma unroll
-                    for (int L = 0; L < 4; ++L) {
+                for (int L = 0; L < 4; ++L) {
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        const int r = 8 * nt + g;
                         const int chunk = (4 * L + c) ^ ((r & 1) << 2);
-                        const uint4 kk = lds128(rowp + chunk * 16);
+                        const uint4 kk = lds128(rec + r * 256 + chunk * 16);
                         mma_s8(sc[nt], qa[L][0][0], qa[L][0][1], qa[L][0][2], qa[L][0][3], kk.x, kk.y);
                         mma_s8(sc[nt], qa[L][1][0], qa[L][1][1], qa[L][1][2], qa[L][1][3], kk.z, kk.w);
                     }
                 }
-                // ---- online softmax; columns 2c, 2c+1 of n-tile nt are tokens tb + 8nt + 2c (+1) ----
-                float p[4];
+                // ---- online softmax; columns 2c, 2c+1 of n-tile nt are tokens 8nt + 2c (+1) ----
+                float p[8];
                 float mx = kNegBig;
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    const uint32_t ks_raw = lds32(rec + kCompactKScaleOff + (tb + 8 * nt + 2 * c) * 2);
+                for (int nt = 0; nt < 4; ++nt) {
+                    const uint32_t ks_raw = lds32(rec + kCompactKScaleOff + (8 * nt + 2 * c) * 2);
                     const float2 ks = __half22float2(*reinterpret_cast<const __half2*>(&ks_raw));
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
@@ -273,44 +271,48 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
                     m_run = m_new;
                 }
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
+                for (int e = 0; e < 8; ++e) {
                     p[e] = p[e] > 0.5f * kNegBig ? fast_exp2(p[e] - m_run) : 0.f;
                     l_run += p[e];
                 }
-                // fold the V scales into P: one B operand per transform block (dims 0-127 / 128-255)
-                uint32_t pb[2][2];
+                // ---- the two 16-token halves: acc[dims][heads] += centroids(V codes)^T (P * scale)^T ----
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    const uint2 raw = lds64(rec + kCompactVScaleOff + (tb + 8 * nt + 2 * c) * 4);
-                    const float2 t0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));  // even token
-                    const float2 t1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));  // odd token
-                    // rows beyond the sequence may hold anything: their p is 0, keep the product 0
-                    const float p0 = p[nt * 2], p1 = p[nt * 2 + 1];
-                    pb[0][nt] = pack_h2(p0 > 0.f ? p0 * t0.x : 0.f, p1 > 0.f ? p1 * t1.x : 0.f);
-                    pb[1][nt] = pack_h2(p0 > 0.f ? p0 * t0.y : 0.f, p1 > 0.f ? p1 * t1.y : 0.f);
-                }
-                // ---- acc[dims][heads] += centroids(V codes)^T (P * scale)^T, rotated domain ----
-                uint32_t wa[6], wb[6];
-                {
-                    const uint32_t va = rec + kCompactVOff + (tb >> 4) * 1536 + g * 96 + c * 24;
-                    const uint2 a0 = lds64(va), a1 = lds64(va + 8), a2 = lds64(va + 16);
-                    const uint2 b0 = lds64(va + 768), b1 = lds64(va + 776), b2 = lds64(va + 784);
-                    wa[0] = a0.x; wa[1] = a0.y; wa[2] = a1.x; wa[3] = a1.y; wa[4] = a2.x; wa[5] = a2.y;
-                    wb[0] = b0.x; wb[1] = b0.y; wb[2] = b1.x; wb[3] = b1.y; wb[4] = b2.x; wb[5] = b2.y;
-                }
-                // codes of rows past the end are arbitrary but finite table entries; with p = 0
-                // they contribute exactly 0, nothing to clear
+                for (int blk = 0; blk < 2; ++blk) {
+                    // fold the V scales into P: one B operand per transform block (dims 0-127 / 128-255)
+                    uint32_t pb[2][2];
+#pragma unroll
+                    for (int q2 = 0; q2 < 2; ++q2) {
+                        const int nt = 2 * blk + q2;
+                        const uint2 raw = lds64(rec + kCompactVScaleOff + (8 * nt + 2 * c) * 4);
+                        const float2 t0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));  // even token
+                        const float2 t1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));  // odd token
+                        // rows beyond the sequence may hold anything: their p is 0, keep the product 0
+                        const float p0 = p[nt * 2], p1 = p[nt * 2 + 1];
+                        pb[0][q2] = pack_h2(p0 > 0.f ? p0 * t0.x : 0.f, p1 > 0.f ? p1 * t1.x : 0.f);
+                        pb[1][q2] = pack_h2(p0 > 0.f ? p0 * t0.y : 0.f, p1 > 0.f ? p1 * t1.y : 0.f);
+                    }
+                    uint32_t wa[6], wb[6];
+                    {
+                        const uint32_t va = rec + kCompactVOff + blk * 1536 + g * 96 + c * 24;
+                        const uint2 a0 = lds64(va), a1 = lds64(va + 8), a2 = lds64(va + 16);
+                        const uint2 b0 = lds64(va + 768), b1 = lds64(va + 776), b2 = lds64(va + 784);
+                        wa[0] = a0.x; wa[1] = a0.y; wa[2] = a1.x; wa[3] = a1.y; wa[4] = a2.x; wa[5] = a2.y;
+                        wb[0] = b0.x; wb[1] = b0.y; wb[2] = b1.x; wb[3] = b1.y; wb[4] = b2.x; wb[5] = b2.y;
+                    }
+                    // codes of rows past the end are arbitrary but finite table entries; with p = 0
+                    // they contribute exactly 0, nothing to clear
 #define RL_TQ_LUT(W, BIT) lds32(lut + index_offset<(BIT)>(W))
 #define RL_TQ_MMA(J, I)                                                                              \
     mma_f16(acc[J][I], RL_TQ_LUT(wa, 12 * (4 * (J) + (I))), RL_TQ_LUT(wa, 12 * (4 * (J) + (I)) + 6), \
             RL_TQ_LUT(wb, 12 * (4 * (J) + (I))), RL_TQ_LUT(wb, 12 * (4 * (J) + (I)) + 6),            \
             pb[(J) >> 1][0], pb[(J) >> 1][1]);
-                RL_TQ_MMA(0, 0) RL_TQ_MMA(0, 1) RL_TQ_MMA(0, 2) RL_TQ_MMA(0, 3)
-                RL_TQ_MMA(1, 0) RL_TQ_MMA(1, 1) RL_TQ_MMA(1, 2) RL_TQ_MMA(1, 3)
-                RL_TQ_MMA(2, 0) RL_TQ_MMA(2, 1) RL_TQ_MMA(2, 2) RL_TQ_MMA(2, 3)
-                RL_TQ_MMA(3, 0) RL_TQ_MMA(3, 1) RL_TQ_MMA(3, 2) RL_TQ_MMA(3, 3)
+                    RL_TQ_MMA(0, 0) RL_TQ_MMA(0, 1) RL_TQ_MMA(0, 2) RL_TQ_MMA(0, 3)
+                    RL_TQ_MMA(1, 0) RL_TQ_MMA(1, 1) RL_TQ_MMA(1, 2) RL_TQ_MMA(1, 3)
+                    RL_TQ_MMA(2, 0) RL_TQ_MMA(2, 1) RL_TQ_MMA(2, 2) RL_TQ_MMA(2, 3)
+                    RL_TQ_MMA(3, 0) RL_TQ_MMA(3, 1) RL_TQ_MMA(3, 2) RL_TQ_MMA(3, 3)
 #undef RL_TQ_MMA
 #undef RL_TQ_LUT
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.empty[st]);

@@ -1,23 +1,24 @@
 // Pieces shared by the split-KV decode kernels (F16 and compact KV): the division of
-// the work among the persistent CTAs, and the fixed-order merge of the six consumer
-// warps of a CTA.
+// the work among the persistent CTAs, and the fixed-order merge of the consumer warps
+// of a CTA.
 #pragma once
 #include "common.cuh"
 
 namespace rl {
 namespace split {
 
-constexpr int kConsumerWarps = 6;            // three pairs; the merge below is a tree over six
-constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kMaxBatch = 1024;
 constexpr float kNegBig = -1e30f;
 constexpr int kMergeStride = kHeadDim + 1;   // row stride 257 floats: conflict-free
 
+// NW = consumer warps of the kernel (6..8); the merge tree needs NW - 4 buffers
+template <int NW>
 struct Shared {
-    float o[3][8][kMergeStride];    // segment merge buffers
-    float m[kConsumerWarps][8];
-    float l[kConsumerWarps][8];
-    int prefix[kMaxBatch + 1];      // half pages (32 tokens) before sequence b, per KV head
+    static_assert(NW >= 6 && NW <= 8, "merge tree written for 6..8 consumer warps");
+    float o[NW - 4][8][kMergeStride];   // segment merge buffers
+    float m[NW][8];
+    float l[NW][8];
+    int prefix[kMaxBatch + 1];          // half pages (32 tokens) before sequence b, per KV head
 };
 
 // The work of a launch is the list of all (sequence b, KV head h, half page hp) units in the
@@ -36,7 +37,8 @@ struct Segment {
 __device__ __forceinline__ int half_pages(int len) { return (len + 31) >> 5; }
 
 // Warp 0 fills s.prefix; lengths outside [0, max_pages_per_seq * 64] count as 0 and are reported.
-__device__ __forceinline__ void build_prefix(Shared& s, const int32_t* seq_lens, int len_add, int batch,
+template <int NW>
+__device__ __forceinline__ void build_prefix(Shared<NW>& s, const int32_t* seq_lens, int len_add, int batch,
                                              int max_pages_per_seq, int* err, int lane) {
     int run = 0;
     for (int b0 = 0; b0 < batch; b0 += 32) {
@@ -61,7 +63,8 @@ __device__ __forceinline__ void build_prefix(Shared& s, const int32_t* seq_lens,
     if (lane == 0) s.prefix[batch] = run;
 }
 
-__device__ __forceinline__ void cta_range(const Shared& s, int batch, int n_kv, int& begin, int& end) {
+template <int NW>
+__device__ __forceinline__ void cta_range(const Shared<NW>& s, int batch, int n_kv, int& begin, int& end) {
     const int total = s.prefix[batch] * n_kv;
     const int q = (total + int(gridDim.x) - 1) / int(gridDim.x);
     begin = min(int(blockIdx.x) * q, total);
@@ -69,7 +72,8 @@ __device__ __forceinline__ void cta_range(const Shared& s, int batch, int n_kv, 
 }
 
 // The segment that starts at unit `pos` (pos < end <= total).
-__device__ __forceinline__ Segment segment_at(const Shared& s, int pos, int end, int batch, int n_kv,
+template <int NW>
+__device__ __forceinline__ Segment segment_at(const Shared<NW>& s, int pos, int end, int batch, int n_kv,
                                               const int32_t* seq_lens, int len_add) {
     Segment g;
     int lo = 0, hi = batch;         // largest b with prefix[b] * n_kv <= pos
@@ -91,9 +95,11 @@ __device__ __forceinline__ Segment segment_at(const Shared& s, int pos, int end,
 // acc[j][i][0..3] of lane (g, c) holds dims d = 64j + 8*dsel + 2i (+1 for [2],[3]) of heads
 // 2c ([0],[2]) and 2c+1 ([1],[3]); m_run is the running maximum (log2 domain) of head g and
 // l_run this lane's share of the row sum.  All consumer threads must call this.
-__device__ __forceinline__ void merge_segment(Shared& s, float (&acc)[4][4][4], float m_run, float l_run,
+template <int NW>
+__device__ __forceinline__ void merge_segment(Shared<NW>& s, float (&acc)[4][4][4], float m_run, float l_run,
                                               int warp, int lane, int dsel, int G, float* part_o,
                                               float* part_ml, size_t item) {
+    constexpr int kThreads = NW * 32;
     const int g = lane >> 2, c = lane & 3;
     const int tid = warp * 32 + lane;
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -102,14 +108,14 @@ __device__ __forceinline__ void merge_segment(Shared& s, float (&acc)[4][4][4], 
         s.m[warp][g] = m_run;
         s.l[warp][g] = l_run;
     }
-    named_bar_sync(1, kConsumerThreads);
-    {   // scale this warp's accumulators to the item-wide maximum
+    named_bar_sync(1, kThreads);
+    {   // scale this warp's accumulators to the segment-wide maximum
         float f[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             float mm = kNegBig;
 #pragma unroll
-            for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
+            for (int ww = 0; ww < NW; ++ww) mm = fmaxf(mm, s.m[ww][2 * c + e]);
             f[e] = fast_exp2(s.m[warp][2 * c + e] - mm);
         }
 #pragma unroll
@@ -122,9 +128,9 @@ __device__ __forceinline__ void merge_segment(Shared& s, float (&acc)[4][4][4], 
                 acc[j][i][3] *= f[1];
             }
     }
-    // Fixed-order tree (bit-reproducible, unlike atomics): warps 3,4,5 -> buffers 0,1,2; warps
-    // 0,1,2 add; warps 1,2 -> buffers 0,1; warp 0 adds them in order and leaves the total in
-    // buffer 2.  Lanes with dsel >= 4 touch the odd dim first so a warp's 32 accesses hit 32 banks.
+    // Fixed-order binary tree (bit-reproducible, unlike atomics): at stride 4, 2, 1 the warps
+    // [stride, 2 stride) store their accumulators and the warps below add them.  Lanes with
+    // dsel >= 4 touch the odd dim first so a warp's 32 accesses hit 32 banks.
     const int odd = dsel >> 2;
     auto put = [&](float (*buf)[kMergeStride]) {
 #pragma unroll
@@ -152,29 +158,26 @@ __device__ __forceinline__ void merge_segment(Shared& s, float (&acc)[4][4][4], 
                 acc[j][i][3] += odd ? y0 : y1;
             }
     };
-    if (warp >= 3) put(s.o[warp - 3]);
-    named_bar_sync(1, kConsumerThreads);
-    if (warp < 3) add(s.o[warp]);
-    named_bar_sync(1, kConsumerThreads);
-    if (warp == 1 || warp == 2) put(s.o[warp - 1]);
-    named_bar_sync(1, kConsumerThreads);
-    if (warp == 0) {
-        add(s.o[0]);
-        add(s.o[1]);
-        put(s.o[2]);
+#pragma unroll
+    for (int stride = 4; stride >= 1; stride >>= 1) {
+        if (warp >= stride && warp < 2 * stride) put(s.o[warp - stride]);
+        named_bar_sync(1, kThreads);
+        if (warp < stride && warp + stride < NW) add(s.o[warp]);
+        named_bar_sync(1, kThreads);
     }
-    named_bar_sync(1, kConsumerThreads);
+    if (warp == 0) put(s.o[0]);
+    named_bar_sync(1, kThreads);
     float* po = part_o + item * G * kHeadDim;
-    for (int x = tid; x < G * kHeadDim; x += kConsumerThreads) po[x] = s.o[2][x >> 8][x & (kHeadDim - 1)];
+    for (int x = tid; x < G * kHeadDim; x += kThreads) po[x] = s.o[0][x >> 8][x & (kHeadDim - 1)];
     if (tid < G) {
         float mm = kNegBig;
-        for (int ww = 0; ww < kConsumerWarps; ++ww) mm = fmaxf(mm, s.m[ww][tid]);
+        for (int ww = 0; ww < NW; ++ww) mm = fmaxf(mm, s.m[ww][tid]);
         float ll = 0.f;
-        for (int ww = 0; ww < kConsumerWarps; ++ww) ll += s.l[ww][tid] * fast_exp2(s.m[ww][tid] - mm);
+        for (int ww = 0; ww < NW; ++ww) ll += s.l[ww][tid] * fast_exp2(s.m[ww][tid] - mm);
         part_ml[(item * G + tid) * 2 + 0] = mm * 0.6931471805599453f;   // natural-log units
         part_ml[(item * G + tid) * 2 + 1] = ll;
     }
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(1, kThreads);
 }
 
 }  // namespace split
