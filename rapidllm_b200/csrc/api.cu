@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -535,6 +536,7 @@ int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, c
     a.n_kv = p->n_kv;
     a.n_pages = p->n_pages;
     a.scale = 1.f / sqrtf(float(p->head_dim));
+    a.trace = reinterpret_cast<unsigned long long*>(getenv("RL_B200_PREFILL_TRACE") ? strtoull(getenv("RL_B200_PREFILL_TRACE"), nullptr, 0) : 0ull);
     const int n_qtiles = (p->seq + rl::attn_prefill_q_rows() - 1) / rl::attn_prefill_q_rows();
     rl::attn_prefill_kernel<<<dim3(n_qtiles, p->n_q), rl::attn_prefill_threads(), rl::attn_prefill_smem_bytes(),
                               as_stream(stream)>>>(a);

@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
+    const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0;
+#define RL_TRACE(J, SLOT) if (tr && (J) < 64) a.trace[(J) * 8 + (SLOT)] = global_ns();
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
     // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the two threads
     // of a row stores 128 dims
@@ -168,11 +170,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             for (int j = 0; j < n_tiles && ok; ++j) {
                 // S buffer (j+1)&1 was last read by the softmax of tile j-1, which finished before
                 // it signalled P_{j-1} (awaited in the previous iteration)
+                RL_TRACE(j, 0)
                 if (j + 1 < n_tiles) issue_qk(j + 1);
                 if (!ok) break;
+                RL_TRACE(j, 1)
                 const int st = j % kStages;
                 if (!mbar_wait(&s.v_full[st], (j / kStages) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_p, j & 1)) { ok = false; break; }
+                RL_TRACE(j, 2)
                 tc::fence_after_sync();
                 const uint32_t v_addr = smem_u32(s.v[st]);
 #pragma unroll
@@ -182,6 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 }
                 tc::commit(&s.v_empty[st]);           // V stage free
                 tc::commit(&s.bar_pv[j & 1]);         // this P buffer free, O consistent
+                RL_TRACE(j, 3)
             }
             if (!ok) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -204,6 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 ok = false;
             }
             tc::fence_after_sync();
+            if (tid == 0) { RL_TRACE(j, 4) }
             const uint32_t s_addr = lane_addr + kColS + (j & 1) * 64;
             uint32_t raw[32];
             if (ok) {
@@ -240,6 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
             }
+            if (tid == 0) { RL_TRACE(j, 5) }
             // the row maximum over both halves: exchange with the partner warp of this quadrant
             s.xch[j & 1][r][half] = mx;
             named_bar_sync(1 + quad, 64);
@@ -271,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                     tc::tmem_wait_st();
                 }
             }
+            if (tid == 0) { RL_TRACE(j, 6) }
             l_run *= alpha;
             // p = 2^(s * scale - m): one FFMA + one EX2 per score (-inf gives exactly 0)
             uint32_t ph[16];
@@ -293,6 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             }
             tc::fence_before_sync();
             mbar_arrive(&s.bar_p);
+            if (tid == 0) { RL_TRACE(j, 7) }
         }
         // ------------------------------ epilogue ------------------------------
         s.lsum[r][half] = l_run;
