@@ -7,8 +7,8 @@
 // replaces the reference's CUDA-core prefill kernels and its cuBLAS TF32 path
 // (launch_attn_gqa_gemm, 9038-9125).
 //
-// One CTA = 128 query rows of one query head.  Q (bf16 -> fp16) sits in shared memory as a
-// K-major 128-byte-swizzled operand.  KV tiles are whole pages: a (page, head) slice is
+// One CTA = 128 query rows of one query head.  Q (bf16 -> fp16) is written once into tensor
+// memory.  KV tiles are whole pages: a (page, head) slice is
 // stored in HBM in exactly the tensor-core tile format (kv_slice_offset), so a tile moves
 // with linear TMA bulk copies and is consumed in place: K as the K-major B operand of
 // S = Q K^T (M 128, N 64, 16 MMAs of K 16), V as the MN-major B operand of O += P V (M 128,
