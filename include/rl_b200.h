@@ -344,6 +344,13 @@ typedef struct rl_stack_io {
  * Per linear-attention layer: conv1d_update on the q|k|v channels, then the
  * delta rule.  All pointers in io are device pointers. */
 int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream);
+/* Graph replay of rl_stack_decode, the counterpart of the reference's captured decode step
+ * (cuda_engine.cu:18787-18789 keeps positions on the device for that purpose).  Enabled by
+ * default: the first step with a given io (same pointers and batch) runs as plain launches,
+ * the second is captured into a CUDA graph, later ones replay it.  Positions, page table and
+ * slot ids are read from device memory at run time, so the caller may advance them between
+ * steps; a different io re-captures.  Disabled while rl_stack_set_timing is on. */
+int rl_stack_set_graph(rl_cache* c, int enable);
 
 /* The same step for a caller that keeps its tensors in HOST memory (pinned for
  * full speed): copies every input of io (host pointers) to staging buffers on

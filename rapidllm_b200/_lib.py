@@ -114,6 +114,7 @@ SYMBOLS = {
     "rl_stack_set_conv_w": (_i, [_vp, _vp]),
     "rl_stack_launches_per_step": (_i, [_vp]),
     "rl_stack_set_timing": (_i, [_vp, _i]),
+    "rl_stack_set_graph": (_i, [_vp, _i]),
     "rl_stack_timing": (_i, [_vp, C.POINTER(C.c_float)]),
 }
 

@@ -82,6 +82,10 @@ class HybridCache:
     def launches_per_step(self):
         return lib().rl_stack_launches_per_step(self._h)
 
+    def set_graph(self, enable: bool):
+        """Graph replay of decode() (on by default; off while timing is on)."""
+        check(lib().rl_stack_set_graph(self._h, int(enable)))
+
     def set_timing(self, enable: bool):
         check(lib().rl_stack_set_timing(self._h, int(enable)))
 

@@ -216,6 +216,14 @@ struct rl_cache {
     bool timing = false;
     std::vector<cudaEvent_t> tev;   // 4 per layer: boundaries between the layer's kernels
     int tev_used = 0;
+    // graph replay of rl_stack_decode: the step's launches are captured once per distinct io
+    // (same pointers, same batch) and replayed afterwards; positions, page table and slots are
+    // read from device memory by the kernels, so the captured step stays valid as they advance
+    bool graph_enabled = true;
+    cudaGraphExec_t gexec = nullptr;
+    rl_stack_io gkey;               // io of the captured graph / of the last eager step
+    int gkey_seen = 0;              // 0 none, 1 ran eagerly once, 2 captured
+    cudaStream_t s_cap = nullptr;
     rl_attn_decode_params attn_params(int batch) const {
         rl_attn_decode_params p;
         std::memset(&p, 0, sizeof p);
@@ -482,7 +490,9 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     a.max_pages_per_seq = p->max_pages_per_seq;
     a.pos0 = p->pos0;
     a.rows_fp16 = p->rows_fp16;
-    rl::kv_write_kernel<<<dim3(p->n_tok, p->n_kv, p->batch), 32, 0, as_stream(stream)>>>(a);
+    const int rows_per_block = p->n_tok >= 8 ? 8 : 1;
+    rl::kv_write_kernel<<<dim3((p->n_tok + rows_per_block - 1) / rows_per_block, p->n_kv, p->batch),
+                          dim3(32, rows_per_block), 0, as_stream(stream)>>>(a);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -806,6 +816,8 @@ void rl_cache_destroy(rl_cache* c) {
     for (cudaEvent_t e : c->ev_in) cudaEventDestroy(e);
     for (cudaEvent_t e : c->ev_out) cudaEventDestroy(e);
     for (cudaEvent_t e : c->tev) cudaEventDestroy(e);
+    if (c->gexec) cudaGraphExecDestroy(c->gexec);
+    if (c->s_cap) cudaStreamDestroy(c->s_cap);
     if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
     if (c->s_run) cudaStreamDestroy(c->s_run);
     if (c->s_d2h) cudaStreamDestroy(c->s_d2h);
@@ -880,7 +892,57 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
     if ((c->n_attn && (!io->attn_q || !io->attn_k || !io->attn_v || !io->attn_o || !io->page_table || !io->pos)) ||
         (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    if (!c->graph_enabled || c->timing) return stack_decode_layers(c, io, as_stream(stream), false);
+    const rl_stack_io& k = c->gkey;
+    const bool same = c->gkey_seen > 0 && k.attn_q == io->attn_q && k.attn_gate == io->attn_gate &&
+                      k.attn_k == io->attn_k && k.attn_v == io->attn_v && k.attn_o == io->attn_o &&
+                      k.delta_qkv == io->delta_qkv && k.delta_beta == io->delta_beta && k.delta_g == io->delta_g &&
+                      k.delta_o == io->delta_o && k.conv_w == io->conv_w && k.page_table == io->page_table &&
+                      k.pos == io->pos && k.slot_ids == io->slot_ids && k.batch == io->batch;
+    if (same && c->gkey_seen == 2) {
+        RL_CUDA(cudaGraphLaunch(c->gexec, as_stream(stream)));
+        return RL_OK;
+    }
+    if (!same) {
+        // first step with this io: run it eagerly (also finishes every lazy set-up outside capture)
+        if (c->gexec) {
+            cudaGraphExecDestroy(c->gexec);
+            c->gexec = nullptr;
+        }
+        c->gkey = *io;
+        c->gkey_seen = 1;
+        return stack_decode_layers(c, io, as_stream(stream), false);
+    }
+    // second step with the same io: capture on an internal stream, then replay on the caller's
+    if (!c->s_cap) RL_CUDA(cudaStreamCreateWithFlags(&c->s_cap, cudaStreamNonBlocking));
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(c->s_cap, cudaStreamCaptureModeRelaxed) == cudaSuccess) {
+        const int st = stack_decode_layers(c, io, c->s_cap, false);
+        const cudaError_t ce = cudaStreamEndCapture(c->s_cap, &graph);
+        if (st == RL_OK && ce == cudaSuccess && graph &&
+            cudaGraphInstantiate(&c->gexec, graph, 0) == cudaSuccess) {
+            cudaGraphDestroy(graph);
+            c->gkey_seen = 2;
+            RL_CUDA(cudaGraphLaunch(c->gexec, as_stream(stream)));
+            return RL_OK;
+        }
+        if (graph) cudaGraphDestroy(graph);
+    }
+    cudaGetLastError();
+    c->gexec = nullptr;
+    c->graph_enabled = false;       // capture is not possible here: stay on plain launches
     return stack_decode_layers(c, io, as_stream(stream), false);
+}
+
+int rl_stack_set_graph(rl_cache* c, int enable) {
+    if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
+    c->graph_enabled = enable != 0;
+    if (!enable && c->gexec) {
+        cudaGraphExecDestroy(c->gexec);
+        c->gexec = nullptr;
+    }
+    if (!enable) c->gkey_seen = 0;
+    return RL_OK;
 }
 
 static int ensure_staging(rl_cache* c) {

@@ -13,14 +13,15 @@
 // with linear TMA bulk copies and is consumed in place: K as the K-major B operand of
 // S = Q K^T (M 128, N 64, 16 MMAs of K 16), V as the MN-major B operand of O += P V (M 128,
 // N 256, 4 MMAs).  S (two buffers of 64 columns) and O (256 columns) live in tensor memory;
-// S of the next tile is issued before P.V of the current one, so the softmax of a tile
+// S of the next tile is issued as soon as its buffer is free, so the softmax of a tile
 // overlaps tensor-core work.  Q and P are A operands read from tensor memory.  Eight softmax
 // warps: TMEM lane = query row, and the two warps that share a lane quadrant split a row's
 // 64 scores (and the columns of O) between them, exchanging the row maximum through shared
 // memory.  Scores are read with tcgen05.ld, the running maximum is only raised when it grows
 // by more than 2^8 (then O is rescaled in TMEM), and P overwrites the start of its S buffer.
-// Warp 8 streams pages, one thread of warp 9 issues all MMAs and signals completion through
-// tcgen05.commit on mbarriers.  All waits are bounded.
+// Warp 8 streams pages; one thread of warp 9 issues the S MMAs and one thread of warp 10 the
+// P.V MMAs (two issuers keep the in-order tensor pipe fed while either waits), signalling
+// completion through tcgen05.commit on mbarriers.  All waits are bounded.
 #include "kernels.h"
 #include "tcgen05.cuh"
 
@@ -30,10 +31,10 @@ namespace {
 
 constexpr int kQRows = 128;
 constexpr int kKvTile = kPageTokens;              // 64
-constexpr int kStages = 3;                        // per ring: K tiles and V tiles are staged separately
+constexpr int kKStages = 2, kVStages = 3;         // K tiles and V tiles are staged in separate rings
 constexpr int kSliceBytes = kPageTokens * kHeadDim * 2;   // 32 KiB
 constexpr int kSoftmaxThreads = 256;              // 8 softmax warps
-constexpr int kThreads = 320;                     // + loader warp + MMA warp
+constexpr int kThreads = 352;                     // + loader warp + two MMA-issuing warps
 constexpr uint32_t kTmemCols = 512;
 // Tensor memory map (512 columns x 128 lanes, lane = query row): S double-buffered in columns
 // [0,64) and [64,128) -- P (fp16 pairs, 32 columns) overwrites the start of its S buffer --,
@@ -41,11 +42,14 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 128, kColQ = 384;
 constexpr float kRescaleThreshold = 8.f;          // log2 units
 
+constexpr int kPBytes = kQRows * kKvTile * 2;     // one P tile, fp16: 16 KiB
+
 struct Smem {
-    alignas(1024) unsigned char k[kStages][kSliceBytes];      // K page slices
-    alignas(1024) unsigned char v[kStages][kSliceBytes];      // V page slices
-    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-    uint64_t bar_s[2], bar_p, bar_pv[2], bar_done;
+    alignas(1024) unsigned char k[kKStages][kSliceBytes];     // K page slices
+    alignas(1024) unsigned char v[kVStages][kSliceBytes];     // V page slices
+    alignas(1024) unsigned char p[2][kPBytes];                // P tiles, K-major 128-byte-swizzled A operands
+    uint64_t k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
+    uint64_t bar_s[2], bar_sfree[2], bar_p[2], bar_pv[2], bar_done;
     float xch[2][kQRows][2];                          // row maxima of the two column halves
     float lsum[kQRows][2];
     uint32_t tmem_base;
@@ -69,17 +73,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     const int n_tiles = last_pos / kKvTile + 1;               // KV tiles [0, n_tiles)
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < kKStages; ++i) {
             mbar_init(&s.k_full[i], 1);
             mbar_init(&s.k_empty[i], 1);
+        }
+        for (int i = 0; i < kVStages; ++i) {
             mbar_init(&s.v_full[i], 1);
             mbar_init(&s.v_empty[i], 1);
         }
-        mbar_init(&s.bar_s[0], 1);
-        mbar_init(&s.bar_s[1], 1);
-        mbar_init(&s.bar_p, kSoftmaxThreads);
-        mbar_init(&s.bar_pv[0], 1);
-        mbar_init(&s.bar_pv[1], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s.bar_s[i], 1);
+            mbar_init(&s.bar_sfree[i], kSoftmaxThreads);
+            mbar_init(&s.bar_p[i], kSoftmaxThreads);
+            mbar_init(&s.bar_pv[i], 1);
+        }
         mbar_init(&s.bar_done, 1);
         s.failed = 0;
         mbar_fence_init();
@@ -90,6 +97,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
     const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0;
+    // per-CTA record after the 64 x 8 tile timestamps: start, main loop start, end, SM id
+    unsigned long long* cta_rec = a.trace ? a.trace + 512 + (size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 4 : nullptr;
+    if (cta_rec && tid == 0) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        cta_rec[0] = global_ns();
+        cta_rec[3] = smid;
+    }
 #define RL_TRACE(J, SLOT) if (tr && (J) < 64) a.trace[(J) * 8 + (SLOT)] = global_ns();
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
     // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the two threads
@@ -119,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
+    if (cta_rec && tid == 0) cta_rec[1] = global_ns();
 
     if (warp == 8) {
         // ------------------------------ page loader ------------------------------
@@ -126,68 +142,86 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         // two rings, each freed by the MMA that last read it.
         if (lane == 0) {
             for (int j = 0; j < n_tiles; ++j) {
-                const int st = j % kStages;
-                const uint32_t ph = ((j / kStages) & 1) ^ 1;
+                const int ks = j % kKStages, vs = j % kVStages;
                 int page = a.page_table[j];
                 if (page < 0 || page >= a.n_pages) {
                     set_err(a.err, DEV_ERR_BAD_PAGE);
                     page = 0;
                 }
                 const size_t slice = (size_t(page) * a.n_kv + hkv) * kv_slice_elems();
-                if (!mbar_wait(&s.k_empty[st], ph)) { s.failed = 1; break; }
-                mbar_arrive_expect_tx(&s.k_full[st], kSliceBytes);
-                bulk_g2s(s.k[st], a.k_pool + slice, kSliceBytes, &s.k_full[st]);
-                if (!mbar_wait(&s.v_empty[st], ph)) { s.failed = 1; break; }
-                mbar_arrive_expect_tx(&s.v_full[st], kSliceBytes);
-                bulk_g2s(s.v[st], a.v_pool + slice, kSliceBytes, &s.v_full[st]);
+                if (!mbar_wait(&s.k_empty[ks], ((j / kKStages) & 1) ^ 1)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.k_full[ks], kSliceBytes);
+                bulk_g2s(s.k[ks], a.k_pool + slice, kSliceBytes, &s.k_full[ks]);
+                if (!mbar_wait(&s.v_empty[vs], ((j / kVStages) & 1) ^ 1)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.v_full[vs], kSliceBytes);
+                bulk_g2s(s.v[vs], a.v_pool + slice, kSliceBytes, &s.v_full[vs]);
             }
             if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
     } else if (warp == 9) {
-        // ------------------------------ MMA issuer ------------------------------
-        // Order on the tensor pipe: S_0, S_1, PV_0, S_2, PV_1, ... so that the softmax of tile j
-        // overlaps S_{j+1} and PV_{j-1}.
+        // ------------------------------ S = Q K^T issuer ------------------------------
+        // Two issuing threads (this one and warp 10) feed the one in-order tensor pipe: while one
+        // is waiting on a barrier the other keeps the pipe busy.  S_j goes into buffer j & 1.
+        // The issuing thread must spend only a few instructions per tcgen05.mma (a 128x64x16 MMA
+        // retires in about 45 clocks): descriptors are built once per ring stage and advanced by
+        // constants (their address field counts 16-byte units).
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::idesc_f16(kQRows, kKvTile, false, false);
-            constexpr uint32_t idesc_pv = tc::idesc_f16(kQRows, kHeadDim, false, true);
+            uint64_t k_desc[kKStages];
+#pragma unroll
+            for (int i = 0; i < kKStages; ++i) k_desc[i] = tc::smem_desc(smem_u32(s.k[i]), 16, 1024);
+            const uint32_t q_tmem = tmem + kColQ;
             bool ok = true;
-            auto issue_qk = [&](int j) {
-                const int st = j % kStages;
-                if (!mbar_wait(&s.k_full[st], (j / kStages) & 1)) { ok = false; return; }
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kKStages;
+                if (tr) { RL_TRACE(j, 0) }
+                if (!mbar_wait(&s.k_full[st], (j / kKStages) & 1)) { ok = false; break; }
+                // buffer j & 1 is free once every softmax thread has read S_{j-2} out of it
+                if (j >= 2 && !mbar_wait(&s.bar_sfree[j & 1], ((j - 2) >> 1) & 1)) { ok = false; break; }
                 tc::fence_after_sync();
-                const uint32_t k_addr = smem_u32(s.k[st]);
+                const uint64_t kd = st == 0 ? k_desc[0] : k_desc[1];
+                const uint32_t s_tmem = tmem + kColS + (j & 1) * 64;
                 // 16 K-steps of 16 dims: A = 8 columns of Q in tensor memory, B = 32 bytes further
                 // into the 64-dim sub-tile of the K slice
 #pragma unroll
-                for (int kk = 0; kk < 16; ++kk) {
-                    const uint64_t db = tc::smem_desc(k_addr + (kk >> 2) * (kKvTile * 128) + (kk & 3) * 32, 16, 1024);
-                    tc::mma_ts(tmem + kColS + (j & 1) * 64, tmem + kColQ + kk * 8, db, idesc_qk, kk > 0);
-                }
+                for (int kk = 0; kk < 16; ++kk)
+                    tc::mma_ts(s_tmem, q_tmem + kk * 8, kd + uint64_t(((kk >> 2) * (kKvTile * 128) + (kk & 3) * 32) >> 4),
+                               idesc_qk, kk > 0);
                 tc::commit(&s.k_empty[st]);           // K stage free once S_j is done
                 tc::commit(&s.bar_s[j & 1]);
-            };
-            issue_qk(0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                // S buffer (j+1)&1 was last read by the softmax of tile j-1, which finished before
-                // it signalled P_{j-1} (awaited in the previous iteration)
-                RL_TRACE(j, 0)
-                if (j + 1 < n_tiles) issue_qk(j + 1);
-                if (!ok) break;
-                RL_TRACE(j, 1)
-                const int st = j % kStages;
-                if (!mbar_wait(&s.v_full[st], (j / kStages) & 1)) { ok = false; break; }
-                if (!mbar_wait(&s.bar_p, j & 1)) { ok = false; break; }
-                RL_TRACE(j, 2)
-                tc::fence_after_sync();
-                const uint32_t v_addr = smem_u32(s.v[st]);
+                if (tr) { RL_TRACE(j, 1) }
+            }
+            if (!ok) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                s.failed = 1;
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------------------ O += P V issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = tc::idesc_f16(kQRows, kHeadDim, false, true);
+            uint64_t v_desc[kVStages], p_desc[2];
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t db = tc::smem_desc(v_addr + kk * (16 * 128), kKvTile * 128, 1024);
-                    tc::mma_ts(tmem + kColO, tmem + kColS + (j & 1) * 64 + kk * 8, db, idesc_pv, (j > 0) || (kk > 0));
-                }
+            for (int i = 0; i < kVStages; ++i) v_desc[i] = tc::smem_desc(smem_u32(s.v[i]), kKvTile * 128, 1024);
+            p_desc[0] = tc::smem_desc(smem_u32(s.p[0]), 16, 1024);
+            p_desc[1] = tc::smem_desc(smem_u32(s.p[1]), 16, 1024);
+            bool ok = true;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kVStages;
+                if (!mbar_wait(&s.v_full[st], (j / kVStages) & 1)) { ok = false; break; }
+                if (!mbar_wait(&s.bar_p[j & 1], (j >> 1) & 1)) { ok = false; break; }
+                if (tr) { RL_TRACE(j, 2) }
+                tc::fence_after_sync();
+                const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[2]);
+                const uint64_t pd = (j & 1) ? p_desc[1] : p_desc[0];
+                // 4 K-steps of 16 tokens: A = 32 bytes further into P's 128-byte rows, B = 16 rows of V
+                tc::mma_ss(tmem + kColO, pd, vd, idesc_pv, j > 0);
+#pragma unroll
+                for (int kk = 1; kk < 4; ++kk)
+                    tc::mma_ss(tmem + kColO, pd + uint64_t((kk * 32) >> 4), vd + uint64_t((kk * 16 * 128) >> 4), idesc_pv, 1);
                 tc::commit(&s.v_empty[st]);           // V stage free
                 tc::commit(&s.bar_pv[j & 1]);         // this P buffer free, O consistent
-                RL_TRACE(j, 3)
+                if (tr) { RL_TRACE(j, 3) }
             }
             if (!ok) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -217,15 +251,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 tc::tmem_ld32(s_addr + half * 32, raw);
                 tc::tmem_wait_ld();
             }
+            tc::fence_before_sync();
+            mbar_arrive(&s.bar_sfree[j & 1]);                 // the scores are in registers: S buffer free
             const int tok0 = j * kKvTile;
             if (j == n_tiles - 1 && last_pos + 1 - tok0 < kKvTile) {
                 // V rows past the last position may hold anything (0 * NaN would poison O): clear them
-                if (ok && !mbar_wait(&s.v_full[j % kStages], (j / kStages) & 1)) {
+                if (ok && !mbar_wait(&s.v_full[j % kVStages], (j / kVStages) & 1)) {
                     set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                     ok = false;
                 }
                 const int first = last_pos + 1 - tok0;
-                unsigned char* vt = s.v[j % kStages];
+                unsigned char* vt = s.v[j % kVStages];
                 for (int idx = tid; idx < (kKvTile - first) * 32; idx += kSoftmaxThreads) {
                     const int row = first + (idx >> 5), c16 = idx & 31;
                     *reinterpret_cast<uint4*>(vt + (c16 >> 3) * (kKvTile * 128) + row * 128 + (c16 & 7) * 16) =
@@ -293,15 +329,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 ph[i] = pack_h2(p0, p1);
             }
             l_run += lsum0 + lsum1;
-            // P row -> tensor memory over the start of this tile's S buffer (both warps of the
-            // quadrant are past their tcgen05.ld: the exchange barrier above): the A operand of
-            // O += P V; this thread's 32 tokens are fp16 columns [16 half, 16 half + 16)
-            if (ok) {
-                tc::tmem_st16(s_addr + half * 16, ph);
-                tc::tmem_wait_st();
+            // P row -> shared memory as the K-major 128-byte-swizzled A operand of O += P V (row =
+            // 128 bytes = 64 tokens, 16-byte chunk c of row r stored at chunk c ^ (r & 7)); the buffer
+            // was last read by P.V of tile j-2
+            if (ok && j >= 2 && !mbar_wait(&s.bar_pv[j & 1], ((j - 2) >> 1) & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
             }
-            tc::fence_before_sync();
-            mbar_arrive(&s.bar_p);
+            if (ok) {
+                unsigned char* prow = s.p[j & 1] + r * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) =
+                        make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+            }
+            tc::fence_async_smem();
+            mbar_arrive(&s.bar_p[j & 1]);
             if (tid == 0) { RL_TRACE(j, 7) }
         }
         // ------------------------------ epilogue ------------------------------
@@ -342,6 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         tc::fence_before_sync();
     }
     __syncthreads();
+    if (cta_rec && tid == 0) cta_rec[2] = global_ns();
     if (warp == 9) tc::tmem_dealloc(tmem, kTmemCols);
 }
 

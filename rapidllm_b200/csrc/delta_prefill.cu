@@ -320,41 +320,53 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             constexpr uint32_t id_vt = tc::idesc_f16(128, kC, true, false);            // A = V^T MN-major (smem)
             constexpr uint32_t id_n128 = tc::idesc_f16(128, kD, false, true);          // B = Kt MN-major
             bool ok = true;
+            // Descriptors are built once per ring stage and advanced by constants (their address
+            // field counts 16-byte units): the issuing thread must spend only a few instructions
+            // per tcgen05.mma or it, not the tensor pipe, sets the pace.
+            uint64_t mn_desc[kScanStages], k_desc[kScanStages];
+#pragma unroll
+            for (int i = 0; i < kScanStages; ++i) {
+                mn_desc[i] = tc::smem_desc(smem_u32(s.rec[i]), kC * 128, 1024);   // V^T, Kt: 64 contiguous along M/N
+                k_desc[i] = tc::smem_desc(smem_u32(s.rec[i]), 16, 1024);          // T, W, Qg, P: K-major
+            }
+            const uint32_t t_d = tmem + kColD, t_o = tmem + kColO, t_st = tmem + kColSt;
+            const uint32_t t_shi = tmem + kColShi, t_slo = tmem + kColSlo, t_dhi = tmem + kColDhi, t_dlo = tmem + kColDlo;
             for (int c = 0; c < n_chunks && ok; ++c) {
                 const int st = c % kScanStages;
                 if (!mbar_wait(&s.full[st], (c / kScanStages) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_s, c & 1)) { ok = false; break; }                 // S hi/lo ready
                 tc::fence_after_sync();
-                const uint32_t base = smem_u32(s.rec[st]);
+                const uint64_t mn = st == 0 ? mn_desc[0] : mn_desc[1];
+                const uint64_t km = st == 0 ? k_desc[0] : k_desc[1];
                 // D^T = V^T T^T - S^T W^T
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)                                         // K = 64 tokens i
-                    tc::mma_ss(tmem + kColD, tc::smem_desc(base + kOffV + kk * 2048, kC * 128, 1024),
-                               tc::smem_desc(base + kOffT + kk * 32, 16, 1024), id_vt, kk > 0);
+                    tc::mma_ss(t_d, mn + uint64_t((kOffV + kk * 2048) >> 4), km + uint64_t((kOffT + kk * 32) >> 4), id_vt,
+                               kk > 0);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {                                       // K = 128 key dims
-                    const uint64_t bw = tc::smem_desc(base + kOffW + (kk >> 2) * (kC * 128) + (kk & 3) * 32, 16, 1024);
-                    tc::mma_ts(tmem + kColD, tmem + kColShi + kk * 8, bw, id_n64_neg, 1);
-                    tc::mma_ts(tmem + kColD, tmem + kColSlo + kk * 8, bw, id_n64_neg, 1);
+                    const uint64_t bw = km + uint64_t((kOffW + (kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
+                    tc::mma_ts(t_d, t_shi + kk * 8, bw, id_n64_neg, 1);
+                    tc::mma_ts(t_d, t_slo + kk * 8, bw, id_n64_neg, 1);
                 }
                 // O^T = S^T Qg^T (+ D^T P^T below)
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t bq = tc::smem_desc(base + kOffQg + (kk >> 2) * (kC * 128) + (kk & 3) * 32, 16, 1024);
-                    tc::mma_ts(tmem + kColO, tmem + kColShi + kk * 8, bq, id_n64, kk > 0);
-                    tc::mma_ts(tmem + kColO, tmem + kColSlo + kk * 8, bq, id_n64, 1);
+                    const uint64_t bq = km + uint64_t((kOffQg + (kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
+                    tc::mma_ts(t_o, t_shi + kk * 8, bq, id_n64, kk > 0);
+                    tc::mma_ts(t_o, t_slo + kk * 8, bq, id_n64, 1);
                 }
                 tc::commit(&s.bar_g1);
                 if (!mbar_wait(&s.bar_d, c & 1)) { ok = false; break; }                 // D hi/lo ready, S^T decayed
                 tc::fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {                                       // K = 64 tokens
-                    const uint64_t bp = tc::smem_desc(base + kOffP + kk * 32, 16, 1024);
-                    tc::mma_ts(tmem + kColO, tmem + kColDhi + kk * 8, bp, id_n64, 1);
-                    tc::mma_ts(tmem + kColO, tmem + kColDlo + kk * 8, bp, id_n64, 1);
-                    const uint64_t bk = tc::smem_desc(base + kOffKt + kk * 2048, kC * 128, 1024);
-                    tc::mma_ts(tmem + kColSt, tmem + kColDhi + kk * 8, bk, id_n128, 1);
-                    tc::mma_ts(tmem + kColSt, tmem + kColDlo + kk * 8, bk, id_n128, 1);
+                    const uint64_t bp = km + uint64_t((kOffP + kk * 32) >> 4);
+                    tc::mma_ts(t_o, t_dhi + kk * 8, bp, id_n64, 1);
+                    tc::mma_ts(t_o, t_dlo + kk * 8, bp, id_n64, 1);
+                    const uint64_t bk = mn + uint64_t((kOffKt + kk * 2048) >> 4);
+                    tc::mma_ts(t_st, t_dhi + kk * 8, bk, id_n128, 1);
+                    tc::mma_ts(t_st, t_dlo + kk * 8, bk, id_n128, 1);
                 }
                 tc::commit(&s.empty[st]);
                 tc::commit(&s.bar_g3);

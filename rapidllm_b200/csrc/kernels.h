@@ -42,7 +42,7 @@ struct AttnPrefillArgs {
     int* err;
     int T, pos0, n_q, n_kv, n_pages;
     float scale;
-    unsigned long long* trace;   // development aid: null, or room for 8 timestamps x 64 tiles of CTA (0,0)
+    unsigned long long* trace;   // development aid: null, or room for 8 timestamps x 64 tiles of CTA (0,0) + 4 words per CTA
 };
 __global__ void attn_prefill_kernel(AttnPrefillArgs a);
 size_t attn_prefill_smem_bytes();

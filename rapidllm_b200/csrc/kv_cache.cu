@@ -10,10 +10,12 @@
 
 namespace rl {
 
-// grid (n_tok, n_kv, batch), 32 threads: one 16-byte chunk (8 dims) per thread.
-__global__ void __launch_bounds__(32) kv_write_kernel(KvWriteArgs a) {
-    const int t = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+// grid (ceil(n_tok / blockDim.y), n_kv, batch), block (32, 1 or 8): one token row per warp, one
+// 16-byte chunk (8 dims) per thread.
+__global__ void __launch_bounds__(256) kv_write_kernel(KvWriteArgs a) {
+    const int t = blockIdx.x * blockDim.y + threadIdx.y, h = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x;
+    if (t >= a.n_tok) return;
     const int pos = (a.pos ? a.pos[b] : a.pos0) + t;
     const int pi = pos / kPageTokens;
     if (pos < 0 || pi >= a.max_pages_per_seq) {
