@@ -548,7 +548,7 @@ int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, c
     a.scale = 1.f / sqrtf(float(p->head_dim));
     a.trace = reinterpret_cast<unsigned long long*>(getenv("RL_B200_PREFILL_TRACE") ? strtoull(getenv("RL_B200_PREFILL_TRACE"), nullptr, 0) : 0ull);
     const int n_qtiles = (p->seq + rl::attn_prefill_q_rows() - 1) / rl::attn_prefill_q_rows();
-    rl::attn_prefill_kernel<<<dim3(n_qtiles, p->n_q), rl::attn_prefill_threads(), rl::attn_prefill_smem_bytes(),
+    rl::attn_prefill_kernel<<<dim3(unsigned(n_qtiles) * unsigned(p->n_q)), rl::attn_prefill_threads(), rl::attn_prefill_smem_bytes(),
                               as_stream(stream)>>>(a);
     RL_CUDA(cudaGetLastError());
     return RL_OK;

@@ -8,20 +8,25 @@
 // (launch_attn_gqa_gemm, 9038-9125).
 //
 // One CTA = 128 query rows of one query head.  Q (bf16 -> fp16) is written once into tensor
-// memory.  KV tiles are whole pages: a (page, head) slice is
-// stored in HBM in exactly the tensor-core tile format (kv_slice_offset), so a tile moves
-// with linear TMA bulk copies and is consumed in place: K as the K-major B operand of
-// S = Q K^T (M 128, N 64, 16 MMAs of K 16), V as the MN-major B operand of O += P V (M 128,
-// N 256, 4 MMAs).  S (two buffers of 64 columns) and O (256 columns) live in tensor memory;
-// S of the next tile is issued as soon as its buffer is free, so the softmax of a tile
-// overlaps tensor-core work.  Q and P are A operands read from tensor memory.  Eight softmax
-// warps: TMEM lane = query row, and the two warps that share a lane quadrant split a row's
-// 64 scores (and the columns of O) between them, exchanging the row maximum through shared
-// memory.  Scores are read with tcgen05.ld, the running maximum is only raised when it grows
-// by more than 2^8 (then O is rescaled in TMEM), and P overwrites the start of its S buffer.
-// Warp 8 streams pages; one thread of warp 9 issues the S MMAs and one thread of warp 10 the
-// P.V MMAs (two issuers keep the in-order tensor pipe fed while either waits), signalling
-// completion through tcgen05.commit on mbarriers.  All waits are bounded.
+// memory.  KV tiles are whole pages: a (page, head) slice is stored in HBM in exactly the
+// tensor-core tile format (kv_slice_offset), so a tile moves with linear TMA bulk copies and is
+// consumed in place: K as the K-major B operand of S = Q K^T (M 128, N 64, 16 MMAs of K 16), V
+// as the MN-major B operand of O += P V (M 128, N 256, 4 MMAs).  Q and P are A operands read
+// from tensor memory, so shared memory carries only the K/V tiles (fills + one read each).
+// Tensor memory: S (64 columns), two P buffers (fp16 pairs, 32 columns each), O (256), Q (128).
+//
+// Warps: 16 softmax warps in two groups that take alternate KV tiles (TMEM lane = query row; the
+// two warps of a group that share a lane quadrant split a row's 64 scores and exchange the row
+// maximum through shared memory); a loader warp streaming pages; one thread issuing the S MMAs
+// and one thread of another warp issuing the P.V MMAs -- two issuers keep the in-order tensor
+// pipe fed while either waits, and each spends only a few instructions per tcgen05.mma
+// (descriptors are prebuilt per ring stage).  S is released as soon as a group has it in
+// registers, so the next S = Q K^T runs under the current tile's exponentials.  The running
+// row maximum is handed from tile to tile through shared memory (mrow/bar_m) and is only
+// raised when it grows by more than 2^8; then the deciding group rescales O in tensor memory.
+// Each thread keeps its partial row sum relative to the maximum it last saw.  Epilogue: O / l
+// goes through shared memory so that the gate is read and the output written by whole rows.
+// Completion is signalled through tcgen05.commit on mbarriers; all waits are bounded.
 #include "kernels.h"
 #include "tcgen05.cuh"
 
@@ -31,27 +36,26 @@ namespace {
 
 constexpr int kQRows = 128;
 constexpr int kKvTile = kPageTokens;              // 64
-constexpr int kKStages = 2, kVStages = 3;         // K tiles and V tiles are staged in separate rings
+constexpr int kKStages = 3, kVStages = 3;         // K tiles and V tiles are staged in separate rings
 constexpr int kSliceBytes = kPageTokens * kHeadDim * 2;   // 32 KiB
-constexpr int kSoftmaxThreads = 256;              // 8 softmax warps
-constexpr int kThreads = 352;                     // + loader warp + two MMA-issuing warps
+constexpr int kGroupThreads = 256;                // one softmax group: 8 warps
+constexpr int kSoftmaxThreads = 512;              // two groups, alternating KV tiles
+constexpr int kThreads = 608;                     // + loader warp + two MMA-issuing warps
+constexpr int kWarpLoader = 16, kWarpQK = 17, kWarpPV = 18;
 constexpr uint32_t kTmemCols = 512;
-// Tensor memory map (512 columns x 128 lanes, lane = query row): S double-buffered in columns
-// [0,64) and [64,128) -- P (fp16 pairs, 32 columns) overwrites the start of its S buffer --,
-// O in [128,384), Q (fp16 pairs) in [384,512).
-constexpr uint32_t kColS = 0, kColO = 128, kColQ = 384;
+// Tensor memory map (512 columns x 128 lanes, lane = query row): S in columns [0,64), two P
+// buffers (fp16 pairs, 32 columns each) in [64,128), O in [128,384), Q (fp16 pairs) in [384,512).
+constexpr uint32_t kColS = 0, kColP = 64, kColO = 128, kColQ = 384;
 constexpr float kRescaleThreshold = 8.f;          // log2 units
-
-constexpr int kPBytes = kQRows * kKvTile * 2;     // one P tile, fp16: 16 KiB
 
 struct Smem {
     alignas(1024) unsigned char k[kKStages][kSliceBytes];     // K page slices
     alignas(1024) unsigned char v[kVStages][kSliceBytes];     // V page slices
-    alignas(1024) unsigned char p[2][kPBytes];                // P tiles, K-major 128-byte-swizzled A operands
     uint64_t k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
-    uint64_t bar_s[2], bar_sfree[2], bar_p[2], bar_pv[2], bar_done;
-    float xch[2][kQRows][2];                          // row maxima of the two column halves
-    float lsum[kQRows][2];
+    uint64_t bar_s[2], bar_sfree[2], bar_p[2], bar_pv[2], bar_m[2], bar_q, bar_done;
+    float xch[2][2][kQRows][2];                       // [group][use parity] row maxima of the two column halves
+    float mrow[2][kQRows];                            // [tile parity] running maximum after that tile
+    alignas(16) float lsum[kQRows][4];                 // read back as one float4 per row
     uint32_t tmem_base;
     int failed;
 };
@@ -63,10 +67,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_qtiles = (a.T + kQRows - 1) / kQRows;
-    const int qt = n_qtiles - 1 - int(blockIdx.x);            // heaviest tiles first
-    const int hq = blockIdx.y;
+    // 1-D grid; launch order = one KV head after the other (its K/V stay hot in L2 and the CTAs
+    // running side by side read the same tiles), inside a KV head the longest jobs first: the
+    // group's query heads of the last (heaviest) query tile, then of the one before, ...
     const int G = a.n_q / a.n_kv;
-    const int hkv = hq / G;
+    const int per_kv = n_qtiles * G;
+    const int hkv = int(blockIdx.x) / per_kv;
+    const int rem = int(blockIdx.x) - hkv * per_kv;
+    const int qt = n_qtiles - 1 - rem / G;
+    const int hq = hkv * G + rem % G;
     const int q0 = qt * kQRows;                               // first query row of this CTA
     const int rows = min(kQRows, a.T - q0);
     const int last_pos = a.pos0 + q0 + rows - 1;              // position of the last query row
@@ -83,60 +92,64 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s.bar_s[i], 1);
-            mbar_init(&s.bar_sfree[i], kSoftmaxThreads);
-            mbar_init(&s.bar_p[i], kSoftmaxThreads);
+            mbar_init(&s.bar_sfree[i], kGroupThreads);
+            mbar_init(&s.bar_p[i], kGroupThreads);
             mbar_init(&s.bar_pv[i], 1);
+            mbar_init(&s.bar_m[i], kGroupThreads);
         }
+        mbar_init(&s.bar_q, kSoftmaxThreads);
         mbar_init(&s.bar_done, 1);
         s.failed = 0;
         mbar_fence_init();
     }
-    if (warp == 9) tc::tmem_alloc(&s.tmem_base, kTmemCols);
+    if (warp == kWarpQK) tc::tmem_alloc(&s.tmem_base, kTmemCols);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
-    const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0;
+    const bool tr = a.trace && blockIdx.x == 0;
     // per-CTA record after the 64 x 8 tile timestamps: start, main loop start, end, SM id
-    unsigned long long* cta_rec = a.trace ? a.trace + 512 + (size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 4 : nullptr;
+    unsigned long long* cta_rec = a.trace ? a.trace + 512 + (size_t(hq) * n_qtiles + (n_qtiles - 1 - qt)) * 4 : nullptr;
     if (cta_rec && tid == 0) {
         uint32_t smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
         cta_rec[0] = global_ns();
-        cta_rec[3] = smid;
+        cta_rec[3] = smid | (static_cast<unsigned long long>(clock64()) << 16);
     }
 #define RL_TRACE(J, SLOT) if (tr && (J) < 64) a.trace[(J) * 8 + (SLOT)] = global_ns();
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
-    // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the two threads
-    // of a row stores 128 dims
+    // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the four threads
+    // of a row stores 64 dims
     if (tid < kSoftmaxThreads) {
-        const int half = warp >> 2, r = (warp & 3) * 32 + lane;
-        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + half * 128;
+        const int part = warp >> 2, r = (warp & 3) * 32 + lane;
+        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + part * 64;
         const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
-#pragma unroll 1
-        for (int part = 0; part < 2; ++part) {
-            uint32_t regs[32];
+        uint32_t regs[32];
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint4 in = make_uint4(0, 0, 0, 0);
-                if (r < rows) in = *reinterpret_cast<const uint4*>(src + part * 64 + ch * 8);
-                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in);
+        for (int ch = 0; ch < 8; ++ch) {
+            uint4 in = make_uint4(0, 0, 0, 0);
+            if (r < rows) in = *reinterpret_cast<const uint4*>(src + ch * 8);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = __bfloat1622float2(b2[e]);
-                    regs[ch * 4 + e] = pack_h2(f.x, f.y);
-                }
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(b2[e]);
+                regs[ch * 4 + e] = pack_h2(f.x, f.y);
             }
-            tc::tmem_st32(lane_addr + kColQ + half * 64 + part * 32, regs);
         }
+        tc::tmem_st32(lane_addr + kColQ + part * 32, regs);
         tc::tmem_wait_st();
+        tc::fence_before_sync();
+        mbar_arrive(&s.bar_q);                                // Q is in tensor memory (awaited by the S issuer)
+        if (cta_rec && tid == 0) cta_rec[1] = global_ns();
+        // the epilogue's gate rows: start them on their way into L2 now (2 of the row's 8 lines each)
+        if (a.gate && r < rows) {
+            const float* gp = a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + part * 64;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(gp));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + 32));
+        }
     }
-    tc::fence_before_sync();
-    __syncthreads();
-    tc::fence_after_sync();
-    if (cta_rec && tid == 0) cta_rec[1] = global_ns();
 
-    if (warp == 8) {
+    if (warp == kWarpLoader) {
         // ------------------------------ page loader ------------------------------
         // K_j is needed early (S_j = Q K_j^T is issued one tile ahead), V_j late (O += P_j V_j):
         // two rings, each freed by the MMA that last read it.
@@ -158,10 +171,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             }
             if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
-    } else if (warp == 9) {
+    } else if (warp == kWarpQK) {
         // ------------------------------ S = Q K^T issuer ------------------------------
-        // Two issuing threads (this one and warp 10) feed the one in-order tensor pipe: while one
-        // is waiting on a barrier the other keeps the pipe busy.  S_j goes into buffer j & 1.
+        // Two issuing threads (this one and the next warp) feed the one in-order tensor pipe: while one
+        // is waiting on a barrier the other keeps the pipe busy.
         // The issuing thread must spend only a few instructions per tcgen05.mma (a 128x64x16 MMA
         // retires in about 45 clocks): descriptors are built once per ring stage and advanced by
         // constants (their address field counts 16-byte units).
@@ -171,16 +184,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
 #pragma unroll
             for (int i = 0; i < kKStages; ++i) k_desc[i] = tc::smem_desc(smem_u32(s.k[i]), 16, 1024);
             const uint32_t q_tmem = tmem + kColQ;
-            bool ok = true;
-            for (int j = 0; j < n_tiles; ++j) {
+            bool ok = mbar_wait(&s.bar_q, 0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
                 const int st = j % kKStages;
                 if (tr) { RL_TRACE(j, 0) }
                 if (!mbar_wait(&s.k_full[st], (j / kKStages) & 1)) { ok = false; break; }
-                // buffer j & 1 is free once every softmax thread has read S_{j-2} out of it
-                if (j >= 2 && !mbar_wait(&s.bar_sfree[j & 1], ((j - 2) >> 1) & 1)) { ok = false; break; }
+                // the S buffer is free once every softmax thread of the previous tile has read it out
+                if (tr) { RL_TRACE(j, 5) }
+                if (j >= 1 && !mbar_wait(&s.bar_sfree[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
                 tc::fence_after_sync();
-                const uint64_t kd = st == 0 ? k_desc[0] : k_desc[1];
-                const uint32_t s_tmem = tmem + kColS + (j & 1) * 64;
+                const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[2]);
+                const uint32_t s_tmem = tmem + kColS;
                 // 16 K-steps of 16 dims: A = 8 columns of Q in tensor memory, B = 32 bytes further
                 // into the 64-dim sub-tile of the K slice
 #pragma unroll
@@ -196,15 +210,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 s.failed = 1;
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == kWarpPV) {
         // ------------------------------ O += P V issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_pv = tc::idesc_f16(kQRows, kHeadDim, false, true);
-            uint64_t v_desc[kVStages], p_desc[2];
+            uint64_t v_desc[kVStages];
 #pragma unroll
             for (int i = 0; i < kVStages; ++i) v_desc[i] = tc::smem_desc(smem_u32(s.v[i]), kKvTile * 128, 1024);
-            p_desc[0] = tc::smem_desc(smem_u32(s.p[0]), 16, 1024);
-            p_desc[1] = tc::smem_desc(smem_u32(s.p[1]), 16, 1024);
             bool ok = true;
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j % kVStages;
@@ -213,12 +225,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 if (tr) { RL_TRACE(j, 2) }
                 tc::fence_after_sync();
                 const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[2]);
-                const uint64_t pd = (j & 1) ? p_desc[1] : p_desc[0];
-                // 4 K-steps of 16 tokens: A = 32 bytes further into P's 128-byte rows, B = 16 rows of V
-                tc::mma_ss(tmem + kColO, pd, vd, idesc_pv, j > 0);
+                const uint32_t p_tmem = tmem + kColP + (j & 1) * 32;
+                // 4 K-steps of 16 tokens: A = 8 columns of P in tensor memory, B = 16 rows of V
+                tc::mma_ts(tmem + kColO, p_tmem, vd, idesc_pv, j > 0);
 #pragma unroll
                 for (int kk = 1; kk < 4; ++kk)
-                    tc::mma_ss(tmem + kColO, pd + uint64_t((kk * 32) >> 4), vd + uint64_t((kk * 16 * 128) >> 4), idesc_pv, 1);
+                    tc::mma_ts(tmem + kColO, p_tmem + kk * 8, vd + uint64_t((kk * 16 * 128) >> 4), idesc_pv, 1);
                 tc::commit(&s.v_empty[st]);           // V stage free
                 tc::commit(&s.bar_pv[j & 1]);         // this P buffer free, O consistent
                 if (tr) { RL_TRACE(j, 3) }
@@ -231,28 +243,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         }
     } else {
         // ------------------------------ softmax warps ------------------------------
-        const int half = warp >> 2, quad = warp & 3;          // column half, TMEM lane quadrant
+        // Group g (warps 8g .. 8g+7) owns the tiles j with j & 1 == g, so two tiles are in flight:
+        // the latency of one tile (TMEM load, maxima, exponentials, P store) overlaps the other's.
+        // The only hand-over between consecutive tiles is the running row maximum (mrow + bar_m).
+        const int grp = warp >> 3, half = (warp >> 2) & 1, quad = warp & 3;   // column half, TMEM lane quadrant
         const int r = quad * 32 + lane;                       // query row = TMEM lane
         const int pos = a.pos0 + q0 + r;                      // its position (rows >= `rows` are padding)
         const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
         const float scale_log2 = a.scale * 1.4426950408889634f;
-        float m_run = -1e30f, l_run = 0.f;
+        float m_known = -1e30f, l_part = 0.f;                 // l_part is relative to m_known
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            if (ok && !mbar_wait(&s.bar_s[j & 1], (j >> 1) & 1)) {
+        for (int j = grp; j < n_tiles; j += 2) {
+            const uint32_t par = (j >> 1) & 1;                // phase of this tile on the [j & 1] barriers
+            if (ok && !mbar_wait(&s.bar_s[grp], par)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
             }
             tc::fence_after_sync();
-            if (tid == 0) { RL_TRACE(j, 4) }
-            const uint32_t s_addr = lane_addr + kColS + (j & 1) * 64;
+            if (tid == 0 || tid == kGroupThreads) { RL_TRACE(j, 4) }
             uint32_t raw[32];
             if (ok) {
-                tc::tmem_ld32(s_addr + half * 32, raw);
+                tc::tmem_ld32(lane_addr + kColS + half * 32, raw);
                 tc::tmem_wait_ld();
             }
             tc::fence_before_sync();
-            mbar_arrive(&s.bar_sfree[j & 1]);                 // the scores are in registers: S buffer free
+            mbar_arrive(&s.bar_sfree[grp]);                   // the scores are in registers: S buffer free
             const int tok0 = j * kKvTile;
             if (j == n_tiles - 1 && last_pos + 1 - tok0 < kKvTile) {
                 // V rows past the last position may hold anything (0 * NaN would poison O): clear them
@@ -262,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 }
                 const int first = last_pos + 1 - tok0;
                 unsigned char* vt = s.v[j % kVStages];
-                for (int idx = tid; idx < (kKvTile - first) * 32; idx += kSoftmaxThreads) {
+                for (int idx = tid - grp * kGroupThreads; idx < (kKvTile - first) * 32; idx += kGroupThreads) {
                     const int row = first + (idx >> 5), c16 = idx & 31;
                     *reinterpret_cast<uint4*>(vt + (c16 >> 3) * (kKvTile * 128) + row * 128 + (c16 & 7) * 16) =
                         make_uint4(0, 0, 0, 0);
@@ -283,21 +298,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
             }
-            if (tid == 0) { RL_TRACE(j, 5) }
             // the row maximum over both halves: exchange with the partner warp of this quadrant
-            s.xch[j & 1][r][half] = mx;
-            named_bar_sync(1 + quad, 64);
-            mx = fmaxf(mx, s.xch[j & 1][r][half ^ 1]);
+            s.xch[grp][par][r][half] = mx;
+            named_bar_sync(1 + grp * 4 + quad, 64);
+            mx = fmaxf(mx, s.xch[grp][par][r][half ^ 1]);
             mx = fmaxf(mx * scale_log2, -1e30f);
-            // raise the running maximum only when it grew by more than the threshold
-            float alpha = 1.f;
-            if (mx > m_run + kRescaleThreshold) {
-                alpha = fast_exp2(m_run - mx);                // 0 on the first tile
-                m_run = mx;
+            // running maximum after the previous tile (owned by the other group)
+            float m_prev = -1e30f;
+            if (j > 0) {
+                if (ok && !mbar_wait(&s.bar_m[grp ^ 1], ((j - 1) >> 1) & 1)) {
+                    set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                    ok = false;
+                }
+                m_prev = s.mrow[grp ^ 1][r];
             }
+            // raise it only when it grew by more than the threshold
+            float m_new = m_prev, alpha = 1.f;
+            if (mx > m_prev + kRescaleThreshold) {
+                alpha = fast_exp2(m_prev - mx);                   // 0 on the first tile
+                m_new = mx;
+            }
+            if (half == 0) s.mrow[grp][r] = m_new;
+            mbar_arrive(&s.bar_m[grp]);                       // release: the next tile may read mrow[grp]
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O must not be in use by the tensor core: wait for P.V of tile j-1
-                if (ok && !mbar_wait(&s.bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1)) {
+                // O must not be in use by the tensor core: wait for P.V of tile j-1 (P_j is not
+                // published before this is done, so P.V of tile j and later come after it)
+                if (ok && !mbar_wait(&s.bar_pv[grp ^ 1], ((j - 1) >> 1) & 1)) {
                     set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                     ok = false;
                 }
@@ -315,78 +341,108 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                     tc::tmem_wait_st();
                 }
             }
-            if (tid == 0) { RL_TRACE(j, 6) }
-            l_run *= alpha;
+            if (tid == 0 || tid == kGroupThreads) { RL_TRACE(j, 6) }
+            // this thread's partial row sum follows the maximum (it may have moved twice since
+            // this group's previous tile)
+            if (m_new != m_known) {
+                l_part *= fast_exp2(m_known - m_new);
+                m_known = m_new;
+            }
             // p = 2^(s * scale - m): one FFMA + one EX2 per score (-inf gives exactly 0)
             uint32_t ph[16];
             float lsum0 = 0.f, lsum1 = 0.f;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * i]), scale_log2, -m_run));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), scale_log2, -m_run));
+                const float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * i]), scale_log2, -m_new));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), scale_log2, -m_new));
                 lsum0 += p0;
                 lsum1 += p1;
                 ph[i] = pack_h2(p0, p1);
             }
-            l_run += lsum0 + lsum1;
-            // P row -> shared memory as the K-major 128-byte-swizzled A operand of O += P V (row =
-            // 128 bytes = 64 tokens, 16-byte chunk c of row r stored at chunk c ^ (r & 7)); the buffer
-            // was last read by P.V of tile j-2
-            if (ok && j >= 2 && !mbar_wait(&s.bar_pv[j & 1], ((j - 2) >> 1) & 1)) {
+            l_part += lsum0 + lsum1;
+            // P row -> tensor memory, the A operand of O += P V: this thread's 32 tokens are fp16
+            // columns [16 half, 16 half + 16) of P buffer grp, last read by P.V of tile j-2
+            if (ok && j >= 2 && !mbar_wait(&s.bar_pv[grp], ((j - 2) >> 1) & 1)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
             }
+            tc::fence_after_sync();
             if (ok) {
-                unsigned char* prow = s.p[j & 1] + r * 128;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) =
-                        make_uint4(ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+                tc::tmem_st16(lane_addr + kColP + grp * 32 + half * 16, ph);
+                tc::tmem_wait_st();
             }
-            tc::fence_async_smem();
-            mbar_arrive(&s.bar_p[j & 1]);
-            if (tid == 0) { RL_TRACE(j, 7) }
+            tc::fence_before_sync();
+            mbar_arrive(&s.bar_p[grp]);
+            if (tid == 0 || tid == kGroupThreads) { RL_TRACE(j, 7) }
         }
         // ------------------------------ epilogue ------------------------------
-        s.lsum[r][half] = l_run;
-        named_bar_sync(1 + quad, 64);
-        l_run += s.lsum[r][half ^ 1];
+        // final maximum = after the last tile; the four partial sums of a row are brought to it
+        if (ok && !mbar_wait(&s.bar_m[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) {
+            set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+            ok = false;
+        }
+        const float m_fin = s.mrow[(n_tiles - 1) & 1][r];
+        s.lsum[r][grp * 2 + half] = l_part * fast_exp2(m_known - m_fin);
+        named_bar_sync(9, kSoftmaxThreads);
+        const float4 lp = *reinterpret_cast<const float4*>(s.lsum[r]);
+        const float l_run = (lp.x + lp.y) + (lp.z + lp.w);
         if (ok && !mbar_wait(&s.bar_done, 0)) {
             set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
             ok = false;
         }
         tc::fence_after_sync();
-        if (ok && !s.failed) {
+        // O / l -> shared memory (the K and V rings are free now: every MMA has completed), row
+        // stride 260 floats so that the thread-per-row stores spread over the banks; then each
+        // warp takes whole rows, so the gate is read and the output written in full 512-byte
+        // requests
+        float* stage = reinterpret_cast<float*>(s.k[0]);
+        constexpr int kStageStride = kHeadDim + 4;
+        static_assert(sizeof(float) * kQRows * kStageStride <= sizeof(s.k) + sizeof(s.v), "O staging must fit the rings");
+        const bool good = ok && !s.failed;
+        if (good) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            float* dst = a.o + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + half * 128;
-            const float* gp = a.gate ? a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + half * 128 : nullptr;
+            const int col0 = (half * 2 + grp) * 64;           // this thread's 64 output columns
 #pragma unroll 1
-            for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t o[32];
-                tc::tmem_ld32(lane_addr + kColO + half * 128 + c0, o);
+                tc::tmem_ld32(lane_addr + kColO + col0 + c0, o);
                 tc::tmem_wait_ld();
-                if (r < rows) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        float4 v = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                                               __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                        if (gp) {
-                            const float4 gq = *reinterpret_cast<const float4*>(gp + c0 + i);
-                            v.x *= 1.f / (1.f + expf(-gq.x));
-                            v.y *= 1.f / (1.f + expf(-gq.y));
-                            v.z *= 1.f / (1.f + expf(-gq.z));
-                            v.w *= 1.f / (1.f + expf(-gq.w));
-                        }
-                        *reinterpret_cast<float4*>(dst + c0 + i) = v;
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(stage + r * kStageStride + col0 + c0 + i) =
+                        make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                    __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            }
+        }
+        named_bar_sync(9, kSoftmaxThreads);
+        if (good) {
+            for (int row = warp; row < rows; row += kSoftmaxThreads / 32) {
+                float* dst = a.o + (size_t(q0 + row) * a.n_q + hq) * kHeadDim;
+                const float* gp = a.gate ? a.gate + (size_t(q0 + row) * a.n_q + hq) * kHeadDim : nullptr;
+#pragma unroll
+                for (int hcol = 0; hcol < 2; ++hcol) {
+                    const int c = hcol * 128 + lane * 4;
+                    float4 v = *reinterpret_cast<const float4*>(stage + row * kStageStride + c);
+                    if (gp) {
+                        const float4 gq = __ldcs(reinterpret_cast<const float4*>(gp + c));
+                        v.x *= 1.f / (1.f + expf(-gq.x));
+                        v.y *= 1.f / (1.f + expf(-gq.y));
+                        v.z *= 1.f / (1.f + expf(-gq.z));
+                        v.w *= 1.f / (1.f + expf(-gq.w));
                     }
+                    __stcs(reinterpret_cast<float4*>(dst + c), v);
                 }
             }
         }
         tc::fence_before_sync();
     }
     __syncthreads();
-    if (cta_rec && tid == 0) cta_rec[2] = global_ns();
-    if (warp == 9) tc::tmem_dealloc(tmem, kTmemCols);
+    if (cta_rec && tid == 0) {
+        cta_rec[2] = global_ns();
+        const unsigned long long c0 = cta_rec[3] >> 16;
+        cta_rec[3] = (cta_rec[3] & 0xffff) | (((static_cast<unsigned long long>(clock64()) - c0) & 0xffffffffffffull) << 16);
+    }
+    if (warp == kWarpQK) tc::tmem_dealloc(tmem, kTmemCols);
 }
 
 size_t attn_prefill_smem_bytes() { return sizeof(Smem) + 1024; }
