@@ -77,14 +77,44 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     const int k1 = hpb > 0 ? (u0 + hpb - 1) / q : k0 - 1;
     const size_t unit = size_t(b) * a.n_kv + h;
 
-    float mm = -1e30f;
-    for (int k = k0; k <= k1; ++k) mm = fmaxf(mm, a.part_ml[((k + unit) * G + gi) * 2]);
-    float acc = 0.f, l = 0.f;
-    for (int k = k0; k <= k1; ++k) {
-        const size_t row = (k + unit) * G + gi;
-        const float al = expf(a.part_ml[row * 2] - mm);
-        l += a.part_ml[row * 2 + 1] * al;
-        acc += a.part_o[row * kHeadDim + d] * al;
+    // A long sequence at a small batch is spread over many CTAs: fetch all their (m, l) pairs at
+    // once (one per thread), reduce the maximum across the block, keep the weights in shared
+    // memory and let the accumulation loop run with several independent loads in flight.
+    const int n = k1 - k0 + 1;
+    float mm = -1e30f, acc = 0.f, l = 0.f;
+    if (n <= 256) {
+        __shared__ float s_w[256];
+        __shared__ float s_red[2][8];
+        float my_m = -1e30f, my_l = 0.f;
+        if (d < n) {
+            const size_t row = (k0 + d + unit) * G + gi;
+            my_m = a.part_ml[row * 2];
+            my_l = a.part_ml[row * 2 + 1];
+        }
+        float wm = my_m;
+        for (int off = 16; off > 0; off >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, off));
+        if ((d & 31) == 0) s_red[0][d >> 5] = wm;
+        __syncthreads();
+        for (int w = 0; w < 8; ++w) mm = fmaxf(mm, s_red[0][w]);
+        const float al = d < n ? expf(my_m - mm) : 0.f;
+        s_w[d] = al;
+        float wl = my_l * al;
+        for (int off = 16; off > 0; off >>= 1) wl += __shfl_xor_sync(0xffffffffu, wl, off);
+        if ((d & 31) == 0) s_red[1][d >> 5] = wl;
+        __syncthreads();
+        for (int w = 0; w < 8; ++w) l += s_red[1][w];
+        const float* po = a.part_o + ((k0 + unit) * G + gi) * kHeadDim + d;
+        const size_t stride = size_t(G) * kHeadDim;       // next CTA's slot of this head
+#pragma unroll 8
+        for (int i = 0; i < n; ++i) acc += po[i * stride] * s_w[i];
+    } else {
+        for (int k = k0; k <= k1; ++k) mm = fmaxf(mm, a.part_ml[((k + unit) * G + gi) * 2]);
+        for (int k = k0; k <= k1; ++k) {
+            const size_t row = (k + unit) * G + gi;
+            const float al = expf(a.part_ml[row * 2] - mm);
+            l += a.part_ml[row * 2 + 1] * al;
+            acc += a.part_o[row * kHeadDim + d] * al;
+        }
     }
     const size_t oi = (size_t(b) * a.n_q + hq) * kHeadDim + d;
     if (a.out_ml) {
