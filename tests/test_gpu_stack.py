@@ -97,3 +97,46 @@ def test_stack_decode_matches_oracle_layer_by_layer(oracle):
     assert np.array_equal(host["attn_o"].numpy(), attn_o)
     assert np.array_equal(host["delta_o"].numpy(), delta_o)
     cache.close()
+
+
+def test_graph_replay_matches_plain_launches():
+    """rl_stack_decode replays its step as a CUDA graph from the third call with the same io; the
+    positions live in device memory and advance between replays.  Same bits as plain launches."""
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    types = QWEN35_LAYER_TYPES
+    B, n_slots, max_pages, n_pages = 2, 2, 3, 6
+    lens = [61, 120]
+    outs = []
+    for graph in (True, False):
+        gen = torch.Generator().manual_seed(11)
+        cache = HybridCache(types, n_pages=n_pages, n_slots=n_slots, max_batch=B, max_pages_per_seq=max_pages)
+        cache.set_graph(graph)
+        for a in range(cache.n_attn):
+            cache.k_pool(a).copy_(torch.randn(cache.k_pool(a).shape, generator=gen).half())
+            cache.v_pool(a).copy_(torch.randn(cache.v_pool(a).shape, generator=gen).half())
+        for d in range(cache.n_delta):
+            cache.state(d).copy_(torch.randn(cache.state(d).shape, generator=gen) * 0.02)
+            cache.conv(d).copy_(torch.randn(cache.conv(d).shape, generator=gen))
+        t = _inputs(cache, B, gen, lens)
+        t["page_table"] = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
+        dev = {n: x.cuda() for n, x in t.items()}
+        steps = []
+        for step in range(5):                    # crosses a page boundary for sequence 0 (61 -> 65)
+            if step:
+                fresh = _inputs(cache, B, gen, lens)
+                for n in ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv", "delta_beta", "delta_g"):
+                    dev[n].copy_(fresh[n])       # same device tensors: the io of the captured graph stays valid
+                dev["pos"] += 1
+            cache.decode(dev, B)
+            _lib.check_device()
+            steps.append((dev["attn_o"].cpu().clone(), dev["delta_o"].cpu().clone()))
+        final = [cache.state(d).cpu().clone() for d in range(cache.n_delta)]
+        final += [cache.conv(d).cpu().clone() for d in range(cache.n_delta)]
+        final += [cache.k_pool(a).cpu().clone() for a in range(cache.n_attn)]
+        outs.append((steps, final))
+        cache.close()
+    for (ao, do), (ao2, do2) in zip(outs[0][0], outs[1][0]):
+        assert torch.equal(ao, ao2) and torch.equal(do, do2)
+    for x, y in zip(outs[0][1], outs[1][1]):
+        assert torch.equal(x, y)
