@@ -50,10 +50,13 @@ def parse():
                     choices=["stack", "compact_decode", "f16_decode", "delta_step", "attn_prefill", "delta_prefill"],
                     help="stack = the headline workload; the others time one operator at the shapes of "
                          "BASELINE configs 2, 0 and 1 (secondary lines, N=1 only)")
-    ap.add_argument("--shard", default="seq", choices=["seq", "heads"],
+    ap.add_argument("--shard", default="seq", choices=["seq", "heads", "splitkv"],
                     help="N > 1: seq = every rank owns 32 sequences of its own (weak scaling, no collective); "
                          "heads = ONE batch of 32 divided by KV / value heads (up to 4 ways) and then by sequence, "
-                         "head outputs all-gathered over NCCL every step (strong scaling)")
+                         "head outputs all-gathered over NCCL every step (strong scaling); "
+                         "splitkv = ONE batch of 32, every rank holds 1/N of each sequence's KV pages and 1/N of "
+                         "the DeltaNet heads; attention partials (o, max, sum) are all-gathered over NCCL and "
+                         "merged by rl_lse_combine (strong scaling)")
     ap.add_argument("--wht-len", type=int, default=128)
     ap.add_argument("--op-batch", type=int, default=0, help="operator workloads: override the batch")
     ap.add_argument("--op-ctx", type=int, default=0, help="operator workloads: override the context")
@@ -471,20 +474,40 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist.barrier()
-    from rapidllm_b200 import _lib
+    from rapidllm_b200 import _lib, ops
     from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
     if not _lib.lib().rl_b200_available():
         raise SystemExit("no sm_100 device: the CUDA path is the only path")
 
     heads_mode = args.shard == "heads" and world > 1
+    split_mode = args.shard == "splitkv" and world > 1
     head_ways = 1
+    attn_head_ways = 1
+    pos_local = None
     if heads_mode:
         # head shards first (at most one KV head per rank), then sequence shards
         from rapidllm_b200.shard import plan_heads, plan_sequences
-        head_ways = min(world, N_KV)
+        head_ways = attn_head_ways = min(world, N_KV)
         hshard = plan_heads(rank % head_ways, head_ways)
         seqs = plan_sequences(rank // head_ways, world // head_ways, args.batch)
         ctx = [contexts(args, 0)[b] for b in seqs]
+    elif split_mode:
+        # every rank: a contiguous range of whole pages of each of the 32 sequences (the last rank
+        # holds the tail and appends the new token) and 1/N of the DeltaNet heads
+        if N_K % world:
+            raise SystemExit("splitkv needs a world size that divides the %d DeltaNet key heads" % N_K)
+        head_ways = world
+        full = contexts(args, 0)
+        ctx, pos_local = [], []
+        for c in full:
+            p_tot = (c + PAGE - 1) // PAGE
+            p0, p1 = rank * p_tot // world, (rank + 1) * p_tot // world
+            if rank == world - 1:
+                ctx.append(c - p0 * PAGE)                  # tokens this rank holds after the append
+                pos_local.append(c - 1 - p0 * PAGE)
+            else:
+                ctx.append(max(1, (p1 - p0) * PAGE))
+                pos_local.append((p1 - p0) * PAGE)
     else:
         ctx = contexts(args, rank)
     B = len(ctx)
@@ -493,7 +516,7 @@ def main():
     n_pages = sum(pages)
     types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
     cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages,
-                        max_seq_len=max(ctx), n_q=N_Q // head_ways, n_kv=N_KV // head_ways,
+                        max_seq_len=max(ctx), n_q=N_Q // attn_head_ways, n_kv=N_KV // attn_head_ways,
                         n_v=N_V // head_ways, n_k=N_K // head_ways)
     gen = torch.Generator(device="cuda").manual_seed(args.seed + 1000 * rank)
     for a in range(cache.n_attn):
@@ -518,7 +541,7 @@ def main():
     host["attn_o"] = torch.zeros(sh["attn_o"]).pin_memory()
     host["delta_o"] = torch.zeros(sh["delta_o"]).pin_memory()
     host["page_table"] = table.pin_memory()
-    host["pos"] = torch.tensor([c - 1 for c in ctx], dtype=torch.int32).pin_memory()
+    host["pos"] = torch.tensor(pos_local if split_mode else [c - 1 for c in ctx], dtype=torch.int32).pin_memory()
     conv_w = torch.randn(sh["conv_w"], generator=cg) * 0.5
     cache.set_conv_w(conv_w)
     dev = {n: x.cuda() for n, x in host.items()}
@@ -529,12 +552,25 @@ def main():
     if heads_mode:
         gathered = (torch.empty((world,) + tuple(dev["attn_o"].shape), device="cuda"),
                     torch.empty((world,) + tuple(dev["delta_o"].shape), device="cuda"))
+    if split_mode:
+        dev["attn_ml"] = torch.zeros(sh["attn_ml"], device="cuda")
+        dev["no_append"] = rank != world - 1
+        gathered = (torch.empty((world,) + tuple(dev["attn_o"].shape), device="cuda"),
+                    torch.empty((world,) + tuple(dev["delta_o"].shape), device="cuda"),
+                    torch.empty((world,) + tuple(dev["attn_ml"].shape), device="cuda"))
+        gate_rows = dev["attn_gate"].reshape(-1, HD)
 
     def exchange():
         # what a tensor-parallel model does with the mixer outputs: every rank gets every head slice
         if heads_mode:
             dist.all_gather_into_tensor(gathered[0], dev["attn_o"])
             dist.all_gather_into_tensor(gathered[1], dev["delta_o"])
+        if split_mode:
+            # partial (o, max, sum) of every rank's token range -> log-sum-exp merge + gate on every rank
+            dist.all_gather_into_tensor(gathered[0], dev["attn_o"])
+            dist.all_gather_into_tensor(gathered[2], dev["attn_ml"])
+            dist.all_gather_into_tensor(gathered[1], dev["delta_o"])
+            ops.lse_combine(gathered[0].view(world, -1, HD), gathered[2].view(world, -1, 2), gate_rows)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -587,12 +623,12 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
     ms_per_step = ms_max / args.steps
-    total_seqs = args.batch if heads_mode else B * world
+    total_seqs = args.batch if (heads_mode or split_mode) else B * world
     value = total_seqs / (ms_per_step * 1e-3)
 
     # ---------------- end to end through the host-buffer entry point ----------------
     e2e = None
-    if not args.no_e2e and not heads_mode:
+    if not args.no_e2e and not heads_mode and not split_mode:
         for _ in range(2):
             cache.decode_host(host, B)
         sync_all()
@@ -624,6 +660,10 @@ def main():
         ab = algorithmic_bytes(args, ctx)
         if heads_mode:
             ab = {k: v / head_ways for k, v in ab.items()}
+        if split_mode:
+            ab["delta_rule"] /= world
+            ab["conv1d_update"] /= world
+            ab["step"] = ab["attn_decode"] * cache.n_attn + (ab["delta_rule"] + ab["conv1d_update"]) * cache.n_delta
         n_attn = cache.n_attn
         attn_ms_per_launch = fam["attn_decode"] / args.steps / max(1, n_attn)
         achieved = ab["attn_decode"] / (attn_ms_per_launch * 1e-3) / 1e9
@@ -637,16 +677,18 @@ def main():
         line = {
             "metric": "hybrid-layer decode steps/sec", "value": value, "unit": "seq-steps/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong" if heads_mode else "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if (heads_mode or split_mode) else "weak", "vs_baseline": None,
             "dtype": "f16 KV / f32 state", "data": "synthetic",
             "config": {"workload": workload_name(args), "l2": "inputs larger than L2 (%.1f GB streamed per step)"
                        % (ab["step"] / 1e9),
                        "parallelism": ("heads x%d then sequences x%d, NCCL all_gather of head outputs"
                                        % (head_ways, world // head_ways)) if heads_mode
+                       else ("split-KV x%d (token ranges of every sequence) + DeltaNet heads x%d, NCCL all_gather of "
+                             "attention partials merged by rl_lse_combine" % (world, world)) if split_mode
                        else "sequence-sharded x%d, no collective" % world,
                        "ctx_tokens_rank0": sum(ctx), "cache_bytes_rank0": cache.bytes},
             "clocks": clocks,
-            "gpu_launches": cache.launches_per_step * args.steps,
+            "gpu_launches": (cache.launches_per_step + (1 if split_mode else 0)) * args.steps,
             "step_hbm_gbs": ab["step"] * world / (ms_per_step * 1e-3) / 1e9,   # rank 0's bytes x ranks
             "roofline": {"bound": "hbm", "kernel": "attn_decode_f16_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,

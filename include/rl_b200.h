@@ -335,6 +335,15 @@ typedef struct rl_stack_io {
     const int32_t* pos;          /* [batch] position of the token being decoded */
     const int32_t* slot_ids;     /* [batch] DeltaNet slot per sequence or NULL */
     int batch;
+    /* Split-KV across devices (each device holds a token range of every sequence): with
+     * attn_ml != NULL the attention layers emit one partial per (sequence, query head) instead
+     * of the final output -- attn_o unnormalised and ungated, attn_ml [n_attn][batch][n_q][2]
+     * (max in natural-log units, sum) -- to be gathered over the devices and merged with
+     * rl_lse_combine (which applies the gate).  no_append != 0: this device does not hold the
+     * sequences' tail, so nothing is appended and the layer attends over pos tokens instead
+     * of pos + 1. */
+    float* attn_ml;
+    int no_append;
 } rl_stack_io;
 
 /* One decode step over layer_types[]: the scheduler loop of

@@ -71,7 +71,8 @@ class CacheConfig(C.Structure):
 class StackIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta", "delta_g",
-        "delta_o", "conv_w", "page_table", "pos", "slot_ids")] + [("batch", C.c_int)]
+        "delta_o", "conv_w", "page_table", "pos", "slot_ids")] + [
+        ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int)]
 
 
 # every symbol include/rl_b200.h declares: name -> (restype, argtypes)

@@ -104,12 +104,14 @@ class HybridCache:
                 "attn_o": (A, B, self.n_q, 256), "delta_qkv": (D, B, self.conv_dim),
                 "delta_beta": (D, B, self.n_v), "delta_g": (D, B, self.n_v),
                 "delta_o": (D, B, self.n_v, self.dv), "conv_w": (D, self.conv_dim, self.conv_k),
-                "page_table": (B, self.max_pages_per_seq), "pos": (B,), "slot_ids": (B,)}
+                "page_table": (B, self.max_pages_per_seq), "pos": (B,), "slot_ids": (B,),
+                "attn_ml": (A, B, self.n_q, 2)}
 
     def _io(self, t, batch, cuda):
         io = StackIO(batch=batch)
+        io.no_append = int(bool(t.get("no_append", False)))
         for name in ("attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta",
-                     "delta_g", "delta_o", "conv_w", "page_table", "pos", "slot_ids"):
+                     "delta_g", "delta_o", "conv_w", "page_table", "pos", "slot_ids", "attn_ml"):
             x = t.get(name)
             if x is None:
                 continue

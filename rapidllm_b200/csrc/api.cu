@@ -282,15 +282,19 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             ap.wht_len = 0;
             void* kp = rl_cache_k_pool(c, ai);
             void* vp = rl_cache_v_pool(c, ai);
-            if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
-                                      io->attn_v + ai * kv_sz, &ap, run))
-                return st;
+            if (!io->no_append)
+                if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
+                                          io->attn_v + ai * kv_sz, &ap, run))
+                    return st;
             mark(L, 1);
-            const rl_attn_decode_params dp = c->attn_params(B);
+            rl_attn_decode_params dp = c->attn_params(B);
+            dp.len_add = io->no_append ? 0 : 1;
             if (int st = attn_decode_impl(kp, vp, io->page_table, io->pos, io->attn_q + ai * q_sz,
-                                          io->attn_gate ? io->attn_gate + ai * q_sz : nullptr,
-                                          io->attn_o + ai * q_sz, nullptr, c->attn_ws, c->attn_ws_bytes, &dp,
-                                          run, tm ? c->tev[size_t(L) * 4 + 3] : nullptr))
+                                          (io->attn_gate && !io->attn_ml) ? io->attn_gate + ai * q_sz : nullptr,
+                                          io->attn_o + ai * q_sz,
+                                          io->attn_ml ? io->attn_ml + size_t(ai) * B * f.n_q * 2 : nullptr,
+                                          c->attn_ws, c->attn_ws_bytes, &dp, run,
+                                          tm ? c->tev[size_t(L) * 4 + 3] : nullptr))
                 return st;
             mark(L, 2);
             ++ai;
@@ -889,7 +893,8 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
     if (io->batch < 0 || io->batch > c->cfg.max_batch)
         return fail(RL_ERR_RANGE, "batch %d outside [0, max_batch %d]", io->batch, c->cfg.max_batch);
     if (io->batch == 0) return RL_OK;
-    if ((c->n_attn && (!io->attn_q || !io->attn_k || !io->attn_v || !io->attn_o || !io->page_table || !io->pos)) ||
+    if ((c->n_attn && (!io->attn_q || !io->attn_o || !io->page_table || !io->pos ||
+                       (!io->no_append && (!io->attn_k || !io->attn_v)))) ||
         (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
     if (!c->graph_enabled || c->timing) return stack_decode_layers(c, io, as_stream(stream), false);
@@ -898,7 +903,8 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
                       k.attn_k == io->attn_k && k.attn_v == io->attn_v && k.attn_o == io->attn_o &&
                       k.delta_qkv == io->delta_qkv && k.delta_beta == io->delta_beta && k.delta_g == io->delta_g &&
                       k.delta_o == io->delta_o && k.conv_w == io->conv_w && k.page_table == io->page_table &&
-                      k.pos == io->pos && k.slot_ids == io->slot_ids && k.batch == io->batch;
+                      k.pos == io->pos && k.slot_ids == io->slot_ids && k.batch == io->batch &&
+                      k.attn_ml == io->attn_ml && k.no_append == io->no_append;
     if (same && c->gkey_seen == 2) {
         RL_CUDA(cudaGraphLaunch(c->gexec, as_stream(stream)));
         return RL_OK;
@@ -1000,6 +1006,8 @@ int rl_stack_decode_host(rl_cache* c, const rl_stack_io* h) {
     if ((c->n_attn && (!h->attn_q || !h->attn_k || !h->attn_v || !h->attn_o || !h->page_table || !h->pos)) ||
         (c->n_delta && (!h->delta_qkv || !h->delta_beta || !h->delta_g || !h->delta_o)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    if (h->attn_ml || h->no_append)
+        return fail(RL_ERR_UNSUPPORTED, "split-KV partials are offered by rl_stack_decode (device pointers) only");
     if (c->n_delta && !c->d_conv_w) return fail(RL_ERR_RANGE, "call rl_stack_set_conv_w first");
     if (int st = ensure_staging(c)) return st;
     const rl_cache_config& f = c->cfg;

@@ -140,3 +140,55 @@ def test_graph_replay_matches_plain_launches():
         assert torch.equal(ao, ao2) and torch.equal(do, do2)
     for x, y in zip(outs[0][1], outs[1][1]):
         assert torch.equal(x, y)
+
+
+def test_split_kv_partials_merge_to_the_unsplit_step():
+    """Two caches that each hold a token range of every sequence (what two devices hold under
+    split-KV) emit partials through rl_stack_decode; rl_lse_combine over the two equals the step of
+    one cache that holds everything."""
+    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200.cache import HybridCache
+    gen = torch.Generator().manual_seed(21)
+    types = [_lib.RL_LAYER_FULL_ATTENTION] * 2
+    lens = [200, 75]                              # cached tokens per sequence; page 64
+    head = [128, 64]                              # tokens on the first "device" (whole pages)
+    B = 2
+    k_hist = [[torch.randn(n, 4, 256, generator=gen).half() for n in lens] for _ in types]
+    v_hist = [[torch.randn(n, 4, 256, generator=gen).half() for n in lens] for _ in types]
+
+    def make(tok_from, tok_to):
+        cache = HybridCache(types, n_pages=8, n_slots=1, max_batch=B, max_pages_per_seq=4)
+        table = torch.tensor([[0, 1, 2, 3], [4, 5, 6, 7]], dtype=torch.int32).cuda()
+        for a in range(len(types)):
+            for b in range(B):
+                ops.kv_append(cache.k_pool(a), cache.v_pool(a), table[b], k_hist[a][b][tok_from[b]:tok_to[b]].cuda(),
+                              v_hist[a][b][tok_from[b]:tok_to[b]].cuda(), pos0=0)
+        return cache, table
+
+    sh = None
+    full, table = make([0, 0], lens)
+    sh = full.io_shapes(B)
+    t = {n: torch.randn(sh[n], generator=gen).cuda() for n in ("attn_q", "attn_gate", "attn_k", "attn_v")}
+    io = dict(t, attn_o=torch.zeros(sh["attn_o"]).cuda(), page_table=table,
+              pos=torch.tensor(lens, dtype=torch.int32).cuda())
+    full.decode(io, B)
+    want = io["attn_o"].clone()
+    full.close()
+
+    parts_o, parts_ml = [], []
+    for rank in range(2):
+        frm = [0, 0] if rank == 0 else head
+        to = head if rank == 0 else lens
+        cache, table = make(frm, to)
+        io = dict(t, attn_o=torch.zeros(sh["attn_o"]).cuda(), attn_ml=torch.zeros(sh["attn_ml"]).cuda(),
+                  page_table=table, pos=torch.tensor([to[b] - frm[b] for b in range(B)], dtype=torch.int32).cuda(),
+                  no_append=(rank == 0))
+        cache.decode(io, B)
+        _lib.check_device()
+        parts_o.append(io["attn_o"].reshape(-1, 256))
+        parts_ml.append(io["attn_ml"].reshape(-1, 2))
+        cache.close()
+    got = ops.lse_combine(torch.stack(parts_o), torch.stack(parts_ml), t["attn_gate"].reshape(-1, 256))
+    got = got.reshape(want.shape)
+    assert (got - want).abs().max().item() <= 1e-5
+    assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) <= 1e-5
