@@ -499,15 +499,11 @@ def main():
         head_ways = world
         full = contexts(args, 0)
         ctx, pos_local = [], []
+        from rapidllm_b200.shard import token_range_of_part
         for c in full:
-            p_tot = (c + PAGE - 1) // PAGE
-            p0, p1 = rank * p_tot // world, (rank + 1) * p_tot // world
-            if rank == world - 1:
-                ctx.append(c - p0 * PAGE)                  # tokens this rank holds after the append
-                pos_local.append(c - 1 - p0 * PAGE)
-            else:
-                ctx.append(max(1, (p1 - p0) * PAGE))
-                pos_local.append((p1 - p0) * PAGE)
+            first, n_local = token_range_of_part(c, world, rank, PAGE)   # c counts the token being decoded
+            ctx.append(max(1, n_local))
+            pos_local.append(n_local - 1 if rank == world - 1 else n_local)
     else:
         ctx = contexts(args, rank)
     B = len(ctx)

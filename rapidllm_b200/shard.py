@@ -6,9 +6,10 @@ axes, none of which moves KV or state between GPUs:
   * heads       -- rank r owns KV heads and DeltaNet value heads (with their key heads: value
                    head h uses key head h // 3, so groups of 3 stay together); outputs are
                    disjoint head slices, gathered with one all_gather;
-  * kv_split    -- when there are more ranks than KV heads, the ranks that share a KV head
-                   hold alternating pages of every sequence and exchange (o, max, sum)
-                   partials, merged by rl_lse_combine.
+  * kv_split    -- the ranks that share a KV head hold different pages of every sequence
+                   (alternating pages: pages_of_part; or one contiguous page range per rank:
+                   token_range_of_part, where the last rank holds the tail and appends) and
+                   exchange (o, max, sum) partials, merged by rl_lse_combine.
 """
 from __future__ import annotations
 
@@ -67,3 +68,16 @@ def plan_sequences(rank: int, world: int, batch: int) -> range:
     per, extra = divmod(batch, world)
     start = rank * per + min(rank, extra)
     return range(start, start + per + (1 if rank < extra else 0))
+
+
+def token_range_of_part(n_tokens: int, world: int, rank: int, page_tokens: int = 64):
+    """(first token, token count) of the contiguous page range rank holds out of n_tokens.
+
+    Whole pages go to every rank but the last, which also holds the partly filled tail page;
+    a rank may hold nothing when there are fewer pages than ranks.
+    """
+    n_pages = (n_tokens + page_tokens - 1) // page_tokens
+    p0, p1 = rank * n_pages // world, (rank + 1) * n_pages // world
+    first = p0 * page_tokens
+    last = n_tokens if rank == world - 1 else p1 * page_tokens
+    return first, max(0, last - first)

@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from conftest import ROOT
-from rapidllm_b200.shard import pages_of_part, plan_heads, plan_sequences
+from rapidllm_b200.shard import pages_of_part, plan_heads, plan_sequences, token_range_of_part
 
 
 def test_shard_plans():
@@ -33,6 +33,12 @@ def test_shard_plans():
     assert [len(plan_sequences(r, 4, 30)) for r in range(4)] == [8, 8, 7, 7]
     with pytest.raises(ValueError):
         plan_heads(0, 3)
+    for n_tok in (1, 63, 64, 65, 1000, 32768):
+        for world in (1, 2, 4, 8):
+            parts = [token_range_of_part(n_tok, world, r) for r in range(world)]
+            assert parts[0][0] == 0 and sum(n for _, n in parts) == n_tok
+            assert all(parts[r][0] + parts[r][1] == parts[r + 1][0] or parts[r + 1][1] == 0 for r in range(world - 1))
+            assert all(f % 64 == 0 for f, _ in parts)
 
 
 def _worker(rank, world, port, ret):
@@ -69,6 +75,16 @@ def _worker(rank, world, port, ret):
     merged = np.stack([orc.lse_combine([x[h, 0].item() for x in gml], [x[h, 1].item() for x in gml],
                                        np.stack([x[h].numpy() for x in go])) for h in range(n_q)])
     err = float(np.abs(merged - full).max())
+    # (2b) the same exchange with one contiguous page range per rank (token_range_of_part)
+    first, n_loc = token_range_of_part(seq, world, rank)
+    for h in range(n_q):
+        m, l, acc = orc.attn_partial(q[h], k[first:first + n_loc], v[first:first + n_loc], 0, n_loc, h // (n_q // n_kv))
+        po[h], pml[h] = acc, (m, l)
+    dist.all_gather(go, torch.from_numpy(po))
+    dist.all_gather(gml, torch.from_numpy(pml))
+    merged = np.stack([orc.lse_combine([x[h, 0].item() for x in gml], [x[h, 1].item() for x in gml],
+                                       np.stack([x[h].numpy() for x in go])) for h in range(n_q)])
+    err = max(err, float(np.abs(merged - full).max()))
     # (3) a rank that fails is seen by the others on the host, not by a hung collective
     flag = torch.tensor([1 if rank == 1 else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MAX)
