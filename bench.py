@@ -102,12 +102,13 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.lines = []
+        self.first = 0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -117,6 +118,14 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
+
+    def mark(self, wait_s=3.0):
+        """Samples taken before this call (start-up of the tool, warm-up steps) are not reported;
+        waits (bounded) until the tool has produced its first sample."""
+        t0 = time.time()
+        while self.proc and not self.lines and time.time() - t0 < wait_s:
+            time.sleep(0.02)
+        self.first = len(self.lines)
 
     def stop(self):
         if not self.proc:
@@ -129,7 +138,7 @@ class ClockSampler:
         self.thread.join(timeout=2)
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in self.lines[self.first:]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -579,13 +588,14 @@ def main():
     # second warm-up step), no host synchronisation between steps.
     if args.no_graph:
         cache.set_graph(False)
+    sampler = ClockSampler(local)
+    sampler.start()                              # the tool needs a moment to come up: start it before the warm-up
     for _ in range(max(3, args.warmup)):
         cache.decode(dev, B)
         exchange()
     _lib.check_device()
     sync_all()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
