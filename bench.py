@@ -49,7 +49,8 @@ def parse():
     ap.add_argument("--workload", default="stack",
                     choices=["stack", "compact_decode", "f16_decode", "delta_step", "attn_prefill", "delta_prefill"],
                     help="stack = the headline workload; the others time one operator at the shapes of "
-                         "BASELINE configs 2, 0 and 1 (secondary lines, N=1 only)")
+                         "the single-layer configurations: 131 072-token compact-KV decode, 4 096-token F16 decode, one "
+                         "DeltaNet step, 8 192-token prefills (secondary lines, N=1 only)")
     ap.add_argument("--shard", default="seq", choices=["seq", "heads", "splitkv"],
                     help="N > 1: seq = every rank owns 32 sequences of its own (weak scaling, no collective); "
                          "heads = ONE batch of 32 divided by KV / value heads (up to 4 ways) and then by sequence, "
@@ -258,7 +259,7 @@ def run_reference(args):
 
 # --------------------------------------------------------------------------------------
 def run_operator(args):
-    """Secondary lines: one operator at the shapes of BASELINE configs 0, 1, 2 (single GPU)."""
+    """Secondary lines: one operator at its single-layer benchmark shapes (single GPU)."""
     import torch
 
     import __graft_entry__ as ge
