@@ -282,6 +282,40 @@ int rl_conv1d_update(const float* x, const float* w, float* state, const int32_t
 int rl_conv1d_causal(const float* x, const float* w, float* y, float* state_io, int seq,
                      const rl_conv1d_params* p, int use_state_in, void* stream);
 
+/* ---- element-wise steps around the mixers (the "next" ring of the path) ---- */
+
+typedef struct rl_attn_qk_prepare_params {
+    int n_q, n_kv, head_dim;     /* head_dim 256 */
+    int rotary_dim;              /* 64: even, <= head_dim */
+    int rows;                    /* tokens: batch at decode, chunk length at prefill */
+    int pos0;                    /* used when pos == NULL: row r is at position pos0 + r */
+    float theta;                 /* 1e7 */
+    float eps;                   /* 1e-6 */
+} rl_attn_qk_prepare_params;
+
+/* What fused_attn_decode does between its projections and the cache append
+ * (src/kernels/ops_fused.cpp:154-171; cuda_engine.cu:5819-5839, 93-115): split
+ * qg [rows][n_q][2*hd] ([q | gate] per head) into q_out and gate_out, head RMSNorm
+ * with weight (1 + gamma) on q and on k (ops::qwen3_rmsnorm, ops.cpp:107-127; q_norm,
+ * k_norm [hd] or NULL), partial RoPE at pos[row] on the first rotary_dim dims
+ * (ops::rope_partial, ops.cpp:470-493).  k [rows][n_kv][hd] is updated in place. */
+int rl_attn_qk_prepare(const float* qg, float* k, const float* q_norm, const float* k_norm,
+                       const int32_t* pos, float* q_out, float* gate_out,
+                       const rl_attn_qk_prepare_params* p, void* stream);
+
+/* ops::gated_rmsnorm in its per-head form (ops.h:22, ops.cpp:129-157), applied to
+ * the delta-rule output (ops_fused.cpp:131): y = gamma * (x / rms(x)) * silu(z) per
+ * head.  x, z, y [rows][n_heads][head_dim] (head_dim 128); gamma [head_dim] or NULL. */
+int rl_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* y, int rows,
+                     int n_heads, int head_dim, float eps, void* stream);
+
+/* The gate maths in front of the delta rule (ops_fused.cpp:12-13, 122-123):
+ * beta = sigmoid(b), g_log = -exp(A_log) * softplus(a + dt_bias).  a, b, beta, g_log
+ * [rows][n_v]; A_log, dt_bias [n_v]. */
+int rl_delta_gates(const float* a, const float* b, const float* A_log, const float* dt_bias,
+                   float* beta, float* g_log, int rows, int n_v, void* stream);
+
+
 /* ------------------------------------------------------------------------- */
 /* Caches and the layer_types[] dispatch                                      */
 /* ------------------------------------------------------------------------- */

@@ -195,6 +195,49 @@ class Oracle:
         self.lib.rlo_l2norm(xp, _ptr(y, C.c_float), x.size, C.c_float(eps))
         return y
 
+    def qwen3_rmsnorm(self, x, gamma, eps=1e-6):
+        """rlo_qwen3_rmsnorm over the last axis: x [..., n], gamma [n] or None."""
+        x, _ = _f32(x)
+        y = np.empty_like(x)
+        g = None if gamma is None else np.ascontiguousarray(gamma, np.float32)
+        rows = x.reshape(-1, x.shape[-1])
+        out = y.reshape(-1, x.shape[-1])
+        for r in range(rows.shape[0]):
+            self.lib.rlo_qwen3_rmsnorm(_ptr(rows[r], C.c_float), None if g is None else _ptr(g, C.c_float),
+                                       _ptr(out[r], C.c_float), rows.shape[1], C.c_float(eps))
+        return y
+
+    def rope_partial(self, q, k, pos, rotary_dim=64, theta=1e7):
+        """rlo_rope_partial: q [n_q,hd], k [n_kv,hd] -> rotated copies."""
+        q = np.array(q, np.float32, order="C")
+        k = np.array(k, np.float32, order="C")
+        self.lib.rlo_rope_partial(_ptr(q, C.c_float), _ptr(k, C.c_float), q.shape[0], k.shape[0], q.shape[1],
+                                  int(rotary_dim), int(pos), C.c_float(theta))
+        return q, k
+
+    def attn_qk_prepare(self, qg, k, q_norm, k_norm, pos, rotary_dim=64, theta=1e7, eps=1e-6):
+        """rlo_attn_qk_prepare: qg [n_q, 2*hd] ([q | gate] per head), k [n_kv, hd] -> q, gate, k."""
+        qg, qgp = _f32(qg)
+        k = np.array(k, np.float32, order="C")
+        qn, qnp = _f32(q_norm)
+        kn, knp = _f32(k_norm)
+        n_q, hd = qg.shape[0], qg.shape[1] // 2
+        q = np.empty((n_q, hd), np.float32)
+        gate = np.empty((n_q, hd), np.float32)
+        self.lib.rlo_attn_qk_prepare(qgp, _ptr(k, C.c_float), qnp, knp, _ptr(q, C.c_float), _ptr(gate, C.c_float),
+                                     n_q, k.shape[0], hd, int(rotary_dim), int(pos), C.c_float(theta),
+                                     C.c_float(eps))
+        return q, gate, k
+
+    def gated_rmsnorm(self, x, z, gamma, eps=1e-6):
+        """rlo_gated_rmsnorm: x, z [n]; gamma [gamma_n] (per head when gamma_n < n)."""
+        x, xp = _f32(x)
+        z, zp = _f32(z)
+        g, gp = _f32(gamma)
+        y = np.empty_like(x)
+        self.lib.rlo_gated_rmsnorm(xp, zp, gp, _ptr(y, C.c_float), x.size, C.c_float(eps), g.size)
+        return y
+
     def conv1d_update(self, x_t, w, state):
         """rlo_conv1d_update: state [dim,k] updated in place; returns y [dim]."""
         assert state.dtype == np.float32 and state.flags.c_contiguous
@@ -328,6 +371,28 @@ class Reference:
         y = np.empty_like(x)
         self.lib.ref_conv1d_causal_prefill(xp, wp, _ptr(y, C.c_float), x.shape[0], x.shape[1],
                                            w.shape[1])
+        return y
+
+    def qwen3_rmsnorm(self, x, gamma, eps=1e-6):
+        x, xp = _f32(x)
+        g, gp = _f32(gamma)
+        y = np.empty_like(x)
+        self.lib.ref_qwen3_rmsnorm(xp, gp, _ptr(y, C.c_float), x.size, C.c_float(eps))
+        return y
+
+    def rope_partial(self, q, k, pos, rotary_dim=64, theta=1e7):
+        q = np.array(q, np.float32, order="C")
+        k = np.array(k, np.float32, order="C")
+        self.lib.ref_rope_partial(_ptr(q, C.c_float), _ptr(k, C.c_float), q.shape[0], k.shape[0], q.shape[1],
+                                  int(rotary_dim), int(pos), C.c_float(theta))
+        return q, k
+
+    def gated_rmsnorm(self, x, z, gamma, eps=1e-6):
+        x, xp = _f32(x)
+        z, zp = _f32(z)
+        g, gp = _f32(gamma)
+        y = np.empty_like(x)
+        self.lib.ref_gated_rmsnorm(xp, zp, gp, _ptr(y, C.c_float), x.size, C.c_float(eps), g.size)
         return y
 
     def l2norm(self, x, eps=1e-6):

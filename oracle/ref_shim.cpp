@@ -47,6 +47,20 @@ void ref_conv1d_causal_prefill(const float* x, const float* w, float* y, int seq
 
 void ref_l2norm(const float* x, float* y, int n, float eps) { ops::l2norm(x, y, n, eps); }
 
+void ref_qwen3_rmsnorm(const float* x, const float* gamma, float* y, int n, float eps) {
+    ops::qwen3_rmsnorm(x, gamma, y, n, eps);
+}
+
+void ref_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* y, int n, float eps,
+                       int gamma_n) {
+    ops::gated_rmsnorm(x, z, gamma, y, n, eps, gamma_n);
+}
+
+void ref_rope_partial(float* q, float* k, int n_q, int n_kv, int head_dim, int rotary_dim, int pos,
+                      float theta) {
+    ops::rope_partial(q, k, n_q, n_kv, head_dim, rotary_dim, pos, theta);
+}
+
 void ref_set_threads(int n) { set_num_threads(n); }
 int ref_num_threads(void) { return num_threads(); }
 

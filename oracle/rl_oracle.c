@@ -294,6 +294,95 @@ RLO_API void rlo_delta_gates(const float* a, const float* b, const float* A_log,
     }
 }
 
+/* Head RMSNorm with the (1 + gamma) weight, scalar path of src/kernels/ops.cpp:107-127:
+ * double sum of squares, inv = 1 / sqrtf((float)(acc / n) + eps), y = x * inv * (1 + gamma). */
+RLO_API void rlo_qwen3_rmsnorm(const float* x, const float* gamma, float* y, int n, float eps) {
+    double acc = 0;
+    for (int i = 0; i < n; ++i) acc += (double)x[i] * x[i];
+    const float inv = 1.f / sqrtf((float)(acc / n) + eps);
+    for (int i = 0; i < n; ++i) {
+        const float g = gamma ? (1.f + gamma[i]) : 1.f;
+        y[i] = x[i] * inv * g;
+    }
+}
+
+/* Partial rotary embedding, src/kernels/ops.cpp:470-493: the first rotary_dim dims of every
+ * head, rotate-half pairing (i, i + rotary_dim/2) for head_dim >= 64, adjacent pairs below;
+ * freq_i = 1 / powf(theta, i / pairs), angle = (float)pos * freq_i. */
+static void rope_heads(float* t, int n_heads, int head_dim, int rotary_dim, int pos, float theta) {
+    const int pairs = rotary_dim / 2;
+    for (int h = 0; h < n_heads; ++h) {
+        float* v = t + (size_t)h * head_dim;
+        for (int i = 0; i < pairs; ++i) {
+            const float freq = 1.f / powf(theta, (float)i / (float)pairs);
+            const float ang = (float)pos * freq;
+            const float c = cosf(ang), s = sinf(ang);
+            if (head_dim >= 64) {
+                const float x0 = v[i], x1 = v[i + pairs];
+                v[i] = x0 * c - x1 * s;
+                v[i + pairs] = x0 * s + x1 * c;
+            } else {
+                const float x0 = v[2 * i], x1 = v[2 * i + 1];
+                v[2 * i] = x0 * c - x1 * s;
+                v[2 * i + 1] = x0 * s + x1 * c;
+            }
+        }
+    }
+}
+RLO_API void rlo_rope_partial(float* q, float* k, int n_q, int n_kv, int head_dim, int rotary_dim,
+                              int pos, float theta) {
+    rope_heads(q, n_q, head_dim, rotary_dim, pos, theta);
+    rope_heads(k, n_kv, head_dim, rotary_dim, pos, theta);
+}
+
+/* What fused_attn_decode does between the projections and the cache append,
+ * src/kernels/ops_fused.cpp:154-171: split each query head's row pair into q and gate
+ * (head_dim >= 64: [q | gate] per head; below: all q then all gate), head RMSNorm of q and k
+ * with (1 + gamma), partial RoPE at pos.  qg [n_q * 2 * hd], k [n_kv * hd] in place. */
+RLO_API void rlo_attn_qk_prepare(const float* qg, float* k, const float* q_norm, const float* k_norm,
+                                 float* q, float* gate, int n_q, int n_kv, int hd, int rotary_dim,
+                                 int pos, float theta, float eps) {
+    const int qn = n_q * hd;
+    if (hd >= 64) {
+        for (int h = 0; h < n_q; ++h)
+            for (int d = 0; d < hd; ++d) {
+                q[h * hd + d] = qg[h * hd * 2 + d];
+                gate[h * hd + d] = qg[h * hd * 2 + hd + d];
+            }
+    } else {
+        for (int j = 0; j < qn; ++j) {
+            q[j] = qg[j];
+            gate[j] = qg[qn + j];
+        }
+    }
+    for (int h = 0; h < n_q; ++h) rlo_qwen3_rmsnorm(q + h * hd, q_norm, q + h * hd, hd, eps);
+    for (int h = 0; h < n_kv; ++h) rlo_qwen3_rmsnorm(k + h * hd, k_norm, k + h * hd, hd, eps);
+    rlo_rope_partial(q, k, n_q, n_kv, hd, rotary_dim, pos, theta);
+}
+
+/* Gated RMSNorm after the delta rule, src/kernels/ops.cpp:129-157 (silu at line 13):
+ * per head of gamma_n values when gamma_n < n divides n and n >= 256, else over all n:
+ * y = gamma * (x * inv) * silu(z), silu(z) = z / (1 + expf(-z)). */
+RLO_API void rlo_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* y, int n,
+                               float eps, int gamma_n) {
+    if (gamma_n <= 0) gamma_n = n;
+    const int per_head = gamma_n < n && (n % gamma_n) == 0 && n >= 256;
+    const int span = per_head ? gamma_n : n;
+    for (int h = 0; h < n / span; ++h) {
+        const float* xh = x + (size_t)h * span;
+        const float* zh = z + (size_t)h * span;
+        float* yh = y + (size_t)h * span;
+        double acc = 0;
+        for (int i = 0; i < span; ++i) acc += (double)xh[i] * xh[i];
+        const float inv = 1.f / sqrtf((float)(acc / span) + eps);
+        for (int i = 0; i < span; ++i) {
+            const float g = gamma ? gamma[per_head ? i : i % gamma_n] : 1.f;
+            const float sz = zh[i] / (1.f + expf(-zh[i]));
+            yh[i] = g * (xh[i] * inv) * sz;
+        }
+    }
+}
+
 /* Depthwise causal conv, decode form.  src/kernels/ops.cpp:458-468.
  * state [dim][k] (oldest tap first) shifted left, x appended, dot, SiLU. */
 RLO_API void rlo_conv1d_update(const float* x_t, const float* w, float* state, float* y, int dim,

@@ -59,6 +59,11 @@ class Conv1dParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dim", "k", "silu", "batch", "n_slots")]
 
 
+class AttnQkPrepareParams(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_q", "n_kv", "head_dim", "rotary_dim", "rows", "pos0")] + [
+        ("theta", C.c_float), ("eps", C.c_float)]
+
+
 class CacheConfig(C.Structure):
     _fields_ = [("n_layers", C.c_int), ("layer_types", C.POINTER(C.c_int)),
                 ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int), ("kv_dtype", C.c_int),
@@ -102,6 +107,9 @@ SYMBOLS = {
     "rl_delta_chunk_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(DeltaChunkParams), _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),
     "rl_conv1d_causal": (_i, [_vp, _vp, _vp, _vp, _i, C.POINTER(Conv1dParams), _i, _vp]),
+    "rl_attn_qk_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnQkPrepareParams), _vp]),
+    "rl_gated_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, _vp]),
+    "rl_delta_gates": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "rl_cache_create": (_i, [C.POINTER(CacheConfig), C.POINTER(_vp)]),
     "rl_cache_destroy": (None, [_vp]),
     "rl_cache_bytes": (_sz, [_vp]),

@@ -679,6 +679,73 @@ static int delta_chunk_check(const rl_delta_chunk_params* p) {
     return RL_OK;
 }
 
+int rl_attn_qk_prepare(const float* qg, float* k, const float* q_norm, const float* k_norm, const int32_t* pos,
+                       float* q_out, float* gate_out, const rl_attn_qk_prepare_params* p, void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->head_dim != rl::kHeadDim) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 256", p->head_dim);
+    if (p->n_q <= 0 || p->n_kv <= 0 || p->n_q + p->n_kv > 65535 || p->rows < 0 || p->rows > 65535)
+        return fail(RL_ERR_RANGE, "n_q %d n_kv %d rows %d", p->n_q, p->n_kv, p->rows);
+    if (p->rotary_dim < 0 || p->rotary_dim > p->head_dim || (p->rotary_dim & 1))
+        return fail(RL_ERR_RANGE, "rotary_dim %d must be even and at most head_dim", p->rotary_dim);
+    if (p->rotary_dim > 0 && !(p->theta > 0.f)) return fail(RL_ERR_RANGE, "theta must be positive");
+    if (p->rows == 0) return RL_OK;
+    if (!qg || !k || !q_out || !gate_out) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::AttnQkPrepareArgs a;
+    a.qg = qg;
+    a.k = k;
+    a.q_norm = q_norm;
+    a.k_norm = k_norm;
+    a.pos = pos;
+    a.q_out = q_out;
+    a.gate_out = gate_out;
+    a.n_q = p->n_q;
+    a.n_kv = p->n_kv;
+    a.rotary_dim = p->rotary_dim;
+    a.pos0 = p->pos0;
+    a.eps = p->eps;
+    const int pairs = p->rotary_dim / 2;
+    for (int i = 0; i < pairs; ++i) a.inv_freq[i] = 1.f / powf(p->theta, float(i) / float(pairs));
+    rl::attn_qk_prepare_kernel<<<dim3(p->n_q + p->n_kv, p->rows), rl::kHeadDim, 0, as_stream(stream)>>>(a);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* y, int rows, int n_heads,
+                     int head_dim, float eps, void* stream) {
+    if (head_dim != 128) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 128", head_dim);
+    if (rows < 0 || rows > 65535 || n_heads <= 0 || n_heads > 65535) return fail(RL_ERR_RANGE, "rows %d n_heads %d", rows, n_heads);
+    if (rows == 0) return RL_OK;
+    if (!x || !z || !y) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::GatedRmsnormArgs a;
+    a.x = x;
+    a.z = z;
+    a.gamma = gamma;
+    a.y = y;
+    a.n_heads = n_heads;
+    a.head_dim = head_dim;
+    a.eps = eps;
+    rl::gated_rmsnorm_kernel<<<dim3(n_heads, rows), head_dim, 0, as_stream(stream)>>>(a);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_delta_gates(const float* a, const float* b, const float* A_log, const float* dt_bias, float* beta,
+                   float* g_log, int rows, int n_v, void* stream) {
+    if (rows < 0 || n_v <= 0 || 1LL * rows * n_v > (1LL << 30)) return fail(RL_ERR_RANGE, "rows %d n_v %d", rows, n_v);
+    if (rows == 0) return RL_OK;
+    if (!a || !b || !A_log || !dt_bias || !beta || !g_log) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    const int n = rows * n_v;
+    rl::delta_gates_kernel<<<(n + 255) / 256, 256, 0, as_stream(stream)>>>(a, b, A_log, dt_bias, beta, g_log, n_v, rows);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
 size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p) {
     if (delta_chunk_check(p)) return 0;
     const size_t n_chunks = (size_t(p->seq) + 63) / 64;

@@ -125,6 +125,32 @@ void launch_delta_decode(const DeltaDecodeArgs& a, int sms, cudaStream_t st);
 size_t delta_decode_stream_smem_bytes();
 const void* delta_decode_stream_kernel_ptr();
 
+// ---- element-wise steps around the mixers (layer_glue.cu) ------------------------------------
+struct AttnQkPrepareArgs {
+    const float* qg;             // [rows][n_q][2 * 256]  ([q | gate] per head)
+    float* k;                    // [rows][n_kv][256] in place
+    const float* q_norm;         // [256] or null
+    const float* k_norm;         // [256] or null
+    const int32_t* pos;          // [rows] or null (then pos0 + row)
+    float* q_out;                // [rows][n_q][256]
+    float* gate_out;             // [rows][n_q][256]
+    int n_q, n_kv, rotary_dim, pos0;
+    float eps;
+    float inv_freq[128];         // 1 / theta^(i / pairs), i < rotary_dim / 2, computed on the host
+};
+__global__ void attn_qk_prepare_kernel(AttnQkPrepareArgs a);
+struct GatedRmsnormArgs {
+    const float* x;              // [rows][n_heads][head_dim]
+    const float* z;
+    const float* gamma;          // [head_dim] or null
+    float* y;
+    int n_heads, head_dim;
+    float eps;
+};
+__global__ void gated_rmsnorm_kernel(GatedRmsnormArgs a);
+__global__ void delta_gates_kernel(const float* a_in, const float* b_in, const float* A_log, const float* dt_bias,
+                                   float* beta, float* g_log, int n_v, int rows);
+
 // ---- chunked (WY-form) DeltaNet prefill (tcgen05) --------------------------------------------
 struct DeltaChunkArgs {
     float* S;                    // [n_v][128][128] fp32 state of one sequence, in place

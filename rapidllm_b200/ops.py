@@ -268,3 +268,40 @@ def conv1d_causal_prefill(x, w, state=None, use_state_in=False):
     check(lib().rl_conv1d_causal(_p(x), _p(w), _p(y), _p(state), seq, C.byref(p),
                                  int(use_state_in), _stream()))
     return y
+
+
+def attn_qk_prepare(qg, k, q_norm=None, k_norm=None, pos=None, pos0=0, rotary_dim=64, theta=1e7, eps=1e-6):
+    """The steps of fused_attn_decode between the projections and the cache append: split
+    qg [rows][n_q][512] into q and gate, head RMSNorm (1 + gamma) of q and k, partial RoPE at
+    pos [rows] (int32) or pos0 + row.  k [rows][n_kv][256] is updated in place; returns q, gate."""
+    for t, n in ((qg, "qg"), (k, "k"), (q_norm, "q_norm"), (k_norm, "k_norm")):
+        _need(t, torch.float32, n)
+    _need(pos, torch.int32, "pos")
+    rows, n_q, two_hd = qg.shape
+    q = torch.empty(rows, n_q, two_hd // 2, dtype=torch.float32, device=qg.device)
+    gate = torch.empty_like(q)
+    p = _lib.AttnQkPrepareParams(n_q=n_q, n_kv=k.shape[1], head_dim=two_hd // 2, rotary_dim=rotary_dim,
+                                 rows=rows, pos0=pos0, theta=theta, eps=eps)
+    check(lib().rl_attn_qk_prepare(_p(qg), _p(k), _p(q_norm), _p(k_norm), _p(pos), _p(q), _p(gate),
+                                   C.byref(p), _stream()))
+    return q, gate
+
+
+def gated_rmsnorm(x, z, gamma=None, eps=1e-6):
+    """ops::gated_rmsnorm per head: x, z [rows][n_heads][128], gamma [128] -> y."""
+    for t, n in ((x, "x"), (z, "z"), (gamma, "gamma")):
+        _need(t, torch.float32, n)
+    rows, n_heads, hd = x.shape
+    y = torch.empty_like(x)
+    check(lib().rl_gated_rmsnorm(_p(x), _p(z), _p(gamma), _p(y), rows, n_heads, hd, eps, _stream()))
+    return y
+
+
+def delta_gates(a, b, A_log, dt_bias):
+    """beta = sigmoid(b), g_log = -exp(A_log) * softplus(a + dt_bias); a, b [rows][n_v]."""
+    for t, n in ((a, "a"), (b, "b"), (A_log, "A_log"), (dt_bias, "dt_bias")):
+        _need(t, torch.float32, n)
+    rows, n_v = a.shape
+    beta, g = torch.empty_like(a), torch.empty_like(a)
+    check(lib().rl_delta_gates(_p(a), _p(b), _p(A_log), _p(dt_bias), _p(beta), _p(g), rows, n_v, _stream()))
+    return beta, g

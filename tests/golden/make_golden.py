@@ -8,7 +8,7 @@ box, the vectors can):
 Two sources, both the reference's own code:
   * oracle/_ref/librl_ref.so  -- rapidllm::ops::{attn_decode, attn_prefill,
     delta_recurrent_step_scalar/_simd, conv1d_update, conv1d_causal_prefill,
-    l2norm} compiled from the reference's sources (see oracle/Makefile);
+    l2norm, qwen3_rmsnorm, rope_partial, gated_rmsnorm} compiled from the reference's sources (see oracle/Makefile);
   * python/goldens/tiny_hybrid.py -- the reference's pure-Python model of the
     tiny hybrid net; its delta_step() and its decode-attention arithmetic give
     an independent double-precision statement at tiny dims (dk=dv=8, hd=8).
@@ -132,6 +132,28 @@ def main():
         o.extend([oh[d] * th.sigmoid(gate[hq * HD + d]) for d in range(HD)])
     out["tiny_attn_q"], out["tiny_attn_k"], out["tiny_attn_v"] = map(np.array, (qh, kc, vc))
     out["tiny_attn_gate"], out["tiny_attn_o"] = np.array(gate), np.array(o)
+
+    # the steps around the mixers (own generator, so the vectors above do not move):
+    # head RMSNorm with (1 + gamma), partial RoPE, gated RMSNorm
+    rng2 = np.random.default_rng(20241)
+    for tag, n in {"a": 256, "b": 32}.items():
+        x = rng2.standard_normal(n, dtype=np.float32)
+        gm = (rng2.standard_normal(n, dtype=np.float32) * 0.1).astype(np.float32)
+        out[f"rms_{tag}_x"], out[f"rms_{tag}_gamma"], out[f"rms_{tag}_y"] = x, gm, ref.qwen3_rmsnorm(x, gm)
+    for tag, (n_q, n_kv, hd, rot, pos) in {"a": (24, 4, 256, 64, 4095), "b": (6, 2, 64, 64, 131071),
+                                           "c": (4, 2, 8, 8, 17)}.items():
+        q = rng2.standard_normal((n_q, hd), dtype=np.float32)
+        k = rng2.standard_normal((n_kv, hd), dtype=np.float32)
+        qr, kr = ref.rope_partial(q, k, pos, rotary_dim=rot, theta=1e7)
+        out[f"rope_{tag}_q"], out[f"rope_{tag}_k"] = q, k
+        out[f"rope_{tag}_meta"] = np.array([rot, pos], np.int64)
+        out[f"rope_{tag}_q_out"], out[f"rope_{tag}_k_out"] = qr, kr
+    for tag, (n, gn) in {"a": (48 * 128, 128), "b": (96, 96), "c": (64, 16)}.items():
+        x = rng2.standard_normal(n, dtype=np.float32)
+        z = rng2.standard_normal(n, dtype=np.float32)
+        gm = rng2.standard_normal(gn, dtype=np.float32)
+        out[f"gnorm_{tag}_x"], out[f"gnorm_{tag}_z"], out[f"gnorm_{tag}_gamma"] = x, z, gm
+        out[f"gnorm_{tag}_y"] = ref.gated_rmsnorm(x, z, gm)
 
     path = os.path.join(HERE, "ref_vectors.npz")
     np.savez_compressed(path, **out)

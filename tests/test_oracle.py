@@ -53,6 +53,28 @@ def test_conv1d_vs_reference_golden(oracle, golden):
     assert np.array_equal(oracle.l2norm(golden["l2_x"]), golden["l2_y"])
 
 
+def test_norms_and_rope_bit_exact_vs_reference_golden(oracle, golden):
+    for tag in "ab":
+        y = oracle.qwen3_rmsnorm(golden[f"rms_{tag}_x"], golden[f"rms_{tag}_gamma"])
+        assert np.array_equal(y, golden[f"rms_{tag}_y"])
+    for tag in "abc":
+        rot, pos = (int(v) for v in golden[f"rope_{tag}_meta"])
+        q, k = oracle.rope_partial(golden[f"rope_{tag}_q"], golden[f"rope_{tag}_k"], pos, rotary_dim=rot)
+        assert np.array_equal(q, golden[f"rope_{tag}_q_out"]) and np.array_equal(k, golden[f"rope_{tag}_k_out"])
+    for tag in "abc":
+        y = oracle.gated_rmsnorm(golden[f"gnorm_{tag}_x"], golden[f"gnorm_{tag}_z"], golden[f"gnorm_{tag}_gamma"])
+        assert np.array_equal(y, golden[f"gnorm_{tag}_y"])
+    # the composite of ops_fused.cpp:154-171 equals its parts
+    rng = np.random.default_rng(5)
+    qg = rng.standard_normal((24, 512), dtype=np.float32)
+    k = rng.standard_normal((4, 256), dtype=np.float32)
+    qn = rng.standard_normal(256, dtype=np.float32) * 0.1
+    kn = rng.standard_normal(256, dtype=np.float32) * 0.1
+    q, gate, k2 = oracle.attn_qk_prepare(qg, k, qn, kn, pos=777)
+    q_ref, k_ref = oracle.rope_partial(oracle.qwen3_rmsnorm(qg[:, :256], qn), oracle.qwen3_rmsnorm(k, kn), 777)
+    assert np.array_equal(q, q_ref) and np.array_equal(k2, k_ref) and np.array_equal(gate, qg[:, 256:])
+
+
 def test_tiny_hybrid_python_model(oracle, golden):
     """python/goldens/tiny_hybrid.py delta_step (120-146) and decode attention
     with the sigmoid gate (275-312), double precision, tiny dims."""
