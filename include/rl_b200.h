@@ -241,6 +241,20 @@ int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const 
                        const float* v, const float* beta, const float* g_log, float* o,
                        const rl_delta_recurrent_params* p, void* stream);
 
+/* n_tok consecutive tokens per sequence in one pass with the state kept on chip: the
+ * speculative-verify form of the step (gdn_decode_tn_k, cuda_engine.cu:5289-5536;
+ * gdn_t12.cu:100-220; Engine::spec_verify, cuda_engine.h:69-77).  q,k [batch][n_tok][n_qk][128],
+ * v [batch][n_tok][n_v][128], beta/g_log [batch][n_tok][n_v], o [batch][n_tok][n_v][128];
+ * the strides of p are between sequences (0 = dense), qk_tok_stride / v_tok_stride between
+ * tokens (0 = dense).  When S_backup != NULL (same shape as S) the state of every touched
+ * (slot, head) as it was BEFORE the first token is written there: to roll back to k accepted
+ * tokens, copy those heads back and run k tokens.  The result equals n_tok calls of
+ * rl_delta_recurrent bit for bit.  n_tok <= 64. */
+int rl_delta_recurrent_multi(float* S, float* S_backup, const int32_t* slot_ids, const float* q,
+                             const float* k, const float* v, const float* beta, const float* g_log,
+                             float* o, const rl_delta_recurrent_params* p, int n_tok,
+                             long long qk_tok_stride, long long v_tok_stride, void* stream);
+
 /* DeltaChunkParams {n_v, dk, dv, seq, chunk, eps_l2} (params.h:21; declared but never
  * implemented in the reference) + the key/query head layout. */
 typedef struct rl_delta_chunk_params {

@@ -103,6 +103,8 @@ SYMBOLS = {
     "rl_kv_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_delta_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                 C.POINTER(DeltaRecurrentParams), _vp]),
+    "rl_delta_recurrent_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                      C.POINTER(DeltaRecurrentParams), _i, C.c_longlong, C.c_longlong, _vp]),
     "rl_delta_chunk_workspace_bytes": (_sz, [C.POINTER(DeltaChunkParams)]),
     "rl_delta_chunk_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(DeltaChunkParams), _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),

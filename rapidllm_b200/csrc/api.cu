@@ -626,9 +626,10 @@ int rl_kv_compact_gather(const void* pool, const int32_t* page_table_row, void* 
     return RL_OK;
 }
 
-int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const float* k, const float* v,
-                       const float* beta, const float* g_log, float* o, const rl_delta_recurrent_params* p,
-                       void* stream) {
+// shared by the one-token and the several-token entry points; n_tok scales the dense strides
+static int delta_decode_args(rl::DeltaDecodeArgs* out, float* S, const int32_t* slot_ids, const float* q,
+                             const float* k, const float* v, const float* beta, const float* g_log, float* o,
+                             const rl_delta_recurrent_params* p, int n_tok, DevInfo** dev) {
     if (!p) return fail(RL_ERR_RANGE, "params is NULL");
     if (p->dk != 128 || p->dv != 128) return fail(RL_ERR_UNSUPPORTED, "dk %d dv %d: only 128 x 128", p->dk, p->dv);
     if (p->n_v <= 0 || p->n_v > 65535 || p->batch < 0 || p->batch > 65535 || p->n_slots <= 0)
@@ -638,9 +639,8 @@ int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const 
         return fail(RL_ERR_RANGE, "n_qk %d does not fit n_v %d with head_map %d", p->n_qk, p->n_v, p->head_map);
     if (p->batch == 0) return RL_OK;
     if (!S || !q || !k || !v || !beta || !g_log || !o) return fail(RL_ERR_RANGE, "NULL pointer argument");
-    DevInfo* d;
-    if (int st = dev_info(&d)) return st;
-    rl::DeltaDecodeArgs a;
+    if (int st = dev_info(dev)) return st;
+    rl::DeltaDecodeArgs& a = *out;
     a.S = S;
     a.slot_ids = slot_ids;
     a.q = q;
@@ -649,21 +649,51 @@ int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const 
     a.beta = beta;
     a.g_log = g_log;
     a.o = o;
-    a.err = d->err_ptr;
+    a.err = (*dev)->err_ptr;
     a.batch = p->batch;
     a.n_v = p->n_v;
     a.n_qk = p->n_qk;
     a.n_slots = p->n_slots;
     a.head_map = p->head_map;
     a.eps_l2 = p->eps_l2;
-    a.q_stride = p->q_stride ? p->q_stride : 1LL * p->n_qk * p->dk;
-    a.k_stride = p->k_stride ? p->k_stride : 1LL * p->n_qk * p->dk;
-    a.v_stride = p->v_stride ? p->v_stride : 1LL * p->n_v * p->dv;
+    a.q_stride = p->q_stride ? p->q_stride : 1LL * n_tok * p->n_qk * p->dk;
+    a.k_stride = p->k_stride ? p->k_stride : 1LL * n_tok * p->n_qk * p->dk;
+    a.v_stride = p->v_stride ? p->v_stride : 1LL * n_tok * p->n_v * p->dv;
     if ((a.q_stride | a.k_stride | a.v_stride) % 4 || reinterpret_cast<uintptr_t>(q) % 16 ||
         reinterpret_cast<uintptr_t>(k) % 16 || reinterpret_cast<uintptr_t>(v) % 16 ||
         reinterpret_cast<uintptr_t>(S) % 16)
         return fail(RL_ERR_RANGE, "S, q, k, v must be 16-byte aligned with strides a multiple of 4 floats");
+    return RL_OK;
+}
+
+int rl_delta_recurrent(float* S, const int32_t* slot_ids, const float* q, const float* k, const float* v,
+                       const float* beta, const float* g_log, float* o, const rl_delta_recurrent_params* p,
+                       void* stream) {
+    rl::DeltaDecodeArgs a;
+    DevInfo* d = nullptr;
+    if (int st = delta_decode_args(&a, S, slot_ids, q, k, v, beta, g_log, o, p, 1, &d)) return st;
+    if (p->batch == 0) return RL_OK;
     rl::launch_delta_decode(a, d->sms, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_delta_recurrent_multi(float* S, float* S_backup, const int32_t* slot_ids, const float* q, const float* k,
+                             const float* v, const float* beta, const float* g_log, float* o,
+                             const rl_delta_recurrent_params* p, int n_tok, long long qk_tok_stride,
+                             long long v_tok_stride, void* stream) {
+    if (n_tok < 0 || n_tok > 64) return fail(RL_ERR_RANGE, "n_tok %d outside [0, 64]", n_tok);
+    if (n_tok == 0) return RL_OK;
+    rl::DeltaDecodeArgs a;
+    DevInfo* d = nullptr;
+    if (int st = delta_decode_args(&a, S, slot_ids, q, k, v, beta, g_log, o, p, n_tok, &d)) return st;
+    if (p->batch == 0) return RL_OK;
+    const long long qk_t = qk_tok_stride ? qk_tok_stride : 1LL * p->n_qk * p->dk;
+    const long long v_t = v_tok_stride ? v_tok_stride : 1LL * p->n_v * p->dv;
+    if ((qk_t | v_t) % 4 || reinterpret_cast<uintptr_t>(S_backup) % 16)
+        return fail(RL_ERR_RANGE, "token strides must be a multiple of 4 floats, S_backup 16-byte aligned");
+    if (S_backup == S) return fail(RL_ERR_RANGE, "S_backup must not alias S");
+    rl::launch_delta_decode_multi(a, S_backup, n_tok, qk_t, v_t, as_stream(stream));
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

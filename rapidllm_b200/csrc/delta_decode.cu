@@ -118,6 +118,116 @@ __global__ void __launch_bounds__(256) delta_decode_kernel(DeltaDecodeArgs a) {
     }
 }
 
+// ---- several consecutive tokens per launch (speculative verify) ----
+// The reference verifies T = 2..12 drafted tokens with one pass that keeps S on chip across the
+// tokens and backs the state up for the rollback (gdn_decode_tn_k, src/kernels/cuda/
+// cuda_engine.cu:5289-5536; gdn_t12.cu:100-220).  Same here: the column slice stays in registers
+// for all n_tok steps (one read and one write of S however many tokens), every step's output is
+// written, and the state as it was before the first token goes to S_backup when that is given.
+// Rolling back to k accepted tokens = restore the backup and run k tokens.  Step arithmetic and
+// its order are those of delta_decode_kernel, so n_tok steps here equal n_tok single launches bit
+// for bit.
+__global__ void __launch_bounds__(256) delta_decode_multi_kernel(DeltaDecodeArgs a, float* S_backup, int n_tok,
+                                                                  long long qk_tstride, long long v_tstride) {
+    const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ float sq[kDk], sk[kDk];
+    __shared__ float red[8][kSliceCols];
+    __shared__ float red2[8][kSliceCols];
+
+    int slot = a.slot_ids ? a.slot_ids[b] : b;
+    if (slot < 0 || slot >= a.n_slots) {
+        if (tid == 0) set_err(a.err, DEV_ERR_BAD_SLOT);
+        return;
+    }
+    const int rep = a.n_v / a.n_qk;
+    const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
+    const size_t head_off = (size_t(slot) * a.n_v + h) * (kDk * kDv);
+    float* Sp = a.S + head_off;
+    const int rg = tid >> 3;           // rows 4rg .. 4rg+3
+    const int cg = tid & 7;            // slice columns 4cg .. 4cg+3
+    const int col0 = slice * kSliceCols + cg * 4;
+    float4 s[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        s[r] = *reinterpret_cast<const float4*>(Sp + (4 * rg + r) * kDv + col0);
+        if (S_backup) *reinterpret_cast<float4*>(S_backup + head_off + (4 * rg + r) * kDv + col0) = s[r];
+    }
+    for (int t = 0; t < n_tok; ++t) {
+        if (warp < 2) {
+            const float* src = warp == 0 ? a.q + size_t(b) * a.q_stride + size_t(t) * qk_tstride + size_t(hs) * kDk
+                                         : a.k + size_t(b) * a.k_stride + size_t(t) * qk_tstride + size_t(hs) * kDk;
+            const float4 x = *reinterpret_cast<const float4*>(src + lane * 4);
+            double ss = double(x.x) * x.x + double(x.y) * x.y + double(x.z) * x.z + double(x.w) * x.w;
+            for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+            float inv = 1.f / sqrtf(float(ss) + a.eps_l2);
+            if (warp == 0) inv *= 1.f / sqrtf(float(kDk));
+            float* dst = warp == 0 ? sq : sk;
+            *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(x.x * inv, x.y * inv, x.z * inv, x.w * inv);
+        }
+        const size_t bt = (size_t(b) * n_tok + t) * a.n_v + h;
+        const float g = expf(a.g_log[bt]);
+        const float beta = a.beta[bt];
+        __syncthreads();
+        float kr[4], qr[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            kr[r] = sk[4 * rg + r];
+            qr[r] = sq[4 * rg + r];
+        }
+        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            s[r].x *= g; s[r].y *= g; s[r].z *= g; s[r].w *= g;
+            kv.x += s[r].x * kr[r]; kv.y += s[r].y * kr[r]; kv.z += s[r].z * kr[r]; kv.w += s[r].w * kr[r];
+        }
+#pragma unroll
+        for (int off = 8; off <= 16; off <<= 1) {
+            kv.x += __shfl_xor_sync(0xffffffffu, kv.x, off);
+            kv.y += __shfl_xor_sync(0xffffffffu, kv.y, off);
+            kv.z += __shfl_xor_sync(0xffffffffu, kv.z, off);
+            kv.w += __shfl_xor_sync(0xffffffffu, kv.w, off);
+        }
+        if (lane < 8) *reinterpret_cast<float4*>(&red[warp][lane * 4]) = kv;
+        __syncthreads();
+        float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 x = *reinterpret_cast<const float4*>(&red[w][cg * 4]);
+            tot.x += x.x; tot.y += x.y; tot.z += x.z; tot.w += x.w;
+        }
+        const float4 vv = *reinterpret_cast<const float4*>(a.v + size_t(b) * a.v_stride + size_t(t) * v_tstride +
+                                                           size_t(h) * kDv + col0);
+        const float4 dl = make_float4((vv.x - tot.x) * beta, (vv.y - tot.y) * beta, (vv.z - tot.z) * beta,
+                                      (vv.w - tot.w) * beta);
+        float4 oo = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            s[r].x += kr[r] * dl.x; s[r].y += kr[r] * dl.y; s[r].z += kr[r] * dl.z; s[r].w += kr[r] * dl.w;
+            oo.x += s[r].x * qr[r]; oo.y += s[r].y * qr[r]; oo.z += s[r].z * qr[r]; oo.w += s[r].w * qr[r];
+        }
+#pragma unroll
+        for (int off = 8; off <= 16; off <<= 1) {
+            oo.x += __shfl_xor_sync(0xffffffffu, oo.x, off);
+            oo.y += __shfl_xor_sync(0xffffffffu, oo.y, off);
+            oo.z += __shfl_xor_sync(0xffffffffu, oo.z, off);
+            oo.w += __shfl_xor_sync(0xffffffffu, oo.w, off);
+        }
+        if (lane < 8) *reinterpret_cast<float4*>(&red2[warp][lane * 4]) = oo;
+        __syncthreads();
+        if (tid < kSliceCols) {
+            float x = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) x += red2[w][tid];
+            a.o[bt * kDv + slice * kSliceCols + tid] = x;
+        }
+        // sq, sk, red and red2 are rewritten by the next token only after its first barrier, which
+        // every thread reaches after the reads above
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) *reinterpret_cast<float4*>(Sp + (4 * rg + r) * kDv + col0) = s[r];
+}
+
 // ---- large batches: persistent CTAs streaming whole heads through shared memory with TMA ----
 // One work item = one (sequence, value head): its 64 KiB of S is contiguous in HBM.  A producer
 // thread bulk-loads items into a 3-stage ring; 256 consumer threads decay, reduce S^T k, then
@@ -257,6 +367,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) delta_decode_stream_kernel(
 }
 
 }  // namespace
+
+void launch_delta_decode_multi(const DeltaDecodeArgs& a, float* S_backup, int n_tok, long long qk_tstride,
+                               long long v_tstride, cudaStream_t st) {
+    if (a.batch <= 0 || n_tok <= 0) return;
+    dim3 grid(kSlices, a.n_v, a.batch);
+    delta_decode_multi_kernel<<<grid, 256, 0, st>>>(a, S_backup, n_tok, qk_tstride, v_tstride);
+}
 
 size_t delta_decode_stream_smem_bytes() { return sizeof(StreamSmem) + 128; }
 const void* delta_decode_stream_kernel_ptr() { return reinterpret_cast<const void*>(&delta_decode_stream_kernel); }

@@ -122,6 +122,10 @@ struct DeltaDecodeArgs {
     long long q_stride, k_stride, v_stride;   // floats between sequences
 };
 void launch_delta_decode(const DeltaDecodeArgs& a, int sms, cudaStream_t st);
+// n_tok consecutive tokens per sequence with the state kept on chip; a.beta, a.g_log
+// [batch][n_tok][n_v], a.o [batch][n_tok][n_v][128]; q/k/v token t at + t * tstride floats
+void launch_delta_decode_multi(const DeltaDecodeArgs& a, float* S_backup, int n_tok, long long qk_tstride,
+                               long long v_tstride, cudaStream_t st);
 size_t delta_decode_stream_smem_bytes();
 const void* delta_decode_stream_kernel_ptr();
 

@@ -220,6 +220,27 @@ def delta_recurrent_step(S, q, k, v, beta, g_log, eps_l2=1e-6, slot_ids=None, he
     return o[0] if single else o
 
 
+def delta_recurrent_multi(S, q, k, v, beta, g_log, eps_l2=1e-6, slot_ids=None, head_map=None, backup=None):
+    """n_tok consecutive delta-rule steps per sequence in one pass (speculative verify).
+
+    S [n_slots][n_v][128][128] in place; q,k [batch][n_tok][n_qk][128]; v [batch][n_tok][n_v][128];
+    beta,g_log [batch][n_tok][n_v]; backup (same shape as S) receives the touched heads' state
+    before the first token.  Returns o [batch][n_tok][n_v][128]."""
+    for t, n in ((S, "S"), (q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (g_log, "g_log"), (backup, "backup")):
+        _need(t, torch.float32, n)
+    _need(slot_ids, torch.int32, "slot_ids")
+    n_slots, n_v, dk, dv = S.shape
+    batch, n_tok, n_qk = q.shape[0], q.shape[1], q.shape[2]
+    if head_map is None:
+        head_map = _lib.RL_HEADS_PER_VALUE if n_qk == n_v else _lib.RL_HEADS_GROUPED
+    o = torch.empty(batch, n_tok, n_v, dv, dtype=torch.float32, device=S.device)
+    p = DeltaRecurrentParams(n_v=n_v, dk=dk, dv=dv, eps_l2=eps_l2, batch=batch, n_slots=n_slots,
+                             n_qk=n_qk, head_map=head_map, q_stride=0, k_stride=0, v_stride=0)
+    check(lib().rl_delta_recurrent_multi(_p(S), _p(backup), _p(slot_ids), _p(q), _p(k), _p(v), _p(beta),
+                                         _p(g_log), _p(o), C.byref(p), n_tok, 0, 0, _stream()))
+    return o
+
+
 def delta_chunk_prefill(S, q, k, v, beta, g_log, eps_l2=1e-6, head_map=None, workspace=None):
     """T delta-rule steps of one sequence in chunked (WY) form: the result of T calls of
     ops::delta_recurrent_step.  S [n_v][128][128] fp32 in place; q,k [T][n_qk][128];

@@ -73,6 +73,39 @@ def test_chunks_over_an_existing_cache(oracle):
     assert rel_l2(od[0].cpu().numpy(), o[-1]) < ATTN_REL_L2
 
 
+@pytest.mark.parametrize("n_draft", [2, 4, 12])
+def test_speculative_verify_rows_over_a_cache(oracle, n_draft):
+    """The verify pass of speculative decode (Engine::spec_verify, cuda_engine.h:69-77): a handful
+    of drafted tokens at positions pos0 .. pos0 + T - 1 attend causally over the cache and one
+    another; rejected tokens are simply overwritten by the next append at the rolled-back position."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(50 + n_draft)
+    pos0 = 1000 - n_draft // 2                   # straddles a page boundary for the larger drafts
+    T = pos0 + n_draft
+    q, k, v, gate = _inputs(gen, T)
+    n_pages = 20
+    table = torch.randperm(n_pages, generator=gen)[:17].int().cuda()
+    kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+    ops.kv_append(kp, vp, table, k[:pos0].half().cuda(), v[:pos0].half().cuda(), pos0=0)
+    o = ops.attn_prefill(q[pos0:].cuda(), kp, vp, table, pos0, k[pos0:].cuda(), v[pos0:].cuda(), gate[pos0:].cuda())
+    _lib.check_device()
+    ref = oracle.attn_prefill_rows(q[pos0:].float().numpy(), k.float().numpy(), v.float().numpy(), np.arange(pos0, T))
+    ref = oracle.sigmoid_gate(ref, gate[pos0:].numpy())
+    _check(o, ref, "verify %d" % n_draft)
+    # accept only the first token: the next decode step appends at pos0 + 1 and must not see the
+    # rejected rows
+    k_new = torch.randn(1, N_KV, HD, generator=gen)
+    v_new = torch.randn(1, N_KV, HD, generator=gen)
+    ops.kv_append(kp, vp, table, k_new.half().cuda(), v_new.half().cuda(), pos0=pos0 + 1)
+    lens = torch.tensor([pos0 + 2], dtype=torch.int32, device="cuda")
+    qd = torch.randn(1, N_Q, HD, generator=gen)
+    od = ops.attn_decode(qd.cuda(), kp, vp, table.unsqueeze(0), lens, None)
+    kk = torch.cat([k[:pos0 + 1].float().half().float(), k_new.half().float()]).numpy()
+    vv = torch.cat([v[:pos0 + 1].float().half().float(), v_new.half().float()]).numpy()
+    ref_d = oracle.attn_decode(qd[0].numpy(), kk, vv)
+    assert rel_l2(od[0].cpu().numpy(), ref_d) <= ATTN_REL_L2
+
+
 def test_config3_8192_tokens_sampled_rows(oracle):
     """8192-token prefill in 1024-row chunks; a strided sample of rows against the oracle."""
     from rapidllm_b200 import _lib, ops

@@ -176,3 +176,54 @@ def test_large_batch_streaming_path(oracle):
     assert rel_l2(S.cpu().numpy(), Sr) < 1e-6
     untouched = [s for s in range(n_slots) if s not in slots.tolist()]
     assert np.array_equal(S[untouched].cpu().numpy(), S0[untouched].numpy())
+
+
+@pytest.mark.parametrize("n_tok", [1, 2, 4, 12])
+def test_multi_token_step_equals_single_steps_and_rolls_back(oracle, n_tok):
+    """The speculative-verify form: n_tok tokens in one pass with the state on chip == n_tok
+    single launches bit for bit; the backup holds the state before the first token, so restoring
+    it and running k tokens gives the state after k accepted tokens."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(40 + n_tok)
+    B, n_slots = 2, 3
+    S0 = torch.randn(n_slots, 48, 128, 128, generator=gen) * 0.02
+    slots = torch.tensor([2, 0], dtype=torch.int32)
+    q = torch.randn(B, n_tok, 16, 128, generator=gen)
+    k = torch.randn(B, n_tok, 16, 128, generator=gen)
+    v = torch.randn(B, n_tok, 48, 128, generator=gen)
+    beta = torch.sigmoid(torch.randn(B, n_tok, 48, generator=gen))
+    g = -torch.nn.functional.softplus(torch.randn(B, n_tok, 48, generator=gen))
+    dev = [x.cuda() for x in (q, k, v, beta, g)]
+    S_multi = S0.clone().cuda()
+    backup = torch.full_like(S_multi, float("nan"))
+    o_multi = ops.delta_recurrent_multi(S_multi, *dev, slot_ids=slots.cuda(), backup=backup)
+    _lib.check_device()
+    S_single = S0.clone().cuda()
+    for t in range(n_tok):
+        o_t = ops.delta_recurrent_step(S_single, dev[0][:, t].contiguous(), dev[1][:, t].contiguous(),
+                                       dev[2][:, t].contiguous(), dev[3][:, t].contiguous(),
+                                       dev[4][:, t].contiguous(), slot_ids=slots.cuda())
+        assert torch.equal(o_t, o_multi[:, t])
+    assert torch.equal(S_single, S_multi)
+    # backup: the touched slots as they were, the untouched slot never written
+    assert torch.equal(backup[2].cpu(), S0[2]) and torch.equal(backup[0].cpu(), S0[0])
+    assert torch.isnan(backup[1]).all()
+    # oracle for sequence 0 (slot 2), first and last token
+    Sr = S0[2].numpy().copy()
+    for t in range(n_tok):
+        ref = oracle.delta_step(Sr, oracle.repeat_heads(q[0, t].numpy(), 48), oracle.repeat_heads(k[0, t].numpy(), 48),
+                                v[0, t].numpy(), beta[0, t].numpy(), g[0, t].numpy())
+        assert np.abs(o_multi[0, t].cpu().numpy() - ref).max() < 1e-4
+    assert rel_l2(S_multi[2].cpu().numpy(), Sr) < 1e-6
+    # roll back to k accepted tokens
+    if n_tok >= 2:
+        kacc = n_tok // 2
+        S_multi[2].copy_(backup[2])
+        S_multi[0].copy_(backup[0])
+        ops.delta_recurrent_multi(S_multi, *[x[:, :kacc].contiguous() for x in dev], slot_ids=slots.cuda())
+        S_ref = S0.clone().cuda()
+        for t in range(kacc):
+            ops.delta_recurrent_step(S_ref, dev[0][:, t].contiguous(), dev[1][:, t].contiguous(),
+                                     dev[2][:, t].contiguous(), dev[3][:, t].contiguous(),
+                                     dev[4][:, t].contiguous(), slot_ids=slots.cuda())
+        assert torch.equal(S_ref, S_multi)
