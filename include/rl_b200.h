@@ -406,7 +406,9 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream);
  * default: the first step with a given io (same pointers and batch) runs as plain launches,
  * the second is captured into a CUDA graph, later ones replay it.  Positions, page table and
  * slot ids are read from device memory at run time, so the caller may advance them between
- * steps; a different io re-captures.  Disabled while rl_stack_set_timing is on. */
+ * steps; a different io re-captures.  rl_stack_decode_host does the same with its copies in and
+ * out included (pinned host buffers; with pageable ones it stays on plain launches).  Disabled
+ * while rl_stack_set_timing is on. */
 int rl_stack_set_graph(rl_cache* c, int enable);
 
 /* The same step for a caller that keeps its tensors in HOST memory (pinned for

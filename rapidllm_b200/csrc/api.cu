@@ -224,6 +224,13 @@ struct rl_cache {
     rl_stack_io gkey;               // io of the captured graph / of the last eager step
     int gkey_seen = 0;              // 0 none, 1 ran eagerly once, 2 captured
     cudaStream_t s_cap = nullptr;
+    // the same for rl_stack_decode_host: copies in, layers and copies out as one graph over the
+    // three internal streams (needs pinned host buffers; pageable ones cannot be captured)
+    cudaGraphExec_t hexec = nullptr;
+    rl_stack_io hkey;
+    int hkey_seen = 0;
+    bool host_graph_failed = false;
+    cudaEvent_t ev_fork = nullptr, ev_join_a = nullptr, ev_join_b = nullptr;
     rl_attn_decode_params attn_params(int batch) const {
         rl_attn_decode_params p;
         std::memset(&p, 0, sizeof p);
@@ -918,6 +925,9 @@ void rl_cache_destroy(rl_cache* c) {
     for (cudaEvent_t e : c->ev_out) cudaEventDestroy(e);
     for (cudaEvent_t e : c->tev) cudaEventDestroy(e);
     if (c->gexec) cudaGraphExecDestroy(c->gexec);
+    if (c->hexec) cudaGraphExecDestroy(c->hexec);
+    for (cudaEvent_t e : {c->ev_fork, c->ev_join_a, c->ev_join_b})
+        if (e) cudaEventDestroy(e);
     if (c->s_cap) cudaStreamDestroy(c->s_cap);
     if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
     if (c->s_run) cudaStreamDestroy(c->s_run);
@@ -985,6 +995,15 @@ int rl_stack_timing(rl_cache* c, float* ms) {
 
 int rl_stack_launches_per_step(const rl_cache* c) { return c ? c->n_attn * 3 + c->n_delta * 2 : 0; }
 
+static bool same_io(const rl_stack_io& k, const rl_stack_io* io) {
+    return k.attn_q == io->attn_q && k.attn_gate == io->attn_gate && k.attn_k == io->attn_k &&
+           k.attn_v == io->attn_v && k.attn_o == io->attn_o && k.delta_qkv == io->delta_qkv &&
+           k.delta_beta == io->delta_beta && k.delta_g == io->delta_g && k.delta_o == io->delta_o &&
+           k.conv_w == io->conv_w && k.page_table == io->page_table && k.pos == io->pos &&
+           k.slot_ids == io->slot_ids && k.batch == io->batch && k.attn_ml == io->attn_ml &&
+           k.no_append == io->no_append;
+}
+
 int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
     if (!c || !io) return fail(RL_ERR_RANGE, "NULL argument");
     if (io->batch < 0 || io->batch > c->cfg.max_batch)
@@ -995,13 +1014,7 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
         (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
     if (!c->graph_enabled || c->timing) return stack_decode_layers(c, io, as_stream(stream), false);
-    const rl_stack_io& k = c->gkey;
-    const bool same = c->gkey_seen > 0 && k.attn_q == io->attn_q && k.attn_gate == io->attn_gate &&
-                      k.attn_k == io->attn_k && k.attn_v == io->attn_v && k.attn_o == io->attn_o &&
-                      k.delta_qkv == io->delta_qkv && k.delta_beta == io->delta_beta && k.delta_g == io->delta_g &&
-                      k.delta_o == io->delta_o && k.conv_w == io->conv_w && k.page_table == io->page_table &&
-                      k.pos == io->pos && k.slot_ids == io->slot_ids && k.batch == io->batch &&
-                      k.attn_ml == io->attn_ml && k.no_append == io->no_append;
+    const bool same = c->gkey_seen > 0 && same_io(c->gkey, io);
     if (same && c->gkey_seen == 2) {
         RL_CUDA(cudaGraphLaunch(c->gexec, as_stream(stream)));
         return RL_OK;
@@ -1095,18 +1108,8 @@ int rl_stack_set_conv_w(rl_cache* c, const float* host_conv_w) {
     return RL_OK;
 }
 
-int rl_stack_decode_host(rl_cache* c, const rl_stack_io* h) {
-    if (!c || !h) return fail(RL_ERR_RANGE, "NULL argument");
-    if (h->batch < 0 || h->batch > c->cfg.max_batch)
-        return fail(RL_ERR_RANGE, "batch %d outside [0, max_batch %d]", h->batch, c->cfg.max_batch);
-    if (h->batch == 0) return RL_OK;
-    if ((c->n_attn && (!h->attn_q || !h->attn_k || !h->attn_v || !h->attn_o || !h->page_table || !h->pos)) ||
-        (c->n_delta && (!h->delta_qkv || !h->delta_beta || !h->delta_g || !h->delta_o)))
-        return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
-    if (h->attn_ml || h->no_append)
-        return fail(RL_ERR_UNSUPPORTED, "split-KV partials are offered by rl_stack_decode (device pointers) only");
-    if (c->n_delta && !c->d_conv_w) return fail(RL_ERR_RANGE, "call rl_stack_set_conv_w first");
-    if (int st = ensure_staging(c)) return st;
+// everything rl_stack_decode_host enqueues (copies in, layers, copies out), without waiting
+static int host_step_enqueue(rl_cache* c, const rl_stack_io* h) {
     const rl_cache_config& f = c->cfg;
     const size_t B = h->batch;
     const size_t q_sz = B * f.n_q * f.head_dim, kv_sz = B * f.n_kv * f.head_dim;
@@ -1158,6 +1161,70 @@ int rl_stack_decode_host(rl_cache* c, const rl_stack_io* h) {
             ++di;
         }
     }
+    return RL_OK;
+}
+
+int rl_stack_decode_host(rl_cache* c, const rl_stack_io* h) {
+    if (!c || !h) return fail(RL_ERR_RANGE, "NULL argument");
+    if (h->batch < 0 || h->batch > c->cfg.max_batch)
+        return fail(RL_ERR_RANGE, "batch %d outside [0, max_batch %d]", h->batch, c->cfg.max_batch);
+    if (h->batch == 0) return RL_OK;
+    if ((c->n_attn && (!h->attn_q || !h->attn_k || !h->attn_v || !h->attn_o || !h->page_table || !h->pos)) ||
+        (c->n_delta && (!h->delta_qkv || !h->delta_beta || !h->delta_g || !h->delta_o)))
+        return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    if (h->attn_ml || h->no_append)
+        return fail(RL_ERR_UNSUPPORTED, "split-KV partials are offered by rl_stack_decode (device pointers) only");
+    if (c->n_delta && !c->d_conv_w) return fail(RL_ERR_RANGE, "call rl_stack_set_conv_w first");
+    if (int st = ensure_staging(c)) return st;
+    if (c->graph_enabled && !c->timing && !c->host_graph_failed) {
+        const bool same = c->hkey_seen > 0 && same_io(c->hkey, h);
+        if (same && c->hkey_seen == 2) {
+            RL_CUDA(cudaGraphLaunch(c->hexec, c->s_run));
+            RL_CUDA(cudaStreamSynchronize(c->s_run));
+            return RL_OK;
+        }
+        if (!same) {
+            if (c->hexec) {
+                cudaGraphExecDestroy(c->hexec);
+                c->hexec = nullptr;
+            }
+            c->hkey = *h;
+            c->hkey_seen = 1;                     // this call runs as plain launches
+        } else {
+            // second call with the same host buffers: capture the three streams as one graph
+            if (!c->ev_fork) {
+                RL_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+                RL_CUDA(cudaEventCreateWithFlags(&c->ev_join_a, cudaEventDisableTiming));
+                RL_CUDA(cudaEventCreateWithFlags(&c->ev_join_b, cudaEventDisableTiming));
+            }
+            cudaGraph_t graph = nullptr;
+            bool ok = cudaStreamBeginCapture(c->s_run, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+            if (ok) {
+                ok = cudaEventRecord(c->ev_fork, c->s_run) == cudaSuccess &&
+                     cudaStreamWaitEvent(c->s_h2d, c->ev_fork, 0) == cudaSuccess &&
+                     cudaStreamWaitEvent(c->s_d2h, c->ev_fork, 0) == cudaSuccess;
+                ok = ok && host_step_enqueue(c, h) == RL_OK;
+                ok = ok && cudaEventRecord(c->ev_join_a, c->s_h2d) == cudaSuccess &&
+                     cudaStreamWaitEvent(c->s_run, c->ev_join_a, 0) == cudaSuccess &&
+                     cudaEventRecord(c->ev_join_b, c->s_d2h) == cudaSuccess &&
+                     cudaStreamWaitEvent(c->s_run, c->ev_join_b, 0) == cudaSuccess;
+                const cudaError_t ce = cudaStreamEndCapture(c->s_run, &graph);
+                ok = ok && ce == cudaSuccess && graph &&
+                     cudaGraphInstantiate(&c->hexec, graph, 0) == cudaSuccess;
+                if (graph) cudaGraphDestroy(graph);
+            }
+            cudaGetLastError();
+            if (ok) {
+                c->hkey_seen = 2;
+                RL_CUDA(cudaGraphLaunch(c->hexec, c->s_run));
+                RL_CUDA(cudaStreamSynchronize(c->s_run));
+                return RL_OK;
+            }
+            c->hexec = nullptr;
+            c->host_graph_failed = true;          // e.g. pageable host memory: stay on plain launches
+        }
+    }
+    if (int st = host_step_enqueue(c, h)) return st;
     RL_CUDA(cudaStreamSynchronize(c->s_d2h));
     RL_CUDA(cudaStreamSynchronize(c->s_run));
     return RL_OK;

@@ -192,3 +192,46 @@ def test_split_kv_partials_merge_to_the_unsplit_step():
     got = got.reshape(want.shape)
     assert (got - want).abs().max().item() <= 1e-5
     assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) <= 1e-5
+
+
+def test_host_entry_graph_replay_matches_plain_launches():
+    """rl_stack_decode_host replays copies in + layers + copies out as one graph from the third
+    call with the same pinned buffers; contents and positions change between calls."""
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    types = QWEN35_LAYER_TYPES
+    B, n_slots, max_pages, n_pages = 2, 2, 3, 6
+    lens = [61, 120]
+    outs = []
+    for graph in (True, False):
+        gen = torch.Generator().manual_seed(12)
+        cache = HybridCache(types, n_pages=n_pages, n_slots=n_slots, max_batch=B, max_pages_per_seq=max_pages)
+        cache.set_graph(graph)
+        for a in range(cache.n_attn):
+            cache.k_pool(a).copy_(torch.randn(cache.k_pool(a).shape, generator=gen).half())
+            cache.v_pool(a).copy_(torch.randn(cache.v_pool(a).shape, generator=gen).half())
+        for d in range(cache.n_delta):
+            cache.state(d).copy_(torch.randn(cache.state(d).shape, generator=gen) * 0.02)
+            cache.conv(d).copy_(torch.randn(cache.conv(d).shape, generator=gen))
+        t = _inputs(cache, B, gen, lens)
+        t["page_table"] = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
+        cache.set_conv_w(t["conv_w"])
+        host = {n: x.pin_memory() for n, x in t.items() if n != "conv_w"}
+        steps = []
+        for step in range(5):
+            if step:
+                fresh = _inputs(cache, B, gen, lens)
+                for n in ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv", "delta_beta", "delta_g"):
+                    host[n].copy_(fresh[n])
+                host["pos"] += 1
+            cache.decode_host(host, B)
+            _lib.check_device()
+            steps.append((host["attn_o"].clone(), host["delta_o"].clone()))
+        final = [cache.state(d).cpu().clone() for d in range(cache.n_delta)]
+        final += [cache.k_pool(a).cpu().clone() for a in range(cache.n_attn)]
+        outs.append((steps, final))
+        cache.close()
+    for (ao, do), (ao2, do2) in zip(outs[0][0], outs[1][0]):
+        assert torch.equal(ao, ao2) and torch.equal(do, do2)
+    for x, y in zip(outs[0][1], outs[1][1]):
+        assert torch.equal(x, y)
