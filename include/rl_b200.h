@@ -352,6 +352,39 @@ typedef struct rl_cache_config {
     int max_batch, max_pages_per_seq, max_seq_len;
 } rl_cache_config;
 
+/* Memory plan for a cache: PlannerInput / PlannerResult / plan_memory
+ * (include/rapidllm/runtime/planner.h:11-33, src/runtime/planner.cpp:28-44) plus the engine's
+ * KV-type policy (RAPIDLLM_KV_TQ / automatic switch to the compact cache for long contexts,
+ * src/kernels/cuda/cuda_engine.cu:20106-20118), restated for paged pools: pages come out of
+ * what is left of `available_bytes` after weights, DeltaNet state, conv windows and padding. */
+#define RL_KV_POLICY_AUTO 0      /* F16 when it fits, else the compact cache (RAPIDLLM_KV_TQ unset) */
+#define RL_KV_POLICY_F16 1       /* RAPIDLLM_KV_TQ=0 */
+#define RL_KV_POLICY_COMPACT 2   /* RAPIDLLM_KV_TQ=1 */
+typedef struct rl_plan_input {
+    unsigned long long weight_bytes;     /* what else must stay resident */
+    unsigned long long available_bytes;  /* budget; 0 = do not check (plan_memory's convention) */
+    unsigned long long pad_bytes;        /* head-room; the reference uses 64 MiB */
+    int ctx;                     /* tokens per sequence asked for */
+    int max_batch;               /* sequences (KV page sets and DeltaNet slots) */
+    int n_attn_layers, n_kv, head_dim;
+    int n_delta_layers, n_v, dk, dv, conv_dim, conv_k;
+    int page_tokens;             /* 64 */
+    int kv_policy;               /* RL_KV_POLICY_* */
+    int allow_shrink;            /* != 0: reduce ctx to what fits instead of refusing */
+} rl_plan_input;
+typedef struct rl_plan_result {
+    int ok;                      /* 0: does not fit (message says why), like PlannerResult.ok */
+    int kv_dtype;                /* RL_KV_F16 or RL_KV_Q8K_TQ3V */
+    int ctx;                     /* granted tokens per sequence (a multiple of page_tokens when shrunk) */
+    int max_pages_per_seq;
+    int n_pages;                 /* per attention layer pool: max_batch * max_pages_per_seq */
+    unsigned long long kv_bytes, state_bytes, need_bytes;
+    char message[160];
+} rl_plan_result;
+/* Host-only arithmetic (no device call); returns RL_OK when the plan was computed (see
+ * result->ok for whether it fits) and RL_ERR_RANGE for nonsensical input. */
+int rl_plan_cache(const rl_plan_input* in, rl_plan_result* out);
+
 /* DualCache::DualCache (src/runtime/dual_cache.cpp:7-41): allocates and zeroes. */
 int rl_cache_create(const rl_cache_config* cfg, rl_cache** out);
 void rl_cache_destroy(rl_cache* c);

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, "librl_b200.so")
 
 RL_OK = 0
 RL_KV_F16, RL_KV_Q8K_TQ3V = 0, 1
+RL_KV_POLICY_AUTO, RL_KV_POLICY_F16, RL_KV_POLICY_COMPACT = 0, 1, 2
 RL_LAYER_LINEAR_ATTENTION, RL_LAYER_FULL_ATTENTION = 0, 1
 RL_HEADS_PER_VALUE, RL_HEADS_GROUPED, RL_HEADS_TILED = 0, 1, 2
 STATUS_NAMES = ["RL_OK", "RL_ERR_IO", "RL_ERR_FORMAT", "RL_ERR_NOMEM", "RL_ERR_UNSUPPORTED",
@@ -64,6 +65,18 @@ class AttnQkPrepareParams(C.Structure):
         ("theta", C.c_float), ("eps", C.c_float)]
 
 
+class PlanInput(C.Structure):
+    _fields_ = [("weight_bytes", C.c_ulonglong), ("available_bytes", C.c_ulonglong), ("pad_bytes", C.c_ulonglong)] + [
+        (n, C.c_int) for n in ("ctx", "max_batch", "n_attn_layers", "n_kv", "head_dim", "n_delta_layers", "n_v",
+                               "dk", "dv", "conv_dim", "conv_k", "page_tokens", "kv_policy", "allow_shrink")]
+
+
+class PlanResult(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("ok", "kv_dtype", "ctx", "max_pages_per_seq", "n_pages")] + [
+        ("kv_bytes", C.c_ulonglong), ("state_bytes", C.c_ulonglong), ("need_bytes", C.c_ulonglong),
+        ("message", C.c_char * 160)]
+
+
 class CacheConfig(C.Structure):
     _fields_ = [("n_layers", C.c_int), ("layer_types", C.POINTER(C.c_int)),
                 ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int), ("kv_dtype", C.c_int),
@@ -109,6 +122,7 @@ SYMBOLS = {
     "rl_delta_chunk_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(DeltaChunkParams), _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),
     "rl_conv1d_causal": (_i, [_vp, _vp, _vp, _vp, _i, C.POINTER(Conv1dParams), _i, _vp]),
+    "rl_plan_cache": (_i, [C.POINTER(PlanInput), C.POINTER(PlanResult)]),
     "rl_attn_qk_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnQkPrepareParams), _vp]),
     "rl_gated_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, _vp]),
     "rl_delta_gates": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),

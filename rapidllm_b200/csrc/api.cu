@@ -868,6 +868,52 @@ int rl_conv1d_causal(const float* x, const float* w, float* y, float* state_io, 
 }
 
 // ------------------------------------------------------------------------------------
+int rl_plan_cache(const rl_plan_input* in, rl_plan_result* out) {
+    if (!in || !out) return fail(RL_ERR_RANGE, "NULL argument");
+    if (in->ctx <= 0 || in->max_batch <= 0 || in->page_tokens <= 0 || in->n_attn_layers < 0 || in->n_delta_layers < 0 ||
+        in->n_kv < 0 || in->head_dim < 0 || in->kv_policy < RL_KV_POLICY_AUTO || in->kv_policy > RL_KV_POLICY_COMPACT)
+        return fail(RL_ERR_RANGE, "ctx %d max_batch %d page_tokens %d kv_policy %d", in->ctx, in->max_batch,
+                    in->page_tokens, in->kv_policy);
+    std::memset(out, 0, sizeof *out);
+    typedef unsigned long long u64;
+    // bytes of one page over all attention layers (K and V)
+    const u64 f16_page = u64(in->n_attn_layers) * in->n_kv * in->page_tokens * in->head_dim * 2 * 2;
+    const u64 compact_page = u64(in->n_attn_layers) * in->n_kv * rl_kv_compact_page_bytes();
+    out->state_bytes = u64(in->max_batch) * in->n_delta_layers *
+                       (u64(in->n_v) * in->dk * in->dv * 4 + u64(in->conv_dim) * in->conv_k * 4);
+    const u64 fixed = in->weight_bytes + out->state_bytes + in->pad_bytes;
+    auto pages_for = [&](int ctx) { return u64((ctx + in->page_tokens - 1) / in->page_tokens); };
+    auto fits = [&](u64 page_bytes, int ctx) {
+        return !in->available_bytes || fixed + page_bytes * pages_for(ctx) * in->max_batch <= in->available_bytes;
+    };
+    int dtype = in->kv_policy == RL_KV_POLICY_COMPACT ? RL_KV_Q8K_TQ3V : RL_KV_F16;
+    if (in->kv_policy == RL_KV_POLICY_AUTO && !fits(f16_page, in->ctx)) dtype = RL_KV_Q8K_TQ3V;
+    if (dtype == RL_KV_Q8K_TQ3V && in->head_dim != rl::kHeadDim && in->n_attn_layers > 0) {
+        if (in->kv_policy == RL_KV_POLICY_COMPACT)
+            return fail(RL_ERR_UNSUPPORTED, "the compact cache needs head_dim 256, got %d", in->head_dim);
+        dtype = RL_KV_F16;
+    }
+    const u64 page_bytes = dtype == RL_KV_F16 ? f16_page : compact_page;
+    int ctx = in->ctx;
+    if (!fits(page_bytes, ctx) && in->allow_shrink && in->available_bytes > fixed && page_bytes > 0) {
+        const u64 pages = (in->available_bytes - fixed) / (page_bytes * in->max_batch);
+        ctx = int(std::min<u64>(pages * in->page_tokens, u64(in->ctx)));
+    }
+    out->kv_dtype = dtype;
+    out->ctx = ctx;
+    out->max_pages_per_seq = int(pages_for(std::max(ctx, 1)));
+    out->n_pages = out->max_pages_per_seq * in->max_batch;
+    out->kv_bytes = page_bytes * u64(out->n_pages);
+    out->need_bytes = fixed + out->kv_bytes;
+    out->ok = ctx > 0 && (!in->available_bytes || out->need_bytes <= in->available_bytes);
+    if (out->ok)
+        std::snprintf(out->message, sizeof out->message, ctx == in->ctx ? "ok" : "ok: ctx reduced from %d to %d", in->ctx, ctx);
+    else
+        std::snprintf(out->message, sizeof out->message, "OOM: need %llu bytes, available %llu (ctx=%d)",
+                      out->need_bytes, in->available_bytes, in->ctx);
+    return RL_OK;
+}
+
 int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
     if (!cfg || !out) return fail(RL_ERR_RANGE, "NULL argument");
     *out = nullptr;
