@@ -214,6 +214,15 @@ int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* p
 int rl_kv_compact_gather(const void* pool, const int32_t* page_table_row, void* k_q, void* k_sc,
                          void* v_codes, void* v_sc, int n_tok, int n_kv, int n_pages, int wht_len,
                          void* stream);
+/* Dequantise tokens [src_pos0, src_pos0 + n_tok) of one sequence of the compact cache into
+ * paged F16 pools at positions dst_pos0 ..: the rebuild of the F16 compute window the
+ * reference does for prefill chunks and verify rows over a compact cache (dequant_k_q8_k /
+ * dequant_v_tq3_256, cuda_engine.cu:8286-8314, 293-299).  Afterwards rl_attn_prefill /
+ * rl_attn_decode run over the F16 pools.  Tables are one sequence's rows. */
+int rl_kv_compact_to_f16(const void* pool, const int32_t* src_table_row, int src_pos0, int n_src_pages,
+                         void* k_pool, void* v_pool, const int32_t* dst_table_row, int dst_pos0,
+                         int n_dst_pages, int n_tok, int n_kv, int wht_len, const float* tq_signs,
+                         void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Gated DeltaNet                                                             */

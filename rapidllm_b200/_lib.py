@@ -112,6 +112,7 @@ SYMBOLS = {
     "rl_kv_compact_page_bytes": (_sz, []),
     "rl_kv_compact_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(KvAppendParams), _vp]),
     "rl_kv_compact_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "rl_kv_compact_to_f16": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "rl_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(KvAppendParams), _vp]),
     "rl_kv_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_delta_recurrent": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

@@ -633,6 +633,23 @@ int rl_kv_compact_gather(const void* pool, const int32_t* page_table_row, void* 
     return RL_OK;
 }
 
+int rl_kv_compact_to_f16(const void* pool, const int32_t* src_table_row, int src_pos0, int n_src_pages, void* k_pool,
+                         void* v_pool, const int32_t* dst_table_row, int dst_pos0, int n_dst_pages, int n_tok,
+                         int n_kv, int wht_len, const float* tq_signs, void* stream) {
+    if (wht_len != 128 && wht_len != 256) return fail(RL_ERR_UNSUPPORTED, "wht_len %d: only 128 or 256", wht_len);
+    if (n_tok < 0 || n_kv <= 0 || n_kv > 65535 || src_pos0 < 0 || dst_pos0 < 0 || n_src_pages <= 0 || n_dst_pages <= 0)
+        return fail(RL_ERR_RANGE, "n_tok %d n_kv %d src_pos0 %d dst_pos0 %d", n_tok, n_kv, src_pos0, dst_pos0);
+    if (n_tok == 0) return RL_OK;
+    if (!pool || !src_table_row || !k_pool || !v_pool || !dst_table_row) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::kv_compact_to_f16_kernel<<<dim3(n_tok, n_kv), 256, 0, as_stream(stream)>>>(
+        static_cast<const unsigned char*>(pool), src_table_row, src_pos0, n_src_pages, static_cast<__half*>(k_pool),
+        static_cast<__half*>(v_pool), dst_table_row, dst_pos0, n_dst_pages, n_kv, wht_len, tq_signs, d->err_ptr);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
 // shared by the one-token and the several-token entry points; n_tok scales the dense strides
 static int delta_decode_args(rl::DeltaDecodeArgs* out, float* S, const int32_t* slot_ids, const float* q,
                              const float* k, const float* v, const float* beta, const float* g_log, float* o,

@@ -104,6 +104,10 @@ __global__ void kv_compact_write_kernel(KvCompactWriteArgs a);
 __global__ void kv_compact_gather_kernel(const unsigned char* pool, const int32_t* table, signed char* k_q,
                                          __half* k_sc, unsigned char* v_codes, __half* v_sc, int n_tok,
                                          int n_kv, int n_pages, int wht_len, int* err);
+__global__ void kv_compact_to_f16_kernel(const unsigned char* pool, const int32_t* src_table, int src_pos0,
+                                         int n_src_pages, __half* k_pool, __half* v_pool, const int32_t* dst_table,
+                                         int dst_pos0, int n_dst_pages, int n_kv, int wht_len, const float* signs,
+                                         int* err);
 
 // ---- Gated DeltaNet decode step ----------------------------------------------------
 struct DeltaDecodeArgs {

@@ -204,4 +204,62 @@ kv_compact_gather_kernel(const unsigned char* pool, const int32_t* table, signed
     }
 }
 
+// Dequantise tokens [src_pos0, src_pos0 + n_tok) of one sequence into paged F16 pools at
+// positions dst_pos0 .. : what the reference does when it rebuilds its F16 compute window from
+// the compact cache (dequant_k_q8_k / dequant_v_tq3_256, src/kernels/cuda/cuda_engine.cu:
+// 8286-8314, 293-299) so that prefill chunks and verify rows can attend over it.
+// K = half2float(scale) * int8; V = inverse transform of centroid[code] * half2float(scale)
+// (the orthonormal Walsh-Hadamard transform is its own inverse), times the signs for the
+// 256-point layout; both rounded to fp16 (RNE) into the tile-swizzled page format.
+// grid (n_tok, n_kv), 256 threads: thread = dim.
+__global__ void __launch_bounds__(256)
+kv_compact_to_f16_kernel(const unsigned char* pool, const int32_t* src_table, int src_pos0, int n_src_pages,
+                         __half* k_pool, __half* v_pool, const int32_t* dst_table, int dst_pos0, int n_dst_pages,
+                         int n_kv, int wht_len, const float* signs, int* err) {
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    __shared__ float xs[256];
+    const int sp = src_pos0 + t, dp = dst_pos0 + t;
+    const int spage = src_table[sp / kPageTokens], dpage = dst_table[dp / kPageTokens];
+    if (spage < 0 || spage >= n_src_pages || dpage < 0 || dpage >= n_dst_pages) {
+        if (tid == 0) set_err(err, DEV_ERR_BAD_PAGE);
+        return;
+    }
+    const int row64 = sp % kPageTokens, half = row64 >> 5, row = row64 & 31;
+    const unsigned char* rec = pool + ((size_t(spage) * n_kv + h) * 2 + half) * kCompactRecordBytes;
+    const size_t dst = (size_t(dpage) * n_kv + h) * kv_slice_elems() + kv_slice_offset(dp % kPageTokens, tid);
+    // K
+    {
+        const int chunk = (tid >> 4) ^ ((row & 1) << 2);
+        const float q = float(reinterpret_cast<const signed char*>(rec)[row * 256 + chunk * 16 + (tid & 15)]);
+        const float s = __half2float(reinterpret_cast<const __half*>(rec + kCompactKScaleOff)[row]);
+        k_pool[dst] = __float2half_rn(s * q);
+    }
+    // V
+    const int d = tid;
+    const int j = d >> 6, g = (d >> 3) & 7, i = (d >> 1) & 3, odd_dim = d & 1, e = row & 1;
+    const unsigned char* p = rec + compact_v_offset(row, g, j);
+    unsigned long long w48 = 0;
+    for (int x = 0; x < 6; ++x) w48 |= (unsigned long long)p[x] << (8 * x);
+    const int idx = int((w48 >> (12 * i + 6 * odd_dim + 3 * e)) & 7ull);
+    const float sc = __half2float(reinterpret_cast<const __half*>(rec + kCompactVScaleOff)[row * 2 + d / wht_len]);
+    float v = tq3_cent(idx) * sc;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, s);
+        v = ((lane & s) == 0) ? (v + o) : (o - v);
+    }
+    xs[tid] = v;
+    __syncthreads();
+    for (int s = 32; s < wht_len; s <<= 1) {
+        const int jj = tid ^ s;
+        const float x0 = xs[tid], x1 = xs[jj];
+        __syncthreads();
+        xs[tid] = (tid < jj) ? (x0 + x1) : (x1 - x0);
+        __syncthreads();
+    }
+    v = xs[tid] * (wht_len == 128 ? 0.08838834764831845f : 0.0625f);
+    if (wht_len == 256 && signs) v *= signs[tid];
+    v_pool[dst] = __float2half_rn(v);
+}
+
 }  // namespace rl

@@ -326,3 +326,15 @@ def delta_gates(a, b, A_log, dt_bias):
     beta, g = torch.empty_like(a), torch.empty_like(a)
     check(lib().rl_delta_gates(_p(a), _p(b), _p(A_log), _p(dt_bias), _p(beta), _p(g), rows, n_v, _stream()))
     return beta, g
+
+
+def kv_compact_to_f16(pool, src_table_row, k_pool, v_pool, dst_table_row, n_tok, src_pos0=0, dst_pos0=0,
+                      wht_len=128, signs=None):
+    """Dequantise n_tok tokens of one sequence of the compact cache into paged F16 pools (the
+    F16 compute window for prefill chunks / verify rows over a compact cache)."""
+    _need(src_table_row, torch.int32, "src_table_row")
+    _need(dst_table_row, torch.int32, "dst_table_row")
+    _need(signs, torch.float32, "signs")
+    check(lib().rl_kv_compact_to_f16(_p(pool), _p(src_table_row), src_pos0, pool.shape[0], _p(k_pool), _p(v_pool),
+                                     _p(dst_table_row), dst_pos0, k_pool.shape[0], n_tok, pool.shape[1], wht_len,
+                                     _p(signs), _stream()))

@@ -122,3 +122,45 @@ def test_compact_partials_merge_across_token_ranges(oracle):
     kd, vd = oracle.compact_dequant(*oracle.compact_store(k.numpy(), v.numpy(), 128), 128)
     ref = oracle.gated_attn_decode(q[0].numpy(), kd, vd, gate[0].numpy())
     assert np.abs(o - ref).max() <= ATTN_MAX_ABS and rel_l2(o, ref) <= ATTN_REL_L2
+
+
+@pytest.mark.parametrize("wht_len,use_signs", [(128, False), (256, True)])
+def test_f16_window_rebuilt_from_compact_cache_and_prefill_over_it(oracle, wht_len, use_signs):
+    """The compact cache persists; a prefill chunk (or verify rows) attends over an F16 window
+    dequantised from it (rl_kv_compact_to_f16), as the reference rebuilds its compute window."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(8)
+    n_old, n_new = 64 * 3 + 21, 40
+    k = torch.randn(n_old, N_KV, HD, generator=gen)
+    v = torch.randn(n_old, N_KV, HD, generator=gen)
+    signs = _signs(gen) if use_signs else None
+    sd = signs.cuda() if use_signs else None
+    table, n_pages = _table([n_old], gen)
+    pool = ops.new_compact_pool(n_pages, N_KV)
+    ops.kv_compact_append(pool, table, k.cuda(), v.cuda(), wht_len, sd, pos0=0)
+    # window: its own F16 pools and page table, rebuilt in two pieces (page-unaligned split)
+    wt, wn = _table([n_old + n_new], gen)
+    kp, vp = ops.new_pool(wn, N_KV), ops.new_pool(wn, N_KV)
+    ops.kv_compact_to_f16(pool, table[0], kp, vp, wt[0], 100, 0, 0, wht_len, sd)
+    ops.kv_compact_to_f16(pool, table[0], kp, vp, wt[0], n_old - 100, 100, 100, wht_len, sd)
+    _lib.check_device()
+    kw = ops.kv_gather(kp, wt[0], n_old).cpu().float().numpy()
+    vw = ops.kv_gather(vp, wt[0], n_old).cpu().float().numpy()
+    sn = None if signs is None else signs.numpy()
+    kd, vd = oracle.compact_dequant(*oracle.compact_store(k.numpy(), v.numpy(), wht_len, sn), wht_len, sn)
+    # fp16 of the oracle's fp32 dequantisation; the transform's summation order may move a value
+    # across an fp16 rounding boundary: allow one fp16 ulp (2^-10 relative, 2^-24 absolute floor)
+    assert np.array_equal(kw, kd.astype(np.float16).astype(np.float32))      # K: one exact product
+    ulp = np.maximum(np.abs(vd) * 2.0 ** -10, 2.0 ** -24)
+    assert (np.abs(vw - vd) <= ulp).all()
+    # a prefill chunk over the rebuilt window == the oracle over the dequantised cache + the new rows
+    q = torch.randn(n_new, N_Q, HD, generator=gen).bfloat16()
+    k2 = torch.randn(n_new, N_KV, HD, generator=gen).bfloat16()
+    v2 = torch.randn(n_new, N_KV, HD, generator=gen).bfloat16()
+    o = ops.attn_prefill(q.cuda(), kp, vp, wt[0], n_old, k2.cuda(), v2.cuda(), None)
+    _lib.check_device()
+    k_all = np.concatenate([kd, k2.float().numpy()])
+    v_all = np.concatenate([vd, v2.float().numpy()])
+    ref = oracle.attn_prefill_rows(q.float().numpy(), k_all, v_all, np.arange(n_old, n_old + n_new))
+    o = o.cpu().numpy()
+    assert np.abs(o - ref).max() <= ATTN_MAX_ABS and rel_l2(o, ref) <= ATTN_REL_L2
