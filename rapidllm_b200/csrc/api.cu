@@ -836,7 +836,7 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     a.n_qk = p->n_qk;
     a.head_map = p->head_map;
     a.eps_l2 = p->eps_l2;
-    rl::delta_chunk_prepare_kernel<<<dim3(n_chunks, p->n_qk), rl::delta_chunk_prepare_threads(),
+    rl::delta_chunk_prepare_kernel<<<dim3(n_chunks, p->n_v), rl::delta_chunk_prepare_threads(),
                                      rl::delta_chunk_prepare_smem_bytes(), as_stream(stream)>>>(a);
     rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(),
                                   as_stream(stream)>>>(a);

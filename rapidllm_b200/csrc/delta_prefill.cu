@@ -17,8 +17,8 @@
 // (the diagonal of P is included because the reference reads o_t from the updated state).
 //
 // Kernel 1 (delta_chunk_prepare_kernel) computes everything that does not depend on S for
-// all (chunk, head) pairs in parallel and writes W, Qg, Kt, V, T, P as fp16 tiles already in
-// the 128-byte-swizzled operand format of the tensor cores, 80 KiB per (chunk, head).
+// all (chunk, value head) pairs in parallel, one CTA each, and writes W, Qg, Kt, V, T, P as fp16
+// tiles already in the 128-byte-swizzled operand format of the tensor cores, 80 KiB per pair.
 // Kernel 2 (delta_chunk_scan_kernel), one CTA per value head, walks the chunks in order.
 // Everything is transposed so that the 128 value dims are the MMA M dimension (TMEM lanes):
 // S^T lives in tensor memory in fp32 for the whole sequence, and its fp16 high and low
@@ -52,12 +52,15 @@ constexpr int kB = 16;                    // block size of the triangular invers
 
 struct PrepSmem {
     float kn[kC][kPad];       // k^
-    float qn[kC][kPad];       // q^
-    float kk[kC][kC + 1];     // k^_t . k^_i   (shared by the value heads of this key head)
+    union {
+        float qn[kC][kPad];   // q^, dead once q^.k^ and the Qg tile are out
+        struct {
+            float m[kC][kC + 1];      // (I + A)^-1
+            float tmp[kC][kC + 1];
+        } inv;
+    } u;
+    float l[kC][kC + 1];      // k^_t . k^_i, then in place A (strictly lower part of I + A)
     float qk[kC][kC + 1];     // q^_t . k^_i
-    float l[kC][kC + 1];      // A (strictly lower part of I + A)
-    float m[kC][kC + 1];      // (I + A)^-1
-    float tmp[kC][kC + 1];
     float G[kC], beta[kC], eg[kC];
 };
 
@@ -65,17 +68,32 @@ struct PrepSmem {
 
 size_t delta_chunk_record_bytes() { return kRecordBytes; }
 
-// grid (n_chunks, n_qk), 256 threads: one CTA per chunk and key/query head; the dot products
-// k^.k^ and q^.k^ are computed once and reused by every value head that maps to this key head.
-__global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(DeltaChunkArgs a) {
+// grid (n_chunks, n_v), 256 threads: one CTA per chunk and value head.  98 KB of shared memory, so
+// two CTAs share an SM and hide each other's barriers; the dot products k^.k^ and q^.k^ are
+// recomputed by the value heads that share a key head (cheap next to the latency they hide).
+__global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
-    const int chunk = blockIdx.x, hs = blockIdx.y;
+    const int chunk = blockIdx.x, h = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = a.head_map == 0 ? 1 : a.n_v / a.n_qk;
+    const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
     const int t0 = chunk * kC;
     const int n_tok = min(kC, a.T - t0);
+    unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
 
+    // ---- cumulative log decay, beta (needed by every tile) ----
+    if (tid < kC) {
+        const bool live = tid < n_tok;
+        s.beta[tid] = live ? a.beta[size_t(t0 + tid) * a.n_v + h] : 0.f;
+        float gl = live ? a.g_log[size_t(t0 + tid) * a.n_v + h] : 0.f;
+        // inclusive scan over 64 values held by two warps
+        for (int off = 1; off < 32; off <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, gl, off);
+            if (lane >= off) gl += o;
+        }
+        s.G[tid] = gl;
+    }
     // ---- l2 norms (double accumulators as ops::l2norm); padded tokens are all zero ----
     for (int t = warp; t < kC; t += kPrepThreads / 32) {
         float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), qx = kx;
@@ -94,10 +112,14 @@ __global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(Delta
         if (t >= n_tok) ki = qi = 0.f;
         s.kn[t][lane * 4 + 0] = kx.x * ki; s.kn[t][lane * 4 + 1] = kx.y * ki;
         s.kn[t][lane * 4 + 2] = kx.z * ki; s.kn[t][lane * 4 + 3] = kx.w * ki;
-        s.qn[t][lane * 4 + 0] = qx.x * qi; s.qn[t][lane * 4 + 1] = qx.y * qi;
-        s.qn[t][lane * 4 + 2] = qx.z * qi; s.qn[t][lane * 4 + 3] = qx.w * qi;
+        s.u.qn[t][lane * 4 + 0] = qx.x * qi; s.u.qn[t][lane * 4 + 1] = qx.y * qi;
+        s.u.qn[t][lane * 4 + 2] = qx.z * qi; s.u.qn[t][lane * 4 + 3] = qx.w * qi;
     }
     __syncthreads();
+    if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
+    __syncthreads();
+    if (tid < kC) s.eg[tid] = expf(s.G[tid]);
+    if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
     // ---- k^.k^ and q^.k^ (lower triangle), 4 x 4 outputs per thread ----
     {
         const int tb = (tid >> 4) * 4, ib = (tid & 15) * 4;
@@ -108,7 +130,7 @@ __global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(Delta
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
                     kt[x] = s.kn[tb + x][d];
-                    qt[x] = s.qn[tb + x][d];
+                    qt[x] = s.u.qn[tb + x][d];
                     ki[x] = s.kn[ib + x][d];
                 }
 #pragma unroll
@@ -124,118 +146,99 @@ __global__ void __launch_bounds__(kPrepThreads) delta_chunk_prepare_kernel(Delta
         for (int x = 0; x < 4; ++x)
 #pragma unroll
             for (int y = 0; y < 4; ++y) {
-                s.kk[tb + x][ib + y] = kk[x][y];
+                s.l[tb + x][ib + y] = kk[x][y];
                 s.qk[tb + x][ib + y] = qk[x][y];
             }
     }
     __syncthreads();
-
-    for (int r = 0; r < rep; ++r) {
-        const int h = a.head_map == 0 ? hs : (a.head_map == 1 ? hs * rep + r : hs + r * a.n_qk);
-        unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
-        // ---- cumulative log decay, beta ----
-        if (tid < kC) {
-            const bool live = tid < n_tok;
-            s.beta[tid] = live ? a.beta[size_t(t0 + tid) * a.n_v + h] : 0.f;
-            float gl = live ? a.g_log[size_t(t0 + tid) * a.n_v + h] : 0.f;
-            // inclusive scan over 64 values held by two warps
-            for (int off = 1; off < 32; off <<= 1) {
-                const float o = __shfl_up_sync(0xffffffffu, gl, off);
-                if (lane >= off) gl += o;
-            }
-            s.G[tid] = gl;
+    // ---- tiles that need q^: Qg; with it Kt and V (64 x 128, fp16, swizzled) ----
+    const float gC = s.G[kC - 1];
+    for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
+        const int t = idx >> 5, d = (idx & 31) * 4;
+        const int o = tile_off(t, d);
+        const float e = s.eg[t];
+        *reinterpret_cast<uint2*>(rec + kOffQg + o) =
+            make_uint2(pack_h2(e * s.u.qn[t][d], e * s.u.qn[t][d + 1]), pack_h2(e * s.u.qn[t][d + 2], e * s.u.qn[t][d + 3]));
+        const float kt = expf(gC - s.G[t]);
+        *reinterpret_cast<uint2*>(rec + kOffKt + o) =
+            make_uint2(pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]), pack_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3]));
+        float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < n_tok) vv = *reinterpret_cast<const float4*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
+        *reinterpret_cast<uint2*>(rec + kOffV + o) = make_uint2(pack_h2(vv.x, vv.y), pack_h2(vv.z, vv.w));
+    }
+    __syncthreads();                                  // q^ is dead from here on: its space becomes m and tmp
+    float (*m)[kC + 1] = s.u.inv.m;
+    float (*tmp)[kC + 1] = s.u.inv.tmp;
+    // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t, in place ----
+    for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
+        const int t = idx >> 6, i = idx & 63;
+        s.l[t][i] = i < t ? s.beta[t] * expf(s.G[t] - s.G[i]) * s.l[t][i] : 0.f;
+        m[t][i] = t == i ? 1.f : 0.f;
+    }
+    __syncthreads();
+    // ---- M = (I + A)^-1, blocked: 16 x 16 diagonal blocks by forward substitution ... ----
+    if (tid < kC) {
+        const int bb = (tid >> 4) * kB, c = tid & 15;           // thread owns column c of block bb
+        for (int t = c + 1; t < kB; ++t) {
+            float acc = 0.f;
+            for (int i = c; i < t; ++i) acc -= s.l[bb + t][bb + i] * m[bb + i][bb + c];
+            m[bb + t][bb + c] = acc;
+        }
+    }
+    __syncthreads();
+    // ... then block row by block row: M_ij = -M_ii (sum_{j<=k<i} A_ik M_kj), j < i
+    for (int bi = 1; bi < kC / kB; ++bi) {
+        for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
+            const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
+            float acc = 0.f;
+            for (int kx = bj * kB; kx < bi * kB; ++kx) acc += s.l[bi * kB + x][kx] * m[kx][bj * kB + y];
+            tmp[bi * kB + x][bj * kB + y] = acc;
         }
         __syncthreads();
-        if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
-        __syncthreads();
-        if (tid < kC) s.eg[tid] = expf(s.G[tid]);
-        if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
-        // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t ----
-        for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
-            const int t = idx >> 6, i = idx & 63;
-            s.l[t][i] = i < t ? s.beta[t] * expf(s.G[t] - s.G[i]) * s.kk[t][i] : 0.f;
-            s.m[t][i] = t == i ? 1.f : 0.f;
+        for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
+            const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
+            float acc = 0.f;
+            for (int kx = 0; kx <= x; ++kx) acc -= m[bi * kB + x][bi * kB + kx] * tmp[bi * kB + kx][bj * kB + y];
+            m[bi * kB + x][bj * kB + y] = acc;
         }
         __syncthreads();
-        // ---- M = (I + A)^-1, blocked: 16 x 16 diagonal blocks by forward substitution ... ----
-        if (tid < kC) {
-            const int bb = (tid >> 4) * kB, c = tid & 15;           // thread owns column c of block bb
-            for (int t = c + 1; t < kB; ++t) {
-                float acc = 0.f;
-                for (int i = c; i < t; ++i) acc -= s.l[bb + t][bb + i] * s.m[bb + i][bb + c];
-                s.m[bb + t][bb + c] = acc;
-            }
-        }
-        __syncthreads();
-        // ... then block row by block row: M_ij = -M_ii (sum_{j<=k<i} A_ik M_kj), j < i
-        for (int bi = 1; bi < kC / kB; ++bi) {
-            for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
-                const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
-                float acc = 0.f;
-                for (int kx = bj * kB; kx < bi * kB; ++kx) acc += s.l[bi * kB + x][kx] * s.m[kx][bj * kB + y];
-                s.tmp[bi * kB + x][bj * kB + y] = acc;
-            }
-            __syncthreads();
-            for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
-                const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
-                float acc = 0.f;
-                for (int kx = 0; kx <= x; ++kx) acc -= s.m[bi * kB + x][bi * kB + kx] * s.tmp[bi * kB + kx][bj * kB + y];
-                s.m[bi * kB + x][bj * kB + y] = acc;
-            }
-            __syncthreads();
-        }
-        // ---- tiles: T = M diag(beta), P (64 x 64); W, Qg, Kt, V (64 x 128), fp16, swizzled ----
-        const float gC = s.G[kC - 1];
-        for (int idx = tid; idx < kC * kC / 2; idx += kPrepThreads) {
-            const int t = idx >> 5, i = (idx & 31) * 2;
-            *reinterpret_cast<uint32_t*>(rec + kOffT + tile_off(t, i)) =
-                pack_h2(s.m[t][i] * s.beta[i], s.m[t][i + 1] * s.beta[i + 1]);
-            const float p0 = i <= t ? expf(s.G[t] - s.G[i]) * s.qk[t][i] : 0.f;
-            const float p1 = i + 1 <= t ? expf(s.G[t] - s.G[i + 1]) * s.qk[t][i + 1] : 0.f;
-            *reinterpret_cast<uint32_t*>(rec + kOffP + tile_off(t, i)) = pack_h2(p0, p1);
-        }
-        // fold beta_i exp(G_i) into M once: tmp[t][i] = M[t][i] beta_i exp(G_i)
-        for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
-            const int t = idx >> 6, i = idx & 63;
-            s.tmp[t][i] = s.m[t][i] * s.beta[i] * s.eg[i];
-        }
-        __syncthreads();
-        // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] (tmp is zero above the diagonal).  Warp w owns rows
-        // w, w+8, ..., in two groups of four that share the k^ loads; lane owns dims 2l, 2l+1 (+64).
-        for (int grp = 0; grp < 2; ++grp) {
-            const int tr0 = warp + 8 * (4 * grp);
-            float acc[4][4] = {};
-            const int i_max = tr0 + 24;
-            for (int i = 0; i <= i_max; ++i) {
-                const float k0 = s.kn[i][2 * lane], k1 = s.kn[i][2 * lane + 1];
-                const float k2 = s.kn[i][2 * lane + 64], k3 = s.kn[i][2 * lane + 65];
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float c = s.tmp[tr0 + 8 * r][i];
-                    acc[r][0] += c * k0; acc[r][1] += c * k1; acc[r][2] += c * k2; acc[r][3] += c * k3;
-                }
-            }
+    }
+    // ---- tiles: T = M diag(beta), P (64 x 64), fp16, swizzled ----
+    for (int idx = tid; idx < kC * kC / 2; idx += kPrepThreads) {
+        const int t = idx >> 5, i = (idx & 31) * 2;
+        *reinterpret_cast<uint32_t*>(rec + kOffT + tile_off(t, i)) =
+            pack_h2(m[t][i] * s.beta[i], m[t][i + 1] * s.beta[i + 1]);
+        const float p0 = i <= t ? expf(s.G[t] - s.G[i]) * s.qk[t][i] : 0.f;
+        const float p1 = i + 1 <= t ? expf(s.G[t] - s.G[i + 1]) * s.qk[t][i + 1] : 0.f;
+        *reinterpret_cast<uint32_t*>(rec + kOffP + tile_off(t, i)) = pack_h2(p0, p1);
+    }
+    // fold beta_i exp(G_i) into M once: tmp[t][i] = M[t][i] beta_i exp(G_i)
+    for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
+        const int t = idx >> 6, i = idx & 63;
+        tmp[t][i] = m[t][i] * s.beta[i] * s.eg[i];
+    }
+    __syncthreads();
+    // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] (tmp is zero above the diagonal).  Warp w owns rows
+    // w, w+8, ..., in two groups of four that share the k^ loads; lane owns dims 2l, 2l+1 (+64).
+    for (int grp = 0; grp < 2; ++grp) {
+        const int tr0 = warp + 8 * (4 * grp);
+        float acc[4][4] = {};
+        const int i_max = tr0 + 24;
+        for (int i = 0; i <= i_max; ++i) {
+            const float k0 = s.kn[i][2 * lane], k1 = s.kn[i][2 * lane + 1];
+            const float k2 = s.kn[i][2 * lane + 64], k3 = s.kn[i][2 * lane + 65];
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
-                const int t = tr0 + 8 * r;
-                *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane)) = pack_h2(acc[r][0], acc[r][1]);
-                *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane + 64)) = pack_h2(acc[r][2], acc[r][3]);
+                const float c = tmp[tr0 + 8 * r][i];
+                acc[r][0] += c * k0; acc[r][1] += c * k1; acc[r][2] += c * k2; acc[r][3] += c * k3;
             }
         }
-        for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
-            const int t = idx >> 5, d = (idx & 31) * 4;
-            const int o = tile_off(t, d);
-            const float e = s.eg[t];
-            *reinterpret_cast<uint2*>(rec + kOffQg + o) =
-                make_uint2(pack_h2(e * s.qn[t][d], e * s.qn[t][d + 1]), pack_h2(e * s.qn[t][d + 2], e * s.qn[t][d + 3]));
-            const float kt = expf(gC - s.G[t]);
-            *reinterpret_cast<uint2*>(rec + kOffKt + o) =
-                make_uint2(pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]), pack_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3]));
-            float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < n_tok) vv = *reinterpret_cast<const float4*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
-            *reinterpret_cast<uint2*>(rec + kOffV + o) = make_uint2(pack_h2(vv.x, vv.y), pack_h2(vv.z, vv.w));
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int t = tr0 + 8 * r;
+            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane)) = pack_h2(acc[r][0], acc[r][1]);
+            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane + 64)) = pack_h2(acc[r][2], acc[r][3]);
         }
-        __syncthreads();
     }
 }
 
