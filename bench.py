@@ -13,8 +13,15 @@ delta rule).  Every step streams the whole KV cache and all recurrent state
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-N > 1 (under torchrun, one rank per GPU): the batch is sharded by sequence --
-every rank owns 32 sequences of its own; there is no data-path collective.
+The timed region replays the step as one CUDA graph (rl_stack_decode); a second pass over the
+same steps with CUDA events between the kernels supplies the per-kernel durations behind the
+roofline object.  e2e goes through rl_stack_decode_host with pinned host buffers.
+
+N > 1 (under torchrun, one rank per GPU): by default the batch is sharded by sequence -- every
+rank owns 32 sequences of its own; there is no data-path collective (weak scaling).
+--shard heads / --shard splitkv divide ONE batch of 32 over the ranks instead (strong scaling,
+NCCL all_gather of head outputs / of attention partials merged by rl_lse_combine).
+--workload selects single-operator lines (N = 1).
 """
 from __future__ import annotations
 
