@@ -47,20 +47,42 @@ __device__ __forceinline__ int tile_off(int row, int x) {
 }
 
 constexpr int kPrepThreads = 256;
-constexpr int kPad = kD + 1;
+constexpr int kPad = kD + 4;                // row stride = 4 (mod 32) floats: the MMA fragment loads spread over the banks
+constexpr int kSq = kC + 4;                 // same for the 64 x 64 arrays
 constexpr int kB = 16;                    // block size of the triangular inverse
+
+// fp32 -> tf32 high part and tf32 residual: a x b ~= ah bh + ah bl + al bh to fp32 accuracy
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+}
+// warp MMA m16n8k8, tf32 inputs, fp32 accumulate.  A row-major 16 x 8: a0 (g, c), a1 (g+8, c), a2 (g, c+4),
+// a3 (g+8, c+4); B 8 x 8: b0 (k = c, n = g), b1 (k = c+4, n = g); D: d0 (g, 2c), d1 (g, 2c+1), d2 (g+8, 2c),
+// d3 (g+8, 2c+1), with g = lane / 4, c = lane % 4.
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma_3xtf32(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                           const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
+    mma_tf32(d, al, bh);
+    mma_tf32(d, ah, bl);
+    mma_tf32(d, ah, bh);
+}
 
 struct PrepSmem {
     float kn[kC][kPad];       // k^
     union {
         float qn[kC][kPad];   // q^, dead once q^.k^ and the Qg tile are out
         struct {
-            float m[kC][kC + 1];      // (I + A)^-1
-            float tmp[kC][kC + 1];
+            float m[kC][kSq];         // (I + A)^-1
+            float tmp[kC][kSq];
         } inv;
     } u;
-    float l[kC][kC + 1];      // k^_t . k^_i, then in place A (strictly lower part of I + A)
-    float qk[kC][kC + 1];     // q^_t . k^_i
+    float l[kC][kSq];         // k^_t . k^_i, then in place A (strictly lower part of I + A)
+    float qk[kC][kSq];        // q^_t . k^_i
     float G[kC], beta[kC], eg[kC];
 };
 
@@ -94,81 +116,112 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         }
         s.G[tid] = gl;
     }
-    // ---- l2 norms (double accumulators as ops::l2norm); padded tokens are all zero ----
-    for (int t = warp; t < kC; t += kPrepThreads / 32) {
-        float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), qx = kx;
-        if (t < n_tok) {
-            kx = *reinterpret_cast<const float4*>(a.k + (size_t(t0 + t) * a.n_qk + hs) * kD + lane * 4);
-            qx = *reinterpret_cast<const float4*>(a.q + (size_t(t0 + t) * a.n_qk + hs) * kD + lane * 4);
+    // ---- l2 norms (double accumulators as ops::l2norm); padded tokens are all zero.  A warp owns
+    // 8 tokens; all 16 row loads are issued before the first reduction so their latencies overlap ----
+    {
+        constexpr int kPer = kC / (kPrepThreads / 32);
+        float4 kx[kPer], qx[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int t = warp + u * (kPrepThreads / 32);
+            kx[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            qx[u] = kx[u];
+            if (t < n_tok) {
+                kx[u] = *reinterpret_cast<const float4*>(a.k + (size_t(t0 + t) * a.n_qk + hs) * kD + lane * 4);
+                qx[u] = *reinterpret_cast<const float4*>(a.q + (size_t(t0 + t) * a.n_qk + hs) * kD + lane * 4);
+            }
         }
-        double ks = double(kx.x) * kx.x + double(kx.y) * kx.y + double(kx.z) * kx.z + double(kx.w) * kx.w;
-        double qs = double(qx.x) * qx.x + double(qx.y) * qx.y + double(qx.z) * qx.z + double(qx.w) * qx.w;
-        for (int off = 16; off > 0; off >>= 1) {
-            ks += __shfl_xor_sync(0xffffffffu, ks, off);
-            qs += __shfl_xor_sync(0xffffffffu, qs, off);
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int t = warp + u * (kPrepThreads / 32);
+            double ks = double(kx[u].x) * kx[u].x + double(kx[u].y) * kx[u].y + double(kx[u].z) * kx[u].z + double(kx[u].w) * kx[u].w;
+            double qs = double(qx[u].x) * qx[u].x + double(qx[u].y) * qx[u].y + double(qx[u].z) * qx[u].z + double(qx[u].w) * qx[u].w;
+            for (int off = 16; off > 0; off >>= 1) {
+                ks += __shfl_xor_sync(0xffffffffu, ks, off);
+                qs += __shfl_xor_sync(0xffffffffu, qs, off);
+            }
+            float ki = 1.f / sqrtf(float(ks) + a.eps_l2);
+            float qi = 1.f / sqrtf(float(qs) + a.eps_l2) * (1.f / sqrtf(float(kD)));
+            if (t >= n_tok) ki = qi = 0.f;
+            s.kn[t][lane * 4 + 0] = kx[u].x * ki; s.kn[t][lane * 4 + 1] = kx[u].y * ki;
+            s.kn[t][lane * 4 + 2] = kx[u].z * ki; s.kn[t][lane * 4 + 3] = kx[u].w * ki;
+            s.u.qn[t][lane * 4 + 0] = qx[u].x * qi; s.u.qn[t][lane * 4 + 1] = qx[u].y * qi;
+            s.u.qn[t][lane * 4 + 2] = qx[u].z * qi; s.u.qn[t][lane * 4 + 3] = qx[u].w * qi;
         }
-        float ki = 1.f / sqrtf(float(ks) + a.eps_l2);
-        float qi = 1.f / sqrtf(float(qs) + a.eps_l2) * (1.f / sqrtf(float(kD)));
-        if (t >= n_tok) ki = qi = 0.f;
-        s.kn[t][lane * 4 + 0] = kx.x * ki; s.kn[t][lane * 4 + 1] = kx.y * ki;
-        s.kn[t][lane * 4 + 2] = kx.z * ki; s.kn[t][lane * 4 + 3] = kx.w * ki;
-        s.u.qn[t][lane * 4 + 0] = qx.x * qi; s.u.qn[t][lane * 4 + 1] = qx.y * qi;
-        s.u.qn[t][lane * 4 + 2] = qx.z * qi; s.u.qn[t][lane * 4 + 3] = qx.w * qi;
     }
     __syncthreads();
     if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
     __syncthreads();
     if (tid < kC) s.eg[tid] = expf(s.G[tid]);
     if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
-    // ---- k^.k^ and q^.k^ (lower triangle), 4 x 4 outputs per thread ----
+    // ---- k^.k^ and q^.k^ on the tensor cores (3 x TF32 = fp32 accuracy): warp w owns rows
+    // 16 (w & 3) .. +15 and columns 32 (w >> 2) .. +31; column tiles entirely above the diagonal
+    // are skipped (and zero-filled, nobody reads more than their zero) ----
     {
-        const int tb = (tid >> 4) * 4, ib = (tid & 15) * 4;
-        float kk[4][4] = {}, qk[4][4] = {};
-        if (ib <= tb + 3) {
-            for (int d = 0; d < kD; ++d) {
-                float kt[4], qt[4], ki[4];
+        const int g = lane >> 2, c = lane & 3;
+        const int t_base = (warp & 3) * 16, i_base = (warp >> 2) * 32;
+        float ck[4][4] = {}, cq[4][4] = {};
+        const int n_tiles = min(4, max(0, (t_base + 15 - i_base) / 8 + 1));   // tiles with i0 <= t_base + 15
+        for (int k0 = 0; k0 < kD; k0 += 8) {
+            uint32_t akh[4], akl[4], aqh[4], aql[4];
+            split_tf32(s.kn[t_base + g][k0 + c], akh[0], akl[0]);
+            split_tf32(s.kn[t_base + g + 8][k0 + c], akh[1], akl[1]);
+            split_tf32(s.kn[t_base + g][k0 + c + 4], akh[2], akl[2]);
+            split_tf32(s.kn[t_base + g + 8][k0 + c + 4], akh[3], akl[3]);
+            split_tf32(s.u.qn[t_base + g][k0 + c], aqh[0], aql[0]);
+            split_tf32(s.u.qn[t_base + g + 8][k0 + c], aqh[1], aql[1]);
+            split_tf32(s.u.qn[t_base + g][k0 + c + 4], aqh[2], aql[2]);
+            split_tf32(s.u.qn[t_base + g + 8][k0 + c + 4], aqh[3], aql[3]);
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    kt[x] = s.kn[tb + x][d];
-                    qt[x] = s.u.qn[tb + x][d];
-                    ki[x] = s.kn[ib + x][d];
+            for (int nt = 0; nt < 4; ++nt) {
+                if (nt < n_tiles) {
+                    uint32_t bh[2], bl[2];
+                    split_tf32(s.kn[i_base + 8 * nt + g][k0 + c], bh[0], bl[0]);
+                    split_tf32(s.kn[i_base + 8 * nt + g][k0 + c + 4], bh[1], bl[1]);
+                    mma_3xtf32(ck[nt], akh, akl, bh, bl);
+                    mma_3xtf32(cq[nt], aqh, aql, bh, bl);
                 }
-#pragma unroll
-                for (int x = 0; x < 4; ++x)
-#pragma unroll
-                    for (int y = 0; y < 4; ++y) {
-                        kk[x][y] += kt[x] * ki[y];
-                        qk[x][y] += qt[x] * ki[y];
-                    }
             }
         }
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
-#pragma unroll
-            for (int y = 0; y < 4; ++y) {
-                s.l[tb + x][ib + y] = kk[x][y];
-                s.qk[tb + x][ib + y] = qk[x][y];
-            }
+        for (int nt = 0; nt < 4; ++nt) {
+            const int i0 = i_base + 8 * nt + 2 * c;
+            s.l[t_base + g][i0] = ck[nt][0];      s.l[t_base + g][i0 + 1] = ck[nt][1];
+            s.l[t_base + g + 8][i0] = ck[nt][2];  s.l[t_base + g + 8][i0 + 1] = ck[nt][3];
+            s.qk[t_base + g][i0] = cq[nt][0];     s.qk[t_base + g][i0 + 1] = cq[nt][1];
+            s.qk[t_base + g + 8][i0] = cq[nt][2]; s.qk[t_base + g + 8][i0 + 1] = cq[nt][3];
+        }
     }
     __syncthreads();
     // ---- tiles that need q^: Qg; with it Kt and V (64 x 128, fp16, swizzled) ----
     const float gC = s.G[kC - 1];
-    for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
-        const int t = idx >> 5, d = (idx & 31) * 4;
-        const int o = tile_off(t, d);
-        const float e = s.eg[t];
-        *reinterpret_cast<uint2*>(rec + kOffQg + o) =
-            make_uint2(pack_h2(e * s.u.qn[t][d], e * s.u.qn[t][d + 1]), pack_h2(e * s.u.qn[t][d + 2], e * s.u.qn[t][d + 3]));
-        const float kt = expf(gC - s.G[t]);
-        *reinterpret_cast<uint2*>(rec + kOffKt + o) =
-            make_uint2(pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]), pack_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3]));
-        float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t < n_tok) vv = *reinterpret_cast<const float4*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
-        *reinterpret_cast<uint2*>(rec + kOffV + o) = make_uint2(pack_h2(vv.x, vv.y), pack_h2(vv.z, vv.w));
+    {
+        constexpr int kPer = kC * kD / 4 / kPrepThreads;      // 8 groups of 4 dims per thread
+        float4 vv[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {                      // all value loads in flight together
+            const int idx = tid + u * kPrepThreads;
+            const int t = idx >> 5, d = (idx & 31) * 4;
+            vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < n_tok) vv[u] = *reinterpret_cast<const float4*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int idx = tid + u * kPrepThreads;
+            const int t = idx >> 5, d = (idx & 31) * 4;
+            const int o = tile_off(t, d);
+            const float e = s.eg[t];
+            *reinterpret_cast<uint2*>(rec + kOffQg + o) =
+                make_uint2(pack_h2(e * s.u.qn[t][d], e * s.u.qn[t][d + 1]), pack_h2(e * s.u.qn[t][d + 2], e * s.u.qn[t][d + 3]));
+            const float kt = expf(gC - s.G[t]);
+            *reinterpret_cast<uint2*>(rec + kOffKt + o) =
+                make_uint2(pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]), pack_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3]));
+            *reinterpret_cast<uint2*>(rec + kOffV + o) = make_uint2(pack_h2(vv[u].x, vv[u].y), pack_h2(vv[u].z, vv[u].w));
+        }
     }
     __syncthreads();                                  // q^ is dead from here on: its space becomes m and tmp
-    float (*m)[kC + 1] = s.u.inv.m;
-    float (*tmp)[kC + 1] = s.u.inv.tmp;
+    float (*m)[kSq] = s.u.inv.m;
+    float (*tmp)[kSq] = s.u.inv.tmp;
     // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t, in place ----
     for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
         const int t = idx >> 6, i = idx & 63;
@@ -176,30 +229,67 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         m[t][i] = t == i ? 1.f : 0.f;
     }
     __syncthreads();
-    // ---- M = (I + A)^-1, blocked: 16 x 16 diagonal blocks by forward substitution ... ----
-    if (tid < kC) {
-        const int bb = (tid >> 4) * kB, c = tid & 15;           // thread owns column c of block bb
-        for (int t = c + 1; t < kB; ++t) {
-            float acc = 0.f;
-            for (int i = c; i < t; ++i) acc -= s.l[bb + t][bb + i] * m[bb + i][bb + c];
-            m[bb + t][bb + c] = acc;
-        }
-    }
+    // ---- M = (I + A)^-1 with all 256 threads and a dozen barriers ----
+    // (1) the four 16 x 16 diagonal blocks: N = strictly lower part is nilpotent (N^16 = 0), so
+    //     (I + N)^-1 = (I - N)(I + N^2)(I + N^4)(I + N^8): five small products, element (x, y) of
+    //     block u per thread.  L, T, M below are the block's tiles of s.l, tmp, m.
+    {
+        const int x = tid >> 4, y = tid & 15;
+#define RL_L(r, c) s.l[bb + (r)][bb + (c)]
+#define RL_T(r, c) tmp[bb + (r)][bb + (c)]
+#define RL_M(r, c) m[bb + (r)][bb + (c)]
+#define RL_BLOCKS(BODY)                    \
+    _Pragma("unroll") for (int u = 0; u < 4; ++u) { \
+        const int bb = u * kB;             \
+        BODY                               \
+    }                                      \
     __syncthreads();
-    // ... then block row by block row: M_ij = -M_ii (sum_{j<=k<i} A_ik M_kj), j < i
-    for (int bi = 1; bi < kC / kB; ++bi) {
-        for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
-            const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
+        RL_BLOCKS({ float acc = 0.f; for (int k = 0; k < kB; ++k) acc += RL_L(x, k) * RL_L(k, y); RL_T(x, y) = acc; })          // T = N^2
+        RL_BLOCKS({ float acc = (x == y ? 1.f : 0.f) - RL_L(x, y);
+                    for (int k = 0; k < kB; ++k) acc += ((x == k ? 1.f : 0.f) - RL_L(x, k)) * RL_T(k, y);
+                    RL_M(x, y) = acc; })                                                                                    // M = (I - N)(I + N^2)
+        RL_BLOCKS({ float acc = 0.f; for (int k = 0; k < kB; ++k) acc += RL_T(x, k) * RL_T(k, y); RL_L(x, y) = acc; })          // L = N^4
+        RL_BLOCKS({ float acc = RL_M(x, y); for (int k = 0; k < kB; ++k) acc += RL_M(x, k) * RL_L(k, y); RL_T(x, y) = acc; })   // T = M (I + N^4)
+        RL_BLOCKS({ float acc = 0.f; for (int k = 0; k < kB; ++k) acc += RL_L(x, k) * RL_L(k, y); RL_M(x, y) = acc; })          // M = N^8
+        RL_BLOCKS({ float acc = RL_T(x, y); for (int k = 0; k < kB; ++k) acc += RL_T(x, k) * RL_M(k, y); RL_L(x, y) = acc; })   // L = T (I + N^8): the inverse
+        RL_BLOCKS({ RL_M(x, y) = RL_L(x, y); })
+#undef RL_BLOCKS
+#undef RL_M
+#undef RL_T
+#undef RL_L
+        // (2) off-diagonal blocks from inv [[P, 0], [C, Q]] = [[P^-1, 0], [-Q^-1 C P^-1, Q^-1]], first
+        //     for the two 32 x 32 halves (C = a 16 x 16 block of A), then for the whole (C = 32 x 32)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int bi = (2 * u + 1) * kB, bj = 2 * u * kB;
             float acc = 0.f;
-            for (int kx = bj * kB; kx < bi * kB; ++kx) acc += s.l[bi * kB + x][kx] * m[kx][bj * kB + y];
-            tmp[bi * kB + x][bj * kB + y] = acc;
+            for (int k = 0; k < kB; ++k) acc += s.l[bi + x][bj + k] * m[bj + k][bj + y];
+            tmp[bi + x][bj + y] = acc;
         }
         __syncthreads();
-        for (int idx = tid; idx < bi * kB * kB; idx += kPrepThreads) {
-            const int bj = idx / (kB * kB), x = (idx >> 4) & 15, y = idx & 15;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int bi = (2 * u + 1) * kB, bj = 2 * u * kB;
             float acc = 0.f;
-            for (int kx = 0; kx <= x; ++kx) acc -= m[bi * kB + x][bi * kB + kx] * tmp[bi * kB + kx][bj * kB + y];
-            m[bi * kB + x][bj * kB + y] = acc;
+            for (int k = 0; k < kB; ++k) acc -= m[bi + x][bi + k] * tmp[bi + k][bj + y];
+            m[bi + x][bj + y] = acc;
+        }
+        __syncthreads();
+        const int x2 = tid >> 5, y2 = tid & 31;                 // rows 32 + x2 + 8 u, column y2
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int r = 32 + x2 + 8 * u;
+            float acc = 0.f;
+            for (int k = 0; k < 32; ++k) acc += s.l[r][k] * m[k][y2];
+            tmp[r][y2] = acc;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int r = 32 + x2 + 8 * u;
+            float acc = 0.f;
+            for (int k = 0; k < 32; ++k) acc -= m[r][32 + k] * tmp[32 + k][y2];
+            m[r][y2] = acc;
         }
         __syncthreads();
     }
@@ -218,26 +308,31 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         tmp[t][i] = m[t][i] * s.beta[i] * s.eg[i];
     }
     __syncthreads();
-    // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] (tmp is zero above the diagonal).  Warp w owns rows
-    // w, w+8, ..., in two groups of four that share the k^ loads; lane owns dims 2l, 2l+1 (+64).
-    for (int grp = 0; grp < 2; ++grp) {
-        const int tr0 = warp + 8 * (4 * grp);
-        float acc[4][4] = {};
-        const int i_max = tr0 + 24;
-        for (int i = 0; i <= i_max; ++i) {
-            const float k0 = s.kn[i][2 * lane], k1 = s.kn[i][2 * lane + 1];
-            const float k2 = s.kn[i][2 * lane + 64], k3 = s.kn[i][2 * lane + 65];
+    // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] (tmp is zero above the diagonal), 3 x TF32 MMAs: warp w
+    // owns rows 16 (w & 3) .. +15 and dims 64 (w >> 2) .. +63; K steps beyond the rows' diagonal skipped.
+    {
+        const int g = lane >> 2, c = lane & 3;
+        const int t_base = (warp & 3) * 16, d_base = (warp >> 2) * 64;
+        float acc[8][4] = {};
+        for (int k0 = 0; k0 < t_base + 16; k0 += 8) {
+            uint32_t ah[4], al[4];
+            split_tf32(tmp[t_base + g][k0 + c], ah[0], al[0]);
+            split_tf32(tmp[t_base + g + 8][k0 + c], ah[1], al[1]);
+            split_tf32(tmp[t_base + g][k0 + c + 4], ah[2], al[2]);
+            split_tf32(tmp[t_base + g + 8][k0 + c + 4], ah[3], al[3]);
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const float c = tmp[tr0 + 8 * r][i];
-                acc[r][0] += c * k0; acc[r][1] += c * k1; acc[r][2] += c * k2; acc[r][3] += c * k3;
+            for (int nt = 0; nt < 8; ++nt) {
+                uint32_t bh[2], bl[2];
+                split_tf32(s.kn[k0 + c][d_base + 8 * nt + g], bh[0], bl[0]);
+                split_tf32(s.kn[k0 + c + 4][d_base + 8 * nt + g], bh[1], bl[1]);
+                mma_3xtf32(acc[nt], ah, al, bh, bl);
             }
         }
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int t = tr0 + 8 * r;
-            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane)) = pack_h2(acc[r][0], acc[r][1]);
-            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t, 2 * lane + 64)) = pack_h2(acc[r][2], acc[r][3]);
+        for (int nt = 0; nt < 8; ++nt) {
+            const int d0 = d_base + 8 * nt + 2 * c;
+            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g, d0)) = pack_h2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g + 8, d0)) = pack_h2(acc[nt][2], acc[nt][3]);
         }
     }
 }
