@@ -65,12 +65,6 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
-__device__ __forceinline__ void mma_3xtf32(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
-                                           const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
-    mma_tf32(d, al, bh);
-    mma_tf32(d, ah, bl);
-    mma_tf32(d, ah, bh);
-}
 
 struct PrepSmem {
     float kn[kC][kPad];       // k^
@@ -172,14 +166,24 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
             split_tf32(s.u.qn[t_base + g + 8][k0 + c], aqh[1], aql[1]);
             split_tf32(s.u.qn[t_base + g][k0 + c + 4], aqh[2], aql[2]);
             split_tf32(s.u.qn[t_base + g + 8][k0 + c + 4], aqh[3], aql[3]);
+            // B fragments of all column tiles first, then the three TF32 passes with the accumulators
+            // interleaved: consecutive MMAs never depend on each other
+            uint32_t bh[4][2], bl[4][2];
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
                 if (nt < n_tiles) {
-                    uint32_t bh[2], bl[2];
-                    split_tf32(s.kn[i_base + 8 * nt + g][k0 + c], bh[0], bl[0]);
-                    split_tf32(s.kn[i_base + 8 * nt + g][k0 + c + 4], bh[1], bl[1]);
-                    mma_3xtf32(ck[nt], akh, akl, bh, bl);
-                    mma_3xtf32(cq[nt], aqh, aql, bh, bl);
+                    split_tf32(s.kn[i_base + 8 * nt + g][k0 + c], bh[nt][0], bl[nt][0]);
+                    split_tf32(s.kn[i_base + 8 * nt + g][k0 + c + 4], bh[nt][1], bl[nt][1]);
+                }
+            }
+#pragma unroll
+            for (int pass = 0; pass < 3; ++pass) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    if (nt < n_tiles) {
+                        mma_tf32(ck[nt], pass == 0 ? akl : akh, pass == 1 ? bl[nt] : bh[nt]);
+                        mma_tf32(cq[nt], pass == 0 ? aql : aqh, pass == 1 ? bl[nt] : bh[nt]);
+                    }
                 }
             }
         }
@@ -320,13 +324,16 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
             split_tf32(tmp[t_base + g + 8][k0 + c], ah[1], al[1]);
             split_tf32(tmp[t_base + g][k0 + c + 4], ah[2], al[2]);
             split_tf32(tmp[t_base + g + 8][k0 + c + 4], ah[3], al[3]);
+            uint32_t bh[8][2], bl[8][2];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                uint32_t bh[2], bl[2];
-                split_tf32(s.kn[k0 + c][d_base + 8 * nt + g], bh[0], bl[0]);
-                split_tf32(s.kn[k0 + c + 4][d_base + 8 * nt + g], bh[1], bl[1]);
-                mma_3xtf32(acc[nt], ah, al, bh, bl);
+                split_tf32(s.kn[k0 + c][d_base + 8 * nt + g], bh[nt][0], bl[nt][0]);
+                split_tf32(s.kn[k0 + c + 4][d_base + 8 * nt + g], bh[nt][1], bl[nt][1]);
             }
+#pragma unroll
+            for (int pass = 0; pass < 3; ++pass)
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) mma_tf32(acc[nt], pass == 0 ? al : ah, pass == 1 ? bl[nt] : bh[nt]);
         }
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
