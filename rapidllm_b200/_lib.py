@@ -108,6 +108,8 @@ SYMBOLS = {
     "rl_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz,
                                     C.POINTER(AttnDecodeParams), _vp]),
     "rl_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnPrefillParams), _vp]),
+    "rl_attn_prefill_workspace_bytes": (_sz, [C.POINTER(AttnPrefillParams)]),
+    "rl_attn_prefill_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(AttnPrefillParams), _vp]),
     "rl_lse_combine": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "rl_kv_compact_page_bytes": (_sz, []),
     "rl_kv_compact_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(KvAppendParams), _vp]),

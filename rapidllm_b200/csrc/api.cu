@@ -508,9 +508,23 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     return RL_OK;
 }
 
-int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
-                    const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o,
-                    const rl_attn_prefill_params* p, void* stream) {
+// How many CTAs share the KV range of one (query tile, head): 1 when there is at least one
+// (query tile, head) per SM (dividing a 1024-row chunk in two measured slower: the partials and
+// the second prologue cost more than the emptier second wave), else enough to fill the device
+// twice over, each part keeping at least 8 KV tiles.
+static int prefill_kv_parts(const rl_attn_prefill_params* p, int sms) {
+    const int rows = rl::attn_prefill_q_rows();
+    const long long items = 1LL * ((p->seq + rows - 1) / rows) * p->n_q;
+    if (items <= 0 || items >= sms) return 1;
+    const long long tiles = (1LL * p->pos0 + p->seq + p->page_tokens - 1) / p->page_tokens;   // of the last query tile
+    long long parts = (2LL * sms + items - 1) / items;
+    parts = std::min(parts, std::max(1LL, tiles / 8));
+    return int(std::min(parts, 16LL));
+}
+
+static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
+                             const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o,
+                             void* workspace, size_t workspace_bytes, const rl_attn_prefill_params* p, void* stream) {
     if (!p) return fail(RL_ERR_RANGE, "params is NULL");
     if (p->head_dim != rl::kHeadDim || p->page_tokens != rl::kPageTokens)
         return fail(RL_ERR_UNSUPPORTED, "head_dim %d / page_tokens %d: only 256 / 64", p->head_dim, p->page_tokens);
@@ -559,11 +573,51 @@ int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, c
     a.scale = 1.f / sqrtf(float(p->head_dim));
     a.trace = reinterpret_cast<unsigned long long*>(getenv("RL_B200_PREFILL_TRACE") ? strtoull(getenv("RL_B200_PREFILL_TRACE"), nullptr, 0) : 0ull);
     const int n_qtiles = (p->seq + rl::attn_prefill_q_rows() - 1) / rl::attn_prefill_q_rows();
-    rl::attn_prefill_kernel<<<dim3(unsigned(n_qtiles) * unsigned(p->n_q)), rl::attn_prefill_threads(), rl::attn_prefill_smem_bytes(),
-                              as_stream(stream)>>>(a);
+    // a workspace lets short chunks (or a handful of verify rows over a long cache) spread every
+    // (query tile, head) over several CTAs; without one the call runs unsplit
+    int parts = workspace ? prefill_kv_parts(p, d->sms) : 1;
+    const size_t rows_total = size_t(p->seq) * p->n_q;
+    const size_t o_bytes = align_up(size_t(parts) * rows_total * rl::kHeadDim * sizeof(float), 256);
+    if (parts > 1 && (workspace_bytes < o_bytes + size_t(parts) * rows_total * 2 * sizeof(float) ||
+                      reinterpret_cast<uintptr_t>(workspace) % 16))
+        parts = 1;
+    a.kv_parts = parts;
+    a.part_o = parts > 1 ? static_cast<float*>(workspace) : nullptr;
+    a.part_ml = parts > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + o_bytes) : nullptr;
+    rl::attn_prefill_kernel<<<dim3(unsigned(n_qtiles) * unsigned(p->n_q) * unsigned(parts)), rl::attn_prefill_threads(),
+                              rl::attn_prefill_smem_bytes(), as_stream(stream)>>>(a);
+    if (parts > 1)
+        rl::lse_combine_kernel<<<unsigned(rows_total), 256, 0, as_stream(stream)>>>(a.part_o, a.part_ml, gate, o, parts,
+                                                                                  int(rows_total), 0, nullptr);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
+
+int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
+                    const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o,
+                    const rl_attn_prefill_params* p, void* stream) {
+    return attn_prefill_impl(k_pool, v_pool, page_table_row, q_bf16, k_rows_bf16, v_rows_bf16, gate, o, nullptr, 0, p,
+                             stream);
+}
+
+size_t rl_attn_prefill_workspace_bytes(const rl_attn_prefill_params* p) {
+    if (!p || p->seq <= 0 || p->n_q <= 0 || p->page_tokens <= 0) return 0;
+    DevInfo* d;
+    if (dev_info(&d)) return 0;
+    const int parts = prefill_kv_parts(p, d->sms);
+    if (parts <= 1) return 0;
+    const size_t rows_total = size_t(p->seq) * p->n_q;
+    return align_up(size_t(parts) * rows_total * rl::kHeadDim * sizeof(float), 256) +
+           size_t(parts) * rows_total * 2 * sizeof(float);
+}
+
+int rl_attn_prefill_ws(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
+                       const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o, void* workspace,
+                       size_t workspace_bytes, const rl_attn_prefill_params* p, void* stream) {
+    return attn_prefill_impl(k_pool, v_pool, page_table_row, q_bf16, k_rows_bf16, v_rows_bf16, gate, o, workspace,
+                             workspace_bytes, p, stream);
+}
+
 
 int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16, int n_tok, int n_kv,
                  int head_dim, int n_pages, void* stream) {

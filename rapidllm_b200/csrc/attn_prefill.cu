@@ -72,14 +72,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     // group's query heads of the last (heaviest) query tile, then of the one before, ...
     const int G = a.n_q / a.n_kv;
     const int per_kv = n_qtiles * G;
-    const int hkv = int(blockIdx.x) / per_kv;
-    const int rem = int(blockIdx.x) - hkv * per_kv;
+    const int parts = a.kv_parts > 1 ? a.kv_parts : 1;
+    const int item = int(blockIdx.x) / parts, part = int(blockIdx.x) - item * parts;
+    const int hkv = item / per_kv;
+    const int rem = item - hkv * per_kv;
     const int qt = n_qtiles - 1 - rem / G;
     const int hq = hkv * G + rem % G;
     const int q0 = qt * kQRows;                               // first query row of this CTA
     const int rows = min(kQRows, a.T - q0);
     const int last_pos = a.pos0 + q0 + rows - 1;              // position of the last query row
-    const int n_tiles = last_pos / kKvTile + 1;               // KV tiles [0, n_tiles)
+    const int n_tiles_all = last_pos / kKvTile + 1;           // KV tiles [0, n_tiles_all) of this query tile
+    // this CTA's share [j0, j0 + n_tiles); below j counts from 0 inside the share
+    const int j0 = int(1LL * part * n_tiles_all / parts);
+    const int n_tiles = int(1LL * (part + 1) * n_tiles_all / parts) - j0;
 
     if (tid == 0) {
         for (int i = 0; i < kKStages; ++i) {
@@ -107,9 +112,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
-    const bool tr = a.trace && blockIdx.x == 0;
+    const bool tr = a.trace && blockIdx.x == 0 && parts == 1;
     // per-CTA record after the 64 x 8 tile timestamps: start, main loop start, end, SM id
-    unsigned long long* cta_rec = a.trace ? a.trace + 512 + (size_t(hq) * n_qtiles + (n_qtiles - 1 - qt)) * 4 : nullptr;
+    unsigned long long* cta_rec = a.trace ? a.trace + 512 + ((size_t(hq) * n_qtiles + (n_qtiles - 1 - qt)) * parts + part) * 4 : nullptr;
     if (cta_rec && tid == 0) {
         uint32_t smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -142,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         mbar_arrive(&s.bar_q);                                // Q is in tensor memory (awaited by the S issuer)
         if (cta_rec && tid == 0) cta_rec[1] = global_ns();
         // the epilogue's gate rows: start them on their way into L2 now (2 of the row's 8 lines each)
-        if (a.gate && r < rows) {
+        if (a.gate && a.kv_parts <= 1 && r < rows) {
             const float* gp = a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + part * 64;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(gp));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + 32));
@@ -156,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         if (lane == 0) {
             for (int j = 0; j < n_tiles; ++j) {
                 const int ks = j % kKStages, vs = j % kVStages;
-                int page = a.page_table[j];
+                int page = a.page_table[j0 + j];
                 if (page < 0 || page >= a.n_pages) {
                     set_err(a.err, DEV_ERR_BAD_PAGE);
                     page = 0;
@@ -268,8 +273,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             }
             tc::fence_before_sync();
             mbar_arrive(&s.bar_sfree[grp]);                   // the scores are in registers: S buffer free
-            const int tok0 = j * kKvTile;
-            if (j == n_tiles - 1 && last_pos + 1 - tok0 < kKvTile) {
+            const int tok0 = (j0 + j) * kKvTile;
+            if (j0 + j == n_tiles_all - 1 && last_pos + 1 - tok0 < kKvTile) {
                 // V rows past the last position may hold anything (0 * NaN would poison O): clear them
                 if (ok && !mbar_wait(&s.v_full[j % kVStages], (j / kVStages) & 1)) {
                     set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -377,16 +382,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         }
         // ------------------------------ epilogue ------------------------------
         // final maximum = after the last tile; the four partial sums of a row are brought to it
-        if (ok && !mbar_wait(&s.bar_m[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) {
-            set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
-            ok = false;
+        float m_fin = -1e30f;
+        if (n_tiles > 0) {
+            if (ok && !mbar_wait(&s.bar_m[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
+            }
+            m_fin = s.mrow[(n_tiles - 1) & 1][r];
         }
-        const float m_fin = s.mrow[(n_tiles - 1) & 1][r];
         s.lsum[r][grp * 2 + half] = l_part * fast_exp2(m_known - m_fin);
         named_bar_sync(9, kSoftmaxThreads);
         const float4 lp = *reinterpret_cast<const float4*>(s.lsum[r]);
         const float l_run = (lp.x + lp.y) + (lp.z + lp.w);
-        if (ok && !mbar_wait(&s.bar_done, 0)) {
+        if (n_tiles > 0 && ok && !mbar_wait(&s.bar_done, 0)) {
             set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
             ok = false;
         }
@@ -394,31 +402,43 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         // O / l -> shared memory (the K and V rings are free now: every MMA has completed), row
         // stride 260 floats so that the thread-per-row stores spread over the banks; then each
         // warp takes whole rows, so the gate is read and the output written in full 512-byte
-        // requests
+        // requests.  With kv_parts > 1 the output stays unnormalised and ungated.
         float* stage = reinterpret_cast<float*>(s.k[0]);
         constexpr int kStageStride = kHeadDim + 4;
         static_assert(sizeof(float) * kQRows * kStageStride <= sizeof(s.k) + sizeof(s.v), "O staging must fit the rings");
         const bool good = ok && !s.failed;
+        const bool split = parts > 1;
         if (good) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const float inv = split ? 1.f : (l_run > 0.f ? 1.f / l_run : 0.f);
             const int col0 = (half * 2 + grp) * 64;           // this thread's 64 output columns
 #pragma unroll 1
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t o[32];
-                tc::tmem_ld32(lane_addr + kColO + col0 + c0, o);
-                tc::tmem_wait_ld();
+                if (n_tiles > 0) {
+                    tc::tmem_ld32(lane_addr + kColO + col0 + c0, o);
+                    tc::tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;   // no tile: O was never written
+                }
 #pragma unroll
                 for (int i = 0; i < 32; i += 4)
                     *reinterpret_cast<float4*>(stage + r * kStageStride + col0 + c0 + i) =
                         make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
                                     __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             }
+            if (split && grp == 0 && half == 0 && r < rows) {
+                float* ml = a.part_ml + ((size_t(part) * a.T + q0 + r) * a.n_q + hq) * 2;
+                ml[0] = m_fin * 0.6931471805599453f;          // log2 domain -> natural-log units
+                ml[1] = l_run;
+            }
         }
         named_bar_sync(9, kSoftmaxThreads);
         if (good) {
             for (int row = warp; row < rows; row += kSoftmaxThreads / 32) {
-                float* dst = a.o + (size_t(q0 + row) * a.n_q + hq) * kHeadDim;
-                const float* gp = a.gate ? a.gate + (size_t(q0 + row) * a.n_q + hq) * kHeadDim : nullptr;
+                float* dst = split ? a.part_o + ((size_t(part) * a.T + q0 + row) * a.n_q + hq) * kHeadDim
+                                   : a.o + (size_t(q0 + row) * a.n_q + hq) * kHeadDim;
+                const float* gp = (a.gate && !split) ? a.gate + (size_t(q0 + row) * a.n_q + hq) * kHeadDim : nullptr;
 #pragma unroll
                 for (int hcol = 0; hcol < 2; ++hcol) {
                     const int c = hcol * 128 + lane * 4;

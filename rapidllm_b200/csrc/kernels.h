@@ -42,6 +42,12 @@ struct AttnPrefillArgs {
     int* err;
     int T, pos0, n_q, n_kv, n_pages;
     float scale;
+    // kv_parts > 1: the KV tiles of every (query tile, head) are divided among kv_parts CTAs; part p
+    // writes its unnormalised, ungated output to part_o [p][T][n_q][256] and (max in natural-log
+    // units, sum) to part_ml [p][T][n_q][2] for lse_combine_kernel, which applies the gate
+    int kv_parts;
+    float* part_o;
+    float* part_ml;
     unsigned long long* trace;   // development aid: null, or room for 8 timestamps x 64 tiles of CTA (0,0) + 4 words per CTA
 };
 __global__ void attn_prefill_kernel(AttnPrefillArgs a);

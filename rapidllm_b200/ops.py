@@ -161,7 +161,8 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, gate=None, max_seq_len=
     return o
 
 
-def attn_prefill(q, k_pool, v_pool, page_table_row, pos0=0, k_rows=None, v_rows=None, gate=None):
+def attn_prefill(q, k_pool, v_pool, page_table_row, pos0=0, k_rows=None, v_rows=None, gate=None, split=True,
+                 workspace=None):
     """ops::attn_prefill for one chunk of one sequence over the paged F16 cache.
 
     q bf16 [T][n_q][256]; k_rows, v_rows bf16 [T][n_kv][256] are appended at pos0 first (or the
@@ -177,8 +178,14 @@ def attn_prefill(q, k_pool, v_pool, page_table_row, pos0=0, k_rows=None, v_rows=
     o = torch.empty(T, n_q, HEAD_DIM, dtype=torch.float32, device=q.device)
     p = AttnPrefillParams(n_q=n_q, n_kv=n_kv, head_dim=HEAD_DIM, seq=T, br=128, bc=64, pos0=pos0,
                           page_tokens=PAGE_TOKENS, n_pages=n_pages, n_table=page_table_row.numel())
-    check(lib().rl_attn_prefill(_p(k_pool), _p(v_pool), _p(page_table_row), _p(q), _p(k_rows),
-                                _p(v_rows), _p(gate), _p(o), C.byref(p), _stream()))
+    need = lib().rl_attn_prefill_workspace_bytes(C.byref(p))
+    ws = None
+    if need and split:
+        ws = workspace if workspace is not None and workspace.numel() >= need else \
+            torch.empty(need, dtype=torch.uint8, device=q.device)
+    check(lib().rl_attn_prefill_ws(_p(k_pool), _p(v_pool), _p(page_table_row), _p(q), _p(k_rows),
+                                   _p(v_rows), _p(gate), _p(o), _p(ws), 0 if ws is None else ws.numel(),
+                                   C.byref(p), _stream()))
     return o
 
 
