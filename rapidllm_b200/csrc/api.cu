@@ -512,14 +512,19 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
 // (query tile, head) per SM (dividing a 1024-row chunk in two measured slower: the partials and
 // the second prologue cost more than the emptier second wave), else enough to fill the device
 // twice over, each part keeping at least 8 KV tiles.
+static bool prefill_packed(const rl_attn_prefill_params* p) {
+    // few enough rows that (token, query head of a group) pairs fit one 128-row tile per KV head
+    return p->seq * (p->n_q / p->n_kv) <= rl::attn_prefill_q_rows();
+}
+
 static int prefill_kv_parts(const rl_attn_prefill_params* p, int sms) {
     const int rows = rl::attn_prefill_q_rows();
-    const long long items = 1LL * ((p->seq + rows - 1) / rows) * p->n_q;
+    const long long items = prefill_packed(p) ? p->n_kv : 1LL * ((p->seq + rows - 1) / rows) * p->n_q;
     if (items <= 0 || items >= sms) return 1;
     const long long tiles = (1LL * p->pos0 + p->seq + p->page_tokens - 1) / p->page_tokens;   // of the last query tile
-    long long parts = (2LL * sms + items - 1) / items;
+    long long parts = prefill_packed(p) ? sms / items : (2LL * sms + items - 1) / items;
     parts = std::min(parts, std::max(1LL, tiles / 8));
-    return int(std::min(parts, 16LL));
+    return int(std::min(parts, 64LL));
 }
 
 static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
@@ -581,10 +586,12 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
     if (parts > 1 && (workspace_bytes < o_bytes + size_t(parts) * rows_total * 2 * sizeof(float) ||
                       reinterpret_cast<uintptr_t>(workspace) % 16))
         parts = 1;
+    a.packed = prefill_packed(p) ? 1 : 0;
     a.kv_parts = parts;
     a.part_o = parts > 1 ? static_cast<float*>(workspace) : nullptr;
     a.part_ml = parts > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + o_bytes) : nullptr;
-    rl::attn_prefill_kernel<<<dim3(unsigned(n_qtiles) * unsigned(p->n_q) * unsigned(parts)), rl::attn_prefill_threads(),
+    rl::attn_prefill_kernel<<<dim3((a.packed ? unsigned(p->n_kv) : unsigned(n_qtiles) * unsigned(p->n_q)) * unsigned(parts)),
+                              rl::attn_prefill_threads(),
                               rl::attn_prefill_smem_bytes(), as_stream(stream)>>>(a);
     if (parts > 1)
         rl::lse_combine_kernel<<<unsigned(rows_total), 256, 0, as_stream(stream)>>>(a.part_o, a.part_ml, gate, o, parts,

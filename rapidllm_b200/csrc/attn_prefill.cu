@@ -27,6 +27,11 @@
 // Each thread keeps its partial row sum relative to the maximum it last saw.  Epilogue: O / l
 // goes through shared memory so that the gate is read and the output written by whole rows.
 // Completion is signalled through tcgen05.commit on mbarriers; all waits are bounded.
+//
+// Two variations for calls with few query rows (short chunks, the rows of a speculative verify):
+// kv_parts > 1 divides the KV tiles of an item among several CTAs that write partials for the
+// log-sum-exp merge kernel; packed makes the 128 MMA rows (token, query head of the GQA group)
+// pairs, one item per KV head, so the group's heads share a single pass over K/V.
 #include "kernels.h"
 #include "tcgen05.cuh"
 
@@ -74,13 +79,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     const int per_kv = n_qtiles * G;
     const int parts = a.kv_parts > 1 ? a.kv_parts : 1;
     const int item = int(blockIdx.x) / parts, part = int(blockIdx.x) - item * parts;
-    const int hkv = item / per_kv;
-    const int rem = item - hkv * per_kv;
-    const int qt = n_qtiles - 1 - rem / G;
+    // packed (a few rows, e.g. a speculative verify): one item per KV head, its MMA rows are
+    // (token, query head of the group) pairs, so the group's heads share one pass over K/V
+    const int hkv = a.packed ? item : item / per_kv;
+    const int rem = a.packed ? 0 : item - hkv * per_kv;
+    const int qt = a.packed ? 0 : n_qtiles - 1 - rem / G;
     const int hq = hkv * G + rem % G;
     const int q0 = qt * kQRows;                               // first query row of this CTA
-    const int rows = min(kQRows, a.T - q0);
-    const int last_pos = a.pos0 + q0 + rows - 1;              // position of the last query row
+    const int rows = a.packed ? a.T * G : min(kQRows, a.T - q0);
+    const int last_pos = a.packed ? a.pos0 + a.T - 1 : a.pos0 + q0 + rows - 1;   // position of the last query row
+    // MMA row r -> row of the [T][n_q] tensors, and its position
+    auto flat_row = [&](int r) { return a.packed ? size_t(r / G) * a.n_q + hkv * G + r % G : size_t(q0 + r) * a.n_q + hq; };
+    auto row_pos = [&](int r) { return a.packed ? a.pos0 + r / G : a.pos0 + q0 + r; };
     const int n_tiles_all = last_pos / kKvTile + 1;           // KV tiles [0, n_tiles_all) of this query tile
     // this CTA's share [j0, j0 + n_tiles); below j counts from 0 inside the share
     const int j0 = int(1LL * part * n_tiles_all / parts);
@@ -126,8 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the four threads
     // of a row stores 64 dims
     if (tid < kSoftmaxThreads) {
-        const int part = warp >> 2, r = (warp & 3) * 32 + lane;
-        const __nv_bfloat16* src = a.q + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + part * 64;
+        const int qpart = warp >> 2, r = (warp & 3) * 32 + lane;
+        const __nv_bfloat16* src = a.q + flat_row(r < rows ? r : 0) * kHeadDim + qpart * 64;
         const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
         uint32_t regs[32];
 #pragma unroll
@@ -141,14 +151,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 regs[ch * 4 + e] = pack_h2(f.x, f.y);
             }
         }
-        tc::tmem_st32(lane_addr + kColQ + part * 32, regs);
+        tc::tmem_st32(lane_addr + kColQ + qpart * 32, regs);
         tc::tmem_wait_st();
         tc::fence_before_sync();
         mbar_arrive(&s.bar_q);                                // Q is in tensor memory (awaited by the S issuer)
         if (cta_rec && tid == 0) cta_rec[1] = global_ns();
         // the epilogue's gate rows: start them on their way into L2 now (2 of the row's 8 lines each)
         if (a.gate && a.kv_parts <= 1 && r < rows) {
-            const float* gp = a.gate + (size_t(q0 + r) * a.n_q + hq) * kHeadDim + part * 64;
+            const float* gp = a.gate + flat_row(r) * kHeadDim + qpart * 64;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(gp));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + 32));
         }
@@ -253,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         // The only hand-over between consecutive tiles is the running row maximum (mrow + bar_m).
         const int grp = warp >> 3, half = (warp >> 2) & 1, quad = warp & 3;   // column half, TMEM lane quadrant
         const int r = quad * 32 + lane;                       // query row = TMEM lane
-        const int pos = a.pos0 + q0 + r;                      // its position (rows >= `rows` are padding)
+        const int pos = row_pos(r);                           // its position (rows >= `rows` are padding)
         const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
         const float scale_log2 = a.scale * 1.4426950408889634f;
         float m_known = -1e30f, l_part = 0.f;                 // l_part is relative to m_known
@@ -291,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             }
             // raw scores -> maximum (scale > 0, so the maximum can be taken before scaling);
             // only tiles that reach past the first row's position need the causal mask
-            const bool masked = tok0 + kKvTile - 1 > a.pos0 + q0;
+            const bool masked = tok0 + kKvTile - 1 > row_pos(0);
             float mx = -1e30f;
             if (masked) {
 #pragma unroll
@@ -428,7 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                                     __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             }
             if (split && grp == 0 && half == 0 && r < rows) {
-                float* ml = a.part_ml + ((size_t(part) * a.T + q0 + r) * a.n_q + hq) * 2;
+                float* ml = a.part_ml + (size_t(part) * a.T * a.n_q + flat_row(r)) * 2;
                 ml[0] = m_fin * 0.6931471805599453f;          // log2 domain -> natural-log units
                 ml[1] = l_run;
             }
@@ -436,9 +446,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         named_bar_sync(9, kSoftmaxThreads);
         if (good) {
             for (int row = warp; row < rows; row += kSoftmaxThreads / 32) {
-                float* dst = split ? a.part_o + ((size_t(part) * a.T + q0 + row) * a.n_q + hq) * kHeadDim
-                                   : a.o + (size_t(q0 + row) * a.n_q + hq) * kHeadDim;
-                const float* gp = (a.gate && !split) ? a.gate + (size_t(q0 + row) * a.n_q + hq) * kHeadDim : nullptr;
+                float* dst = split ? a.part_o + (size_t(part) * a.T * a.n_q + flat_row(row)) * kHeadDim
+                                   : a.o + flat_row(row) * kHeadDim;
+                const float* gp = (a.gate && !split) ? a.gate + flat_row(row) * kHeadDim : nullptr;
 #pragma unroll
                 for (int hcol = 0; hcol < 2; ++hcol) {
                     const int c = hcol * 128 + lane * 4;

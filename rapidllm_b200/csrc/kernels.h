@@ -48,6 +48,7 @@ struct AttnPrefillArgs {
     int kv_parts;
     float* part_o;
     float* part_ml;
+    int packed;                  // T * (n_q / n_kv) <= 128: one item per KV head, MMA rows = (token, head of the group)
     unsigned long long* trace;   // development aid: null, or room for 8 timestamps x 64 tiles of CTA (0,0) + 4 words per CTA
 };
 __global__ void attn_prefill_kernel(AttnPrefillArgs a);
