@@ -390,6 +390,7 @@ typedef struct rl_plan_input {
     int page_tokens;             /* 64 */
     int kv_policy;               /* RL_KV_POLICY_* */
     int allow_shrink;            /* != 0: reduce ctx to what fits instead of refusing */
+    int prefill_chunk;           /* longest prefill chunk (the engine's pf_cap_); 0 = 1024 */
 } rl_plan_input;
 typedef struct rl_plan_result {
     int ok;                      /* 0: does not fit (message says why), like PlannerResult.ok */
@@ -398,6 +399,12 @@ typedef struct rl_plan_result {
     int max_pages_per_seq;
     int n_pages;                 /* per attention layer pool: max_batch * max_pages_per_seq */
     unsigned long long kv_bytes, state_bytes, need_bytes;
+    /* With the compact cache the engine also keeps an F16 compute window over the first
+     * min(ctx, max(8192, 2 * prefill_chunk)) tokens of every sequence and attends over it while
+     * a sequence still fits (cuda_engine.cu:20118-20123, 18948, 18487-18493); 0 with F16 KV.
+     * kv_bytes counts both. */
+    int window_tokens, window_pages_per_seq;
+    unsigned long long window_bytes;
     char message[160];
 } rl_plan_result;
 /* Host-only arithmetic (no device call); returns RL_OK when the plan was computed (see

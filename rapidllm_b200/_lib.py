@@ -68,12 +68,14 @@ class AttnQkPrepareParams(C.Structure):
 class PlanInput(C.Structure):
     _fields_ = [("weight_bytes", C.c_ulonglong), ("available_bytes", C.c_ulonglong), ("pad_bytes", C.c_ulonglong)] + [
         (n, C.c_int) for n in ("ctx", "max_batch", "n_attn_layers", "n_kv", "head_dim", "n_delta_layers", "n_v",
-                               "dk", "dv", "conv_dim", "conv_k", "page_tokens", "kv_policy", "allow_shrink")]
+                               "dk", "dv", "conv_dim", "conv_k", "page_tokens", "kv_policy", "allow_shrink",
+                               "prefill_chunk")]
 
 
 class PlanResult(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("ok", "kv_dtype", "ctx", "max_pages_per_seq", "n_pages")] + [
         ("kv_bytes", C.c_ulonglong), ("state_bytes", C.c_ulonglong), ("need_bytes", C.c_ulonglong),
+        ("window_tokens", C.c_int), ("window_pages_per_seq", C.c_int), ("window_bytes", C.c_ulonglong),
         ("message", C.c_char * 160)]
 
 

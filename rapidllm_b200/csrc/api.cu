@@ -961,27 +961,43 @@ int rl_plan_cache(const rl_plan_input* in, rl_plan_result* out) {
                        (u64(in->n_v) * in->dk * in->dv * 4 + u64(in->conv_dim) * in->conv_k * 4);
     const u64 fixed = in->weight_bytes + out->state_bytes + in->pad_bytes;
     auto pages_for = [&](int ctx) { return u64((ctx + in->page_tokens - 1) / in->page_tokens); };
-    auto fits = [&](u64 page_bytes, int ctx) {
-        return !in->available_bytes || fixed + page_bytes * pages_for(ctx) * in->max_batch <= in->available_bytes;
+    // the compact cache carries an F16 window over the first tokens of every sequence
+    auto window_of = [&](int ctx) { return std::min(ctx, std::max(8192, 2 * (in->prefill_chunk > 0 ? in->prefill_chunk : 1024))); };
+    auto kv_bytes_of = [&](int dtype, int ctx) {
+        if (dtype == RL_KV_F16) return f16_page * pages_for(ctx) * in->max_batch;
+        return (compact_page * pages_for(ctx) + f16_page * pages_for(window_of(ctx))) * in->max_batch;
+    };
+    auto fits = [&](int dtype, int ctx) {
+        return !in->available_bytes || fixed + kv_bytes_of(dtype, ctx) <= in->available_bytes;
     };
     int dtype = in->kv_policy == RL_KV_POLICY_COMPACT ? RL_KV_Q8K_TQ3V : RL_KV_F16;
-    if (in->kv_policy == RL_KV_POLICY_AUTO && !fits(f16_page, in->ctx)) dtype = RL_KV_Q8K_TQ3V;
+    if (in->kv_policy == RL_KV_POLICY_AUTO && !fits(RL_KV_F16, in->ctx)) dtype = RL_KV_Q8K_TQ3V;
     if (dtype == RL_KV_Q8K_TQ3V && in->head_dim != rl::kHeadDim && in->n_attn_layers > 0) {
         if (in->kv_policy == RL_KV_POLICY_COMPACT)
             return fail(RL_ERR_UNSUPPORTED, "the compact cache needs head_dim 256, got %d", in->head_dim);
         dtype = RL_KV_F16;
     }
-    const u64 page_bytes = dtype == RL_KV_F16 ? f16_page : compact_page;
     int ctx = in->ctx;
-    if (!fits(page_bytes, ctx) && in->allow_shrink && in->available_bytes > fixed && page_bytes > 0) {
-        const u64 pages = (in->available_bytes - fixed) / (page_bytes * in->max_batch);
-        ctx = int(std::min<u64>(pages * in->page_tokens, u64(in->ctx)));
+    if (!fits(dtype, ctx) && in->allow_shrink) {
+        // largest whole number of pages per sequence that fits (the window makes the cost piecewise linear)
+        int lo = 0, hi = int(pages_for(in->ctx));
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) / 2;
+            if (fits(dtype, mid * in->page_tokens)) lo = mid;
+            else hi = mid - 1;
+        }
+        ctx = int(std::min<u64>(u64(lo) * in->page_tokens, u64(in->ctx)));
     }
     out->kv_dtype = dtype;
     out->ctx = ctx;
     out->max_pages_per_seq = int(pages_for(std::max(ctx, 1)));
     out->n_pages = out->max_pages_per_seq * in->max_batch;
-    out->kv_bytes = page_bytes * u64(out->n_pages);
+    if (dtype != RL_KV_F16 && ctx > 0) {
+        out->window_tokens = window_of(ctx);
+        out->window_pages_per_seq = int(pages_for(out->window_tokens));
+        out->window_bytes = f16_page * u64(out->window_pages_per_seq) * in->max_batch;
+    }
+    out->kv_bytes = ctx > 0 ? kv_bytes_of(dtype, ctx) : 0;
     out->need_bytes = fixed + out->kv_bytes;
     out->ok = ctx > 0 && (!in->available_bytes || out->need_bytes <= in->available_bytes);
     if (out->ok)

@@ -12,7 +12,7 @@ GIB = 1 << 30
 def _plan(**kw):
     base = dict(weight_bytes=0, available_bytes=0, pad_bytes=64 << 20, ctx=32768, max_batch=1, n_attn_layers=16,
                 n_kv=4, head_dim=256, n_delta_layers=48, n_v=48, dk=128, dv=128, conv_dim=10240, conv_k=4,
-                page_tokens=64, kv_policy=_lib.RL_KV_POLICY_AUTO, allow_shrink=0)
+                page_tokens=64, kv_policy=_lib.RL_KV_POLICY_AUTO, allow_shrink=0, prefill_chunk=0)
     base.update(kw)
     inp, out = _lib.PlanInput(**base), _lib.PlanResult()
     st = _lib.lib().rl_plan_cache(C.byref(inp), C.byref(out))
@@ -38,7 +38,10 @@ def test_policy_and_budget():
     # 262144 tokens x 8 sequences = 128 GiB of F16 KV does not fit next to the weights: compact (22.4 KiB/token)
     st, r = _plan(ctx=262144, max_batch=8, weight_bytes=60 * GIB, available_bytes=180 * 10**9)
     assert r.ok and r.kv_dtype == _lib.RL_KV_Q8K_TQ3V
-    assert r.kv_bytes == 16 * 4 * _lib.lib().rl_kv_compact_page_bytes() * 4096 * 8
+    # ... plus the F16 compute window over the first max(8192, 2 * prefill chunk) tokens of each sequence
+    assert r.window_tokens == 8192 and r.window_pages_per_seq == 128
+    assert r.window_bytes == 16 * 4 * 256 * 2 * 2 * 8192 * 8
+    assert r.kv_bytes == 16 * 4 * _lib.lib().rl_kv_compact_page_bytes() * 4096 * 8 + r.window_bytes
     # forced F16 refuses with the reference's message shape ...
     st, r = _plan(ctx=262144, max_batch=8, weight_bytes=60 * GIB, available_bytes=180 * 10**9,
                   kv_policy=_lib.RL_KV_POLICY_F16)
@@ -51,9 +54,17 @@ def test_policy_and_budget():
     st2, r2 = _plan(ctx=r.ctx + 64, max_batch=8, weight_bytes=60 * GIB, available_bytes=180 * 10**9,
                     kv_policy=_lib.RL_KV_POLICY_F16)
     assert not r2.ok                                        # one more page would not have fitted
-    # forced compact
-    st, r = _plan(kv_policy=_lib.RL_KV_POLICY_COMPACT)
-    assert r.kv_dtype == _lib.RL_KV_Q8K_TQ3V
+    # forced compact; the window follows the prefill chunk and never exceeds ctx
+    st, r = _plan(kv_policy=_lib.RL_KV_POLICY_COMPACT, prefill_chunk=8192)
+    assert r.kv_dtype == _lib.RL_KV_Q8K_TQ3V and r.window_tokens == 16384
+    st, r = _plan(kv_policy=_lib.RL_KV_POLICY_COMPACT, ctx=4096)
+    assert r.window_tokens == 4096 and r.window_pages_per_seq == 64
+    st, r = _plan(kv_policy=_lib.RL_KV_POLICY_COMPACT, ctx=1 << 20, max_batch=8, weight_bytes=60 * GIB,
+                  available_bytes=180 * 10**9, allow_shrink=1)
+    assert r.ok and r.ctx % 64 == 0 and r.need_bytes <= 180 * 10**9 and r.window_tokens == 8192
+    st2, r2 = _plan(kv_policy=_lib.RL_KV_POLICY_COMPACT, ctx=r.ctx + 64, max_batch=8, weight_bytes=60 * GIB,
+                    available_bytes=180 * 10**9)
+    assert not r2.ok
     # nothing left after the weights
     st, r = _plan(weight_bytes=200 * GIB, available_bytes=180 * 10**9, allow_shrink=1)
     assert st == 0 and not r.ok
