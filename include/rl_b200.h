@@ -336,6 +336,11 @@ int rl_attn_qk_prepare(const float* qg, float* k, const float* q_norm, const flo
                        const int32_t* pos, float* q_out, float* gate_out,
                        const rl_attn_qk_prepare_params* p, void* stream);
 
+/* ops::qwen3_rmsnorm (ops.h, ops.cpp:107-127) over rows of n values: the norm in front of a
+ * mixer's projections (ops_fused.cpp:99, 151): y = x / rms(x) * (1 + gamma); gamma [n] or NULL.
+ * x and y may be the same buffer. */
+int rl_rmsnorm(const float* x, const float* gamma, float* y, int rows, int n, float eps, void* stream);
+
 /* ops::gated_rmsnorm in its per-head form (ops.h:22, ops.cpp:129-157), applied to
  * the delta-rule output (ops_fused.cpp:131): y = gamma * (x / rms(x)) * silu(z) per
  * head.  x, z, y [rows][n_heads][head_dim] (head_dim 128); gamma [head_dim] or NULL. */

@@ -256,6 +256,51 @@ class Oracle:
         self.lib.rlo_conv1d_causal_prefill(xp, wp, _ptr(y, C.c_float), seq, dim, w.shape[1])
         return y
 
+    # -- whole decode mixers ---------------------------------------------------
+    def gemv(self, W, x):
+        """rlo_gemv_f32: W [m,n] @ x [n] with a double accumulator in index order."""
+        W, Wp = _f32(W)
+        x, xp = _f32(x)
+        y = np.empty(W.shape[0], np.float32)
+        self.lib.rlo_gemv_f32(Wp, xp, _ptr(y, C.c_float), W.shape[0], W.shape[1])
+        return y
+
+    def fused_delta_decode(self, x, w, S, conv_state, n_k, n_v, dk=128, dv=128, eps=1e-6, v_tiled=False):
+        """One token through a DeltaNet mixer, in the order of ops::fused_delta_decode
+        (src/kernels/ops_fused.cpp:84-135): norm, four projections, conv + SiLU, head repeat and
+        gate maths, the delta rule, gated RMSNorm, output projection, residual.  w: dict of
+        rms_w, Wqkv, Wz, Wa, Wb, Wo, A_log, dt_bias, conv_w, gnorm.  S [n_v,dk,dv] and
+        conv_state [conv_dim,k] are updated in place; returns the new hidden state."""
+        x = np.asarray(x, np.float32)
+        qdim = n_k * dk
+        xn = self.qwen3_rmsnorm(x, w["rms_w"], eps)
+        qkv, z = self.gemv(w["Wqkv"], xn), self.gemv(w["Wz"], xn)
+        aa, bb = self.gemv(w["Wa"], xn), self.gemv(w["Wb"], xn)
+        mixed = self.conv1d_update(qkv, w["conv_w"], conv_state)
+        qh = self.repeat_heads(mixed[:qdim].reshape(n_k, dk), n_v, v_tiled)
+        kh = self.repeat_heads(mixed[qdim:2 * qdim].reshape(n_k, dk), n_v, v_tiled)
+        vh = mixed[2 * qdim:].reshape(n_v, dv)
+        beta, g = self.delta_gates(aa, bb, w["A_log"], w["dt_bias"])
+        o = self.delta_step(S, qh, kh, vh, beta, g, 1e-6)
+        og = self.gated_rmsnorm(o.reshape(-1), z, w["gnorm"], 1e-6)
+        return x + self.gemv(w["Wo"], og)
+
+    def fused_attn_decode(self, x, w, k_cache, v_cache, pos, n_q, n_kv, hd=256, rotary_dim=64, theta=1e7,
+                          eps=1e-6):
+        """One token through a gated-attention mixer, in the order of ops::fused_attn_decode
+        (src/kernels/ops_fused.cpp:137-182).  w: dict of rms_w, Wq ([q | gate] rows per head), Wk,
+        Wv, Wo, q_norm, k_norm.  k_cache, v_cache fp32 [ctx,n_kv,hd] get row pos; returns the
+        new hidden state."""
+        x = np.asarray(x, np.float32)
+        xn = self.qwen3_rmsnorm(x, w["rms_w"], eps)
+        qg = self.gemv(w["Wq"], xn).reshape(n_q, 2 * hd)
+        k = self.gemv(w["Wk"], xn).reshape(n_kv, hd)
+        v = self.gemv(w["Wv"], xn).reshape(n_kv, hd)
+        q, gate, k = self.attn_qk_prepare(qg, k, w["q_norm"], w["k_norm"], pos, rotary_dim, theta, eps)
+        k_cache[pos], v_cache[pos] = k, v
+        o = self.gated_attn_decode(q, k_cache[:pos + 1], v_cache[:pos + 1], gate)
+        return x + self.gemv(w["Wo"], o.reshape(-1))
+
     # -- compact KV ------------------------------------------------------------
     def centroids(self):
         return np.ctypeslib.as_array(self.lib.rlo_tq3_centroids(), shape=(8,)).copy()
@@ -394,6 +439,31 @@ class Reference:
         y = np.empty_like(x)
         self.lib.ref_gated_rmsnorm(xp, zp, gp, _ptr(y, C.c_float), x.size, C.c_float(eps), g.size)
         return y
+
+    def fused_delta_decode(self, x, w, S, conv_state, n_k, n_v, dk=128, dv=128, eps=1e-6, v_tiled=False,
+                           simd=False):
+        """ops::fused_delta_decode with dense fp32 weights; S and conv_state updated in place."""
+        assert S.dtype == np.float32 and S.flags.c_contiguous
+        assert conv_state.dtype == np.float32 and conv_state.flags.c_contiguous
+        x = np.array(x, np.float32, order="C")
+        keep = [_f32(w[n]) for n in ("rms_w", "Wqkv", "Wz", "Wa", "Wb", "Wo", "A_log", "dt_bias", "conv_w",
+                                     "gnorm")]
+        self.lib.ref_fused_delta_decode(_ptr(x, C.c_float), *[p for _, p in keep], _ptr(S, C.c_float),
+                                        _ptr(conv_state, C.c_float), x.size, n_k, n_v, dk, dv,
+                                        conv_state.shape[1], C.c_float(eps), int(simd), int(v_tiled))
+        return x
+
+    def fused_attn_decode(self, x, w, k_cache, v_cache, pos, n_q, n_kv, hd=256, rotary_dim=64, theta=1e7,
+                          eps=1e-6, simd=False):
+        """ops::fused_attn_decode with dense fp32 weights; the caches get row pos."""
+        assert k_cache.dtype == np.float32 and k_cache.flags.c_contiguous
+        assert v_cache.dtype == np.float32 and v_cache.flags.c_contiguous
+        x = np.array(x, np.float32, order="C")
+        keep = [_f32(w[n]) for n in ("rms_w", "Wq", "Wk", "Wv", "Wo", "q_norm", "k_norm")]
+        self.lib.ref_fused_attn_decode(_ptr(x, C.c_float), *[p for _, p in keep], _ptr(k_cache, C.c_float),
+                                       _ptr(v_cache, C.c_float), x.size, n_q, n_kv, hd, int(rotary_dim),
+                                       int(pos), C.c_float(theta), C.c_float(eps), int(simd))
+        return x
 
     def l2norm(self, x, eps=1e-6):
         x, xp = _f32(x)

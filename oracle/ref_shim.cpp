@@ -61,6 +61,74 @@ void ref_rope_partial(float* q, float* k, int n_q, int n_kv, int head_dim, int r
     ops::rope_partial(q, k, n_q, n_kv, head_dim, rotary_dim, pos, theta);
 }
 
+// The whole decode mixers (ops::fused_delta_decode / fused_attn_decode, ops_fused.cpp:84-182) with
+// dense fp32 weights: norm, projections, the operator, output projection, residual.
+static ops::QuantW dense(const float* w) {
+    ops::QuantW q;
+    q.data = reinterpret_cast<const uint8_t*>(w);
+    return q;
+}
+
+void ref_fused_delta_decode(float* x, const float* rms_w, const float* Wqkv, const float* Wz, const float* Wa,
+                            const float* Wb, const float* Wo, const float* A_log, const float* dt_bias,
+                            const float* conv_w, const float* gnorm, float* S, float* conv_state, int hidden,
+                            int nk, int nv, int dk, int dv, int conv_k, float eps, int use_simd, int v_tiled) {
+    ops::FusedDeltaArgs a{};
+    a.x = x;
+    a.x_inout = x;
+    a.rms_w = rms_w;
+    a.Wqkv = dense(Wqkv);
+    a.Wz = dense(Wz);
+    a.Wa = dense(Wa);
+    a.Wb = dense(Wb);
+    a.Wo = dense(Wo);
+    a.A_log = A_log;
+    a.dt_bias = dt_bias;
+    a.conv_w = conv_w;
+    a.gnorm = gnorm;
+    a.S = S;
+    a.conv_state = conv_state;
+    a.hidden = hidden;
+    a.nk = nk;
+    a.nv = nv;
+    a.dk = dk;
+    a.dv = dv;
+    a.conv_k = conv_k;
+    a.gnorm_n = dv;
+    a.eps = eps;
+    a.use_simd = use_simd != 0;
+    a.v_tiled = v_tiled != 0;
+    ops::fused_delta_decode(a);
+}
+
+void ref_fused_attn_decode(float* x, const float* rms_w, const float* Wq, const float* Wk, const float* Wv,
+                           const float* Wo, const float* q_norm, const float* k_norm, float* k_cache,
+                           float* v_cache, int hidden, int n_q, int n_kv, int head_dim, int rotary_dim, int pos,
+                           float theta, float eps, int use_simd) {
+    ops::FusedAttnArgs a{};
+    a.x = x;
+    a.x_inout = x;
+    a.rms_w = rms_w;
+    a.Wq = dense(Wq);
+    a.Wk = dense(Wk);
+    a.Wv = dense(Wv);
+    a.Wo = dense(Wo);
+    a.q_norm = q_norm;
+    a.k_norm = k_norm;
+    a.k_cache = k_cache;
+    a.v_cache = v_cache;
+    a.hidden = hidden;
+    a.n_q = n_q;
+    a.n_kv = n_kv;
+    a.head_dim = head_dim;
+    a.rotary_dim = rotary_dim;
+    a.pos = pos;
+    a.theta = theta;
+    a.eps = eps;
+    a.use_simd = use_simd != 0;
+    ops::fused_attn_decode(a);
+}
+
 void ref_set_threads(int n) { set_num_threads(n); }
 int ref_num_threads(void) { return num_threads(); }
 

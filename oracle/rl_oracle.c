@@ -294,6 +294,18 @@ RLO_API void rlo_delta_gates(const float* a, const float* b, const float* A_log,
     }
 }
 
+/* Dense projection, scalar path of src/kernels/ops.cpp:165-172 (gemv_f32_scalar, what
+ * gemv_w calls without SIMD, ops_fused.cpp:36-41): y[i] = (float) sum_j (double) W[i][j] x[j],
+ * summed in index order. */
+RLO_API void rlo_gemv_f32(const float* W, const float* x, float* y, int m, int n) {
+    for (int i = 0; i < m; ++i) {
+        double acc = 0;
+        const float* row = W + (size_t)i * n;
+        for (int j = 0; j < n; ++j) acc += (double)row[j] * x[j];
+        y[i] = (float)acc;
+    }
+}
+
 /* Head RMSNorm with the (1 + gamma) weight, scalar path of src/kernels/ops.cpp:107-127:
  * double sum of squares, inv = 1 / sqrtf((float)(acc / n) + eps), y = x * inv * (1 + gamma). */
 RLO_API void rlo_qwen3_rmsnorm(const float* x, const float* gamma, float* y, int n, float eps) {

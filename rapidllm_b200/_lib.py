@@ -130,6 +130,7 @@ SYMBOLS = {
     "rl_plan_cache": (_i, [C.POINTER(PlanInput), C.POINTER(PlanResult)]),
     "rl_attn_qk_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnQkPrepareParams), _vp]),
     "rl_gated_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, _vp]),
+    "rl_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, C.c_float, _vp]),
     "rl_delta_gates": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "rl_cache_create": (_i, [C.POINTER(CacheConfig), C.POINTER(_vp)]),
     "rl_cache_destroy": (None, [_vp]),

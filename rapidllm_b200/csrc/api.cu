@@ -827,6 +827,17 @@ int rl_attn_qk_prepare(const float* qg, float* k, const float* q_norm, const flo
     return RL_OK;
 }
 
+int rl_rmsnorm(const float* x, const float* gamma, float* y, int rows, int n, float eps, void* stream) {
+    if (rows < 0 || n <= 0) return fail(RL_ERR_RANGE, "rows %d n %d", rows, n);
+    if (rows == 0) return RL_OK;
+    if (!x || !y) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::rmsnorm_kernel<<<rows, 256, 0, as_stream(stream)>>>(x, gamma, y, n, eps);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
 int rl_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* y, int rows, int n_heads,
                      int head_dim, float eps, void* stream) {
     if (head_dim != 128) return fail(RL_ERR_UNSUPPORTED, "head_dim %d: only 128", head_dim);

@@ -163,6 +163,7 @@ struct GatedRmsnormArgs {
     float eps;
 };
 __global__ void gated_rmsnorm_kernel(GatedRmsnormArgs a);
+__global__ void rmsnorm_kernel(const float* x, const float* gamma, float* y, int n, float eps);
 __global__ void delta_gates_kernel(const float* a_in, const float* b_in, const float* A_log, const float* dt_bias,
                                    float* beta, float* g_log, int n_v, int rows);
 

@@ -88,6 +88,18 @@ __global__ void __launch_bounds__(128) gated_rmsnorm_kernel(GatedRmsnormArgs a) 
     a.y[i] = (a.gamma ? a.gamma[d] : 1.f) * (x * inv) * sz;
 }
 
+// grid rows, block 256: y = x * inv_rms * (1 + gamma) over rows of n values (the pre-mixer norm of the hidden state).
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const float* gamma, float* y, int n, float eps) {
+    __shared__ double red[8];
+    const float* xr = x + size_t(blockIdx.x) * n;
+    float* yr = y + size_t(blockIdx.x) * n;
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) acc += double(xr[i]) * xr[i];
+    acc = block_sum(acc, red);
+    const float inv = 1.f / sqrtf(float(acc / n) + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) yr[i] = xr[i] * inv * (gamma ? 1.f + gamma[i] : 1.f);
+}
+
 // one thread per (row, value head)
 __global__ void delta_gates_kernel(const float* a_in, const float* b_in, const float* A_log, const float* dt_bias,
                                    float* beta, float* g_log, int n_v, int rows) {

@@ -315,6 +315,16 @@ def attn_qk_prepare(qg, k, q_norm=None, k_norm=None, pos=None, pos0=0, rotary_di
     return q, gate
 
 
+def rmsnorm(x, gamma=None, eps=1e-6, out=None):
+    """ops::qwen3_rmsnorm over the last dimension: x / rms(x) * (1 + gamma)."""
+    _need(x, torch.float32, "x")
+    _need(gamma, torch.float32, "gamma")
+    y = torch.empty_like(x) if out is None else out
+    n = x.shape[-1]
+    check(lib().rl_rmsnorm(_p(x), _p(gamma), _p(y), x.numel() // n, n, eps, _stream()))
+    return y
+
+
 def gated_rmsnorm(x, z, gamma=None, eps=1e-6):
     """ops::gated_rmsnorm per head: x, z [rows][n_heads][128], gamma [128] -> y."""
     for t, n in ((x, "x"), (z, "z"), (gamma, "gamma")):

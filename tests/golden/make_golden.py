@@ -155,6 +155,51 @@ def main():
         out[f"gnorm_{tag}_x"], out[f"gnorm_{tag}_z"], out[f"gnorm_{tag}_gamma"] = x, z, gm
         out[f"gnorm_{tag}_y"] = ref.gated_rmsnorm(x, z, gm)
 
+    # the whole decode mixers (ops::fused_delta_decode / fused_attn_decode) with dense fp32 weights,
+    # three tokens each.  The reference's own switch RAPIDLLM_SIMD=scalar selects its scalar norm
+    # (its qwen3_rmsnorm otherwise takes the AVX kernel for n >= 64, whose summation order differs
+    # by an ulp); the vectors above were made without it and do not move.
+    os.environ["RAPIDLLM_SIMD"] = "scalar"
+    rng3 = np.random.default_rng(20242)
+    f = lambda *shape: rng3.standard_normal(shape, dtype=np.float32)  # noqa: E731
+    hidden, nk, nv, dk, dv, ck = 32, 1, 3, 128, 128, 4
+    cd = 2 * nk * dk + nv * dv
+    for tag, tiled in {"grouped": False, "tiled": True}.items():
+        w = dict(rms_w=f(hidden) * 0.1, Wqkv=f(cd, hidden) / 6, Wz=f(nv * dv, hidden) / 6, Wa=f(nv, hidden) / 6,
+                 Wb=f(nv, hidden) / 6, Wo=f(hidden, nv * dv) / 20, A_log=f(nv) * 0.5, dt_bias=f(nv),
+                 conv_w=f(cd, ck) * 0.5, gnorm=f(dv))
+        S = np.zeros((nv, dk, dv), np.float32)
+        conv = np.zeros((cd, ck), np.float32)
+        x = f(hidden)
+        for name, arr in w.items():
+            out[f"mixer_delta_{tag}_{name}"] = arr
+        out[f"mixer_delta_{tag}_x"] = x
+        xs = []
+        for _ in range(3):
+            x = ref.fused_delta_decode(x, w, S, conv, nk, nv, dk, dv, v_tiled=tiled)
+            xs.append(x.copy())
+        out[f"mixer_delta_{tag}_x_out"] = np.stack(xs)
+        out[f"mixer_delta_{tag}_S_out"], out[f"mixer_delta_{tag}_conv_out"] = S, conv
+        if tag == "grouped":     # nk = 1 makes both head maps equal; the tiled case uses nk = 2 below
+            nk, nv = 2, 4
+            cd = 2 * nk * dk + nv * dv
+    n_q, n_kv, hd = 2, 1, 256
+    w = dict(rms_w=f(hidden) * 0.1, Wq=f(n_q * 2 * hd, hidden) / 6, Wk=f(n_kv * hd, hidden) / 6,
+             Wv=f(n_kv * hd, hidden) / 6, Wo=f(hidden, n_q * hd) / 20, q_norm=f(hd) * 0.1, k_norm=f(hd) * 0.1)
+    kc = np.zeros((4, n_kv, hd), np.float32)
+    vc = np.zeros((4, n_kv, hd), np.float32)
+    x = f(hidden)
+    for name, arr in w.items():
+        out[f"mixer_attn_{name}"] = arr
+    out["mixer_attn_x"] = x
+    xs = []
+    for pos in range(3):
+        x = ref.fused_attn_decode(x, w, kc, vc, pos, n_q, n_kv, hd)
+        xs.append(x.copy())
+    out["mixer_attn_x_out"] = np.stack(xs)
+    out["mixer_attn_k_cache"], out["mixer_attn_v_cache"] = kc, vc
+    del os.environ["RAPIDLLM_SIMD"]
+
     path = os.path.join(HERE, "ref_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

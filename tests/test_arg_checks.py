@@ -35,6 +35,8 @@ def test_null_params_and_bad_shapes_are_refused():
                                       None) == RANGE
     assert L.rl_gated_rmsnorm(None, None, None, None, 1, 48, 64, 1e-6, None) == UNSUPPORTED
     assert L.rl_delta_gates(None, None, None, None, None, None, -1, 48, None) == RANGE
+    assert L.rl_rmsnorm(None, None, None, 1, 0, 1e-6, None) == RANGE
+    assert L.rl_rmsnorm(None, None, None, 1, 8, 1e-6, None) == RANGE
     qp = _lib.AttnQkPrepareParams(n_q=24, n_kv=4, head_dim=256, rotary_dim=63, rows=1, pos0=0, theta=1e7, eps=1e-6)
     assert L.rl_attn_qk_prepare(None, None, None, None, None, None, None, C.byref(qp), None) == RANGE
     assert L.rl_kv_compact_to_f16(None, None, 0, 1, None, None, None, 0, 1, 4, 4, 100, None, None) == UNSUPPORTED
@@ -50,6 +52,7 @@ def test_zero_sized_calls_are_no_ops():
     assert L.rl_attn_prefill(None, None, None, None, None, None, None, None, C.byref(pp), None) == 0
     assert L.rl_gated_rmsnorm(None, None, None, None, 0, 48, 128, 1e-6, None) == 0
     assert L.rl_delta_gates(None, None, None, None, None, None, 0, 48, None) == 0
+    assert L.rl_rmsnorm(None, None, None, 0, 8, 1e-6, None) == 0
     dp = _lib.DeltaRecurrentParams(n_v=48, dk=128, dv=128, eps_l2=1e-6, batch=0, n_slots=1, n_qk=16, head_map=1)
     assert L.rl_delta_recurrent(None, None, None, None, None, None, None, None, C.byref(dp), None) == 0
     assert L.rl_delta_recurrent_multi(None, None, None, None, None, None, None, None, None, C.byref(dp), 0, 0, 0,

@@ -70,3 +70,21 @@ def test_gated_rmsnorm_and_gates_match_oracle(oracle, rows):
         beta_ref, g_ref = oracle.delta_gates(a[r].numpy(), b[r].numpy(), A_log.numpy(), dt.numpy())
         assert rel_l2(beta[r].cpu().numpy(), beta_ref) <= 1e-6
         assert rel_l2(g[r].cpu().numpy(), g_ref) <= 1e-6
+
+
+def test_hidden_rmsnorm(oracle):
+    """rl_rmsnorm over rows of the hidden size (the norm in front of a mixer's projections), also in place."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(77)
+    for n in (5120, 96, 1):
+        x = torch.randn(5, n, generator=gen) * 3.0
+        gamma = torch.randn(n, generator=gen) * 0.1
+        y = ops.rmsnorm(x.cuda(), gamma.cuda())
+        y0 = ops.rmsnorm(x.cuda(), None)
+        xi = x.cuda()
+        ops.rmsnorm(xi, gamma.cuda(), out=xi)
+        _lib.check_device()
+        ref = oracle.qwen3_rmsnorm(x.numpy(), gamma.numpy())
+        assert np.abs(y.cpu().numpy() - ref).max() <= 2e-6 * max(1.0, np.abs(ref).max())
+        assert torch.equal(xi, y)
+        assert np.abs(y0.cpu().numpy() - oracle.qwen3_rmsnorm(x.numpy(), None)).max() <= 2e-6 * np.abs(ref).max() + 2e-6

@@ -1,0 +1,102 @@
+"""Whole decode mixers (rapidllm_b200/mixer.py) against the oracle's restatement of
+ops::fused_delta_decode / fused_attn_decode (src/kernels/ops_fused.cpp:84-182), which the CPU suite
+pins bit for bit on the reference's outputs.  Model shapes of the operators (16/48 heads of 128,
+24/4 heads of 256), a reduced hidden size to keep the oracle's scalar projections short.
+
+Tolerances: the projections run as fp32 library GEMMs (fp32 accumulation in another order than the
+oracle's double accumulator) in front of and behind the operators, so the hidden state is compared
+with the attention tolerance (max-abs 2e-2, rel-L2 1e-3) per step and the DeltaNet state with
+rel-L2 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import ATTN_MAX_ABS, ATTN_REL_L2, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+HIDDEN = 512
+
+
+def _f(rs, *shape):
+    return rs.standard_normal(shape).astype(np.float32)
+
+
+def test_deltanet_mixer_steps(oracle):
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.mixer import DeltaNetMixer
+    torch.backends.cuda.matmul.allow_tf32 = False
+    rs = np.random.RandomState(41)
+    nk, nv = 16, 48
+    cd = 2 * nk * 128 + nv * 128
+    w = dict(rms_w=_f(rs, HIDDEN) * 0.1, Wqkv=_f(rs, cd, HIDDEN) / 20, Wz=_f(rs, nv * 128, HIDDEN) / 20,
+             Wa=_f(rs, nv, HIDDEN) / 20, Wb=_f(rs, nv, HIDDEN) / 20, Wo=_f(rs, HIDDEN, nv * 128) / 80,
+             A_log=_f(rs, nv) * 0.5, dt_bias=_f(rs, nv), conv_w=_f(rs, cd, 4) * 0.5, gnorm=_f(rs, 128))
+    for head_map, tiled in ((_lib.RL_HEADS_GROUPED, False), (_lib.RL_HEADS_TILED, True)):
+        B = 3
+        mix = DeltaNetMixer(w, nk, nv, n_slots=5, head_map=head_map)
+        slots = torch.tensor([4, 0, 2], dtype=torch.int32, device="cuda")
+        x = _f(rs, B, HIDDEN)
+        xd = torch.from_numpy(x).cuda()
+        S = [np.zeros((nv, 128, 128), np.float32) for _ in range(B)]
+        conv = [np.zeros((cd, 4), np.float32) for _ in range(B)]
+        for step in range(4):
+            xd = mix.decode(xd, slots)
+            _lib.check_device()
+            got = xd.cpu().numpy()
+            for b in range(B):
+                x[b] = oracle.fused_delta_decode(x[b], w, S[b], conv[b], nk, nv, v_tiled=tiled)
+                assert np.abs(got[b] - x[b]).max() <= ATTN_MAX_ABS and rel_l2(got[b], x[b]) <= ATTN_REL_L2, \
+                    (tiled, step, b, np.abs(got[b] - x[b]).max(), rel_l2(got[b], x[b]))
+            xd = torch.from_numpy(x).cuda()          # same inputs every step: errors do not compound
+        for b, s in enumerate([4, 0, 2]):
+            assert rel_l2(mix.S[s].cpu().numpy(), S[b]) <= 1e-5
+            assert np.abs(mix.conv_state[s].cpu().numpy() - conv[b]).max() <= 1e-4
+        assert not mix.S[1].any() and not mix.S[3].any()
+        print("deltanet mixer tiled=%s: x max-abs %.2e rel-l2 %.2e, S rel-l2 %.2e" %
+              (tiled, np.abs(got - x).max(), rel_l2(got, x), rel_l2(mix.S[4].cpu().numpy(), S[0])))
+
+
+def test_attention_mixer_steps(oracle):
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.mixer import GatedAttentionMixer
+    torch.backends.cuda.matmul.allow_tf32 = False
+    rs = np.random.RandomState(42)
+    n_q, n_kv, hd = 24, 4, 256
+    w = dict(rms_w=_f(rs, HIDDEN) * 0.1, Wq=_f(rs, n_q * 2 * hd, HIDDEN) / 20, Wk=_f(rs, n_kv * hd, HIDDEN) / 20,
+             Wv=_f(rs, n_kv * hd, HIDDEN) / 20, Wo=_f(rs, HIDDEN, n_q * hd) / 80, q_norm=_f(rs, hd) * 0.1,
+             k_norm=_f(rs, hd) * 0.1)
+    B, start = 2, [62, 5000]                      # one sequence crosses a page edge; one far out for RoPE
+    max_pages = 80
+    mix = GatedAttentionMixer(w, n_pages=B * max_pages + 3)
+    perm = torch.randperm(B * max_pages + 3, generator=torch.Generator().manual_seed(1)).int()
+    table = perm[:B * max_pages].view(B, max_pages).contiguous().cuda()
+    # caches of earlier tokens: random rows in both the oracle's contiguous caches and the pages
+    kc = [np.zeros((start[b] + 4, n_kv, hd), np.float32) for b in range(B)]
+    vc = [np.zeros((start[b] + 4, n_kv, hd), np.float32) for b in range(B)]
+    from rapidllm_b200 import ops
+    for b in range(B):
+        k0, v0 = _f(rs, start[b], n_kv, hd), _f(rs, start[b], n_kv, hd)
+        k0, v0 = k0.astype(np.float16).astype(np.float32), v0.astype(np.float16).astype(np.float32)
+        kc[b][:start[b]], vc[b][:start[b]] = k0, v0
+        ops.kv_append(mix.k_pool, mix.v_pool, table[b], torch.from_numpy(k0).cuda(), torch.from_numpy(v0).cuda(),
+                      pos0=0)
+    x = _f(rs, B, HIDDEN)
+    for step in range(4):
+        pos = [s + step for s in start]
+        got = mix.decode(torch.from_numpy(x).cuda(), table, torch.tensor(pos, dtype=torch.int32, device="cuda"))
+        _lib.check_device()
+        got = got.cpu().numpy()
+        for b in range(B):
+            x[b] = oracle.fused_attn_decode(x[b], w, kc[b], vc[b], pos[b], n_q, n_kv)
+            # the device cache holds fp16 rows: round the oracle's new rows the same way for later steps
+            kc[b][pos[b]] = kc[b][pos[b]].astype(np.float16).astype(np.float32)
+            vc[b][pos[b]] = vc[b][pos[b]].astype(np.float16).astype(np.float32)
+            assert np.abs(got[b] - x[b]).max() <= ATTN_MAX_ABS and rel_l2(got[b], x[b]) <= ATTN_REL_L2, \
+                (step, b, np.abs(got[b] - x[b]).max(), rel_l2(got[b], x[b]))
+    print("attention mixer: x max-abs %.2e rel-l2 %.2e" % (np.abs(got - x).max(), rel_l2(got, x)))
+    # the appended rows equal the oracle's, rounded to fp16
+    for b in range(B):
+        n = start[b] + 4
+        kd = ops.kv_gather(mix.k_pool, table[b], n).float().cpu().numpy()
+        assert np.abs(kd - kc[b][:n]).max() <= 2e-3

@@ -195,3 +195,68 @@ def test_compact_kv_properties(oracle, wht_len, use_signs):
         idx = (w >> (3 * j)) & 7
         assert idx == np.argmin(np.abs(yb[j] / r - cent)) or \
             abs(abs(yb[j] / r - cent[idx]) - np.abs(yb[j] / r - cent).min()) < 1e-5
+
+
+def _mixer_weights(golden, prefix, names):
+    return {n: golden[f"{prefix}_{n}"] for n in names}
+
+
+DELTA_W = ("rms_w", "Wqkv", "Wz", "Wa", "Wb", "Wo", "A_log", "dt_bias", "conv_w", "gnorm")
+ATTN_W = ("rms_w", "Wq", "Wk", "Wv", "Wo", "q_norm", "k_norm")
+
+
+def test_whole_mixers_bit_exact_vs_reference_golden(oracle, golden):
+    """ops::fused_delta_decode / fused_attn_decode outputs (three tokens, both head maps)."""
+    for tag, (nk, nv, tiled) in {"grouped": (1, 3, False), "tiled": (2, 4, True)}.items():
+        w = _mixer_weights(golden, f"mixer_delta_{tag}", DELTA_W)
+        S = np.zeros((nv, 128, 128), np.float32)
+        conv = np.zeros_like(golden[f"mixer_delta_{tag}_conv_out"])
+        x = golden[f"mixer_delta_{tag}_x"]
+        for t in range(3):
+            x = oracle.fused_delta_decode(x, w, S, conv, nk, nv, v_tiled=tiled)
+            assert np.array_equal(x, golden[f"mixer_delta_{tag}_x_out"][t]), (tag, t)
+        assert np.array_equal(S, golden[f"mixer_delta_{tag}_S_out"])
+        assert np.array_equal(conv, golden[f"mixer_delta_{tag}_conv_out"])
+    w = _mixer_weights(golden, "mixer_attn", ATTN_W)
+    kc, vc = np.zeros((4, 1, 256), np.float32), np.zeros((4, 1, 256), np.float32)
+    x = golden["mixer_attn_x"]
+    for pos in range(3):
+        x = oracle.fused_attn_decode(x, w, kc, vc, pos, 2, 1)
+        assert np.array_equal(x, golden["mixer_attn_x_out"][pos]), pos
+    assert np.array_equal(kc, golden["mixer_attn_k_cache"]) and np.array_equal(vc, golden["mixer_attn_v_cache"])
+
+
+def test_whole_mixers_vs_live_reference(oracle, reference, monkeypatch):
+    """Larger shapes against oracle/_ref: bit for bit with the reference's scalar norm
+    (RAPIDLLM_SIMD=scalar, its own switch), within a few ulp with its AVX norm."""
+    rs = np.random.RandomState(9)
+
+    def f(*shape):
+        return rs.standard_normal(shape).astype(np.float32)
+
+    hidden, nk, nv, n_q, n_kv = 96, 4, 12, 6, 2
+    cd = 2 * nk * 128 + nv * 128
+    wd = dict(rms_w=f(hidden) * 0.1, Wqkv=f(cd, hidden) / 8, Wz=f(nv * 128, hidden) / 8, Wa=f(nv, hidden) / 8,
+              Wb=f(nv, hidden) / 8, Wo=f(hidden, nv * 128) / 20, A_log=f(nv) * 0.5, dt_bias=f(nv),
+              conv_w=f(cd, 4) * 0.5, gnorm=f(128))
+    wa = dict(rms_w=f(hidden) * 0.1, Wq=f(n_q * 512, hidden) / 8, Wk=f(n_kv * 256, hidden) / 8,
+              Wv=f(n_kv * 256, hidden) / 8, Wo=f(hidden, n_q * 256) / 20, q_norm=f(256) * 0.1, k_norm=f(256) * 0.1)
+    x0 = f(hidden)
+    for mode in ("scalar", None):
+        if mode:
+            monkeypatch.setenv("RAPIDLLM_SIMD", mode)
+        else:
+            monkeypatch.delenv("RAPIDLLM_SIMD")
+        S1, S2 = np.zeros((nv, 128, 128), np.float32), np.zeros((nv, 128, 128), np.float32)
+        c1, c2 = np.zeros((cd, 4), np.float32), np.zeros((cd, 4), np.float32)
+        k1, k2, v1, v2 = (np.zeros((6, n_kv, 256), np.float32) for _ in range(4))
+        xa = xb = x0
+        for t in range(5):
+            xa = oracle.fused_delta_decode(xa, wd, S1, c1, nk, nv)
+            xb = reference.fused_delta_decode(xb, wd, S2, c2, nk, nv)
+            xa = oracle.fused_attn_decode(xa, wa, k1, v1, t, n_q, n_kv)
+            xb = reference.fused_attn_decode(xb, wa, k2, v2, t, n_q, n_kv)
+            if mode:
+                assert np.array_equal(xa, xb) and np.array_equal(S1, S2) and np.array_equal(k1, k2), t
+            else:
+                assert np.abs(xa - xb).max() <= 2e-5 * np.abs(xb).max(), t
