@@ -54,7 +54,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--seed", type=int, default=4)
     ap.add_argument("--workload", default="stack",
-                    choices=["stack", "compact_decode", "f16_decode", "delta_step", "attn_prefill", "delta_prefill"],
+                    choices=["stack", "compact_decode", "f16_decode", "delta_step", "attn_prefill", "delta_prefill",
+                             "stack_prefill"],
                     help="stack = the headline workload; the others time one operator at the shapes of "
                          "the single-layer configurations: 131 072-token compact-KV decode, 4 096-token F16 decode, one "
                          "DeltaNet step, 8 192-token prefills (secondary lines, N=1 only)")
@@ -68,7 +69,9 @@ def parse():
     ap.add_argument("--wht-len", type=int, default=128)
     ap.add_argument("--op-batch", type=int, default=0, help="operator workloads: override the batch")
     ap.add_argument("--op-ctx", type=int, default=0, help="operator workloads: override the context")
-    ap.add_argument("--chunk", type=int, default=8192, help="attn_prefill: query rows per call")
+    ap.add_argument("--chunk", type=int, default=None,
+                    help="query rows per prefill call: attn_prefill default 8192, stack_prefill default 1024 "
+                         "(the reference's chunk cap)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of graph replay in the timed region")
@@ -281,6 +284,8 @@ def run_operator(args):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     gen = torch.Generator(device="cuda").manual_seed(args.seed)
     wl = args.workload
+    if args.chunk is None:
+        args.chunk = 1024 if wl == "stack_prefill" else 8192
     if wl == "attn_prefill":
         T = args.op_ctx or 8192
         n_pages = (T + PAGE - 1) // PAGE
@@ -324,6 +329,73 @@ def run_operator(args):
             "roofline": {"bound": "tensor", "kernel": "attn_prefill_kernel", "achieved": achieved, "peak": tpeak,
                          "unit": "TFLOP/s", "frac": achieved / tpeak, "flops_per_step": flops, "traffic": None}}),
             flush=True)
+        return
+    if wl == "stack_prefill":
+        # a prompt of T tokens through all layers' mixers in chunks (the reference's launch_prefill loop);
+        # every chunk reuses one set of synthetic per-layer inputs (values do not change the work)
+        from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+        T, chunk = args.op_ctx or 8192, min(args.chunk, args.op_ctx or 8192)
+        types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
+        pages = (T + PAGE - 1) // PAGE
+        cache = HybridCache(types, n_pages=pages, n_slots=1, max_batch=1, max_pages_per_seq=pages)
+        cg = torch.Generator().manual_seed(args.seed)
+        row = torch.randperm(pages, generator=cg).int().cuda()
+        t = {}
+        for name, (shape, dtype) in cache.prefill_shapes(chunk).items():
+            if name in ("attn_o", "delta_o"):
+                t[name] = torch.empty(shape, dtype=dtype, device="cuda")
+            elif name == "delta_beta":
+                t[name] = torch.sigmoid(torch.randn(shape, device="cuda", generator=gen))
+            elif name == "delta_g":
+                t[name] = -torch.nn.functional.softplus(torch.randn(shape, device="cuda", generator=gen))
+            else:
+                t[name] = (torch.randn(shape, device="cuda", generator=gen) * (0.5 if name == "conv_w" else 1.0)).to(dtype)
+        ws = torch.empty(max(256, max(_lib.lib().rl_stack_prefill_workspace_bytes(cache._h, p0, chunk)
+                                      for p0 in range(0, T, chunk))), dtype=torch.uint8, device="cuda")
+        n_chunks = (T + chunk - 1) // chunk
+
+        def call():
+            for p0 in range(0, T, chunk):
+                n = min(chunk, T - p0)
+                if n == chunk:
+                    cache.prefill(t, row, 0, p0, n, ws)
+                else:
+                    cache.prefill({k_: (v_ if k_ == "conv_w" else v_[:, :n].contiguous()) for k_, v_ in t.items()}, row, 0,
+                                  p0, n, ws)
+        for _ in range(max(3, args.warmup)):
+            call()
+        _lib.check_device()
+        sampler = ClockSampler(0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        _lib.check_device()
+        ms = e0.elapsed_time(e1) / args.steps
+        flops_attn = cache.n_attn * 4.0 * N_Q * HD * T * (T + 1) / 2
+        tpeak = float(peaks.get("bf16_tflops", 1590.0))
+        # per chunk: attention layers 2 launches (KV write, prefill), DeltaNet layers 3 (conv, prepare, scan)
+        launches = n_chunks * (cache.n_attn * 2 + cache.n_delta * 3)
+        print(json.dumps({
+            "metric": "prompt tokens/sec through the hybrid stack's mixers", "value": T / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+            "dtype": "f16 attention (bf16 in) / f16 hi+lo + f32 state DeltaNet",
+            "config": {"workload": "chunked prefill, %d layers (%d attention + %d DeltaNet), one sequence of %d tokens in "
+                       "chunks of %d, mixers only (no projections / MLP)" % (len(types), cache.n_attn, cache.n_delta, T, chunk),
+                       "l2": "per-chunk inputs of all layers (%.1f GB) exceed L2" %
+                             (sum(x.numel() * x.element_size() for x in t.values()) / 1e9)},
+            "clocks": clocks, "gpu_launches": args.steps * launches,
+            "roofline": {"bound": "tensor", "kernel": "attn_prefill_kernel (attention layers only)",
+                         "achieved": flops_attn / (ms * 1e-3) / 1e12, "peak": tpeak, "unit": "TFLOP/s",
+                         "frac": flops_attn / (ms * 1e-3) / 1e12 / tpeak, "flops_per_step": flops_attn, "traffic": None,
+                         "note": "whole-stack time in the denominator; the DeltaNet layers' chunk-to-chunk scan is "
+                                 "latency-bound and takes most of it"}}), flush=True)
         return
     if wl == "delta_prefill":
         T = args.op_ctx or 8192

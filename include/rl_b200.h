@@ -282,6 +282,9 @@ typedef struct rl_delta_chunk_params {
     int chunk;                   /* must be 64 */
     float eps_l2;                /* 1e-6 */
     int n_qk, head_map;          /* as in rl_delta_recurrent_params */
+    long long qk_tok_stride;     /* floats between tokens in q and k; 0 = dense (n_qk * dk) */
+    long long v_tok_stride;      /* floats between tokens in v; 0 = dense (n_v * dv).  With both set
+                                  * q, k, v can be column ranges of the conv output [T][conv_dim] */
 } rl_delta_chunk_params;
 
 size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p);
@@ -375,6 +378,39 @@ typedef struct rl_cache_config {
     int n_slots;                 /* sequences that can hold DeltaNet state */
     int max_batch, max_pages_per_seq, max_seq_len;
 } rl_cache_config;
+
+/* One chunk of one sequence's prompt through every layer: the reference's chunked-prefill driver
+ * (launch_prefill / launch_prefill_chunk, src/kernels/cuda/cuda_engine.cu:18854-18873, 18338-18590)
+ * for the mixers.  Attention layers append the chunk's K/V rows at pos0 .. pos0+T-1 and attend
+ * causally over cache rows [0, pos0+t] (rl_attn_prefill); DeltaNet layers run the causal conv with
+ * the slot's window carried from the previous chunk (rl_conv1d_causal) and T delta-rule steps in
+ * chunked form on the slot's state (rl_delta_chunk_prefill; q | k | v are column ranges of the conv
+ * output).  pos0 == 0 starts the sequence: the slot's state is zeroed and its conv window ignored.
+ * Per-layer tensors are stacked over the layers of a kind, like rl_stack_io:
+ *   attn_q bf16 [n_attn][T][n_q][256], attn_k, attn_v bf16 [n_attn][T][n_kv][256] (normed, rotated),
+ *   attn_gate fp32 [n_attn][T][n_q][256] or NULL, attn_o fp32 [n_attn][T][n_q][256];
+ *   delta_qkv fp32 [n_delta][T][conv_dim] (before the conv), delta_beta, delta_g fp32 [n_delta][T][n_v],
+ *   delta_o fp32 [n_delta][T][n_v][128]; conv_w fp32 [n_delta][conv_dim][k].
+ * After the last chunk rl_stack_decode continues at pos = prompt length with the same page table row
+ * and slot.  workspace: rl_stack_prefill_workspace_bytes(cache, pos0, T) bytes, 256-byte aligned. */
+typedef struct rl_stack_prefill_io {
+    const void* attn_q;
+    const void* attn_k;
+    const void* attn_v;
+    const float* attn_gate;
+    float* attn_o;
+    const float* delta_qkv;
+    const float* delta_beta;
+    const float* delta_g;
+    float* delta_o;
+    const float* conv_w;
+    const int32_t* page_table_row;   /* int32 [max_pages_per_seq] of this sequence, on the device */
+    int slot;                        /* DeltaNet state slot of this sequence */
+    int pos0, T;
+} rl_stack_prefill_io;
+size_t rl_stack_prefill_workspace_bytes(const rl_cache* c, int pos0, int T);
+int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace, size_t workspace_bytes,
+                     void* stream);
 
 /* Memory plan for a cache: PlannerInput / PlannerResult / plan_memory
  * (include/rapidllm/runtime/planner.h:11-33, src/runtime/planner.cpp:28-44) plus the engine's

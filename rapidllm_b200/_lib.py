@@ -53,7 +53,8 @@ class DeltaRecurrentParams(C.Structure):
 
 class DeltaChunkParams(C.Structure):
     _fields_ = [("n_v", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("seq", C.c_int), ("chunk", C.c_int),
-                ("eps_l2", C.c_float), ("n_qk", C.c_int), ("head_map", C.c_int)]
+                ("eps_l2", C.c_float), ("n_qk", C.c_int), ("head_map", C.c_int),
+                ("qk_tok_stride", C.c_longlong), ("v_tok_stride", C.c_longlong)]
 
 
 class Conv1dParams(C.Structure):
@@ -93,6 +94,12 @@ class StackIO(C.Structure):
         "attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta", "delta_g",
         "delta_o", "conv_w", "page_table", "pos", "slot_ids")] + [
         ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int)]
+
+
+class StackPrefillIO(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "attn_q", "attn_k", "attn_v", "attn_gate", "attn_o", "delta_qkv", "delta_beta", "delta_g", "delta_o",
+        "conv_w", "page_table_row")] + [("slot", C.c_int), ("pos0", C.c_int), ("T", C.c_int)]
 
 
 # every symbol include/rl_b200.h declares: name -> (restype, argtypes)
@@ -141,6 +148,8 @@ SYMBOLS = {
     "rl_cache_conv": (_vp, [_vp, _i]),
     "rl_cache_zero": (_i, [_vp, _vp]),
     "rl_stack_decode": (_i, [_vp, C.POINTER(StackIO), _vp]),
+    "rl_stack_prefill_workspace_bytes": (_sz, [_vp, _i, _i]),
+    "rl_stack_prefill": (_i, [_vp, C.POINTER(StackPrefillIO), _vp, _sz, _vp]),
     "rl_stack_decode_host": (_i, [_vp, C.POINTER(StackIO)]),
     "rl_stack_set_conv_w": (_i, [_vp, _vp]),
     "rl_stack_launches_per_step": (_i, [_vp]),

@@ -128,6 +128,39 @@ class HybridCache:
         io = self._io(tensors, batch, True)
         check(lib().rl_stack_decode(self._h, C.byref(io), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
 
+    def prefill_shapes(self, T):
+        """Tensor name -> (shape, dtype) of one prefill chunk's inputs and outputs."""
+        A, D = self.n_attn, self.n_delta
+        bf, f32 = torch.bfloat16, torch.float32
+        return {"attn_q": ((A, T, self.n_q, 256), bf), "attn_k": ((A, T, self.n_kv, 256), bf),
+                "attn_v": ((A, T, self.n_kv, 256), bf), "attn_gate": ((A, T, self.n_q, 256), f32),
+                "attn_o": ((A, T, self.n_q, 256), f32), "delta_qkv": ((D, T, self.conv_dim), f32),
+                "delta_beta": ((D, T, self.n_v), f32), "delta_g": ((D, T, self.n_v), f32),
+                "delta_o": ((D, T, self.n_v, self.dv), f32), "conv_w": ((D, self.conv_dim, self.conv_k), f32)}
+
+    def prefill(self, tensors: dict, page_table_row, slot: int, pos0: int, T: int, workspace=None):
+        """One chunk of one sequence's prompt through every layer (rl_stack_prefill): device tensors
+        shaped as prefill_shapes(T); page_table_row int32 [max_pages_per_seq] on the device."""
+        io = _lib.StackPrefillIO(slot=slot, pos0=pos0, T=T)
+        shapes = self.prefill_shapes(T)
+        for name, (shape, dtype) in shapes.items():
+            x = tensors.get(name)
+            if x is None:
+                continue
+            if not (x.is_cuda and x.is_contiguous() and x.dtype == dtype and tuple(x.shape) == shape):
+                raise _lib.RlError(6, f"{name}: need a contiguous CUDA tensor {shape} of {dtype}")
+            setattr(io, name, x.data_ptr())
+        if not (page_table_row.is_cuda and page_table_row.dtype == torch.int32 and page_table_row.is_contiguous()
+                and page_table_row.numel() == self.max_pages_per_seq):
+            raise _lib.RlError(6, "page_table_row: need int32 [max_pages_per_seq] on the device")
+        io.page_table_row = page_table_row.data_ptr()
+        need = lib().rl_stack_prefill_workspace_bytes(self._h, pos0, T)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=page_table_row.device)
+        check(lib().rl_stack_prefill(self._h, C.byref(io), C.c_void_p(workspace.data_ptr()), workspace.numel(),
+                                     C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return workspace
+
     def set_conv_w(self, host_w: torch.Tensor):
         check(lib().rl_stack_set_conv_w(self._h, C.c_void_p(host_w.data_ptr())))
 

@@ -908,6 +908,10 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     a.n_qk = p->n_qk;
     a.head_map = p->head_map;
     a.eps_l2 = p->eps_l2;
+    a.qk_tok_stride = p->qk_tok_stride ? p->qk_tok_stride : 1LL * p->n_qk * p->dk;
+    a.v_tok_stride = p->v_tok_stride ? p->v_tok_stride : 1LL * p->n_v * p->dv;
+    if ((a.qk_tok_stride | a.v_tok_stride) % 4 || a.qk_tok_stride < 0 || a.v_tok_stride < 0)
+        return fail(RL_ERR_RANGE, "token strides must be non-negative multiples of 4 floats");
     rl::delta_chunk_prepare_kernel<<<dim3(n_chunks, p->n_v), rl::delta_chunk_prepare_threads(),
                                      rl::delta_chunk_prepare_smem_bytes(), as_stream(stream)>>>(a);
     rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(),
@@ -1153,6 +1157,113 @@ static bool same_io(const rl_stack_io& k, const rl_stack_io* io) {
            k.conv_w == io->conv_w && k.page_table == io->page_table && k.pos == io->pos &&
            k.slot_ids == io->slot_ids && k.batch == io->batch && k.attn_ml == io->attn_ml &&
            k.no_append == io->no_append;
+}
+
+namespace {
+
+struct StackPrefillPlan {
+    rl_attn_prefill_params ap;
+    rl_delta_chunk_params dp;
+    size_t mixed_bytes, delta_ws, attn_ws, total;
+};
+
+int stack_prefill_plan(const rl_cache* c, int pos0, int T, StackPrefillPlan* pl) {
+    if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
+    const rl_cache_config& f = c->cfg;
+    if (T < 0 || pos0 < 0 || 1LL * pos0 + T > 1LL * f.max_pages_per_seq * f.page_tokens)
+        return fail(RL_ERR_RANGE, "pos0 %d + T %d exceeds the page table (%d pages)", pos0, T, f.max_pages_per_seq);
+    std::memset(pl, 0, sizeof *pl);
+    pl->ap.n_q = f.n_q;
+    pl->ap.n_kv = f.n_kv;
+    pl->ap.head_dim = f.head_dim;
+    pl->ap.seq = T;
+    pl->ap.br = 128;
+    pl->ap.bc = 64;
+    pl->ap.pos0 = pos0;
+    pl->ap.page_tokens = f.page_tokens;
+    pl->ap.n_pages = f.n_pages;
+    pl->ap.n_table = f.max_pages_per_seq;
+    pl->dp.n_v = f.n_v;
+    pl->dp.dk = f.dk;
+    pl->dp.dv = f.dv;
+    pl->dp.seq = T;
+    pl->dp.chunk = 64;
+    pl->dp.eps_l2 = 1e-6f;
+    pl->dp.n_qk = f.n_k;
+    pl->dp.head_map = f.head_map;
+    pl->dp.qk_tok_stride = pl->dp.v_tok_stride = c->conv_dim;
+    pl->mixed_bytes = c->n_delta ? align_up(size_t(T) * c->conv_dim * sizeof(float), 256) : 0;
+    pl->delta_ws = c->n_delta && T ? align_up(rl_delta_chunk_workspace_bytes(&pl->dp), 256) : 0;
+    pl->attn_ws = c->n_attn && T ? align_up(rl_attn_prefill_workspace_bytes(&pl->ap), 256) : 0;
+    pl->total = pl->mixed_bytes + pl->delta_ws + pl->attn_ws;
+    return RL_OK;
+}
+
+}  // namespace
+
+size_t rl_stack_prefill_workspace_bytes(const rl_cache* c, int pos0, int T) {
+    StackPrefillPlan pl;
+    if (stack_prefill_plan(c, pos0, T, &pl)) return 0;
+    return pl.total;
+}
+
+int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!c || !io) return fail(RL_ERR_RANGE, "NULL argument");
+    StackPrefillPlan pl;
+    if (int st = stack_prefill_plan(c, io->pos0, io->T, &pl)) return st;
+    const rl_cache_config& f = c->cfg;
+    if (io->slot < 0 || io->slot >= f.n_slots) return fail(RL_ERR_RANGE, "slot %d outside [0, %d)", io->slot, f.n_slots);
+    if (io->T == 0) return RL_OK;
+    if (!io->page_table_row && c->n_attn) return fail(RL_ERR_RANGE, "page_table_row is NULL");
+    if (c->n_attn && (!io->attn_q || !io->attn_k || !io->attn_v || !io->attn_o)) return fail(RL_ERR_RANGE, "attention tensors are NULL");
+    if (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w))
+        return fail(RL_ERR_RANGE, "DeltaNet tensors are NULL");
+    if (workspace_bytes < pl.total || (pl.total && !workspace))
+        return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, pl.total);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(RL_ERR_RANGE, "workspace must be 256-byte aligned");
+    cudaStream_t run = as_stream(stream);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    float* mixed = reinterpret_cast<float*>(ws);
+    void* delta_ws = ws + pl.mixed_bytes;
+    void* attn_ws = ws + pl.mixed_bytes + pl.delta_ws;
+    const int T = io->T;
+    const size_t q_sz = size_t(T) * f.n_q * f.head_dim, kv_sz = size_t(T) * f.n_kv * f.head_dim;
+    const size_t qkv_sz = size_t(T) * c->conv_dim, hv_sz = size_t(T) * f.n_v, do_sz = size_t(T) * f.n_v * f.dv;
+    const size_t slot_S = size_t(f.n_v) * f.dk * f.dv, slot_cv = size_t(c->conv_dim) * f.conv_k;
+    const size_t st_elems = size_t(f.n_slots) * slot_S, cv_elems = size_t(f.n_slots) * slot_cv;
+    const uint16_t* aq = static_cast<const uint16_t*>(io->attn_q);
+    const uint16_t* ak = static_cast<const uint16_t*>(io->attn_k);
+    const uint16_t* av = static_cast<const uint16_t*>(io->attn_v);
+    int ai = 0, di = 0;
+    for (int L = 0; L < f.n_layers; ++L) {
+        if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
+            if (int st = attn_prefill_impl(rl_cache_k_pool(c, ai), rl_cache_v_pool(c, ai), io->page_table_row, aq + ai * q_sz,
+                                           ak + ai * kv_sz, av + ai * kv_sz, io->attn_gate ? io->attn_gate + ai * q_sz : nullptr,
+                                           io->attn_o + ai * q_sz, pl.attn_ws ? attn_ws : nullptr, pl.attn_ws, &pl.ap, run))
+                return st;
+            ++ai;
+        } else {
+            float* S = c->S + di * st_elems + io->slot * slot_S;
+            float* cv = c->conv + di * cv_elems + io->slot * slot_cv;
+            // a sequence that starts here starts from a zero state and an empty conv window
+            if (io->pos0 == 0) RL_CUDA(cudaMemsetAsync(S, 0, slot_S * sizeof(float), run));
+            rl_conv1d_params cp;
+            cp.dim = c->conv_dim;
+            cp.k = f.conv_k;
+            cp.silu = 1;
+            cp.batch = 1;
+            cp.n_slots = 1;
+            if (int st = rl_conv1d_causal(io->delta_qkv + di * qkv_sz, io->conv_w + size_t(di) * slot_cv, mixed, cv, T, &cp,
+                                          io->pos0 > 0, run))
+                return st;
+            if (int st = rl_delta_chunk_prefill(S, mixed, mixed + size_t(f.n_k) * f.dk, mixed + 2 * size_t(f.n_k) * f.dk,
+                                                io->delta_beta + di * hv_sz, io->delta_g + di * hv_sz, io->delta_o + di * do_sz,
+                                                delta_ws, pl.delta_ws, &pl.dp, run))
+                return st;
+            ++di;
+        }
+    }
+    return RL_OK;
 }
 
 int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {

@@ -121,8 +121,8 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
             kx[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             qx[u] = kx[u];
             if (t < n_tok) {
-                kx[u] = *reinterpret_cast<const float4*>(a.k + (size_t(t0 + t) * a.n_qk + hs) * kD + lane * 4);
-                qx[u] = *reinterpret_cast<const float4*>(a.q + (size_t(t0 + t) * a.n_qk + hs) * kD + lane * 4);
+                kx[u] = *reinterpret_cast<const float4*>(a.k + size_t(t0 + t) * a.qk_tok_stride + size_t(hs) * kD + lane * 4);
+                qx[u] = *reinterpret_cast<const float4*>(a.q + size_t(t0 + t) * a.qk_tok_stride + size_t(hs) * kD + lane * 4);
             }
         }
 #pragma unroll
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
             const int idx = tid + u * kPrepThreads;
             const int t = idx >> 5, d = (idx & 31) * 4;
             vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < n_tok) vv[u] = *reinterpret_cast<const float4*>(a.v + (size_t(t0 + t) * a.n_v + h) * kD + d);
+            if (t < n_tok) vv[u] = *reinterpret_cast<const float4*>(a.v + size_t(t0 + t) * a.v_tok_stride + size_t(h) * kD + d);
         }
 #pragma unroll
         for (int u = 0; u < kPer; ++u) {

@@ -181,6 +181,7 @@ struct DeltaChunkArgs {
     int* err;
     int T, n_v, n_qk, head_map;
     float eps_l2;
+    long long qk_tok_stride, v_tok_stride;   // floats between tokens in q/k and in v
 };
 __global__ void delta_chunk_prepare_kernel(DeltaChunkArgs a);
 __global__ void delta_chunk_scan_kernel(DeltaChunkArgs a);
