@@ -43,6 +43,9 @@ struct DevInfo {
     int cc_major = 0;
     int* err_ptr = nullptr;
     bool attn_attr = false;
+    // second stream + events for the calls that overlap two of their own kernels (rl_delta_chunk_prefill)
+    cudaStream_t aux = nullptr;
+    cudaEvent_t aux_ev[9] = {};
 };
 std::mutex g_mu;
 DevInfo g_dev[64];
@@ -75,6 +78,10 @@ int dev_info(DevInfo** out) {
                                      int(rl::attn_prefill_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_tq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_tq_smem_bytes())));
+        int lo = 0, hi = 0;
+        RL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        RL_CUDA(cudaStreamCreateWithPriority(&d.aux, cudaStreamNonBlocking, hi));
+        for (cudaEvent_t& e : d.aux_ev) RL_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         d.ready = true;
     }
     *out = &d;
@@ -912,10 +919,36 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     a.v_tok_stride = p->v_tok_stride ? p->v_tok_stride : 1LL * p->n_v * p->dv;
     if ((a.qk_tok_stride | a.v_tok_stride) % 4 || a.qk_tok_stride < 0 || a.v_tok_stride < 0)
         return fail(RL_ERR_RANGE, "token strides must be non-negative multiples of 4 floats");
-    rl::delta_chunk_prepare_kernel<<<dim3(n_chunks, p->n_v), rl::delta_chunk_prepare_threads(),
-                                     rl::delta_chunk_prepare_smem_bytes(), as_stream(stream)>>>(a);
-    rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(),
-                                  as_stream(stream)>>>(a);
+    // The scan of a value head walks its chunks in order on one SM (48 CTAs), the chunk-local
+    // precompute fills the device: long sequences are cut into segments so that the scan of one
+    // segment (second stream, higher priority) runs beside the precompute of the next.
+    const int n_seg = n_chunks >= 32 ? 4 : 1;
+    cudaStream_t run = as_stream(stream);
+    auto prepare = [&](int c0, int n, cudaStream_t st) {
+        a.chunk0 = c0;
+        a.chunks = n;
+        rl::delta_chunk_prepare_kernel<<<dim3(n, p->n_v), rl::delta_chunk_prepare_threads(),
+                                         rl::delta_chunk_prepare_smem_bytes(), st>>>(a);
+    };
+    auto scan = [&](int c0, int n, cudaStream_t st) {
+        a.chunk0 = c0;
+        a.chunks = n;
+        rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(), st>>>(a);
+    };
+    if (n_seg == 1) {
+        prepare(0, n_chunks, run);
+        scan(0, n_chunks, run);
+    } else {
+        for (int i = 0; i < n_seg; ++i) {
+            const int c0 = int(1LL * i * n_chunks / n_seg), c1 = int(1LL * (i + 1) * n_chunks / n_seg);
+            prepare(c0, c1 - c0, run);
+            RL_CUDA(cudaEventRecord(d->aux_ev[i], run));
+            RL_CUDA(cudaStreamWaitEvent(d->aux, d->aux_ev[i], 0));     // also orders the first scan after the caller's work
+            scan(c0, c1 - c0, d->aux);
+        }
+        RL_CUDA(cudaEventRecord(d->aux_ev[8], d->aux));
+        RL_CUDA(cudaStreamWaitEvent(run, d->aux_ev[8], 0));
+    }
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

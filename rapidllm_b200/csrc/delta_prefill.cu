@@ -90,7 +90,7 @@ size_t delta_chunk_record_bytes() { return kRecordBytes; }
 __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
-    const int chunk = blockIdx.x, h = blockIdx.y;
+    const int chunk = a.chunk0 + blockIdx.x, h = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = a.head_map == 0 ? 1 : a.n_v / a.n_qk;
     const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
@@ -379,13 +379,15 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint3
 
 }  // namespace
 
-// grid (n_v), 192 threads.  o [T][n_v][128]; S [n_v][128][128] fp32 in place (row = key dim).
+// grid (n_v), 192 threads.  o [T][n_v][128]; S [n_v][128][128] fp32 in place (row = key dim).  A launch
+// walks chunks [chunk0, chunk0 + chunks): S is read at its start and written back at its end, so a
+// sequence can be scanned in several launches while later chunks are still being prepared.
 __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     ScanSmem& s = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int h = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_chunks = (a.T + kC - 1) / kC;
+    const int n_chunks = a.chunks;            // of this launch; c below counts from a.chunk0
     float* Sg = a.S + size_t(h) * kD * kD;
 
     if (tid == 0) {
@@ -413,7 +415,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
                 const int st = c % kScanStages;
                 if (!mbar_wait(&s.empty[st], ((c / kScanStages) & 1) ^ 1)) { s.failed = 1; break; }
                 mbar_arrive_expect_tx(&s.full[st], kRecordBytes);
-                bulk_g2s(s.rec[st], a.work + (size_t(c) * a.n_v + h) * kRecordBytes, kRecordBytes, &s.full[st]);
+                bulk_g2s(s.rec[st], a.work + (size_t(a.chunk0 + c) * a.n_v + h) * kRecordBytes, kRecordBytes, &s.full[st]);
             }
             if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
@@ -502,7 +504,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
         tc::fence_before_sync();
         mbar_arrive(&s.bar_s);
         for (int c = 0; c < n_chunks; ++c) {
-            const float decay = a.chunk_decay[size_t(c) * a.n_v + h];
+            const float decay = a.chunk_decay[size_t(a.chunk0 + c) * a.n_v + h];
             // S^T *= exp(G_C) while the tensor core works from the hi/lo copies
 #pragma unroll 1
             for (int c0 = 0; c0 < kD; c0 += 32) {
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             }
             tc::fence_after_sync();
             // o[t][h][j] = O^T[j][t]
-            const int t0 = c * kC;
+            const int t0 = (a.chunk0 + c) * kC;
 #pragma unroll 1
             for (int c0 = 0; c0 < kC; c0 += 32) {
                 uint32_t f[32];

@@ -182,6 +182,7 @@ struct DeltaChunkArgs {
     int T, n_v, n_qk, head_map;
     float eps_l2;
     long long qk_tok_stride, v_tok_stride;   // floats between tokens in q/k and in v
+    int chunk0, chunks;          // this launch covers chunks [chunk0, chunk0 + chunks) of the T tokens
 };
 __global__ void delta_chunk_prepare_kernel(DeltaChunkArgs a);
 __global__ void delta_chunk_scan_kernel(DeltaChunkArgs a);
