@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace {
 
@@ -48,6 +49,11 @@ struct DevInfo {
     cudaEvent_t aux_ev[9] = {};
 };
 std::mutex g_mu;
+}  // namespace
+namespace rl {
+thread_local bool g_step_overlap = false;
+}
+namespace {
 DevInfo g_dev[64];
 
 int dev_info(DevInfo** out) {
@@ -173,8 +179,8 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
         rl::attn_decode_tq_kernel<<<grid, rl::attn_decode_tq_threads(), rl::attn_decode_tq_smem_bytes(),
                                     as_stream(stream)>>>(a);
     else
-        rl::attn_decode_f16_kernel<<<grid, rl::attn_decode_f16_threads(), rl::attn_decode_f16_smem_bytes(),
-                                     as_stream(stream)>>>(a);
+        RL_CUDA(rl::launch_step(rl::attn_decode_f16_kernel, dim3(grid), dim3(rl::attn_decode_f16_threads()),
+                                rl::attn_decode_f16_smem_bytes(), as_stream(stream), a));
     if (after_main) cudaEventRecord(after_main, as_stream(stream));
     rl::AttnCombineArgs c;
     c.part_o = a.part_o;
@@ -191,7 +197,7 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     c.max_len = p->max_pages_per_seq * p->page_tokens;
     c.wht_len = (tq && !out_ml) ? p->wht_len : 0;      // partial outputs stay in the rotated domain
     c.signs = (tq && p->wht_len == 256) ? p->tq_signs : nullptr;
-    rl::attn_combine_kernel<<<dim3(p->n_q, p->batch), 256, 0, as_stream(stream)>>>(c);
+    RL_CUDA(rl::launch_step(rl::attn_combine_kernel, dim3(p->n_q, p->batch), dim3(256), 0, as_stream(stream), c));
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -226,6 +232,7 @@ struct rl_cache {
     // graph replay of rl_stack_decode: the step's launches are captured once per distinct io
     // (same pointers, same batch) and replayed afterwards; positions, page table and slots are
     // read from device memory by the kernels, so the captured step stays valid as they advance
+    bool overlap = std::getenv("RL_B200_NO_STEP_OVERLAP") == nullptr;   // dependent launch between the step's kernels
     bool graph_enabled = true;
     cudaGraphExec_t gexec = nullptr;
     rl_stack_io gkey;               // io of the captured graph / of the last eager step
@@ -267,7 +274,16 @@ int dev_alloc(T** p, size_t n, size_t* total) {
     return RL_OK;
 }
 
+// Marks the launches of a step for programmatic dependent launch while it is alive.
+struct StepOverlap {
+    bool prev;
+    explicit StepOverlap(bool on) : prev(rl::g_step_overlap) { rl::g_step_overlap = on; }
+    ~StepOverlap() { rl::g_step_overlap = prev; }
+};
+
 int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bool host_mode) {
+    // not with per-kernel timing: an event between two kernels is what the overlap removes
+    StepOverlap overlap(c->overlap && !c->timing);
     const rl_cache_config& f = c->cfg;
     const int B = io->batch;
     const size_t q_sz = size_t(B) * f.n_q * f.head_dim, kv_sz = size_t(B) * f.n_kv * f.head_dim;
@@ -509,8 +525,8 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     a.pos0 = p->pos0;
     a.rows_fp16 = p->rows_fp16;
     const int rows_per_block = p->n_tok >= 8 ? 8 : 1;
-    rl::kv_write_kernel<<<dim3((p->n_tok + rows_per_block - 1) / rows_per_block, p->n_kv, p->batch),
-                          dim3(32, rows_per_block), 0, as_stream(stream)>>>(a);
+    RL_CUDA(rl::launch_step(rl::kv_write_kernel, dim3((p->n_tok + rows_per_block - 1) / rows_per_block, p->n_kv, p->batch),
+                            dim3(32, rows_per_block), 0, as_stream(stream), a));
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

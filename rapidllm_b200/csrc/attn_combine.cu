@@ -37,6 +37,8 @@ __device__ __forceinline__ float block_wht(float v, int wht_len, const float* si
 }  // namespace
 
 __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
+    griddep_launch();
+    griddep_wait();
     const int hq = blockIdx.x;
     const int b = blockIdx.y;
     const int G = a.n_q / a.n_kv;

@@ -60,6 +60,8 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     const int lane = tid & 31;
     const int G = a.n_q / a.n_kv;
 
+    griddep_launch();
+    griddep_wait();       // positions, the appended rows and the workspace belong to earlier kernels
     // chunk prefix over the batch (every CTA computes the same table)
     if (warp == 0)
         split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.err, lane);

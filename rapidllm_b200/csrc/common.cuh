@@ -21,6 +21,15 @@ __device__ __forceinline__ void set_err(int* err, int code) {
     if (err) atomicCAS(err, 0, code);
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may
+// become resident while the kernel before it in the stream is still running.  griddep_wait()
+// blocks until every kernel before this one has completed and its writes are visible (a no-op in
+// a plain launch); griddep_launch() lets the next kernel's CTAs be scheduled from here on.  Every
+// kernel of the decode step waits before it reads or writes anything, so only launch latency and
+// per-CTA set-up overlap the kernel in front.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

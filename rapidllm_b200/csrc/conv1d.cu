@@ -4,6 +4,7 @@
 // a [seq][dim] block (ops::conv1d_causal_prefill, 443-456).
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace rl {
 
@@ -13,6 +14,8 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 
 // k == 4: one channel per thread, window as one float4.
 __global__ void __launch_bounds__(256) conv1d_update4_kernel(ConvUpdateArgs a) {
+    griddep_launch();
+    griddep_wait();       // x, the window and y's previous reader belong to earlier kernels
     const int c = blockIdx.x * 256 + threadIdx.x;
     const int b = blockIdx.y;
     if (c >= a.dim) return;
@@ -102,7 +105,7 @@ conv1d_state_tail_kernel(const float* x, float* state_io, int seq, int dim, int 
 void launch_conv1d_update(const ConvUpdateArgs& a, cudaStream_t st) {
     if (a.batch <= 0 || a.dim <= 0) return;
     dim3 grid((a.dim + 255) / 256, a.batch);
-    if (a.k == 4) conv1d_update4_kernel<<<grid, 256, 0, st>>>(a);
+    if (a.k == 4) launch_step(conv1d_update4_kernel, grid, dim3(256), 0, st, a);
     else conv1d_update_generic_kernel<<<grid, 256, 0, st>>>(a);
 }
 

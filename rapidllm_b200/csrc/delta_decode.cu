@@ -13,6 +13,7 @@
 // batch CTAs keep all SMs busy even at batch 1.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace rl {
 
@@ -23,6 +24,7 @@ constexpr int kSliceCols = 32;
 constexpr int kSlices = kDv / kSliceCols;   // 4
 
 __global__ void __launch_bounds__(256) delta_decode_kernel(DeltaDecodeArgs a) {
+    griddep_wait();
     const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __shared__ float sq[kDk], sk[kDk];
@@ -256,7 +258,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) delta_decode_stream_kernel(
         }
         mbar_fence_init();
     }
+    griddep_launch();
     __syncthreads();
+    griddep_wait();       // barrier set-up above overlaps the tail of the kernel in front; nothing is read before this
     auto slot_of = [&](int b) {
         int slot = a.slot_ids ? a.slot_ids[b] : b;
         if (slot < 0 || slot >= a.n_slots) {
@@ -383,11 +387,11 @@ void launch_delta_decode(const DeltaDecodeArgs& a, int sms, cudaStream_t st) {
     const int items = a.batch * a.n_v;
     if (sms > 0 && items >= 4 * sms) {
         // enough heads to keep every SM streaming: one persistent CTA per SM
-        delta_decode_stream_kernel<<<sms, kStreamThreads, delta_decode_stream_smem_bytes(), st>>>(a);
+        launch_step(delta_decode_stream_kernel, dim3(sms), dim3(kStreamThreads), delta_decode_stream_smem_bytes(), st, a);
         return;
     }
     dim3 grid(kSlices, a.n_v, a.batch);
-    delta_decode_kernel<<<grid, 256, 0, st>>>(a);
+    launch_step(delta_decode_kernel, grid, dim3(256), 0, st, a);
 }
 
 }  // namespace rl

@@ -13,6 +13,8 @@ namespace rl {
 // grid (ceil(n_tok / blockDim.y), n_kv, batch), block (32, 1 or 8): one token row per warp, one
 // 16-byte chunk (8 dims) per thread.
 __global__ void __launch_bounds__(256) kv_write_kernel(KvWriteArgs a) {
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.x * blockDim.y + threadIdx.y, h = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x;
     if (t >= a.n_tok) return;
