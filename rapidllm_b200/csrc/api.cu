@@ -94,6 +94,13 @@ int dev_info(DevInfo** out) {
     return RL_OK;
 }
 
+// Marks the launches of a step for programmatic dependent launch while it is alive.
+struct StepOverlap {
+    bool prev;
+    explicit StepOverlap(bool on) : prev(rl::g_step_overlap) { rl::g_step_overlap = on; }
+    ~StepOverlap() { rl::g_step_overlap = prev; }
+};
+
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -197,7 +204,12 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     c.max_len = p->max_pages_per_seq * p->page_tokens;
     c.wht_len = (tq && !out_ml) ? p->wht_len : 0;      // partial outputs stay in the rotated domain
     c.signs = (tq && p->wht_len == 256) ? p->tq_signs : nullptr;
-    RL_CUDA(rl::launch_step(rl::attn_combine_kernel, dim3(p->n_q, p->batch), dim3(256), 0, as_stream(stream), c));
+    {
+        // the merge always follows its decode kernel, which lets dependents in at its top: scheduled
+        // early, the merge starts the moment the partials are complete
+        StepOverlap merge_behind_decode(true);
+        RL_CUDA(rl::launch_step(rl::attn_combine_kernel, dim3(p->n_q, p->batch), dim3(256), 0, as_stream(stream), c));
+    }
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -273,13 +285,6 @@ int dev_alloc(T** p, size_t n, size_t* total) {
     *total += n * sizeof(T);
     return RL_OK;
 }
-
-// Marks the launches of a step for programmatic dependent launch while it is alive.
-struct StepOverlap {
-    bool prev;
-    explicit StepOverlap(bool on) : prev(rl::g_step_overlap) { rl::g_step_overlap = on; }
-    ~StepOverlap() { rl::g_step_overlap = prev; }
-};
 
 int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bool host_mode) {
     // not with per-kernel timing: an event between two kernels is what the overlap removes

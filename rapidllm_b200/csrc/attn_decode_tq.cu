@@ -77,6 +77,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     const int lane = tid & 31;
     const int G = a.n_q / a.n_kv;
 
+    griddep_launch();     // the merge kernel behind this one may be scheduled; it waits for this grid
+    griddep_wait();
     if (warp == 0)
         split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.err, lane);
     if (tid == 0) {
