@@ -319,6 +319,22 @@ def run_operator(args):
         flops = 4.0 * N_Q * HD * T * (T + 1) / 2
         tpeak = float(peaks.get("bf16_tflops", 1590.0))
         achieved = flops / (ms * 1e-3) / 1e12
+        # The back-to-back loop above runs under the 1 kW power cap (the SM clock drops to ~1.7 GHz within a
+        # few calls).  The burst peak it is divided by is a best-of-10 of single GEMMs, so the like-for-like
+        # figure is taken too: single calls after 20 ms of idle, best and median.
+        import time as _time
+        singles = []
+        for _ in range(10):
+            torch.cuda.synchronize()
+            _time.sleep(0.02)
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record()
+            call()
+            b1.record()
+            torch.cuda.synchronize()
+            singles.append(b0.elapsed_time(b1))
+        singles.sort()
+        speak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         print(json.dumps({
             "metric": "attention prefill tokens/sec (one layer)", "value": T / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
@@ -327,7 +343,13 @@ def run_operator(args):
                        "writes F16 KV" % (T, args.chunk), "l2": "K/V of one layer fit L2 by design (32 MB)"},
             "clocks": clocks, "gpu_launches": args.steps * 2 * ((T + args.chunk - 1) // args.chunk),
             "roofline": {"bound": "tensor", "kernel": "attn_prefill_kernel", "achieved": achieved, "peak": tpeak,
-                         "unit": "TFLOP/s", "frac": achieved / tpeak, "flops_per_step": flops, "traffic": None}}),
+                         "unit": "TFLOP/s", "frac": achieved / tpeak, "flops_per_step": flops, "traffic": None,
+                         "peak_sustained": speak, "frac_of_sustained_peak": achieved / speak,
+                         "single_calls_after_idle": {"ms_best": singles[0], "ms_median": singles[len(singles) // 2],
+                                                     "frac_best": flops / (singles[0] * 1e-3) / 1e12 / tpeak,
+                                                     "frac_median": flops / (singles[len(singles) // 2] * 1e-3) / 1e12 / tpeak},
+                         "note": "achieved = back-to-back loop (power-capped clocks); frac divides it by the burst peak, "
+                                 "frac_of_sustained_peak by the cuBLAS figure taken under the same cap"}}),
             flush=True)
         return
     if wl == "stack_prefill":

@@ -140,11 +140,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         const __nv_bfloat16* src = a.q + flat_row(r < rows ? r : 0) * kHeadDim + qpart * 64;
         const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
         uint32_t regs[32];
+        uint4 in[8];                                          // all eight loads in flight before the first use
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) in[ch] = r < rows ? __ldcs(reinterpret_cast<const uint4*>(src + ch * 8)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
-            uint4 in = make_uint4(0, 0, 0, 0);
-            if (r < rows) in = *reinterpret_cast<const uint4*>(src + ch * 8);
-            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in[ch]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float2 f = __bfloat1622float2(b2[e]);
@@ -443,22 +444,42 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 ml[1] = l_run;
             }
         }
+        // The gate values this warp needs (rows warp, warp + 16, ...: 8 rows x 2 x float4 per lane; the
+        // prologue started them towards L2) are all requested before the first is used.
+        const bool gated = a.gate && parts <= 1;
+        constexpr int kRowsPerWarp = kQRows / (kSoftmaxThreads / 32);
+        float4 gq[kRowsPerWarp][2];
+        if (gated && good) {
+#pragma unroll
+            for (int i = 0; i < kRowsPerWarp; ++i) {
+                const int row = warp + i * (kSoftmaxThreads / 32);
+                if (row < rows) {
+                    const float* gp = a.gate + flat_row(row) * kHeadDim + lane * 4;
+                    gq[i][0] = __ldcs(reinterpret_cast<const float4*>(gp));
+                    gq[i][1] = __ldcs(reinterpret_cast<const float4*>(gp + 128));
+                }
+            }
+        }
         named_bar_sync(9, kSoftmaxThreads);
         if (good) {
-            for (int row = warp; row < rows; row += kSoftmaxThreads / 32) {
+            // sigmoid(g) = 1 / (1 + 2^(-g log2 e)) with the hardware exponential and reciprocal: a few
+            // 1e-7 relative from expf, far inside the tolerance of an fp16 attention
+            auto sig = [](float g) { return __frcp_rn(1.f + fast_exp2(g * -1.4426950408889634f)); };
+#pragma unroll
+            for (int i = 0; i < kRowsPerWarp; ++i) {
+                const int row = warp + i * (kSoftmaxThreads / 32);
+                if (row >= rows) break;
                 float* dst = split ? a.part_o + (size_t(part) * a.T * a.n_q + flat_row(row)) * kHeadDim
                                    : a.o + flat_row(row) * kHeadDim;
-                const float* gp = (a.gate && !split) ? a.gate + flat_row(row) * kHeadDim : nullptr;
 #pragma unroll
                 for (int hcol = 0; hcol < 2; ++hcol) {
                     const int c = hcol * 128 + lane * 4;
                     float4 v = *reinterpret_cast<const float4*>(stage + row * kStageStride + c);
-                    if (gp) {
-                        const float4 gq = __ldcs(reinterpret_cast<const float4*>(gp + c));
-                        v.x *= 1.f / (1.f + expf(-gq.x));
-                        v.y *= 1.f / (1.f + expf(-gq.y));
-                        v.z *= 1.f / (1.f + expf(-gq.z));
-                        v.w *= 1.f / (1.f + expf(-gq.w));
+                    if (gated) {
+                        v.x *= sig(gq[i][hcol].x);
+                        v.y *= sig(gq[i][hcol].y);
+                        v.z *= sig(gq[i][hcol].z);
+                        v.w *= sig(gq[i][hcol].w);
                     }
                     __stcs(reinterpret_cast<float4*>(dst + c), v);
                 }
