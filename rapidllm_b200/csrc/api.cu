@@ -616,6 +616,7 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
         parts = 1;
     a.packed = prefill_packed(p) ? 1 : 0;
     a.kv_parts = parts;
+    a.wave = d->sms;
     a.part_o = parts > 1 ? static_cast<float*>(workspace) : nullptr;
     a.part_ml = parts > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + o_bytes) : nullptr;
     rl::attn_prefill_kernel<<<dim3((a.packed ? unsigned(p->n_kv) : unsigned(n_qtiles) * unsigned(p->n_q)) * unsigned(parts)),

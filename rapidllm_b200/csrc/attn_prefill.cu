@@ -52,12 +52,18 @@ constexpr uint32_t kTmemCols = 512;
 // buffers (fp16 pairs, 32 columns each) in [64,128), O in [128,384), Q (fp16 pairs) in [384,512).
 constexpr uint32_t kColS = 0, kColP = 64, kColO = 128, kColQ = 384;
 constexpr float kRescaleThreshold = 8.f;          // log2 units
+// Q rows arrive by one bulk copy per row into V stages 1 and 2 (not needed before the second P.V), rows
+// 528 bytes apart so that the thread-per-row reads spread over all banks.
+constexpr int kQRowStride = kHeadDim * 2 + 16;
+constexpr int kQStageBytes = kQRows * kQRowStride;            // 67 584
+static_assert(kQStageBytes > 2 * kSliceBytes && kVStages >= 3, "Q staging = V stages 1, 2 + q_pad");
 
 struct Smem {
     alignas(1024) unsigned char k[kKStages][kSliceBytes];     // K page slices
     alignas(1024) unsigned char v[kVStages][kSliceBytes];     // V page slices
+    unsigned char q_pad[kQStageBytes - 2 * kSliceBytes];      // with v[1], v[2]: where the Q rows land first
     uint64_t k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
-    uint64_t bar_s[2], bar_sfree[2], bar_p[2], bar_pv[2], bar_m[2], bar_q, bar_done;
+    uint64_t bar_s[2], bar_sfree[2], bar_p[2], bar_pv[2], bar_m[2], bar_q, bar_done, bar_qload, bar_qfree;
     float xch[2][2][kQRows][2];                       // [group][use parity] row maxima of the two column halves
     float mrow[2][kQRows];                            // [tile parity] running maximum after that tile
     alignas(16) float lsum[kQRows][4];                 // read back as one float4 per row
@@ -114,6 +120,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         }
         mbar_init(&s.bar_q, kSoftmaxThreads);
         mbar_init(&s.bar_done, 1);
+        mbar_init(&s.bar_qload, 1);
+        mbar_init(&s.bar_qfree, kSoftmaxThreads);
         s.failed = 0;
         mbar_fence_init();
     }
@@ -134,15 +142,43 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
 #define RL_TRACE(J, SLOT) if (tr && (J) < 64) a.trace[(J) * 8 + (SLOT)] = global_ns();
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
     // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the four threads
-    // of a row stores 64 dims
+    // of a row stores 64 dims.  The rows come in by bulk copies (one per row), issued by the loader warp
+    // ahead of its first K/V tiles.
+    unsigned char* qstage = s.v[1];
+    if (warp == kWarpLoader) {
+        if (lane == 0) mbar_arrive_expect_tx(&s.bar_qload, uint32_t(rows) * kHeadDim * 2);
+        __syncwarp();
+        for (int r = lane; r < rows; r += 32)
+            bulk_g2s(qstage + r * kQRowStride, a.q + flat_row(r) * kHeadDim, kHeadDim * 2, &s.bar_qload);
+        __syncwarp();
+        // The CTA that follows this one on the SM is, to a good approximation, the one a wave further down
+        // the launch order: start its Q rows on their way into L2.
+        const int nxt = int(blockIdx.x) + int(a.wave);
+        if (!a.packed && parts == 1 && nxt < int(gridDim.x)) {
+            const int n_hkv = nxt / per_kv, n_rem = nxt - n_hkv * per_kv;
+            const int n_q0 = (n_qtiles - 1 - n_rem / G) * kQRows, n_hq = n_hkv * G + n_rem % G;
+            const int n_rows = min(kQRows, a.T - n_q0);
+            for (int i = lane; i < n_rows * 4; i += 32) {     // 4 lines of 128 bytes per row
+                const __nv_bfloat16* pq = a.q + (size_t(n_q0 + (i >> 2)) * a.n_q + n_hq) * kHeadDim + (i & 3) * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pq));
+            }
+        }
+    }
     if (tid < kSoftmaxThreads) {
         const int qpart = warp >> 2, r = (warp & 3) * 32 + lane;
-        const __nv_bfloat16* src = a.q + flat_row(r < rows ? r : 0) * kHeadDim + qpart * 64;
         const uint32_t lane_addr = tmem + (uint32_t((warp & 3) * 32) << 16);
         uint32_t regs[32];
-        uint4 in[8];                                          // all eight loads in flight before the first use
+        bool got = mbar_wait(&s.bar_qload, 0);
+        if (!got) {
+            set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+            s.failed = 1;
+        }
+        uint4 in[8];
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) in[ch] = r < rows ? __ldcs(reinterpret_cast<const uint4*>(src + ch * 8)) : make_uint4(0, 0, 0, 0);
+        for (int ch = 0; ch < 8; ++ch)
+            in[ch] = (got && r < rows) ? *reinterpret_cast<const uint4*>(qstage + r * kQRowStride + qpart * 128 + ch * 16)
+                                       : make_uint4(0, 0, 0, 0);
+        mbar_arrive(&s.bar_qfree);                            // V stages 1, 2 may be filled once all have read
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
             const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&in[ch]);
@@ -182,6 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 mbar_arrive_expect_tx(&s.k_full[ks], kSliceBytes);
                 bulk_g2s(s.k[ks], a.k_pool + slice, kSliceBytes, &s.k_full[ks]);
                 if (!mbar_wait(&s.v_empty[vs], ((j / kVStages) & 1) ^ 1)) { s.failed = 1; break; }
+                if (j == 1 && !mbar_wait(&s.bar_qfree, 0)) { s.failed = 1; break; }   // the Q rows were staged in V stages 1, 2
                 mbar_arrive_expect_tx(&s.v_full[vs], kSliceBytes);
                 bulk_g2s(s.v[vs], a.v_pool + slice, kSliceBytes, &s.v_full[vs]);
             }
