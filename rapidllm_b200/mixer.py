@@ -98,3 +98,35 @@ class GatedAttentionMixer:
         ops.kv_append(self.k_pool, self.v_pool, page_table, k.unsqueeze(1), v.unsqueeze(1), pos=pos)
         o = ops.attn_decode(q, self.k_pool, self.v_pool, page_table, pos + 1, gate)
         return x + _matmul(o.view(B, qn), self.W_out)
+
+
+class MixerStack:
+    """The mixers of a hybrid model in layer order, as Session::forward_hidden walks
+    ModelDesc.layers (src/runtime/session.cpp:325-411; slot = index among the layers of a kind,
+    src/runtime/model_desc.cpp:12-22), without the MLP blocks between them: one decode token of
+    every sequence goes through every layer's mixer, the hidden state carrying the residual.
+
+    layer_types: RL_LAYER_* per layer; weights: one dict per layer (see the two mixer classes).
+    All attention layers share page_table / pos; every DeltaNet layer keeps its own state per slot."""
+
+    def __init__(self, layer_types, weights, n_pages, n_slots, device="cuda", **dims):
+        self.layers = []
+        for kind, w in zip(layer_types, weights):
+            if kind == _lib.RL_LAYER_FULL_ATTENTION:
+                keys = ("n_q", "n_kv", "hd", "rotary_dim", "theta", "eps", "weight_dtype")
+                self.layers.append(GatedAttentionMixer(w, n_pages, device=device,
+                                                       **{k: v for k, v in dims.items() if k in keys}))
+            else:
+                keys = ("n_k", "n_v", "dk", "dv", "eps", "head_map", "weight_dtype")
+                self.layers.append(DeltaNetMixer(w, n_slots=n_slots, device=device,
+                                                 **{k: v for k, v in dims.items() if k in keys}))
+
+    def decode(self, x, page_table, pos, slot_ids=None):
+        """x fp32 [batch][hidden] -> hidden state after the last mixer; pos int32 [batch] on the device is
+        the position the token is written at (the caller advances it between steps)."""
+        for layer in self.layers:
+            if isinstance(layer, GatedAttentionMixer):
+                x = layer.decode(x, page_table, pos)
+            else:
+                x = layer.decode(x, slot_ids)
+        return x

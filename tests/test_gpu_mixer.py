@@ -100,3 +100,51 @@ def test_attention_mixer_steps(oracle):
         n = start[b] + 4
         kd = ops.kv_gather(mix.k_pool, table[b], n).float().cpu().numpy()
         assert np.abs(kd - kc[b][:n]).max() <= 2e-3
+
+
+def test_mixer_stack_two_tokens(oracle):
+    """D, D, D, A in layer order for two decode tokens of two sequences: the residual stream after the
+    last mixer equals the oracle's fused_delta_decode / fused_attn_decode chained in the same order."""
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES
+    from rapidllm_b200.mixer import MixerStack
+    torch.backends.cuda.matmul.allow_tf32 = False
+    rs = np.random.RandomState(43)
+    nk, nv, n_q, n_kv, hd = 16, 48, 24, 4, 256
+    cd = 2 * nk * 128 + nv * 128
+    weights = []
+    for kind in QWEN35_LAYER_TYPES:
+        if kind == _lib.RL_LAYER_FULL_ATTENTION:
+            weights.append(dict(rms_w=_f(rs, HIDDEN) * 0.1, Wq=_f(rs, n_q * 2 * hd, HIDDEN) / 20,
+                                Wk=_f(rs, n_kv * hd, HIDDEN) / 20, Wv=_f(rs, n_kv * hd, HIDDEN) / 20,
+                                Wo=_f(rs, HIDDEN, n_q * hd) / 80, q_norm=_f(rs, hd) * 0.1, k_norm=_f(rs, hd) * 0.1))
+        else:
+            weights.append(dict(rms_w=_f(rs, HIDDEN) * 0.1, Wqkv=_f(rs, cd, HIDDEN) / 20,
+                                Wz=_f(rs, nv * 128, HIDDEN) / 20, Wa=_f(rs, nv, HIDDEN) / 20,
+                                Wb=_f(rs, nv, HIDDEN) / 20, Wo=_f(rs, HIDDEN, nv * 128) / 80, A_log=_f(rs, nv) * 0.5,
+                                dt_bias=_f(rs, nv), conv_w=_f(rs, cd, 4) * 0.5, gnorm=_f(rs, 128)))
+    B, max_pages = 2, 2
+    stack = MixerStack(QWEN35_LAYER_TYPES, weights, n_pages=B * max_pages, n_slots=B)
+    table = torch.arange(B * max_pages, dtype=torch.int32).view(B, max_pages).cuda()
+    S = [[np.zeros((nv, 128, 128), np.float32) for _ in range(B)] for _ in range(3)]
+    conv = [[np.zeros((cd, 4), np.float32) for _ in range(B)] for _ in range(3)]
+    kc = [np.zeros((4, n_kv, hd), np.float32) for _ in range(B)]
+    vc = [np.zeros((4, n_kv, hd), np.float32) for _ in range(B)]
+    for pos in range(2):
+        x = _f(rs, B, HIDDEN)
+        got = stack.decode(torch.from_numpy(x).cuda(), table,
+                           torch.full((B,), pos, dtype=torch.int32, device="cuda")).cpu().numpy()
+        _lib.check_device()
+        for b in range(B):
+            xb, d = x[b], 0
+            for kind, w in zip(QWEN35_LAYER_TYPES, weights):
+                if kind == _lib.RL_LAYER_FULL_ATTENTION:
+                    xb = oracle.fused_attn_decode(xb, w, kc[b], vc[b], pos, n_q, n_kv)
+                    kc[b][pos] = kc[b][pos].astype(np.float16).astype(np.float32)
+                    vc[b][pos] = vc[b][pos].astype(np.float16).astype(np.float32)
+                else:
+                    xb = oracle.fused_delta_decode(xb, w, S[d][b], conv[d][b], nk, nv)
+                    d += 1
+            assert np.abs(got[b] - xb).max() <= ATTN_MAX_ABS and rel_l2(got[b], xb) <= ATTN_REL_L2, \
+                (pos, b, np.abs(got[b] - xb).max(), rel_l2(got[b], xb))
+    print("mixer stack: x max-abs %.2e rel-l2 %.2e" % (np.abs(got[b] - xb).max(), rel_l2(got[b], xb)))
