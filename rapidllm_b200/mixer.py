@@ -70,6 +70,36 @@ class DeltaNetMixer:
         return x + _matmul(og.view(B, zd), self.W_out)
 
 
+    def prefill(self, x, slot=0, start=True, workspace=None):
+        """A chunk of one sequence's prompt: x fp32 [T][hidden] -> new hidden states; the slot's state and
+        conv window advance by T tokens (start=True: the sequence begins here, state zero, window empty).
+        Same arithmetic as T decode steps, with the delta rule in its chunked form."""
+        T = x.shape[0]
+        cd, zd, nv = self.conv_dim, self.zdim, self.n_v
+        xn = ops.rmsnorm(x, self.rms_w, self.eps)
+        proj = _matmul(xn, self.W_in)
+        qkv = proj[:, :cd].contiguous()
+        z = proj[:, cd:cd + zd].contiguous()
+        a = proj[:, cd + zd:cd + zd + nv].contiguous()
+        b = proj[:, cd + zd + nv:].contiguous()
+        if start:
+            self.S[slot].zero_()
+        mixed = ops.conv1d_causal_prefill(qkv, self.conv_w, self.conv_state[slot], use_state_in=not start)
+        beta, g = ops.delta_gates(a, b, self.A_log, self.dt_bias)
+        p = _lib.DeltaChunkParams(n_v=nv, dk=self.dk, dv=self.dv, seq=T, chunk=64, eps_l2=1e-6, n_qk=self.n_k,
+                                  head_map=self.head_map, qk_tok_stride=cd, v_tok_stride=cd)
+        need = lib().rl_delta_chunk_workspace_bytes(C.byref(p))
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        o = torch.empty(T, nv, self.dv, dtype=torch.float32, device=x.device)
+        base = mixed.data_ptr()
+        check(lib().rl_delta_chunk_prefill(ops._p(self.S[slot]), C.c_void_p(base), C.c_void_p(base + 4 * self.qdim),
+                                           C.c_void_p(base + 8 * self.qdim), ops._p(beta), ops._p(g), ops._p(o),
+                                           ops._p(workspace), workspace.numel(), C.byref(p), ops._stream()))
+        og = ops.gated_rmsnorm(o, z.view(T, nv, self.dv), self.gnorm, 1e-6)
+        return x + _matmul(og.view(T, zd), self.W_out)
+
+
 class GatedAttentionMixer:
     """w: rms_w [hidden], Wq [n_q*2*hd, hidden] ([q | gate] rows per head), Wk, Wv [n_kv*hd, hidden],
     Wo [hidden, n_q*hd], q_norm, k_norm [hd].  The KV cache is paged F16 (k_pool, v_pool)."""
@@ -130,3 +160,24 @@ class MixerStack:
             else:
                 x = layer.decode(x, slot_ids)
         return x
+
+
+def _attn_prefill(self, x, page_table_row, pos0):
+    """A chunk of one sequence's prompt: x fp32 [T][hidden] at positions pos0 .. pos0+T-1 -> new hidden
+    states; K/V rows go into the cache as fp16 (round to nearest even, like decode), the query rows reach
+    the tensor cores as bf16."""
+    T = x.shape[0]
+    qn, kn = self.n_q * self.hd, self.n_kv * self.hd
+    xn = ops.rmsnorm(x, self.rms_w, self.eps)
+    proj = _matmul(xn, self.W_in)
+    qg = proj[:, :2 * qn].contiguous().view(T, self.n_q, 2 * self.hd)
+    k = proj[:, 2 * qn:2 * qn + kn].contiguous().view(T, self.n_kv, self.hd)
+    v = proj[:, 2 * qn + kn:].contiguous().view(T, self.n_kv, self.hd)
+    q, gate = ops.attn_qk_prepare(qg, k, self.q_norm, self.k_norm, pos0=pos0, rotary_dim=self.rotary_dim,
+                                  theta=self.theta, eps=self.eps)
+    ops.kv_append(self.k_pool, self.v_pool, page_table_row, k, v, pos0=pos0)
+    o = ops.attn_prefill(q.bfloat16(), self.k_pool, self.v_pool, page_table_row, pos0, None, None, gate)
+    return x + _matmul(o.view(T, qn), self.W_out)
+
+
+GatedAttentionMixer.prefill = _attn_prefill

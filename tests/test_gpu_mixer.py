@@ -148,3 +148,46 @@ def test_mixer_stack_two_tokens(oracle):
             assert np.abs(got[b] - xb).max() <= ATTN_MAX_ABS and rel_l2(got[b], xb) <= ATTN_REL_L2, \
                 (pos, b, np.abs(got[b] - xb).max(), rel_l2(got[b], xb))
     print("mixer stack: x max-abs %.2e rel-l2 %.2e" % (np.abs(got[b] - xb).max(), rel_l2(got[b], xb)))
+
+
+def test_mixers_prefill_chunks(oracle):
+    """Prompt chunks through each mixer (chunked delta rule / tensor-core attention) against the oracle's
+    decode mixers run token by token."""
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.mixer import DeltaNetMixer, GatedAttentionMixer
+    torch.backends.cuda.matmul.allow_tf32 = False
+    rs = np.random.RandomState(44)
+    nk, nv, n_q, n_kv, hd = 16, 48, 24, 4, 256
+    cd = 2 * nk * 128 + nv * 128
+    wd = dict(rms_w=_f(rs, HIDDEN) * 0.1, Wqkv=_f(rs, cd, HIDDEN) / 20, Wz=_f(rs, nv * 128, HIDDEN) / 20,
+              Wa=_f(rs, nv, HIDDEN) / 20, Wb=_f(rs, nv, HIDDEN) / 20, Wo=_f(rs, HIDDEN, nv * 128) / 80,
+              A_log=_f(rs, nv) * 0.5, dt_bias=_f(rs, nv), conv_w=_f(rs, cd, 4) * 0.5, gnorm=_f(rs, 128))
+    wa = dict(rms_w=_f(rs, HIDDEN) * 0.1, Wq=_f(rs, n_q * 2 * hd, HIDDEN) / 20, Wk=_f(rs, n_kv * hd, HIDDEN) / 20,
+              Wv=_f(rs, n_kv * hd, HIDDEN) / 20, Wo=_f(rs, HIDDEN, n_q * hd) / 80, q_norm=_f(rs, hd) * 0.1,
+              k_norm=_f(rs, hd) * 0.1)
+    chunks = [70, 31]
+    T = sum(chunks)
+    x = _f(rs, T, HIDDEN)
+    dm = DeltaNetMixer(wd, nk, nv, n_slots=2)
+    am = GatedAttentionMixer(wa, n_pages=3)
+    row = torch.tensor([2, 0, 1], dtype=torch.int32).cuda()
+    got_d, got_a, p0 = [], [], 0
+    for n in chunks:
+        xc = torch.from_numpy(x[p0:p0 + n]).cuda()
+        got_d.append(dm.prefill(xc, slot=1, start=p0 == 0).cpu().numpy())
+        got_a.append(am.prefill(xc, row, p0).cpu().numpy())
+        _lib.check_device()
+        p0 += n
+    got_d, got_a = np.concatenate(got_d), np.concatenate(got_a)
+    S, conv = np.zeros((nv, 128, 128), np.float32), np.zeros((cd, 4), np.float32)
+    kc, vc = np.zeros((T, n_kv, hd), np.float32), np.zeros((T, n_kv, hd), np.float32)
+    ref_d, ref_a = np.empty_like(x), np.empty_like(x)
+    for t in range(T):
+        ref_d[t] = oracle.fused_delta_decode(x[t], wd, S, conv, nk, nv)
+        ref_a[t] = oracle.fused_attn_decode(x[t], wa, kc, vc, t, n_q, n_kv)
+        kc[t], vc[t] = kc[t].astype(np.float16).astype(np.float32), vc[t].astype(np.float16).astype(np.float32)
+    for name, got, ref in (("deltanet", got_d, ref_d), ("attention", got_a, ref_a)):
+        print("%s mixer prefill: x max-abs %.2e rel-l2 %.2e" % (name, np.abs(got - ref).max(), rel_l2(got, ref)))
+        assert np.abs(got - ref).max() <= ATTN_MAX_ABS and rel_l2(got, ref) <= ATTN_REL_L2
+    assert rel_l2(dm.S[1].cpu().numpy(), S) <= 1e-3           # chunked form: fp16 hi + lo operands
+    assert not dm.S[0].any()
