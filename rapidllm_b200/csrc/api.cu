@@ -3,6 +3,7 @@
 // C++ type crosses this boundary.
 #include "../../include/rl_b200.h"
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -148,6 +149,11 @@ AttnPlan attn_plan(const rl_attn_decode_params* p, int sms) {
     return pl;
 }
 
+const int kTqSegWeight = [] {
+    const char* e = std::getenv("RL_B200_TQ_SEG_WEIGHT");
+    return e ? std::max(0, atoi(e)) : 23;
+}();
+
 int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
                      const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
                      void* workspace, size_t workspace_bytes, const rl_attn_decode_params* p, void* stream,
@@ -181,6 +187,10 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     a.max_pages_per_seq = p->max_pages_per_seq;
     a.len_add = p->len_add;
     a.scale = 1.f / sqrtf(float(p->head_dim));
+    // Compact KV: a CTA that closes one (sequence, head) segment and opens the next spends ~6 us on
+    // it, the time of ~23 records of 32 tokens at 44 GB/s per SM; its share of the records is cut by
+    // that much.  F16: the division stays equal in units.
+    a.seg_weight = tq ? kTqSegWeight : 0;
     const int grid = pl.grid;
     if (tq)
         rl::attn_decode_tq_kernel<<<grid, rl::attn_decode_tq_threads(), rl::attn_decode_tq_smem_bytes(),
@@ -201,6 +211,7 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     c.n_kv = p->n_kv;
     c.len_add = p->len_add;
     c.n_ctas = grid;
+    c.seg_weight = a.seg_weight;
     c.max_len = p->max_pages_per_seq * p->page_tokens;
     c.wht_len = (tq && !out_ml) ? p->wht_len : 0;      // partial outputs stay in the rotated domain
     c.signs = (tq && p->wht_len == 256) ? p->tq_signs : nullptr;

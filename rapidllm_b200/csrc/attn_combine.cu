@@ -74,9 +74,11 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     const int hpb = (len + 31) >> 5;
     // this head's units are [u0, u0 + hpb); CTA k of the decode kernel owned [k*q, (k+1)*q)
     const int u0 = before * a.n_kv + h * hpb;
-    const int q = max(1, (total * a.n_kv + a.n_ctas - 1) / a.n_ctas);
-    const int k0 = u0 / q;
-    const int k1 = hpb > 0 ? (u0 + hpb - 1) / q : k0 - 1;
+    // (equal in cost when seg_weight > 0: unit u of segment sg sits at cost position u + seg_weight * sg)
+    const int c0 = u0 + a.seg_weight * (b * a.n_kv + h);
+    const int q = max(1, (total * a.n_kv + a.seg_weight * a.batch * a.n_kv + a.n_ctas - 1) / a.n_ctas);
+    const int k0 = c0 / q;
+    const int k1 = hpb > 0 ? (c0 + hpb - 1) / q : k0 - 1;
     const size_t unit = size_t(b) * a.n_kv + h;
 
     // A long sequence at a small batch is spread over many CTAs: fetch all their (m, l) pairs at

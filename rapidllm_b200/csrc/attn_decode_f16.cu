@@ -74,7 +74,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     }
     __syncthreads();
     int u_begin, u_end;
-    split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end);
+    split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end, a.seg_weight);
 
     if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_tq_kernel(AttnDecodeA
     }
     __syncthreads();
     int u_begin, u_end;
-    split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end);
+    split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end, a.seg_weight);
 
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------

@@ -63,9 +63,40 @@ __device__ __forceinline__ void build_prefix(Shared<NW>& s, const int32_t* seq_l
     if (lane == 0) s.prefix[batch] = run;
 }
 
+// Units in front of cost position c when every (b, h) segment sg = b * n_kv + h is charged
+// `seg_weight` extra positions in front of its own units (cost of unit u of segment sg = u +
+// seg_weight * sg).
 template <int NW>
-__device__ __forceinline__ void cta_range(const Shared<NW>& s, int batch, int n_kv, int& begin, int& end) {
+__device__ __forceinline__ int units_below_cost(const Shared<NW>& s, int c, int batch, int n_kv, int seg_weight) {
+    auto seg_units0 = [&](int sg, int& hpb) {
+        const int b = sg / n_kv, h = sg - b * n_kv;
+        hpb = s.prefix[b + 1] - s.prefix[b];
+        return s.prefix[b] * n_kv + h * hpb;
+    };
+    int lo = 0, hi = batch * n_kv, hpb;       // largest segment whose cost range starts at or before c
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg_units0(mid, hpb) + seg_weight * mid <= c) lo = mid; else hi = mid;
+    }
+    const int u0 = seg_units0(lo, hpb);
+    return u0 + min(max(c - (u0 + seg_weight * lo), 0), hpb);
+}
+
+// seg_weight = 0: CTA k owns units [k*Q, (k+1)*Q), Q = ceil(total / n).  seg_weight > 0: a CTA
+// whose range runs over a (b, h) boundary closes one segment and opens the next (a merge, a new
+// query), which costs it about as long as streaming seg_weight units; the division is equal in
+// cost instead: CTA k owns the units whose cost position lies in [k*Qc, (k+1)*Qc), Qc =
+// ceil((total + seg_weight * batch * n_kv) / n).  attn_combine_kernel inverts the same formula.
+template <int NW>
+__device__ __forceinline__ void cta_range(const Shared<NW>& s, int batch, int n_kv, int& begin, int& end,
+                                          int seg_weight = 0) {
     const int total = s.prefix[batch] * n_kv;
+    if (seg_weight > 0) {
+        const int qc = max(1, (total + seg_weight * batch * n_kv + int(gridDim.x) - 1) / int(gridDim.x));
+        begin = units_below_cost(s, int(blockIdx.x) * qc, batch, n_kv, seg_weight);
+        end = units_below_cost(s, (int(blockIdx.x) + 1) * qc, batch, n_kv, seg_weight);
+        return;
+    }
     const int q = (total + int(gridDim.x) - 1) / int(gridDim.x);
     begin = min(int(blockIdx.x) * q, total);
     end = min(begin + q, total);

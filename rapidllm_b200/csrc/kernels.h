@@ -21,6 +21,7 @@ struct AttnDecodeArgs {
     int batch, n_q, n_kv, n_pages, max_pages_per_seq;
     int len_add;
     float scale;                 // 1/sqrt(head_dim)
+    int seg_weight;              // charge per (sequence, head) boundary in the division of the units (attn_split.cuh)
 };
 __global__ void attn_decode_f16_kernel(AttnDecodeArgs a);
 // same arguments over the compact cache: k_pool = record pool (kv_compact.cu), v_pool unused
@@ -67,6 +68,7 @@ struct AttnCombineArgs {
     float* out_ml;               // null, or [batch][n_q][2] (max, sum): emit one partial per row
     int batch, n_q, n_kv, len_add;
     int n_ctas;                  // grid size of the decode kernel that wrote the partials
+    int seg_weight;              // the decode kernel's charge per (sequence, head) boundary, in units (attn_split.cuh)
     int max_len;                 // lengths outside [0, max_len] count as 0, as in the decode kernel
     int wht_len;                 // 0, or 128 / 256: the partials are in the rotated domain of TQ3 V
     const float* signs;          // [256] +-1 applied after the inverse transform, or null

@@ -60,12 +60,17 @@ def test_codes_are_bit_exact(oracle, wht_len, use_signs):
     assert torch.equal(again[2], v_codes) and torch.equal(again[0], k_q)
 
 
-@pytest.mark.parametrize("wht_len,use_signs", [(128, False), (256, True)])
-def test_decode_over_compact_cache(oracle, wht_len, use_signs):
+@pytest.mark.parametrize("wht_len,use_signs,lens", [
+    (128, False, [1, 31, 32, 33, 64, 65, 700, 0, 1000]),
+    (256, True, [1, 31, 32, 33, 64, 65, 700, 0, 1000]),
+    # long sequences: every head spreads over tens of CTAs, and the CTAs whose range runs over a
+    # (sequence, head) boundary own fewer records than the others
+    (128, False, [9000, 40, 0, 13000, 6001]),
+])
+def test_decode_over_compact_cache(oracle, wht_len, use_signs, lens):
     """Ragged batch; oracle = dequantise (per-token inverse transform) -> ops::attn_decode -> gate."""
     from rapidllm_b200 import _lib, ops
     gen = torch.Generator().manual_seed(22)
-    lens = [1, 31, 32, 33, 64, 65, 700, 0, 1000]
     signs = _signs(gen) if use_signs else None
     sd = signs.cuda() if use_signs else None
     q = torch.randn(len(lens), N_Q, HD, generator=gen)

@@ -149,11 +149,13 @@ def test_conv1d_update_and_prefill(oracle, golden):
     _lib.check_device()
 
 
-def test_large_batch_streaming_path(oracle):
-    """Batch 16 x 48 heads takes the persistent TMA-streamed kernel; two steps, shuffled slots."""
+@pytest.mark.parametrize("B", [14, 16, 32])
+def test_large_batch_streaming_path(oracle, B):
+    """Batch x 48 heads takes the persistent TMA-streamed kernel; two steps, shuffled slots.  On 148
+    SMs the last round of heads is taken by 80 (batch 14), 28 (batch 16) or 56 (batch 32) of the CTAs."""
     from rapidllm_b200 import _lib, ops
-    gen = torch.Generator().manual_seed(33)
-    B, n_slots = 16, 20
+    gen = torch.Generator().manual_seed(33 + B)
+    n_slots = B + 4
     S0 = torch.randn(n_slots, N_V, DK, DV, generator=gen) * 0.02
     slots = torch.randperm(n_slots, generator=gen)[:B].int()
     S = S0.cuda().clone()
