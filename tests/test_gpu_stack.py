@@ -235,3 +235,80 @@ def test_host_entry_graph_replay_matches_plain_launches():
         assert torch.equal(ao, ao2) and torch.equal(do, do2)
     for x, y in zip(outs[0][1], outs[1][1]):
         assert torch.equal(x, y)
+
+
+def test_config4_full_batch_one_period_of_the_stack(oracle):
+    """One period of the layer pattern (3 DeltaNet + 1 gated attention) at the full batch and contexts of
+    the headline workload: 32 sequences, contexts uniform in [8192, 32768], shuffled page table, seed 4.
+    DeltaNet layers: every sequence against the oracle.  Attention: the three shortest sequences against
+    the oracle; every sequence against a batch-of-one call (another division of the KV range among the
+    CTAs); the appended K/V rows read back bit for bit through the page table."""
+    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    gen = torch.Generator().manual_seed(4)
+    B = 32
+    lens = torch.randint(8192, 32769, (B,), generator=gen).tolist()
+    pages = [(n + 1 + 63) // 64 for n in lens]
+    n_pages, max_pages = sum(pages) + 3, max(pages)
+    cache = HybridCache(QWEN35_LAYER_TYPES, n_pages=n_pages, n_slots=B + 2, max_batch=B, max_pages_per_seq=max_pages)
+    assert cache.n_attn == 1 and cache.n_delta == 3
+    perm = torch.randperm(n_pages, generator=gen).int()
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    at = 0
+    for b, p in enumerate(pages):
+        table[b, :p] = perm[at:at + p]
+        at += p
+    table_d = table.cuda()
+    slots = torch.randperm(B + 2, generator=gen)[:B].int()
+    dgen = torch.Generator(device="cuda").manual_seed(4)
+    short = sorted(range(B), key=lambda b: lens[b])[:3]
+    hist = {}
+    for b in range(B):
+        k = torch.randn(lens[b], 4, 256, generator=dgen, device="cuda").half()
+        v = torch.randn(lens[b], 4, 256, generator=dgen, device="cuda").half()
+        ops.kv_append(cache.k_pool(0), cache.v_pool(0), table_d[b], k, v, pos0=0)
+        if b in short:
+            hist[b] = (k.cpu(), v.cpu())
+    S0 = [torch.randn(B + 2, 48, 128, 128, generator=gen) * 0.02 for _ in range(3)]
+    C0 = [torch.randn(B + 2, cache.conv_dim, 4, generator=gen) for _ in range(3)]
+    for d in range(3):
+        cache.state(d).copy_(S0[d])
+        cache.conv(d).copy_(C0[d])
+    t = _inputs(cache, B, gen, lens)
+    t["page_table"], t["slot_ids"] = table, slots
+    dev = {n: x.cuda() for n, x in t.items()}
+    cache.decode(dev, B)
+    _lib.check_device()
+    attn_o = dev["attn_o"].cpu().numpy()
+    delta_o = dev["delta_o"].cpu().numpy()
+    # attention
+    for b in short:
+        k = torch.cat([hist[b][0], t["attn_k"][0, b:b + 1].half()]).float().numpy()
+        v = torch.cat([hist[b][1], t["attn_v"][0, b:b + 1].half()]).float().numpy()
+        ref = oracle.gated_attn_decode(t["attn_q"][0, b].numpy(), k, v, t["attn_gate"][0, b].numpy())
+        assert np.abs(attn_o[0, b] - ref).max() <= ATTN_MAX_ABS and rel_l2(attn_o[0, b], ref) <= ATTN_REL_L2
+    for b in range(B):
+        one = ops.attn_decode(dev["attn_q"][0, b:b + 1], cache.k_pool(0), cache.v_pool(0), table_d[b:b + 1],
+                              torch.tensor([lens[b] + 1], dtype=torch.int32, device="cuda"),
+                              dev["attn_gate"][0, b:b + 1]).cpu().numpy()
+        assert rel_l2(attn_o[0, b], one[0]) <= ATTN_REL_L2, (b, rel_l2(attn_o[0, b], one[0]))
+        k_new = ops.kv_gather(cache.k_pool(0), table_d[b], lens[b] + 1)[lens[b]].cpu()
+        v_new = ops.kv_gather(cache.v_pool(0), table_d[b], lens[b] + 1)[lens[b]].cpu()
+        assert torch.equal(k_new, t["attn_k"][0, b].half()) and torch.equal(v_new, t["attn_v"][0, b].half())
+    _lib.check_device()
+    # DeltaNet
+    nk = 16 * 128
+    for d in range(3):
+        Sr = S0[d].numpy().copy()
+        Cr = C0[d].numpy().copy()
+        for b in range(B):
+            sl = int(slots[b])
+            mixed = oracle.conv1d_update(t["delta_qkv"][d, b].numpy(), t["conv_w"][d].numpy(), Cr[sl])
+            q = oracle.repeat_heads(mixed[:nk].reshape(16, 128), 48)
+            k = oracle.repeat_heads(mixed[nk:2 * nk].reshape(16, 128), 48)
+            ref = oracle.delta_step(Sr[sl], q, k, mixed[2 * nk:].reshape(48, 128),
+                                    t["delta_beta"][d, b].numpy(), t["delta_g"][d, b].numpy())
+            assert np.abs(delta_o[d, b] - ref).max() < 1e-4
+        assert rel_l2(cache.state(d).cpu().numpy(), Sr) < 1e-6
+        assert np.array_equal(cache.conv(d).cpu().numpy(), Cr)
+    cache.close()
