@@ -561,7 +561,10 @@ def run_operator(args):
         "clocks": clocks, "gpu_launches": args.steps * 2,
         "roofline": {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
-                     "bytes_per_launch": bytes_per_step, "traffic": None}}), flush=True)
+                     "bytes_per_launch": bytes_per_step,
+                     # dram read + write of one ncu capture at this workload's default size
+                     # (profiles/attn_decode_tq_kernel.compact_decode.md); traffic grows with tokens
+                     "traffic": int(1.007 * bytes_per_step) if wl == "compact_decode" else None}}), flush=True)
 
 
 def main():
