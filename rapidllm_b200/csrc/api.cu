@@ -297,6 +297,12 @@ int dev_alloc(T** p, size_t n, size_t* total) {
     return RL_OK;
 }
 
+// layers per synchronisation with the copy streams in rl_stack_decode_host
+const int kHostGroup = [] {
+    const char* e = std::getenv("RL_B200_HOST_GROUP");
+    return e ? std::max(1, atoi(e)) : 4;
+}();
+
 int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bool host_mode) {
     // not with per-kernel timing: an event between two kernels is what the overlap removes
     StepOverlap overlap(c->overlap && !c->timing);
@@ -312,7 +318,10 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
         if (tm) cudaEventRecord(c->tev[size_t(L) * 4 + i], run);
     };
     for (int L = 0; L < f.n_layers; ++L) {
-        if (host_mode) RL_CUDA(cudaStreamWaitEvent(run, c->ev_in[L], 0));
+        // host buffers: the layers synchronise with the copy streams once per group of layers, not per
+        // layer (every wait costs the run stream a few microseconds and the dependent launch behind it)
+        if (host_mode && L % kHostGroup == 0)
+            RL_CUDA(cudaStreamWaitEvent(run, c->ev_in[std::min(L + kHostGroup, f.n_layers) - 1], 0));
         mark(L, 0);
         if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
             rl_kv_append_params ap;
@@ -376,7 +385,7 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             mark(L, 2);
             ++di;
         }
-        if (host_mode) RL_CUDA(cudaEventRecord(c->ev_out[L], run));
+        if (host_mode && ((L + 1) % kHostGroup == 0 || L + 1 == f.n_layers)) RL_CUDA(cudaEventRecord(c->ev_out[L], run));
     }
     return RL_OK;
 }
@@ -1461,7 +1470,7 @@ static int host_step_enqueue(rl_cache* c, const rl_stack_io* h) {
             RL_CUDA(cudaMemcpyAsync(c->d_delta_g + di * hv_sz, h->delta_g + di * hv_sz, hv_sz * 4, H2D, c->s_h2d));
             ++di;
         }
-        RL_CUDA(cudaEventRecord(c->ev_in[L], c->s_h2d));
+        if ((L + 1) % kHostGroup == 0 || L + 1 == f.n_layers) RL_CUDA(cudaEventRecord(c->ev_in[L], c->s_h2d));
     }
     rl_stack_io d = *h;
     d.attn_q = c->d_attn_q;
@@ -1480,7 +1489,8 @@ static int host_step_enqueue(rl_cache* c, const rl_stack_io* h) {
     if (int st = stack_decode_layers(c, &d, c->s_run, true)) return st;
     ai = di = 0;
     for (int L = 0; L < f.n_layers; ++L) {
-        RL_CUDA(cudaStreamWaitEvent(c->s_d2h, c->ev_out[L], 0));
+        if (L % kHostGroup == 0)
+            RL_CUDA(cudaStreamWaitEvent(c->s_d2h, c->ev_out[std::min(L + kHostGroup, f.n_layers) - 1], 0));
         if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
             RL_CUDA(cudaMemcpyAsync(h->attn_o + ai * q_sz, c->d_attn_o + ai * q_sz, q_sz * 4, D2H, c->s_d2h));
             ++ai;
