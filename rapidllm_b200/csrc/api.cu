@@ -154,6 +154,11 @@ const int kTqSegWeight = [] {
     return e ? std::max(0, atoi(e)) : 23;
 }();
 
+const int kF16SegWeight = [] {
+    const char* e = std::getenv("RL_B200_F16_SEG_WEIGHT");
+    return e ? std::max(0, atoi(e)) : 6;
+}();
+
 int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
                      const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
                      void* workspace, size_t workspace_bytes, const rl_attn_decode_params* p, void* stream,
@@ -187,10 +192,12 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     a.max_pages_per_seq = p->max_pages_per_seq;
     a.len_add = p->len_add;
     a.scale = 1.f / sqrtf(float(p->head_dim));
-    // Compact KV: a CTA that closes one (sequence, head) segment and opens the next spends ~6 us on
-    // it, the time of ~23 records of 32 tokens at 44 GB/s per SM; its share of the records is cut by
-    // that much.  F16: the division stays equal in units.
-    a.seg_weight = tq ? kTqSegWeight : 0;
+    // A CTA that closes one (sequence, head) segment and opens the next spends a few microseconds on
+    // it (compact KV: ~6 us, the time of ~23 records of 32 tokens at 44 GB/s per SM; F16: the time of
+    // ~6 half pages).  While only a minority of the CTAs have a boundary in their range, those CTAs
+    // are the last to finish, so their share of the units is cut by that much; once nearly every CTA
+    // has one (segments > CTAs / 4) the division stays equal in units, which measured faster there.
+    a.seg_weight = p->batch * p->n_kv * 4 <= pl.grid ? (tq ? kTqSegWeight : kF16SegWeight) : 0;
     const int grid = pl.grid;
     if (tq)
         rl::attn_decode_tq_kernel<<<grid, rl::attn_decode_tq_threads(), rl::attn_decode_tq_smem_bytes(),
