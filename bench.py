@@ -699,8 +699,8 @@ def main():
         cache.decode(dev, B)
         exchange()
     _lib.check_device()
+    sampler.mark()                               # may sleep: before the barrier, so that the ranks leave it together
     sync_all()
-    sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
