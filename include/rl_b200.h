@@ -114,9 +114,11 @@ int rl_attn_decode(const void* k_pool, const void* v_pool, const int32_t* page_t
  *   - the call needs (SM count + batch * n_kv) * (n_q / n_kv) * 1032 bytes of that array,
  *     rounded up to 512; anything beyond 4 MiB (for 24Q/4KV heads on a 148-SM part:
  *     batch > 132) is refused with RL_ERR_RANGE and a message, nothing is launched;
- *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
- *   - the first call on a device looks up the array's device address (and does the
- *     library's one-time per-device set-up); make that first call outside any stream capture;
+ *   - the first call of any entry point on a device does the library's one-time set-up for that
+ *     device (kernel attributes, a synchronising clear of the 4-byte error word) and this entry
+ *     point's first call also looks up the array's device address; make that first call outside
+ *     any stream capture.  Every later call allocates nothing: no cudaMalloc / cudaFree, no
+ *     stream or event creation, no allocating library routine;
  *   - all calls on a device share the array, which keeps the previous call's contents.
  *     Nothing in it has to start at zero (every slot a call reads, that call wrote first),
  *     but two calls that overlap on the GPU (different streams, or a graph replayed while

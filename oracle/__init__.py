@@ -16,11 +16,19 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "librl_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "librl_ref.so")
+REF_CUDA_SO = os.path.join(_HERE, "_ref", "librl_refcuda.so")
+
+
+def reference_tree() -> str:
+    """Where the RapidLLM sources lie: $RAPIDLLM_REFERENCE, else a `reference` directory beside
+    this repository; "" when neither exists (then only the restatement is built)."""
+    cand = os.environ.get("RAPIDLLM_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.exists(os.path.join(cand, "src", "kernels", "ops.cpp")) else ""
 
 
 def build(quiet: bool = True) -> None:
-    """Compile the restatement (and the reference library when its tree is there)."""
-    subprocess.run(["make", "-C", _HERE], check=True,
+    """Compile the restatement (and the reference libraries when its tree is there)."""
+    subprocess.run(["make", "-C", _HERE, "REF=" + reference_tree()], check=True,
                    stdout=subprocess.DEVNULL if quiet else None)
 
 
@@ -470,3 +478,69 @@ class Reference:
         y = np.empty_like(x)
         self.lib.ref_l2norm(xp, _ptr(y, C.c_float), x.size, C.c_float(eps))
         return y
+
+
+class ReferenceCuda:
+    """The reference's own CUDA kernels for the compact KV cache (oracle/_ref/librl_refcuda.so =
+    its engine translation unit compiled in place behind ref_cuda_shim.cu).  Needs a GPU."""
+
+    def __init__(self):
+        if not os.path.exists(REF_CUDA_SO):
+            raise FileNotFoundError(REF_CUDA_SO)
+        self.lib = C.CDLL(REF_CUDA_SO)
+        self.lib.rlref_cuda_error_string.restype = C.c_char_p
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_CUDA_SO)
+
+    def _check(self, code, what):
+        if code:
+            raise RuntimeError("%s: %s" % (what, self.lib.rlref_cuda_error_string(code).decode()))
+
+    def compact_store(self, k, v):
+        """store_k_q8_th_k + store_v_tq3_th_k (cuda_engine.cu:8224-8284): k, v [T, n_kv, 256] fp32 ->
+        (k_q i8 [T,n_kv,256], k_sc u16 [T,n_kv], v_codes u8 [T,n_kv,96], v_sc u16 [T,n_kv,2])."""
+        k, kp = _f32(k)
+        v, vp = _f32(v)
+        T, n_kv, hd = k.shape
+        assert hd == 256
+        k_q = np.empty((T, n_kv, hd), np.int8)
+        k_sc = np.empty((T, n_kv), np.uint16)
+        v_codes = np.empty((T, n_kv, 96), np.uint8)
+        v_sc = np.empty((T, n_kv, 2), np.uint16)
+        self._check(self.lib.rlref_cuda_compact_store(kp, vp, T, n_kv, _ptr(k_q, C.c_int8), _ptr(k_sc, C.c_uint16),
+                                                      _ptr(v_codes, C.c_uint8), _ptr(v_sc, C.c_uint16)),
+                    "rlref_cuda_compact_store")
+        return k_q, k_sc, v_codes, v_sc
+
+    def compact_dequant(self, k_q, k_sc, v_codes, v_sc):
+        """dequant_k_q8_h_k + dequant_v_tq3_h_k (cuda_engine.cu:8286-8314) -> k, v fp16 bits [T,n_kv,256]."""
+        k_q = np.ascontiguousarray(k_q, np.int8)
+        k_sc = np.ascontiguousarray(k_sc, np.uint16)
+        v_codes = np.ascontiguousarray(v_codes, np.uint8)
+        v_sc = np.ascontiguousarray(v_sc, np.uint16)
+        T, n_kv, hd = k_q.shape
+        k16 = np.empty((T, n_kv, hd), np.uint16)
+        v16 = np.empty((T, n_kv, hd), np.uint16)
+        self._check(self.lib.rlref_cuda_compact_dequant(_ptr(k_q, C.c_int8), _ptr(k_sc, C.c_uint16),
+                                                        _ptr(v_codes, C.c_uint8), _ptr(v_sc, C.c_uint16), T, n_kv,
+                                                        _ptr(k16, C.c_uint16), _ptr(v16, C.c_uint16)),
+                    "rlref_cuda_compact_dequant")
+        return k16.view(np.float16), v16.view(np.float16)
+
+    def attn_decode_tq(self, q, k_q, k_sc, v_codes, v_sc, pos=None):
+        """qk_attn_decode_tq_gqa_k (cuda_engine.cu:8382-8454): q [n_q,256] over tokens [0, pos]."""
+        q, qp = _f32(q)
+        k_q = np.ascontiguousarray(k_q, np.int8)
+        k_sc = np.ascontiguousarray(k_sc, np.uint16)
+        v_codes = np.ascontiguousarray(v_codes, np.uint8)
+        v_sc = np.ascontiguousarray(v_sc, np.uint16)
+        T, n_kv, _ = k_q.shape
+        pos = T - 1 if pos is None else pos
+        o = np.empty_like(q)
+        self._check(self.lib.rlref_cuda_attn_decode_tq(qp, int(pos), q.shape[0], n_kv, _ptr(k_q, C.c_int8),
+                                                       _ptr(k_sc, C.c_uint16), _ptr(v_codes, C.c_uint8),
+                                                       _ptr(v_sc, C.c_uint16), T, _ptr(o, C.c_float)),
+                    "rlref_cuda_attn_decode_tq")
+        return o

@@ -45,9 +45,18 @@ struct DevInfo {
     int cc_major = 0;
     int* err_ptr = nullptr;
     bool attn_attr = false;
-    // second stream + events for the calls that overlap two of their own kernels (rl_delta_chunk_prefill)
-    cudaStream_t aux = nullptr;
-    cudaEvent_t aux_ev[9] = {};
+    // second streams + events for the calls that overlap two of their own kernels
+    // (rl_delta_chunk_prefill): a pool, one set per call in flight (aux_acquire)
+    std::vector<struct AuxSet*> aux_pool;
+};
+// One side stream with its fork/join events.  A set belongs to one call from aux_acquire()
+// until the join event that call recorded last has completed, so two host threads (or two
+// streams) running such calls on one device never share events.
+struct AuxSet {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork[8] = {};
+    cudaEvent_t join = nullptr;
+    bool used = false;              // join has been recorded at least once
 };
 std::mutex g_mu;
 }  // namespace
@@ -85,13 +94,39 @@ int dev_info(DevInfo** out) {
                                      int(rl::attn_prefill_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_decode_tq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::attn_decode_tq_smem_bytes())));
-        int lo = 0, hi = 0;
-        RL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-        RL_CUDA(cudaStreamCreateWithPriority(&d.aux, cudaStreamNonBlocking, hi));
-        for (cudaEvent_t& e : d.aux_ev) RL_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         d.ready = true;
     }
     *out = &d;
+    return RL_OK;
+}
+
+// A side-stream set no earlier call is still using: one whose last join event has completed,
+// else a new one (the pool only grows to the number of such calls in flight at once).
+int aux_acquire(DevInfo* d, AuxSet** out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (AuxSet* a : d->aux_pool) {
+        if (!a->used) { *out = a; return RL_OK; }
+        const cudaError_t q = cudaEventQuery(a->join);
+        if (q == cudaSuccess) { *out = a; return RL_OK; }
+        if (q != cudaErrorNotReady) cudaGetLastError();   // e.g. recorded inside a capture: treat as busy
+    }
+    AuxSet* a = new (std::nothrow) AuxSet();
+    if (!a) return fail(RL_ERR_NOMEM, "host allocation failed");
+    int lo = 0, hi = 0;
+    cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&a->stream, cudaStreamNonBlocking, hi);
+    for (cudaEvent_t& ev : a->fork)
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&a->join, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        for (cudaEvent_t ev : a->fork) if (ev) cudaEventDestroy(ev);
+        if (a->join) cudaEventDestroy(a->join);
+        if (a->stream) cudaStreamDestroy(a->stream);
+        delete a;
+        return fail(RL_ERR_DEVICE, "creating a side stream: %s", cudaGetErrorString(e));
+    }
+    d->aux_pool.push_back(a);
+    *out = a;
     return RL_OK;
 }
 
@@ -149,15 +184,17 @@ AttnPlan attn_plan(const rl_attn_decode_params* p, int sms) {
     return pl;
 }
 
-const int kTqSegWeight = [] {
-    const char* e = std::getenv("RL_B200_TQ_SEG_WEIGHT");
-    return e ? std::max(0, atoi(e)) : 23;
-}();
-
-const int kF16SegWeight = [] {
-    const char* e = std::getenv("RL_B200_F16_SEG_WEIGHT");
-    return e ? std::max(0, atoi(e)) : 6;
-}();
+// Tuning constants.  The shipped library never looks at the environment; a development build
+// (-DRL_B200_DEV_KNOBS) lets a measurement override them once, at load time.
+int knob(const char* name, int dflt) {
+#ifdef RL_B200_DEV_KNOBS
+    if (const char* e = std::getenv(name)) return std::max(0, atoi(e));
+#endif
+    (void)name;
+    return dflt;
+}
+const int kTqSegWeight = knob("RL_B200_TQ_SEG_WEIGHT", 23);
+const int kF16SegWeight = knob("RL_B200_F16_SEG_WEIGHT", 6);
 
 int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
                      const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
@@ -262,7 +299,7 @@ struct rl_cache {
     // graph replay of rl_stack_decode: the step's launches are captured once per distinct io
     // (same pointers, same batch) and replayed afterwards; positions, page table and slots are
     // read from device memory by the kernels, so the captured step stays valid as they advance
-    bool overlap = std::getenv("RL_B200_NO_STEP_OVERLAP") == nullptr;   // dependent launch between the step's kernels
+    bool overlap = true;            // dependent launch between the step's kernels
     bool graph_enabled = true;
     cudaGraphExec_t gexec = nullptr;
     rl_stack_io gkey;               // io of the captured graph / of the last eager step
@@ -305,10 +342,7 @@ int dev_alloc(T** p, size_t n, size_t* total) {
 }
 
 // layers per synchronisation with the copy streams in rl_stack_decode_host
-const int kHostGroup = [] {
-    const char* e = std::getenv("RL_B200_HOST_GROUP");
-    return e ? std::max(1, atoi(e)) : 4;
-}();
+const int kHostGroup = std::max(1, knob("RL_B200_HOST_GROUP", 4));
 
 int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bool host_mode) {
     // not with per-kernel timing: an event between two kernels is what the overlap removes
@@ -631,7 +665,6 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
     a.n_kv = p->n_kv;
     a.n_pages = p->n_pages;
     a.scale = 1.f / sqrtf(float(p->head_dim));
-    a.trace = reinterpret_cast<unsigned long long*>(getenv("RL_B200_PREFILL_TRACE") ? strtoull(getenv("RL_B200_PREFILL_TRACE"), nullptr, 0) : 0ull);
     const int n_qtiles = (p->seq + rl::attn_prefill_q_rows() - 1) / rl::attn_prefill_q_rows();
     // a workspace lets short chunks (or a handful of verify rows over a long cache) spread every
     // (query tile, head) over several CTAs; without one the call runs unsplit
@@ -988,15 +1021,18 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
         prepare(0, n_chunks, run);
         scan(0, n_chunks, run);
     } else {
+        AuxSet* aux = nullptr;
+        if (int st = aux_acquire(d, &aux)) return st;
         for (int i = 0; i < n_seg; ++i) {
             const int c0 = int(1LL * i * n_chunks / n_seg), c1 = int(1LL * (i + 1) * n_chunks / n_seg);
             prepare(c0, c1 - c0, run);
-            RL_CUDA(cudaEventRecord(d->aux_ev[i], run));
-            RL_CUDA(cudaStreamWaitEvent(d->aux, d->aux_ev[i], 0));     // also orders the first scan after the caller's work
-            scan(c0, c1 - c0, d->aux);
+            RL_CUDA(cudaEventRecord(aux->fork[i], run));
+            RL_CUDA(cudaStreamWaitEvent(aux->stream, aux->fork[i], 0));   // also orders the first scan after the caller's work
+            scan(c0, c1 - c0, aux->stream);
         }
-        RL_CUDA(cudaEventRecord(d->aux_ev[8], d->aux));
-        RL_CUDA(cudaStreamWaitEvent(run, d->aux_ev[8], 0));
+        RL_CUDA(cudaEventRecord(aux->join, aux->stream));
+        aux->used = true;
+        RL_CUDA(cudaStreamWaitEvent(run, aux->join, 0));
     }
     RL_CUDA(cudaGetLastError());
     return RL_OK;

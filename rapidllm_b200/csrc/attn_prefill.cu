@@ -130,16 +130,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
-    const bool tr = a.trace && blockIdx.x == 0 && parts == 1;
-    // per-CTA record after the 64 x 8 tile timestamps: start, main loop start, end, SM id
-    unsigned long long* cta_rec = a.trace ? a.trace + 512 + ((size_t(hq) * n_qtiles + (n_qtiles - 1 - qt)) * parts + part) * 4 : nullptr;
-    if (cta_rec && tid == 0) {
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        cta_rec[0] = global_ns();
-        cta_rec[3] = smid | (static_cast<unsigned long long>(clock64()) << 16);
-    }
-#define RL_TRACE(J, SLOT) if (tr && (J) < 64) a.trace[(J) * 8 + (SLOT)] = global_ns();
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
     // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the four threads
     // of a row stores 64 dims.  The rows come in by bulk copies (one per row), issued by the loader warp
@@ -192,7 +182,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         tc::tmem_wait_st();
         tc::fence_before_sync();
         mbar_arrive(&s.bar_q);                                // Q is in tensor memory (awaited by the S issuer)
-        if (cta_rec && tid == 0) cta_rec[1] = global_ns();
         // the epilogue's gate rows: start them on their way into L2 now (2 of the row's 8 lines each)
         if (a.gate && a.kv_parts <= 1 && r < rows) {
             const float* gp = a.gate + flat_row(r) * kHeadDim + qpart * 64;
@@ -240,10 +229,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             bool ok = mbar_wait(&s.bar_q, 0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int st = j % kKStages;
-                if (tr) { RL_TRACE(j, 0) }
                 if (!mbar_wait(&s.k_full[st], (j / kKStages) & 1)) { ok = false; break; }
                 // the S buffer is free once every softmax thread of the previous tile has read it out
-                if (tr) { RL_TRACE(j, 5) }
                 if (j >= 1 && !mbar_wait(&s.bar_sfree[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
                 tc::fence_after_sync();
                 const uint64_t kd = st == 0 ? k_desc[0] : (st == 1 ? k_desc[1] : k_desc[2]);
@@ -256,7 +243,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                                idesc_qk, kk > 0);
                 tc::commit(&s.k_empty[st]);           // K stage free once S_j is done
                 tc::commit(&s.bar_s[j & 1]);
-                if (tr) { RL_TRACE(j, 1) }
             }
             if (!ok) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -275,7 +261,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 const int st = j % kVStages;
                 if (!mbar_wait(&s.v_full[st], (j / kVStages) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_p[j & 1], (j >> 1) & 1)) { ok = false; break; }
-                if (tr) { RL_TRACE(j, 2) }
                 tc::fence_after_sync();
                 const uint64_t vd = st == 0 ? v_desc[0] : (st == 1 ? v_desc[1] : v_desc[2]);
                 const uint32_t p_tmem = tmem + kColP + (j & 1) * 32;
@@ -286,7 +271,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                     tc::mma_ts(tmem + kColO, p_tmem + kk * 8, vd + uint64_t((kk * 16 * 128) >> 4), idesc_pv, 1);
                 tc::commit(&s.v_empty[st]);           // V stage free
                 tc::commit(&s.bar_pv[j & 1]);         // this P buffer free, O consistent
-                if (tr) { RL_TRACE(j, 3) }
             }
             if (!ok) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -313,7 +297,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                 ok = false;
             }
             tc::fence_after_sync();
-            if (tid == 0 || tid == kGroupThreads) { RL_TRACE(j, 4) }
             uint32_t raw[32];
             if (ok) {
                 tc::tmem_ld32(lane_addr + kColS + half * 32, raw);
@@ -394,7 +377,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                     tc::tmem_wait_st();
                 }
             }
-            if (tid == 0 || tid == kGroupThreads) { RL_TRACE(j, 6) }
             // this thread's partial row sum follows the maximum (it may have moved twice since
             // this group's previous tile)
             if (m_new != m_known) {
@@ -426,7 +408,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             }
             tc::fence_before_sync();
             mbar_arrive(&s.bar_p[grp]);
-            if (tid == 0 || tid == kGroupThreads) { RL_TRACE(j, 7) }
         }
         // ------------------------------ epilogue ------------------------------
         // final maximum = after the last tile; the four partial sums of a row are brought to it
@@ -525,11 +506,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         tc::fence_before_sync();
     }
     __syncthreads();
-    if (cta_rec && tid == 0) {
-        cta_rec[2] = global_ns();
-        const unsigned long long c0 = cta_rec[3] >> 16;
-        cta_rec[3] = (cta_rec[3] & 0xffff) | (((static_cast<unsigned long long>(clock64()) - c0) & 0xffffffffffffull) << 16);
-    }
     if (warp == kWarpQK) tc::tmem_dealloc(tmem, kTmemCols);
 }
 

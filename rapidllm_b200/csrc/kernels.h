@@ -51,7 +51,6 @@ struct AttnPrefillArgs {
     float* part_ml;
     int packed;                  // T * (n_q / n_kv) <= 128: one item per KV head, MMA rows = (token, head of the group)
     int wave;                    // CTAs resident at a time (one per SM): CTA i + wave is taken to follow CTA i on its SM
-    unsigned long long* trace;   // development aid: null, or room for 8 timestamps x 64 tiles of CTA (0,0) + 4 words per CTA
 };
 __global__ void attn_prefill_kernel(AttnPrefillArgs a);
 size_t attn_prefill_smem_bytes();

@@ -30,7 +30,7 @@ from oracle import Reference  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of the RapidLLM tree")
     args = ap.parse_args()
     ref = Reference()
     out = {}
