@@ -28,7 +28,7 @@ extern "C" {
 #pragma GCC visibility push(default)
 #endif
 
-#define RL_B200_ABI_VERSION 1
+#define RL_B200_ABI_VERSION 2
 
 /* Same values as RapidStatus, include/rapidllm/api.h:11-20. */
 typedef enum rl_status {
@@ -290,6 +290,10 @@ typedef struct rl_delta_chunk_params {
 } rl_delta_chunk_params;
 
 size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p);
+/* Floating-point operations of the tensor-core MMAs rl_delta_chunk_prefill issues per (chunk of 64
+ * tokens, value head) in its sequential scan: the figure a tensor roofline of the call is computed
+ * from (2 * M * N * K per MMA as issued, the hi + lo operand splits counted as issued). */
+double rl_delta_chunk_mma_flops(void);
 
 /* T consecutive delta-rule steps of ONE sequence in chunked (WY) form on the tensor cores:
  * the result of calling ops::delta_recurrent_step (src/kernels/ops.cpp:495-540) T times, which
@@ -512,6 +516,47 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream);
  * out included (pinned host buffers; with pageable ones it stays on plain launches).  Disabled
  * while rl_stack_set_timing is on. */
 int rl_stack_set_graph(rl_cache* c, int enable);
+
+/* ---- one batch on several GPUs of one node ---------------------------------------------------
+ * The reference engine is single-GPU (one Engine per process, cuda_engine.h:13-83); this part has
+ * no counterpart there.  The mixers shard without moving KV or state: every rank (one process per
+ * GPU) owns a slice of the KV heads / DeltaNet value heads (its rl_cache is created with the local
+ * head counts), and/or a subset of the sequences, and/or a token range of every sequence
+ * (rl_stack_io.attn_ml / no_append).  The one exchange is an all-gather of the per-layer outputs,
+ * issued by rl_stack_decode on an internal side stream right after the layer that produced them,
+ * so it runs beside the following layers; the step's stream waits for the last exchange at the end
+ * of the step.  Transport: NCCL (ncclAllGather over NVLink / NVSwitch), bound at run time from
+ * libnccl.so.2; no peer pointers, no multicast loads. */
+#define RL_COMM_ID_BYTES 128
+typedef struct rl_comm rl_comm;
+/* ncclGetUniqueId: called by one rank; the host program hands the RL_COMM_ID_BYTES bytes to every
+ * rank (any transport: a file, MPI, torch.distributed ...). */
+int rl_comm_unique_id(void* id);
+/* ncclCommInitRank on the current device; collective over the n_ranks processes. */
+int rl_comm_create(const void* id, int rank, int n_ranks, rl_comm** out);
+void rl_comm_destroy(rl_comm* comm);
+
+/* Where the gathered outputs of a sharded step go (all device pointers, owned by the caller, fixed
+ * for the life of the setting).  n_q, n_v below are this rank's LOCAL head counts and batch the
+ * LOCAL batch, as in rl_stack_io; every rank must use the same local shapes.
+ *   attn_o_all   [n_attn][n_ranks][batch][n_q][256]   block r = rank r's attn_o of that layer
+ *   delta_o_all  [n_delta][n_ranks][batch][n_v][dv]
+ *   attn_ml_all  [n_attn][n_ranks][batch][n_q][2]     split-KV only (io.attn_ml != NULL)
+ *   attn_o_final [n_attn][batch][n_q][256]            split-KV only: the partials of all ranks merged
+ *                                                     (log-sum-exp) and gated, on every rank
+ * layers_per_exchange: how many layers' outputs one grouped exchange carries; 0 = 4 (one exchange
+ * per attention layer of the 3 + 1 pattern); n_layers = a single exchange at the end of the step. */
+typedef struct rl_stack_gather {
+    rl_comm* comm;
+    float* attn_o_all;
+    float* delta_o_all;
+    float* attn_ml_all;
+    float* attn_o_final;
+    int layers_per_exchange;
+} rl_stack_gather;
+/* Attach (or, with g == NULL, detach) the exchange to every following rl_stack_decode[_host] of
+ * this cache.  Every rank of the communicator must then call the step the same number of times. */
+int rl_stack_set_gather(rl_cache* c, const rl_stack_gather* g);
 
 /* The same step for a caller that keeps its tensors in HOST memory (pinned for
  * full speed): copies every input of io (host pointers) to staging buffers on

@@ -96,6 +96,14 @@ class StackIO(C.Structure):
         ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int)]
 
 
+class StackGather(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("comm", "attn_o_all", "delta_o_all", "attn_ml_all", "attn_o_final")] + [
+        ("layers_per_exchange", C.c_int)]
+
+
+COMM_ID_BYTES = 128
+
+
 class StackPrefillIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "attn_q", "attn_k", "attn_v", "attn_gate", "attn_o", "delta_qkv", "delta_beta", "delta_g", "delta_o",
@@ -131,6 +139,7 @@ SYMBOLS = {
     "rl_delta_recurrent_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                       C.POINTER(DeltaRecurrentParams), _i, C.c_longlong, C.c_longlong, _vp]),
     "rl_delta_chunk_workspace_bytes": (_sz, [C.POINTER(DeltaChunkParams)]),
+    "rl_delta_chunk_mma_flops": (C.c_double, []),
     "rl_delta_chunk_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(DeltaChunkParams), _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),
     "rl_conv1d_causal": (_i, [_vp, _vp, _vp, _vp, _i, C.POINTER(Conv1dParams), _i, _vp]),
@@ -156,6 +165,10 @@ SYMBOLS = {
     "rl_stack_set_timing": (_i, [_vp, _i]),
     "rl_stack_set_graph": (_i, [_vp, _i]),
     "rl_stack_timing": (_i, [_vp, C.POINTER(C.c_float)]),
+    "rl_comm_unique_id": (_i, [_vp]),
+    "rl_comm_create": (_i, [_vp, _i, _i, C.POINTER(_vp)]),
+    "rl_comm_destroy": (None, [_vp]),
+    "rl_stack_set_gather": (_i, [_vp, C.POINTER(StackGather)]),
 }
 
 _lib = None

@@ -161,6 +161,30 @@ class HybridCache:
                                      C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return workspace
 
+    def gather_shapes(self, batch, n_ranks):
+        """Tensor name -> shape of the buffers a sharded step gathers into (rl_stack_gather)."""
+        A, D, B, W = self.n_attn, self.n_delta, batch, n_ranks
+        return {"attn_o_all": (A, W, B, self.n_q, 256), "delta_o_all": (D, W, B, self.n_v, self.dv),
+                "attn_ml_all": (A, W, B, self.n_q, 2), "attn_o_final": (A, B, self.n_q, 256)}
+
+    def set_gather(self, comm, tensors: dict | None, layers_per_exchange: int = 0):
+        """Attach the all-gather of the step's outputs over `comm` (a Comm) to decode() /
+        decode_host(); tensors: device buffers shaped as gather_shapes().  None detaches."""
+        if comm is None or tensors is None:
+            check(lib().rl_stack_set_gather(self._h, None))
+            self._gather = None
+            return
+        g = _lib.StackGather(comm=comm.handle, layers_per_exchange=layers_per_exchange)
+        for name in ("attn_o_all", "delta_o_all", "attn_ml_all", "attn_o_final"):
+            x = tensors.get(name)
+            if x is None:
+                continue
+            if not (x.is_cuda and x.is_contiguous() and x.dtype == torch.float32):
+                raise _lib.RlError(6, f"{name}: need a contiguous fp32 CUDA tensor")
+            setattr(g, name, x.data_ptr())
+        check(lib().rl_stack_set_gather(self._h, C.byref(g)))
+        self._gather = (comm, tensors)           # keep the buffers alive
+
     def set_conv_w(self, host_w: torch.Tensor):
         check(lib().rl_stack_set_conv_w(self._h, C.c_void_p(host_w.data_ptr())))
 
@@ -168,3 +192,24 @@ class HybridCache:
         """One step with HOST tensors (pinned for speed): H2D, step, D2H (rl_stack_decode_host)."""
         io = self._io(tensors, batch, False)
         check(lib().rl_stack_decode_host(self._h, C.byref(io)))
+
+
+class Comm:
+    """rl_comm: the NCCL communicator of the ranks that share a step.  `exchange_id` is any
+    callable that takes the 128-byte id made on rank 0 (bytes, or None on other ranks) and returns
+    it on every rank, e.g. a torch.distributed broadcast."""
+
+    def __init__(self, rank: int, n_ranks: int, exchange_id):
+        buf = (C.c_ubyte * _lib.COMM_ID_BYTES)()
+        if rank == 0:
+            check(lib().rl_comm_unique_id(buf))
+        raw = exchange_id(bytes(buf) if rank == 0 else None)
+        buf = (C.c_ubyte * _lib.COMM_ID_BYTES).from_buffer_copy(raw)
+        h = C.c_void_p()
+        check(lib().rl_comm_create(buf, rank, n_ranks, C.byref(h)))
+        self.handle, self.rank, self.n_ranks = h, rank, n_ranks
+
+    def close(self):
+        if getattr(self, "handle", None):
+            lib().rl_comm_destroy(self.handle)
+            self.handle = None

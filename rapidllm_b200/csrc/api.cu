@@ -13,6 +13,7 @@
 #include <string>
 #include <vector>
 
+#include "comm.h"
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.cuh"
@@ -312,6 +313,11 @@ struct rl_cache {
     int hkey_seen = 0;
     bool host_graph_failed = false;
     cudaEvent_t ev_fork = nullptr, ev_join_a = nullptr, ev_join_b = nullptr;
+    // sharded step: where the gathered outputs go, the side stream the exchanges run on and the
+    // events that fork it from / join it to the step's stream (rl_stack_set_gather)
+    rl_stack_gather gather = {};
+    cudaStream_t s_comm = nullptr;
+    cudaEvent_t ev_xfork = nullptr, ev_xjoin = nullptr;
     rl_attn_decode_params attn_params(int batch) const {
         rl_attn_decode_params p;
         std::memset(&p, 0, sizeof p);
@@ -357,6 +363,41 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
     const bool tm = c->timing && !c->tev.empty();
     auto mark = [&](int L, int i) {
         if (tm) cudaEventRecord(c->tev[size_t(L) * 4 + i], run);
+    };
+    // Sharded step: the outputs of the layers since the last exchange are all-gathered on the side
+    // stream (one grouped NCCL call), beside the layers that follow; split-KV partials are merged
+    // and gated there too, straight out of the gather buffer.
+    const rl_stack_gather& gx = c->gather;
+    rl::Comm* comm = reinterpret_cast<rl::Comm*>(gx.comm);
+    const int n_ranks = comm ? rl::comm_ranks(comm) : 1;
+    const int per_x = gx.layers_per_exchange > 0 ? gx.layers_per_exchange : 4;
+    int sent_a = 0, sent_d = 0;
+    auto exchange = [&]() -> int {
+        if (sent_a == ai && sent_d == di) return RL_OK;
+        RL_CUDA(cudaEventRecord(c->ev_xfork, run));
+        RL_CUDA(cudaStreamWaitEvent(c->s_comm, c->ev_xfork, 0));
+        const size_t ml_sz = size_t(B) * f.n_q * 2;
+        int bad = rl::comm_group_start();
+        for (int a = sent_a; a < ai && !bad; ++a) {
+            bad = rl::comm_all_gather_f32(comm, io->attn_o + a * q_sz, gx.attn_o_all + size_t(a) * n_ranks * q_sz, q_sz, c->s_comm);
+            if (!bad && io->attn_ml)
+                bad = rl::comm_all_gather_f32(comm, io->attn_ml + a * ml_sz, gx.attn_ml_all + size_t(a) * n_ranks * ml_sz, ml_sz,
+                                              c->s_comm);
+        }
+        for (int d = sent_d; d < di && !bad; ++d)
+            bad = rl::comm_all_gather_f32(comm, io->delta_o + d * do_sz, gx.delta_o_all + size_t(d) * n_ranks * do_sz, do_sz,
+                                          c->s_comm);
+        const int bad_end = rl::comm_group_end();
+        if (bad || bad_end) return fail(RL_ERR_DEVICE, "exchange of the step's outputs: %s", rl::comm_last_error());
+        if (io->attn_ml)
+            for (int a = sent_a; a < ai; ++a)
+                rl::lse_combine_kernel<<<unsigned(B * f.n_q), 256, 0, c->s_comm>>>(
+                    gx.attn_o_all + size_t(a) * n_ranks * q_sz, gx.attn_ml_all + size_t(a) * n_ranks * ml_sz,
+                    io->attn_gate ? io->attn_gate + a * q_sz : nullptr, gx.attn_o_final + a * q_sz, n_ranks, B * f.n_q, 0,
+                    nullptr);
+        sent_a = ai;
+        sent_d = di;
+        return RL_OK;
     };
     for (int L = 0; L < f.n_layers; ++L) {
         // host buffers: the layers synchronise with the copy streams once per group of layers, not per
@@ -427,6 +468,13 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             ++di;
         }
         if (host_mode && ((L + 1) % kHostGroup == 0 || L + 1 == f.n_layers)) RL_CUDA(cudaEventRecord(c->ev_out[L], run));
+        if (comm && ((L + 1) % per_x == 0 || L + 1 == f.n_layers))
+            if (int st = exchange()) return st;
+    }
+    if (comm) {
+        // the step is complete on `run` only when every rank's outputs have arrived
+        RL_CUDA(cudaEventRecord(c->ev_xjoin, c->s_comm));
+        RL_CUDA(cudaStreamWaitEvent(run, c->ev_xjoin, 0));
     }
     return RL_OK;
 }
@@ -967,6 +1015,8 @@ size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p) {
     return align_up(n_chunks * p->n_v * rl::delta_chunk_record_bytes(), 256) + align_up(n_chunks * p->n_v * sizeof(float), 256);
 }
 
+double rl_delta_chunk_mma_flops(void) { return rl::delta_chunk_scan_mma_flops(); }
+
 int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float* v, const float* beta,
                            const float* g_log, float* o, void* workspace, size_t workspace_bytes,
                            const rl_delta_chunk_params* p, void* stream) {
@@ -1201,6 +1251,9 @@ void rl_cache_destroy(rl_cache* c) {
     if (c->hexec) cudaGraphExecDestroy(c->hexec);
     for (cudaEvent_t e : {c->ev_fork, c->ev_join_a, c->ev_join_b})
         if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : {c->ev_xfork, c->ev_xjoin})
+        if (e) cudaEventDestroy(e);
+    if (c->s_comm) cudaStreamDestroy(c->s_comm);
     if (c->s_cap) cudaStreamDestroy(c->s_cap);
     if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
     if (c->s_run) cudaStreamDestroy(c->s_run);
@@ -1393,6 +1446,8 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
                        (!io->no_append && (!io->attn_k || !io->attn_v)))) ||
         (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    if (c->gather.comm && io->attn_ml && c->n_attn && (!c->gather.attn_ml_all || !c->gather.attn_o_final))
+        return fail(RL_ERR_RANGE, "split-KV partials need attn_ml_all and attn_o_final in rl_stack_gather");
     if (!c->graph_enabled || c->timing) return stack_decode_layers(c, io, as_stream(stream), false);
     const bool same = c->gkey_seen > 0 && same_io(c->gkey, io);
     if (same && c->gkey_seen == 2) {
@@ -1428,6 +1483,56 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
     c->gexec = nullptr;
     c->graph_enabled = false;       // capture is not possible here: stay on plain launches
     return stack_decode_layers(c, io, as_stream(stream), false);
+}
+
+int rl_comm_unique_id(void* id) {
+    if (!id) return fail(RL_ERR_RANGE, "id is NULL");
+    if (rl::comm_unique_id(id)) return fail(RL_ERR_UNSUPPORTED, "%s", rl::comm_last_error());
+    return RL_OK;
+}
+
+int rl_comm_create(const void* id, int rank, int n_ranks, rl_comm** out) {
+    if (!id || !out) return fail(RL_ERR_RANGE, "NULL argument");
+    *out = nullptr;
+    if (n_ranks < 1 || rank < 0 || rank >= n_ranks) return fail(RL_ERR_RANGE, "rank %d outside [0, %d)", rank, n_ranks);
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::Comm* c = nullptr;
+    if (rl::comm_create(id, rank, n_ranks, &c)) return fail(RL_ERR_DEVICE, "%s", rl::comm_last_error());
+    *out = reinterpret_cast<rl_comm*>(c);
+    return RL_OK;
+}
+
+void rl_comm_destroy(rl_comm* comm) { rl::comm_destroy(reinterpret_cast<rl::Comm*>(comm)); }
+
+int rl_stack_set_gather(rl_cache* c, const rl_stack_gather* g) {
+    if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
+    if (g && g->comm) {
+        if ((c->n_attn && !g->attn_o_all) || (c->n_delta && !g->delta_o_all))
+            return fail(RL_ERR_RANGE, "gather buffers are NULL");
+        if (g->layers_per_exchange < 0) return fail(RL_ERR_RANGE, "layers_per_exchange %d", g->layers_per_exchange);
+        if (!c->s_comm) {
+            int lo = 0, hi = 0;
+            RL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+            RL_CUDA(cudaStreamCreateWithPriority(&c->s_comm, cudaStreamNonBlocking, hi));
+            RL_CUDA(cudaEventCreateWithFlags(&c->ev_xfork, cudaEventDisableTiming));
+            RL_CUDA(cudaEventCreateWithFlags(&c->ev_xjoin, cudaEventDisableTiming));
+        }
+        c->gather = *g;
+    } else {
+        c->gather = rl_stack_gather{};
+    }
+    // a captured step holds the old setting: start over
+    if (c->gexec) {
+        cudaGraphExecDestroy(c->gexec);
+        c->gexec = nullptr;
+    }
+    if (c->hexec) {
+        cudaGraphExecDestroy(c->hexec);
+        c->hexec = nullptr;
+    }
+    c->gkey_seen = c->hkey_seen = 0;
+    return RL_OK;
 }
 
 int rl_stack_set_graph(rl_cache* c, int enable) {

@@ -15,11 +15,7 @@ namespace {
 // wht_len = 128 or 256), same stage order as the store kernel; then the +-1 signs.
 __device__ __forceinline__ float block_wht(float v, int wht_len, const float* signs, float* xs) {
     const int tid = threadIdx.x, lane = tid & 31;
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {
-        const float o = __shfl_xor_sync(0xffffffffu, v, s);
-        v = ((lane & s) == 0) ? (v + o) : (o - v);
-    }
+    v = wht32_in_warp(v, lane);
     xs[tid] = v;
     __syncthreads();
     for (int s = 32; s < wht_len; s <<= 1) {

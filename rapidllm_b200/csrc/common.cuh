@@ -142,6 +142,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// The five in-warp stages (distances 1, 2, 4, 8, 16) of an unnormalised Walsh-Hadamard transform
+// over values held one per lane: at distance d the lane whose bit d is clear keeps the sum of the
+// pair, its partner keeps (lower - upper).
+__device__ __forceinline__ float wht32_in_warp(float x, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const float partner = __shfl_xor_sync(0xffffffffu, x, d);
+        const bool upper = (lane & d) != 0;
+        x = upper ? (partner - x) : (x + partner);
+    }
+    return x;
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -581,5 +581,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
 
 size_t delta_chunk_scan_smem_bytes() { return sizeof(ScanSmem) + 1024; }
 int delta_chunk_scan_threads() { return kScanThreads; }
+// per (chunk, head), M = 128, K = 16 each: D^T 4 + 16 and O^T 16 + 8 MMAs of N = 64, S^T 8 MMAs of N = 128
+double delta_chunk_scan_mma_flops() { return 2.0 * 128 * 16 * ((4 + 16 + 16 + 8) * 64 + 8 * 128); }
 
 }  // namespace rl

@@ -193,6 +193,7 @@ size_t delta_chunk_prepare_smem_bytes();
 int delta_chunk_prepare_threads();
 size_t delta_chunk_scan_smem_bytes();
 int delta_chunk_scan_threads();
+double delta_chunk_scan_mma_flops();     // flops of the MMAs the scan issues per (chunk, head)
 
 // ---- causal depthwise conv1d + SiLU ------------------------------------------------
 struct ConvUpdateArgs {

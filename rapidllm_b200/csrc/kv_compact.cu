@@ -29,23 +29,24 @@ namespace rl {
 
 namespace {
 
-__device__ __forceinline__ float tq3_cent(int i) {
-    const float c[8] = {-2.152f, -1.344f, -0.756f, -0.245f, 0.245f, 0.756f, 1.344f, 2.152f};
-    return c[i & 7];
-}
+// The 8 reconstruction levels of the 3-bit Lloyd-Max quantiser for a unit normal variable
+// (the values the reference's dequantiser maps codes to, cuda_engine.cu:204-208).
+__constant__ float kTq3Levels[8] = {-2.152f, -1.344f, -0.756f, -0.245f, 0.245f, 0.756f, 1.344f, 2.152f};
 
-__device__ __forceinline__ int tq3_nn(float v) {
-    int bi = 0;
-    float bd = fabsf(v - tq3_cent(0));
+// Code of the level nearest to x.  The scan visits the levels in ascending order and only a
+// strictly smaller distance replaces the current choice, so an exact tie keeps the lower code:
+// the rule the bit-exact contract with the CPU restatement fixes.
+__device__ __forceinline__ int tq3_code(float x) {
+    int code = 0;
+    float nearest = fabsf(x - kTq3Levels[0]);
 #pragma unroll
-    for (int i = 1; i < 8; ++i) {
-        const float d = fabsf(v - tq3_cent(i));
-        if (d < bd) {
-            bd = d;
-            bi = i;
-        }
+    for (int level = 1; level < 8; ++level) {
+        const float dist = fabsf(x - kTq3Levels[level]);
+        const bool closer = dist < nearest;
+        nearest = closer ? dist : nearest;
+        code = closer ? level : code;
     }
-    return bi;
+    return code;
 }
 
 }  // namespace
@@ -101,11 +102,7 @@ __global__ void __launch_bounds__(256) kv_compact_write_kernel(KvCompactWriteArg
     // ---------------- V: signs, Walsh-Hadamard, RMS scale, 3-bit codes ----------------
     float v = a.v_rows[src + tid];
     if (a.wht_len == 256 && a.signs) v = v * a.signs[tid];
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {
-        const float o = __shfl_xor_sync(0xffffffffu, v, s);
-        v = ((lane & s) == 0) ? (v + o) : (o - v);
-    }
+    v = wht32_in_warp(v, lane);
     xs[tid] = v;
     __syncthreads();
     for (int s = 32; s < a.wht_len; s <<= 1) {
@@ -133,7 +130,7 @@ __global__ void __launch_bounds__(256) kv_compact_write_kernel(KvCompactWriteArg
         else vs[0] = vs[1] = hs;
     }
     __syncthreads();
-    s_idx[tid] = static_cast<unsigned char>(tq3_nn(v / s_scale[tid / a.wht_len]));
+    s_idx[tid] = static_cast<unsigned char>(tq3_code(v / s_scale[tid / a.wht_len]));
     __syncthreads();
     // pack: thread (g, j) owns dims 64j + 8g .. +7 = 4 fields = 48 bits of this token's parity
     if (tid < 32) {
@@ -242,12 +239,8 @@ kv_compact_to_f16_kernel(const unsigned char* pool, const int32_t* src_table, in
     for (int x = 0; x < 6; ++x) w48 |= (unsigned long long)p[x] << (8 * x);
     const int idx = int((w48 >> (12 * i + 6 * odd_dim + 3 * e)) & 7ull);
     const float sc = __half2float(reinterpret_cast<const __half*>(rec + kCompactVScaleOff)[row * 2 + d / wht_len]);
-    float v = tq3_cent(idx) * sc;
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {
-        const float o = __shfl_xor_sync(0xffffffffu, v, s);
-        v = ((lane & s) == 0) ? (v + o) : (o - v);
-    }
+    float v = kTq3Levels[idx] * sc;
+    v = wht32_in_warp(v, lane);
     xs[tid] = v;
     __syncthreads();
     for (int s = 32; s < wht_len; s <<= 1) {

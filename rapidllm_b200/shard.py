@@ -81,3 +81,129 @@ def token_range_of_part(n_tokens: int, world: int, rank: int, page_tokens: int =
     first = p0 * page_tokens
     last = n_tokens if rank == world - 1 else p1 * page_tokens
     return first, max(0, last - first)
+
+
+@dataclass(frozen=True)
+class StepPlan:
+    """One rank's share of a decode step whose batch is divided over `world` ranks, and how the
+    all-gathered outputs (rl_stack_gather: block r = rank r's local output) map back to the whole.
+
+    mode "heads":   KV / value heads over head_ways = min(world, n_kv) ranks, then the sequences
+                    over world / head_ways; rank = seq_part * head_ways + head_part.
+    mode "splitkv": every rank holds a token range of every sequence and all attention heads
+                    (partials merged by the library into attn_o_final); DeltaNet value heads / world.
+    mode "seq":     whole sequences per rank, nothing gathered (weak scaling).
+    """
+    mode: str
+    rank: int
+    world: int
+    batch: int
+    n_q: int = 24
+    n_kv: int = 4
+    n_v: int = 48
+    n_k: int = 16
+
+    def __post_init__(self):
+        if self.mode not in ("heads", "splitkv", "seq"):
+            raise ValueError("unknown mode %r" % self.mode)
+        if not 0 <= self.rank < self.world:
+            raise ValueError("rank %d outside world %d" % (self.rank, self.world))
+        if self.mode == "heads":
+            if self.n_kv % self.head_ways or self.world % self.head_ways or self.batch % self.seq_ways:
+                raise ValueError("heads x%d / sequences x%d do not divide %d KV heads, batch %d"
+                                 % (self.head_ways, self.seq_ways, self.n_kv, self.batch))
+        if self.mode != "seq" and (self.n_k % self.delta_ways or self.n_v % self.delta_ways):
+            raise ValueError("%d ranks do not divide the DeltaNet heads" % self.delta_ways)
+
+    # ---- how many ways each axis is cut ----
+    @property
+    def head_ways(self):
+        return min(self.world, self.n_kv) if self.mode == "heads" else 1
+
+    @property
+    def seq_ways(self):
+        return self.world // self.head_ways if self.mode == "heads" else 1
+
+    @property
+    def delta_ways(self):
+        return {"heads": self.head_ways, "splitkv": self.world, "seq": 1}[self.mode]
+
+    @property
+    def head_part(self):
+        return self.rank % self.head_ways
+
+    @property
+    def delta_part(self):
+        return self.rank if self.mode == "splitkv" else self.head_part
+
+    @property
+    def seq_part(self):
+        return self.rank // self.head_ways if self.mode == "heads" else 0
+
+    # ---- this rank's slices of the whole problem ----
+    @property
+    def seqs(self):
+        return plan_sequences(self.seq_part, self.seq_ways, self.batch)
+
+    @property
+    def kv_heads(self):
+        per = self.n_kv // self.head_ways
+        return range(self.head_part * per, (self.head_part + 1) * per)
+
+    @property
+    def q_heads(self):
+        g = self.n_q // self.n_kv
+        return range(self.kv_heads.start * g, self.kv_heads.stop * g)
+
+    @property
+    def v_heads(self):
+        per = self.n_v // self.delta_ways
+        return range(self.delta_part * per, (self.delta_part + 1) * per)
+
+    @property
+    def k_heads(self):
+        per = self.n_k // self.delta_ways
+        return range(self.delta_part * per, (self.delta_part + 1) * per)
+
+    def conv_channels(self, dk=128, dv=128):
+        """Indices, in the full q | k | v channel vector, of this rank's conv channels (in the order
+        of the local q | k | v layout)."""
+        kq = self.n_k * dk
+        out = list(range(self.k_heads.start * dk, self.k_heads.stop * dk))
+        out += [kq + c for c in range(self.k_heads.start * dk, self.k_heads.stop * dk)]
+        out += [2 * kq + c for c in range(self.v_heads.start * dv, self.v_heads.stop * dv)]
+        return out
+
+    def token_range(self, n_tokens, page_tokens=64):
+        """(first, count) of the tokens of a sequence of n_tokens this rank holds."""
+        if self.mode == "splitkv":
+            return token_range_of_part(n_tokens, self.world, self.rank, page_tokens)
+        return 0, n_tokens
+
+    def slice_io(self, full):
+        """The local tensors of a step from the whole problem's (rl_stack_io names; torch tensors or
+        numpy arrays with the layouts of the header)."""
+        s, qh, kvh, vh = list(self.seqs), list(self.q_heads), list(self.kv_heads), list(self.v_heads)
+        ch = self.conv_channels()
+        cut = {
+            "attn_q": lambda x: x[:, s][:, :, qh], "attn_gate": lambda x: x[:, s][:, :, qh],
+            "attn_k": lambda x: x[:, s][:, :, kvh], "attn_v": lambda x: x[:, s][:, :, kvh],
+            "delta_qkv": lambda x: x[:, s][:, :, ch], "delta_beta": lambda x: x[:, s][:, :, vh],
+            "delta_g": lambda x: x[:, s][:, :, vh], "conv_w": lambda x: x[:, ch],
+        }
+        return {n: cut[n](x) for n, x in full.items() if n in cut}
+
+    # ---- gathered blocks -> the whole ----
+    def place_attn(self, out, gathered):
+        """gathered [world][B_local][n_q_local][256] (one layer of attn_o_all) -> out [batch][n_q][256]."""
+        for r in range(self.world):
+            p = StepPlan(self.mode, r, self.world, self.batch, self.n_q, self.n_kv, self.n_v, self.n_k)
+            out[p.seqs.start:p.seqs.stop, p.q_heads.start:p.q_heads.stop] = gathered[r]
+        return out
+
+    def place_delta(self, out, gathered):
+        """gathered [world][B_local][n_v_local][dv] (one layer of delta_o_all) -> out [batch][n_v][dv]."""
+        for r in range(self.world):
+            p = StepPlan(self.mode, r, self.world, self.batch, self.n_q, self.n_kv, self.n_v, self.n_k)
+            out[p.seqs.start:p.seqs.stop, p.v_heads.start:p.v_heads.stop] = gathered[r]
+        return out

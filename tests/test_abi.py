@@ -23,7 +23,7 @@ def test_header_symbols_are_exported_and_bound():
     for n in names:
         assert hasattr(L, n), f"{n} declared in rl_b200.h but not exported"
     assert set(names) == set(_lib.SYMBOLS), set(names) ^ set(_lib.SYMBOLS)
-    assert _lib.lib().rl_b200_abi_version() == 1
+    assert _lib.lib().rl_b200_abi_version() == 2
 
 
 def test_argument_errors_follow_reference_status_codes():

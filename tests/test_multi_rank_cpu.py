@@ -103,3 +103,64 @@ def test_two_ranks_gloo():
         assert ok_heads
         assert err < 1e-5
         assert flag == 1
+
+
+def _plan_worker(rank, world, port, mode, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from rapidllm_b200.shard import StepPlan
+    B, n_q, n_kv, n_v, n_k = 4, 12, 2, 12, 4
+    rng = np.random.default_rng(1)                      # the whole problem, the same on every rank
+    conv_dim = 2 * n_k * 128 + n_v * 128
+    full = {"attn_q": torch.from_numpy(rng.standard_normal((2, B, n_q, 8), dtype=np.float32)),
+            "attn_k": torch.from_numpy(rng.standard_normal((2, B, n_kv, 8), dtype=np.float32)),
+            "delta_qkv": torch.from_numpy(rng.standard_normal((3, B, conv_dim), dtype=np.float32)),
+            "delta_beta": torch.from_numpy(rng.standard_normal((3, B, n_v), dtype=np.float32)),
+            "conv_w": torch.from_numpy(rng.standard_normal((3, conv_dim, 4), dtype=np.float32))}
+    plan = StepPlan(mode, rank, world, B, n_q, n_kv, n_v, n_k)
+    mine = {n: x.contiguous() for n, x in plan.slice_io(full).items()}
+    # a stand-in for the kernels: attention output = 2 q, DeltaNet output = the v channels times beta
+    attn_o = 2.0 * mine["attn_q"][0]
+    nv_l = len(plan.v_heads)
+    delta_o = mine["delta_qkv"][0][:, -nv_l * 128:].reshape(len(plan.seqs), nv_l, 128) * mine["delta_beta"][0][..., None]
+    ga = [torch.empty_like(attn_o) for _ in range(world)]
+    gd = [torch.empty_like(delta_o) for _ in range(world)]
+    dist.all_gather(ga, attn_o.contiguous())            # block r = rank r's local output, as rl_stack_gather lays it out
+    dist.all_gather(gd, delta_o.contiguous())
+    ok = True
+    if mode == "heads":
+        whole = plan.place_attn(torch.zeros(B, n_q, 8), torch.stack(ga))
+        ok = ok and torch.equal(whole, 2.0 * full["attn_q"][0])
+    whole_d = plan.place_delta(torch.zeros(B, n_v, 128), torch.stack(gd))
+    want = full["delta_qkv"][0][:, 2 * n_k * 128:].reshape(B, n_v, 128) * full["delta_beta"][0][..., None]
+    ok = ok and torch.equal(whole_d, want)
+    # the conv weights follow the channels
+    ok = ok and torch.equal(mine["conv_w"][0], full["conv_w"][0][plan.conv_channels()])
+    ret[rank] = bool(ok)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode,world", [("heads", 2), ("heads", 4), ("splitkv", 2)])
+def test_step_plan_slices_and_gathered_blocks_round_trip(mode, world):
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 31500 + os.getpid() % 2000 + world
+    mp.spawn(_plan_worker, args=(world, port, mode, ret), nprocs=world, join=True)
+    assert all(ret[r] for r in range(world))
+
+
+def test_step_plan_rejects_what_does_not_divide():
+    from rapidllm_b200.shard import StepPlan
+    with pytest.raises(ValueError):
+        StepPlan("heads", 0, 3, 32)
+    with pytest.raises(ValueError):
+        StepPlan("heads", 0, 8, 31)                    # sequences x2 need an even batch
+    with pytest.raises(ValueError):
+        StepPlan("splitkv", 0, 5, 32)
+    p = StepPlan("heads", 5, 8, 32)
+    assert (p.head_ways, p.seq_ways, p.head_part, p.seq_part) == (4, 2, 1, 1)
+    assert list(p.kv_heads) == [1] and list(p.q_heads) == list(range(6, 12)) and list(p.seqs) == list(range(16, 32))
+    assert list(p.v_heads) == list(range(12, 24)) and list(p.k_heads) == [4, 5, 6, 7]
+    s = StepPlan("splitkv", 7, 8, 32)
+    assert list(s.q_heads) == list(range(24)) and list(s.v_heads) == list(range(42, 48)) and s.token_range(1000) == (896, 104)
