@@ -324,6 +324,41 @@ int rl_conv1d_update(const float* x, const float* w, float* state, const int32_t
 int rl_conv1d_causal(const float* x, const float* w, float* y, float* state_io, int seq,
                      const rl_conv1d_params* p, int use_state_in, void* stream);
 
+/* The whole Gated DeltaNet decode step of one layer in one kernel, as the reference's CUDA engine
+ * runs it (gdn_decode_t1_k, src/kernels/cuda/cuda_engine.cu:5166-5286): ops::conv1d_update on the
+ * q | k | v channels (src/kernels/ops.cpp:458-468), l2 norms, then ops::delta_recurrent_step
+ * (495-540), with the CPU operators' arithmetic (double conv accumulator, FP32 state).
+ *   qkv       fp32 [batch][conv_dim] channels before the conv, conv_dim = 2 * n_qk * 128 + n_v * 128
+ *   conv_w    fp32 [conv_dim][4] taps, oldest first
+ *   conv_ring fp32 [n_slots][conv_dim][4] windows kept as RINGS: nothing is shifted, tap slot
+ *             (t & 3) holds input x_t, so that the value heads sharing a key head can all read its
+ *             channels while one of them stores the new tap.  conv_phase int32 [n_slots] holds
+ *             t & 3 of each slot's next token; this call only reads it.  After the layer's step
+ *             call rl_gdn_phase_advance once.  rl_conv_ring_export / _import convert to and from
+ *             the reference's shifted [conv_dim][4] window (oldest tap first).
+ * The other arguments are those of rl_delta_recurrent; conv k must be 4. */
+typedef struct rl_gdn_decode_params {
+    int n_v, n_qk, dk, dv;       /* 48, 16, 128, 128 */
+    int conv_k;                  /* 4 */
+    int batch, n_slots;
+    int head_map;                /* RL_HEADS_* */
+    float eps_l2;                /* 1e-6 */
+} rl_gdn_decode_params;
+int rl_gdn_decode(float* S, float* conv_ring, const int32_t* conv_phase, const int32_t* slot_ids,
+                  const float* qkv, const float* conv_w, const float* beta, const float* g_log, float* o,
+                  const rl_gdn_decode_params* p, void* stream);
+/* conv_phase[l][slot_ids[b]] = (phase + n_tok) & 3 for l < n_layers, b < batch; conv_phase int32
+ * [n_layers][n_slots]. */
+int rl_gdn_phase_advance(int32_t* conv_phase, const int32_t* slot_ids, int n_layers, int n_slots, int batch,
+                         int n_tok, void* stream);
+/* Rings [n_layers][n_slots][conv_dim][4] <-> the reference's windows (ops::conv1d_update's state,
+ * DualCache::conv_ptr, src/runtime/dual_cache.cpp:67-70) of slot `slot`, or of every slot when
+ * slot < 0: canon fp32 [n_layers][n_slots or 1][conv_dim][4].  Import resets the phases it covers. */
+int rl_conv_ring_export(const float* conv_ring, const int32_t* conv_phase, float* canon, int n_layers,
+                        int n_slots, int slot, int conv_dim, void* stream);
+int rl_conv_ring_import(float* conv_ring, int32_t* conv_phase, const float* canon, int n_layers, int n_slots,
+                        int slot, int conv_dim, void* stream);
+
 /* ---- element-wise steps around the mixers (the "next" ring of the path) ---- */
 
 typedef struct rl_attn_qk_prepare_params {
@@ -379,7 +414,7 @@ typedef struct rl_cache_config {
     int kv_dtype;                /* RL_KV_F16 */
     int page_tokens, n_pages;    /* 64, pool size shared by all attention layers */
     int n_v, n_k, dk, dv;        /* DeltaNet: 48, 16, 128, 128 */
-    int conv_k;                  /* 4; conv_dim = 2*n_k*dk + n_v*dv */
+    int conv_k;                  /* must be 4; conv_dim = 2*n_k*dk + n_v*dv */
     int head_map;                /* RL_HEADS_GROUPED (HF) or RL_HEADS_TILED (GGUF) */
     int n_slots;                 /* sequences that can hold DeltaNet state */
     int max_batch, max_pages_per_seq, max_seq_len;
@@ -468,7 +503,13 @@ size_t rl_cache_bytes(const rl_cache* c);
 void* rl_cache_k_pool(rl_cache* c, int attn_index);
 void* rl_cache_v_pool(rl_cache* c, int attn_index);
 float* rl_cache_state(rl_cache* c, int delta_index);
+/* The conv windows of a layer as stored: rings [n_slots][conv_dim][4] (see rl_gdn_decode); equal to
+ * the reference's shifted windows only while no token has been consumed since creation, rl_cache_zero
+ * or rl_cache_conv_import.  rl_cache_conv_export / _import convert: canon fp32
+ * [n_slots][conv_dim][conv_k], oldest tap first (DualCache::conv_ptr). */
 float* rl_cache_conv(rl_cache* c, int delta_index);
+int rl_cache_conv_export(rl_cache* c, int delta_index, float* canon, void* stream);
+int rl_cache_conv_import(rl_cache* c, int delta_index, const float* canon, void* stream);
 /* DualCache::zero (dual_cache.cpp:43-47). */
 int rl_cache_zero(rl_cache* c, void* stream);
 
@@ -505,7 +546,7 @@ typedef struct rl_stack_io {
  * (cuda_engine.cu:18999-19106) restricted to the mixer operators.  Per
  * full-attention layer: append K,V at pos, attend over pos+1 tokens, gate.
  * Per linear-attention layer: conv1d_update on the q|k|v channels, then the
- * delta rule.  All pointers in io are device pointers. */
+ * delta rule, in one kernel (rl_gdn_decode).  All pointers in io are device pointers. */
 int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream);
 /* Graph replay of rl_stack_decode, the counterpart of the reference's captured decode step
  * (cuda_engine.cu:18787-18789 keeps positions on the device for that purpose).  Enabled by

@@ -57,6 +57,11 @@ class DeltaChunkParams(C.Structure):
                 ("qk_tok_stride", C.c_longlong), ("v_tok_stride", C.c_longlong)]
 
 
+class GdnDecodeParams(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_v", "n_qk", "dk", "dv", "conv_k", "batch", "n_slots", "head_map")] + [
+        ("eps_l2", C.c_float)]
+
+
 class Conv1dParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dim", "k", "silu", "batch", "n_slots")]
 
@@ -141,6 +146,12 @@ SYMBOLS = {
     "rl_delta_chunk_workspace_bytes": (_sz, [C.POINTER(DeltaChunkParams)]),
     "rl_delta_chunk_mma_flops": (C.c_double, []),
     "rl_delta_chunk_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(DeltaChunkParams), _vp]),
+    "rl_gdn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(GdnDecodeParams), _vp]),
+    "rl_gdn_phase_advance": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
+    "rl_conv_ring_export": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "rl_conv_ring_import": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "rl_cache_conv_export": (_i, [_vp, _i, _vp, _vp]),
+    "rl_cache_conv_import": (_i, [_vp, _i, _vp, _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),
     "rl_conv1d_causal": (_i, [_vp, _vp, _vp, _vp, _i, C.POINTER(Conv1dParams), _i, _vp]),
     "rl_plan_cache": (_i, [C.POINTER(PlanInput), C.POINTER(PlanResult)]),

@@ -75,6 +75,21 @@ class HybridCache:
     def conv(self, i):
         return _view(lib().rl_cache_conv(self._h, i), (self.n_slots, self.conv_dim, self.conv_k), torch.float32)
 
+    def conv_windows(self, i):
+        """The conv windows of DeltaNet layer i in the reference's form [n_slots][conv_dim][4], oldest
+        tap first (a copy: the cache keeps them as rings, see rl_gdn_decode)."""
+        out = torch.empty(self.n_slots, self.conv_dim, self.conv_k, dtype=torch.float32, device="cuda")
+        check(lib().rl_cache_conv_export(self._h, i, C.c_void_p(out.data_ptr()),
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
+    def set_conv_windows(self, i, windows):
+        """Load layer i's windows from the reference's form [n_slots][conv_dim][4]."""
+        w = windows.to(device="cuda", dtype=torch.float32).contiguous()
+        assert tuple(w.shape) == (self.n_slots, self.conv_dim, self.conv_k)
+        check(lib().rl_cache_conv_import(self._h, i, C.c_void_p(w.data_ptr()),
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
     def zero(self):
         check(lib().rl_cache_zero(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
 

@@ -87,6 +87,8 @@ int dev_info(DevInfo** out) {
                                      int(rl::attn_decode_f16_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_decode_stream_kernel_ptr(), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::delta_decode_stream_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::gdn_decode_stream_kernel_ptr(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::gdn_decode_stream_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::delta_chunk_prepare_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -280,8 +282,8 @@ struct rl_cache {
     size_t pool_elems = 0;          // halves per (layer, K or V) pool
     __half* kv = nullptr;           // [n_attn][2][pool_elems]
     float* S = nullptr;             // [n_delta][n_slots][n_v][dk][dv]
-    float* conv = nullptr;          // [n_delta][n_slots][conv_dim][conv_k]
-    float* mixed = nullptr;         // [max_batch][conv_dim] conv output of the layer in flight
+    float* conv = nullptr;          // [n_delta][n_slots][conv_dim][conv_k] ring windows (gdn_decode.cu)
+    int32_t* conv_phase = nullptr;  // [n_delta][n_slots] ring position of each slot's next token
     void* attn_ws = nullptr;
     size_t attn_ws_bytes = 0;
     size_t bytes = 0;
@@ -436,33 +438,22 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             mark(L, 2);
             ++ai;
         } else {
-            rl_conv1d_params cp;
-            cp.dim = c->conv_dim;
-            cp.k = f.conv_k;
-            cp.silu = 1;
-            cp.batch = B;
-            cp.n_slots = f.n_slots;
-            if (int st = rl_conv1d_update(io->delta_qkv + di * qkv_sz,
-                                          io->conv_w + size_t(di) * c->conv_dim * f.conv_k,
-                                          c->conv + di * cv_elems, io->slot_ids, c->mixed, &cp, run))
-                return st;
+            // conv window + SiLU + l2 norms + delta rule in one kernel
             mark(L, 1);
-            rl_delta_recurrent_params rp;
-            rp.n_v = f.n_v;
-            rp.dk = f.dk;
-            rp.dv = f.dv;
-            rp.eps_l2 = 1e-6f;
-            rp.batch = B;
-            rp.n_slots = f.n_slots;
-            rp.n_qk = f.n_k;
-            rp.head_map = f.head_map;
-            rp.q_stride = rp.k_stride = rp.v_stride = c->conv_dim;
-            const float* mq = c->mixed;
-            const float* mk = c->mixed + size_t(f.n_k) * f.dk;
-            const float* mv = c->mixed + 2 * size_t(f.n_k) * f.dk;
-            if (int st = rl_delta_recurrent(c->S + di * st_elems, io->slot_ids, mq, mk, mv,
-                                            io->delta_beta + di * hv_sz, io->delta_g + di * hv_sz,
-                                            io->delta_o + di * do_sz, &rp, run))
+            rl_gdn_decode_params gp;
+            gp.n_v = f.n_v;
+            gp.n_qk = f.n_k;
+            gp.dk = f.dk;
+            gp.dv = f.dv;
+            gp.conv_k = f.conv_k;
+            gp.batch = B;
+            gp.n_slots = f.n_slots;
+            gp.head_map = f.head_map;
+            gp.eps_l2 = 1e-6f;
+            if (int st = rl_gdn_decode(c->S + di * st_elems, c->conv + di * cv_elems, c->conv_phase + size_t(di) * f.n_slots,
+                                       io->slot_ids, io->delta_qkv + di * qkv_sz,
+                                       io->conv_w + size_t(di) * c->conv_dim * f.conv_k, io->delta_beta + di * hv_sz,
+                                       io->delta_g + di * hv_sz, io->delta_o + di * do_sz, &gp, run))
                 return st;
             mark(L, 2);
             ++di;
@@ -471,6 +462,9 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
         if (comm && ((L + 1) % per_x == 0 || L + 1 == f.n_layers))
             if (int st = exchange()) return st;
     }
+    // every layer's window has taken this step's token: move the rings on
+    if (c->n_delta)
+        if (int st = rl_gdn_phase_advance(c->conv_phase, io->slot_ids, c->n_delta, f.n_slots, B, 1, run)) return st;
     if (comm) {
         // the step is complete on `run` only when every rank's outputs have arrived
         RL_CUDA(cudaEventRecord(c->ev_xjoin, c->s_comm));
@@ -1088,6 +1082,84 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     return RL_OK;
 }
 
+int rl_gdn_decode(float* S, float* conv_ring, const int32_t* conv_phase, const int32_t* slot_ids, const float* qkv,
+                  const float* conv_w, const float* beta, const float* g_log, float* o, const rl_gdn_decode_params* p,
+                  void* stream) {
+    if (!p) return fail(RL_ERR_RANGE, "params is NULL");
+    if (p->dk != 128 || p->dv != 128 || p->conv_k != 4)
+        return fail(RL_ERR_UNSUPPORTED, "dk %d dv %d conv_k %d: only 128 x 128, 4 taps", p->dk, p->dv, p->conv_k);
+    if (p->n_v <= 0 || p->n_v > 65535 || p->batch < 0 || p->batch > 65535 || p->n_slots <= 0)
+        return fail(RL_ERR_RANGE, "n_v %d batch %d n_slots %d", p->n_v, p->batch, p->n_slots);
+    if (p->head_map == RL_HEADS_PER_VALUE ? p->n_qk != p->n_v
+                                          : (p->n_qk <= 0 || p->n_v % p->n_qk != 0 || p->head_map > RL_HEADS_TILED))
+        return fail(RL_ERR_RANGE, "n_qk %d does not fit n_v %d with head_map %d", p->n_qk, p->n_v, p->head_map);
+    if (p->batch == 0) return RL_OK;
+    if (!S || !conv_ring || !conv_phase || !qkv || !conv_w || !beta || !g_log || !o) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    if (reinterpret_cast<uintptr_t>(S) % 16 || reinterpret_cast<uintptr_t>(conv_ring) % 16 ||
+        reinterpret_cast<uintptr_t>(qkv) % 16 || reinterpret_cast<uintptr_t>(conv_w) % 16)
+        return fail(RL_ERR_RANGE, "S, conv_ring, qkv and conv_w must be 16-byte aligned");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::GdnDecodeArgs a;
+    a.S = S;
+    a.conv = conv_ring;
+    a.conv_phase = conv_phase;
+    a.slot_ids = slot_ids;
+    a.x = qkv;
+    a.w = conv_w;
+    a.beta = beta;
+    a.g_log = g_log;
+    a.o = o;
+    a.err = d->err_ptr;
+    a.batch = p->batch;
+    a.n_v = p->n_v;
+    a.n_qk = p->n_qk;
+    a.n_slots = p->n_slots;
+    a.head_map = p->head_map;
+    a.conv_dim = 2 * p->n_qk * p->dk + p->n_v * p->dv;
+    a.eps_l2 = p->eps_l2;
+    rl::launch_gdn_decode(a, d->sms, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_gdn_phase_advance(int32_t* conv_phase, const int32_t* slot_ids, int n_layers, int n_slots, int batch, int n_tok,
+                         void* stream) {
+    if (n_layers < 0 || n_slots <= 0 || batch < 0 || n_tok < 0) return fail(RL_ERR_RANGE, "n_layers %d n_slots %d batch %d n_tok %d", n_layers, n_slots, batch, n_tok);
+    if (n_layers == 0 || batch == 0) return RL_OK;
+    if (!conv_phase) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    DevInfo* d;
+    if (int st = dev_info(&d)) return st;
+    rl::launch_gdn_phase_advance(conv_phase, slot_ids, n_layers, n_slots, batch, n_tok, d->err_ptr, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+static int ring_args_check(const void* ring, const void* phase, const void* canon, int n_layers, int n_slots, int slot, int dim) {
+    if (n_layers < 0 || n_slots <= 0 || n_slots > 65535 || n_layers > 65535 || slot >= n_slots || dim <= 0)
+        return fail(RL_ERR_RANGE, "n_layers %d n_slots %d slot %d conv_dim %d", n_layers, n_slots, slot, dim);
+    if (n_layers && (!ring || !phase || !canon)) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    if (reinterpret_cast<uintptr_t>(ring) % 16 || reinterpret_cast<uintptr_t>(canon) % 16)
+        return fail(RL_ERR_RANGE, "windows must be 16-byte aligned");
+    return RL_OK;
+}
+
+int rl_conv_ring_export(const float* conv_ring, const int32_t* conv_phase, float* canon, int n_layers, int n_slots,
+                        int slot, int conv_dim, void* stream) {
+    if (int st = ring_args_check(conv_ring, conv_phase, canon, n_layers, n_slots, slot, conv_dim)) return st;
+    rl::launch_conv_ring_export(conv_ring, conv_phase, canon, n_layers, n_slots, slot, conv_dim, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
+int rl_conv_ring_import(float* conv_ring, int32_t* conv_phase, const float* canon, int n_layers, int n_slots, int slot,
+                        int conv_dim, void* stream) {
+    if (int st = ring_args_check(conv_ring, conv_phase, canon, n_layers, n_slots, slot, conv_dim)) return st;
+    rl::launch_conv_ring_import(conv_ring, conv_phase, canon, n_layers, n_slots, slot, conv_dim, as_stream(stream));
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
 int rl_conv1d_update(const float* x, const float* w, float* state, const int32_t* slot_ids, float* y,
                      const rl_conv1d_params* p, void* stream) {
     if (!p) return fail(RL_ERR_RANGE, "params is NULL");
@@ -1198,6 +1270,7 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
     if (cfg->head_dim != rl::kHeadDim || cfg->page_tokens != rl::kPageTokens || cfg->dk != 128 || cfg->dv != 128)
         return fail(RL_ERR_UNSUPPORTED, "shapes: head_dim 256, page_tokens 64, dk = dv = 128 only");
     if (cfg->kv_dtype != RL_KV_F16) return fail(RL_ERR_UNSUPPORTED, "rl_cache holds F16 KV only");
+    if (cfg->conv_k != 4) return fail(RL_ERR_UNSUPPORTED, "conv_k %d: the cache keeps 4-tap ring windows", cfg->conv_k);
     if (cfg->n_slots <= 0 || cfg->max_batch <= 0 || cfg->n_pages <= 0 || cfg->max_pages_per_seq <= 0 ||
         cfg->n_k <= 0 || cfg->n_v % cfg->n_k)
         return fail(RL_ERR_RANGE, "bad cache sizes");
@@ -1221,7 +1294,7 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
     if (!st) st = dev_alloc(&c->kv, size_t(c->n_attn) * 2 * c->pool_elems, &c->bytes);
     if (!st) st = dev_alloc(&c->S, size_t(c->n_delta) * cfg->n_slots * cfg->n_v * cfg->dk * cfg->dv, &c->bytes);
     if (!st) st = dev_alloc(&c->conv, size_t(c->n_delta) * cfg->n_slots * c->conv_dim * cfg->conv_k, &c->bytes);
-    if (!st) st = dev_alloc(&c->mixed, size_t(cfg->max_batch) * c->conv_dim, &c->bytes);
+    if (!st) st = dev_alloc(&c->conv_phase, size_t(c->n_delta) * cfg->n_slots, &c->bytes);
     if (!st) {
         char* ws = nullptr;
         st = dev_alloc(&ws, c->attn_ws_bytes, &c->bytes);
@@ -1239,7 +1312,7 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
 
 void rl_cache_destroy(rl_cache* c) {
     if (!c) return;
-    void* ptrs[] = {c->kv, c->S, c->conv, c->mixed, c->attn_ws, c->d_attn_q, c->d_attn_gate, c->d_attn_k,
+    void* ptrs[] = {c->kv, c->S, c->conv, c->conv_phase, c->attn_ws, c->d_attn_q, c->d_attn_gate, c->d_attn_k,
                     c->d_attn_v, c->d_attn_o, c->d_delta_qkv, c->d_delta_beta, c->d_delta_g, c->d_delta_o,
                     c->d_conv_w, c->d_page_table, c->d_pos, c->d_slot_ids};
     for (void* p : ptrs)
@@ -1277,12 +1350,25 @@ float* rl_cache_conv(rl_cache* c, int i) {
                ? c->conv + size_t(i) * c->cfg.n_slots * c->conv_dim * c->cfg.conv_k : nullptr;
 }
 
+int rl_cache_conv_export(rl_cache* c, int i, float* canon, void* stream) {
+    if (!c || i < 0 || i >= c->n_delta) return fail(RL_ERR_RANGE, "no such DeltaNet layer");
+    return rl_conv_ring_export(rl_cache_conv(c, i), c->conv_phase + size_t(i) * c->cfg.n_slots, canon, 1, c->cfg.n_slots, -1,
+                               c->conv_dim, stream);
+}
+
+int rl_cache_conv_import(rl_cache* c, int i, const float* canon, void* stream) {
+    if (!c || i < 0 || i >= c->n_delta) return fail(RL_ERR_RANGE, "no such DeltaNet layer");
+    return rl_conv_ring_import(rl_cache_conv(c, i), c->conv_phase + size_t(i) * c->cfg.n_slots, canon, 1, c->cfg.n_slots, -1,
+                               c->conv_dim, stream);
+}
+
 int rl_cache_zero(rl_cache* c, void* stream) {
     if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
     const rl_cache_config& f = c->cfg;
     if (c->kv) RL_CUDA(cudaMemsetAsync(c->kv, 0, size_t(c->n_attn) * 2 * c->pool_elems * sizeof(__half), as_stream(stream)));
     if (c->S) RL_CUDA(cudaMemsetAsync(c->S, 0, size_t(c->n_delta) * f.n_slots * f.n_v * f.dk * f.dv * sizeof(float), as_stream(stream)));
     if (c->conv) RL_CUDA(cudaMemsetAsync(c->conv, 0, size_t(c->n_delta) * f.n_slots * c->conv_dim * f.conv_k * sizeof(float), as_stream(stream)));
+    if (c->conv_phase) RL_CUDA(cudaMemsetAsync(c->conv_phase, 0, size_t(c->n_delta) * f.n_slots * sizeof(int32_t), as_stream(stream)));
     return RL_OK;
 }
 
@@ -1319,7 +1405,7 @@ int rl_stack_timing(rl_cache* c, float* ms) {
     return RL_OK;
 }
 
-int rl_stack_launches_per_step(const rl_cache* c) { return c ? c->n_attn * 3 + c->n_delta * 2 : 0; }
+int rl_stack_launches_per_step(const rl_cache* c) { return c ? c->n_attn * 3 + c->n_delta + (c->n_delta ? 1 : 0) : 0; }
 
 static bool same_io(const rl_stack_io& k, const rl_stack_io* io) {
     return k.attn_q == io->attn_q && k.attn_gate == io->attn_gate && k.attn_k == io->attn_k &&
@@ -1335,7 +1421,7 @@ namespace {
 struct StackPrefillPlan {
     rl_attn_prefill_params ap;
     rl_delta_chunk_params dp;
-    size_t mixed_bytes, delta_ws, attn_ws, total;
+    size_t mixed_bytes, delta_ws, attn_ws, canon_bytes, total;
 };
 
 int stack_prefill_plan(const rl_cache* c, int pos0, int T, StackPrefillPlan* pl) {
@@ -1366,7 +1452,9 @@ int stack_prefill_plan(const rl_cache* c, int pos0, int T, StackPrefillPlan* pl)
     pl->mixed_bytes = c->n_delta ? align_up(size_t(T) * c->conv_dim * sizeof(float), 256) : 0;
     pl->delta_ws = c->n_delta && T ? align_up(rl_delta_chunk_workspace_bytes(&pl->dp), 256) : 0;
     pl->attn_ws = c->n_attn && T ? align_up(rl_attn_prefill_workspace_bytes(&pl->ap), 256) : 0;
-    pl->total = pl->mixed_bytes + pl->delta_ws + pl->attn_ws;
+    // the slot's conv windows of every DeltaNet layer in the reference's shifted form, for the chunk
+    pl->canon_bytes = c->n_delta ? align_up(size_t(c->n_delta) * c->conv_dim * f.conv_k * sizeof(float), 256) : 0;
+    pl->total = pl->mixed_bytes + pl->delta_ws + pl->attn_ws + pl->canon_bytes;
     return RL_OK;
 }
 
@@ -1397,6 +1485,7 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
     float* mixed = reinterpret_cast<float*>(ws);
     void* delta_ws = ws + pl.mixed_bytes;
     void* attn_ws = ws + pl.mixed_bytes + pl.delta_ws;
+    float* canon = reinterpret_cast<float*>(ws + pl.mixed_bytes + pl.delta_ws + pl.attn_ws);
     const int T = io->T;
     const size_t q_sz = size_t(T) * f.n_q * f.head_dim, kv_sz = size_t(T) * f.n_kv * f.head_dim;
     const size_t qkv_sz = size_t(T) * c->conv_dim, hv_sz = size_t(T) * f.n_v, do_sz = size_t(T) * f.n_v * f.dv;
@@ -1406,6 +1495,9 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
     const uint16_t* ak = static_cast<const uint16_t*>(io->attn_k);
     const uint16_t* av = static_cast<const uint16_t*>(io->attn_v);
     int ai = 0, di = 0;
+    // a later chunk starts from the windows the previous chunk (or decode steps) left in the rings
+    if (c->n_delta && io->pos0 > 0)
+        rl::launch_conv_ring_export(c->conv, c->conv_phase, canon, c->n_delta, f.n_slots, io->slot, c->conv_dim, run);
     for (int L = 0; L < f.n_layers; ++L) {
         if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
             if (int st = attn_prefill_impl(rl_cache_k_pool(c, ai), rl_cache_v_pool(c, ai), io->page_table_row, aq + ai * q_sz,
@@ -1415,7 +1507,7 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
             ++ai;
         } else {
             float* S = c->S + di * st_elems + io->slot * slot_S;
-            float* cv = c->conv + di * cv_elems + io->slot * slot_cv;
+            float* cv = canon + size_t(di) * slot_cv;
             // a sequence that starts here starts from a zero state and an empty conv window
             if (io->pos0 == 0) RL_CUDA(cudaMemsetAsync(S, 0, slot_S * sizeof(float), run));
             rl_conv1d_params cp;
@@ -1433,6 +1525,10 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
                 return st;
             ++di;
         }
+    }
+    if (c->n_delta) {
+        rl::launch_conv_ring_import(c->conv, c->conv_phase, canon, c->n_delta, f.n_slots, io->slot, c->conv_dim, run);
+        RL_CUDA(cudaGetLastError());
     }
     return RL_OK;
 }

@@ -142,6 +142,38 @@ void launch_delta_decode_multi(const DeltaDecodeArgs& a, float* S_backup, int n_
 size_t delta_decode_stream_smem_bytes();
 const void* delta_decode_stream_kernel_ptr();
 
+// ---- fused Gated DeltaNet decode step: conv window + SiLU + l2 norms + delta rule (gdn_decode.cu) ----
+// The conv windows of the cache are kept as rings: tap slot (t & 3) of a channel holds input x_t,
+// nothing is shifted.  conv_phase [n_slots] = t & 3 of the NEXT token of each slot; a step reads the
+// three older taps, writes x into slot phase, and gdn_phase_advance_kernel bumps the phase once
+// after the layer's last reader is done.
+struct GdnDecodeArgs {
+    float* S;                    // [n_slots][n_v][128][128] fp32 recurrent state
+    float* conv;                 // [n_slots][conv_dim][4] ring windows
+    const int32_t* conv_phase;   // [n_slots]
+    const int32_t* slot_ids;     // [batch] or null (slot = b)
+    const float* x;              // [batch][conv_dim] q | k | v channels before the conv
+    const float* w;              // [conv_dim][4] taps, oldest first
+    const float* beta;           // [batch][n_v]
+    const float* g_log;          // [batch][n_v]
+    float* o;                    // [batch][n_v][128]
+    int* err;
+    int batch, n_v, n_qk, n_slots, head_map, conv_dim;
+    float eps_l2;
+};
+void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st);
+size_t gdn_decode_stream_smem_bytes();
+const void* gdn_decode_stream_kernel_ptr();
+// phase[l][slot_ids[b]] = (phase + n_tok) & 3 for l < n_layers, b < batch (phase [n_layers][n_slots])
+void launch_gdn_phase_advance(int32_t* phase, const int32_t* slot_ids, int n_layers, int n_slots, int batch, int n_tok,
+                              int* err, cudaStream_t st);
+// ring [n_layers][n_slots][dim][4] <-> oldest-first windows for slot `slot` (or every slot when slot < 0):
+// canon [n_layers][n_slots or 1][dim][4]; import also resets the phases it covers to 0
+void launch_conv_ring_export(const float* ring, const int32_t* phase, float* canon, int n_layers, int n_slots, int slot,
+                             int dim, cudaStream_t st);
+void launch_conv_ring_import(float* ring, int32_t* phase, const float* canon, int n_layers, int n_slots, int slot,
+                             int dim, cudaStream_t st);
+
 // ---- element-wise steps around the mixers (layer_glue.cu) ------------------------------------
 struct AttnQkPrepareArgs {
     const float* qg;             // [rows][n_q][2 * 256]  ([q | gate] per head)

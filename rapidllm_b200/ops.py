@@ -355,3 +355,35 @@ def kv_compact_to_f16(pool, src_table_row, k_pool, v_pool, dst_table_row, n_tok,
     check(lib().rl_kv_compact_to_f16(_p(pool), _p(src_table_row), src_pos0, pool.shape[0], _p(k_pool), _p(v_pool),
                                      _p(dst_table_row), dst_pos0, k_pool.shape[0], n_tok, pool.shape[1], wht_len,
                                      _p(signs), _stream()))
+
+
+def gdn_decode(S, conv_ring, conv_phase, qkv, conv_w, beta, g_log, n_qk, slot_ids=None, head_map=None,
+               eps_l2=1e-6, advance=True):
+    """The fused Gated DeltaNet decode step of one layer (rl_gdn_decode): conv window + SiLU + l2
+    norms + delta rule.  S [n_slots][n_v][128][128], conv_ring [n_slots][conv_dim][4] (ring windows),
+    conv_phase int32 [n_slots], qkv [batch][conv_dim], conv_w [conv_dim][4]; returns o.  With
+    advance the rings' phases move on afterwards (rl_gdn_phase_advance), as after a layer's step."""
+    for t, n in ((S, "S"), (conv_ring, "conv_ring"), (qkv, "qkv"), (conv_w, "conv_w"), (beta, "beta"), (g_log, "g_log")):
+        _need(t, torch.float32, n)
+    _need(conv_phase, torch.int32, "conv_phase")
+    _need(slot_ids, torch.int32, "slot_ids")
+    n_slots, n_v, dk, dv = S.shape
+    batch = qkv.shape[0]
+    if head_map is None:
+        head_map = _lib.RL_HEADS_PER_VALUE if n_qk == n_v else _lib.RL_HEADS_GROUPED
+    o = torch.empty(batch, n_v, dv, dtype=torch.float32, device=S.device)
+    p = _lib.GdnDecodeParams(n_v=n_v, n_qk=n_qk, dk=dk, dv=dv, conv_k=conv_w.shape[1], batch=batch, n_slots=n_slots,
+                             head_map=head_map, eps_l2=eps_l2)
+    check(lib().rl_gdn_decode(_p(S), _p(conv_ring), _p(conv_phase), _p(slot_ids), _p(qkv), _p(conv_w), _p(beta),
+                              _p(g_log), _p(o), C.byref(p), _stream()))
+    if advance:
+        check(lib().rl_gdn_phase_advance(_p(conv_phase), _p(slot_ids), 1, n_slots, batch, 1, _stream()))
+    return o
+
+
+def conv_ring_export(conv_ring, conv_phase):
+    """Ring windows [n_slots][conv_dim][4] -> the reference's shifted windows, oldest tap first."""
+    out = torch.empty_like(conv_ring)
+    check(lib().rl_conv_ring_export(_p(conv_ring), _p(conv_phase), _p(out), 1, conv_ring.shape[0], -1,
+                                    conv_ring.shape[1], _stream()))
+    return out

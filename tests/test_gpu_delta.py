@@ -229,3 +229,78 @@ def test_multi_token_step_equals_single_steps_and_rolls_back(oracle, n_tok):
                                      dev[2][:, t].contiguous(), dev[3][:, t].contiguous(),
                                      dev[4][:, t].contiguous(), slot_ids=slots.cuda())
         assert torch.equal(S_ref, S_multi)
+
+
+def _fused_oracle_step(oracle, S, C, x, w, beta, g, n_k, n_v, tiled):
+    mixed = oracle.conv1d_update(x, w, C)
+    q = oracle.repeat_heads(mixed[:n_k * DK].reshape(n_k, DK), n_v, tiled)
+    k = oracle.repeat_heads(mixed[n_k * DK:2 * n_k * DK].reshape(n_k, DK), n_v, tiled)
+    return oracle.delta_step(S, q, k, mixed[2 * n_k * DK:].reshape(n_v, DV), beta, g)
+
+
+@pytest.mark.parametrize("batch,head_map_name", [(3, "RL_HEADS_GROUPED"), (3, "RL_HEADS_TILED"), (14, "RL_HEADS_GROUPED"),
+                                                 (14, "RL_HEADS_TILED")])
+def test_fused_gdn_decode_matches_conv_then_delta(oracle, batch, head_map_name):
+    """rl_gdn_decode (conv window + SiLU + l2 norms + delta rule in one kernel, ring windows) over
+    six consecutive steps against ops::conv1d_update + ops::delta_recurrent_step: outputs, state,
+    and the windows bit for bit after every step.  Batch 3 runs the slice kernel, batch 14 (672
+    heads) the streaming kernel on a 148-SM part; slots are shuffled and one is left untouched."""
+    from rapidllm_b200 import _lib, ops
+    head_map = getattr(_lib, head_map_name)
+    tiled = head_map == _lib.RL_HEADS_TILED
+    gen = torch.Generator().manual_seed(70 + batch)
+    n_slots = batch + 1
+    S0 = torch.randn(n_slots, N_V, DK, DV, generator=gen) * 0.02
+    C0 = torch.randn(n_slots, CONV_DIM, CONV_K, generator=gen)
+    w = torch.randn(CONV_DIM, CONV_K, generator=gen) * 0.5
+    slots = torch.randperm(n_slots, generator=gen)[:batch].int()
+    S, ring = S0.cuda().clone(), C0.cuda().clone()          # phase 0: the ring equals the shifted window
+    phase = torch.zeros(n_slots, dtype=torch.int32, device="cuda")
+    Sr, Cr = S0.numpy().copy(), C0.numpy().copy()
+    wd, sd = w.cuda(), slots.cuda()
+    for step in range(6):
+        x = torch.randn(batch, CONV_DIM, generator=gen)
+        beta = torch.sigmoid(torch.randn(batch, N_V, generator=gen))
+        g = -softplus(torch.randn(batch, N_V, generator=gen))
+        o = ops.gdn_decode(S, ring, phase, x.cuda(), wd, beta.cuda(), g.cuda(), N_K, slot_ids=sd, head_map=head_map)
+        _lib.check_device()
+        o = o.cpu().numpy()
+        for b in range(batch):
+            sl = int(slots[b])
+            ref = _fused_oracle_step(oracle, Sr[sl], Cr[sl], x[b].numpy(), w.numpy(), beta[b].numpy(), g[b].numpy(),
+                                     N_K, N_V, tiled)
+            assert np.abs(o[b] - ref).max() <= 1e-5, (step, b, np.abs(o[b] - ref).max())
+        assert np.array_equal(ops.conv_ring_export(ring, phase).cpu().numpy(), Cr), step
+        assert rel_l2(S.cpu().numpy(), Sr) <= 1e-6
+    assert phase.cpu().tolist().count(0) == 1 and int(phase[slots[0]]) == 2      # 6 steps = phase 2; the idle slot stays 0
+    idle = [s for s in range(n_slots) if s not in slots.tolist()][0]
+    assert torch.equal(S[idle].cpu(), S0[idle])
+
+
+def test_config1_1024_steps_fused(oracle):
+    """The single-layer DeltaNet configuration (batch 1, 1024 consecutive steps from seed 1) through the
+    fused kernel: state rel-L2 <= 1e-5, outputs max-abs <= 1e-4, window equal bit for bit."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(1)
+    S0 = torch.randn(N_V, DK, DV, generator=gen) * 0.02
+    w = torch.randn(CONV_DIM, CONV_K, generator=gen) * 0.5
+    steps = 1024
+    xs = torch.randn(steps, CONV_DIM, generator=gen)
+    beta = torch.sigmoid(torch.randn(steps, N_V, generator=gen))
+    g = -softplus(torch.randn(steps, N_V, generator=gen))
+    S = S0.cuda().unsqueeze(0).clone()
+    ring = torch.zeros(1, CONV_DIM, CONV_K, device="cuda")
+    phase = torch.zeros(1, dtype=torch.int32, device="cuda")
+    wd, xd, bd, gd = w.cuda(), xs.cuda(), beta.cuda(), g.cuda()
+    outs = [ops.gdn_decode(S, ring, phase, xd[t:t + 1], wd, bd[t:t + 1], gd[t:t + 1], N_K) for t in range(steps)]
+    _lib.check_device()
+    o_gpu = torch.cat(outs).cpu().numpy()
+    Sr = S0.numpy().copy()
+    cr = np.zeros((CONV_DIM, CONV_K), np.float32)
+    o_ref = np.empty_like(o_gpu)
+    for t in range(steps):
+        o_ref[t] = _fused_oracle_step(oracle, Sr, cr, xs[t].numpy(), w.numpy(), beta[t].numpy(), g[t].numpy(), N_K, N_V, False)
+    s_err, o_err = rel_l2(S[0].cpu().numpy(), Sr), np.abs(o_gpu - o_ref).max()
+    print("cfg1 fused: state rel-l2 %.3e, o max-abs %.3e" % (s_err, o_err))
+    assert s_err <= STATE_REL_L2 and o_err <= 1e-4
+    assert np.array_equal(ops.conv_ring_export(ring, phase)[0].cpu().numpy(), cr)

@@ -82,7 +82,7 @@ def _worker(rank, world, port, mode, ret):
                               prob["v_hist"][a][b][first:first + n_h][:, kvh].contiguous().cuda(), pos0=0)
     for d in range(cache.n_delta):
         cache.state(d).copy_(prob["S0"][d][:, vh])
-        cache.conv(d).copy_(prob["C0"][d][:, plan.conv_channels()])
+        cache.set_conv_windows(d, prob["C0"][d][:, plan.conv_channels()])
     dev = {n: x.contiguous().cuda() for n, x in plan.slice_io(prob).items()}
     sh = cache.io_shapes(B)
     dev["attn_o"] = torch.zeros(sh["attn_o"], device="cuda")

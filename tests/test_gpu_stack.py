@@ -32,7 +32,7 @@ def test_stack_decode_matches_oracle_layer_by_layer(oracle):
     n_pages = 16
     cache = HybridCache(types, n_pages=n_pages, n_slots=n_slots, max_batch=4,
                         max_pages_per_seq=max_pages)
-    assert cache.n_attn == 2 and cache.n_delta == 6 and cache.launches_per_step == 2 * 3 + 6 * 2
+    assert cache.n_attn == 2 and cache.n_delta == 6 and cache.launches_per_step == 2 * 3 + 6 + 1
     # page table: disjoint shuffled pages
     perm = torch.randperm(n_pages, generator=gen).int()
     table = torch.zeros(B, max_pages, dtype=torch.int32)
@@ -53,7 +53,7 @@ def test_stack_decode_matches_oracle_layer_by_layer(oracle):
     C0 = [torch.randn(n_slots, cache.conv_dim, 4, generator=gen) for _ in range(6)]
     for d in range(6):
         cache.state(d).copy_(S0[d])
-        cache.conv(d).copy_(C0[d])
+        cache.set_conv_windows(d, C0[d])
     t = _inputs(cache, B, gen, lens)
     t["page_table"], t["slot_ids"] = table, slots
     dev = {n: x.cuda() for n, x in t.items()}
@@ -82,12 +82,12 @@ def test_stack_decode_matches_oracle_layer_by_layer(oracle):
                                     t["delta_beta"][d, b].numpy(), t["delta_g"][d, b].numpy())
             assert np.abs(delta_o[d, b] - ref).max() < 1e-4
         assert rel_l2(cache.state(d).cpu().numpy(), Sr) < 1e-6
-        assert np.array_equal(cache.conv(d).cpu().numpy(), Cr)
+        assert np.array_equal(cache.conv_windows(d).cpu().numpy(), Cr)
 
     # the host-buffer entry point gives the same bits
     for d in range(6):
         cache.state(d).copy_(S0[d])
-        cache.conv(d).copy_(C0[d])
+        cache.set_conv_windows(d, C0[d])
     host = {n: (x.pin_memory() if n != "conv_w" else x) for n, x in t.items()}
     host["attn_o"].zero_()
     host["delta_o"].zero_()
@@ -117,7 +117,7 @@ def test_graph_replay_matches_plain_launches():
             cache.v_pool(a).copy_(torch.randn(cache.v_pool(a).shape, generator=gen).half())
         for d in range(cache.n_delta):
             cache.state(d).copy_(torch.randn(cache.state(d).shape, generator=gen) * 0.02)
-            cache.conv(d).copy_(torch.randn(cache.conv(d).shape, generator=gen))
+            cache.set_conv_windows(d, torch.randn(cache.conv(d).shape, generator=gen))
         t = _inputs(cache, B, gen, lens)
         t["page_table"] = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
         dev = {n: x.cuda() for n, x in t.items()}
@@ -132,7 +132,7 @@ def test_graph_replay_matches_plain_launches():
             _lib.check_device()
             steps.append((dev["attn_o"].cpu().clone(), dev["delta_o"].cpu().clone()))
         final = [cache.state(d).cpu().clone() for d in range(cache.n_delta)]
-        final += [cache.conv(d).cpu().clone() for d in range(cache.n_delta)]
+        final += [cache.conv_windows(d).cpu().clone() for d in range(cache.n_delta)]
         final += [cache.k_pool(a).cpu().clone() for a in range(cache.n_attn)]
         outs.append((steps, final))
         cache.close()
@@ -212,7 +212,7 @@ def test_host_entry_graph_replay_matches_plain_launches():
             cache.v_pool(a).copy_(torch.randn(cache.v_pool(a).shape, generator=gen).half())
         for d in range(cache.n_delta):
             cache.state(d).copy_(torch.randn(cache.state(d).shape, generator=gen) * 0.02)
-            cache.conv(d).copy_(torch.randn(cache.conv(d).shape, generator=gen))
+            cache.set_conv_windows(d, torch.randn(cache.conv(d).shape, generator=gen))
         t = _inputs(cache, B, gen, lens)
         t["page_table"] = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
         cache.set_conv_w(t["conv_w"])
@@ -273,7 +273,7 @@ def test_config4_full_batch_one_period_of_the_stack(oracle):
     C0 = [torch.randn(B + 2, cache.conv_dim, 4, generator=gen) for _ in range(3)]
     for d in range(3):
         cache.state(d).copy_(S0[d])
-        cache.conv(d).copy_(C0[d])
+        cache.set_conv_windows(d, C0[d])
     t = _inputs(cache, B, gen, lens)
     t["page_table"], t["slot_ids"] = table, slots
     dev = {n: x.cuda() for n, x in t.items()}
@@ -310,5 +310,5 @@ def test_config4_full_batch_one_period_of_the_stack(oracle):
                                     t["delta_beta"][d, b].numpy(), t["delta_g"][d, b].numpy())
             assert np.abs(delta_o[d, b] - ref).max() < 1e-4
         assert rel_l2(cache.state(d).cpu().numpy(), Sr) < 1e-6
-        assert np.array_equal(cache.conv(d).cpu().numpy(), Cr)
+        assert np.array_equal(cache.conv_windows(d).cpu().numpy(), Cr)
     cache.close()

@@ -78,7 +78,7 @@ def test_prompt_in_chunks_then_decode(oracle, head_map_name):
         # the chunked form passes operands through fp16 hi + lo pairs: the tolerance of its own test
         assert rel_l2(got["delta_o"][d], o) <= CHUNKED_REL_L2, (d, rel_l2(got["delta_o"][d], o))
         assert rel_l2(cache.state(d)[slot].cpu().numpy(), S) <= CHUNKED_REL_L2
-        assert np.abs(cache.conv(d)[slot].cpu().numpy() - cs).max() == 0.0
+        assert np.abs(cache.conv_windows(d)[slot].cpu().numpy() - cs).max() == 0.0
         S_ref.append(S)
         C_ref.append(cs)
     # attention layers: row t attends to the fp16-rounded rows [0, t] of the whole prompt
