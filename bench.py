@@ -108,12 +108,14 @@ def algorithmic_bytes(n_layers, ctx, n_q=N_Q, n_kv=N_KV, n_v=N_V, n_k=N_K):
     n_delta = n_layers - n_attn
     conv_dim = 2 * n_k * DK + n_v * DV
     attn_launch = sum(ctx) * n_kv * HD * 2 * 2 + B * n_q * HD * 4 * 3
-    delta_launch = B * (2 * n_v * DK * DV * 4 + 2 * (n_k * DK * 4) + n_v * DV * 4 * 2 + n_v * 8)
-    conv_launch = B * (2 * conv_dim * CONV_K * 4 + 2 * conv_dim * 4) + conv_dim * CONV_K * 4
+    # fused DeltaNet step: state read + write, the conv rings (three older taps read, one tap written per
+    # channel), the channels' inputs and taps' weights, beta, g, o
+    conv_launch = B * conv_dim * (3 * 4 + 4 + 4) + conv_dim * CONV_K * 4
+    delta_launch = B * (2 * n_v * DK * DV * 4 + n_v * DV * 4 + n_v * 8) + conv_launch
     append_launch = B * n_kv * HD * (4 + 2) * 2
-    return {"attn_decode": attn_launch, "delta_rule": delta_launch, "conv1d_update": conv_launch,
+    return {"attn_decode": attn_launch, "delta_rule": delta_launch, "conv_part_of_delta_rule": conv_launch,
             "kv_append": append_launch,
-            "step": n_attn * (attn_launch + append_launch) + n_delta * (delta_launch + conv_launch)}
+            "step": n_attn * (attn_launch + append_launch) + n_delta * delta_launch}
 
 
 def load_peaks():
@@ -441,43 +443,38 @@ def op_decode(name, args, sampler, peaks, gen):
 
 
 def op_delta_step(args, sampler, peaks, gen):
-    """One Gated DeltaNet decode step of one layer, batch 1: conv1d update + delta rule."""
+    """One Gated DeltaNet decode step of one layer, batch 1: conv window + l2 norms + delta rule (one kernel)."""
     import torch
 
-    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200 import _lib
     B = args.op_batch or 1
-    ab = algorithmic_bytes(4, [1] * B)
-    bytes_per_launch = ab["delta_rule"] + ab["conv1d_update"]
+    bytes_per_launch = algorithmic_bytes(4, [1] * B)["delta_rule"]
     n_sets = max(1, min(96, int(math.ceil(300e6 / bytes_per_launch))))
     sets = []
     for _ in range(n_sets):
         S = torch.randn(B, N_V, DK, DV, device="cuda", generator=gen) * 0.02
-        cst = torch.zeros(B, CONV_DIM, CONV_K, device="cuda")
+        ring = torch.zeros(B, CONV_DIM, CONV_K, device="cuda")
+        phase = torch.zeros(B, dtype=torch.int32, device="cuda")
         x = torch.randn(B, CONV_DIM, device="cuda", generator=gen)
-        sets.append((S, cst, x))
+        sets.append((S, ring, phase, x))
     w = torch.randn(CONV_DIM, CONV_K, device="cuda", generator=gen) * 0.5
     beta = torch.sigmoid(torch.randn(B, N_V, device="cuda", generator=gen))
     gl = -torch.nn.functional.softplus(torch.randn(B, N_V, device="cuda", generator=gen))
     od = torch.empty(B, N_V, DV, device="cuda")
-    mixed = torch.empty(B, CONV_DIM, device="cuda")
-    qk = 2 * N_K * DK
-    p = _lib.DeltaRecurrentParams(n_v=N_V, dk=DK, dv=DV, eps_l2=1e-6, batch=B, n_slots=B, n_qk=N_K,
-                                  head_map=_lib.RL_HEADS_GROUPED, q_stride=CONV_DIM, k_stride=CONV_DIM, v_stride=CONV_DIM)
-    cp = _lib.Conv1dParams(dim=CONV_DIM, k=CONV_K, silu=1, batch=B, n_slots=B)
+    p = _lib.GdnDecodeParams(n_v=N_V, n_qk=N_K, dk=DK, dv=DV, conv_k=CONV_K, batch=B, n_slots=B,
+                             head_map=_lib.RL_HEADS_GROUPED, eps_l2=1e-6)
     state = {"i": 0}
     L = _lib.lib()
     vp = ctypes.c_void_p
 
     def call():
-        S, cst, x = sets[state["i"] % n_sets]
+        S, ring, phase, x = sets[state["i"] % n_sets]
         state["i"] += 1
         st = vp(torch.cuda.current_stream().cuda_stream)
-        _lib.check(L.rl_conv1d_update(vp(x.data_ptr()), vp(w.data_ptr()), vp(cst.data_ptr()), None, vp(mixed.data_ptr()),
-                                      ctypes.byref(cp), st))
-        # q | k | v are column ranges of the conv output, as in the stack step
-        _lib.check(L.rl_delta_recurrent(vp(S.data_ptr()), None, vp(mixed.data_ptr()), vp(mixed.data_ptr() + N_K * DK * 4),
-                                        vp(mixed.data_ptr() + qk * 4), vp(beta.data_ptr()), vp(gl.data_ptr()),
-                                        vp(od.data_ptr()), ctypes.byref(p), st))
+        _lib.check(L.rl_gdn_decode(vp(S.data_ptr()), vp(ring.data_ptr()), vp(phase.data_ptr()), None, vp(x.data_ptr()),
+                                   vp(w.data_ptr()), vp(beta.data_ptr()), vp(gl.data_ptr()), vp(od.data_ptr()),
+                                   ctypes.byref(p), st))
+        _lib.check(L.rl_gdn_phase_advance(vp(phase.data_ptr()), None, 1, B, B, 1, st))
     ms, calls, clocks = _timed(call, sampler, args.op_seconds, max(3, args.warmup), graph_calls=n_sets)
     _lib.check_device()
     return {
@@ -485,8 +482,8 @@ def op_delta_step(args, sampler, peaks, gen):
         "ms": ms, "value": B / (ms * 1e-3), "unit": "seq-steps/s (one layer)", "calls_timed": calls,
         "dtype": "f32 state", "gpu_launches_per_call": 2,
         "l2": "rotates over %d independent states, %.0f MB in all" % (n_sets, n_sets * bytes_per_launch / 1e6),
-        "timed": "conv1d update + delta rule, CUDA-graph replay back to back",
-        "roofline": _hbm_roofline("delta_decode_kernel + conv1d_update4_kernel", bytes_per_launch, ms, peaks),
+        "timed": "fused conv + delta rule kernel and the ring-phase kernel, CUDA-graph replay back to back",
+        "roofline": _hbm_roofline("gdn_decode_kernel", bytes_per_launch, ms, peaks),
         "clocks": clocks}
 
 
@@ -863,7 +860,7 @@ def main():
         achieved = ab["attn_decode"] / (attn_ms_per_launch * 1e-3) / 1e9
         families = {}
         for k, nl in (("attn_decode", n_attn), ("attn_combine", n_attn), ("kv_append", n_attn),
-                      ("delta_rule", cache.n_delta), ("conv1d_update", cache.n_delta)):
+                      ("delta_rule", cache.n_delta)):
             per = fam[k] / args.steps / max(1, nl)
             families[k] = {"ms_per_launch": round(per, 5), "share": round(fam[k] / args.steps / ms_events, 4)}
             if k in ab:

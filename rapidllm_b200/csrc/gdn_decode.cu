@@ -12,9 +12,9 @@
 // head stores x into slot `phase`; the phase moves on after the step (gdn_phase_advance_kernel).
 //
 // Two forms, as for the unfused delta rule (delta_decode.cu): with at least four heads per SM,
-// persistent CTAs stream whole 64 KiB heads through a 3-stage TMA ring while three warps run
-// the conv + norms of the NEXT item's 384 channels; otherwise one CTA per 32-column slice of a
-// head with the slice in registers.
+// persistent CTAs stream whole 64 KiB heads through a 3-stage TMA ring while three further warps
+// run the conv + norms of the 384 channels of the items ahead and hand q, k, v over through
+// shared memory; otherwise one CTA per 32-column slice of a head with the slice in registers.
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.cuh"
@@ -99,14 +99,16 @@ __device__ __forceinline__ int conv_channel0(int role, int hs, int h, int n_qk, 
 
 // ------------------------------------------------------------------------------------------------
 constexpr int kStreamStages = 3;
-constexpr int kStreamThreads = 288;            // 8 consumer warps + producer warp
+constexpr int kStreamThreads = 384;            // 8 consumer warps + TMA producer warp + 3 conv warps
 constexpr int kHeadBytes = kDk * kDv * 4;      // 64 KiB
+constexpr int kWarpProducer = 8, kWarpConv0 = 9;
 
 struct StreamSmem {
     alignas(128) float S[kStreamStages][kDk * kDv];
     float q[2][kDk], k[2][kDk], v[2][kDv];
     float red[8][kDv], red2[8][kDv];
     uint64_t full[kStreamStages], empty[kStreamStages];
+    uint64_t vec_ready[2], vec_free[2];        // q, k, v of an item: written by the conv warps, read by the consumers
 };
 
 __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(GdnDecodeArgs a) {
@@ -118,6 +120,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
         for (int i = 0; i < kStreamStages; ++i) {
             mbar_init(&s.full[i], 1);
             mbar_init(&s.empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s.vec_ready[i], 3);     // one arrival per conv warp
+            mbar_init(&s.vec_free[i], 1);
         }
         mbar_fence_init();
     }
@@ -133,8 +139,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
         return slot;
     };
 
-    if (warp == 8) {
-        // ------------------------------ producer ------------------------------
+    if (warp == kWarpProducer) {
+        // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t it = 0;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
@@ -152,49 +158,67 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
         }
         return;
     }
+    if (warp >= kWarpConv0) {
+        // ------------------------------ conv warps: q, k, v of the items, one item ahead ------------------------------
+        const int role = warp - kWarpConv0;    // 0 = q, 1 = k (key head's channels), 2 = v (this head's channels)
+        ConvIn cin;
+        auto fetch = [&](int item) {
+            if (item < n_items) {
+                const int b = item / a.n_v, h = item - b * a.n_v;
+                const int slot = slot_of(b);
+                conv_fetch(cin, a, b, slot < 0 ? 0 : slot,
+                           conv_channel0(role, key_head_of(h, a.n_v, a.n_qk, a.head_map), h, a.n_qk, lane));
+            }
+        };
+        fetch(blockIdx.x);
+        uint32_t it = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+            const int buf = it & 1;
+            const int b = item / a.n_v, h = item - b * a.n_v;
+            const int hs = key_head_of(h, a.n_v, a.n_qk, a.head_map);
+            const int slot = slot_of(b);
+            float4 y = conv_four(cin);
+            if (slot >= 0 && (role == 2 || stores_key_taps(h, a.n_v, a.n_qk, a.head_map)))
+                conv_store_taps(cin, a, slot, conv_channel0(role, hs, h, a.n_qk, lane));
+            fetch(item + gridDim.x);           // the next item's inputs are on their way while this one is finished
+            if (role == 0) y = l2norm_warp(y, a.eps_l2, 1.f / sqrtf(float(kDk)));
+            if (role == 1) y = l2norm_warp(y, a.eps_l2, 1.f);
+            // the buffer was last read for item it - 2
+            if (it >= 2 && !mbar_wait(&s.vec_free[buf], ((it - 2) >> 1) & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                break;
+            }
+            float* dst = role == 0 ? s.q[buf] : (role == 1 ? s.k[buf] : s.v[buf]);
+            *reinterpret_cast<float4*>(dst + lane * 4) = y;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.vec_ready[buf]);
+        }
+        return;
+    }
     // ------------------------------ consumers ------------------------------
     const int cg = tid & 31;                  // columns 4cg .. 4cg+3
     const int rg = tid >> 5;                  // rows 16rg .. 16rg+15 (= warp)
-    // warps 0, 1, 2 run the conv of the q, k, v channels; the inputs of an item are fetched while
-    // the previous item's state is being processed
-    ConvIn cin;
-    auto fetch = [&](int item) {
-        if (warp < 3 && item < n_items) {
-            const int b = item / a.n_v, h = item - b * a.n_v;
-            const int slot = slot_of(b);
-            conv_fetch(cin, a, b, slot < 0 ? 0 : slot, conv_channel0(warp, key_head_of(h, a.n_v, a.n_qk, a.head_map), h, a.n_qk, lane));
-        }
-    };
-    fetch(blockIdx.x);
     uint32_t it = 0;
     bool alive = true;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
-        const int st = it % kStreamStages;
+        const int st = it % kStreamStages, buf = it & 1;
         const int b = item / a.n_v, h = item - b * a.n_v;
-        const int hs = key_head_of(h, a.n_v, a.n_qk, a.head_map);
         const int slot = slot_of(b);
-        if (warp < 3) {
-            float4 y = conv_four(cin);
-            if (slot >= 0 && (warp == 2 || stores_key_taps(h, a.n_v, a.n_qk, a.head_map)))
-                conv_store_taps(cin, a, slot, conv_channel0(warp, hs, h, a.n_qk, lane));
-            if (warp == 0) y = l2norm_warp(y, a.eps_l2, 1.f / sqrtf(float(kDk)));
-            if (warp == 1) y = l2norm_warp(y, a.eps_l2, 1.f);
-            float* dst = warp == 0 ? s.q[it & 1] : (warp == 1 ? s.k[it & 1] : s.v[it & 1]);
-            *reinterpret_cast<float4*>(dst + lane * 4) = y;
-            fetch(item + gridDim.x);
-        }
         const float g = expf(a.g_log[size_t(b) * a.n_v + h]);
         const float beta = a.beta[size_t(b) * a.n_v + h];
+        if (alive && !mbar_wait(&s.vec_ready[buf], (it >> 1) & 1)) {
+            set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+            alive = false;
+        }
         if (alive && !mbar_wait(&s.full[st], (it / kStreamStages) & 1)) {
             set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
             alive = false;
         }
-        named_bar_sync(1, 256);               // q, k, v of this item visible
-        const float4 vv = *reinterpret_cast<const float4*>(&s.v[it & 1][cg * 4]);
+        const float4 vv = *reinterpret_cast<const float4*>(&s.v[buf][cg * 4]);
         const float* Sp = s.S[st];
         float* Sg = a.S + (size_t(slot < 0 ? 0 : slot) * a.n_v + h) * (kDk * kDv);
-        const float* kq = s.k[it & 1];
-        const float* qq = s.q[it & 1];
+        const float* kq = s.k[buf];
+        const float* qq = s.q[buf];
         // pass 1: kv = (g S)^T k over this warp's 16 rows
         float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
         if (alive) {
@@ -230,14 +254,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
             }
         }
         *reinterpret_cast<float4*>(&s.red2[rg][cg * 4]) = oo;
-        named_bar_sync(1, 256);               // every thread is done reading this stage
+        named_bar_sync(1, 256);               // every thread is done reading this stage and this item's q, k, v
         if (tid < kDv) {
             float t = 0.f;
 #pragma unroll
             for (int w = 0; w < 8; ++w) t += s.red2[w][tid];
             if (slot >= 0) a.o[(size_t(b) * a.n_v + h) * kDv + tid] = t;
         }
-        if (tid == 0) mbar_arrive(&s.empty[st]);
+        if (tid == 0) {
+            mbar_arrive(&s.empty[st]);
+            mbar_arrive(&s.vec_free[buf]);
+        }
     }
 }
 
