@@ -391,6 +391,10 @@ int rl_rmsnorm(const float* x, const float* gamma, float* y, int rows, int n, fl
 int rl_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* y, int rows,
                      int n_heads, int head_dim, float eps, void* stream);
 
+/* fp32 -> bf16 (round to nearest even) over n values: the reference's prefill keeps its chunk
+ * activations in fp32 (cuda_engine.cu:18338-18590) while rl_attn_prefill takes bf16 rows. */
+int rl_cast_f32_to_bf16(const float* x, void* y_bf16, size_t n, void* stream);
+
 /* The gate maths in front of the delta rule (ops_fused.cpp:12-13, 122-123):
  * beta = sigmoid(b), g_log = -exp(A_log) * softplus(a + dt_bias).  a, b, beta, g_log
  * [rows][n_v]; A_log, dt_bias [n_v]. */
@@ -453,6 +457,17 @@ size_t rl_stack_prefill_workspace_bytes(const rl_cache* c, int pos0, int T);
 int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace, size_t workspace_bytes,
                      void* stream);
 
+/* One DeltaNet layer of rl_stack_prefill on its own, for a host that runs the layers one after the
+ * other with its projections in between (launch_gdn, cuda_engine.cu:10584-10606, inside
+ * launch_prefill_chunk): causal conv over the chunk's T rows with slot's window carried (pos0 > 0) or
+ * empty (pos0 == 0, which also zeroes the slot's state), then T delta-rule steps in chunked form.
+ * qkv fp32 [T][conv_dim] before the conv, conv_w [conv_dim][4], beta / g_log [T][n_v], o [T][n_v][dv].
+ * workspace: rl_cache_delta_prefill_workspace_bytes(c, T) bytes, 256-byte aligned. */
+size_t rl_cache_delta_prefill_workspace_bytes(const rl_cache* c, int T);
+int rl_cache_delta_prefill(rl_cache* c, int delta_index, int slot, int pos0, int T, const float* qkv,
+                           const float* conv_w, const float* beta, const float* g_log, float* o,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
 /* Memory plan for a cache: PlannerInput / PlannerResult / plan_memory
  * (include/rapidllm/runtime/planner.h:11-33, src/runtime/planner.cpp:28-44) plus the engine's
  * KV-type policy (RAPIDLLM_KV_TQ / automatic switch to the compact cache for long contexts,
@@ -508,6 +523,7 @@ float* rl_cache_state(rl_cache* c, int delta_index);
  * or rl_cache_conv_import.  rl_cache_conv_export / _import convert: canon fp32
  * [n_slots][conv_dim][conv_k], oldest tap first (DualCache::conv_ptr). */
 float* rl_cache_conv(rl_cache* c, int delta_index);
+int32_t* rl_cache_conv_phase(rl_cache* c, int delta_index);     /* int32 [n_slots], see rl_gdn_decode */
 int rl_cache_conv_export(rl_cache* c, int delta_index, float* canon, void* stream);
 int rl_cache_conv_import(rl_cache* c, int delta_index, const float* canon, void* stream);
 /* DualCache::zero (dual_cache.cpp:43-47). */

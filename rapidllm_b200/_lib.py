@@ -150,6 +150,9 @@ SYMBOLS = {
     "rl_gdn_phase_advance": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_conv_ring_export": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rl_conv_ring_import": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "rl_cache_conv_phase": (_vp, [_vp, _i]),
+    "rl_cache_delta_prefill_workspace_bytes": (_sz, [_vp, _i]),
+    "rl_cache_delta_prefill": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rl_cache_conv_export": (_i, [_vp, _i, _vp, _vp]),
     "rl_cache_conv_import": (_i, [_vp, _i, _vp, _vp]),
     "rl_conv1d_update": (_i, [_vp, _vp, _vp, _vp, _vp, C.POINTER(Conv1dParams), _vp]),
@@ -158,6 +161,7 @@ SYMBOLS = {
     "rl_attn_qk_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(AttnQkPrepareParams), _vp]),
     "rl_gated_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, _vp]),
     "rl_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, C.c_float, _vp]),
+    "rl_cast_f32_to_bf16": (_i, [_vp, _vp, _sz, _vp]),
     "rl_delta_gates": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "rl_cache_create": (_i, [C.POINTER(CacheConfig), C.POINTER(_vp)]),
     "rl_cache_destroy": (None, [_vp]),

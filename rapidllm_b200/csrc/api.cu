@@ -198,6 +198,8 @@ int knob(const char* name, int dflt) {
 }
 const int kTqSegWeight = knob("RL_B200_TQ_SEG_WEIGHT", 23);
 const int kF16SegWeight = knob("RL_B200_F16_SEG_WEIGHT", 6);
+// heads per launch from which the fused DeltaNet step streams whole heads through persistent CTAs
+const int kGdnStreamMin = knob("RL_B200_GDN_STREAM_MIN", 96);
 
 int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
                      const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
@@ -990,6 +992,18 @@ int rl_gated_rmsnorm(const float* x, const float* z, const float* gamma, float* 
     return RL_OK;
 }
 
+int rl_cast_f32_to_bf16(const float* x, void* y_bf16, size_t n, void* stream) {
+    if (n == 0) return RL_OK;
+    if (!x || !y_bf16) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y_bf16) % 8)
+        return fail(RL_ERR_RANGE, "x must be 16-byte and y 8-byte aligned");
+    const size_t blocks = (n + 1023) / 1024;
+    if (blocks > 0x7fffffffull) return fail(RL_ERR_RANGE, "n too large");
+    rl::cast_f32_bf16_kernel<<<unsigned(blocks), 256, 0, as_stream(stream)>>>(x, static_cast<__nv_bfloat16*>(y_bf16), n);
+    RL_CUDA(cudaGetLastError());
+    return RL_OK;
+}
+
 int rl_delta_gates(const float* a, const float* b, const float* A_log, const float* dt_bias, float* beta,
                    float* g_log, int rows, int n_v, void* stream) {
     if (rows < 0 || n_v <= 0 || 1LL * rows * n_v > (1LL << 30)) return fail(RL_ERR_RANGE, "rows %d n_v %d", rows, n_v);
@@ -1118,7 +1132,7 @@ int rl_gdn_decode(float* S, float* conv_ring, const int32_t* conv_phase, const i
     a.head_map = p->head_map;
     a.conv_dim = 2 * p->n_qk * p->dk + p->n_v * p->dv;
     a.eps_l2 = p->eps_l2;
-    rl::launch_gdn_decode(a, d->sms, as_stream(stream));
+    rl::launch_gdn_decode(a, d->sms, as_stream(stream), kGdnStreamMin);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -1350,6 +1364,10 @@ float* rl_cache_conv(rl_cache* c, int i) {
                ? c->conv + size_t(i) * c->cfg.n_slots * c->conv_dim * c->cfg.conv_k : nullptr;
 }
 
+int32_t* rl_cache_conv_phase(rl_cache* c, int i) {
+    return (c && i >= 0 && i < c->n_delta) ? c->conv_phase + size_t(i) * c->cfg.n_slots : nullptr;
+}
+
 int rl_cache_conv_export(rl_cache* c, int i, float* canon, void* stream) {
     if (!c || i < 0 || i >= c->n_delta) return fail(RL_ERR_RANGE, "no such DeltaNet layer");
     return rl_conv_ring_export(rl_cache_conv(c, i), c->conv_phase + size_t(i) * c->cfg.n_slots, canon, 1, c->cfg.n_slots, -1,
@@ -1530,6 +1548,51 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
         rl::launch_conv_ring_import(c->conv, c->conv_phase, canon, c->n_delta, f.n_slots, io->slot, c->conv_dim, run);
         RL_CUDA(cudaGetLastError());
     }
+    return RL_OK;
+}
+
+size_t rl_cache_delta_prefill_workspace_bytes(const rl_cache* c, int T) {
+    StackPrefillPlan pl;
+    if (!c || !c->n_delta || stack_prefill_plan(c, 0, T, &pl)) return 0;
+    return pl.mixed_bytes + pl.delta_ws + align_up(size_t(c->conv_dim) * c->cfg.conv_k * sizeof(float), 256);
+}
+
+int rl_cache_delta_prefill(rl_cache* c, int di, int slot, int pos0, int T, const float* qkv, const float* conv_w,
+                           const float* beta, const float* g_log, float* o, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+    if (!c || di < 0 || di >= c->n_delta) return fail(RL_ERR_RANGE, "no such DeltaNet layer");
+    StackPrefillPlan pl;
+    if (int st = stack_prefill_plan(c, pos0, T, &pl)) return st;
+    const rl_cache_config& f = c->cfg;
+    if (slot < 0 || slot >= f.n_slots) return fail(RL_ERR_RANGE, "slot %d outside [0, %d)", slot, f.n_slots);
+    if (T == 0) return RL_OK;
+    if (!qkv || !conv_w || !beta || !g_log || !o || !workspace) return fail(RL_ERR_RANGE, "NULL pointer argument");
+    const size_t need = rl_cache_delta_prefill_workspace_bytes(c, T);
+    if (workspace_bytes < need) return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, need);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(RL_ERR_RANGE, "workspace must be 256-byte aligned");
+    cudaStream_t run = as_stream(stream);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    float* mixed = reinterpret_cast<float*>(ws);
+    void* delta_ws = ws + pl.mixed_bytes;
+    float* canon = reinterpret_cast<float*>(ws + pl.mixed_bytes + pl.delta_ws);
+    const size_t slot_S = size_t(f.n_v) * f.dk * f.dv;
+    float* S = rl_cache_state(c, di) + size_t(slot) * slot_S;
+    float* ring = rl_cache_conv(c, di);
+    int32_t* phase = rl_cache_conv_phase(c, di);
+    if (pos0 == 0) RL_CUDA(cudaMemsetAsync(S, 0, slot_S * sizeof(float), run));
+    else rl::launch_conv_ring_export(ring, phase, canon, 1, f.n_slots, slot, c->conv_dim, run);
+    rl_conv1d_params cp;
+    cp.dim = c->conv_dim;
+    cp.k = f.conv_k;
+    cp.silu = 1;
+    cp.batch = 1;
+    cp.n_slots = 1;
+    if (int st = rl_conv1d_causal(qkv, conv_w, mixed, canon, T, &cp, pos0 > 0, run)) return st;
+    if (int st = rl_delta_chunk_prefill(S, mixed, mixed + size_t(f.n_k) * f.dk, mixed + 2 * size_t(f.n_k) * f.dk, beta, g_log,
+                                        o, delta_ws, pl.delta_ws, &pl.dp, run))
+        return st;
+    rl::launch_conv_ring_import(ring, phase, canon, 1, f.n_slots, slot, c->conv_dim, run);
+    RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
 

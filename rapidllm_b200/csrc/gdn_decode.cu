@@ -416,11 +416,12 @@ __global__ void conv_ring_import_kernel(float* ring, int32_t* phase, const float
 size_t gdn_decode_stream_smem_bytes() { return sizeof(StreamSmem) + 128; }
 const void* gdn_decode_stream_kernel_ptr() { return reinterpret_cast<const void*>(&gdn_decode_stream_kernel); }
 
-void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st) {
+void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st, int stream_min_items) {
     if (a.batch <= 0) return;
     const int items = a.batch * a.n_v;
-    if (sms > 0 && items >= 4 * sms) {
-        launch_step(gdn_decode_stream_kernel, dim3(sms), dim3(kStreamThreads), gdn_decode_stream_smem_bytes(), st, a);
+    if (sms > 0 && items >= stream_min_items) {
+        launch_step(gdn_decode_stream_kernel, dim3(items < sms ? items : sms), dim3(kStreamThreads),
+                    gdn_decode_stream_smem_bytes(), st, a);
         return;
     }
     launch_step(gdn_decode_kernel, dim3(kSlices, a.n_v, a.batch), dim3(256), 0, st, a);

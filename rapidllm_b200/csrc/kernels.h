@@ -161,7 +161,8 @@ struct GdnDecodeArgs {
     int batch, n_v, n_qk, n_slots, head_map, conv_dim;
     float eps_l2;
 };
-void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st);
+// heads (items) from which the streaming form is used instead of one CTA per column slice
+void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st, int stream_min_items);
 size_t gdn_decode_stream_smem_bytes();
 const void* gdn_decode_stream_kernel_ptr();
 // phase[l][slot_ids[b]] = (phase + n_tok) & 3 for l < n_layers, b < batch (phase [n_layers][n_slots])
@@ -198,6 +199,7 @@ struct GatedRmsnormArgs {
 };
 __global__ void gated_rmsnorm_kernel(GatedRmsnormArgs a);
 __global__ void rmsnorm_kernel(const float* x, const float* gamma, float* y, int n, float eps);
+__global__ void cast_f32_bf16_kernel(const float* x, __nv_bfloat16* y, size_t n);
 __global__ void delta_gates_kernel(const float* a_in, const float* b_in, const float* A_log, const float* dt_bias,
                                    float* beta, float* g_log, int n_v, int rows);
 

@@ -112,4 +112,19 @@ __global__ void delta_gates_kernel(const float* a_in, const float* b_in, const f
     g_log[i] = -expf(A_log[h]) * sp;
 }
 
+// fp32 rows -> bf16 (round to nearest even): the element type rl_attn_prefill takes its chunk rows in
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* x, __nv_bfloat16* y, size_t n) {
+    const size_t i = (size_t(blockIdx.x) * 256 + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 v = *reinterpret_cast<const float4*>(x + i);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 out;
+        out.x = *reinterpret_cast<uint32_t*>(&a);
+        out.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(y + i) = out;
+    } else {
+        for (size_t j = i; j < n; ++j) y[j] = __float2bfloat16_rn(x[j]);
+    }
+}
+
 }  // namespace rl
