@@ -54,7 +54,7 @@ PAGE = 64
 # tolerances of the sharded-step check (those of the tests: fp16-KV attention / FP32 DeltaNet)
 ATTN_MAX_ABS, ATTN_REL_L2, DELTA_MAX_ABS = 2e-2, 1e-3, 1e-4
 OPERATORS = ["f16_decode", "f16_decode_long", "delta_step", "compact_decode", "compact_decode_wht256",
-             "attn_prefill", "attn_prefill_chunk1024", "delta_prefill", "stack_prefill"]
+             "attn_prefill", "attn_prefill_chunk1024", "delta_prefill", "stack_prefill", "stack_long_compact"]
 
 
 def parse():
@@ -610,6 +610,77 @@ def op_stack_prefill(args, sampler, peaks, gen):
     return entry
 
 
+def op_stack_long(args, sampler, peaks, gen):
+    """The 64-layer stack decode at the metric's context range on the compact cache: batch 32, ragged ctx
+    U[32768, 131072], q8-K / TQ3-V pages inside rl_cache (every sequence is past the F16 window)."""
+    import torch
+
+    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    B = args.op_batch or 32
+    lo, hi = 32768, args.op_ctx or 131072
+    cg = torch.Generator().manual_seed(args.seed)
+    ctx = torch.randint(lo, hi + 1, (B,), generator=cg).tolist()
+    pages = [(c + PAGE - 1) // PAGE for c in ctx]
+    max_pages, n_pages = max(pages), sum(pages)
+    types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
+    window = 8192
+    cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages, max_seq_len=max(ctx),
+                        kv_dtype=_lib.RL_KV_Q8K_TQ3V, wht_len=128, window_tokens=window)
+    perm = torch.randperm(n_pages, generator=cg).int()
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    at = 0
+    for b, p in enumerate(pages):
+        table[b, :p] = perm[at:at + p]
+        at += p
+    table_d = table.cuda()
+    # layer 0's pages are quantised from N(0,1) rows, the other layers get a copy (same page table)
+    p0 = cache.k_pool(0)
+    step = 8192
+    for b in range(B):
+        for t0 in range(0, ctx[b] - 1, step):
+            n = min(step, ctx[b] - 1 - t0)
+            k = torch.randn(n, N_KV, HD, device="cuda", generator=gen)
+            v = torch.randn(n, N_KV, HD, device="cuda", generator=gen)
+            ops.kv_compact_append(p0, table_d[b], k, v, 128, None, pos0=t0)
+    for a in range(1, cache.n_attn):
+        cache.k_pool(a).copy_(p0)
+    for d in range(cache.n_delta):
+        cache.state(d).normal_(0.0, 0.02, generator=gen)
+        cache.conv(d).normal_(generator=gen)
+    sh = cache.io_shapes(B)
+    dev = {n: torch.randn(sh[n], device="cuda", generator=gen) for n in ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv")}
+    dev["delta_beta"] = torch.sigmoid(torch.randn(sh["delta_beta"], device="cuda", generator=gen))
+    dev["delta_g"] = -torch.nn.functional.softplus(torch.randn(sh["delta_g"], device="cuda", generator=gen))
+    dev["conv_w"] = torch.randn(sh["conv_w"], device="cuda", generator=gen) * 0.5
+    dev["attn_o"], dev["delta_o"] = torch.zeros(sh["attn_o"], device="cuda"), torch.zeros(sh["delta_o"], device="cuda")
+    dev["page_table"] = table_d
+    dev["pos"] = torch.tensor([c - 1 for c in ctx], dtype=torch.int32, device="cuda")
+    dev["kv_window_ok"] = False
+
+    def call():
+        cache.decode(dev, B)
+    ms, calls, clocks = _timed(call, sampler, args.op_seconds, max(3, args.warmup))
+    _lib.check_device()
+    finite = bool(torch.isfinite(dev["attn_o"]).all() and torch.isfinite(dev["delta_o"]).all())
+    per_tok = _lib.lib().rl_kv_compact_page_bytes() // PAGE
+    ab = algorithmic_bytes(args.layers, ctx)
+    attn_bytes = sum(ctx) * N_KV * per_tok + B * N_Q * HD * 4 * 3
+    step_bytes = cache.n_attn * (attn_bytes + ab["kv_append"]) + cache.n_delta * ab["delta_rule"]
+    entry = {
+        "workload": "hybrid_stack_decode on the compact cache: %d layers, batch %d, ragged ctx U[%d,%d], q8-K / TQ3-V pages "
+                    "(358 B per token and head) + F16 window of %d tokens, page 64" % (len(types), B, lo, hi, window),
+        "ms": ms, "value": B / (ms * 1e-3), "unit": "seq-steps/s", "calls_timed": calls,
+        "dtype": "q8 K / tq3 V / f32 state", "gpu_launches_per_call": cache.launches_per_step,
+        "l2": "inputs larger than L2 (%.1f GB streamed per step)" % (step_bytes / 1e9),
+        "timed": "rl_stack_decode (graph replay), back to back", "outputs_finite": finite,
+        "ctx_tokens": sum(ctx), "cache_bytes": cache.bytes,
+        "roofline": _hbm_roofline("whole step (attn_decode_tq_kernel dominates)", step_bytes, ms, peaks),
+        "clocks": clocks}
+    cache.close()
+    return entry
+
+
 def run_one_operator(name, args, sampler, peaks):
     import torch
     gen = torch.Generator(device="cuda").manual_seed(args.seed)
@@ -623,6 +694,8 @@ def run_one_operator(name, args, sampler, peaks):
         return op_delta_prefill(args, sampler, peaks, gen)
     if name == "stack_prefill":
         return op_stack_prefill(args, sampler, peaks, gen)
+    if name == "stack_long_compact":
+        return op_stack_long(args, sampler, peaks, gen)
     raise SystemExit("unknown operator %s" % name)
 
 

@@ -196,6 +196,8 @@ typedef struct rl_kv_append_params {
     int pos0;                    /* first position when pos == NULL */
     int rows_fp16;               /* row element type: 0 fp32 (rounded to nearest even), 1 fp16, 2 bf16 */
     int wht_len;                 /* compact cache only: 128 or 256 */
+    int pos_limit;               /* F16 cache only, > 0: rows at positions >= pos_limit are left out (used
+                                  * for the F16 window beside a compact cache); 0 = write every row */
 } rl_kv_append_params;
 
 /* DualCache::append_kv (src/runtime/dual_cache.cpp:74-79) / store_kv_batch_h_k
@@ -217,9 +219,10 @@ int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16,
  * evaluated in IEEE fp32.  The pool is n_pages * n_kv * rl_kv_compact_page_bytes()
  * bytes, 358 bytes per token and head as in the reference (cuda_engine.cu:18305-18318). */
 size_t rl_kv_compact_page_bytes(void);
-/* k_rows, v_rows fp32 [batch][n_tok][n_kv][256]; tq_signs device [256] or NULL. */
+/* k_rows, v_rows [batch][n_tok][n_kv][256], fp32 (rows_fp16 == 0) or bf16 (rows_fp16 == 2, widened
+ * exactly before quantising); tq_signs device [256] or NULL. */
 int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* pos,
-                         const float* k_rows, const float* v_rows, const float* tq_signs,
+                         const void* k_rows, const void* v_rows, const float* tq_signs,
                          const rl_kv_append_params* p, void* stream);
 /* Tokens [0, n_tok) of one sequence in the reference's packing: k_q int8 [n_tok][n_kv][256],
  * k_sc fp16 [n_tok][n_kv], v_codes u8 [n_tok][n_kv][96], v_sc fp16 [n_tok][n_kv][256/wht_len]. */
@@ -415,13 +418,23 @@ typedef struct rl_cache_config {
     int n_layers;                /* length of layer_types */
     const int* layer_types;      /* RL_LAYER_* per layer (ModelDesc.layers[i].kind) */
     int n_q, n_kv, head_dim;     /* attention: 24, 4, 256 */
-    int kv_dtype;                /* RL_KV_F16 */
+    int kv_dtype;                /* RL_KV_F16, or RL_KV_Q8K_TQ3V (then see wht_len, window_tokens below) */
     int page_tokens, n_pages;    /* 64, pool size shared by all attention layers */
     int n_v, n_k, dk, dv;        /* DeltaNet: 48, 16, 128, 128 */
     int conv_k;                  /* must be 4; conv_dim = 2*n_k*dk + n_v*dv */
     int head_map;                /* RL_HEADS_GROUPED (HF) or RL_HEADS_TILED (GGUF) */
     int n_slots;                 /* sequences that can hold DeltaNet state */
     int max_batch, max_pages_per_seq, max_seq_len;
+    /* RL_KV_Q8K_TQ3V only (the engine's compact cache, cuda_engine.cu:20106-20165): every token
+     * persists as q8 K + TQ3 V; beside it an F16 compute window holds the first window_tokens
+     * tokens of every slot (rl_plan_cache gives the size; 0 = no window).  Decode steps attend
+     * over the window while the caller says every sequence is inside it (rl_stack_io.kv_window_ok,
+     * the engine's rule at 18948-18953, 19048), else over the compact pages; a prefill chunk
+     * [pos0, pos0 + T) attends over the window when it ends inside it, else over F16 scratch
+     * pages rebuilt from the compact pages (18487-18497, 18331-18336). */
+    int wht_len;                 /* 128 (the reference's layout) or 256 */
+    int window_tokens;
+    const float* tq_signs;       /* HOST [256] +-1 sign vector for wht_len 256, else NULL */
 } rl_cache_config;
 
 /* One chunk of one sequence's prompt through every layer: the reference's chunked-prefill driver
@@ -517,6 +530,11 @@ size_t rl_cache_bytes(const rl_cache* c);
  * src/ir/model_desc.cpp:12-22). */
 void* rl_cache_k_pool(rl_cache* c, int attn_index);
 void* rl_cache_v_pool(rl_cache* c, int attn_index);
+/* Compact cache: k_pool above is the layer's record pool (rl_kv_compact_append's format) and v_pool is
+ * NULL; these are the F16 window pools [n_slots * window pages][n_kv] of 64x256 slices (slot s owns
+ * pages [s * wp, (s + 1) * wp), wp = ceil(window_tokens / 64)), NULL without a window. */
+void* rl_cache_window_k_pool(rl_cache* c, int attn_index);
+void* rl_cache_window_v_pool(rl_cache* c, int attn_index);
 float* rl_cache_state(rl_cache* c, int delta_index);
 /* The conv windows of a layer as stored: rings [n_slots][conv_dim][4] (see rl_gdn_decode); equal to
  * the reference's shifted windows only while no token has been consumed since creation, rl_cache_zero
@@ -555,6 +573,10 @@ typedef struct rl_stack_io {
      * of pos + 1. */
     float* attn_ml;
     int no_append;
+    /* Compact cache only: != 0 = the caller (who knows the positions on the host, like the engine's
+     * decode_tokens(tokens, poss, B)) asserts that every pos[b] < window_tokens, so the attention
+     * layers read the F16 window; 0 = they read the compact pages (always valid). */
+    int kv_window_ok;
 } rl_stack_io;
 
 /* One decode step over layer_types[]: the scheduler loop of

@@ -42,7 +42,7 @@ class AttnPrefillParams(C.Structure):
 class KvAppendParams(C.Structure):
     _fields_ = [(n, C.c_int) for n in (
         "n_kv", "head_dim", "batch", "n_tok", "page_tokens", "n_pages", "max_pages_per_seq",
-        "pos0", "rows_fp16", "wht_len")]
+        "pos0", "rows_fp16", "wht_len", "pos_limit")]
 
 
 class DeltaRecurrentParams(C.Structure):
@@ -91,14 +91,15 @@ class CacheConfig(C.Structure):
                 ("page_tokens", C.c_int), ("n_pages", C.c_int),
                 ("n_v", C.c_int), ("n_k", C.c_int), ("dk", C.c_int), ("dv", C.c_int),
                 ("conv_k", C.c_int), ("head_map", C.c_int), ("n_slots", C.c_int),
-                ("max_batch", C.c_int), ("max_pages_per_seq", C.c_int), ("max_seq_len", C.c_int)]
+                ("max_batch", C.c_int), ("max_pages_per_seq", C.c_int), ("max_seq_len", C.c_int),
+                ("wht_len", C.c_int), ("window_tokens", C.c_int), ("tq_signs", C.c_void_p)]
 
 
 class StackIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta", "delta_g",
         "delta_o", "conv_w", "page_table", "pos", "slot_ids")] + [
-        ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int)]
+        ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int), ("kv_window_ok", C.c_int)]
 
 
 class StackGather(C.Structure):
@@ -168,6 +169,8 @@ SYMBOLS = {
     "rl_cache_bytes": (_sz, [_vp]),
     "rl_cache_k_pool": (_vp, [_vp, _i]),
     "rl_cache_v_pool": (_vp, [_vp, _i]),
+    "rl_cache_window_k_pool": (_vp, [_vp, _i]),
+    "rl_cache_window_v_pool": (_vp, [_vp, _i]),
     "rl_cache_state": (_vp, [_vp, _i]),
     "rl_cache_conv": (_vp, [_vp, _i]),
     "rl_cache_zero": (_i, [_vp, _vp]),

@@ -25,14 +25,15 @@ class _DevView:
 
 
 def _view(ptr, shape, dtype):
-    typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.int32: "<i4"}[dtype]
+    typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.int32: "<i4", torch.uint8: "|u1"}[dtype]
     return torch.as_tensor(_DevView(ptr, shape, typestr), device="cuda")
 
 
 class HybridCache:
     def __init__(self, layer_types, n_pages, n_slots, max_batch, max_pages_per_seq,
                  max_seq_len=None, n_q=24, n_kv=4, head_dim=256, n_v=48, n_k=16, dk=128, dv=128,
-                 conv_k=4, head_map=_lib.RL_HEADS_GROUPED):
+                 conv_k=4, head_map=_lib.RL_HEADS_GROUPED, kv_dtype=_lib.RL_KV_F16, wht_len=128, window_tokens=0,
+                 tq_signs=None):
         self.layer_types = list(layer_types)
         self.n_attn = sum(1 for t in self.layer_types if t == _lib.RL_LAYER_FULL_ATTENTION)
         self.n_delta = len(self.layer_types) - self.n_attn
@@ -42,9 +43,13 @@ class HybridCache:
         self.n_pages, self.n_slots, self.max_batch = n_pages, n_slots, max_batch
         self.max_pages_per_seq = max_pages_per_seq
         self.max_seq_len = max_seq_len or max_pages_per_seq * 64
+        self.kv_dtype, self.wht_len, self.window_tokens = kv_dtype, wht_len, window_tokens
+        self.window_pages = -(-window_tokens // 64) if kv_dtype == _lib.RL_KV_Q8K_TQ3V else 0
         arr = (C.c_int * len(self.layer_types))(*self.layer_types)
+        signs = None if tq_signs is None else tq_signs.detach().cpu().float().contiguous()   # HOST [256]
         cfg = CacheConfig(n_layers=len(self.layer_types), layer_types=arr, n_q=n_q, n_kv=n_kv,
-                          head_dim=head_dim, kv_dtype=_lib.RL_KV_F16, page_tokens=64,
+                          head_dim=head_dim, kv_dtype=kv_dtype, wht_len=wht_len, window_tokens=window_tokens,
+                          tq_signs=None if signs is None else signs.data_ptr(), page_tokens=64,
                           n_pages=n_pages, n_v=n_v, n_k=n_k, dk=dk, dv=dv, conv_k=conv_k,
                           head_map=head_map, n_slots=n_slots, max_batch=max_batch,
                           max_pages_per_seq=max_pages_per_seq, max_seq_len=self.max_seq_len)
@@ -64,7 +69,17 @@ class HybridCache:
         return lib().rl_cache_bytes(self._h)
 
     def k_pool(self, i):
+        if self.kv_dtype == _lib.RL_KV_Q8K_TQ3V:           # record pool of the compact cache (bytes)
+            return _view(lib().rl_cache_k_pool(self._h, i), (self.n_pages, self.n_kv, lib().rl_kv_compact_page_bytes()),
+                         torch.uint8)
         return _view(lib().rl_cache_k_pool(self._h, i), (self.n_pages, self.n_kv, 64 * 256), torch.float16)
+
+    def window_pools(self, i):
+        """(K, V) F16 window pools of attention layer i beside a compact cache: slot s owns pages
+        [s * window_pages, (s + 1) * window_pages)."""
+        shape = (self.n_slots * self.window_pages, self.n_kv, 64 * 256)
+        return (_view(lib().rl_cache_window_k_pool(self._h, i), shape, torch.float16),
+                _view(lib().rl_cache_window_v_pool(self._h, i), shape, torch.float16))
 
     def v_pool(self, i):
         return _view(lib().rl_cache_v_pool(self._h, i), (self.n_pages, self.n_kv, 64 * 256), torch.float16)
@@ -125,6 +140,7 @@ class HybridCache:
     def _io(self, t, batch, cuda):
         io = StackIO(batch=batch)
         io.no_append = int(bool(t.get("no_append", False)))
+        io.kv_window_ok = int(bool(t.get("kv_window_ok", False)))
         for name in ("attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta",
                      "delta_g", "delta_o", "conv_w", "page_table", "pos", "slot_ids", "attn_ml"):
             x = t.get(name)

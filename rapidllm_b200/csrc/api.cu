@@ -286,9 +286,22 @@ struct rl_cache {
     float* S = nullptr;             // [n_delta][n_slots][n_v][dk][dv]
     float* conv = nullptr;          // [n_delta][n_slots][conv_dim][conv_k] ring windows (gdn_decode.cu)
     int32_t* conv_phase = nullptr;  // [n_delta][n_slots] ring position of each slot's next token
+    int* dev_err = nullptr;         // the device error word
     void* attn_ws = nullptr;
     size_t attn_ws_bytes = 0;
     size_t bytes = 0;
+    // compact cache (kv_dtype == RL_KV_Q8K_TQ3V): record pools, the F16 window and the prefill scratch
+    unsigned char* kvc = nullptr;   // [n_attn][cpool_bytes] q8-K / TQ3-V records of every page
+    size_t cpool_bytes = 0;
+    int win_pages = 0;              // window pages per slot
+    size_t wpool_elems = 0;         // halves per (layer, K or V) window pool = n_slots * win_pages pages
+    __half* kvw = nullptr;          // [n_attn][2][wpool_elems]
+    int32_t* win_table = nullptr;   // [n_slots][win_pages]: slot s owns window pages s * win_pages ..
+    int32_t* win_rows = nullptr;    // [max_batch][win_pages] rows of the sequences of the step in flight
+    float* d_signs = nullptr;       // [256] or null
+    __half* scratch = nullptr;      // [2][max_pages_per_seq pages] F16 pages a prefill chunk past the window reads
+    int32_t* scratch_table = nullptr;   // [max_pages_per_seq] identity
+    bool compact() const { return cfg.kv_dtype == RL_KV_Q8K_TQ3V; }
     // host-call staging
     bool staging = false;
     float *d_attn_q = nullptr, *d_attn_gate = nullptr, *d_attn_k = nullptr, *d_attn_v = nullptr,
@@ -336,6 +349,17 @@ struct rl_cache {
         p.max_seq_len = cfg.max_seq_len;
         p.len_add = 1;
         p.chunk_pages = 0;
+        p.wht_len = cfg.wht_len;
+        p.tq_signs = d_signs;
+        return p;
+    }
+    // the same over the F16 window pools (rows from win_rows / win_table)
+    rl_attn_decode_params window_params(int batch) const {
+        rl_attn_decode_params p = attn_params(batch);
+        p.kv_dtype = RL_KV_F16;
+        p.n_pages = cfg.n_slots * win_pages;
+        p.max_pages_per_seq = win_pages;
+        p.max_seq_len = std::min(cfg.max_seq_len, win_pages * cfg.page_tokens);
         return p;
     }
 };
@@ -403,6 +427,11 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
         sent_d = di;
         return RL_OK;
     };
+    if (c->compact() && c->win_pages && c->n_attn) {
+        if (host_mode) RL_CUDA(cudaStreamWaitEvent(run, c->ev_in[std::min(kHostGroup, f.n_layers) - 1], 0));
+        RL_CUDA(rl::launch_step(rl::kv_slot_rows_kernel, dim3(B), dim3(128), 0, run, c->win_rows, io->slot_ids, c->win_pages,
+                                f.n_slots, c->dev_err));
+    }
     for (int L = 0; L < f.n_layers; ++L) {
         // host buffers: the layers synchronise with the copy streams once per group of layers, not per
         // layer (every wait costs the run stream a few microseconds and the dependent launch behind it)
@@ -421,22 +450,54 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             ap.pos0 = 0;
             ap.rows_fp16 = 0;
             ap.wht_len = 0;
+            ap.pos_limit = 0;
+            ap.pos_limit = 0;
             void* kp = rl_cache_k_pool(c, ai);
             void* vp = rl_cache_v_pool(c, ai);
-            if (!io->no_append)
-                if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
-                                          io->attn_v + ai * kv_sz, &ap, run))
+            const float* q_l = io->attn_q + ai * q_sz;
+            const float* gate_l = (io->attn_gate && !io->attn_ml) ? io->attn_gate + ai * q_sz : nullptr;
+            float* ml_l = io->attn_ml ? io->attn_ml + size_t(ai) * B * f.n_q * 2 : nullptr;
+            cudaEvent_t after_main = tm ? c->tev[size_t(L) * 4 + 3] : nullptr;
+            if (!c->compact()) {
+                if (!io->no_append)
+                    if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
+                                              io->attn_v + ai * kv_sz, &ap, run))
+                        return st;
+                mark(L, 1);
+                rl_attn_decode_params dp = c->attn_params(B);
+                dp.len_add = io->no_append ? 0 : 1;
+                if (int st = attn_decode_impl(kp, vp, io->page_table, io->pos, q_l, gate_l, io->attn_o + ai * q_sz, ml_l,
+                                              c->attn_ws, c->attn_ws_bytes, &dp, run, after_main))
                     return st;
-            mark(L, 1);
-            rl_attn_decode_params dp = c->attn_params(B);
-            dp.len_add = io->no_append ? 0 : 1;
-            if (int st = attn_decode_impl(kp, vp, io->page_table, io->pos, io->attn_q + ai * q_sz,
-                                          (io->attn_gate && !io->attn_ml) ? io->attn_gate + ai * q_sz : nullptr,
-                                          io->attn_o + ai * q_sz,
-                                          io->attn_ml ? io->attn_ml + size_t(ai) * B * f.n_q * 2 : nullptr,
-                                          c->attn_ws, c->attn_ws_bytes, &dp, run,
-                                          tm ? c->tev[size_t(L) * 4 + 3] : nullptr))
-                return st;
+            } else {
+                // every token persists in the compact pages; the F16 window rows of the sequences still
+                // inside it are kept current whichever of the two this step reads
+                void* kw = rl_cache_window_k_pool(c, ai);
+                void* vw = rl_cache_window_v_pool(c, ai);
+                if (!io->no_append) {
+                    ap.wht_len = f.wht_len;
+                    if (int st = rl_kv_compact_append(kp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
+                                                      io->attn_v + ai * kv_sz, c->d_signs, &ap, run))
+                        return st;
+                    if (c->win_pages) {
+                        rl_kv_append_params wp = ap;
+                        wp.n_pages = f.n_slots * c->win_pages;
+                        wp.max_pages_per_seq = c->win_pages;
+                        wp.pos_limit = f.window_tokens;
+                        if (int st = rl_kv_append(kw, vw, c->win_rows, io->pos, io->attn_k + ai * kv_sz,
+                                                  io->attn_v + ai * kv_sz, &wp, run))
+                            return st;
+                    }
+                }
+                mark(L, 1);
+                const bool over_window = io->kv_window_ok && c->win_pages;
+                rl_attn_decode_params dp = over_window ? c->window_params(B) : c->attn_params(B);
+                dp.len_add = io->no_append ? 0 : 1;
+                if (int st = attn_decode_impl(over_window ? kw : kp, over_window ? vw : nullptr,
+                                              over_window ? c->win_rows : io->page_table, io->pos, q_l, gate_l,
+                                              io->attn_o + ai * q_sz, ml_l, c->attn_ws, c->attn_ws_bytes, &dp, run, after_main))
+                    return st;
+            }
             mark(L, 2);
             ++ai;
         } else {
@@ -634,6 +695,7 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     a.max_pages_per_seq = p->max_pages_per_seq;
     a.pos0 = p->pos0;
     a.rows_fp16 = p->rows_fp16;
+    a.pos_limit = p->pos_limit;
     const int rows_per_block = p->n_tok >= 8 ? 8 : 1;
     RL_CUDA(rl::launch_step(rl::kv_write_kernel, dim3((p->n_tok + rows_per_block - 1) / rows_per_block, p->n_kv, p->batch),
                             dim3(32, rows_per_block), 0, as_stream(stream), a));
@@ -692,6 +754,7 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
         ap.pos0 = p->pos0;
         ap.rows_fp16 = 2;
         ap.wht_len = 0;
+            ap.pos_limit = 0;
         if (int st = rl_kv_append(k_pool, v_pool, page_table_row, nullptr, k_rows_bf16, v_rows_bf16, &ap, stream))
             return st;
     }
@@ -776,14 +839,14 @@ int rl_kv_gather(const void* pool, const int32_t* page_table_row, void* out_f16,
 
 size_t rl_kv_compact_page_bytes(void) { return 2 * size_t(rl::kCompactRecordBytes); }
 
-int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* pos, const float* k_rows,
-                         const float* v_rows, const float* tq_signs, const rl_kv_append_params* p,
+int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* pos, const void* k_rows,
+                         const void* v_rows, const float* tq_signs, const rl_kv_append_params* p,
                          void* stream) {
     if (!p) return fail(RL_ERR_RANGE, "params is NULL");
     if (p->head_dim != rl::kHeadDim || p->page_tokens != rl::kPageTokens)
         return fail(RL_ERR_UNSUPPORTED, "head_dim %d / page_tokens %d: only 256 / 64", p->head_dim, p->page_tokens);
     if (p->wht_len != 128 && p->wht_len != 256) return fail(RL_ERR_UNSUPPORTED, "wht_len %d: only 128 or 256", p->wht_len);
-    if (p->rows_fp16) return fail(RL_ERR_UNSUPPORTED, "the compact cache quantises fp32 rows");
+    if (p->rows_fp16 != 0 && p->rows_fp16 != 2) return fail(RL_ERR_UNSUPPORTED, "the compact cache quantises fp32 or bf16 rows");
     if (p->batch < 0 || p->n_tok < 0 || p->n_kv <= 0 || p->n_kv > 65535 || p->batch > 65535)
         return fail(RL_ERR_RANGE, "batch %d n_tok %d n_kv %d", p->batch, p->n_tok, p->n_kv);
     if (p->batch == 0 || p->n_tok == 0) return RL_OK;
@@ -806,6 +869,7 @@ int rl_kv_compact_append(void* pool, const int32_t* page_table, const int32_t* p
     a.max_pages_per_seq = p->max_pages_per_seq;
     a.pos0 = p->pos0;
     a.wht_len = p->wht_len;
+    a.rows_bf16 = p->rows_fp16 == 2;
     rl::kv_compact_write_kernel<<<dim3(p->n_tok, p->n_kv, p->batch), 256, 0, as_stream(stream)>>>(a);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
@@ -1283,7 +1347,12 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
     if (cfg->n_layers <= 0 || !cfg->layer_types) return fail(RL_ERR_RANGE, "no layers");
     if (cfg->head_dim != rl::kHeadDim || cfg->page_tokens != rl::kPageTokens || cfg->dk != 128 || cfg->dv != 128)
         return fail(RL_ERR_UNSUPPORTED, "shapes: head_dim 256, page_tokens 64, dk = dv = 128 only");
-    if (cfg->kv_dtype != RL_KV_F16) return fail(RL_ERR_UNSUPPORTED, "rl_cache holds F16 KV only");
+    if (cfg->kv_dtype != RL_KV_F16 && cfg->kv_dtype != RL_KV_Q8K_TQ3V) return fail(RL_ERR_UNSUPPORTED, "kv_dtype %d unknown", cfg->kv_dtype);
+    const bool compact = cfg->kv_dtype == RL_KV_Q8K_TQ3V;
+    if (compact && ((cfg->wht_len != 128 && cfg->wht_len != 256) || cfg->window_tokens < 0 ||
+                    cfg->window_tokens > cfg->max_pages_per_seq * cfg->page_tokens || (cfg->wht_len == 256 && !cfg->tq_signs)))
+        return fail(RL_ERR_RANGE, "compact cache: wht_len %d (128 or 256, 256 with tq_signs), window_tokens %d within the context",
+                    cfg->wht_len, cfg->window_tokens);
     if (cfg->conv_k != 4) return fail(RL_ERR_UNSUPPORTED, "conv_k %d: the cache keeps 4-tap ring windows", cfg->conv_k);
     if (cfg->n_slots <= 0 || cfg->max_batch <= 0 || cfg->n_pages <= 0 || cfg->max_pages_per_seq <= 0 ||
         cfg->n_k <= 0 || cfg->n_v % cfg->n_k)
@@ -1297,15 +1366,48 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
     c->cfg.layer_types = c->types.data();
     for (int t : c->types) (t == RL_LAYER_FULL_ATTENTION ? c->n_attn : c->n_delta)++;
     c->conv_dim = 2 * cfg->n_k * cfg->dk + cfg->n_v * cfg->dv;
-    c->pool_elems = size_t(cfg->n_pages) * cfg->n_kv * rl::kv_slice_elems();
+    c->dev_err = d->err_ptr;
+    c->cfg.tq_signs = nullptr;                 // the host vector is copied below, not kept
+    if (!compact) c->cfg.wht_len = c->cfg.window_tokens = 0;
+    c->pool_elems = compact ? 0 : size_t(cfg->n_pages) * cfg->n_kv * rl::kv_slice_elems();
+    c->cpool_bytes = compact ? size_t(cfg->n_pages) * cfg->n_kv * rl_kv_compact_page_bytes() : 0;
+    c->win_pages = compact ? ceil_div(cfg->window_tokens, cfg->page_tokens) : 0;
+    c->wpool_elems = size_t(cfg->n_slots) * c->win_pages * cfg->n_kv * rl::kv_slice_elems();
     const rl_attn_decode_params ap = c->attn_params(cfg->max_batch);
     if (int st = attn_check(&ap)) {
         delete c;
         return st;
     }
     c->attn_ws_bytes = attn_plan(&ap, d->sms).total_bytes;
+    if (c->win_pages) {
+        const rl_attn_decode_params wp = c->window_params(cfg->max_batch);
+        c->attn_ws_bytes = std::max(c->attn_ws_bytes, attn_plan(&wp, d->sms).total_bytes);
+    }
     int st = RL_OK;
     if (!st) st = dev_alloc(&c->kv, size_t(c->n_attn) * 2 * c->pool_elems, &c->bytes);
+    if (!st && compact) {
+        st = dev_alloc(&c->kvc, size_t(c->n_attn) * c->cpool_bytes, &c->bytes);
+        if (!st) st = dev_alloc(&c->kvw, size_t(c->n_attn) * 2 * c->wpool_elems, &c->bytes);
+        if (!st) st = dev_alloc(&c->win_table, size_t(cfg->n_slots) * c->win_pages, &c->bytes);
+        if (!st) st = dev_alloc(&c->win_rows, size_t(cfg->max_batch) * c->win_pages, &c->bytes);
+        if (!st) st = dev_alloc(&c->scratch, 2 * size_t(cfg->max_pages_per_seq) * cfg->n_kv * rl::kv_slice_elems(), &c->bytes);
+        if (!st) st = dev_alloc(&c->scratch_table, size_t(cfg->max_pages_per_seq), &c->bytes);
+        if (!st && cfg->wht_len == 256) {
+            st = dev_alloc(&c->d_signs, 256, &c->bytes);
+            if (!st && cudaMemcpy(c->d_signs, cfg->tq_signs, 256 * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+                st = fail(RL_ERR_DEVICE, "copying the sign vector failed");
+        }
+        if (!st) {
+            // identity tables: window pages by slot, scratch pages in order
+            std::vector<int32_t> ids(std::max(size_t(cfg->n_slots) * c->win_pages, size_t(cfg->max_pages_per_seq)));
+            for (size_t i = 0; i < ids.size(); ++i) ids[i] = int32_t(i);
+            if ((c->win_table && cudaMemcpy(c->win_table, ids.data(), size_t(cfg->n_slots) * c->win_pages * sizeof(int32_t),
+                                            cudaMemcpyHostToDevice) != cudaSuccess) ||
+                cudaMemcpy(c->scratch_table, ids.data(), size_t(cfg->max_pages_per_seq) * sizeof(int32_t),
+                           cudaMemcpyHostToDevice) != cudaSuccess)
+                st = fail(RL_ERR_DEVICE, "writing the page tables failed");
+        }
+    }
     if (!st) st = dev_alloc(&c->S, size_t(c->n_delta) * cfg->n_slots * cfg->n_v * cfg->dk * cfg->dv, &c->bytes);
     if (!st) st = dev_alloc(&c->conv, size_t(c->n_delta) * cfg->n_slots * c->conv_dim * cfg->conv_k, &c->bytes);
     if (!st) st = dev_alloc(&c->conv_phase, size_t(c->n_delta) * cfg->n_slots, &c->bytes);
@@ -1326,7 +1428,8 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
 
 void rl_cache_destroy(rl_cache* c) {
     if (!c) return;
-    void* ptrs[] = {c->kv, c->S, c->conv, c->conv_phase, c->attn_ws, c->d_attn_q, c->d_attn_gate, c->d_attn_k,
+    void* ptrs[] = {c->kvc, c->kvw, c->win_table, c->win_rows, c->d_signs, c->scratch, c->scratch_table,
+                    c->kv, c->S, c->conv, c->conv_phase, c->attn_ws, c->d_attn_q, c->d_attn_gate, c->d_attn_k,
                     c->d_attn_v, c->d_attn_o, c->d_delta_qkv, c->d_delta_beta, c->d_delta_g, c->d_delta_o,
                     c->d_conv_w, c->d_page_table, c->d_pos, c->d_slot_ids};
     for (void* p : ptrs)
@@ -1350,10 +1453,18 @@ void rl_cache_destroy(rl_cache* c) {
 
 size_t rl_cache_bytes(const rl_cache* c) { return c ? c->bytes : 0; }
 void* rl_cache_k_pool(rl_cache* c, int i) {
-    return (c && i >= 0 && i < c->n_attn) ? c->kv + (size_t(i) * 2) * c->pool_elems : nullptr;
+    if (!c || i < 0 || i >= c->n_attn) return nullptr;
+    if (c->compact()) return c->kvc + size_t(i) * c->cpool_bytes;
+    return c->kv + (size_t(i) * 2) * c->pool_elems;
 }
 void* rl_cache_v_pool(rl_cache* c, int i) {
-    return (c && i >= 0 && i < c->n_attn) ? c->kv + (size_t(i) * 2 + 1) * c->pool_elems : nullptr;
+    return (c && !c->compact() && i >= 0 && i < c->n_attn) ? c->kv + (size_t(i) * 2 + 1) * c->pool_elems : nullptr;
+}
+void* rl_cache_window_k_pool(rl_cache* c, int i) {
+    return (c && c->win_pages && i >= 0 && i < c->n_attn) ? c->kvw + (size_t(i) * 2) * c->wpool_elems : nullptr;
+}
+void* rl_cache_window_v_pool(rl_cache* c, int i) {
+    return (c && c->win_pages && i >= 0 && i < c->n_attn) ? c->kvw + (size_t(i) * 2 + 1) * c->wpool_elems : nullptr;
 }
 float* rl_cache_state(rl_cache* c, int i) {
     return (c && i >= 0 && i < c->n_delta)
@@ -1384,6 +1495,8 @@ int rl_cache_zero(rl_cache* c, void* stream) {
     if (!c) return fail(RL_ERR_RANGE, "cache is NULL");
     const rl_cache_config& f = c->cfg;
     if (c->kv) RL_CUDA(cudaMemsetAsync(c->kv, 0, size_t(c->n_attn) * 2 * c->pool_elems * sizeof(__half), as_stream(stream)));
+    if (c->kvc) RL_CUDA(cudaMemsetAsync(c->kvc, 0, size_t(c->n_attn) * c->cpool_bytes, as_stream(stream)));
+    if (c->kvw) RL_CUDA(cudaMemsetAsync(c->kvw, 0, size_t(c->n_attn) * 2 * c->wpool_elems * sizeof(__half), as_stream(stream)));
     if (c->S) RL_CUDA(cudaMemsetAsync(c->S, 0, size_t(c->n_delta) * f.n_slots * f.n_v * f.dk * f.dv * sizeof(float), as_stream(stream)));
     if (c->conv) RL_CUDA(cudaMemsetAsync(c->conv, 0, size_t(c->n_delta) * f.n_slots * c->conv_dim * f.conv_k * sizeof(float), as_stream(stream)));
     if (c->conv_phase) RL_CUDA(cudaMemsetAsync(c->conv_phase, 0, size_t(c->n_delta) * f.n_slots * sizeof(int32_t), as_stream(stream)));
@@ -1423,7 +1536,12 @@ int rl_stack_timing(rl_cache* c, float* ms) {
     return RL_OK;
 }
 
-int rl_stack_launches_per_step(const rl_cache* c) { return c ? c->n_attn * 3 + c->n_delta + (c->n_delta ? 1 : 0) : 0; }
+int rl_stack_launches_per_step(const rl_cache* c) {
+    if (!c) return 0;
+    // attention layer: append, decode, merge (+ the window append and one row-table kernel per step with a compact cache)
+    const int per_attn = 3 + ((c->compact() && c->win_pages) ? 1 : 0);
+    return c->n_attn * per_attn + ((c->compact() && c->win_pages && c->n_attn) ? 1 : 0) + c->n_delta + (c->n_delta ? 1 : 0);
+}
 
 static bool same_io(const rl_stack_io& k, const rl_stack_io* io) {
     return k.attn_q == io->attn_q && k.attn_gate == io->attn_gate && k.attn_k == io->attn_k &&
@@ -1431,7 +1549,7 @@ static bool same_io(const rl_stack_io& k, const rl_stack_io* io) {
            k.delta_beta == io->delta_beta && k.delta_g == io->delta_g && k.delta_o == io->delta_o &&
            k.conv_w == io->conv_w && k.page_table == io->page_table && k.pos == io->pos &&
            k.slot_ids == io->slot_ids && k.batch == io->batch && k.attn_ml == io->attn_ml &&
-           k.no_append == io->no_append;
+           k.no_append == io->no_append && k.kv_window_ok == io->kv_window_ok;
 }
 
 namespace {
@@ -1518,10 +1636,45 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
         rl::launch_conv_ring_export(c->conv, c->conv_phase, canon, c->n_delta, f.n_slots, io->slot, c->conv_dim, run);
     for (int L = 0; L < f.n_layers; ++L) {
         if (c->types[L] == RL_LAYER_FULL_ATTENTION) {
-            if (int st = attn_prefill_impl(rl_cache_k_pool(c, ai), rl_cache_v_pool(c, ai), io->page_table_row, aq + ai * q_sz,
-                                           ak + ai * kv_sz, av + ai * kv_sz, io->attn_gate ? io->attn_gate + ai * q_sz : nullptr,
-                                           io->attn_o + ai * q_sz, pl.attn_ws ? attn_ws : nullptr, pl.attn_ws, &pl.ap, run))
-                return st;
+            const float* gate_l = io->attn_gate ? io->attn_gate + ai * q_sz : nullptr;
+            if (!c->compact()) {
+                if (int st = attn_prefill_impl(rl_cache_k_pool(c, ai), rl_cache_v_pool(c, ai), io->page_table_row, aq + ai * q_sz,
+                                               ak + ai * kv_sz, av + ai * kv_sz, gate_l, io->attn_o + ai * q_sz,
+                                               pl.attn_ws ? attn_ws : nullptr, pl.attn_ws, &pl.ap, run))
+                    return st;
+            } else {
+                // the chunk's rows persist in the compact pages; it attends over the F16 window when it ends
+                // inside it, else over F16 scratch pages rebuilt from the compact pages
+                rl_kv_append_params cp;
+                std::memset(&cp, 0, sizeof cp);
+                cp.n_kv = f.n_kv, cp.head_dim = f.head_dim, cp.batch = 1, cp.n_tok = T, cp.page_tokens = f.page_tokens;
+                cp.n_pages = f.n_pages, cp.max_pages_per_seq = f.max_pages_per_seq, cp.pos0 = io->pos0, cp.rows_fp16 = 2;
+                cp.wht_len = f.wht_len;
+                if (int st = rl_kv_compact_append(rl_cache_k_pool(c, ai), io->page_table_row, nullptr, ak + ai * kv_sz,
+                                                  av + ai * kv_sz, c->d_signs, &cp, run))
+                    return st;
+                rl_attn_prefill_params ap = pl.ap;
+                if (io->pos0 + T <= f.window_tokens) {
+                    ap.n_pages = f.n_slots * c->win_pages;
+                    ap.n_table = c->win_pages;
+                    if (int st = attn_prefill_impl(rl_cache_window_k_pool(c, ai), rl_cache_window_v_pool(c, ai),
+                                                   c->win_table + size_t(io->slot) * c->win_pages, aq + ai * q_sz, ak + ai * kv_sz,
+                                                   av + ai * kv_sz, gate_l, io->attn_o + ai * q_sz,
+                                                   pl.attn_ws ? attn_ws : nullptr, pl.attn_ws, &ap, run))
+                        return st;
+                } else {
+                    __half* sk = c->scratch;
+                    __half* sv = c->scratch + size_t(f.max_pages_per_seq) * f.n_kv * rl::kv_slice_elems();
+                    if (int st = rl_kv_compact_to_f16(rl_cache_k_pool(c, ai), io->page_table_row, 0, f.n_pages, sk, sv,
+                                                      c->scratch_table, 0, f.max_pages_per_seq, io->pos0 + T, f.n_kv, f.wht_len,
+                                                      c->d_signs, run))
+                        return st;
+                    ap.n_pages = f.max_pages_per_seq;
+                    if (int st = attn_prefill_impl(sk, sv, c->scratch_table, aq + ai * q_sz, nullptr, nullptr, gate_l,
+                                                   io->attn_o + ai * q_sz, pl.attn_ws ? attn_ws : nullptr, pl.attn_ws, &ap, run))
+                        return st;
+                }
+            }
             ++ai;
         } else {
             float* S = c->S + di * st_elems + io->slot * slot_S;
@@ -1605,6 +1758,7 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
                        (!io->no_append && (!io->attn_k || !io->attn_v)))) ||
         (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
+    if (c->compact() && io->attn_ml) return fail(RL_ERR_UNSUPPORTED, "split-KV partials over the compact cache are offered by rl_attn_decode_partial only");
     if (c->gather.comm && io->attn_ml && c->n_attn && (!c->gather.attn_ml_all || !c->gather.attn_o_final))
         return fail(RL_ERR_RANGE, "split-KV partials need attn_ml_all and attn_o_final in rl_stack_gather");
     if (!c->graph_enabled || c->timing) return stack_decode_layers(c, io, as_stream(stream), false);

@@ -92,8 +92,12 @@ struct KvWriteArgs {
     int batch, n_tok, n_kv, n_pages, max_pages_per_seq;
     int pos0;                    // used when pos == null
     int rows_fp16;               // row element type: 0 fp32 (rounded to nearest even), 1 fp16, 2 bf16
+    int pos_limit;               // > 0: rows at positions >= pos_limit are left out (the F16 window of a compact cache)
 };
 __global__ void kv_write_kernel(KvWriteArgs a);
+// rows[b][j] = slot_ids[b] * pages_per_slot + j: the page-table rows of a step's sequences in a pool
+// where slot s owns pages [s * pages_per_slot, (s + 1) * pages_per_slot); grid (batch), any block
+__global__ void kv_slot_rows_kernel(int32_t* rows, const int32_t* slot_ids, int pages_per_slot, int n_slots, int* err);
 // Read tokens [0, n_tok) of one sequence back as contiguous fp16 [n_tok][n_kv][256].
 __global__ void kv_gather_kernel(const __half* pool, const int32_t* table, __half* out, int n_tok,
                                  int n_kv, int n_pages, int* err);
@@ -103,11 +107,12 @@ struct KvCompactWriteArgs {
     unsigned char* pool;         // [n_pages][n_kv][2] records of kCompactRecordBytes
     const int32_t* page_table;
     const int32_t* pos;          // [batch] or null
-    const float* k_rows;         // [batch][n_tok][n_kv][256] fp32
-    const float* v_rows;
+    const void* k_rows;          // [batch][n_tok][n_kv][256] fp32 (or bf16 when rows_bf16)
+    const void* v_rows;
     const float* signs;          // [256] +-1 (wht_len 256) or null
     int* err;
     int batch, n_tok, n_kv, n_pages, max_pages_per_seq, pos0, wht_len;
+    int rows_bf16;               // rows are bf16 (a prefill chunk's rows), widened exactly before quantising
 };
 __global__ void kv_compact_write_kernel(KvCompactWriteArgs a);
 __global__ void kv_compact_gather_kernel(const unsigned char* pool, const int32_t* table, signed char* k_q,

@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(256) kv_write_kernel(KvWriteArgs a) {
     const int lane = threadIdx.x;
     if (t >= a.n_tok) return;
     const int pos = (a.pos ? a.pos[b] : a.pos0) + t;
+    if (a.pos_limit > 0 && pos >= a.pos_limit) return;
     const int pi = pos / kPageTokens;
     if (pos < 0 || pi >= a.max_pages_per_seq) {
         if (lane == 0) set_err(a.err, DEV_ERR_BAD_LEN);
@@ -75,6 +76,19 @@ kv_gather_kernel(const __half* pool, const int32_t* table, __half* out, int n_to
     const size_t src = (size_t(page) * n_kv + h) * kv_slice_elems() + kv_slice_offset(t % kPageTokens, lane * 8);
     *reinterpret_cast<uint4*>(out + (size_t(t) * n_kv + h) * kHeadDim + lane * 8) =
         *reinterpret_cast<const uint4*>(pool + src);
+}
+
+__global__ void kv_slot_rows_kernel(int32_t* rows, const int32_t* slot_ids, int pages_per_slot, int n_slots, int* err) {
+    griddep_launch();
+    griddep_wait();
+    const int b = blockIdx.x;
+    int slot = slot_ids ? slot_ids[b] : b;
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) set_err(err, DEV_ERR_BAD_SLOT);
+        slot = 0;
+    }
+    for (int j = threadIdx.x; j < pages_per_slot; j += blockDim.x)
+        rows[size_t(b) * pages_per_slot + j] = slot * pages_per_slot + j;
 }
 
 }  // namespace rl

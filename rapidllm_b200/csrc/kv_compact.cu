@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(256) kv_compact_write_kernel(KvCompactWriteArg
     const size_t src = ((size_t(b) * a.n_tok + t) * a.n_kv + h) * kHeadDim;
 
     // ---------------- K: int8 + fp16 scale ----------------
-    const float kx = a.k_rows[src + tid];
+    const float kx = a.rows_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.k_rows)[src + tid])
+                                 : static_cast<const float*>(a.k_rows)[src + tid];
     float amax = fabsf(kx);
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     if (lane == 0) wred[warp] = amax;
@@ -100,7 +101,8 @@ __global__ void __launch_bounds__(256) kv_compact_write_kernel(KvCompactWriteArg
     __syncthreads();
 
     // ---------------- V: signs, Walsh-Hadamard, RMS scale, 3-bit codes ----------------
-    float v = a.v_rows[src + tid];
+    float v = a.rows_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.v_rows)[src + tid])
+                          : static_cast<const float*>(a.v_rows)[src + tid];
     if (a.wht_len == 256 && a.signs) v = v * a.signs[tid];
     v = wht32_in_warp(v, lane);
     xs[tid] = v;
