@@ -547,6 +547,28 @@ int rl_cache_conv_import(rl_cache* c, int delta_index, const float* canon, void*
 /* DualCache::zero (dual_cache.cpp:43-47). */
 int rl_cache_zero(rl_cache* c, void* stream);
 
+/* Optional: the element-wise steps on either side of the operators run inside the step, as the
+ * reference fuses them into its decode kernels (q/gate split + head RMSNorm + partial RoPE before the
+ * attention, cuda_engine.cu:5819-5850; the gate maths before and the gated RMSNorm after the delta
+ * rule, 5644-5653, 4400-4424): rl_attn_qk_prepare, rl_delta_gates, rl_gated_rmsnorm.  The step then
+ * takes the raw projections instead of the prepared tensors.  Indexing as in rl_stack_io. */
+typedef struct rl_stack_glue {
+    const float* attn_qg;        /* [n_attn][batch][n_q][2*256] ([q | gate] per head): replaces attn_q, attn_gate */
+    float* attn_k_raw;           /* [n_attn][batch][n_kv][256] K rows before norm and RoPE, updated in place:
+                                  * replaces attn_k (attn_v is still read from rl_stack_io) */
+    const float* q_norm;         /* [n_attn][256] or NULL */
+    const float* k_norm;         /* [n_attn][256] or NULL */
+    int rotary_dim;              /* 64 */
+    float theta;                 /* 1e7 */
+    float rms_eps;               /* 1e-6 */
+    const float* delta_a;        /* [n_delta][batch][n_v]: with delta_b replaces delta_beta, delta_g */
+    const float* delta_b;
+    const float* A_log;          /* [n_delta][n_v] */
+    const float* dt_bias;        /* [n_delta][n_v] */
+    const float* delta_z;        /* [n_delta][batch][n_v][dv] or NULL: delta_o = gated RMSNorm(o, z) */
+    const float* gnorm;          /* [n_delta][dv] or NULL */
+} rl_stack_glue;
+
 /* Inputs of one decode step of the attention/DeltaNet-only stack.  Arrays are
  * indexed by the layer's index among its kind, then by sequence. */
 typedef struct rl_stack_io {
@@ -577,6 +599,7 @@ typedef struct rl_stack_io {
      * decode_tokens(tokens, poss, B)) asserts that every pos[b] < window_tokens, so the attention
      * layers read the F16 window; 0 = they read the compact pages (always valid). */
     int kv_window_ok;
+    const rl_stack_glue* glue;   /* NULL, or the raw projections and the small weights (device step only) */
 } rl_stack_io;
 
 /* One decode step over layer_types[]: the scheduler loop of

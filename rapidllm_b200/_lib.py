@@ -99,7 +99,15 @@ class StackIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta", "delta_g",
         "delta_o", "conv_w", "page_table", "pos", "slot_ids")] + [
-        ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int), ("kv_window_ok", C.c_int)]
+        ("batch", C.c_int), ("attn_ml", C.c_void_p), ("no_append", C.c_int), ("kv_window_ok", C.c_int),
+        ("glue", C.c_void_p)]
+
+
+class StackGlue(C.Structure):
+    _fields_ = [("attn_qg", C.c_void_p), ("attn_k_raw", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("rotary_dim", C.c_int), ("theta", C.c_float), ("rms_eps", C.c_float),
+                ("delta_a", C.c_void_p), ("delta_b", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p),
+                ("delta_z", C.c_void_p), ("gnorm", C.c_void_p)]
 
 
 class StackGather(C.Structure):

@@ -141,6 +141,21 @@ class HybridCache:
         io = StackIO(batch=batch)
         io.no_append = int(bool(t.get("no_append", False)))
         io.kv_window_ok = int(bool(t.get("kv_window_ok", False)))
+        glue = t.get("glue")
+        if glue is not None:
+            # raw projections and small weights: the element-wise steps run inside the step (rl_stack_glue)
+            g = _lib.StackGlue(rotary_dim=int(glue.get("rotary_dim", 64)), theta=float(glue.get("theta", 1e7)),
+                               rms_eps=float(glue.get("rms_eps", 1e-6)))
+            for name in ("attn_qg", "attn_k_raw", "q_norm", "k_norm", "delta_a", "delta_b", "A_log", "dt_bias",
+                         "delta_z", "gnorm"):
+                x = glue.get(name)
+                if x is None:
+                    continue
+                if not (x.is_cuda and x.is_contiguous() and x.dtype == torch.float32):
+                    raise _lib.RlError(6, f"glue.{name}: need a contiguous fp32 CUDA tensor")
+                setattr(g, name, x.data_ptr())
+            io.glue = C.addressof(g)
+            io._glue_keepalive = g
         for name in ("attn_q", "attn_gate", "attn_k", "attn_v", "attn_o", "delta_qkv", "delta_beta",
                      "delta_g", "delta_o", "conv_w", "page_table", "pos", "slot_ids", "attn_ml"):
             x = t.get(name)

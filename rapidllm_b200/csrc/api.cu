@@ -287,6 +287,10 @@ struct rl_cache {
     float* conv = nullptr;          // [n_delta][n_slots][conv_dim][conv_k] ring windows (gdn_decode.cu)
     int32_t* conv_phase = nullptr;  // [n_delta][n_slots] ring position of each slot's next token
     int* dev_err = nullptr;         // the device error word
+    // scratch of the optional element-wise steps inside the step (rl_stack_glue)
+    float *g_q = nullptr, *g_gate = nullptr;      // [max_batch][n_q][256]
+    float *g_beta = nullptr, *g_g = nullptr;      // [max_batch][n_v]
+    rl_stack_glue gglue = {};       // contents of the glue the captured graph was built with
     void* attn_ws = nullptr;
     size_t attn_ws_bytes = 0;
     size_t bytes = 0;
@@ -395,6 +399,7 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
     // Sharded step: the outputs of the layers since the last exchange are all-gathered on the side
     // stream (one grouped NCCL call), beside the layers that follow; split-KV partials are merged
     // and gated there too, straight out of the gather buffer.
+    const rl_stack_glue* glue = io->glue;
     const rl_stack_gather& gx = c->gather;
     rl::Comm* comm = reinterpret_cast<rl::Comm*>(gx.comm);
     const int n_ranks = comm ? rl::comm_ranks(comm) : 1;
@@ -454,14 +459,26 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             ap.pos_limit = 0;
             void* kp = rl_cache_k_pool(c, ai);
             void* vp = rl_cache_v_pool(c, ai);
-            const float* q_l = io->attn_q + ai * q_sz;
-            const float* gate_l = (io->attn_gate && !io->attn_ml) ? io->attn_gate + ai * q_sz : nullptr;
+            const float* q_l = glue ? c->g_q : io->attn_q + ai * q_sz;
+            const float* gate_l = glue ? (io->attn_ml ? nullptr : c->g_gate)
+                                       : ((io->attn_gate && !io->attn_ml) ? io->attn_gate + ai * q_sz : nullptr);
+            const float* k_new = glue ? glue->attn_k_raw + ai * kv_sz : io->attn_k + ai * kv_sz;
+            if (glue) {
+                rl_attn_qk_prepare_params qp;
+                qp.n_q = f.n_q, qp.n_kv = f.n_kv, qp.head_dim = f.head_dim, qp.rotary_dim = glue->rotary_dim, qp.rows = B;
+                qp.pos0 = 0, qp.theta = glue->theta, qp.eps = glue->rms_eps;
+                if (int st = rl_attn_qk_prepare(glue->attn_qg + size_t(ai) * B * f.n_q * 2 * f.head_dim,
+                                                glue->attn_k_raw + ai * kv_sz,
+                                                glue->q_norm ? glue->q_norm + size_t(ai) * f.head_dim : nullptr,
+                                                glue->k_norm ? glue->k_norm + size_t(ai) * f.head_dim : nullptr, io->pos,
+                                                c->g_q, c->g_gate, &qp, run))
+                    return st;
+            }
             float* ml_l = io->attn_ml ? io->attn_ml + size_t(ai) * B * f.n_q * 2 : nullptr;
             cudaEvent_t after_main = tm ? c->tev[size_t(L) * 4 + 3] : nullptr;
             if (!c->compact()) {
                 if (!io->no_append)
-                    if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
-                                              io->attn_v + ai * kv_sz, &ap, run))
+                    if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, k_new, io->attn_v + ai * kv_sz, &ap, run))
                         return st;
                 mark(L, 1);
                 rl_attn_decode_params dp = c->attn_params(B);
@@ -476,16 +493,15 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
                 void* vw = rl_cache_window_v_pool(c, ai);
                 if (!io->no_append) {
                     ap.wht_len = f.wht_len;
-                    if (int st = rl_kv_compact_append(kp, io->page_table, io->pos, io->attn_k + ai * kv_sz,
-                                                      io->attn_v + ai * kv_sz, c->d_signs, &ap, run))
+                    if (int st = rl_kv_compact_append(kp, io->page_table, io->pos, k_new, io->attn_v + ai * kv_sz, c->d_signs,
+                                                      &ap, run))
                         return st;
                     if (c->win_pages) {
                         rl_kv_append_params wp = ap;
                         wp.n_pages = f.n_slots * c->win_pages;
                         wp.max_pages_per_seq = c->win_pages;
                         wp.pos_limit = f.window_tokens;
-                        if (int st = rl_kv_append(kw, vw, c->win_rows, io->pos, io->attn_k + ai * kv_sz,
-                                                  io->attn_v + ai * kv_sz, &wp, run))
+                        if (int st = rl_kv_append(kw, vw, c->win_rows, io->pos, k_new, io->attn_v + ai * kv_sz, &wp, run))
                             return st;
                     }
                 }
@@ -513,11 +529,23 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             gp.n_slots = f.n_slots;
             gp.head_map = f.head_map;
             gp.eps_l2 = 1e-6f;
+            const float* beta_l = glue ? c->g_beta : io->delta_beta + di * hv_sz;
+            const float* g_l = glue ? c->g_g : io->delta_g + di * hv_sz;
+            if (glue)
+                if (int st = rl_delta_gates(glue->delta_a + di * hv_sz, glue->delta_b + di * hv_sz,
+                                            glue->A_log + size_t(di) * f.n_v, glue->dt_bias + size_t(di) * f.n_v, c->g_beta,
+                                            c->g_g, B, f.n_v, run))
+                    return st;
             if (int st = rl_gdn_decode(c->S + di * st_elems, c->conv + di * cv_elems, c->conv_phase + size_t(di) * f.n_slots,
                                        io->slot_ids, io->delta_qkv + di * qkv_sz,
-                                       io->conv_w + size_t(di) * c->conv_dim * f.conv_k, io->delta_beta + di * hv_sz,
-                                       io->delta_g + di * hv_sz, io->delta_o + di * do_sz, &gp, run))
+                                       io->conv_w + size_t(di) * c->conv_dim * f.conv_k, beta_l, g_l,
+                                       io->delta_o + di * do_sz, &gp, run))
                 return st;
+            if (glue && glue->delta_z)
+                if (int st = rl_gated_rmsnorm(io->delta_o + di * do_sz, glue->delta_z + di * do_sz,
+                                              glue->gnorm ? glue->gnorm + size_t(di) * f.dv : nullptr, io->delta_o + di * do_sz, B,
+                                              f.n_v, f.dv, glue->rms_eps, run))
+                    return st;
             mark(L, 2);
             ++di;
         }
@@ -1411,6 +1439,10 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
     if (!st) st = dev_alloc(&c->S, size_t(c->n_delta) * cfg->n_slots * cfg->n_v * cfg->dk * cfg->dv, &c->bytes);
     if (!st) st = dev_alloc(&c->conv, size_t(c->n_delta) * cfg->n_slots * c->conv_dim * cfg->conv_k, &c->bytes);
     if (!st) st = dev_alloc(&c->conv_phase, size_t(c->n_delta) * cfg->n_slots, &c->bytes);
+    if (!st && c->n_attn) st = dev_alloc(&c->g_q, size_t(cfg->max_batch) * cfg->n_q * cfg->head_dim, &c->bytes);
+    if (!st && c->n_attn) st = dev_alloc(&c->g_gate, size_t(cfg->max_batch) * cfg->n_q * cfg->head_dim, &c->bytes);
+    if (!st && c->n_delta) st = dev_alloc(&c->g_beta, size_t(cfg->max_batch) * cfg->n_v, &c->bytes);
+    if (!st && c->n_delta) st = dev_alloc(&c->g_g, size_t(cfg->max_batch) * cfg->n_v, &c->bytes);
     if (!st) {
         char* ws = nullptr;
         st = dev_alloc(&ws, c->attn_ws_bytes, &c->bytes);
@@ -1428,7 +1460,7 @@ int rl_cache_create(const rl_cache_config* cfg, rl_cache** out) {
 
 void rl_cache_destroy(rl_cache* c) {
     if (!c) return;
-    void* ptrs[] = {c->kvc, c->kvw, c->win_table, c->win_rows, c->d_signs, c->scratch, c->scratch_table,
+    void* ptrs[] = {c->g_q, c->g_gate, c->g_beta, c->g_g, c->kvc, c->kvw, c->win_table, c->win_rows, c->d_signs, c->scratch, c->scratch_table,
                     c->kv, c->S, c->conv, c->conv_phase, c->attn_ws, c->d_attn_q, c->d_attn_gate, c->d_attn_k,
                     c->d_attn_v, c->d_attn_o, c->d_delta_qkv, c->d_delta_beta, c->d_delta_g, c->d_delta_o,
                     c->d_conv_w, c->d_page_table, c->d_pos, c->d_slot_ids};
@@ -1549,7 +1581,7 @@ static bool same_io(const rl_stack_io& k, const rl_stack_io* io) {
            k.delta_beta == io->delta_beta && k.delta_g == io->delta_g && k.delta_o == io->delta_o &&
            k.conv_w == io->conv_w && k.page_table == io->page_table && k.pos == io->pos &&
            k.slot_ids == io->slot_ids && k.batch == io->batch && k.attn_ml == io->attn_ml &&
-           k.no_append == io->no_append && k.kv_window_ok == io->kv_window_ok;
+           k.no_append == io->no_append && k.kv_window_ok == io->kv_window_ok && (k.glue != nullptr) == (io->glue != nullptr);
 }
 
 namespace {
@@ -1754,19 +1786,23 @@ int rl_stack_decode(rl_cache* c, const rl_stack_io* io, void* stream) {
     if (io->batch < 0 || io->batch > c->cfg.max_batch)
         return fail(RL_ERR_RANGE, "batch %d outside [0, max_batch %d]", io->batch, c->cfg.max_batch);
     if (io->batch == 0) return RL_OK;
-    if ((c->n_attn && (!io->attn_q || !io->attn_o || !io->page_table || !io->pos ||
-                       (!io->no_append && (!io->attn_k || !io->attn_v)))) ||
-        (c->n_delta && (!io->delta_qkv || !io->delta_beta || !io->delta_g || !io->delta_o || !io->conv_w)))
+    const rl_stack_glue* gl = io->glue;
+    if ((c->n_attn && (!(gl ? (const void*)gl->attn_qg : (const void*)io->attn_q) || !io->attn_o || !io->page_table || !io->pos ||
+                       (!io->no_append && (!(gl ? (const void*)gl->attn_k_raw : (const void*)io->attn_k) || !io->attn_v)))) ||
+        (c->n_delta && (!io->delta_qkv || !io->delta_o || !io->conv_w ||
+                        (gl ? (!gl->delta_a || !gl->delta_b || !gl->A_log || !gl->dt_bias) : (!io->delta_beta || !io->delta_g)))))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
     if (c->compact() && io->attn_ml) return fail(RL_ERR_UNSUPPORTED, "split-KV partials over the compact cache are offered by rl_attn_decode_partial only");
     if (c->gather.comm && io->attn_ml && c->n_attn && (!c->gather.attn_ml_all || !c->gather.attn_o_final))
         return fail(RL_ERR_RANGE, "split-KV partials need attn_ml_all and attn_o_final in rl_stack_gather");
     if (!c->graph_enabled || c->timing) return stack_decode_layers(c, io, as_stream(stream), false);
-    const bool same = c->gkey_seen > 0 && same_io(c->gkey, io);
+    const bool same = c->gkey_seen > 0 && same_io(c->gkey, io) &&
+                      (!io->glue || std::memcmp(&c->gglue, io->glue, sizeof(rl_stack_glue)) == 0);
     if (same && c->gkey_seen == 2) {
         RL_CUDA(cudaGraphLaunch(c->gexec, as_stream(stream)));
         return RL_OK;
     }
+    if (io->glue) c->gglue = *io->glue;
     if (!same) {
         // first step with this io: run it eagerly (also finishes every lazy set-up outside capture)
         if (c->gexec) {
@@ -1971,8 +2007,8 @@ int rl_stack_decode_host(rl_cache* c, const rl_stack_io* h) {
     if ((c->n_attn && (!h->attn_q || !h->attn_k || !h->attn_v || !h->attn_o || !h->page_table || !h->pos)) ||
         (c->n_delta && (!h->delta_qkv || !h->delta_beta || !h->delta_g || !h->delta_o)))
         return fail(RL_ERR_RANGE, "NULL tensor in rl_stack_io");
-    if (h->attn_ml || h->no_append)
-        return fail(RL_ERR_UNSUPPORTED, "split-KV partials are offered by rl_stack_decode (device pointers) only");
+    if (h->attn_ml || h->no_append || h->glue)
+        return fail(RL_ERR_UNSUPPORTED, "split-KV partials and the fused element-wise steps are offered by rl_stack_decode (device pointers) only");
     if (c->n_delta && !c->d_conv_w) return fail(RL_ERR_RANGE, "call rl_stack_set_conv_w first");
     if (int st = ensure_staging(c)) return st;
     if (c->graph_enabled && !c->timing && !c->host_graph_failed) {

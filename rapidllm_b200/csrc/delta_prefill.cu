@@ -17,14 +17,20 @@
 // (the diagonal of P is included because the reference reads o_t from the updated state).
 //
 // Kernel 1 (delta_chunk_prepare_kernel) computes everything that does not depend on S for
-// all (chunk, value head) pairs in parallel, one CTA each, and writes W, Qg, Kt, V, T, P as fp16
-// tiles already in the 128-byte-swizzled operand format of the tensor cores, 80 KiB per pair.
+// all (chunk, value head) pairs in parallel, one CTA each: W, Kt (each as an fp16 high part and
+// an fp16 residual, ~22 bits together), Qg, P (fp16) as tiles already in the 128-byte-swizzled
+// operand format of the tensor cores, and the product T V in fp32; 120 KiB per pair.
 // Kernel 2 (delta_chunk_scan_kernel), one CTA per value head, walks the chunks in order.
 // Everything is transposed so that the 128 value dims are the MMA M dimension (TMEM lanes):
 // S^T lives in tensor memory in fp32 for the whole sequence, and its fp16 high and low
-// parts (S = hi + lo, ~22 bits) are the tensor-memory A operands of D^T = V^T T^T - S^T W^T
-// and O^T = S^T Qg^T + D^T P^T; D^T (again hi + lo) is the A operand of S^T += D^T Kt.  A
-// chunk's six tiles arrive with ONE linear TMA bulk copy into a two-stage ring.
+// parts are the tensor-memory A operands of -S^T W^T and O^T = S^T Qg^T + D^T P^T;
+// D^T = (T V)^T - S^T W^T is formed by the worker threads (fp32 T V from shared memory plus
+// the accumulator) and, again as hi + lo, is the A operand of S^T += D^T Kt.  Every product
+// that feeds the state (S W^T, D Kt) runs as hi*hi + lo*hi + hi*lo, so the state keeps fp32
+// accuracy; the two that only feed the output (S Qg^T, D P^T) use a single fp16 B operand.
+// The tiles of a chunk arrive by three linear TMA bulk copies into three rings, one per stage
+// of the chunk's work (before D, for D, after D), so that 208 KiB of shared memory hold the
+// current chunk and most of the next.
 #include "kernels.h"
 #include "tcgen05.cuh"
 
@@ -36,10 +42,18 @@ constexpr int kC = 64;                    // chunk length
 constexpr int kD = 128;                   // dk = dv
 constexpr int kTileWide = kC * kD * 2;    // 16 KiB: 64 x 128 fp16
 constexpr int kTileSq = kC * kC * 2;      // 8 KiB: 64 x 64 fp16
-// record of one (chunk, head): byte offsets of the tiles
-constexpr int kOffW = 0, kOffQg = kTileWide, kOffKt = 2 * kTileWide, kOffV = 3 * kTileWide;
-constexpr int kOffT = 4 * kTileWide, kOffP = 4 * kTileWide + kTileSq;
-constexpr int kRecordBytes = 4 * kTileWide + 2 * kTileSq;   // 81920
+// record of one (chunk, head): three parts, one per ring of the scan kernel
+//   part A (needed first):  W hi, W lo, Qg                 48 KiB
+//   part B (for D):         T V, fp32 [64 tokens][128]     32 KiB
+//   part C (after D):       P, Kt hi, Kt lo                40 KiB
+constexpr int kOffW = 0, kOffWlo = kTileWide, kOffQg = 2 * kTileWide;
+constexpr int kPartABytes = 3 * kTileWide;
+constexpr int kOffTV = kPartABytes;
+constexpr int kPartBBytes = kC * kD * 4;
+constexpr int kOffPartC = kOffTV + kPartBBytes;
+constexpr int kOffP = 0, kOffKt = kTileSq, kOffKtlo = kTileSq + kTileWide;      // inside part C
+constexpr int kPartCBytes = kTileSq + 2 * kTileWide;
+constexpr int kRecordBytes = kPartABytes + kPartBBytes + kPartCBytes;            // 122880
 
 // byte offset of element (row, x) in a swizzled tile whose rows are 64-element (128-byte) atoms
 __device__ __forceinline__ int tile_off(int row, int x) {
@@ -75,10 +89,23 @@ struct PrepSmem {
             float tmp[kC][kSq];
         } inv;
     } u;
-    float l[kC][kSq];         // k^_t . k^_i, then in place A (strictly lower part of I + A)
-    float qk[kC][kSq];        // q^_t . k^_i
+    union {
+        struct {
+            float l[kC][kSq];     // k^_t . k^_i, then in place A (strictly lower part of I + A)
+            float qk[kC][kSq];    // q^_t . k^_i
+        } d;
+        float v[kC][kPad];        // the chunk's value rows in fp32, once l and qk are no longer needed
+    } w;
     float G[kC], beta[kC], eg[kC];
 };
+
+// fp32 -> (fp16 high part, fp16 residual), two values per register
+__device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
+    const __half2 hh = __halves2half2(h0, h1);
+    hi = *reinterpret_cast<const uint32_t*>(&hh);
+    lo = pack_h2(x0 - __half2float(h0), x1 - __half2float(h1));
+}
 
 }  // namespace
 
@@ -190,25 +217,17 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
             const int i0 = i_base + 8 * nt + 2 * c;
-            s.l[t_base + g][i0] = ck[nt][0];      s.l[t_base + g][i0 + 1] = ck[nt][1];
-            s.l[t_base + g + 8][i0] = ck[nt][2];  s.l[t_base + g + 8][i0 + 1] = ck[nt][3];
-            s.qk[t_base + g][i0] = cq[nt][0];     s.qk[t_base + g][i0 + 1] = cq[nt][1];
-            s.qk[t_base + g + 8][i0] = cq[nt][2]; s.qk[t_base + g + 8][i0 + 1] = cq[nt][3];
+            s.w.d.l[t_base + g][i0] = ck[nt][0];      s.w.d.l[t_base + g][i0 + 1] = ck[nt][1];
+            s.w.d.l[t_base + g + 8][i0] = ck[nt][2];  s.w.d.l[t_base + g + 8][i0 + 1] = ck[nt][3];
+            s.w.d.qk[t_base + g][i0] = cq[nt][0];     s.w.d.qk[t_base + g][i0 + 1] = cq[nt][1];
+            s.w.d.qk[t_base + g + 8][i0] = cq[nt][2]; s.w.d.qk[t_base + g + 8][i0 + 1] = cq[nt][3];
         }
     }
     __syncthreads();
-    // ---- tiles that need q^: Qg; with it Kt and V (64 x 128, fp16, swizzled) ----
+    // ---- tiles that need q^: Qg (fp16); with it Kt as fp16 hi + lo (64 x 128, swizzled) ----
     const float gC = s.G[kC - 1];
     {
         constexpr int kPer = kC * kD / 4 / kPrepThreads;      // 8 groups of 4 dims per thread
-        float4 vv[kPer];
-#pragma unroll
-        for (int u = 0; u < kPer; ++u) {                      // all value loads in flight together
-            const int idx = tid + u * kPrepThreads;
-            const int t = idx >> 5, d = (idx & 31) * 4;
-            vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < n_tok) vv[u] = *reinterpret_cast<const float4*>(a.v + size_t(t0 + t) * a.v_tok_stride + size_t(h) * kD + d);
-        }
 #pragma unroll
         for (int u = 0; u < kPer; ++u) {
             const int idx = tid + u * kPrepThreads;
@@ -218,9 +237,11 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
             *reinterpret_cast<uint2*>(rec + kOffQg + o) =
                 make_uint2(pack_h2(e * s.u.qn[t][d], e * s.u.qn[t][d + 1]), pack_h2(e * s.u.qn[t][d + 2], e * s.u.qn[t][d + 3]));
             const float kt = expf(gC - s.G[t]);
-            *reinterpret_cast<uint2*>(rec + kOffKt + o) =
-                make_uint2(pack_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1]), pack_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3]));
-            *reinterpret_cast<uint2*>(rec + kOffV + o) = make_uint2(pack_h2(vv[u].x, vv[u].y), pack_h2(vv[u].z, vv[u].w));
+            uint32_t h0, l0, h1, l1;
+            split_h2(kt * s.kn[t][d], kt * s.kn[t][d + 1], h0, l0);
+            split_h2(kt * s.kn[t][d + 2], kt * s.kn[t][d + 3], h1, l1);
+            *reinterpret_cast<uint2*>(rec + kOffPartC + kOffKt + o) = make_uint2(h0, h1);
+            *reinterpret_cast<uint2*>(rec + kOffPartC + kOffKtlo + o) = make_uint2(l0, l1);
         }
     }
     __syncthreads();                                  // q^ is dead from here on: its space becomes m and tmp
@@ -229,7 +250,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
     // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t, in place ----
     for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
         const int t = idx >> 6, i = idx & 63;
-        s.l[t][i] = i < t ? s.beta[t] * expf(s.G[t] - s.G[i]) * s.l[t][i] : 0.f;
+        s.w.d.l[t][i] = i < t ? s.beta[t] * expf(s.G[t] - s.G[i]) * s.w.d.l[t][i] : 0.f;
         m[t][i] = t == i ? 1.f : 0.f;
     }
     __syncthreads();
@@ -239,7 +260,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
     //     block u per thread.  L, T, M below are the block's tiles of s.l, tmp, m.
     {
         const int x = tid >> 4, y = tid & 15;
-#define RL_L(r, c) s.l[bb + (r)][bb + (c)]
+#define RL_L(r, c) s.w.d.l[bb + (r)][bb + (c)]
 #define RL_T(r, c) tmp[bb + (r)][bb + (c)]
 #define RL_M(r, c) m[bb + (r)][bb + (c)]
 #define RL_BLOCKS(BODY)                    \
@@ -267,7 +288,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         for (int u = 0; u < 2; ++u) {
             const int bi = (2 * u + 1) * kB, bj = 2 * u * kB;
             float acc = 0.f;
-            for (int k = 0; k < kB; ++k) acc += s.l[bi + x][bj + k] * m[bj + k][bj + y];
+            for (int k = 0; k < kB; ++k) acc += s.w.d.l[bi + x][bj + k] * m[bj + k][bj + y];
             tmp[bi + x][bj + y] = acc;
         }
         __syncthreads();
@@ -284,7 +305,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         for (int u = 0; u < 4; ++u) {
             const int r = 32 + x2 + 8 * u;
             float acc = 0.f;
-            for (int k = 0; k < 32; ++k) acc += s.l[r][k] * m[k][y2];
+            for (int k = 0; k < 32; ++k) acc += s.w.d.l[r][k] * m[k][y2];
             tmp[r][y2] = acc;
         }
         __syncthreads();
@@ -297,49 +318,84 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         }
         __syncthreads();
     }
-    // ---- tiles: T = M diag(beta), P (64 x 64), fp16, swizzled ----
+    // ---- tile P (64 x 64, fp16, swizzled) ----
     for (int idx = tid; idx < kC * kC / 2; idx += kPrepThreads) {
         const int t = idx >> 5, i = (idx & 31) * 2;
-        *reinterpret_cast<uint32_t*>(rec + kOffT + tile_off(t, i)) =
-            pack_h2(m[t][i] * s.beta[i], m[t][i + 1] * s.beta[i + 1]);
-        const float p0 = i <= t ? expf(s.G[t] - s.G[i]) * s.qk[t][i] : 0.f;
-        const float p1 = i + 1 <= t ? expf(s.G[t] - s.G[i + 1]) * s.qk[t][i + 1] : 0.f;
-        *reinterpret_cast<uint32_t*>(rec + kOffP + tile_off(t, i)) = pack_h2(p0, p1);
+        const float p0 = i <= t ? expf(s.G[t] - s.G[i]) * s.w.d.qk[t][i] : 0.f;
+        const float p1 = i + 1 <= t ? expf(s.G[t] - s.G[i + 1]) * s.w.d.qk[t][i + 1] : 0.f;
+        *reinterpret_cast<uint32_t*>(rec + kOffPartC + kOffP + tile_off(t, i)) = pack_h2(p0, p1);
     }
-    // fold beta_i exp(G_i) into M once: tmp[t][i] = M[t][i] beta_i exp(G_i)
+    // T = M diag(beta) in place, and tmp[t][i] = T[t][i] exp(G_i) for W
     for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
         const int t = idx >> 6, i = idx & 63;
-        tmp[t][i] = m[t][i] * s.beta[i] * s.eg[i];
+        const float tv = m[t][i] * s.beta[i];
+        m[t][i] = tv;
+        tmp[t][i] = tv * s.eg[i];
+    }
+    __syncthreads();                                  // l and qk are dead: their space takes the value rows
+    {
+        constexpr int kPer = kC * kD / 4 / kPrepThreads;
+        float4 vv[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {                      // all value loads in flight together
+            const int idx = tid + u * kPrepThreads;
+            const int t = idx >> 5, d = (idx & 31) * 4;
+            vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < n_tok) vv[u] = *reinterpret_cast<const float4*>(a.v + size_t(t0 + t) * a.v_tok_stride + size_t(h) * kD + d);
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int idx = tid + u * kPrepThreads;
+            const int t = idx >> 5, d = (idx & 31) * 4;
+            *reinterpret_cast<float4*>(&s.w.v[t][d]) = vv[u];
+        }
     }
     __syncthreads();
-    // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] (tmp is zero above the diagonal), 3 x TF32 MMAs: warp w
-    // owns rows 16 (w & 3) .. +15 and dims 64 (w >> 2) .. +63; K steps beyond the rows' diagonal skipped.
+    // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] and (T V)[t][d] = sum_{i<=t} T[t][i] v[i][d] (tmp and T are zero
+    // above the diagonal), 3 x TF32 MMAs: warp w owns rows 16 (w & 3) .. +15 and dims 64 (w >> 2) .. +63; K steps
+    // beyond the rows' diagonal are skipped.  W leaves as fp16 hi + lo tiles, T V as plain fp32 rows.
     {
         const int g = lane >> 2, c = lane & 3;
         const int t_base = (warp & 3) * 16, d_base = (warp >> 2) * 64;
-        float acc[8][4] = {};
-        for (int k0 = 0; k0 < t_base + 16; k0 += 8) {
-            uint32_t ah[4], al[4];
-            split_tf32(tmp[t_base + g][k0 + c], ah[0], al[0]);
-            split_tf32(tmp[t_base + g + 8][k0 + c], ah[1], al[1]);
-            split_tf32(tmp[t_base + g][k0 + c + 4], ah[2], al[2]);
-            split_tf32(tmp[t_base + g + 8][k0 + c + 4], ah[3], al[3]);
-            uint32_t bh[8][2], bl[8][2];
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+            const float (*A)[kSq] = which == 0 ? tmp : m;
+            const float (*B)[kPad] = which == 0 ? s.kn : s.w.v;
+            float acc[8][4] = {};
+            for (int k0 = 0; k0 < t_base + 16; k0 += 8) {
+                uint32_t ah[4], al[4];
+                split_tf32(A[t_base + g][k0 + c], ah[0], al[0]);
+                split_tf32(A[t_base + g + 8][k0 + c], ah[1], al[1]);
+                split_tf32(A[t_base + g][k0 + c + 4], ah[2], al[2]);
+                split_tf32(A[t_base + g + 8][k0 + c + 4], ah[3], al[3]);
+                uint32_t bh[8][2], bl[8][2];
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                split_tf32(s.kn[k0 + c][d_base + 8 * nt + g], bh[nt][0], bl[nt][0]);
-                split_tf32(s.kn[k0 + c + 4][d_base + 8 * nt + g], bh[nt][1], bl[nt][1]);
+                for (int nt = 0; nt < 8; ++nt) {
+                    split_tf32(B[k0 + c][d_base + 8 * nt + g], bh[nt][0], bl[nt][0]);
+                    split_tf32(B[k0 + c + 4][d_base + 8 * nt + g], bh[nt][1], bl[nt][1]);
+                }
+#pragma unroll
+                for (int pass = 0; pass < 3; ++pass)
+#pragma unroll
+                    for (int nt = 0; nt < 8; ++nt) mma_tf32(acc[nt], pass == 0 ? al : ah, pass == 1 ? bl[nt] : bh[nt]);
             }
 #pragma unroll
-            for (int pass = 0; pass < 3; ++pass)
-#pragma unroll
-                for (int nt = 0; nt < 8; ++nt) mma_tf32(acc[nt], pass == 0 ? al : ah, pass == 1 ? bl[nt] : bh[nt]);
-        }
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const int d0 = d_base + 8 * nt + 2 * c;
-            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g, d0)) = pack_h2(acc[nt][0], acc[nt][1]);
-            *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g + 8, d0)) = pack_h2(acc[nt][2], acc[nt][3]);
+            for (int nt = 0; nt < 8; ++nt) {
+                const int d0 = d_base + 8 * nt + 2 * c;
+                if (which == 0) {
+                    uint32_t h0, l0, h1, l1;
+                    split_h2(acc[nt][0], acc[nt][1], h0, l0);
+                    split_h2(acc[nt][2], acc[nt][3], h1, l1);
+                    *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g, d0)) = h0;
+                    *reinterpret_cast<uint32_t*>(rec + kOffWlo + tile_off(t_base + g, d0)) = l0;
+                    *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g + 8, d0)) = h1;
+                    *reinterpret_cast<uint32_t*>(rec + kOffWlo + tile_off(t_base + g + 8, d0)) = l1;
+                } else {
+                    float* tv = reinterpret_cast<float*>(rec + kOffTV);
+                    *reinterpret_cast<float2*>(tv + (t_base + g) * kD + d0) = make_float2(acc[nt][0], acc[nt][1]);
+                    *reinterpret_cast<float2*>(tv + (t_base + g + 8) * kD + d0) = make_float2(acc[nt][2], acc[nt][3]);
+                }
+            }
         }
     }
 }
@@ -351,37 +407,41 @@ int delta_chunk_prepare_threads() { return kPrepThreads; }
 namespace {
 
 constexpr int kScanThreads = 192;         // 4 worker warps (lane = value dim) + loader warp + MMA warp
-constexpr int kScanStages = 2;
+constexpr int kStagesA = 2, kStagesC = 2; // part B (T V) has one buffer: it is read early in a chunk's work
 // tensor memory map (columns); lane = value dim
 constexpr uint32_t kColSt = 0;            // S^T fp32, 128 columns (column = key dim)
 constexpr uint32_t kColShi = 128;         // fp16 pairs: 64 columns
 constexpr uint32_t kColSlo = 192;
-constexpr uint32_t kColD = 256;           // D^T fp32, 64 columns (column = token)
+constexpr uint32_t kColD = 256;           // -S^T W^T fp32, 64 columns (column = token)
 constexpr uint32_t kColO = 320;           // O^T fp32, 64 columns
-constexpr uint32_t kColDhi = 384;         // fp16 pairs: 32 columns
+constexpr uint32_t kColDhi = 384;         // D^T as fp16 pairs: 32 columns
 constexpr uint32_t kColDlo = 416;
 
 struct ScanSmem {
-    alignas(1024) unsigned char rec[kScanStages][kRecordBytes];
-    uint64_t full[kScanStages], empty[kScanStages];
-    uint64_t bar_s, bar_g1, bar_d, bar_g3;
+    alignas(1024) unsigned char pa[kStagesA][kPartABytes];   // W hi, W lo, Qg
+    alignas(1024) unsigned char pc[kStagesC][kPartCBytes];   // P, Kt hi, Kt lo
+    alignas(1024) unsigned char pb[kPartBBytes];             // T V fp32
+    uint64_t full_a[kStagesA], empty_a[kStagesA], full_c[kStagesC], empty_c[kStagesC], full_b, empty_b;
+    uint64_t bar_s;      // workers -> MMA: S hi/lo of the chunk are in tensor memory
+    uint64_t bar_w;      // MMA -> workers: -S^T W^T is complete
+    uint64_t bar_d;      // workers -> MMA: D hi/lo are in tensor memory (and S^T is decayed)
+    uint64_t bar_k;      // MMA -> workers: S^T += D^T Kt is complete
+    uint64_t bar_o;      // MMA -> workers: O^T of the chunk is complete
+    uint64_t bar_oread;  // workers -> MMA: O^T has been read out (its columns may be overwritten)
     uint32_t tmem_base;
     int failed;
 };
-
-// fp32 -> (fp16 high part, fp16 residual), two values per register
-__device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
-    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
-    const __half2 hh = __halves2half2(h0, h1);
-    hi = *reinterpret_cast<const uint32_t*>(&hh);
-    lo = pack_h2(x0 - __half2float(h0), x1 - __half2float(h1));
-}
 
 }  // namespace
 
 // grid (n_v), 192 threads.  o [T][n_v][128]; S [n_v][128][128] fp32 in place (row = key dim).  A launch
 // walks chunks [chunk0, chunk0 + chunks): S is read at its start and written back at its end, so a
 // sequence can be scanned in several launches while later chunks are still being prepared.
+//
+// The chain from one chunk's state to the next is: 24 MMAs (-S^T W^T) -> workers form D -> 12 MMAs
+// (S^T += D^T Kt) -> workers split the new S^T.  The output products (S^T Qg^T before D is known,
+// D^T P^T after the state update) are issued behind the chain's MMAs and read out by the workers while
+// the next chunk's first MMAs run.
 __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     ScanSmem& s = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -391,14 +451,22 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
     float* Sg = a.S + size_t(h) * kD * kD;
 
     if (tid == 0) {
-        for (int i = 0; i < kScanStages; ++i) {
-            mbar_init(&s.full[i], 1);
-            mbar_init(&s.empty[i], 1);
+        for (int i = 0; i < kStagesA; ++i) {
+            mbar_init(&s.full_a[i], 1);
+            mbar_init(&s.empty_a[i], 1);
         }
+        for (int i = 0; i < kStagesC; ++i) {
+            mbar_init(&s.full_c[i], 1);
+            mbar_init(&s.empty_c[i], 1);
+        }
+        mbar_init(&s.full_b, 1);
+        mbar_init(&s.empty_b, 128);
         mbar_init(&s.bar_s, 128);
-        mbar_init(&s.bar_g1, 1);
+        mbar_init(&s.bar_w, 1);
         mbar_init(&s.bar_d, 128);
-        mbar_init(&s.bar_g3, 1);
+        mbar_init(&s.bar_k, 1);
+        mbar_init(&s.bar_o, 1);
+        mbar_init(&s.bar_oread, 128);
         s.failed = 0;
         mbar_fence_init();
     }
@@ -412,71 +480,90 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
         // ------------------------------ loader ------------------------------
         if (lane == 0) {
             for (int c = 0; c < n_chunks; ++c) {
-                const int st = c % kScanStages;
-                if (!mbar_wait(&s.empty[st], ((c / kScanStages) & 1) ^ 1)) { s.failed = 1; break; }
-                mbar_arrive_expect_tx(&s.full[st], kRecordBytes);
-                bulk_g2s(s.rec[st], a.work + (size_t(a.chunk0 + c) * a.n_v + h) * kRecordBytes, kRecordBytes, &s.full[st]);
+                const unsigned char* rec = a.work + (size_t(a.chunk0 + c) * a.n_v + h) * kRecordBytes;
+                const int sa = c % kStagesA, sc = c % kStagesC;
+                if (!mbar_wait(&s.empty_a[sa], ((c / kStagesA) & 1) ^ 1)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.full_a[sa], kPartABytes);
+                bulk_g2s(s.pa[sa], rec, kPartABytes, &s.full_a[sa]);
+                if (!mbar_wait(&s.empty_b, (c & 1) ^ 1)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.full_b, kPartBBytes);
+                bulk_g2s(s.pb, rec + kOffTV, kPartBBytes, &s.full_b);
+                if (!mbar_wait(&s.empty_c[sc], ((c / kStagesC) & 1) ^ 1)) { s.failed = 1; break; }
+                mbar_arrive_expect_tx(&s.full_c[sc], kPartCBytes);
+                bulk_g2s(s.pc[sc], rec + kOffPartC, kPartCBytes, &s.full_c[sc]);
             }
             if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t id_n64 = tc::idesc_f16(128, kC, false, false);           // A K-major/TMEM, B K-major
+            constexpr uint32_t id_n64 = tc::idesc_f16(128, kC, false, false);           // A from TMEM, B K-major
             constexpr uint32_t id_n64_neg = id_n64 | (1u << 13);                        // -A
-            constexpr uint32_t id_vt = tc::idesc_f16(128, kC, true, false);            // A = V^T MN-major (smem)
             constexpr uint32_t id_n128 = tc::idesc_f16(128, kD, false, true);          // B = Kt MN-major
             bool ok = true;
             // Descriptors are built once per ring stage and advanced by constants (their address
             // field counts 16-byte units): the issuing thread must spend only a few instructions
             // per tcgen05.mma or it, not the tensor pipe, sets the pace.
-            uint64_t mn_desc[kScanStages], k_desc[kScanStages];
+            uint64_t a_desc[kStagesA], ck_desc[kStagesC], cmn_desc[kStagesC];
 #pragma unroll
-            for (int i = 0; i < kScanStages; ++i) {
-                mn_desc[i] = tc::smem_desc(smem_u32(s.rec[i]), kC * 128, 1024);   // V^T, Kt: 64 contiguous along M/N
-                k_desc[i] = tc::smem_desc(smem_u32(s.rec[i]), 16, 1024);          // T, W, Qg, P: K-major
+            for (int i = 0; i < kStagesA; ++i) a_desc[i] = tc::smem_desc(smem_u32(s.pa[i]), 16, 1024);        // W, Qg: K-major
+#pragma unroll
+            for (int i = 0; i < kStagesC; ++i) {
+                ck_desc[i] = tc::smem_desc(smem_u32(s.pc[i]), 16, 1024);                                       // P: K-major
+                cmn_desc[i] = tc::smem_desc(smem_u32(s.pc[i]), kC * 128, 1024);                                // Kt: 64 contiguous along N
             }
             const uint32_t t_d = tmem + kColD, t_o = tmem + kColO, t_st = tmem + kColSt;
             const uint32_t t_shi = tmem + kColShi, t_slo = tmem + kColSlo, t_dhi = tmem + kColDhi, t_dlo = tmem + kColDlo;
             for (int c = 0; c < n_chunks && ok; ++c) {
-                const int st = c % kScanStages;
-                if (!mbar_wait(&s.full[st], (c / kScanStages) & 1)) { ok = false; break; }
+                const int sa = c % kStagesA, sc = c % kStagesC;
+                if (!mbar_wait(&s.full_a[sa], (c / kStagesA) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_s, c & 1)) { ok = false; break; }                 // S hi/lo ready
                 tc::fence_after_sync();
-                const uint64_t mn = st == 0 ? mn_desc[0] : mn_desc[1];
-                const uint64_t km = st == 0 ? k_desc[0] : k_desc[1];
-                // D^T = V^T T^T - S^T W^T
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk)                                         // K = 64 tokens i
-                    tc::mma_ss(t_d, mn + uint64_t((kOffV + kk * 2048) >> 4), km + uint64_t((kOffT + kk * 32) >> 4), id_vt,
-                               kk > 0);
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {                                       // K = 128 key dims
-                    const uint64_t bw = km + uint64_t((kOffW + (kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
-                    tc::mma_ts(t_d, t_shi + kk * 8, bw, id_n64_neg, 1);
-                    tc::mma_ts(t_d, t_slo + kk * 8, bw, id_n64_neg, 1);
-                }
-                // O^T = S^T Qg^T (+ D^T P^T below)
+                const uint64_t ka = sa == 0 ? a_desc[0] : a_desc[1];
+                // -S^T W^T with hi*hi + lo*hi + hi*lo: K = 128 key dims in 8 steps
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t bq = km + uint64_t((kOffQg + (kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
+                    const uint64_t off = uint64_t(((kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
+                    const uint64_t bw = ka + uint64_t(kOffW >> 4) + off, bwl = ka + uint64_t(kOffWlo >> 4) + off;
+                    tc::mma_ts(t_d, t_shi + kk * 8, bw, id_n64_neg, kk > 0);
+                    tc::mma_ts(t_d, t_slo + kk * 8, bw, id_n64_neg, 1);
+                    tc::mma_ts(t_d, t_shi + kk * 8, bwl, id_n64_neg, 1);
+                }
+                tc::commit(&s.bar_w);
+                // O^T = S^T Qg^T: behind the chain's MMAs, while the workers form D.  The previous chunk's
+                // O^T must have been read out first.
+                if (c > 0 && !mbar_wait(&s.bar_oread, (c - 1) & 1)) { ok = false; break; }
+                tc::fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t bq = ka + uint64_t((kOffQg + (kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
                     tc::mma_ts(t_o, t_shi + kk * 8, bq, id_n64, kk > 0);
                     tc::mma_ts(t_o, t_slo + kk * 8, bq, id_n64, 1);
                 }
-                tc::commit(&s.bar_g1);
+                tc::commit(&s.empty_a[sa]);                                             // part A free once these are done
+                if (!mbar_wait(&s.full_c[sc], (c / kStagesC) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_d, c & 1)) { ok = false; break; }                 // D hi/lo ready, S^T decayed
                 tc::fence_after_sync();
+                const uint64_t kc = sc == 0 ? ck_desc[0] : ck_desc[1];
+                const uint64_t mc = sc == 0 ? cmn_desc[0] : cmn_desc[1];
+                // S^T += D^T Kt with hi*hi + lo*hi + hi*lo: K = 64 tokens in 4 steps
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {                                       // K = 64 tokens
-                    const uint64_t bp = km + uint64_t((kOffP + kk * 32) >> 4);
-                    tc::mma_ts(t_o, t_dhi + kk * 8, bp, id_n64, 1);
-                    tc::mma_ts(t_o, t_dlo + kk * 8, bp, id_n64, 1);
-                    const uint64_t bk = mn + uint64_t((kOffKt + kk * 2048) >> 4);
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t bk = mc + uint64_t((kOffKt + kk * 2048) >> 4), bkl = mc + uint64_t((kOffKtlo + kk * 2048) >> 4);
                     tc::mma_ts(t_st, t_dhi + kk * 8, bk, id_n128, 1);
                     tc::mma_ts(t_st, t_dlo + kk * 8, bk, id_n128, 1);
+                    tc::mma_ts(t_st, t_dhi + kk * 8, bkl, id_n128, 1);
                 }
-                tc::commit(&s.empty[st]);
-                tc::commit(&s.bar_g3);
+                tc::commit(&s.bar_k);
+                // O^T += D^T P^T
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t bp = kc + uint64_t((kOffP + kk * 32) >> 4);
+                    tc::mma_ts(t_o, t_dhi + kk * 8, bp, id_n64, 1);
+                    tc::mma_ts(t_o, t_dlo + kk * 8, bp, id_n64, 1);
+                }
+                tc::commit(&s.empty_c[sc]);
+                tc::commit(&s.bar_o);
             }
             if (!ok) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
@@ -503,6 +590,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
         tc::tmem_wait_st();
         tc::fence_before_sync();
         mbar_arrive(&s.bar_s);
+        const float* tv = reinterpret_cast<const float*>(s.pb);
         for (int c = 0; c < n_chunks; ++c) {
             const float decay = a.chunk_decay[size_t(a.chunk0 + c) * a.n_v + h];
             // S^T *= exp(G_C) while the tensor core works from the hi/lo copies
@@ -516,42 +604,38 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
                 tc::tmem_st32(lane_addr + kColSt + c0, f);
             }
             tc::tmem_wait_st();
-            if (ok && !mbar_wait(&s.bar_g1, c & 1)) {
+            if (ok && !mbar_wait(&s.full_b, c & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
+            }
+            if (ok && !mbar_wait(&s.bar_w, c & 1)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
             }
             tc::fence_after_sync();
-            // D^T -> hi/lo A operands
+            // D^T = (T V)^T - S^T W^T -> hi/lo A operands; (T V)[t][j] comes from shared memory in fp32
 #pragma unroll 1
             for (int c0 = 0; c0 < kC; c0 += 32) {
                 uint32_t f[32], hi[16], lo[16];
                 tc::tmem_ld32(lane_addr + kColD + c0, f);
                 tc::tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) split_h2(__uint_as_float(f[2 * i]), __uint_as_float(f[2 * i + 1]), hi[i], lo[i]);
+                for (int i = 0; i < 16; ++i)
+                    split_h2(__uint_as_float(f[2 * i]) + tv[(c0 + 2 * i) * kD + j],
+                             __uint_as_float(f[2 * i + 1]) + tv[(c0 + 2 * i + 1) * kD + j], hi[i], lo[i]);
                 tc::tmem_st16(lane_addr + kColDhi + c0 / 2, hi);
                 tc::tmem_st16(lane_addr + kColDlo + c0 / 2, lo);
             }
             tc::tmem_wait_st();
             tc::fence_before_sync();
             mbar_arrive(&s.bar_d);
-            if (ok && !mbar_wait(&s.bar_g3, c & 1)) {
+            mbar_arrive(&s.empty_b);                           // T V has been read: the next chunk's may land
+            if (ok && !mbar_wait(&s.bar_k, c & 1)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
             }
             tc::fence_after_sync();
-            // o[t][h][j] = O^T[j][t]
-            const int t0 = (a.chunk0 + c) * kC;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kC; c0 += 32) {
-                uint32_t f[32];
-                tc::tmem_ld32(lane_addr + kColO + c0, f);
-                tc::tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (ok && t0 + c0 + i < a.T) a.o[(size_t(t0 + c0 + i) * a.n_v + h) * kD + j] = __uint_as_float(f[i]);
-            }
-            // new S^T -> hi/lo for the next chunk (or back to the cache after the last one)
+            // new S^T -> hi/lo for the next chunk (or back to the cache after the last one): on the chain, first
             const bool last = c == n_chunks - 1;
 #pragma unroll 1
             for (int c0 = 0; c0 < kD; c0 += 32) {
@@ -572,6 +656,24 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             tc::tmem_wait_st();
             tc::fence_before_sync();
             if (!last) mbar_arrive(&s.bar_s);
+            // o[t][h][j] = O^T[j][t]: off the chain, while the next chunk's first MMAs run
+            if (ok && !mbar_wait(&s.bar_o, c & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
+            }
+            tc::fence_after_sync();
+            const int t0 = (a.chunk0 + c) * kC;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kC; c0 += 32) {
+                uint32_t f[32];
+                tc::tmem_ld32(lane_addr + kColO + c0, f);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (ok && t0 + c0 + i < a.T) a.o[(size_t(t0 + c0 + i) * a.n_v + h) * kD + j] = __uint_as_float(f[i]);
+            }
+            tc::fence_before_sync();
+            mbar_arrive(&s.bar_oread);
         }
     }
     tc::fence_before_sync();
@@ -581,7 +683,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
 
 size_t delta_chunk_scan_smem_bytes() { return sizeof(ScanSmem) + 1024; }
 int delta_chunk_scan_threads() { return kScanThreads; }
-// per (chunk, head), M = 128, K = 16 each: D^T 4 + 16 and O^T 16 + 8 MMAs of N = 64, S^T 8 MMAs of N = 128
-double delta_chunk_scan_mma_flops() { return 2.0 * 128 * 16 * ((4 + 16 + 16 + 8) * 64 + 8 * 128); }
+// per (chunk, head), M = 128, K = 16 each: -S^T W^T 24 and O^T 16 + 8 MMAs of N = 64, S^T += D^T Kt 12 MMAs of N = 128
+double delta_chunk_scan_mma_flops() { return 2.0 * 128 * 16 * ((24 + 16 + 8) * 64 + 12 * 128); }
 
 }  // namespace rl

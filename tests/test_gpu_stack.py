@@ -312,3 +312,77 @@ def test_config4_full_batch_one_period_of_the_stack(oracle):
         assert rel_l2(cache.state(d).cpu().numpy(), Sr) < 1e-6
         assert np.array_equal(cache.conv_windows(d).cpu().numpy(), Cr)
     cache.close()
+
+
+def test_stack_decode_with_the_element_wise_steps_inside(oracle):
+    """rl_stack_io.glue: the step takes the raw projections and runs q/gate split + head RMSNorm +
+    partial RoPE before the attention, the gate maths before and the gated RMSNorm after the delta
+    rule itself.  One period of layers, two steps (the second replays the captured graph), against
+    the oracle's statements of those steps chained with its operators."""
+    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    gen = torch.Generator().manual_seed(21)
+    lens = [70, 5]
+    B, max_pages, n_pages = 2, 2, 5
+    cache = HybridCache(QWEN35_LAYER_TYPES, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages)
+    A, D = cache.n_attn, cache.n_delta
+    table = torch.tensor([[3, 1], [4, 0]], dtype=torch.int32)
+    k_hist = [torch.randn(n, 4, 256, generator=gen).half() for n in lens]
+    v_hist = [torch.randn(n, 4, 256, generator=gen).half() for n in lens]
+    for b in range(B):
+        ops.kv_append(cache.k_pool(0), cache.v_pool(0), table[b].cuda(), k_hist[b].cuda(), v_hist[b].cuda(), pos0=0)
+    S0 = [torch.randn(B, 48, 128, 128, generator=gen) * 0.02 for _ in range(D)]
+    C0 = [torch.randn(B, cache.conv_dim, 4, generator=gen) for _ in range(D)]
+    for d in range(D):
+        cache.state(d).copy_(S0[d])
+        cache.set_conv_windows(d, C0[d])
+    w = {"q_norm": torch.randn(A, 256, generator=gen) * 0.1, "k_norm": torch.randn(A, 256, generator=gen) * 0.1,
+         "A_log": torch.randn(D, 48, generator=gen) * 0.3, "dt_bias": torch.randn(D, 48, generator=gen) * 0.3,
+         "gnorm": 1.0 + torch.randn(D, 128, generator=gen) * 0.1, "conv_w": torch.randn(D, cache.conv_dim, 4, generator=gen) * 0.5}
+    Sr = [x.numpy().copy() for x in S0]
+    Cr = [x.numpy().copy() for x in C0]
+    dev_fixed = {n: x.cuda() for n, x in w.items()}
+    sh = cache.io_shapes(B)
+    raw = {"attn_qg": torch.empty(A, B, 24, 512).cuda(), "attn_k_raw": torch.empty(A, B, 4, 256).cuda(),
+           "delta_a": torch.empty(D, B, 48).cuda(), "delta_b": torch.empty(D, B, 48).cuda(),
+           "delta_z": torch.empty(D, B, 48, 128).cuda()}
+    dev = {"attn_v": torch.empty(sh["attn_v"]).cuda(), "delta_qkv": torch.empty(sh["delta_qkv"]).cuda(),
+           "attn_o": torch.zeros(sh["attn_o"]).cuda(), "delta_o": torch.zeros(sh["delta_o"]).cuda(),
+           "conv_w": dev_fixed["conv_w"], "page_table": table.cuda(), "pos": torch.tensor(lens, dtype=torch.int32).cuda()}
+    dev["glue"] = dict(raw, q_norm=dev_fixed["q_norm"], k_norm=dev_fixed["k_norm"], A_log=dev_fixed["A_log"],
+                       dt_bias=dev_fixed["dt_bias"], gnorm=dev_fixed["gnorm"], rotary_dim=64, theta=1e7, rms_eps=1e-6)
+    kh = [[k_hist[b].float().numpy()] for b in range(B)]
+    vh = [[v_hist[b].float().numpy()] for b in range(B)]
+    nk = 16 * 128
+    for step in range(3):
+        t = {"attn_qg": torch.randn(A, B, 24, 512, generator=gen), "attn_k_raw": torch.randn(A, B, 4, 256, generator=gen),
+             "attn_v": torch.randn(A, B, 4, 256, generator=gen), "delta_qkv": torch.randn(D, B, cache.conv_dim, generator=gen),
+             "delta_a": torch.randn(D, B, 48, generator=gen), "delta_b": torch.randn(D, B, 48, generator=gen),
+             "delta_z": torch.randn(D, B, 48, 128, generator=gen)}
+        for n, x in t.items():
+            (raw[n] if n in raw else dev[n]).copy_(x)          # same device tensors: the captured graph stays valid
+        if step:
+            dev["pos"] += 1
+        cache.decode(dev, B)
+        _lib.check_device()
+        attn_o, delta_o = dev["attn_o"].cpu().numpy(), dev["delta_o"].cpu().numpy()
+        for b in range(B):
+            pos = lens[b] + step
+            q, gate, k = oracle.attn_qk_prepare(t["attn_qg"][0, b].numpy(), t["attn_k_raw"][0, b].numpy(),
+                                                w["q_norm"][0].numpy(), w["k_norm"][0].numpy(), pos)
+            kh[b].append(torch.from_numpy(k).half().float().numpy()[None])
+            vh[b].append(t["attn_v"][0, b].half().float().numpy()[None])
+            ref = oracle.gated_attn_decode(q, np.concatenate(kh[b]), np.concatenate(vh[b]), gate)
+            assert np.abs(attn_o[0, b] - ref).max() <= ATTN_MAX_ABS and rel_l2(attn_o[0, b], ref) <= ATTN_REL_L2, (step, b)
+        for d in range(D):
+            for b in range(B):
+                beta, g = oracle.delta_gates(t["delta_a"][d, b].numpy(), t["delta_b"][d, b].numpy(), w["A_log"][d].numpy(),
+                                             w["dt_bias"][d].numpy())
+                mixed = oracle.conv1d_update(t["delta_qkv"][d, b].numpy(), w["conv_w"][d].numpy(), Cr[d][b])
+                q = oracle.repeat_heads(mixed[:nk].reshape(16, 128), 48)
+                k = oracle.repeat_heads(mixed[nk:2 * nk].reshape(16, 128), 48)
+                o = oracle.delta_step(Sr[d][b], q, k, mixed[2 * nk:].reshape(48, 128), beta, g)
+                ref = oracle.gated_rmsnorm(o.reshape(-1), t["delta_z"][d, b].numpy().reshape(-1), w["gnorm"][d].numpy()).reshape(48, 128)
+                assert np.abs(delta_o[d, b] - ref).max() <= 2e-4, (step, d, b, np.abs(delta_o[d, b] - ref).max())
+            assert rel_l2(cache.state(d).cpu().numpy(), Sr[d]) < 1e-6
+    cache.close()

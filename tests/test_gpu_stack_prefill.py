@@ -9,7 +9,8 @@ from helpers import ATTN_MAX_ABS, ATTN_REL_L2, rel_l2, softplus
 
 pytestmark = pytest.mark.gpu
 
-CHUNKED_REL_L2 = 1e-3
+CHUNKED_REL_L2 = 1e-3      # outputs of the chunked form (fp16 operands on the output products)
+STATE_REL_L2 = 1e-5        # its FP32 state
 
 
 def _chunk_inputs(cache, T, gen):
@@ -77,7 +78,7 @@ def test_prompt_in_chunks_then_decode(oracle, head_map_name):
             o[tok] = oracle.delta_step(S, q, k, v, cat["delta_beta"][d, tok].numpy(), cat["delta_g"][d, tok].numpy())
         # the chunked form passes operands through fp16 hi + lo pairs: the tolerance of its own test
         assert rel_l2(got["delta_o"][d], o) <= CHUNKED_REL_L2, (d, rel_l2(got["delta_o"][d], o))
-        assert rel_l2(cache.state(d)[slot].cpu().numpy(), S) <= CHUNKED_REL_L2
+        assert rel_l2(cache.state(d)[slot].cpu().numpy(), S) <= STATE_REL_L2
         assert np.abs(cache.conv_windows(d)[slot].cpu().numpy() - cs).max() == 0.0
         S_ref.append(S)
         C_ref.append(cs)
