@@ -91,6 +91,8 @@ int dev_info(DevInfo** out) {
                                      int(rl::gdn_decode_stream_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::delta_chunk_prepare_smem_bytes())));
+        RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(rl::delta_chunk_prepare_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::delta_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(rl::delta_chunk_scan_smem_bytes())));
         RL_CUDA(cudaFuncSetAttribute(rl::attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1112,7 +1114,8 @@ int rl_delta_gates(const float* a, const float* b, const float* A_log, const flo
 size_t rl_delta_chunk_workspace_bytes(const rl_delta_chunk_params* p) {
     if (delta_chunk_check(p)) return 0;
     const size_t n_chunks = (size_t(p->seq) + 63) / 64;
-    return align_up(n_chunks * p->n_v * rl::delta_chunk_record_bytes(), 256) + align_up(n_chunks * p->n_v * sizeof(float), 256);
+    return align_up(n_chunks * p->n_v * rl::delta_chunk_record_bytes(), 256) + align_up(n_chunks * p->n_v * sizeof(float), 256) +
+           align_up(n_chunks * p->n_qk * rl::delta_chunk_keys_bytes(), 256);
 }
 
 double rl_delta_chunk_mma_flops(void) { return rl::delta_chunk_scan_mma_flops(); }
@@ -1141,6 +1144,7 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     a.o = o;
     a.work = static_cast<unsigned char*>(workspace);
     a.chunk_decay = reinterpret_cast<float*>(a.work + align_up(size_t(n_chunks) * p->n_v * rl::delta_chunk_record_bytes(), 256));
+    a.keys = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(a.chunk_decay) + align_up(size_t(n_chunks) * p->n_v * sizeof(float), 256));
     a.err = d->err_ptr;
     a.T = p->seq;
     a.n_v = p->n_v;
@@ -1159,6 +1163,8 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     auto prepare = [&](int c0, int n, cudaStream_t st) {
         a.chunk0 = c0;
         a.chunks = n;
+        rl::delta_chunk_keys_kernel<<<dim3(n, p->n_qk), rl::delta_chunk_prepare_threads(),
+                                      rl::delta_chunk_prepare_smem_bytes(), st>>>(a);
         rl::delta_chunk_prepare_kernel<<<dim3(n, p->n_v), rl::delta_chunk_prepare_threads(),
                                          rl::delta_chunk_prepare_smem_bytes(), st>>>(a);
     };

@@ -111,32 +111,20 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint3
 
 size_t delta_chunk_record_bytes() { return kRecordBytes; }
 
-// grid (n_chunks, n_v), 256 threads: one CTA per chunk and value head.  98 KB of shared memory, so
-// two CTAs share an SM and hide each other's barriers; the dot products k^.k^ and q^.k^ are
-// recomputed by the value heads that share a key head (cheap next to the latency they hide).
-__global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(DeltaChunkArgs a) {
+// What a chunk's value heads share: per (chunk, key head) the normalised keys and queries and their
+// dot products.  Record: k^ [64][128], q^ [64][128], k^.k^ [64][64], q^.k^ [64][64], fp32.
+constexpr int kKeysFloats = 2 * kC * kD + 2 * kC * kC;
+
+// grid (n_chunks, n_qk), 256 threads: l2 norms and the two 64 x 64 x 128 products once per key head
+// (the value heads that share it, 3 in qwen3_5, read the result instead of recomputing it).
+__global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
-    const int chunk = a.chunk0 + blockIdx.x, h = blockIdx.y;
+    const int chunk = a.chunk0 + blockIdx.x, hs = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rep = a.head_map == 0 ? 1 : a.n_v / a.n_qk;
-    const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
     const int t0 = chunk * kC;
     const int n_tok = min(kC, a.T - t0);
-    unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
-
-    // ---- cumulative log decay, beta (needed by every tile) ----
-    if (tid < kC) {
-        const bool live = tid < n_tok;
-        s.beta[tid] = live ? a.beta[size_t(t0 + tid) * a.n_v + h] : 0.f;
-        float gl = live ? a.g_log[size_t(t0 + tid) * a.n_v + h] : 0.f;
-        // inclusive scan over 64 values held by two warps
-        for (int off = 1; off < 32; off <<= 1) {
-            const float o = __shfl_up_sync(0xffffffffu, gl, off);
-            if (lane >= off) gl += o;
-        }
-        s.G[tid] = gl;
-    }
+    float* rec = a.keys + (size_t(chunk) * a.n_qk + hs) * kKeysFloats;
     // ---- l2 norms (double accumulators as ops::l2norm); padded tokens are all zero.  A warp owns
     // 8 tokens; all 16 row loads are issued before the first reduction so their latencies overlap ----
     {
@@ -171,10 +159,6 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         }
     }
     __syncthreads();
-    if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
-    __syncthreads();
-    if (tid < kC) s.eg[tid] = expf(s.G[tid]);
-    if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
     // ---- k^.k^ and q^.k^ on the tensor cores (3 x TF32 = fp32 accuracy): warp w owns rows
     // 16 (w & 3) .. +15 and columns 32 (w >> 2) .. +31; column tiles entirely above the diagonal
     // are skipped (and zero-filled, nobody reads more than their zero) ----
@@ -223,6 +207,65 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
             s.w.d.qk[t_base + g + 8][i0] = cq[nt][2]; s.w.d.qk[t_base + g + 8][i0 + 1] = cq[nt][3];
         }
     }
+    __syncthreads();
+    __syncthreads();
+    // rows out, unpadded
+    for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
+        const int t = idx >> 5, d = (idx & 31) * 4;
+        *reinterpret_cast<float4*>(rec + t * kD + d) = *reinterpret_cast<const float4*>(&s.kn[t][d]);
+        *reinterpret_cast<float4*>(rec + kC * kD + t * kD + d) = *reinterpret_cast<const float4*>(&s.u.qn[t][d]);
+    }
+    for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
+        const int t = idx >> 4, i = (idx & 15) * 4;
+        *reinterpret_cast<float4*>(rec + 2 * kC * kD + t * kC + i) = *reinterpret_cast<const float4*>(&s.w.d.l[t][i]);
+        *reinterpret_cast<float4*>(rec + 2 * kC * kD + kC * kC + t * kC + i) = *reinterpret_cast<const float4*>(&s.w.d.qk[t][i]);
+    }
+}
+
+// grid (n_chunks, n_v), 256 threads: one CTA per chunk and value head.  103 KB of shared memory, so
+// two CTAs share an SM and hide each other's barriers.
+__global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(DeltaChunkArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
+    const int chunk = a.chunk0 + blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rep = a.head_map == 0 ? 1 : a.n_v / a.n_qk;
+    const int hs = a.head_map == 0 ? h : (a.head_map == 1 ? h / rep : h % a.n_qk);
+    const int t0 = chunk * kC;
+    const int n_tok = min(kC, a.T - t0);
+    unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
+
+    // ---- cumulative log decay, beta (needed by every tile) ----
+    if (tid < kC) {
+        const bool live = tid < n_tok;
+        s.beta[tid] = live ? a.beta[size_t(t0 + tid) * a.n_v + h] : 0.f;
+        float gl = live ? a.g_log[size_t(t0 + tid) * a.n_v + h] : 0.f;
+        // inclusive scan over 64 values held by two warps
+        for (int off = 1; off < 32; off <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, gl, off);
+            if (lane >= off) gl += o;
+        }
+        s.G[tid] = gl;
+    }
+    // ---- what the key head's pass left: k^, q^, k^.k^, q^.k^ ----
+    {
+        const float* keys = a.keys + (size_t(chunk) * a.n_qk + hs) * kKeysFloats;
+        for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
+            const int t = idx >> 5, d = (idx & 31) * 4;
+            *reinterpret_cast<float4*>(&s.kn[t][d]) = *reinterpret_cast<const float4*>(keys + t * kD + d);
+            *reinterpret_cast<float4*>(&s.u.qn[t][d]) = *reinterpret_cast<const float4*>(keys + kC * kD + t * kD + d);
+        }
+        for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
+            const int t = idx >> 4, i = (idx & 15) * 4;
+            *reinterpret_cast<float4*>(&s.w.d.l[t][i]) = *reinterpret_cast<const float4*>(keys + 2 * kC * kD + t * kC + i);
+            *reinterpret_cast<float4*>(&s.w.d.qk[t][i]) = *reinterpret_cast<const float4*>(keys + 2 * kC * kD + kC * kC + t * kC + i);
+        }
+    }
+    __syncthreads();
+    if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
+    __syncthreads();
+    if (tid < kC) s.eg[tid] = expf(s.G[tid]);
+    if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
     __syncthreads();
     // ---- tiles that need q^: Qg (fp16); with it Kt as fp16 hi + lo (64 x 128, swizzled) ----
     const float gC = s.G[kC - 1];
@@ -401,6 +444,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
 }
 
 size_t delta_chunk_prepare_smem_bytes() { return sizeof(PrepSmem); }
+size_t delta_chunk_keys_bytes() { return size_t(kKeysFloats) * sizeof(float); }
 int delta_chunk_prepare_threads() { return kPrepThreads; }
 
 // ================================================================================================

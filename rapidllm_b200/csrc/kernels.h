@@ -219,13 +219,16 @@ struct DeltaChunkArgs {
     float* o;                    // [T][n_v][128]
     unsigned char* work;         // [n_chunks][n_v] records of delta_chunk_record_bytes()
     float* chunk_decay;          // [n_chunks][n_v]
+    float* keys;                 // [n_chunks][n_qk] records of delta_chunk_keys_bytes(): what a key head's value heads share
     int* err;
     int T, n_v, n_qk, head_map;
     float eps_l2;
     long long qk_tok_stride, v_tok_stride;   // floats between tokens in q/k and in v
     int chunk0, chunks;          // this launch covers chunks [chunk0, chunk0 + chunks) of the T tokens
 };
+__global__ void delta_chunk_keys_kernel(DeltaChunkArgs a);
 __global__ void delta_chunk_prepare_kernel(DeltaChunkArgs a);
+size_t delta_chunk_keys_bytes();
 __global__ void delta_chunk_scan_kernel(DeltaChunkArgs a);
 size_t delta_chunk_record_bytes();
 size_t delta_chunk_prepare_smem_bytes();
