@@ -451,7 +451,7 @@ int delta_chunk_prepare_threads() { return kPrepThreads; }
 namespace {
 
 constexpr int kScanThreads = 192;         // 4 worker warps (lane = value dim) + loader warp + MMA warp
-constexpr int kStagesA = 2, kStagesC = 2; // part B (T V) has one buffer: it is read early in a chunk's work
+constexpr int kStagesA = 1, kStagesC = 1;
 // tensor memory map (columns); lane = value dim
 constexpr uint32_t kColSt = 0;            // S^T fp32, 128 columns (column = key dim)
 constexpr uint32_t kColShi = 128;         // fp16 pairs: 64 columns
@@ -468,7 +468,7 @@ struct ScanSmem {
     uint64_t full_a[kStagesA], empty_a[kStagesA], full_c[kStagesC], empty_c[kStagesC], full_b, empty_b;
     uint64_t bar_s;      // workers -> MMA: S hi/lo of the chunk are in tensor memory
     uint64_t bar_w;      // MMA -> workers: -S^T W^T is complete
-    uint64_t bar_d;      // workers -> MMA: D hi/lo are in tensor memory (and S^T is decayed)
+    uint64_t bar_d;      // workers -> MMA: D hi/lo are in tensor memory
     uint64_t bar_k;      // MMA -> workers: S^T += D^T Kt is complete
     uint64_t bar_o;      // MMA -> workers: O^T of the chunk is complete
     uint64_t bar_oread;  // workers -> MMA: O^T has been read out (its columns may be overwritten)
@@ -563,7 +563,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
                 if (!mbar_wait(&s.full_a[sa], (c / kStagesA) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_s, c & 1)) { ok = false; break; }                 // S hi/lo ready
                 tc::fence_after_sync();
-                const uint64_t ka = sa == 0 ? a_desc[0] : a_desc[1];
+                const uint64_t ka = a_desc[kStagesA > 1 ? sa : 0];
                 // -S^T W^T with hi*hi + lo*hi + hi*lo: K = 128 key dims in 8 steps
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
@@ -588,8 +588,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
                 if (!mbar_wait(&s.full_c[sc], (c / kStagesC) & 1)) { ok = false; break; }
                 if (!mbar_wait(&s.bar_d, c & 1)) { ok = false; break; }                 // D hi/lo ready, S^T decayed
                 tc::fence_after_sync();
-                const uint64_t kc = sc == 0 ? ck_desc[0] : ck_desc[1];
-                const uint64_t mc = sc == 0 ? cmn_desc[0] : cmn_desc[1];
+                const uint64_t kc = ck_desc[kStagesC > 1 ? sc : 0];
+                const uint64_t mc = cmn_desc[kStagesC > 1 ? sc : 0];
                 // S^T += D^T Kt with hi*hi + lo*hi + hi*lo: K = 64 tokens in 4 steps
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
@@ -616,38 +616,37 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
         }
     } else {
         // ------------------------------ workers: thread = value dim j = TMEM lane ------------------------------
+        // Every pass over tensor memory issues all its loads before it waits once, so a pass costs one
+        // load latency, not one per 32 columns.
         const int j = tid;
         const uint32_t lane_addr = tmem + (uint32_t(warp * 32) << 16);
         bool ok = true;
-        // S_0^T into tensor memory (fp32 and hi/lo): column i of lane j = S[i][j]
+        // S_0^T into tensor memory: hi/lo of S_0 for the first chunk's products, and S_0 exp(G_C) of the
+        // first chunk as the accumulator S^T += D^T Kt adds to.  Column i of lane j = S[i][j].
+        {
+            const float decay0 = a.chunk_decay[size_t(a.chunk0) * a.n_v + h];
 #pragma unroll 1
-        for (int c0 = 0; c0 < kD; c0 += 32) {
-            uint32_t f[32], hi[16], lo[16];
+            for (int c0 = 0; c0 < kD; c0 += 32) {
+                uint32_t f[32], hi[16], lo[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = __float_as_uint(Sg[size_t(c0 + i) * kD + j]);
+                for (int i = 0; i < 32; ++i) f[i] = __float_as_uint(Sg[size_t(c0 + i) * kD + j]);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) split_h2(__uint_as_float(f[2 * i]), __uint_as_float(f[2 * i + 1]), hi[i], lo[i]);
-            tc::tmem_st32(lane_addr + kColSt + c0, f);
-            tc::tmem_st16(lane_addr + kColShi + c0 / 2, hi);
-            tc::tmem_st16(lane_addr + kColSlo + c0 / 2, lo);
+                for (int i = 0; i < 16; ++i) split_h2(__uint_as_float(f[2 * i]), __uint_as_float(f[2 * i + 1]), hi[i], lo[i]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) f[i] = __float_as_uint(__uint_as_float(f[i]) * decay0);
+                tc::tmem_st32(lane_addr + kColSt + c0, f);
+                tc::tmem_st16(lane_addr + kColShi + c0 / 2, hi);
+                tc::tmem_st16(lane_addr + kColSlo + c0 / 2, lo);
+            }
         }
         tc::tmem_wait_st();
         tc::fence_before_sync();
         mbar_arrive(&s.bar_s);
         const float* tv = reinterpret_cast<const float*>(s.pb);
         for (int c = 0; c < n_chunks; ++c) {
-            const float decay = a.chunk_decay[size_t(a.chunk0 + c) * a.n_v + h];
-            // S^T *= exp(G_C) while the tensor core works from the hi/lo copies
-#pragma unroll 1
-            for (int c0 = 0; c0 < kD; c0 += 32) {
-                uint32_t f[32];
-                tc::tmem_ld32(lane_addr + kColSt + c0, f);
-                tc::tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) f[i] = __float_as_uint(__uint_as_float(f[i]) * decay);
-                tc::tmem_st32(lane_addr + kColSt + c0, f);
-            }
-            tc::tmem_wait_st();
+            const bool last = c == n_chunks - 1;
+            // exp(G_C) of the NEXT chunk: folded into the pass that splits the new state
+            const float next_decay = last ? 1.f : a.chunk_decay[size_t(a.chunk0 + c + 1) * a.n_v + h];
             if (ok && !mbar_wait(&s.full_b, c & 1)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
@@ -658,17 +657,21 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             }
             tc::fence_after_sync();
             // D^T = (T V)^T - S^T W^T -> hi/lo A operands; (T V)[t][j] comes from shared memory in fp32
-#pragma unroll 1
-            for (int c0 = 0; c0 < kC; c0 += 32) {
-                uint32_t f[32], hi[16], lo[16];
-                tc::tmem_ld32(lane_addr + kColD + c0, f);
+            {
+                uint32_t f[2][32];
+                tc::tmem_ld32(lane_addr + kColD, f[0]);
+                tc::tmem_ld32(lane_addr + kColD + 32, f[1]);
                 tc::tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    split_h2(__uint_as_float(f[2 * i]) + tv[(c0 + 2 * i) * kD + j],
-                             __uint_as_float(f[2 * i + 1]) + tv[(c0 + 2 * i + 1) * kD + j], hi[i], lo[i]);
-                tc::tmem_st16(lane_addr + kColDhi + c0 / 2, hi);
-                tc::tmem_st16(lane_addr + kColDlo + c0 / 2, lo);
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        split_h2(__uint_as_float(f[q][2 * i]) + tv[(32 * q + 2 * i) * kD + j],
+                                 __uint_as_float(f[q][2 * i + 1]) + tv[(32 * q + 2 * i + 1) * kD + j], hi[i], lo[i]);
+                    tc::tmem_st16(lane_addr + kColDhi + 16 * q, hi);
+                    tc::tmem_st16(lane_addr + kColDlo + 16 * q, lo);
+                }
             }
             tc::tmem_wait_st();
             tc::fence_before_sync();
@@ -679,25 +682,36 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
                 ok = false;
             }
             tc::fence_after_sync();
-            // new S^T -> hi/lo for the next chunk (or back to the cache after the last one): on the chain, first
-            const bool last = c == n_chunks - 1;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kD; c0 += 32) {
-                uint32_t f[32], hi[16], lo[16];
-                tc::tmem_ld32(lane_addr + kColSt + c0, f);
+            // the new S^T: hi/lo for the next chunk's products and, times the next chunk's exp(G_C), the
+            // accumulator its state update adds to (or back to the cache after the last chunk)
+            {
+                uint32_t f[4][32];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tc::tmem_ld32(lane_addr + kColSt + 32 * q, f[q]);
                 tc::tmem_wait_ld();
                 if (last) {
-                    if (ok && !s.failed)
+                    if (ok && !s.failed) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) Sg[size_t(c0 + i) * kD + j] = __uint_as_float(f[i]);
+                        for (int q = 0; q < 4; ++q)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) Sg[size_t(32 * q + i) * kD + j] = __uint_as_float(f[q][i]);
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) split_h2(__uint_as_float(f[2 * i]), __uint_as_float(f[2 * i + 1]), hi[i], lo[i]);
-                    tc::tmem_st16(lane_addr + kColShi + c0 / 2, hi);
-                    tc::tmem_st16(lane_addr + kColSlo + c0 / 2, lo);
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t hi[16], lo[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            split_h2(__uint_as_float(f[q][2 * i]), __uint_as_float(f[q][2 * i + 1]), hi[i], lo[i]);
+                        tc::tmem_st16(lane_addr + kColShi + 16 * q, hi);
+                        tc::tmem_st16(lane_addr + kColSlo + 16 * q, lo);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[q][i] = __float_as_uint(__uint_as_float(f[q][i]) * next_decay);
+                        tc::tmem_st32(lane_addr + kColSt + 32 * q, f[q]);
+                    }
+                    tc::tmem_wait_st();
                 }
             }
-            tc::tmem_wait_st();
             tc::fence_before_sync();
             if (!last) mbar_arrive(&s.bar_s);
             // o[t][h][j] = O^T[j][t]: off the chain, while the next chunk's first MMAs run
@@ -707,17 +721,19 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             }
             tc::fence_after_sync();
             const int t0 = (a.chunk0 + c) * kC;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kC; c0 += 32) {
-                uint32_t f[32];
-                tc::tmem_ld32(lane_addr + kColO + c0, f);
+            {
+                uint32_t f[2][32];
+                tc::tmem_ld32(lane_addr + kColO, f[0]);
+                tc::tmem_ld32(lane_addr + kColO + 32, f[1]);
                 tc::tmem_wait_ld();
+                tc::fence_before_sync();
+                mbar_arrive(&s.bar_oread);                     // O^T is in registers: its columns may be overwritten
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (ok && t0 + c0 + i < a.T) a.o[(size_t(t0 + c0 + i) * a.n_v + h) * kD + j] = __uint_as_float(f[i]);
+                for (int q = 0; q < 2; ++q)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (ok && t0 + 32 * q + i < a.T) a.o[(size_t(t0 + 32 * q + i) * a.n_v + h) * kD + j] = __uint_as_float(f[q][i]);
             }
-            tc::fence_before_sync();
-            mbar_arrive(&s.bar_oread);
         }
     }
     tc::fence_before_sync();
