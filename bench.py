@@ -78,10 +78,15 @@ def parse():
                          "seq = every rank owns a whole batch of 32 (weak scaling, no collective)")
     ap.add_argument("--layers-per-exchange", type=int, default=0,
                     help="N > 1: layers whose outputs one grouped all-gather carries (0 = 4)")
+    ap.add_argument("--reserve-sms", type=int, default=0,
+                    help="N > 1: SMs the step's persistent kernels leave to the exchange kernels")
     ap.add_argument("--op-seconds", type=float, default=1.0, help="least length of an operator's timed region")
     ap.add_argument("--op-batch", type=int, default=0, help="--workload NAME: override the batch")
     ap.add_argument("--op-ctx", type=int, default=0, help="--workload NAME: override the context / token count")
     ap.add_argument("--chunk", type=int, default=None, help="--workload NAME: query rows per prefill call")
+    ap.add_argument("--emulate-ranks", type=int, default=0,
+                    help="N = 1 only: time rank 0's share of a step divided over this many ranks (--shard heads or "
+                         "splitkv), without the exchange: the per-rank kernel time of a multi-GPU run on one GPU")
     ap.add_argument("--no-operators", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="N > 1: skip the sharded-step check")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -768,10 +773,13 @@ def main():
     mode = shard_mode(args, world)
     strong = mode in ("heads", "splitkv")
     plan = StepPlan(mode if world > 1 else "seq", rank if strong else 0, world if strong else 1, args.batch)
-    split_mode = mode == "splitkv"
+    emulated = world == 1 and args.emulate_ranks > 1
+    if emulated:
+        plan = StepPlan("heads" if args.shard == "auto" else args.shard, 0, args.emulate_ranks, args.batch)
+    split_mode = mode == "splitkv" or (emulated and plan.mode == "splitkv")
     ctx_full = contexts(args)                       # tokens attended per sequence, the one being decoded included
     seqs = list(plan.seqs)
-    last_part = (not split_mode) or rank == world - 1
+    last_part = (not split_mode) or (rank == world - 1 and not emulated)
     # tokens of every local sequence this rank holds after the step, and the value of pos[] it passes
     hist, ctx, pos_local = [], [], []
     for b in seqs:
@@ -838,10 +846,10 @@ def main():
         gs = cache.gather_shapes(B, world)
         names = ["attn_o_all", "delta_o_all"] + (["attn_ml_all", "attn_o_final"] if split_mode else [])
         gathered = {n: torch.zeros(gs[n], device="cuda") for n in names}
-        if split_mode:
-            dev["attn_ml"] = torch.zeros(sh["attn_ml"], device="cuda")
-            dev["no_append"] = not last_part
-        cache.set_gather(comm, gathered, args.layers_per_exchange)
+        cache.set_gather(comm, gathered, args.layers_per_exchange, args.reserve_sms)
+    if split_mode:
+        dev["attn_ml"] = torch.zeros(sh["attn_ml"], device="cuda")
+        dev["no_append"] = not last_part
 
     def sync_all():
         torch.cuda.synchronize()
@@ -900,7 +908,7 @@ def main():
 
     # ---------------- end to end through the host-buffer entry point ----------------
     e2e = None
-    if not args.no_e2e and not split_mode:
+    if not args.no_e2e and not split_mode and not emulated:
         for _ in range(3):
             cache.decode_host(host, B)
         sync_all()
@@ -941,7 +949,8 @@ def main():
         gather_bytes = 0
         if strong:
             gather_bytes = sum(x.numel() * x.element_size() for n, x in gathered.items() if n.endswith("_all"))
-        par = {"single": "one GPU",
+        par = {"single": "one GPU" if not emulated else "one GPU running rank 0's share of a %d-rank %s step, no exchange"
+               % (args.emulate_ranks, plan.mode),
                "seq": "weak: every rank owns a whole batch of %d (same contexts), no collective" % args.batch,
                "heads": "strong: KV / value heads x%d, then sequences x%d; per-layer outputs all-gathered by the library "
                         "(ncclAllGather on a side stream, one grouped call per %d layers, %d bytes received per rank "
@@ -979,9 +988,9 @@ def main():
     del cache, dev, gathered
     torch.cuda.empty_cache()
     if rank == 0:
-        if world == 1 and not args.no_operators:
+        if world == 1 and not args.no_operators and not emulated:
             line["operators"] = run_operators(args, sampler, peaks)
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not emulated:
             line["cpu_baseline"] = cpu_reference_leg(args, ctx_full)
         print(json.dumps(line), flush=True)
     sampler.stop()

@@ -655,6 +655,8 @@ typedef struct rl_stack_gather {
     float* attn_ml_all;
     float* attn_o_final;
     int layers_per_exchange;
+    int reserve_sms;             /* SMs the step's persistent kernels leave free so that the exchange kernels
+                                  * run beside them instead of between them; 0 = none */
 } rl_stack_gather;
 /* Attach (or, with g == NULL, detach) the exchange to every following rl_stack_decode[_host] of
  * this cache.  Every rank of the communicator must then call the step the same number of times. */

@@ -112,7 +112,7 @@ class StackGlue(C.Structure):
 
 class StackGather(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("comm", "attn_o_all", "delta_o_all", "attn_ml_all", "attn_o_final")] + [
-        ("layers_per_exchange", C.c_int)]
+        ("layers_per_exchange", C.c_int), ("reserve_sms", C.c_int)]
 
 
 COMM_ID_BYTES = 128

@@ -213,14 +213,14 @@ class HybridCache:
         return {"attn_o_all": (A, W, B, self.n_q, 256), "delta_o_all": (D, W, B, self.n_v, self.dv),
                 "attn_ml_all": (A, W, B, self.n_q, 2), "attn_o_final": (A, B, self.n_q, 256)}
 
-    def set_gather(self, comm, tensors: dict | None, layers_per_exchange: int = 0):
+    def set_gather(self, comm, tensors: dict | None, layers_per_exchange: int = 0, reserve_sms: int = 0):
         """Attach the all-gather of the step's outputs over `comm` (a Comm) to decode() /
         decode_host(); tensors: device buffers shaped as gather_shapes().  None detaches."""
         if comm is None or tensors is None:
             check(lib().rl_stack_set_gather(self._h, None))
             self._gather = None
             return
-        g = _lib.StackGather(comm=comm.handle, layers_per_exchange=layers_per_exchange)
+        g = _lib.StackGather(comm=comm.handle, layers_per_exchange=layers_per_exchange, reserve_sms=reserve_sms)
         for name in ("attn_o_all", "delta_o_all", "attn_ml_all", "attn_o_final"):
             x = tensors.get(name)
             if x is None:

@@ -65,6 +65,16 @@ namespace rl {
 thread_local bool g_step_overlap = false;
 }
 namespace {
+// SMs the persistent kernels of the step in flight leave free (for the exchange kernels of a sharded step)
+thread_local int g_sm_reserve = 0;
+struct SmReserve {
+    int prev;
+    explicit SmReserve(int n) : prev(g_sm_reserve) { g_sm_reserve = n; }
+    ~SmReserve() { g_sm_reserve = prev; }
+};
+inline int step_sms(int sms) { return std::max(1, sms - g_sm_reserve); }
+}  // namespace
+namespace {
 DevInfo g_dev[64];
 
 int dev_info(DevInfo** out) {
@@ -214,7 +224,7 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
         return fail(RL_ERR_RANGE, "NULL pointer argument");
     DevInfo* d;
     if (int st = dev_info(&d)) return st;
-    const AttnPlan pl = attn_plan(p, d->sms);
+    const AttnPlan pl = attn_plan(p, step_sms(d->sms));
     if (workspace_bytes < pl.total_bytes)
         return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, pl.total_bytes);
     if (reinterpret_cast<uintptr_t>(k_pool) % 128 || (!tq && reinterpret_cast<uintptr_t>(v_pool) % 128) ||
@@ -403,6 +413,9 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
     // and gated there too, straight out of the gather buffer.
     const rl_stack_glue* glue = io->glue;
     const rl_stack_gather& gx = c->gather;
+    // a sharded step leaves a few SMs to the exchange kernels, which otherwise find no room beside
+    // persistent CTAs that fill every SM's shared memory and run only in the gaps between kernels
+    SmReserve reserve(gx.comm ? gx.reserve_sms : 0);
     rl::Comm* comm = reinterpret_cast<rl::Comm*>(gx.comm);
     const int n_ranks = comm ? rl::comm_ranks(comm) : 1;
     const int per_x = gx.layers_per_exchange > 0 ? gx.layers_per_exchange : 4;
@@ -1230,7 +1243,7 @@ int rl_gdn_decode(float* S, float* conv_ring, const int32_t* conv_phase, const i
     a.head_map = p->head_map;
     a.conv_dim = 2 * p->n_qk * p->dk + p->n_v * p->dv;
     a.eps_l2 = p->eps_l2;
-    rl::launch_gdn_decode(a, d->sms, as_stream(stream), kGdnStreamMin);
+    rl::launch_gdn_decode(a, step_sms(d->sms), as_stream(stream), kGdnStreamMin);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -1866,6 +1879,7 @@ int rl_stack_set_gather(rl_cache* c, const rl_stack_gather* g) {
         if ((c->n_attn && !g->attn_o_all) || (c->n_delta && !g->delta_o_all))
             return fail(RL_ERR_RANGE, "gather buffers are NULL");
         if (g->layers_per_exchange < 0) return fail(RL_ERR_RANGE, "layers_per_exchange %d", g->layers_per_exchange);
+        if (g->reserve_sms < 0 || g->reserve_sms > 64) return fail(RL_ERR_RANGE, "reserve_sms %d outside [0, 64]", g->reserve_sms);
         if (!c->s_comm) {
             int lo = 0, hi = 0;
             RL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
