@@ -13,10 +13,15 @@
  * it is bit-identical to the reference when both are built without FMA
  * contraction; tests pin that against outputs of the reference itself.
  *
- * Where the reference has CUDA code only (q8 K / TQ3 V compact KV) parity is
- * UNPINNED by any reference test or CPU function: the restatement follows the
- * cited CUDA lines in IEEE fp32 (true division, sqrtf, no fast-math) with one
- * documented summation order.
+ * Where the reference has CUDA code only (q8 K / TQ3 V compact KV) no
+ * reference test or CPU function exists: the restatement follows the cited
+ * CUDA lines in IEEE fp32 (true division, sqrtf, no fast-math) with one
+ * documented summation order, and is pinned on the reference's own CUDA
+ * kernels run on a GPU (ref_cuda_shim.cu; tests/test_gpu_compact_ref_pin.py:
+ * V codes and all scales equal, K codes equal but for ~1 in 10^6 that sit
+ * on a rounding boundary of the reference's fast-math division).  The
+ * 256-point layout with a sign vector has no reference kernel: that
+ * variant alone stays unpinned.
  *
  * Build: gcc -O2 -ffp-contract=off -fno-fast-math (see oracle/Makefile).
  */
@@ -425,8 +430,8 @@ RLO_API void rlo_conv1d_causal_prefill(const float* x, const float* w, float* y,
 }
 
 /* ------------------------------------------------------------------ */
-/* Compact KV: q8 K + TurboQuant-3 V.  CUDA-only in the reference; no   */
-/* reference test pins it (PARITY UNPINNED).                           */
+/* Compact KV: q8 K + TurboQuant-3 V.  CUDA-only in the reference;      */
+/* pinned on its own CUDA kernels (see the header of this file).        */
 /* ------------------------------------------------------------------ */
 
 /* 3-bit Lloyd-Max centroids for N(0,1), cuda_engine.cu:205-209. */

@@ -212,6 +212,7 @@ const int kTqSegWeight = knob("RL_B200_TQ_SEG_WEIGHT", 23);
 const int kF16SegWeight = knob("RL_B200_F16_SEG_WEIGHT", 6);
 // heads per launch from which the fused DeltaNet step streams whole heads through persistent CTAs
 const int kGdnStreamMin = knob("RL_B200_GDN_STREAM_MIN", 96);
+const int kGdnGrid = knob("RL_B200_GDN_GRID", 0);       // development builds: force the streaming form's grid
 
 int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
                      const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
@@ -1171,7 +1172,7 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     // The scan of a value head walks its chunks in order on one SM (48 CTAs), the chunk-local
     // precompute fills the device: long sequences are cut into segments so that the scan of one
     // segment (second stream, higher priority) runs beside the precompute of the next.
-    const int n_seg = n_chunks >= 32 ? 4 : 1;
+    const int n_seg = n_chunks >= 32 ? 4 : (n_chunks >= 8 ? 2 : 1);
     cudaStream_t run = as_stream(stream);
     auto prepare = [&](int c0, int n, cudaStream_t st) {
         a.chunk0 = c0;
@@ -1243,7 +1244,7 @@ int rl_gdn_decode(float* S, float* conv_ring, const int32_t* conv_phase, const i
     a.head_map = p->head_map;
     a.conv_dim = 2 * p->n_qk * p->dk + p->n_v * p->dv;
     a.eps_l2 = p->eps_l2;
-    rl::launch_gdn_decode(a, step_sms(d->sms), as_stream(stream), kGdnStreamMin);
+    rl::launch_gdn_decode(a, step_sms(d->sms), as_stream(stream), kGdnStreamMin, kGdnGrid);
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }

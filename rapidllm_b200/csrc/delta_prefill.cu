@@ -486,7 +486,9 @@ struct ScanSmem {
 // (S^T += D^T Kt) -> workers split the new S^T.  The output products (S^T Qg^T before D is known,
 // D^T P^T after the state update) are issued behind the chain's MMAs and read out by the workers while
 // the next chunk's first MMAs run.
-__global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(DeltaChunkArgs a) {
+// (launch bounds for two CTAs per SM: not to run two scans side by side -- tensor memory has room for one --
+// but to keep the registers low enough that a prepare CTA of the next segment fits beside a scan CTA)
+__global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     ScanSmem& s = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int h = blockIdx.x;

@@ -167,7 +167,8 @@ struct GdnDecodeArgs {
     float eps_l2;
 };
 // heads (items) from which the streaming form is used instead of one CTA per column slice
-void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st, int stream_min_items);
+void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st, int stream_min_items, int grid_override = 0);
+int gdn_stream_grid(int items, int sms);
 size_t gdn_decode_stream_smem_bytes();
 const void* gdn_decode_stream_kernel_ptr();
 // phase[l][slot_ids[b]] = (phase + n_tok) & 3 for l < n_layers, b < batch (phase [n_layers][n_slots])

@@ -88,3 +88,17 @@ def test_hidden_rmsnorm(oracle):
         assert np.abs(y.cpu().numpy() - ref).max() <= 2e-6 * max(1.0, np.abs(ref).max())
         assert torch.equal(xi, y)
         assert np.abs(y0.cpu().numpy() - oracle.qwen3_rmsnorm(x.numpy(), None)).max() <= 2e-6 * np.abs(ref).max() + 2e-6
+
+
+def test_cast_f32_to_bf16_rounds_to_nearest_even():
+    import ctypes as C
+    from rapidllm_b200 import _lib
+    gen = torch.Generator().manual_seed(5)
+    for n in (1, 3, 4, 1021, 4096 * 3 + 2):
+        x = (torch.randn(n, generator=gen) * 3).cuda()
+        if n > 8:
+            x[1], x[2], x[5] = 1.00390625, 1.01171875, -0.0        # ties: to even (down), to even (up); signed zero
+        y = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        _lib.check(_lib.lib().rl_cast_f32_to_bf16(C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), n,
+                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        assert torch.equal(y, x.to(torch.bfloat16))

@@ -133,3 +133,43 @@ def test_argument_errors():
     with pytest.raises(_lib.RlError):
         cache.prefill({}, row, 0, 0, 16)                        # tensors missing
     cache.prefill({}, row, 0, 0, 0)                             # nothing to do
+
+
+def test_one_deltanet_layer_at_a_time_equals_the_stack_call():
+    """rl_cache_delta_prefill (a host that runs its projections between the layers calls the DeltaNet
+    prefill per layer) leaves the same state, windows and outputs as rl_stack_prefill over the same
+    inputs, bit for bit, across two chunks (the second starts from the carried window)."""
+    import ctypes as C
+    from rapidllm_b200 import _lib
+    from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
+    gen = torch.Generator().manual_seed(13)
+    mk = lambda: HybridCache(QWEN35_LAYER_TYPES, n_pages=6, n_slots=2, max_batch=2, max_pages_per_seq=3)
+    a, b = mk(), mk()
+    D, cd = a.n_delta, a.conv_dim
+    row = torch.tensor([4, 1, 2], dtype=torch.int32).cuda()
+    conv_w = (torch.randn(D, cd, 4, generator=gen) * 0.5).cuda()
+    slot, pos0 = 1, 0
+    L = _lib.lib()
+    vp = C.c_void_p
+    for T in (100, 37):
+        t = _chunk_inputs(a, T, gen)
+        dev = {n: x.cuda() for n, x in t.items()}
+        dev["conv_w"] = conv_w
+        a.prefill(dev, row, slot, pos0, T)
+        o = torch.zeros(D, T, 48, 128, device="cuda")
+        need = L.rl_cache_delta_prefill_workspace_bytes(b._h, T)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        for d in range(D):
+            _lib.check(L.rl_cache_delta_prefill(b._h, d, slot, pos0, T, vp(dev["delta_qkv"][d].data_ptr()),
+                                                vp(conv_w[d].data_ptr()), vp(dev["delta_beta"][d].data_ptr()),
+                                                vp(dev["delta_g"][d].data_ptr()), vp(o[d].data_ptr()), vp(ws.data_ptr()),
+                                                ws.numel(), st))
+        _lib.check_device()
+        assert torch.equal(o, dev["delta_o"])
+        for d in range(D):
+            assert torch.equal(a.state(d), b.state(d))
+            assert torch.equal(a.conv_windows(d), b.conv_windows(d))
+        pos0 += T
+    a.close()
+    b.close()
