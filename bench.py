@@ -54,7 +54,7 @@ PAGE = 64
 # tolerances of the sharded-step check (those of the tests: fp16-KV attention / FP32 DeltaNet)
 ATTN_MAX_ABS, ATTN_REL_L2, DELTA_MAX_ABS = 2e-2, 1e-3, 1e-4
 OPERATORS = ["f16_decode", "f16_decode_long", "delta_step", "compact_decode", "compact_decode_wht256",
-             "attn_prefill", "attn_prefill_chunk1024", "delta_prefill", "stack_prefill", "stack_long_compact"]
+             "attn_prefill", "attn_prefill_chunk1024", "delta_prefill", "stack_prefill", "stack_long_compact", "stack_long_f16"]
 
 
 def parse():
@@ -615,14 +615,15 @@ def op_stack_prefill(args, sampler, peaks, gen):
     return entry
 
 
-def op_stack_long(args, sampler, peaks, gen):
-    """The 64-layer stack decode at the metric's context range on the compact cache: batch 32, ragged ctx
-    U[32768, 131072], q8-K / TQ3-V pages inside rl_cache (every sequence is past the F16 window)."""
+def op_stack_long(args, sampler, peaks, gen, compact=True):
+    """The 64-layer stack decode at the metric's context range, ragged ctx U[32768, 131072]: batch 32 on the
+    compact cache (q8-K / TQ3-V pages inside rl_cache, every sequence past the F16 window), or batch 8 on the
+    F16 cache (the batch whose 43 GB of pages fit beside the rest)."""
     import torch
 
     from rapidllm_b200 import _lib, ops
     from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
-    B = args.op_batch or 32
+    B = args.op_batch or (32 if compact else 8)
     lo, hi = 32768, args.op_ctx or 131072
     cg = torch.Generator().manual_seed(args.seed)
     ctx = torch.randint(lo, hi + 1, (B,), generator=cg).tolist()
@@ -630,8 +631,11 @@ def op_stack_long(args, sampler, peaks, gen):
     max_pages, n_pages = max(pages), sum(pages)
     types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
     window = 8192
-    cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages, max_seq_len=max(ctx),
-                        kv_dtype=_lib.RL_KV_Q8K_TQ3V, wht_len=128, window_tokens=window)
+    if compact:
+        cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages, max_seq_len=max(ctx),
+                            kv_dtype=_lib.RL_KV_Q8K_TQ3V, wht_len=128, window_tokens=window)
+    else:
+        cache = HybridCache(types, n_pages=n_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages, max_seq_len=max(ctx))
     perm = torch.randperm(n_pages, generator=cg).int()
     table = torch.zeros(B, max_pages, dtype=torch.int32)
     at = 0
@@ -639,17 +643,22 @@ def op_stack_long(args, sampler, peaks, gen):
         table[b, :p] = perm[at:at + p]
         at += p
     table_d = table.cuda()
-    # layer 0's pages are quantised from N(0,1) rows, the other layers get a copy (same page table)
-    p0 = cache.k_pool(0)
-    step = 8192
-    for b in range(B):
-        for t0 in range(0, ctx[b] - 1, step):
-            n = min(step, ctx[b] - 1 - t0)
-            k = torch.randn(n, N_KV, HD, device="cuda", generator=gen)
-            v = torch.randn(n, N_KV, HD, device="cuda", generator=gen)
-            ops.kv_compact_append(p0, table_d[b], k, v, 128, None, pos0=t0)
-    for a in range(1, cache.n_attn):
-        cache.k_pool(a).copy_(p0)
+    if compact:
+        # layer 0's pages are quantised from N(0,1) rows, the other layers get a copy (same page table)
+        p0 = cache.k_pool(0)
+        step = 8192
+        for b in range(B):
+            for t0 in range(0, ctx[b] - 1, step):
+                n = min(step, ctx[b] - 1 - t0)
+                k = torch.randn(n, N_KV, HD, device="cuda", generator=gen)
+                v = torch.randn(n, N_KV, HD, device="cuda", generator=gen)
+                ops.kv_compact_append(p0, table_d[b], k, v, 128, None, pos0=t0)
+        for a in range(1, cache.n_attn):
+            cache.k_pool(a).copy_(p0)
+    else:
+        for a in range(cache.n_attn):
+            cache.k_pool(a).normal_(generator=gen)
+            cache.v_pool(a).normal_(generator=gen)
     for d in range(cache.n_delta):
         cache.state(d).normal_(0.0, 0.02, generator=gen)
         cache.conv(d).normal_(generator=gen)
@@ -668,19 +677,22 @@ def op_stack_long(args, sampler, peaks, gen):
     ms, calls, clocks = _timed(call, sampler, args.op_seconds, max(3, args.warmup))
     _lib.check_device()
     finite = bool(torch.isfinite(dev["attn_o"]).all() and torch.isfinite(dev["delta_o"]).all())
-    per_tok = _lib.lib().rl_kv_compact_page_bytes() // PAGE
+    per_tok = (_lib.lib().rl_kv_compact_page_bytes() // PAGE) if compact else HD * 2 * 2
     ab = algorithmic_bytes(args.layers, ctx)
     attn_bytes = sum(ctx) * N_KV * per_tok + B * N_Q * HD * 4 * 3
     step_bytes = cache.n_attn * (attn_bytes + ab["kv_append"]) + cache.n_delta * ab["delta_rule"]
     entry = {
-        "workload": "hybrid_stack_decode on the compact cache: %d layers, batch %d, ragged ctx U[%d,%d], q8-K / TQ3-V pages "
-                    "(358 B per token and head) + F16 window of %d tokens, page 64" % (len(types), B, lo, hi, window),
+        "workload": ("hybrid_stack_decode on the compact cache: %d layers, batch %d, ragged ctx U[%d,%d], q8-K / TQ3-V pages "
+                     "(358 B per token and head) + F16 window of %d tokens, page 64" % (len(types), B, lo, hi, window))
+        if compact else ("hybrid_stack_decode: %d layers, batch %d, ragged ctx U[%d,%d], paged F16 KV page 64"
+                         % (len(types), B, lo, hi)),
         "ms": ms, "value": B / (ms * 1e-3), "unit": "seq-steps/s", "calls_timed": calls,
-        "dtype": "q8 K / tq3 V / f32 state", "gpu_launches_per_call": cache.launches_per_step,
+        "dtype": "q8 K / tq3 V / f32 state" if compact else "f16 KV / f32 state", "gpu_launches_per_call": cache.launches_per_step,
         "l2": "inputs larger than L2 (%.1f GB streamed per step)" % (step_bytes / 1e9),
         "timed": "rl_stack_decode (graph replay), back to back", "outputs_finite": finite,
         "ctx_tokens": sum(ctx), "cache_bytes": cache.bytes,
-        "roofline": _hbm_roofline("whole step (attn_decode_tq_kernel dominates)", step_bytes, ms, peaks),
+        "roofline": _hbm_roofline("whole step (%s dominates)" % ("attn_decode_tq_kernel" if compact else "attn_decode_f16_kernel"),
+                                  step_bytes, ms, peaks),
         "clocks": clocks}
     cache.close()
     return entry
@@ -699,8 +711,8 @@ def run_one_operator(name, args, sampler, peaks):
         return op_delta_prefill(args, sampler, peaks, gen)
     if name == "stack_prefill":
         return op_stack_prefill(args, sampler, peaks, gen)
-    if name == "stack_long_compact":
-        return op_stack_long(args, sampler, peaks, gen)
+    if name in ("stack_long_compact", "stack_long_f16"):
+        return op_stack_long(args, sampler, peaks, gen, compact=name == "stack_long_compact")
     raise SystemExit("unknown operator %s" % name)
 
 

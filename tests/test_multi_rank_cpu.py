@@ -110,7 +110,7 @@ def _plan_worker(rank, world, port, mode, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from rapidllm_b200.shard import StepPlan
-    B, n_q, n_kv, n_v, n_k = 4, 12, 2, 12, 4
+    B, n_q, n_kv, n_v, n_k = 4, 24, 4, 12, 4
     rng = np.random.default_rng(1)                      # the whole problem, the same on every rank
     conv_dim = 2 * n_k * 128 + n_v * 128
     full = {"attn_q": torch.from_numpy(rng.standard_normal((2, B, n_q, 8), dtype=np.float32)),
@@ -141,7 +141,7 @@ def _plan_worker(rank, world, port, mode, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,world", [("heads", 2), ("heads", 4), ("splitkv", 2)])
+@pytest.mark.parametrize("mode,world", [("heads", 2), ("heads", 4), ("heads", 8), ("splitkv", 2)])
 def test_step_plan_slices_and_gathered_blocks_round_trip(mode, world):
     mgr = mp.Manager()
     ret = mgr.dict()
