@@ -747,23 +747,59 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     return RL_OK;
 }
 
-// How many CTAs share the KV range of one (query tile, head): 1 when there is at least one
-// (query tile, head) per SM (dividing a 1024-row chunk in two measured slower: the partials and
-// the second prologue cost more than the emptier second wave), else enough to fill the device
-// twice over, each part keeping at least 8 KV tiles.
+// How the (query tile, head) items of a prefill call are divided among CTAs.
+//  * fewer items than SMs (short chunks, verify rows): every item's KV range is shared by `parts`
+//    CTAs, enough to fill the device twice over, each part keeping at least 8 KV tiles;
+//  * a last wave that is at most half full (192 items of a 1 024-row chunk on 148 SMs): the first
+//    n_full items run whole, the items of the last wave are divided among tail_parts CTAs each, so
+//    that its work is spread over every SM (dividing EVERY item of such a chunk in two measured
+//    slower than not dividing: the partials and second prologues cost more than the wave);
+//  * otherwise nothing is divided.
 static bool prefill_packed(const rl_attn_prefill_params* p) {
     // few enough rows that (token, query head of a group) pairs fit one 128-row tile per KV head
     return p->seq * (p->n_q / p->n_kv) <= rl::attn_prefill_q_rows();
 }
 
-static int prefill_kv_parts(const rl_attn_prefill_params* p, int sms) {
+struct PrefillSplit {
+    int parts = 1;                   // uniform division of every item
+    int n_full = 0, tail_parts = 1;  // or: items from n_full on divided in tail_parts
+    long long items = 0;
+    size_t ws_bytes(const rl_attn_prefill_params* p) const {
+        if (tail_parts > 1) {
+            const size_t units = size_t(items - n_full) * tail_parts, rows = rl::attn_prefill_q_rows();
+            return align_up(units * rows * rl::kHeadDim * sizeof(float), 256) + units * rows * 2 * sizeof(float);
+        }
+        if (parts <= 1) return 0;
+        const size_t rows_total = size_t(p->seq) * p->n_q;
+        return align_up(size_t(parts) * rows_total * rl::kHeadDim * sizeof(float), 256) +
+               size_t(parts) * rows_total * 2 * sizeof(float);
+    }
+};
+
+static PrefillSplit prefill_split(const rl_attn_prefill_params* p, int sms) {
+    PrefillSplit sp;
     const int rows = rl::attn_prefill_q_rows();
-    const long long items = prefill_packed(p) ? p->n_kv : 1LL * ((p->seq + rows - 1) / rows) * p->n_q;
-    if (items <= 0 || items >= sms) return 1;
-    const long long tiles = (1LL * p->pos0 + p->seq + p->page_tokens - 1) / p->page_tokens;   // of the last query tile
-    long long parts = prefill_packed(p) ? sms / items : (2LL * sms + items - 1) / items;
-    parts = std::min(parts, std::max(1LL, tiles / 8));
-    return int(std::min(parts, 64LL));
+    const int n_qtiles = (p->seq + rows - 1) / rows;
+    sp.items = prefill_packed(p) ? p->n_kv : 1LL * n_qtiles * p->n_q;
+    if (sp.items <= 0) return sp;
+    if (sp.items < sms) {
+        const long long tiles = (1LL * p->pos0 + p->seq + p->page_tokens - 1) / p->page_tokens;   // of the last query tile
+        long long parts = prefill_packed(p) ? sms / sp.items : (2LL * sms + sp.items - 1) / sp.items;
+        parts = std::min(parts, std::max(1LL, tiles / 8));
+        sp.parts = int(std::min(parts, 64LL));
+        return sp;
+    }
+    const long long rest = sp.items % sms;
+    if (rest == 0 || 2 * rest > sms) return sp;
+    // the items of the last wave are the last of the launch order: the lowest query tiles of the
+    // last KV head; the shortest of them attends to this many KV tiles
+    const long long tiles_min = (1LL * p->pos0 + std::min<long long>(p->seq, rows) + p->page_tokens - 1) / p->page_tokens;
+    const long long tp = std::min({1LL * sms / rest, 8LL, tiles_min / 8});
+    if (tp > 1) {
+        sp.n_full = int(sp.items - rest);
+        sp.tail_parts = int(tp);
+    }
+    return sp;
 }
 
 static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
@@ -819,23 +855,38 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
     const int n_qtiles = (p->seq + rl::attn_prefill_q_rows() - 1) / rl::attn_prefill_q_rows();
     // a workspace lets short chunks (or a handful of verify rows over a long cache) spread every
     // (query tile, head) over several CTAs; without one the call runs unsplit
-    int parts = workspace ? prefill_kv_parts(p, d->sms) : 1;
+    PrefillSplit sp = workspace ? prefill_split(p, d->sms) : PrefillSplit();
+    if (workspace_bytes < sp.ws_bytes(p) || reinterpret_cast<uintptr_t>(workspace) % 16) sp = PrefillSplit();
+    const int parts = sp.parts;
     const size_t rows_total = size_t(p->seq) * p->n_q;
-    const size_t o_bytes = align_up(size_t(parts) * rows_total * rl::kHeadDim * sizeof(float), 256);
-    if (parts > 1 && (workspace_bytes < o_bytes + size_t(parts) * rows_total * 2 * sizeof(float) ||
-                      reinterpret_cast<uintptr_t>(workspace) % 16))
-        parts = 1;
+    const size_t units = sp.tail_parts > 1 ? size_t(sp.items - sp.n_full) * sp.tail_parts : 0;
+    const size_t o_bytes = sp.tail_parts > 1
+                               ? align_up(units * rl::attn_prefill_q_rows() * rl::kHeadDim * sizeof(float), 256)
+                               : align_up(size_t(parts) * rows_total * rl::kHeadDim * sizeof(float), 256);
+    const bool divided = parts > 1 || sp.tail_parts > 1;
     a.packed = prefill_packed(p) ? 1 : 0;
     a.kv_parts = parts;
+    a.n_full = sp.tail_parts > 1 ? sp.n_full : 0;
+    a.tail_parts = sp.tail_parts;
     a.wave = d->sms;
-    a.part_o = parts > 1 ? static_cast<float*>(workspace) : nullptr;
-    a.part_ml = parts > 1 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + o_bytes) : nullptr;
-    rl::attn_prefill_kernel<<<dim3((a.packed ? unsigned(p->n_kv) : unsigned(n_qtiles) * unsigned(p->n_q)) * unsigned(parts)),
-                              rl::attn_prefill_threads(),
-                              rl::attn_prefill_smem_bytes(), as_stream(stream)>>>(a);
+    a.part_o = divided ? static_cast<float*>(workspace) : nullptr;
+    a.part_ml = divided ? reinterpret_cast<float*>(static_cast<char*>(workspace) + o_bytes) : nullptr;
+    const unsigned n_items = a.packed ? unsigned(p->n_kv) : unsigned(n_qtiles) * unsigned(p->n_q);
+    {
+        // both kernels wait for the kernel before them (griddepcontrol.wait) ahead of their first global access
+        StepOverlap overlap(true);
+        RL_CUDA(rl::launch_step(rl::attn_prefill_kernel,
+                                dim3(sp.tail_parts > 1 ? unsigned(sp.n_full) + unsigned(units) : n_items * unsigned(parts)),
+                                dim3(unsigned(rl::attn_prefill_threads())), rl::attn_prefill_smem_bytes(), as_stream(stream), a));
+        if (sp.tail_parts > 1 && parts <= 1)
+            RL_CUDA(rl::launch_step(rl::attn_prefill_tail_merge_kernel,
+                                    dim3(unsigned(rl::attn_prefill_q_rows()), unsigned(sp.items - sp.n_full)),
+                                    dim3(unsigned(rl::kHeadDim)), 0, as_stream(stream), a));
+    }
     if (parts > 1)
         rl::lse_combine_kernel<<<unsigned(rows_total), 256, 0, as_stream(stream)>>>(a.part_o, a.part_ml, gate, o, parts,
                                                                                   int(rows_total), 0, nullptr);
+
     RL_CUDA(cudaGetLastError());
     return RL_OK;
 }
@@ -851,11 +902,7 @@ size_t rl_attn_prefill_workspace_bytes(const rl_attn_prefill_params* p) {
     if (!p || p->seq <= 0 || p->n_q <= 0 || p->page_tokens <= 0) return 0;
     DevInfo* d;
     if (dev_info(&d)) return 0;
-    const int parts = prefill_kv_parts(p, d->sms);
-    if (parts <= 1) return 0;
-    const size_t rows_total = size_t(p->seq) * p->n_q;
-    return align_up(size_t(parts) * rows_total * rl::kHeadDim * sizeof(float), 256) +
-           size_t(parts) * rows_total * 2 * sizeof(float);
+    return prefill_split(p, d->sms).ws_bytes(p);
 }
 
 int rl_attn_prefill_ws(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,

@@ -32,7 +32,12 @@
 // kv_parts > 1 divides the KV tiles of an item among several CTAs that write partials for the
 // log-sum-exp merge kernel; packed makes the 128 MMA rows (token, query head of the GQA group)
 // pairs, one item per KV head, so the group's heads share a single pass over K/V.
+// A third for item counts a little above a multiple of the SM count (192 items of a 1 024-row chunk
+// on 148 SMs): tail_parts > 1 divides only the items of the last, partly filled wave, so that the
+// wave's work is spread over every SM; attn_prefill_tail_merge_kernel merges those items' partials.
+#include "common.cuh"
 #include "kernels.h"
+#include "launch.cuh"
 #include "tcgen05.cuh"
 
 namespace rl {
@@ -83,8 +88,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     // group's query heads of the last (heaviest) query tile, then of the one before, ...
     const int G = a.n_q / a.n_kv;
     const int per_kv = n_qtiles * G;
-    const int parts = a.kv_parts > 1 ? a.kv_parts : 1;
-    const int item = int(blockIdx.x) / parts, part = int(blockIdx.x) - item * parts;
+    const bool tail = a.tail_parts > 1 && int(blockIdx.x) >= a.n_full;
+    const int tail_unit = int(blockIdx.x) - a.n_full;
+    const int parts = tail ? a.tail_parts : (a.kv_parts > 1 ? a.kv_parts : 1);
+    const int item = tail ? a.n_full + tail_unit / parts : int(blockIdx.x) / parts;
+    const int part = tail ? tail_unit % parts : int(blockIdx.x) - item * parts;
     // packed (a few rows, e.g. a speculative verify): one item per KV head, its MMA rows are
     // (token, query head of the group) pairs, so the group's heads share one pass over K/V
     const int hkv = a.packed ? item : item / per_kv;
@@ -126,9 +134,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         mbar_fence_init();
     }
     if (warp == kWarpQK) tc::tmem_alloc(&s.tmem_base, kTmemCols);
+    griddep_launch();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
+    griddep_wait();       // the barriers and the tensor memory were set up beside the tail of the kernel before
     const uint32_t tmem = s.tmem_base;
     // Q rows -> tensor memory as the A operand of S = Q K^T (bf16 -> fp16 is exact for
     // normal-range values): lane = row, column c holds dims 2c, 2c+1; each of the four threads
@@ -144,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         // The CTA that follows this one on the SM is, to a good approximation, the one a wave further down
         // the launch order: start its Q rows on their way into L2.
         const int nxt = int(blockIdx.x) + int(a.wave);
-        if (!a.packed && parts == 1 && nxt < int(gridDim.x)) {
+        if (!a.packed && parts == 1 && nxt < (a.tail_parts > 1 ? a.n_full : int(gridDim.x))) {
             const int n_hkv = nxt / per_kv, n_rem = nxt - n_hkv * per_kv;
             const int n_q0 = (n_qtiles - 1 - n_rem / G) * kQRows, n_hq = n_hkv * G + n_rem % G;
             const int n_rows = min(kQRows, a.T - n_q0);
@@ -183,7 +193,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         tc::fence_before_sync();
         mbar_arrive(&s.bar_q);                                // Q is in tensor memory (awaited by the S issuer)
         // the epilogue's gate rows: start them on their way into L2 now (2 of the row's 8 lines each)
-        if (a.gate && a.kv_parts <= 1 && r < rows) {
+        if (a.gate && parts <= 1 && r < rows) {
             const float* gp = a.gate + flat_row(r) * kHeadDim + qpart * 64;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(gp));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + 32));
@@ -457,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
                                     __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             }
             if (split && grp == 0 && half == 0 && r < rows) {
-                float* ml = a.part_ml + (size_t(part) * a.T * a.n_q + flat_row(r)) * 2;
+                float* ml = a.part_ml + (tail ? size_t(tail_unit) * kQRows + r : size_t(part) * a.T * a.n_q + flat_row(r)) * 2;
                 ml[0] = m_fin * 0.6931471805599453f;          // log2 domain -> natural-log units
                 ml[1] = l_run;
             }
@@ -487,8 +497,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
             for (int i = 0; i < kRowsPerWarp; ++i) {
                 const int row = warp + i * (kSoftmaxThreads / 32);
                 if (row >= rows) break;
-                float* dst = split ? a.part_o + (size_t(part) * a.T * a.n_q + flat_row(row)) * kHeadDim
-                                   : a.o + flat_row(row) * kHeadDim;
+                float* dst = !split ? a.o + flat_row(row) * kHeadDim
+                             : a.part_o + (tail ? size_t(tail_unit) * kQRows + row : size_t(part) * a.T * a.n_q + flat_row(row)) * kHeadDim;
 #pragma unroll
                 for (int hcol = 0; hcol < 2; ++hcol) {
                     const int c = hcol * 128 + lane * 4;
@@ -507,6 +517,34 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     }
     __syncthreads();
     if (warp == kWarpQK) tc::tmem_dealloc(tmem, kTmemCols);
+}
+
+// Rows of the items the main kernel divided (tail_parts > 1): block = (row of the item, item - n_full),
+// thread = output dim.  Log-sum-exp merge of the item's partials, 1 / l and the sigmoid gate.
+__global__ void __launch_bounds__(kHeadDim) attn_prefill_tail_merge_kernel(AttnPrefillArgs a) {
+    griddep_launch();
+    griddep_wait();
+    const int r = blockIdx.x, d = threadIdx.x;
+    const int n_qtiles = (a.T + kQRows - 1) / kQRows;
+    const int G = a.n_q / a.n_kv, per_kv = n_qtiles * G;
+    const int item = a.n_full + int(blockIdx.y);
+    const int hkv = item / per_kv, rem = item - hkv * per_kv;
+    const int q0 = (n_qtiles - 1 - rem / G) * kQRows, hq = hkv * G + rem % G;
+    if (q0 + r >= a.T) return;
+    const size_t u0 = size_t(blockIdx.y) * a.tail_parts;
+    float mm = -1e30f;
+    for (int p = 0; p < a.tail_parts; ++p) mm = fmaxf(mm, a.part_ml[((u0 + p) * kQRows + r) * 2]);
+    float acc = 0.f, l = 0.f;
+    for (int p = 0; p < a.tail_parts; ++p) {
+        const size_t row = (u0 + p) * kQRows + r;
+        const float al = expf(a.part_ml[row * 2] - mm);
+        l += a.part_ml[row * 2 + 1] * al;
+        acc += __ldcs(a.part_o + row * kHeadDim + d) * al;
+    }
+    float out = l > 0.f ? acc / l : 0.f;
+    const size_t oi = (size_t(q0 + r) * a.n_q + hq) * kHeadDim + d;
+    if (a.gate) out *= 1.f / (1.f + expf(-__ldcs(a.gate + oi)));
+    a.o[oi] = out;
 }
 
 size_t attn_prefill_smem_bytes() { return sizeof(Smem) + 1024; }

@@ -51,8 +51,14 @@ struct AttnPrefillArgs {
     float* part_ml;
     int packed;                  // T * (n_q / n_kv) <= 128: one item per KV head, MMA rows = (token, head of the group)
     int wave;                    // CTAs resident at a time (one per SM): CTA i + wave is taken to follow CTA i on its SM
+    // tail_parts > 1 (with kv_parts <= 1): the first n_full items of the launch order run whole; each
+    // later item is divided among tail_parts CTAs, launched after all whole items, so that the last,
+    // partly filled wave is spread over every SM.  Unit u = (item - n_full) * tail_parts + part writes
+    // part_o [u][128][256] and part_ml [u][128][2]; attn_prefill_tail_merge_kernel finishes those rows.
+    int n_full, tail_parts;
 };
 __global__ void attn_prefill_kernel(AttnPrefillArgs a);
+__global__ void attn_prefill_tail_merge_kernel(AttnPrefillArgs a);
 size_t attn_prefill_smem_bytes();
 int attn_prefill_threads();
 int attn_prefill_q_rows();

@@ -121,7 +121,10 @@ def test_config3_8192_tokens_sampled_rows(oracle):
         outs.append(ops.attn_prefill(q[sl].cuda(), kp, vp, table, p0, k[sl].cuda(), v[sl].cuda(), gate[sl].cuda()))
     _lib.check_device()
     o = torch.cat(outs).cpu().numpy()
-    rows = np.array([0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 4095, 5000, 8191], np.int32)
+    # 192 (query tile, head) items per chunk on 148 SMs: the lowest query tiles of the last KV head are
+    # the ones whose KV range is divided (rows 0-255 of a chunk, more parts the longer the cache)
+    rows = np.array([0, 1, 63, 64, 127, 128, 1000, 1023, 1024, 1100, 2053, 3272, 4095, 5000, 7168 + 130, 7168 + 255,
+                     7168 + 256, 8191], np.int32)
     ref = oracle.attn_prefill_rows(q[rows].float().numpy(), k.float().numpy(), v.float().numpy(), rows)
     ref = oracle.sigmoid_gate(ref, gate[rows].numpy())
     _check(o[rows], ref, "cfg3 rows")
