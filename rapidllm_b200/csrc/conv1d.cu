@@ -88,6 +88,59 @@ conv1d_prefill_kernel(const float* x, const float* w, float* y, const float* sta
     }
 }
 
+// The same for k = 4 and an even dim: thread = 2 adjacent channels x 8 time steps, every input of the
+// tile requested before the first is used (the walk above has one load in flight per thread and is bound
+// by their latency); small enough per thread that three CTAs fit an SM (the fp64 copies of the inputs are
+// what costs registers).  Taps are accumulated in the same order and width.
+constexpr int kVecSteps = 8;
+__global__ void __launch_bounds__(256, 3)
+conv1d_prefill4_kernel(const float* x, const float* w, float* y, const float* state_in, float* state_out, int seq,
+                       int dim) {
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
+    if (c >= dim) return;
+    const int t0 = blockIdx.y * kVecSteps;
+    float2 in[kVecSteps + 3];
+#pragma unroll
+    for (int i = 0; i < kVecSteps + 3; ++i) {
+        const int src = t0 - 3 + i;
+        float2 v = make_float2(0.f, 0.f);
+        if (src >= 0) {
+            if (src < seq) v = *reinterpret_cast<const float2*>(x + size_t(src) * dim + c);
+        } else if (state_in) {
+            // src = -1 is the newest tap (index 3) of each channel's window
+            const float* sp = state_in + size_t(c) * 4 + (4 + src);
+            v = make_float2(sp[0], sp[4]);
+        }
+        in[i] = v;
+    }
+    const float4 w0 = *reinterpret_cast<const float4*>(w + size_t(c) * 4);
+    const float4 w1 = *reinterpret_cast<const float4*>(w + size_t(c + 1) * 4);
+    if (state_out && blockIdx.y == 0) {
+        // seq >= 4: the window after the call is the last four inputs.  The thread that read this channel
+        // pair's old window (above, first tile) is the one that replaces it.
+        float2 last[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) last[p] = *reinterpret_cast<const float2*>(x + size_t(seq - 4 + p) * dim + c);
+        *reinterpret_cast<float4*>(state_out + size_t(c) * 4) = make_float4(last[0].x, last[1].x, last[2].x, last[3].x);
+        *reinterpret_cast<float4*>(state_out + size_t(c + 1) * 4) = make_float4(last[0].y, last[1].y, last[2].y, last[3].y);
+    }
+#pragma unroll
+    for (int i = 0; i < kVecSteps; ++i) {
+        if (t0 + i >= seq) break;
+        auto one = [&](const float4& wj, float a0, float a1, float a2, float a3) {
+            double acc = 0.0;
+            acc += double(wj.x) * a0;
+            acc += double(wj.y) * a1;
+            acc += double(wj.z) * a2;
+            acc += double(wj.w) * a3;
+            return silu(float(acc));
+        };
+        *reinterpret_cast<float2*>(y + size_t(t0 + i) * dim + c) =
+            make_float2(one(w0, in[i].x, in[i + 1].x, in[i + 2].x, in[i + 3].x),
+                        one(w1, in[i].y, in[i + 1].y, in[i + 2].y, in[i + 3].y));
+    }
+}
+
 __global__ void __launch_bounds__(256)
 conv1d_state_tail_kernel(const float* x, float* state_io, int seq, int dim, int k, int use_state_in) {
     const int c = blockIdx.x * 256 + threadIdx.x;
@@ -112,10 +165,19 @@ void launch_conv1d_update(const ConvUpdateArgs& a, cudaStream_t st) {
 void launch_conv1d_prefill(const float* x, const float* w, float* y, float* state_io, int seq,
                            int dim, int k, int use_state_in, cudaStream_t st) {
     if (seq <= 0 || dim <= 0) return;
-    const int tile = 64;
-    dim3 grid((dim + 255) / 256, (seq + tile - 1) / tile);
-    conv1d_prefill_kernel<<<grid, 256, 0, st>>>(x, w, y, (use_state_in && state_io) ? state_io : nullptr,
-                                                seq, dim, k, tile);
+    const float* state_in = (use_state_in && state_io) ? state_io : nullptr;
+    const bool vec = k == 4 && dim % 2 == 0 && reinterpret_cast<uintptr_t>(x) % 8 == 0 &&
+                     reinterpret_cast<uintptr_t>(y) % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
+    if (vec) {
+        const bool tail_fused = state_io && seq >= 4 && reinterpret_cast<uintptr_t>(state_io) % 16 == 0;
+        conv1d_prefill4_kernel<<<dim3((dim / 2 + 255) / 256, (seq + kVecSteps - 1) / kVecSteps), 256, 0, st>>>(
+            x, w, y, state_in, tail_fused ? state_io : nullptr, seq, dim);
+        if (tail_fused) return;
+    } else {
+        const int tile = 64;
+        conv1d_prefill_kernel<<<dim3((dim + 255) / 256, (seq + tile - 1) / tile), 256, 0, st>>>(x, w, y, state_in, seq, dim,
+                                                                                             k, tile);
+    }
     if (state_io)
         conv1d_state_tail_kernel<<<(dim + 255) / 256, 256, 0, st>>>(x, state_io, seq, dim, k, use_state_in);
 }

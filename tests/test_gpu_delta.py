@@ -146,6 +146,19 @@ def test_conv1d_update_and_prefill(oracle, golden):
         assert np.abs(got.cpu().numpy() - ref).max() < 2e-6
         assert np.array_equal(sd[0].cpu().numpy(), s)
         assert np.abs(ops.conv1d_causal_prefill(x.cuda(), ww.cuda()).cpu().numpy() - ref).max() < 2e-6
+    # the model's width (k 4, dim % 4 == 0: four channels x 16 steps per thread), ragged lengths, window carried
+    dim, k = 10240, 4
+    ww = torch.randn(dim, k, generator=gen)
+    x = torch.randn(100, dim, generator=gen)
+    s = np.zeros((dim, k), np.float32)
+    ref = np.stack([oracle.conv1d_update(x[t].numpy(), ww.numpy(), s) for t in range(100)])
+    sd = torch.zeros(dim, k, device="cuda")
+    ya = ops.conv1d_causal_prefill(x[:37].cuda(), ww.cuda(), sd)
+    yb = ops.conv1d_causal_prefill(x[37:].cuda(), ww.cuda(), sd, use_state_in=True)
+    assert np.abs(torch.cat([ya, yb]).cpu().numpy() - ref).max() < 2e-6
+    assert np.array_equal(sd.cpu().numpy(), s)
+    whole = ops.conv1d_causal_prefill(x.cuda(), ww.cuda())
+    assert torch.equal(whole, torch.cat([ya, yb]))
     _lib.check_device()
 
 
