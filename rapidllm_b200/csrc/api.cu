@@ -55,7 +55,7 @@ struct DevInfo {
 // streams) running such calls on one device never share events.
 struct AuxSet {
     cudaStream_t stream = nullptr;
-    cudaEvent_t fork[8] = {};
+    cudaEvent_t fork[32] = {};
     cudaEvent_t join = nullptr;
     bool used = false;              // join has been recorded at least once
 };
@@ -213,6 +213,7 @@ const int kF16SegWeight = knob("RL_B200_F16_SEG_WEIGHT", 6);
 // heads per launch from which the fused DeltaNet step streams whole heads through persistent CTAs
 const int kGdnStreamMin = knob("RL_B200_GDN_STREAM_MIN", 96);
 const int kGdnGrid = knob("RL_B200_GDN_GRID", 0);       // development builds: force the streaming form's grid
+const int kDeltaChunkSegs = knob("RL_B200_DELTA_SEGS", 0);   // development builds: force the segment count of the chunked prefill
 
 int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page_table,
                      const int32_t* seq_lens, const float* q, const float* gate, float* o, float* out_ml,
@@ -1216,16 +1217,19 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     a.v_tok_stride = p->v_tok_stride ? p->v_tok_stride : 1LL * p->n_v * p->dv;
     if ((a.qk_tok_stride | a.v_tok_stride) % 4 || a.qk_tok_stride < 0 || a.v_tok_stride < 0)
         return fail(RL_ERR_RANGE, "token strides must be non-negative multiples of 4 floats");
-    // The scan of a value head walks its chunks in order on one SM (48 CTAs), the chunk-local
-    // precompute fills the device: long sequences are cut into segments so that the scan of one
-    // segment (second stream, higher priority) runs beside the precompute of the next.
-    const int n_seg = n_chunks >= 32 ? 4 : (n_chunks >= 8 ? 2 : 1);
+    // The scan of a value head walks its chunks in order on one SM (n_v CTAs), the chunk-local
+    // precompute fills the device.  The sequence is cut into segments so that the scan of one segment
+    // (second stream, higher priority) runs beside the precompute of the next; a segment is as many
+    // chunks as give the SMs one wave of precompute CTAs (two per SM, one on the SMs that host a scan
+    // CTA).  What the key heads share is computed for all chunks first.
+    constexpr int kMaxSeg = int(sizeof(AuxSet::fork) / sizeof(AuxSet::fork[0]));
+    const int wave_chunks = std::max(1, (2 * d->sms - p->n_v) / p->n_v);
+    int n_seg = n_chunks <= wave_chunks + 1 ? 1 : std::min(kMaxSeg, (n_chunks + wave_chunks - 1) / wave_chunks);
+    if (kDeltaChunkSegs > 0) n_seg = std::max(1, std::min({kDeltaChunkSegs, kMaxSeg, n_chunks}));
     cudaStream_t run = as_stream(stream);
     auto prepare = [&](int c0, int n, cudaStream_t st) {
         a.chunk0 = c0;
         a.chunks = n;
-        rl::delta_chunk_keys_kernel<<<dim3(n, p->n_qk), rl::delta_chunk_prepare_threads(),
-                                      rl::delta_chunk_prepare_smem_bytes(), st>>>(a);
         rl::delta_chunk_prepare_kernel<<<dim3(n, p->n_v), rl::delta_chunk_prepare_threads(),
                                          rl::delta_chunk_prepare_smem_bytes(), st>>>(a);
     };
@@ -1234,6 +1238,10 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
         a.chunks = n;
         rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(), st>>>(a);
     };
+    a.chunk0 = 0;
+    a.chunks = n_chunks;
+    rl::delta_chunk_keys_kernel<<<dim3(n_chunks, p->n_qk), rl::delta_chunk_prepare_threads(),
+                                  rl::delta_chunk_prepare_smem_bytes(), run>>>(a);
     if (n_seg == 1) {
         prepare(0, n_chunks, run);
         scan(0, n_chunks, run);

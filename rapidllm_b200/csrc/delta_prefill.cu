@@ -97,7 +97,13 @@ struct PrepSmem {
         float v[kC][kPad];        // the chunk's value rows in fp32, once l and qk are no longer needed
     } w;
     float G[kC], beta[kC], eg[kC];
+    uint64_t bar;             // the key head's record has landed
 };
+// the struct from its start to the end of qk, padding included, is what the key head's pass hands to its
+// value heads (k^, q^, a gap where the union is larger than q^, k^.k^, q^.k^)
+constexpr int kKeysBytes = (kC * kPad + 2 * kC * kSq + 2 * kC * kSq) * 4;     // 103 424
+static_assert(offsetof(PrepSmem, w) + 2 * kC * kSq * 4 == kKeysBytes && kKeysBytes % 64 == 0,
+              "k^, q^, k^.k^, q^.k^ lie at the start of PrepSmem");
 
 // fp32 -> (fp16 high part, fp16 residual), two values per register
 __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
@@ -112,8 +118,9 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint3
 size_t delta_chunk_record_bytes() { return kRecordBytes; }
 
 // What a chunk's value heads share: per (chunk, key head) the normalised keys and queries and their
-// dot products.  Record: k^ [64][128], q^ [64][128], k^.k^ [64][64], q^.k^ [64][64], fp32.
-constexpr int kKeysFloats = 2 * kC * kD + 2 * kC * kC;
+// dot products.  Record: k^ [64][132], q^ [64][132], k^.k^ [64][68], q^.k^ [64][68], fp32 -- laid out
+// exactly as in shared memory (PrepSmem), so that a value head's CTA fetches the record with bulk copies.
+constexpr int kKeysFloats = kKeysBytes / 4;
 
 // grid (n_chunks, n_qk), 256 threads: l2 norms and the two 64 x 64 x 128 products once per key head
 // (the value heads that share it, 3 in qwen3_5, read the result instead of recomputing it).
@@ -208,18 +215,9 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(Delta
         }
     }
     __syncthreads();
-    __syncthreads();
-    // rows out, unpadded
-    for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
-        const int t = idx >> 5, d = (idx & 31) * 4;
-        *reinterpret_cast<float4*>(rec + t * kD + d) = *reinterpret_cast<const float4*>(&s.kn[t][d]);
-        *reinterpret_cast<float4*>(rec + kC * kD + t * kD + d) = *reinterpret_cast<const float4*>(&s.u.qn[t][d]);
-    }
-    for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
-        const int t = idx >> 4, i = (idx & 15) * 4;
-        *reinterpret_cast<float4*>(rec + 2 * kC * kD + t * kC + i) = *reinterpret_cast<const float4*>(&s.w.d.l[t][i]);
-        *reinterpret_cast<float4*>(rec + 2 * kC * kD + kC * kC + t * kC + i) = *reinterpret_cast<const float4*>(&s.w.d.qk[t][i]);
-    }
+    // the four arrays out as they lie (the padding columns carry whatever shared memory held; nobody reads them)
+    const float4* src = reinterpret_cast<const float4*>(smem_raw);
+    for (int idx = tid; idx < kKeysBytes / 16; idx += kPrepThreads) reinterpret_cast<float4*>(rec)[idx] = src[idx];
 }
 
 // grid (n_chunks, n_v), 256 threads: one CTA per chunk and value head.  103 KB of shared memory, so
@@ -235,6 +233,16 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
     const int n_tok = min(kC, a.T - t0);
     unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
 
+    // ---- what the key head's pass left (k^, q^, k^.k^, q^.k^) comes in by bulk copies beside the gates ----
+    if (tid == 0) {
+        mbar_init(&s.bar, 1);
+        mbar_fence_init();
+        mbar_arrive_expect_tx(&s.bar, kKeysBytes);
+        const unsigned char* keys = reinterpret_cast<const unsigned char*>(a.keys + (size_t(chunk) * a.n_qk + hs) * kKeysFloats);
+        constexpr int kPiece = kKeysBytes / 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) bulk_g2s(smem_raw + i * kPiece, keys + i * kPiece, kPiece, &s.bar);
+    }
     // ---- cumulative log decay, beta (needed by every tile) ----
     if (tid < kC) {
         const bool live = tid < n_tok;
@@ -247,22 +255,12 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
         }
         s.G[tid] = gl;
     }
-    // ---- what the key head's pass left: k^, q^, k^.k^, q^.k^ ----
-    {
-        const float* keys = a.keys + (size_t(chunk) * a.n_qk + hs) * kKeysFloats;
-        for (int idx = tid; idx < kC * kD / 4; idx += kPrepThreads) {
-            const int t = idx >> 5, d = (idx & 31) * 4;
-            *reinterpret_cast<float4*>(&s.kn[t][d]) = *reinterpret_cast<const float4*>(keys + t * kD + d);
-            *reinterpret_cast<float4*>(&s.u.qn[t][d]) = *reinterpret_cast<const float4*>(keys + kC * kD + t * kD + d);
-        }
-        for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
-            const int t = idx >> 4, i = (idx & 15) * 4;
-            *reinterpret_cast<float4*>(&s.w.d.l[t][i]) = *reinterpret_cast<const float4*>(keys + 2 * kC * kD + t * kC + i);
-            *reinterpret_cast<float4*>(&s.w.d.qk[t][i]) = *reinterpret_cast<const float4*>(keys + 2 * kC * kD + kC * kC + t * kC + i);
-        }
-    }
     __syncthreads();
     if (tid >= 32 && tid < kC) s.G[tid] += s.G[31];
+    if (!mbar_wait(&s.bar, 0)) {
+        set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+        return;
+    }
     __syncthreads();
     if (tid < kC) s.eg[tid] = expf(s.G[tid]);
     if (tid == 0) a.chunk_decay[size_t(chunk) * a.n_v + h] = expf(s.G[kC - 1]);
@@ -290,90 +288,146 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
     __syncthreads();                                  // q^ is dead from here on: its space becomes m and tmp
     float (*m)[kSq] = s.u.inv.m;
     float (*tmp)[kSq] = s.u.inv.tmp;
-    // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t, in place ----
-    for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
-        const int t = idx >> 6, i = idx & 63;
-        s.w.d.l[t][i] = i < t ? s.beta[t] * expf(s.G[t] - s.G[i]) * s.w.d.l[t][i] : 0.f;
-        m[t][i] = t == i ? 1.f : 0.f;
+    // ---- A_ti = beta_t exp(G_t - G_i) (k^_t . k^_i), i < t, in place (four columns per thread and pass) ----
+    for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
+        const int t = idx >> 4, i = (idx & 15) * 4;
+        const float4 kk = *reinterpret_cast<const float4*>(&s.w.d.l[t][i]);
+        const float4 gi = *reinterpret_cast<const float4*>(&s.G[i]);
+        const float gt = s.G[t], bt = s.beta[t];
+        float4 av;
+        av.x = i < t ? bt * expf(gt - gi.x) * kk.x : 0.f;
+        av.y = i + 1 < t ? bt * expf(gt - gi.y) * kk.y : 0.f;
+        av.z = i + 2 < t ? bt * expf(gt - gi.z) * kk.z : 0.f;
+        av.w = i + 3 < t ? bt * expf(gt - gi.w) * kk.w : 0.f;
+        *reinterpret_cast<float4*>(&s.w.d.l[t][i]) = av;
+        *reinterpret_cast<float4*>(&m[t][i]) = make_float4(t == i ? 1.f : 0.f, t == i + 1 ? 1.f : 0.f, t == i + 2 ? 1.f : 0.f,
+                                                           t == i + 3 ? 1.f : 0.f);
     }
     __syncthreads();
     // ---- M = (I + A)^-1 with all 256 threads and a dozen barriers ----
     // (1) the four 16 x 16 diagonal blocks: N = strictly lower part is nilpotent (N^16 = 0), so
-    //     (I + N)^-1 = (I - N)(I + N^2)(I + N^4)(I + N^8): five small products, element (x, y) of
-    //     block u per thread.  L, T, M below are the block's tiles of s.l, tmp, m.
+    //     (I + N)^-1 = (I - N)(I + N^2)(I + N^4)(I + N^8): six small products.  64 threads per block, each
+    //     row x, columns y0 .. y0+3 (one scalar and one 16-byte load per four multiply-adds).
     {
-        const int x = tid >> 4, y = tid & 15;
-#define RL_L(r, c) s.w.d.l[bb + (r)][bb + (c)]
-#define RL_T(r, c) tmp[bb + (r)][bb + (c)]
-#define RL_M(r, c) m[bb + (r)][bb + (c)]
-#define RL_BLOCKS(BODY)                    \
-    _Pragma("unroll") for (int u = 0; u < 4; ++u) { \
-        const int bb = u * kB;             \
-        BODY                               \
-    }                                      \
-    __syncthreads();
-        RL_BLOCKS({ float acc = 0.f; for (int k = 0; k < kB; ++k) acc += RL_L(x, k) * RL_L(k, y); RL_T(x, y) = acc; })          // T = N^2
-        RL_BLOCKS({ float acc = (x == y ? 1.f : 0.f) - RL_L(x, y);
-                    for (int k = 0; k < kB; ++k) acc += ((x == k ? 1.f : 0.f) - RL_L(x, k)) * RL_T(k, y);
-                    RL_M(x, y) = acc; })                                                                                    // M = (I - N)(I + N^2)
-        RL_BLOCKS({ float acc = 0.f; for (int k = 0; k < kB; ++k) acc += RL_T(x, k) * RL_T(k, y); RL_L(x, y) = acc; })          // L = N^4
-        RL_BLOCKS({ float acc = RL_M(x, y); for (int k = 0; k < kB; ++k) acc += RL_M(x, k) * RL_L(k, y); RL_T(x, y) = acc; })   // T = M (I + N^4)
-        RL_BLOCKS({ float acc = 0.f; for (int k = 0; k < kB; ++k) acc += RL_L(x, k) * RL_L(k, y); RL_M(x, y) = acc; })          // M = N^8
-        RL_BLOCKS({ float acc = RL_T(x, y); for (int k = 0; k < kB; ++k) acc += RL_T(x, k) * RL_M(k, y); RL_L(x, y) = acc; })   // L = T (I + N^8): the inverse
-        RL_BLOCKS({ RL_M(x, y) = RL_L(x, y); })
-#undef RL_BLOCKS
-#undef RL_M
-#undef RL_T
-#undef RL_L
+        const int bb = (tid >> 6) * kB, x = (tid & 63) >> 2, y0 = (tid & 3) * 4;
+        float (*L)[kSq] = s.w.d.l;
+        // acc[j] += sum_k a(k) B[bb + k][bb + y0 + j]
+        auto mm16 = [&](float (&acc)[4], auto a_of_k, const float (*B)[kSq]) {
+#pragma unroll
+            for (int k = 0; k < kB; ++k) {
+                const float av = a_of_k(k);
+                const float4 bv = *reinterpret_cast<const float4*>(&B[bb + k][bb + y0]);
+                acc[0] += av * bv.x; acc[1] += av * bv.y; acc[2] += av * bv.z; acc[3] += av * bv.w;
+            }
+        };
+        auto put = [&](float (*D)[kSq], const float (&acc)[4]) {
+            *reinterpret_cast<float4*>(&D[bb + x][bb + y0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        };
+        auto get = [&](const float (*D)[kSq], float (&acc)[4]) {
+            const float4 v = *reinterpret_cast<const float4*>(&D[bb + x][bb + y0]);
+            acc[0] = v.x; acc[1] = v.y; acc[2] = v.z; acc[3] = v.w;
+        };
+        float acc[4];
+        // tmp = N^2
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        mm16(acc, [&](int k) { return L[bb + x][bb + k]; }, L);
+        put(tmp, acc);
+        __syncthreads();
+        // m = (I - N)(I + N^2)
+        get(L, acc);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = (x == y0 + j ? 1.f : 0.f) - acc[j];
+        mm16(acc, [&](int k) { return (x == k ? 1.f : 0.f) - L[bb + x][bb + k]; }, tmp);
+        put(m, acc);
+        __syncthreads();
+        // l = N^4
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        mm16(acc, [&](int k) { return tmp[bb + x][bb + k]; }, tmp);
+        put(L, acc);
+        __syncthreads();
+        // tmp = m (I + N^4)
+        get(m, acc);
+        mm16(acc, [&](int k) { return m[bb + x][bb + k]; }, L);
+        put(tmp, acc);
+        __syncthreads();
+        // m = N^8
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        mm16(acc, [&](int k) { return L[bb + x][bb + k]; }, L);
+        put(m, acc);
+        __syncthreads();
+        // m = tmp (I + N^8): the inverse of the block (through registers: m is read by other threads until the barrier)
+        get(tmp, acc);
+        mm16(acc, [&](int k) { return tmp[bb + x][bb + k]; }, m);
+        __syncthreads();
+        put(m, acc);
+        __syncthreads();
+    }
+    {
         // (2) off-diagonal blocks from inv [[P, 0], [C, Q]] = [[P^-1, 0], [-Q^-1 C P^-1, Q^-1]], first
         //     for the two 32 x 32 halves (C = a 16 x 16 block of A), then for the whole (C = 32 x 32)
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        {
+            const int u = tid >> 7, x = (tid & 127) >> 3, y0 = (tid & 7) * 2;
             const int bi = (2 * u + 1) * kB, bj = 2 * u * kB;
-            float acc = 0.f;
-            for (int k = 0; k < kB; ++k) acc += s.w.d.l[bi + x][bj + k] * m[bj + k][bj + y];
-            tmp[bi + x][bj + y] = acc;
-        }
-        __syncthreads();
+            float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int bi = (2 * u + 1) * kB, bj = 2 * u * kB;
-            float acc = 0.f;
-            for (int k = 0; k < kB; ++k) acc -= m[bi + x][bi + k] * tmp[bi + k][bj + y];
-            m[bi + x][bj + y] = acc;
-        }
-        __syncthreads();
-        const int x2 = tid >> 5, y2 = tid & 31;                 // rows 32 + x2 + 8 u, column y2
+            for (int k = 0; k < kB; ++k) {
+                const float av = s.w.d.l[bi + x][bj + k];
+                const float2 bv = *reinterpret_cast<const float2*>(&m[bj + k][bj + y0]);
+                a0 += av * bv.x; a1 += av * bv.y;
+            }
+            *reinterpret_cast<float2*>(&tmp[bi + x][bj + y0]) = make_float2(a0, a1);
+            __syncthreads();
+            a0 = a1 = 0.f;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int r = 32 + x2 + 8 * u;
-            float acc = 0.f;
-            for (int k = 0; k < 32; ++k) acc += s.w.d.l[r][k] * m[k][y2];
-            tmp[r][y2] = acc;
+            for (int k = 0; k < kB; ++k) {
+                const float av = m[bi + x][bi + k];
+                const float2 bv = *reinterpret_cast<const float2*>(&tmp[bi + k][bj + y0]);
+                a0 -= av * bv.x; a1 -= av * bv.y;
+            }
+            *reinterpret_cast<float2*>(&m[bi + x][bj + y0]) = make_float2(a0, a1);
+            __syncthreads();
         }
+        const int r = 32 + (tid >> 3), y0 = (tid & 7) * 4;        // row r, columns y0 .. y0+3 of the lower left quarter
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float av = s.w.d.l[r][k];
+            const float4 bv = *reinterpret_cast<const float4*>(&m[k][y0]);
+            acc[0] += av * bv.x; acc[1] += av * bv.y; acc[2] += av * bv.z; acc[3] += av * bv.w;
+        }
+        *reinterpret_cast<float4*>(&tmp[r][y0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         __syncthreads();
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int r = 32 + x2 + 8 * u;
-            float acc = 0.f;
-            for (int k = 0; k < 32; ++k) acc -= m[r][32 + k] * tmp[32 + k][y2];
-            m[r][y2] = acc;
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float av = m[r][32 + k];
+            const float4 bv = *reinterpret_cast<const float4*>(&tmp[32 + k][y0]);
+            acc[0] -= av * bv.x; acc[1] -= av * bv.y; acc[2] -= av * bv.z; acc[3] -= av * bv.w;
         }
+        *reinterpret_cast<float4*>(&m[r][y0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         __syncthreads();
     }
-    // ---- tile P (64 x 64, fp16, swizzled) ----
-    for (int idx = tid; idx < kC * kC / 2; idx += kPrepThreads) {
-        const int t = idx >> 5, i = (idx & 31) * 2;
-        const float p0 = i <= t ? expf(s.G[t] - s.G[i]) * s.w.d.qk[t][i] : 0.f;
-        const float p1 = i + 1 <= t ? expf(s.G[t] - s.G[i + 1]) * s.w.d.qk[t][i + 1] : 0.f;
-        *reinterpret_cast<uint32_t*>(rec + kOffPartC + kOffP + tile_off(t, i)) = pack_h2(p0, p1);
+    // ---- tile P (64 x 64, fp16, swizzled), four columns per thread and pass ----
+    for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
+        const int t = idx >> 4, i = (idx & 15) * 4;
+        const float4 qk = *reinterpret_cast<const float4*>(&s.w.d.qk[t][i]);
+        const float4 gi = *reinterpret_cast<const float4*>(&s.G[i]);
+        const float gt = s.G[t];
+        const float p0 = i <= t ? expf(gt - gi.x) * qk.x : 0.f;
+        const float p1 = i + 1 <= t ? expf(gt - gi.y) * qk.y : 0.f;
+        const float p2 = i + 2 <= t ? expf(gt - gi.z) * qk.z : 0.f;
+        const float p3 = i + 3 <= t ? expf(gt - gi.w) * qk.w : 0.f;
+        *reinterpret_cast<uint2*>(rec + kOffPartC + kOffP + tile_off(t, i)) = make_uint2(pack_h2(p0, p1), pack_h2(p2, p3));
     }
     // T = M diag(beta) in place, and tmp[t][i] = T[t][i] exp(G_i) for W
-    for (int idx = tid; idx < kC * kC; idx += kPrepThreads) {
-        const int t = idx >> 6, i = idx & 63;
-        const float tv = m[t][i] * s.beta[i];
-        m[t][i] = tv;
-        tmp[t][i] = tv * s.eg[i];
+    for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
+        const int t = idx >> 4, i = (idx & 15) * 4;
+        const float4 mv = *reinterpret_cast<const float4*>(&m[t][i]);
+        const float4 bv = *reinterpret_cast<const float4*>(&s.beta[i]);
+        const float4 ev = *reinterpret_cast<const float4*>(&s.eg[i]);
+        const float4 tv = make_float4(mv.x * bv.x, mv.y * bv.y, mv.z * bv.z, mv.w * bv.w);
+        *reinterpret_cast<float4*>(&m[t][i]) = tv;
+        *reinterpret_cast<float4*>(&tmp[t][i]) = make_float4(tv.x * ev.x, tv.y * ev.y, tv.z * ev.z, tv.w * ev.w);
     }
     __syncthreads();                                  // l and qk are dead: their space takes the value rows
     {
@@ -450,7 +504,9 @@ int delta_chunk_prepare_threads() { return kPrepThreads; }
 // ================================================================================================
 namespace {
 
-constexpr int kScanThreads = 192;         // 4 worker warps (lane = value dim) + loader warp + MMA warp
+constexpr int kScanWorkers = 256;         // 8 worker warps: TMEM lane = value dim, two warps per lane quadrant split the columns
+constexpr int kScanThreads = kScanWorkers + 64;   // + loader warp + MMA warp
+constexpr int kWarpScanLoader = kScanWorkers / 32, kWarpScanMma = kWarpScanLoader + 1;
 constexpr int kStagesA = 1, kStagesC = 1;
 // tensor memory map (columns); lane = value dim
 constexpr uint32_t kColSt = 0;            // S^T fp32, 128 columns (column = key dim)
@@ -486,9 +542,7 @@ struct ScanSmem {
 // (S^T += D^T Kt) -> workers split the new S^T.  The output products (S^T Qg^T before D is known,
 // D^T P^T after the state update) are issued behind the chain's MMAs and read out by the workers while
 // the next chunk's first MMAs run.
-// (launch bounds for two CTAs per SM: not to run two scans side by side -- tensor memory has room for one --
-// but to keep the registers low enough that a prepare CTA of the next segment fits beside a scan CTA)
-__global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(DeltaChunkArgs a) {
+__global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     ScanSmem& s = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int h = blockIdx.x;
@@ -506,23 +560,23 @@ __global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(Delta
             mbar_init(&s.empty_c[i], 1);
         }
         mbar_init(&s.full_b, 1);
-        mbar_init(&s.empty_b, 128);
-        mbar_init(&s.bar_s, 128);
+        mbar_init(&s.empty_b, kScanWorkers);
+        mbar_init(&s.bar_s, kScanWorkers);
         mbar_init(&s.bar_w, 1);
-        mbar_init(&s.bar_d, 128);
+        mbar_init(&s.bar_d, kScanWorkers);
         mbar_init(&s.bar_k, 1);
         mbar_init(&s.bar_o, 1);
-        mbar_init(&s.bar_oread, 128);
+        mbar_init(&s.bar_oread, kScanWorkers);
         s.failed = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tc::tmem_alloc(&s.tmem_base, 512);
+    if (warp == kWarpScanMma) tc::tmem_alloc(&s.tmem_base, 512);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = s.tmem_base;
 
-    if (warp == 4) {
+    if (warp == kWarpScanLoader) {
         // ------------------------------ loader ------------------------------
         if (lane == 0) {
             for (int c = 0; c < n_chunks; ++c) {
@@ -540,7 +594,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(Delta
             }
             if (s.failed) set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
         }
-    } else if (warp == 5) {
+    } else if (warp == kWarpScanMma) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t id_n64 = tc::idesc_f16(128, kC, false, false);           // A from TMEM, B K-major
@@ -617,18 +671,20 @@ __global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(Delta
             }
         }
     } else {
-        // ------------------------------ workers: thread = value dim j = TMEM lane ------------------------------
-        // Every pass over tensor memory issues all its loads before it waits once, so a pass costs one
-        // load latency, not one per 32 columns.
-        const int j = tid;
-        const uint32_t lane_addr = tmem + (uint32_t(warp * 32) << 16);
+        // ------------------------------ workers: thread = (value dim j = TMEM lane, half of the columns) ------------------------------
+        // A warp reaches the 32 lanes of its quadrant (warp % 4); the two warps of a quadrant take one half
+        // of every pass's columns each, so a pass is half as long as with one thread per lane.  Every pass
+        // issues all its tensor-memory loads before it waits once.
+        const int wq = warp & 3, half = warp >> 2;
+        const int j = wq * 32 + lane;
+        const uint32_t lane_addr = tmem + (uint32_t(wq * 32) << 16);
         bool ok = true;
         // S_0^T into tensor memory: hi/lo of S_0 for the first chunk's products, and S_0 exp(G_C) of the
         // first chunk as the accumulator S^T += D^T Kt adds to.  Column i of lane j = S[i][j].
         {
             const float decay0 = a.chunk_decay[size_t(a.chunk0) * a.n_v + h];
 #pragma unroll 1
-            for (int c0 = 0; c0 < kD; c0 += 32) {
+            for (int c0 = 64 * half; c0 < 64 * half + 64; c0 += 32) {
                 uint32_t f[32], hi[16], lo[16];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) f[i] = __float_as_uint(Sg[size_t(c0 + i) * kD + j]);
@@ -660,20 +716,15 @@ __global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(Delta
             tc::fence_after_sync();
             // D^T = (T V)^T - S^T W^T -> hi/lo A operands; (T V)[t][j] comes from shared memory in fp32
             {
-                uint32_t f[2][32];
-                tc::tmem_ld32(lane_addr + kColD, f[0]);
-                tc::tmem_ld32(lane_addr + kColD + 32, f[1]);
+                uint32_t f[32], hi[16], lo[16];
+                tc::tmem_ld32(lane_addr + kColD + 32 * half, f);
                 tc::tmem_wait_ld();
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    uint32_t hi[16], lo[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        split_h2(__uint_as_float(f[q][2 * i]) + tv[(32 * q + 2 * i) * kD + j],
-                                 __uint_as_float(f[q][2 * i + 1]) + tv[(32 * q + 2 * i + 1) * kD + j], hi[i], lo[i]);
-                    tc::tmem_st16(lane_addr + kColDhi + 16 * q, hi);
-                    tc::tmem_st16(lane_addr + kColDlo + 16 * q, lo);
-                }
+                for (int i = 0; i < 16; ++i)
+                    split_h2(__uint_as_float(f[2 * i]) + tv[(32 * half + 2 * i) * kD + j],
+                             __uint_as_float(f[2 * i + 1]) + tv[(32 * half + 2 * i + 1) * kD + j], hi[i], lo[i]);
+                tc::tmem_st16(lane_addr + kColDhi + 16 * half, hi);
+                tc::tmem_st16(lane_addr + kColDlo + 16 * half, lo);
             }
             tc::tmem_wait_st();
             tc::fence_before_sync();
@@ -687,29 +738,29 @@ __global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(Delta
             // the new S^T: hi/lo for the next chunk's products and, times the next chunk's exp(G_C), the
             // accumulator its state update adds to (or back to the cache after the last chunk)
             {
-                uint32_t f[4][32];
+                uint32_t f[2][32];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) tc::tmem_ld32(lane_addr + kColSt + 32 * q, f[q]);
+                for (int q = 0; q < 2; ++q) tc::tmem_ld32(lane_addr + kColSt + 32 * (2 * half + q), f[q]);
                 tc::tmem_wait_ld();
                 if (last) {
                     if (ok && !s.failed) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q)
+                        for (int q = 0; q < 2; ++q)
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) Sg[size_t(32 * q + i) * kD + j] = __uint_as_float(f[q][i]);
+                            for (int i = 0; i < 32; ++i) Sg[size_t(32 * (2 * half + q) + i) * kD + j] = __uint_as_float(f[q][i]);
                     }
                 } else {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < 2; ++q) {
                         uint32_t hi[16], lo[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
                             split_h2(__uint_as_float(f[q][2 * i]), __uint_as_float(f[q][2 * i + 1]), hi[i], lo[i]);
-                        tc::tmem_st16(lane_addr + kColShi + 16 * q, hi);
-                        tc::tmem_st16(lane_addr + kColSlo + 16 * q, lo);
+                        tc::tmem_st16(lane_addr + kColShi + 16 * (2 * half + q), hi);
+                        tc::tmem_st16(lane_addr + kColSlo + 16 * (2 * half + q), lo);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) f[q][i] = __float_as_uint(__uint_as_float(f[q][i]) * next_decay);
-                        tc::tmem_st32(lane_addr + kColSt + 32 * q, f[q]);
+                        tc::tmem_st32(lane_addr + kColSt + 32 * (2 * half + q), f[q]);
                     }
                     tc::tmem_wait_st();
                 }
@@ -724,23 +775,20 @@ __global__ void __launch_bounds__(kScanThreads, 2) delta_chunk_scan_kernel(Delta
             tc::fence_after_sync();
             const int t0 = (a.chunk0 + c) * kC;
             {
-                uint32_t f[2][32];
-                tc::tmem_ld32(lane_addr + kColO, f[0]);
-                tc::tmem_ld32(lane_addr + kColO + 32, f[1]);
+                uint32_t f[32];
+                tc::tmem_ld32(lane_addr + kColO + 32 * half, f);
                 tc::tmem_wait_ld();
                 tc::fence_before_sync();
                 mbar_arrive(&s.bar_oread);                     // O^T is in registers: its columns may be overwritten
 #pragma unroll
-                for (int q = 0; q < 2; ++q)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (ok && t0 + 32 * q + i < a.T) a.o[(size_t(t0 + 32 * q + i) * a.n_v + h) * kD + j] = __uint_as_float(f[q][i]);
+                for (int i = 0; i < 32; ++i)
+                    if (ok && t0 + 32 * half + i < a.T) a.o[(size_t(t0 + 32 * half + i) * a.n_v + h) * kD + j] = __uint_as_float(f[i]);
             }
         }
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 5) tc::tmem_dealloc(tmem, 512);
+    if (warp == kWarpScanMma) tc::tmem_dealloc(tmem, 512);
 }
 
 size_t delta_chunk_scan_smem_bytes() { return sizeof(ScanSmem) + 1024; }
