@@ -553,9 +553,9 @@ def op_delta_prefill(args, sampler, peaks, gen):
     return {
         "workload": "gated DeltaNet chunked (WY, chunk 64) prefill, T %d, batch 1, 16K/48V heads 128x128" % T,
         "ms": ms, "value": T / (ms * 1e-3), "unit": "tokens/s (one layer)", "calls_timed": calls,
-        "dtype": "f16 hi+lo operands / f32 state", "gpu_launches_per_call": 2 * (4 if n_chunks >= 32 else 1),
+        "dtype": "f16 hi+lo operands / f32 state", "gpu_launches_per_call": 1 + 2 * (1 if n_chunks < 32 else (2 if n_chunks < 64 else (3 if n_chunks < 128 else 4))),
         "l2": "operands streamed once (%.2f GB workspace)" % (ws.numel() / 1e9),
-        "timed": "prepare + scan kernels of one call, back to back",
+        "timed": "keys + prepare + scan kernels of one call, back to back",
         "roofline": _tensor_roofline("delta_chunk_scan_kernel + delta_chunk_prepare_kernel", flops, ms, peaks,
                                      "flops = tensor-core MMAs the scan kernel issues per (chunk, value head) x chunks x "
                                      "heads; the chunk-to-chunk dependency, not tensor throughput, bounds the operator"),
@@ -605,7 +605,9 @@ def op_stack_prefill(args, sampler, peaks, gen):
                     "mixers only (no projections / MLP)" % (len(types), cache.n_attn, cache.n_delta, T, chunk),
         "ms": ms, "value": T / (ms * 1e-3), "unit": "tokens/s", "calls_timed": calls,
         "dtype": "f16 attention (bf16 in) / f16 hi+lo + f32 state DeltaNet",
-        "gpu_launches_per_call": n_chunks * (cache.n_attn * 2 + cache.n_delta * 4),
+        # attention: append + prefill (+ the merge of the divided last wave from the second chunk on);
+        # DeltaNet: conv, keys, prepare, scan
+        "gpu_launches_per_call": n_chunks * (cache.n_attn * 2 + cache.n_delta * 4) + (n_chunks - 1) * cache.n_attn,
         "l2": "per-chunk inputs of all layers (%.1f GB) exceed L2" % (sum(x.numel() * x.element_size() for x in t.values()) / 1e9),
         "timed": "rl_stack_prefill of every chunk, back to back",
         "roofline": _tensor_roofline("attn_prefill_kernel (attention layers' flops only)", flops_attn, ms, peaks,

@@ -505,9 +505,10 @@ int delta_chunk_prepare_threads() { return kPrepThreads; }
 namespace {
 
 constexpr int kScanWorkers = 256;         // 8 worker warps: TMEM lane = value dim, two warps per lane quadrant split the columns
-constexpr int kScanThreads = kScanWorkers + 64;   // + loader warp + MMA warp
-constexpr int kWarpScanLoader = kScanWorkers / 32, kWarpScanMma = kWarpScanLoader + 1;
-constexpr int kStagesA = 1, kStagesC = 1;
+constexpr int kScanOutput = 128;          // 4 output warps (one per lane quadrant) write o while the chain goes on
+constexpr int kScanThreads = kScanWorkers + kScanOutput + 64;   // + loader warp + MMA warp
+constexpr int kWarpScanOut0 = kScanWorkers / 32, kWarpScanLoader = (kScanWorkers + kScanOutput) / 32, kWarpScanMma = kWarpScanLoader + 1;
+constexpr int kStagesA = 2, kStagesC = 1;
 // tensor memory map (columns); lane = value dim
 constexpr uint32_t kColSt = 0;            // S^T fp32, 128 columns (column = key dim)
 constexpr uint32_t kColShi = 128;         // fp16 pairs: 64 columns
@@ -521,8 +522,9 @@ struct ScanSmem {
     alignas(1024) unsigned char pa[kStagesA][kPartABytes];   // W hi, W lo, Qg
     alignas(1024) unsigned char pc[kStagesC][kPartCBytes];   // P, Kt hi, Kt lo
     alignas(1024) unsigned char pb[kPartBBytes];             // T V fp32
+    alignas(16) float ostage[kC][kD];                        // O of a chunk, token-major, on its way out
     uint64_t full_a[kStagesA], empty_a[kStagesA], full_c[kStagesC], empty_c[kStagesC], full_b, empty_b;
-    uint64_t bar_s;      // workers -> MMA: S hi/lo of the chunk are in tensor memory
+    uint64_t bar_s[2];   // workers -> MMA: S hi/lo of the chunk are in tensor memory ([0]: key dims 0-31 and 64-95, [1]: the rest)
     uint64_t bar_w;      // MMA -> workers: -S^T W^T is complete
     uint64_t bar_d;      // workers -> MMA: D hi/lo are in tensor memory
     uint64_t bar_k;      // MMA -> workers: S^T += D^T Kt is complete
@@ -560,13 +562,16 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             mbar_init(&s.empty_c[i], 1);
         }
         mbar_init(&s.full_b, 1);
-        mbar_init(&s.empty_b, kScanWorkers);
-        mbar_init(&s.bar_s, kScanWorkers);
+        // the worker and output warps arrive once per warp (lane 0, behind a __syncwarp): 256 single arrivals on
+        // one barrier word took ~600 clocks of every hand-over
+        mbar_init(&s.empty_b, kScanWorkers / 32);
+        mbar_init(&s.bar_s[0], kScanWorkers / 32);
+        mbar_init(&s.bar_s[1], kScanWorkers / 32);
         mbar_init(&s.bar_w, 1);
-        mbar_init(&s.bar_d, kScanWorkers);
+        mbar_init(&s.bar_d, kScanWorkers / 32);
         mbar_init(&s.bar_k, 1);
         mbar_init(&s.bar_o, 1);
-        mbar_init(&s.bar_oread, kScanWorkers);
+        mbar_init(&s.bar_oread, kScanOutput / 32);
         s.failed = 0;
         mbar_fence_init();
     }
@@ -617,18 +622,24 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             for (int c = 0; c < n_chunks && ok; ++c) {
                 const int sa = c % kStagesA, sc = c % kStagesC;
                 if (!mbar_wait(&s.full_a[sa], (c / kStagesA) & 1)) { ok = false; break; }
-                if (!mbar_wait(&s.bar_s, c & 1)) { ok = false; break; }                 // S hi/lo ready
-                tc::fence_after_sync();
                 const uint64_t ka = a_desc[kStagesA > 1 ? sa : 0];
-                // -S^T W^T with hi*hi + lo*hi + hi*lo: K = 128 key dims in 8 steps
+                // -S^T W^T with hi*hi + lo*hi + hi*lo: K = 128 key dims in 8 steps, taken in the order in which
+                // the workers hand the split state over (each warp its first 32 key dims, then its second 32)
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t off = uint64_t(((kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
-                    const uint64_t bw = ka + uint64_t(kOffW >> 4) + off, bwl = ka + uint64_t(kOffWlo >> 4) + off;
-                    tc::mma_ts(t_d, t_shi + kk * 8, bw, id_n64_neg, kk > 0);
-                    tc::mma_ts(t_d, t_slo + kk * 8, bw, id_n64_neg, 1);
-                    tc::mma_ts(t_d, t_shi + kk * 8, bwl, id_n64_neg, 1);
+                for (int grp = 0; grp < 2; ++grp) {
+                    if (!mbar_wait(&s.bar_s[grp], c & 1)) { ok = false; break; }        // S hi/lo of these key dims ready
+                    tc::fence_after_sync();
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int kk = (u >> 1) * 4 + grp * 2 + (u & 1);                // 0, 1, 4, 5 then 2, 3, 6, 7
+                        const uint64_t off = uint64_t(((kk >> 2) * (kC * 128) + (kk & 3) * 32) >> 4);
+                        const uint64_t bw = ka + uint64_t(kOffW >> 4) + off, bwl = ka + uint64_t(kOffWlo >> 4) + off;
+                        tc::mma_ts(t_d, t_shi + kk * 8, bw, id_n64_neg, (grp | u) > 0);
+                        tc::mma_ts(t_d, t_slo + kk * 8, bw, id_n64_neg, 1);
+                        tc::mma_ts(t_d, t_shi + kk * 8, bwl, id_n64_neg, 1);
+                    }
                 }
+                if (!ok) break;
                 tc::commit(&s.bar_w);
                 // O^T = S^T Qg^T: behind the chain's MMAs, while the workers form D.  The previous chunk's
                 // O^T must have been read out first.
@@ -670,6 +681,44 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
                 s.failed = 1;
             }
         }
+    } else if (warp >= kWarpScanOut0) {
+        // ------------------------------ output warps: o[t][h][j] = O^T[j][t], off the chain ------------------------------
+        const int wq = warp & 3;
+        const int j = wq * 32 + lane;
+        const uint32_t lane_addr = tmem + (uint32_t(wq * 32) << 16);
+        bool ok = true;
+        for (int c = 0; c < n_chunks; ++c) {
+            if (ok && !mbar_wait(&s.bar_o, c & 1)) {
+                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
+                ok = false;
+            }
+            tc::fence_after_sync();
+            const int t0 = (a.chunk0 + c) * kC;
+            uint32_t f[2][32];
+            tc::tmem_ld32(lane_addr + kColO, f[0]);
+            tc::tmem_ld32(lane_addr + kColO + 32, f[1]);
+            tc::tmem_wait_ld();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.bar_oread);          // O^T is in registers: its columns may be overwritten
+            // through shared memory, so that a warp writes whole 512-byte rows of o (one request per token
+            // instead of four, a quarter of the store instructions)
+            named_bar_sync(1, kScanOutput);                    // the previous chunk's rows have left the stage
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s.ostage[32 * q + i][j] = __uint_as_float(f[q][i]);
+            named_bar_sync(2, kScanOutput);
+            if (ok && !s.failed) {
+#pragma unroll
+                for (int i = 0; i < kC / 4; ++i) {
+                    const int t = wq * (kC / 4) + i;
+                    if (t0 + t < a.T)
+                        __stcs(reinterpret_cast<float4*>(a.o + (size_t(t0 + t) * a.n_v + h) * kD) + lane,
+                               *reinterpret_cast<const float4*>(&s.ostage[t][lane * 4]));
+                }
+            }
+        }
     } else {
         // ------------------------------ workers: thread = (value dim j = TMEM lane, half of the columns) ------------------------------
         // A warp reaches the 32 lanes of its quadrant (warp % 4); the two warps of a quadrant take one half
@@ -699,7 +748,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
         }
         tc::tmem_wait_st();
         tc::fence_before_sync();
-        mbar_arrive(&s.bar_s);
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(&s.bar_s[0]);
+            mbar_arrive(&s.bar_s[1]);
+        }
         const float* tv = reinterpret_cast<const float*>(s.pb);
         for (int c = 0; c < n_chunks; ++c) {
             const bool last = c == n_chunks - 1;
@@ -728,8 +781,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
             }
             tc::tmem_wait_st();
             tc::fence_before_sync();
-            mbar_arrive(&s.bar_d);
-            mbar_arrive(&s.empty_b);                           // T V has been read: the next chunk's may land
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&s.bar_d);
+                mbar_arrive(&s.empty_b);                       // T V has been read: the next chunk's may land
+            }
             if (ok && !mbar_wait(&s.bar_k, c & 1)) {
                 set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                 ok = false;
@@ -761,29 +817,16 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
 #pragma unroll
                         for (int i = 0; i < 32; ++i) f[q][i] = __float_as_uint(__uint_as_float(f[q][i]) * next_decay);
                         tc::tmem_st32(lane_addr + kColSt + 32 * (2 * half + q), f[q]);
+                        // hand these 32 key dims over: the first product's K steps over them start while the
+                        // other 32 are being split
+                        tc::tmem_wait_st();
+                        tc::fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&s.bar_s[q]);
                     }
-                    tc::tmem_wait_st();
                 }
             }
             tc::fence_before_sync();
-            if (!last) mbar_arrive(&s.bar_s);
-            // o[t][h][j] = O^T[j][t]: off the chain, while the next chunk's first MMAs run
-            if (ok && !mbar_wait(&s.bar_o, c & 1)) {
-                set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
-                ok = false;
-            }
-            tc::fence_after_sync();
-            const int t0 = (a.chunk0 + c) * kC;
-            {
-                uint32_t f[32];
-                tc::tmem_ld32(lane_addr + kColO + 32 * half, f);
-                tc::tmem_wait_ld();
-                tc::fence_before_sync();
-                mbar_arrive(&s.bar_oread);                     // O^T is in registers: its columns may be overwritten
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (ok && t0 + 32 * half + i < a.T) a.o[(size_t(t0 + 32 * half + i) * a.n_v + h) * kD + j] = __uint_as_float(f[i]);
-            }
         }
     }
     tc::fence_before_sync();
