@@ -869,6 +869,7 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
     a.kv_parts = parts;
     a.n_full = sp.tail_parts > 1 ? sp.n_full : 0;
     a.tail_parts = sp.tail_parts;
+    a.by_size = sp.items < 2LL * d->sms ? 1 : 0;
     a.wave = d->sms;
     a.part_o = divided ? static_cast<float*>(workspace) : nullptr;
     a.part_ml = divided ? reinterpret_cast<float*>(static_cast<char*>(workspace) + o_bytes) : nullptr;
@@ -881,8 +882,8 @@ static int attn_prefill_impl(void* k_pool, void* v_pool, const int32_t* page_tab
                                 dim3(unsigned(rl::attn_prefill_threads())), rl::attn_prefill_smem_bytes(), as_stream(stream), a));
         if (sp.tail_parts > 1 && parts <= 1)
             RL_CUDA(rl::launch_step(rl::attn_prefill_tail_merge_kernel,
-                                    dim3(unsigned(rl::attn_prefill_q_rows()), unsigned(sp.items - sp.n_full)),
-                                    dim3(unsigned(rl::kHeadDim)), 0, as_stream(stream), a));
+                                    dim3(unsigned(rl::attn_prefill_q_rows() / 8), unsigned(sp.items - sp.n_full)),
+                                    dim3(256), 0, as_stream(stream), a));   // 8 rows per block, a warp each
     }
     if (parts > 1)
         rl::lse_combine_kernel<<<unsigned(rows_total), 256, 0, as_stream(stream)>>>(a.part_o, a.part_ml, gate, o, parts,

@@ -63,6 +63,19 @@ constexpr int kQRowStride = kHeadDim * 2 + 16;
 constexpr int kQStageBytes = kQRows * kQRowStride;            // 67 584
 static_assert(kQStageBytes > 2 * kSliceBytes && kVStages >= 3, "Q staging = V stages 1, 2 + q_pad");
 
+// item of the launch order -> (query tile, query head)
+__device__ __forceinline__ void item_tile(const AttnPrefillArgs& a, int item, int n_qtiles, int& qt, int& hq) {
+    const int G = a.n_q / a.n_kv;
+    if (a.by_size) {
+        qt = n_qtiles - 1 - item / a.n_q;
+        hq = item % a.n_q;
+    } else {
+        const int per_kv = n_qtiles * G, hkv = item / per_kv, rem = item - hkv * per_kv;
+        qt = n_qtiles - 1 - rem / G;
+        hq = hkv * G + rem % G;
+    }
+}
+
 struct Smem {
     alignas(1024) unsigned char k[kKStages][kSliceBytes];     // K page slices
     alignas(1024) unsigned char v[kVStages][kSliceBytes];     // V page slices
@@ -87,7 +100,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     // running side by side read the same tiles), inside a KV head the longest jobs first: the
     // group's query heads of the last (heaviest) query tile, then of the one before, ...
     const int G = a.n_q / a.n_kv;
-    const int per_kv = n_qtiles * G;
     const bool tail = a.tail_parts > 1 && int(blockIdx.x) >= a.n_full;
     const int tail_unit = int(blockIdx.x) - a.n_full;
     const int parts = tail ? a.tail_parts : (a.kv_parts > 1 ? a.kv_parts : 1);
@@ -95,10 +107,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     const int part = tail ? tail_unit % parts : int(blockIdx.x) - item * parts;
     // packed (a few rows, e.g. a speculative verify): one item per KV head, its MMA rows are
     // (token, query head of the group) pairs, so the group's heads share one pass over K/V
-    const int hkv = a.packed ? item : item / per_kv;
-    const int rem = a.packed ? 0 : item - hkv * per_kv;
-    const int qt = a.packed ? 0 : n_qtiles - 1 - rem / G;
-    const int hq = hkv * G + rem % G;
+    int qt = 0, hq = item * G;
+    if (!a.packed) item_tile(a, item, n_qtiles, qt, hq);
+    const int hkv = hq / G;
     const int q0 = qt * kQRows;                               // first query row of this CTA
     const int rows = a.packed ? a.T * G : min(kQRows, a.T - q0);
     const int last_pos = a.packed ? a.pos0 + a.T - 1 : a.pos0 + q0 + rows - 1;   // position of the last query row
@@ -155,8 +166,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
         // the launch order: start its Q rows on their way into L2.
         const int nxt = int(blockIdx.x) + int(a.wave);
         if (!a.packed && parts == 1 && nxt < (a.tail_parts > 1 ? a.n_full : int(gridDim.x))) {
-            const int n_hkv = nxt / per_kv, n_rem = nxt - n_hkv * per_kv;
-            const int n_q0 = (n_qtiles - 1 - n_rem / G) * kQRows, n_hq = n_hkv * G + n_rem % G;
+            int n_qt, n_hq;
+            item_tile(a, nxt, n_qtiles, n_qt, n_hq);
+            const int n_q0 = n_qt * kQRows;
             const int n_rows = min(kQRows, a.T - n_q0);
             for (int i = lane; i < n_rows * 4; i += 32) {     // 4 lines of 128 bytes per row
                 const __nv_bfloat16* pq = a.q + (size_t(n_q0 + (i >> 2)) * a.n_q + n_hq) * kHeadDim + (i & 3) * 64;
@@ -519,32 +531,59 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_kernel(AttnPrefillAr
     if (warp == kWarpQK) tc::tmem_dealloc(tmem, kTmemCols);
 }
 
-// Rows of the items the main kernel divided (tail_parts > 1): block = (row of the item, item - n_full),
-// thread = output dim.  Log-sum-exp merge of the item's partials, 1 / l and the sigmoid gate.
-__global__ void __launch_bounds__(kHeadDim) attn_prefill_tail_merge_kernel(AttnPrefillArgs a) {
+// Rows of the items the main kernel divided (tail_parts > 1): block = (8 rows of the item, item - n_full), one
+// warp per row, a lane 2 x 4 output dims.  Log-sum-exp merge of the item's partials, 1 / l and the sigmoid
+// gate; every load of a row is requested before the first is used.
+constexpr int kMergeRows = 8, kMergeMaxParts = 8;
+__global__ void __launch_bounds__(kMergeRows * 32) attn_prefill_tail_merge_kernel(AttnPrefillArgs a) {
     griddep_launch();
     griddep_wait();
-    const int r = blockIdx.x, d = threadIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * kMergeRows + warp;
     const int n_qtiles = (a.T + kQRows - 1) / kQRows;
-    const int G = a.n_q / a.n_kv, per_kv = n_qtiles * G;
-    const int item = a.n_full + int(blockIdx.y);
-    const int hkv = item / per_kv, rem = item - hkv * per_kv;
-    const int q0 = (n_qtiles - 1 - rem / G) * kQRows, hq = hkv * G + rem % G;
+    int qt, hq;
+    item_tile(a, a.n_full + int(blockIdx.y), n_qtiles, qt, hq);
+    const int q0 = qt * kQRows;
     if (q0 + r >= a.T) return;
+    const int parts = min(a.tail_parts, kMergeMaxParts);
     const size_t u0 = size_t(blockIdx.y) * a.tail_parts;
-    float mm = -1e30f;
-    for (int p = 0; p < a.tail_parts; ++p) mm = fmaxf(mm, a.part_ml[((u0 + p) * kQRows + r) * 2]);
-    float acc = 0.f, l = 0.f;
-    for (int p = 0; p < a.tail_parts; ++p) {
-        const size_t row = (u0 + p) * kQRows + r;
-        const float al = expf(a.part_ml[row * 2] - mm);
-        l += a.part_ml[row * 2 + 1] * al;
-        acc += __ldcs(a.part_o + row * kHeadDim + d) * al;
+    const size_t oi = (size_t(q0 + r) * a.n_q + hq) * kHeadDim + lane * 4;
+    float2 ml[kMergeMaxParts];
+    float4 o0[kMergeMaxParts], o1[kMergeMaxParts];
+    float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+#pragma unroll
+    for (int p = 0; p < kMergeMaxParts; ++p) {
+        if (p < parts) {
+            const size_t row = (u0 + p) * kQRows + r;
+            ml[p] = *reinterpret_cast<const float2*>(a.part_ml + row * 2);
+            o0[p] = __ldcs(reinterpret_cast<const float4*>(a.part_o + row * kHeadDim + lane * 4));
+            o1[p] = __ldcs(reinterpret_cast<const float4*>(a.part_o + row * kHeadDim + 128 + lane * 4));
+        }
     }
-    float out = l > 0.f ? acc / l : 0.f;
-    const size_t oi = (size_t(q0 + r) * a.n_q + hq) * kHeadDim + d;
-    if (a.gate) out *= 1.f / (1.f + expf(-__ldcs(a.gate + oi)));
-    a.o[oi] = out;
+    if (a.gate) {
+        g0 = __ldcs(reinterpret_cast<const float4*>(a.gate + oi));
+        g1 = __ldcs(reinterpret_cast<const float4*>(a.gate + oi + 128));
+    }
+    float mm = -1e30f;
+#pragma unroll
+    for (int p = 0; p < kMergeMaxParts; ++p)
+        if (p < parts) mm = fmaxf(mm, ml[p].x);
+    float l = 0.f;
+    float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+#pragma unroll
+    for (int p = 0; p < kMergeMaxParts; ++p) {
+        if (p < parts) {
+            const float al = expf(ml[p].x - mm);
+            l += ml[p].y * al;
+            x0.x += o0[p].x * al; x0.y += o0[p].y * al; x0.z += o0[p].z * al; x0.w += o0[p].w * al;
+            x1.x += o1[p].x * al; x1.y += o1[p].y * al; x1.z += o1[p].z * al; x1.w += o1[p].w * al;
+        }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    auto fin = [&](float v, float g) { return a.gate ? v * inv * (1.f / (1.f + expf(-g))) : v * inv; };
+    __stcs(reinterpret_cast<float4*>(a.o + oi), make_float4(fin(x0.x, g0.x), fin(x0.y, g0.y), fin(x0.z, g0.z), fin(x0.w, g0.w)));
+    __stcs(reinterpret_cast<float4*>(a.o + oi + 128),
+           make_float4(fin(x1.x, g1.x), fin(x1.y, g1.y), fin(x1.z, g1.z), fin(x1.w, g1.w)));
 }
 
 size_t attn_prefill_smem_bytes() { return sizeof(Smem) + 1024; }

@@ -56,6 +56,10 @@ struct AttnPrefillArgs {
     // partly filled wave is spread over every SM.  Unit u = (item - n_full) * tail_parts + part writes
     // part_o [u][128][256] and part_ml [u][128][2]; attn_prefill_tail_merge_kernel finishes those rows.
     int n_full, tail_parts;
+    // order of the items along the grid: 0 = one KV head after the other, inside it the longest jobs first;
+    // 1 = by size over all heads (all query heads of the last query tile, then of the one before, ...), for calls
+    // of fewer than two waves, whose second wave should hold the shortest items
+    int by_size;
 };
 __global__ void attn_prefill_kernel(AttnPrefillArgs a);
 __global__ void attn_prefill_tail_merge_kernel(AttnPrefillArgs a);
