@@ -1227,33 +1227,45 @@ int rl_delta_chunk_prefill(float* S, const float* q, const float* k, const float
     int n_seg = n_chunks < 32 ? 1 : (n_chunks < 64 ? 2 : (n_chunks < 128 ? 3 : 4));
     if (kDeltaChunkSegs > 0) n_seg = std::max(1, std::min({kDeltaChunkSegs, int(sizeof(AuxSet::fork) / sizeof(AuxSet::fork[0])), n_chunks}));
     cudaStream_t run = as_stream(stream);
+    // All three kernels wait for the kernel in front (griddepcontrol.wait) before their first global access, so
+    // on the caller's stream they are launched for programmatic dependent launch; the scans of a segmented call
+    // follow an event on the second stream and are launched plainly.
     auto prepare = [&](int c0, int n, cudaStream_t st) {
         a.chunk0 = c0;
         a.chunks = n;
-        rl::delta_chunk_prepare_kernel<<<dim3(n, p->n_v), rl::delta_chunk_prepare_threads(),
-                                         rl::delta_chunk_prepare_smem_bytes(), st>>>(a);
+        return rl::launch_step(rl::delta_chunk_prepare_kernel, dim3(n, p->n_v), dim3(rl::delta_chunk_prepare_threads()),
+                               rl::delta_chunk_prepare_smem_bytes(), st, a);
     };
     auto scan = [&](int c0, int n, cudaStream_t st) {
         a.chunk0 = c0;
         a.chunks = n;
-        rl::delta_chunk_scan_kernel<<<p->n_v, rl::delta_chunk_scan_threads(), rl::delta_chunk_scan_smem_bytes(), st>>>(a);
+        return rl::launch_step(rl::delta_chunk_scan_kernel, dim3(p->n_v), dim3(rl::delta_chunk_scan_threads()),
+                               rl::delta_chunk_scan_smem_bytes(), st, a);
     };
     a.chunk0 = 0;
     a.chunks = n_chunks;
-    rl::delta_chunk_keys_kernel<<<dim3(n_chunks, p->n_qk), rl::delta_chunk_prepare_threads(),
-                                  rl::delta_chunk_prepare_smem_bytes(), run>>>(a);
+    {
+        StepOverlap overlap(true);
+        RL_CUDA(rl::launch_step(rl::delta_chunk_keys_kernel, dim3(n_chunks, p->n_qk), dim3(rl::delta_chunk_prepare_threads()),
+                                rl::delta_chunk_prepare_smem_bytes(), run, a));
+    }
     if (n_seg == 1) {
-        prepare(0, n_chunks, run);
-        scan(0, n_chunks, run);
+        StepOverlap overlap(true);
+        RL_CUDA(prepare(0, n_chunks, run));
+        RL_CUDA(scan(0, n_chunks, run));
     } else {
         AuxSet* aux = nullptr;
         if (int st = aux_acquire(d, &aux)) return st;
         for (int i = 0; i < n_seg; ++i) {
             const int c0 = int(1LL * i * n_chunks / n_seg), c1 = int(1LL * (i + 1) * n_chunks / n_seg);
-            prepare(c0, c1 - c0, run);
+            {
+                StepOverlap overlap(true);
+                RL_CUDA(prepare(c0, c1 - c0, run));
+            }
             RL_CUDA(cudaEventRecord(aux->fork[i], run));
             RL_CUDA(cudaStreamWaitEvent(aux->stream, aux->fork[i], 0));   // also orders the first scan after the caller's work
-            scan(c0, c1 - c0, aux->stream);
+            StepOverlap plain(false);
+            RL_CUDA(scan(c0, c1 - c0, aux->stream));
         }
         RL_CUDA(cudaEventRecord(aux->join, aux->stream));
         aux->used = true;

@@ -96,6 +96,8 @@ constexpr int kVecSteps = 8;
 __global__ void __launch_bounds__(256, 3)
 conv1d_prefill4_kernel(const float* x, const float* w, float* y, const float* state_in, float* state_out, int seq,
                        int dim) {
+    griddep_launch();
+    griddep_wait();
     const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
     if (c >= dim) return;
     const int t0 = blockIdx.y * kVecSteps;

@@ -31,6 +31,7 @@
 // The tiles of a chunk arrive by three linear TMA bulk copies into three rings, one per stage
 // of the chunk's work (before D, for D, after D), so that 208 KiB of shared memory hold the
 // current chunk and most of the next.
+#include "common.cuh"
 #include "kernels.h"
 #include "tcgen05.cuh"
 
@@ -127,6 +128,8 @@ constexpr int kKeysFloats = kKeysBytes / 4;
 __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     PrepSmem& s = *reinterpret_cast<PrepSmem*>(smem_raw);
+    griddep_launch();
+    griddep_wait();
     const int chunk = a.chunk0 + blockIdx.x, hs = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int t0 = chunk * kC;
@@ -232,6 +235,8 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
     const int t0 = chunk * kC;
     const int n_tok = min(kC, a.T - t0);
     unsigned char* rec = a.work + (size_t(chunk) * a.n_v + h) * kRecordBytes;
+    griddep_launch();
+    griddep_wait();
 
     // ---- what the key head's pass left (k^, q^, k^.k^, q^.k^) comes in by bulk copies beside the gates ----
     if (tid == 0) {
@@ -576,9 +581,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(Delta
         mbar_fence_init();
     }
     if (warp == kWarpScanMma) tc::tmem_alloc(&s.tmem_base, 512);
+    griddep_launch();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
+    griddep_wait();       // barriers and tensor memory were set up beside the tail of the kernel in front
     const uint32_t tmem = s.tmem_base;
 
     if (warp == kWarpScanLoader) {
