@@ -1734,6 +1734,8 @@ int rl_stack_prefill(rl_cache* c, const rl_stack_prefill_io* io, void* workspace
         return fail(RL_ERR_RANGE, "DeltaNet tensors are NULL");
     if (workspace_bytes < pl.total || (pl.total && !workspace))
         return fail(RL_ERR_RANGE, "workspace %zu bytes < %zu required", workspace_bytes, pl.total);
+    // the chunk's kernels that wait for the kernel in front themselves (launch_step) overlap their heads with its tail
+    StepOverlap overlap(true);
     if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(RL_ERR_RANGE, "workspace must be 256-byte aligned");
     cudaStream_t run = as_stream(stream);
     unsigned char* ws = static_cast<unsigned char*>(workspace);

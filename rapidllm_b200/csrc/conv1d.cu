@@ -172,8 +172,8 @@ void launch_conv1d_prefill(const float* x, const float* w, float* y, float* stat
                      reinterpret_cast<uintptr_t>(y) % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
     if (vec) {
         const bool tail_fused = state_io && seq >= 4 && reinterpret_cast<uintptr_t>(state_io) % 16 == 0;
-        conv1d_prefill4_kernel<<<dim3((dim / 2 + 255) / 256, (seq + kVecSteps - 1) / kVecSteps), 256, 0, st>>>(
-            x, w, y, state_in, tail_fused ? state_io : nullptr, seq, dim);
+        launch_step(conv1d_prefill4_kernel, dim3((dim / 2 + 255) / 256, (seq + kVecSteps - 1) / kVecSteps), dim3(256), 0, st,
+                    x, w, y, state_in, tail_fused ? state_io : nullptr, seq, dim);
         if (tail_fused) return;
     } else {
         const int tile = 64;
