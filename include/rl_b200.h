@@ -174,9 +174,11 @@ int rl_attn_prefill(void* k_pool, void* v_pool, const int32_t* page_table_row, c
                     const void* k_rows_bf16, const void* v_rows_bf16, const float* gate, float* o,
                     const rl_attn_prefill_params* p, void* stream);
 /* The same with a workspace: short chunks (the reference's chunks are at most 1024 rows) and the
- * few rows of a speculative verify leave most SMs idle when every (query tile, head) is one CTA,
- * so with a workspace of rl_attn_prefill_workspace_bytes() the KV range of each is divided among
- * several CTAs whose partials are merged (log-sum-exp, then the gate) by a second kernel.
+ * few rows of a speculative verify leave SMs idle when every (query tile, head) is one CTA.  With a
+ * workspace of rl_attn_prefill_workspace_bytes() a call with fewer items than SMs divides the KV
+ * range of each among several CTAs, and a call whose last wave of CTAs is at most half full (192
+ * items of a 1024-row chunk on 148 SMs) divides the items of that wave only; the partials are
+ * merged (log-sum-exp, then the gate) by a second kernel.
  * 0 bytes = this call would not be divided; rl_attn_prefill_ws then equals rl_attn_prefill. */
 size_t rl_attn_prefill_workspace_bytes(const rl_attn_prefill_params* p);
 int rl_attn_prefill_ws(void* k_pool, void* v_pool, const int32_t* page_table_row, const void* q_bf16,
