@@ -81,6 +81,26 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// One 16 x 8 output tile of a small product on the tensor cores with fp32 accuracy (3 x TF32):
+// d += A[16][K] B[K][8], a_at(row, k) and b_at(k, col) give the elements (row, col inside the tile);
+// g = lane / 4, c = lane % 4; d follows the accumulator layout of mma_tf32.
+template <int K, class FA, class FB>
+__device__ __forceinline__ void tile_mma3(float (&d)[4], FA a_at, FB b_at, int g, int c) {
+#pragma unroll
+    for (int k0 = 0; k0 < K; k0 += 8) {
+        uint32_t ah[4], al[4], bh[2], bl[2];
+        split_tf32(a_at(g, k0 + c), ah[0], al[0]);
+        split_tf32(a_at(g + 8, k0 + c), ah[1], al[1]);
+        split_tf32(a_at(g, k0 + c + 4), ah[2], al[2]);
+        split_tf32(a_at(g + 8, k0 + c + 4), ah[3], al[3]);
+        split_tf32(b_at(k0 + c, g), bh[0], bl[0]);
+        split_tf32(b_at(k0 + c + 4, g), bh[1], bl[1]);
+        mma_tf32(d, al, bh);
+        mma_tf32(d, ah, bl);
+        mma_tf32(d, ah, bh);
+    }
+}
+
 struct PrepSmem {
     float kn[kC][kPad];       // k^
     union {
@@ -309,108 +329,94 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
                                                            t == i + 3 ? 1.f : 0.f);
     }
     __syncthreads();
-    // ---- M = (I + A)^-1 with all 256 threads and a dozen barriers ----
-    // (1) the four 16 x 16 diagonal blocks: N = strictly lower part is nilpotent (N^16 = 0), so
-    //     (I + N)^-1 = (I - N)(I + N^2)(I + N^4)(I + N^8): six small products.  64 threads per block, each
-    //     row x, columns y0 .. y0+3 (one scalar and one 16-byte load per four multiply-adds).
+    // ---- M = (I + A)^-1 on the tensor cores (3 x TF32 = fp32 accuracy), a dozen barriers ----
+    // Every product is cut into 16 x 8 output tiles, one per warp (tile_mma3).
     {
-        const int bb = (tid >> 6) * kB, x = (tid & 63) >> 2, y0 = (tid & 3) * 4;
+        const int g = lane >> 2, c = lane & 3;
         float (*L)[kSq] = s.w.d.l;
-        // acc[j] += sum_k a(k) B[bb + k][bb + y0 + j]
-        auto mm16 = [&](float (&acc)[4], auto a_of_k, const float (*B)[kSq]) {
-#pragma unroll
-            for (int k = 0; k < kB; ++k) {
-                const float av = a_of_k(k);
-                const float4 bv = *reinterpret_cast<const float4*>(&B[bb + k][bb + y0]);
-                acc[0] += av * bv.x; acc[1] += av * bv.y; acc[2] += av * bv.z; acc[3] += av * bv.w;
-            }
+        auto ld_tile = [&](const float (*X)[kSq], int r0, int n0, float (&d)[4]) {
+            const float2 lo = *reinterpret_cast<const float2*>(&X[r0 + g][n0 + 2 * c]);
+            const float2 hi = *reinterpret_cast<const float2*>(&X[r0 + g + 8][n0 + 2 * c]);
+            d[0] = lo.x; d[1] = lo.y; d[2] = hi.x; d[3] = hi.y;
         };
-        auto put = [&](float (*D)[kSq], const float (&acc)[4]) {
-            *reinterpret_cast<float4*>(&D[bb + x][bb + y0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        auto st_tile = [&](float (*X)[kSq], int r0, int n0, const float (&d)[4]) {
+            *reinterpret_cast<float2*>(&X[r0 + g][n0 + 2 * c]) = make_float2(d[0], d[1]);
+            *reinterpret_cast<float2*>(&X[r0 + g + 8][n0 + 2 * c]) = make_float2(d[2], d[3]);
         };
-        auto get = [&](const float (*D)[kSq], float (&acc)[4]) {
-            const float4 v = *reinterpret_cast<const float4*>(&D[bb + x][bb + y0]);
-            acc[0] = v.x; acc[1] = v.y; acc[2] = v.z; acc[3] = v.w;
-        };
-        float acc[4];
-        // tmp = N^2
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        mm16(acc, [&](int k) { return L[bb + x][bb + k]; }, L);
-        put(tmp, acc);
-        __syncthreads();
-        // m = (I - N)(I + N^2)
-        get(L, acc);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = (x == y0 + j ? 1.f : 0.f) - acc[j];
-        mm16(acc, [&](int k) { return (x == k ? 1.f : 0.f) - L[bb + x][bb + k]; }, tmp);
-        put(m, acc);
-        __syncthreads();
-        // l = N^4
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        mm16(acc, [&](int k) { return tmp[bb + x][bb + k]; }, tmp);
-        put(L, acc);
-        __syncthreads();
-        // tmp = m (I + N^4)
-        get(m, acc);
-        mm16(acc, [&](int k) { return m[bb + x][bb + k]; }, L);
-        put(tmp, acc);
-        __syncthreads();
-        // m = N^8
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        mm16(acc, [&](int k) { return L[bb + x][bb + k]; }, L);
-        put(m, acc);
-        __syncthreads();
-        // m = tmp (I + N^8): the inverse of the block (through registers: m is read by other threads until the barrier)
-        get(tmp, acc);
-        mm16(acc, [&](int k) { return tmp[bb + x][bb + k]; }, m);
-        __syncthreads();
-        put(m, acc);
-        __syncthreads();
-    }
-    {
-        // (2) off-diagonal blocks from inv [[P, 0], [C, Q]] = [[P^-1, 0], [-Q^-1 C P^-1, Q^-1]], first
-        //     for the two 32 x 32 halves (C = a 16 x 16 block of A), then for the whole (C = 32 x 32)
+        // (1) the four 16 x 16 diagonal blocks: N = strictly lower part is nilpotent (N^16 = 0), so
+        //     (I + N)^-1 = (I - N)(I + N^2)(I + N^4)(I + N^8): six products per block, block = warp / 2,
+        //     the warp's tile = 8 of its 16 columns.
         {
-            const int u = tid >> 7, x = (tid & 127) >> 3, y0 = (tid & 7) * 2;
-            const int bi = (2 * u + 1) * kB, bj = 2 * u * kB;
-            float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-            for (int k = 0; k < kB; ++k) {
-                const float av = s.w.d.l[bi + x][bj + k];
-                const float2 bv = *reinterpret_cast<const float2*>(&m[bj + k][bj + y0]);
-                a0 += av * bv.x; a1 += av * bv.y;
-            }
-            *reinterpret_cast<float2*>(&tmp[bi + x][bj + y0]) = make_float2(a0, a1);
+            const int bb = (warp >> 1) * kB, nb = bb + (warp & 1) * 8;
+            float d[4];
+            // tmp = N^2
+            d[0] = d[1] = d[2] = d[3] = 0.f;
+            tile_mma3<kB>(d, [&](int r, int k) { return L[bb + r][bb + k]; }, [&](int k, int n) { return L[bb + k][nb + n]; }, g, c);
+            st_tile(tmp, bb, nb, d);
             __syncthreads();
-            a0 = a1 = 0.f;
-#pragma unroll
-            for (int k = 0; k < kB; ++k) {
-                const float av = m[bi + x][bi + k];
-                const float2 bv = *reinterpret_cast<const float2*>(&tmp[bi + k][bj + y0]);
-                a0 -= av * bv.x; a1 -= av * bv.y;
-            }
-            *reinterpret_cast<float2*>(&m[bi + x][bj + y0]) = make_float2(a0, a1);
+            // m = (I - N) + (I - N) N^2
+            ld_tile(L, bb, nb, d);
+            d[0] = (bb + g == nb + 2 * c ? 1.f : 0.f) - d[0];
+            d[1] = (bb + g == nb + 2 * c + 1 ? 1.f : 0.f) - d[1];
+            d[2] = (bb + g + 8 == nb + 2 * c ? 1.f : 0.f) - d[2];
+            d[3] = (bb + g + 8 == nb + 2 * c + 1 ? 1.f : 0.f) - d[3];
+            tile_mma3<kB>(d, [&](int r, int k) { return (r == k ? 1.f : 0.f) - L[bb + r][bb + k]; },
+                          [&](int k, int n) { return tmp[bb + k][nb + n]; }, g, c);
+            st_tile(m, bb, nb, d);
+            __syncthreads();
+            // l = N^4
+            d[0] = d[1] = d[2] = d[3] = 0.f;
+            tile_mma3<kB>(d, [&](int r, int k) { return tmp[bb + r][bb + k]; }, [&](int k, int n) { return tmp[bb + k][nb + n]; }, g, c);
+            st_tile(L, bb, nb, d);
+            __syncthreads();
+            // tmp = m + m N^4
+            ld_tile(m, bb, nb, d);
+            tile_mma3<kB>(d, [&](int r, int k) { return m[bb + r][bb + k]; }, [&](int k, int n) { return L[bb + k][nb + n]; }, g, c);
+            st_tile(tmp, bb, nb, d);
+            __syncthreads();
+            // m = N^8
+            d[0] = d[1] = d[2] = d[3] = 0.f;
+            tile_mma3<kB>(d, [&](int r, int k) { return L[bb + r][bb + k]; }, [&](int k, int n) { return L[bb + k][nb + n]; }, g, c);
+            st_tile(m, bb, nb, d);
+            __syncthreads();
+            // m = tmp + tmp N^8: the inverse of the block (kept in registers until every warp has read m)
+            ld_tile(tmp, bb, nb, d);
+            tile_mma3<kB>(d, [&](int r, int k) { return tmp[bb + r][bb + k]; }, [&](int k, int n) { return m[bb + k][nb + n]; }, g, c);
+            __syncthreads();
+            st_tile(m, bb, nb, d);
             __syncthreads();
         }
-        const int r = 32 + (tid >> 3), y0 = (tid & 7) * 4;        // row r, columns y0 .. y0+3 of the lower left quarter
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-        for (int k = 0; k < 32; ++k) {
-            const float av = s.w.d.l[r][k];
-            const float4 bv = *reinterpret_cast<const float4*>(&m[k][y0]);
-            acc[0] += av * bv.x; acc[1] += av * bv.y; acc[2] += av * bv.z; acc[3] += av * bv.w;
+        // (2) off-diagonal blocks from inv [[P, 0], [C, Q]] = [[P^-1, 0], [-Q^-1 C P^-1, Q^-1]], first
+        //     for the two 32 x 32 halves (C = a 16 x 16 block of A; four tiles, warps 0-3), then for the whole
+        //     (C = 32 x 32; eight tiles)
+        {
+            const int u = warp >> 1, bi = (2 * u + 1) * kB, bj = 2 * u * kB, nb = bj + (warp & 1) * 8;
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            if (warp < 4) {
+                tile_mma3<kB>(d, [&](int r, int k) { return L[bi + r][bj + k]; }, [&](int k, int n) { return m[bj + k][nb + n]; }, g, c);
+                st_tile(tmp, bi, nb, d);
+            }
+            __syncthreads();
+            if (warp < 4) {
+                d[0] = d[1] = d[2] = d[3] = 0.f;
+                tile_mma3<kB>(d, [&](int r, int k) { return m[bi + r][bi + k]; }, [&](int k, int n) { return tmp[bi + k][nb + n]; }, g, c);
+                d[0] = -d[0]; d[1] = -d[1]; d[2] = -d[2]; d[3] = -d[3];
+                st_tile(m, bi, nb, d);
+            }
+            __syncthreads();
         }
-        *reinterpret_cast<float4*>(&tmp[r][y0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        __syncthreads();
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-#pragma unroll 8
-        for (int k = 0; k < 32; ++k) {
-            const float av = m[r][32 + k];
-            const float4 bv = *reinterpret_cast<const float4*>(&tmp[32 + k][y0]);
-            acc[0] -= av * bv.x; acc[1] -= av * bv.y; acc[2] -= av * bv.z; acc[3] -= av * bv.w;
+        {
+            const int r0 = 32 + (warp >> 2) * 16, n0 = (warp & 3) * 8;
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            tile_mma3<32>(d, [&](int r, int k) { return L[r0 + r][k]; }, [&](int k, int n) { return m[k][n0 + n]; }, g, c);
+            st_tile(tmp, r0, n0, d);
+            __syncthreads();
+            d[0] = d[1] = d[2] = d[3] = 0.f;
+            tile_mma3<32>(d, [&](int r, int k) { return m[r0 + r][32 + k]; }, [&](int k, int n) { return tmp[32 + k][n0 + n]; }, g, c);
+            d[0] = -d[0]; d[1] = -d[1]; d[2] = -d[2]; d[3] = -d[3];
+            st_tile(m, r0, n0, d);
+            __syncthreads();
         }
-        *reinterpret_cast<float4*>(&m[r][y0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        __syncthreads();
     }
     // ---- tile P (64 x 64, fp16, swizzled), four columns per thread and pass ----
     for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
