@@ -460,48 +460,53 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_prepare_kernel(De
     }
     __syncthreads();
     // W[t][d] = sum_{i<=t} tmp[t][i] k^[i][d] and (T V)[t][d] = sum_{i<=t} T[t][i] v[i][d] (tmp and T are zero
-    // above the diagonal), 3 x TF32 MMAs: warp w owns rows 16 (w & 3) .. +15 and dims 64 (w >> 2) .. +63; K steps
-    // beyond the rows' diagonal are skipped.  W leaves as fp16 hi + lo tiles, T V as plain fp32 rows.
+    // above the diagonal), 3 x TF32 MMAs.  K steps beyond a row block's diagonal are skipped, so the four
+    // 16-row blocks cost 2, 4, 6 and 8 steps: a warp takes blocks {0, 3} or {1, 2} (10 steps either way) of
+    // one 32-dim column group.  W leaves as fp16 hi + lo tiles, T V as plain fp32 rows.
     {
         const int g = lane >> 2, c = lane & 3;
-        const int t_base = (warp & 3) * 16, d_base = (warp >> 2) * 64;
+        const int d_base = (warp >> 1) * 32;
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
             const float (*A)[kSq] = which == 0 ? tmp : m;
             const float (*B)[kPad] = which == 0 ? s.kn : s.w.v;
-            float acc[8][4] = {};
-            for (int k0 = 0; k0 < t_base + 16; k0 += 8) {
-                uint32_t ah[4], al[4];
-                split_tf32(A[t_base + g][k0 + c], ah[0], al[0]);
-                split_tf32(A[t_base + g + 8][k0 + c], ah[1], al[1]);
-                split_tf32(A[t_base + g][k0 + c + 4], ah[2], al[2]);
-                split_tf32(A[t_base + g + 8][k0 + c + 4], ah[3], al[3]);
-                uint32_t bh[8][2], bl[8][2];
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int t_base = (half == 0 ? (warp & 1) : 3 - (warp & 1)) * 16;
+                float acc[4][4] = {};
+                for (int k0 = 0; k0 < t_base + 16; k0 += 8) {
+                    uint32_t ah[4], al[4];
+                    split_tf32(A[t_base + g][k0 + c], ah[0], al[0]);
+                    split_tf32(A[t_base + g + 8][k0 + c], ah[1], al[1]);
+                    split_tf32(A[t_base + g][k0 + c + 4], ah[2], al[2]);
+                    split_tf32(A[t_base + g + 8][k0 + c + 4], ah[3], al[3]);
+                    uint32_t bh[4][2], bl[4][2];
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
-                    split_tf32(B[k0 + c][d_base + 8 * nt + g], bh[nt][0], bl[nt][0]);
-                    split_tf32(B[k0 + c + 4][d_base + 8 * nt + g], bh[nt][1], bl[nt][1]);
+                    for (int nt = 0; nt < 4; ++nt) {
+                        split_tf32(B[k0 + c][d_base + 8 * nt + g], bh[nt][0], bl[nt][0]);
+                        split_tf32(B[k0 + c + 4][d_base + 8 * nt + g], bh[nt][1], bl[nt][1]);
+                    }
+#pragma unroll
+                    for (int pass = 0; pass < 3; ++pass)
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt) mma_tf32(acc[nt], pass == 0 ? al : ah, pass == 1 ? bl[nt] : bh[nt]);
                 }
 #pragma unroll
-                for (int pass = 0; pass < 3; ++pass)
-#pragma unroll
-                    for (int nt = 0; nt < 8; ++nt) mma_tf32(acc[nt], pass == 0 ? al : ah, pass == 1 ? bl[nt] : bh[nt]);
-            }
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const int d0 = d_base + 8 * nt + 2 * c;
-                if (which == 0) {
-                    uint32_t h0, l0, h1, l1;
-                    split_h2(acc[nt][0], acc[nt][1], h0, l0);
-                    split_h2(acc[nt][2], acc[nt][3], h1, l1);
-                    *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g, d0)) = h0;
-                    *reinterpret_cast<uint32_t*>(rec + kOffWlo + tile_off(t_base + g, d0)) = l0;
-                    *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g + 8, d0)) = h1;
-                    *reinterpret_cast<uint32_t*>(rec + kOffWlo + tile_off(t_base + g + 8, d0)) = l1;
-                } else {
-                    float* tv = reinterpret_cast<float*>(rec + kOffTV);
-                    *reinterpret_cast<float2*>(tv + (t_base + g) * kD + d0) = make_float2(acc[nt][0], acc[nt][1]);
-                    *reinterpret_cast<float2*>(tv + (t_base + g + 8) * kD + d0) = make_float2(acc[nt][2], acc[nt][3]);
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int d0 = d_base + 8 * nt + 2 * c;
+                    if (which == 0) {
+                        uint32_t h0, l0, h1, l1;
+                        split_h2(acc[nt][0], acc[nt][1], h0, l0);
+                        split_h2(acc[nt][2], acc[nt][3], h1, l1);
+                        *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g, d0)) = h0;
+                        *reinterpret_cast<uint32_t*>(rec + kOffWlo + tile_off(t_base + g, d0)) = l0;
+                        *reinterpret_cast<uint32_t*>(rec + kOffW + tile_off(t_base + g + 8, d0)) = h1;
+                        *reinterpret_cast<uint32_t*>(rec + kOffWlo + tile_off(t_base + g + 8, d0)) = l1;
+                    } else {
+                        float* tv = reinterpret_cast<float*>(rec + kOffTV);
+                        *reinterpret_cast<float2*>(tv + (t_base + g) * kD + d0) = make_float2(acc[nt][0], acc[nt][1]);
+                        *reinterpret_cast<float2*>(tv + (t_base + g + 8) * kD + d0) = make_float2(acc[nt][2], acc[nt][3]);
+                    }
                 }
             }
         }
