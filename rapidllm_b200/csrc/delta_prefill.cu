@@ -189,14 +189,24 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(Delta
         }
     }
     __syncthreads();
-    // ---- k^.k^ and q^.k^ on the tensor cores (3 x TF32 = fp32 accuracy): warp w owns rows
-    // 16 (w & 3) .. +15 and columns 32 (w >> 2) .. +31; column tiles entirely above the diagonal
-    // are skipped (and zero-filled, nobody reads more than their zero) ----
+    // ---- k^.k^ and q^.k^ on the tensor cores (3 x TF32 = fp32 accuracy).  Only the 8-column tiles that
+    // touch the lower triangle are computed: 2, 4, 6, 8 of them for the four 16-row blocks.  Warp -> (row
+    // block, first tile, tiles): at most three tiles each; the rest of l and qk is zero-filled first (nobody
+    // reads more than their zero) ----
+    for (int idx = tid; idx < kC * kC / 4; idx += kPrepThreads) {
+        const int t = idx >> 4, i = (idx & 15) * 4;
+        if (i >= (t & ~15) + 16) {
+            *reinterpret_cast<float4*>(&s.w.d.l[t][i]) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(&s.w.d.qk[t][i]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     {
         const int g = lane >> 2, c = lane & 3;
-        const int t_base = (warp & 3) * 16, i_base = (warp >> 2) * 32;
-        float ck[4][4] = {}, cq[4][4] = {};
-        const int n_tiles = min(4, max(0, (t_base + 15 - i_base) / 8 + 1));   // tiles with i0 <= t_base + 15
+        // warps 0..7 -> row blocks 0, 1, 1, 2, 2, 3, 3, 3; first tiles 0, 0, 2, 0, 3, 0, 3, 6; tiles 2, 2, 2, 3, 3, 3, 3, 2
+        const int rb = (0x33322110u >> (4 * warp)) & 15, tile0 = (0x63030200u >> (4 * warp)) & 15;
+        const int n_tiles = (0x23333222u >> (4 * warp)) & 15;
+        const int t_base = rb * 16, i_base = tile0 * 8;
+        float ck[3][4] = {}, cq[3][4] = {};
         for (int k0 = 0; k0 < kD; k0 += 8) {
             uint32_t akh[4], akl[4], aqh[4], aql[4];
             split_tf32(s.kn[t_base + g][k0 + c], akh[0], akl[0]);
@@ -209,9 +219,9 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(Delta
             split_tf32(s.u.qn[t_base + g + 8][k0 + c + 4], aqh[3], aql[3]);
             // B fragments of all column tiles first, then the three TF32 passes with the accumulators
             // interleaved: consecutive MMAs never depend on each other
-            uint32_t bh[4][2], bl[4][2];
+            uint32_t bh[3][2], bl[3][2];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
+            for (int nt = 0; nt < 3; ++nt) {
                 if (nt < n_tiles) {
                     split_tf32(s.kn[i_base + 8 * nt + g][k0 + c], bh[nt][0], bl[nt][0]);
                     split_tf32(s.kn[i_base + 8 * nt + g][k0 + c + 4], bh[nt][1], bl[nt][1]);
@@ -220,7 +230,7 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(Delta
 #pragma unroll
             for (int pass = 0; pass < 3; ++pass) {
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
+                for (int nt = 0; nt < 3; ++nt) {
                     if (nt < n_tiles) {
                         mma_tf32(ck[nt], pass == 0 ? akl : akh, pass == 1 ? bl[nt] : bh[nt]);
                         mma_tf32(cq[nt], pass == 0 ? aql : aqh, pass == 1 ? bl[nt] : bh[nt]);
@@ -229,12 +239,14 @@ __global__ void __launch_bounds__(kPrepThreads, 2) delta_chunk_keys_kernel(Delta
             }
         }
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            const int i0 = i_base + 8 * nt + 2 * c;
-            s.w.d.l[t_base + g][i0] = ck[nt][0];      s.w.d.l[t_base + g][i0 + 1] = ck[nt][1];
-            s.w.d.l[t_base + g + 8][i0] = ck[nt][2];  s.w.d.l[t_base + g + 8][i0 + 1] = ck[nt][3];
-            s.w.d.qk[t_base + g][i0] = cq[nt][0];     s.w.d.qk[t_base + g][i0 + 1] = cq[nt][1];
-            s.w.d.qk[t_base + g + 8][i0] = cq[nt][2]; s.w.d.qk[t_base + g + 8][i0 + 1] = cq[nt][3];
+        for (int nt = 0; nt < 3; ++nt) {
+            if (nt < n_tiles) {
+                const int i0 = i_base + 8 * nt + 2 * c;
+                s.w.d.l[t_base + g][i0] = ck[nt][0];      s.w.d.l[t_base + g][i0 + 1] = ck[nt][1];
+                s.w.d.l[t_base + g + 8][i0] = ck[nt][2];  s.w.d.l[t_base + g + 8][i0 + 1] = ck[nt][3];
+                s.w.d.qk[t_base + g][i0] = cq[nt][0];     s.w.d.qk[t_base + g][i0 + 1] = cq[nt][1];
+                s.w.d.qk[t_base + g + 8][i0] = cq[nt][2]; s.w.d.qk[t_base + g + 8][i0 + 1] = cq[nt][3];
+            }
         }
     }
     __syncthreads();
