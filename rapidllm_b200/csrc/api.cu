@@ -63,6 +63,7 @@ std::mutex g_mu;
 }  // namespace
 namespace rl {
 thread_local bool g_step_overlap = false;
+thread_local bool g_step_first = false;
 }
 namespace {
 // SMs the persistent kernels of the step in flight leave free (for the exchange kernels of a sharded step)
@@ -399,6 +400,7 @@ const int kHostGroup = std::max(1, knob("RL_B200_HOST_GROUP", 4));
 int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bool host_mode) {
     // not with per-kernel timing: an event between two kernels is what the overlap removes
     StepOverlap overlap(c->overlap && !c->timing);
+    rl::g_step_first = true;      // the step's first kernel waits for all earlier work in the stream (launch.cuh)
     const rl_cache_config& f = c->cfg;
     const int B = io->batch;
     const size_t q_sz = size_t(B) * f.n_q * f.head_dim, kv_sz = size_t(B) * f.n_kv * f.head_dim;

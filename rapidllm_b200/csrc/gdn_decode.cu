@@ -129,7 +129,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
     }
     griddep_launch();
     __syncthreads();
-    griddep_wait();       // nothing of an earlier kernel is read, and nothing written, before this
+    // The producer warp only reads this layer's state, which no kernel since this layer's previous step has
+    // written (the kernel in front belongs to another layer, or to the end of the previous step), so its first
+    // copies are on their way while that kernel finishes.  Everything else -- the step's inputs, the conv
+    // rings, every write -- waits for the kernel in front.
+    if (warp != kWarpProducer) griddep_wait();
     auto slot_of = [&](int b) {
         int slot = a.slot_ids ? a.slot_ids[b] : b;
         if (slot < 0 || slot >= a.n_slots) {
@@ -277,7 +281,6 @@ constexpr int kSlices = kDv / kSliceCols;   // 4
 
 __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeArgs a) {
     griddep_launch();
-    griddep_wait();
     const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __shared__ float sq[kDk], sk[kDk], sv[kSliceCols];
@@ -294,9 +297,12 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeArgs a) {
     const int rg = tid >> 3;           // rows 4rg .. 4rg+3
     const int cg = tid & 7;            // slice columns 4cg .. 4cg+3
     const int col0 = slice * kSliceCols + cg * 4;
+    // the slice of the state is requested before the wait for the kernel in front: only this layer's own
+    // step writes it (see the streaming form)
     float4 s[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) s[r] = *reinterpret_cast<const float4*>(Sp + (4 * rg + r) * kDv + col0);
+    griddep_wait();
 
     if (warp < 2 || (warp == 2 && lane < kSliceCols / 4)) {
         // warp 0: q, warp 1: k (128 channels each), warp 2 lanes 0..7: this slice's 32 v channels
