@@ -16,7 +16,9 @@
 //   S_C = exp(G_C) S_0 + Kt^T D,  Kt = diag(exp(G_C - G)) K
 // (the diagonal of P is included because the reference reads o_t from the updated state).
 //
-// Kernel 1 (delta_chunk_prepare_kernel) computes everything that does not depend on S for
+// Kernel 0 (delta_chunk_keys_kernel) computes, per (chunk, key head), what the value heads of a key
+// head share: k^, q^ and their dot products.
+// Kernel 1 (delta_chunk_prepare_kernel) computes everything else that does not depend on S for
 // all (chunk, value head) pairs in parallel, one CTA each: W, Kt (each as an fp16 high part and
 // an fp16 residual, ~22 bits together), Qg, P (fp16) as tiles already in the 128-byte-swizzled
 // operand format of the tensor cores, and the product T V in fp32; 120 KiB per pair.
@@ -28,9 +30,9 @@
 // the accumulator) and, again as hi + lo, is the A operand of S^T += D^T Kt.  Every product
 // that feeds the state (S W^T, D Kt) runs as hi*hi + lo*hi + hi*lo, so the state keeps fp32
 // accuracy; the two that only feed the output (S Qg^T, D P^T) use a single fp16 B operand.
-// The tiles of a chunk arrive by three linear TMA bulk copies into three rings, one per stage
-// of the chunk's work (before D, for D, after D), so that 208 KiB of shared memory hold the
-// current chunk and most of the next.
+// The tiles of a chunk arrive by three linear TMA bulk copies into three buffers, one per stage
+// of the chunk's work (before D, for D, after D; the first is double), each refilled for the next
+// chunk as soon as the products that read it have completed.
 #include "common.cuh"
 #include "kernels.h"
 #include "tcgen05.cuh"
@@ -564,14 +566,14 @@ struct ScanSmem {
 
 }  // namespace
 
-// grid (n_v), 192 threads.  o [T][n_v][128]; S [n_v][128][128] fp32 in place (row = key dim).  A launch
+// grid (n_v), 448 threads.  o [T][n_v][128]; S [n_v][128][128] fp32 in place (row = key dim).  A launch
 // walks chunks [chunk0, chunk0 + chunks): S is read at its start and written back at its end, so a
 // sequence can be scanned in several launches while later chunks are still being prepared.
 //
 // The chain from one chunk's state to the next is: 24 MMAs (-S^T W^T) -> workers form D -> 12 MMAs
 // (S^T += D^T Kt) -> workers split the new S^T.  The output products (S^T Qg^T before D is known,
-// D^T P^T after the state update) are issued behind the chain's MMAs and read out by the workers while
-// the next chunk's first MMAs run.
+// D^T P^T after the state update) are issued behind the chain's MMAs and read out by four output warps
+// while the next chunk's first MMAs run.
 __global__ void __launch_bounds__(kScanThreads, 1) delta_chunk_scan_kernel(DeltaChunkArgs a) {
     extern __shared__ unsigned char smem_raw[];
     ScanSmem& s = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));

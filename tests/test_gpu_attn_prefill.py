@@ -128,3 +128,25 @@ def test_config3_8192_tokens_sampled_rows(oracle):
     ref = oracle.attn_prefill_rows(q[rows].float().numpy(), k.float().numpy(), v.float().numpy(), rows)
     ref = oracle.sigmoid_gate(ref, gate[rows].numpy())
     _check(o[rows], ref, "cfg3 rows")
+
+
+def test_two_chunks_of_4096_sampled_rows(oracle):
+    """768 (query tile, head) items per chunk = five full waves of 148 + 28: the second chunk runs those 28
+    (the lowest query tiles of the last KV head) divided in parts; sampled rows inside and outside them."""
+    from rapidllm_b200 import _lib, ops
+    gen = torch.Generator().manual_seed(33)
+    T = 8192
+    q, k, v, gate = _inputs(gen, T)
+    n_pages = T // 64
+    table = torch.randperm(n_pages, generator=gen).int().cuda()
+    kp, vp = ops.new_pool(n_pages, N_KV), ops.new_pool(n_pages, N_KV)
+    outs = []
+    for p0 in range(0, T, 4096):
+        sl = slice(p0, p0 + 4096)
+        outs.append(ops.attn_prefill(q[sl].cuda(), kp, vp, table, p0, k[sl].cuda(), v[sl].cuda(), gate[sl].cuda()))
+    _lib.check_device()
+    o = torch.cat(outs).cpu().numpy()
+    rows = np.array([0, 640, 4095, 4096, 4100, 4223, 4500, 4735, 4736, 6000, 8191], np.int32)
+    ref = oracle.attn_prefill_rows(q[rows].float().numpy(), k.float().numpy(), v.float().numpy(), rows)
+    ref = oracle.sigmoid_gate(ref, gate[rows].numpy())
+    _check(o[rows], ref, "2 x 4096 rows")
