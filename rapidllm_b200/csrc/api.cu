@@ -68,6 +68,8 @@ thread_local bool g_step_first = false;
 namespace {
 // SMs the persistent kernels of the step in flight leave free (for the exchange kernels of a sharded step)
 thread_local int g_sm_reserve = 0;
+// set by the decode step around an append whose rows are the caller's own (KvWriteArgs::early)
+thread_local bool g_append_early = false;
 struct SmReserve {
     int prev;
     explicit SmReserve(int n) : prev(g_sm_reserve) { g_sm_reserve = n; }
@@ -496,9 +498,14 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             float* ml_l = io->attn_ml ? io->attn_ml + size_t(ai) * B * f.n_q * 2 : nullptr;
             cudaEvent_t after_main = tm ? c->tev[size_t(L) * 4 + 3] : nullptr;
             if (!c->compact()) {
-                if (!io->no_append)
-                    if (int st = rl_kv_append(kp, vp, io->page_table, io->pos, k_new, io->attn_v + ai * kv_sz, &ap, run))
-                        return st;
+                if (!io->no_append) {
+                    // rows straight from the caller (no in-step kernel made them), pages of this layer only: the
+                    // append need not wait for the kernel of the layer in front before it works
+                    g_append_early = !glue;
+                    const int st = rl_kv_append(kp, vp, io->page_table, io->pos, k_new, io->attn_v + ai * kv_sz, &ap, run);
+                    g_append_early = false;
+                    if (st) return st;
+                }
                 mark(L, 1);
                 rl_attn_decode_params dp = c->attn_params(B);
                 dp.len_add = io->no_append ? 0 : 1;
@@ -743,6 +750,7 @@ int rl_kv_append(void* k_pool, void* v_pool, const int32_t* page_table, const in
     a.pos0 = p->pos0;
     a.rows_fp16 = p->rows_fp16;
     a.pos_limit = p->pos_limit;
+    a.early = g_append_early && rl::g_step_overlap && !rl::g_step_first ? 1 : 0;
     const int rows_per_block = p->n_tok >= 8 ? 8 : 1;
     RL_CUDA(rl::launch_step(rl::kv_write_kernel, dim3((p->n_tok + rows_per_block - 1) / rows_per_block, p->n_kv, p->batch),
                             dim3(32, rows_per_block), 0, as_stream(stream), a));

@@ -34,7 +34,6 @@ __device__ __forceinline__ float block_wht(float v, int wht_len, const float* si
 
 __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     griddep_launch();
-    griddep_wait();
     const int hq = blockIdx.x;
     const int b = blockIdx.y;
     const int G = a.n_q / a.n_kv;
@@ -76,6 +75,9 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(AttnCombineArgs a) {
     const int k0 = c0 / q;
     const int k1 = hpb > 0 ? (c0 + hpb - 1) / q : k0 - 1;
     const size_t unit = size_t(b) * a.n_kv + h;
+    // Up to here only the sequence lengths were read, which the step's kernels never write: which CTAs hold
+    // this head's partials is worked out beside the tail of the decode kernel.  The partials need it finished.
+    griddep_wait();
 
     // A long sequence at a small batch is spread over many CTAs: fetch all their (m, l) pairs at
     // once (one per thread), reduce the maximum across the block, keep the weights in shared

@@ -103,6 +103,9 @@ struct KvWriteArgs {
     int pos0;                    // used when pos == null
     int rows_fp16;               // row element type: 0 fp32 (rounded to nearest even), 1 fp16, 2 bf16
     int pos_limit;               // > 0: rows at positions >= pos_limit are left out (the F16 window of a compact cache)
+    // 1: nothing this kernel reads or writes is touched by the kernels in front of it in the step (its rows are the
+    // caller's, its pages belong to its own layer), so it works first and waits for the kernel in front afterwards
+    int early;
 };
 __global__ void kv_write_kernel(KvWriteArgs a);
 // rows[b][j] = slot_ids[b] * pages_per_slot + j: the page-table rows of a step's sequences in a pool

@@ -12,9 +12,7 @@ namespace rl {
 
 // grid (ceil(n_tok / blockDim.y), n_kv, batch), block (32, 1 or 8): one token row per warp, one
 // 16-byte chunk (8 dims) per thread.
-__global__ void __launch_bounds__(256) kv_write_kernel(KvWriteArgs a) {
-    griddep_launch();
-    griddep_wait();
+__device__ __forceinline__ void kv_write_rows(const KvWriteArgs& a) {
     const int t = blockIdx.x * blockDim.y + threadIdx.y, h = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x;
     if (t >= a.n_tok) return;
@@ -61,6 +59,13 @@ __global__ void __launch_bounds__(256) kv_write_kernel(KvWriteArgs a) {
     }
     *reinterpret_cast<uint4*>(a.k_pool + dst) = kk;
     *reinterpret_cast<uint4*>(a.v_pool + dst) = vv;
+}
+
+__global__ void __launch_bounds__(256) kv_write_kernel(KvWriteArgs a) {
+    griddep_launch();
+    if (!a.early) griddep_wait();
+    kv_write_rows(a);
+    if (a.early) griddep_wait();      // still completes after the kernel in front, as every kernel of a step does
 }
 
 // grid (n_tok, n_kv), 32 threads.
