@@ -70,6 +70,8 @@ namespace {
 thread_local int g_sm_reserve = 0;
 // set by the decode step around an append whose rows are the caller's own (KvWriteArgs::early)
 thread_local bool g_append_early = false;
+// set by the decode step around a decode over the caller's own page table (AttnDecodeArgs::stream_before_wait)
+thread_local bool g_decode_early = false;
 struct SmReserve {
     int prev;
     explicit SmReserve(int n) : prev(g_sm_reserve) { g_sm_reserve = n; }
@@ -257,6 +259,7 @@ int attn_decode_impl(const void* k_pool, const void* v_pool, const int32_t* page
     // are the last to finish, so their share of the units is cut by that much; once nearly every CTA
     // has one (segments > CTAs / 4) the division stays equal in units, which measured faster there.
     a.seg_weight = p->batch * p->n_kv * 4 <= pl.grid ? (tq ? kTqSegWeight : kF16SegWeight) : 0;
+    a.stream_before_wait = !tq && g_decode_early && rl::g_step_overlap && !rl::g_step_first ? 1 : 0;
     const int grid = pl.grid;
     if (tq)
         rl::attn_decode_tq_kernel<<<grid, rl::attn_decode_tq_threads(), rl::attn_decode_tq_smem_bytes(),
@@ -509,9 +512,11 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
                 mark(L, 1);
                 rl_attn_decode_params dp = c->attn_params(B);
                 dp.len_add = io->no_append ? 0 : 1;
-                if (int st = attn_decode_impl(kp, vp, io->page_table, io->pos, q_l, gate_l, io->attn_o + ai * q_sz, ml_l,
-                                              c->attn_ws, c->attn_ws_bytes, &dp, run, after_main))
-                    return st;
+                g_decode_early = true;        // the caller's page table and lengths; only the append in front writes pages
+                const int st = attn_decode_impl(kp, vp, io->page_table, io->pos, q_l, gate_l, io->attn_o + ai * q_sz, ml_l,
+                                                c->attn_ws, c->attn_ws_bytes, &dp, run, after_main);
+                g_decode_early = false;
+                if (st) return st;
             } else {
                 // every token persists in the compact pages; the F16 window rows of the sequences still
                 // inside it are kept current whichever of the two this step reads

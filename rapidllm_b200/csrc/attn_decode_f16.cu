@@ -61,7 +61,8 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     const int G = a.n_q / a.n_kv;
 
     griddep_launch();
-    griddep_wait();       // positions, the appended rows and the workspace belong to earlier kernels
+    // the appended rows, the query and the workspace belong to kernels in front of this one
+    if (!a.stream_before_wait) griddep_wait();
     // chunk prefix over the batch (every CTA computes the same table)
     if (warp == 0)
         split::build_prefix(s.sp, a.seq_lens, a.len_add, a.batch, a.max_pages_per_seq, a.err, lane);
@@ -76,6 +77,7 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
     int u_begin, u_end;
     split::cta_range(s.sp, a.batch, a.n_kv, u_begin, u_end, a.seg_weight);
 
+    if (a.stream_before_wait && warp != kConsumerWarps) griddep_wait();
     if (warp > kConsumerWarps) return;
     if (warp == kConsumerWarps) {
         // ------------------------------ producer ------------------------------
@@ -83,9 +85,11 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
         // paid once per 16 pages; lane 0 waits for free stages and issues the copies.
         uint32_t it = 0;
         bool ok = true;
+        bool waited = !a.stream_before_wait;      // lane 0: the kernel in front has completed
         for (int pos = u_begin; pos < u_end;) {
             const Segment w = split::segment_at(s.sp, pos, u_end, a.batch, a.n_kv, a.seq_lens, a.len_add);
             pos += w.hp1 - w.hp0;
+            const int last_page = (w.len - 1) >> 6;   // where this step's token was appended
             for (int hp_base = w.hp0; hp_base < w.hp1; hp_base += 32) {
                 int my_page = 0;
                 if (hp_base + lane < w.hp1) {
@@ -102,6 +106,10 @@ attn_decode_f16_kernel(AttnDecodeArgs a) {
                     const int hp = hp_base + j;
                     const int st = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
+                    if (!waited && (hp >> 1) >= last_page) {
+                        griddep_wait();
+                        waited = true;
+                    }
                     if (!mbar_wait(&s.empty[st], ph ^ 1)) {
                         set_err(a.err, DEV_ERR_WAIT_TIMEOUT);
                         ok = false;

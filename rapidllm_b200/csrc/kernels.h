@@ -22,6 +22,10 @@ struct AttnDecodeArgs {
     int len_add;
     float scale;                 // 1/sqrt(head_dim)
     int seg_weight;              // charge per (sequence, head) boundary in the division of the units (attn_split.cuh)
+    // 1 (F16 kernel, inside a step): lengths, page table and every page but a sequence's last are the caller's or an
+    // earlier step's, so the producer streams them before it waits for the kernel in front (the append of this
+    // step's token, which writes into the last page)
+    int stream_before_wait;
 };
 __global__ void attn_decode_f16_kernel(AttnDecodeArgs a);
 // same arguments over the compact cache: k_pool = record pool (kv_compact.cu), v_pool unused
