@@ -72,6 +72,8 @@ thread_local int g_sm_reserve = 0;
 thread_local bool g_append_early = false;
 // set by the decode step around a decode over the caller's own page table (AttnDecodeArgs::stream_before_wait)
 thread_local bool g_decode_early = false;
+// set by the decode step around a fused DeltaNet step whose inputs are the caller's (GdnDecodeArgs::early)
+thread_local bool g_gdn_early = false;
 struct SmReserve {
     int prev;
     explicit SmReserve(int n) : prev(g_sm_reserve) { g_sm_reserve = n; }
@@ -567,11 +569,15 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
                                             glue->A_log + size_t(di) * f.n_v, glue->dt_bias + size_t(di) * f.n_v, c->g_beta,
                                             c->g_g, B, f.n_v, run))
                     return st;
-            if (int st = rl_gdn_decode(c->S + di * st_elems, c->conv + di * cv_elems, c->conv_phase + size_t(di) * f.n_slots,
-                                       io->slot_ids, io->delta_qkv + di * qkv_sz,
-                                       io->conv_w + size_t(di) * c->conv_dim * f.conv_k, beta_l, g_l,
-                                       io->delta_o + di * do_sz, &gp, run))
-                return st;
+            // caller-made inputs, state and conv ring of this layer only: no kernel in front of it in the step touches
+            // anything it does, so it need not wait before it works
+            g_gdn_early = !glue;
+            const int gst = rl_gdn_decode(c->S + di * st_elems, c->conv + di * cv_elems, c->conv_phase + size_t(di) * f.n_slots,
+                                          io->slot_ids, io->delta_qkv + di * qkv_sz,
+                                          io->conv_w + size_t(di) * c->conv_dim * f.conv_k, beta_l, g_l,
+                                          io->delta_o + di * do_sz, &gp, run);
+            g_gdn_early = false;
+            if (gst) return gst;
             if (glue && glue->delta_z)
                 if (int st = rl_gated_rmsnorm(io->delta_o + di * do_sz, glue->delta_z + di * do_sz,
                                               glue->gnorm ? glue->gnorm + size_t(di) * f.dv : nullptr, io->delta_o + di * do_sz, B,
@@ -1326,6 +1332,7 @@ int rl_gdn_decode(float* S, float* conv_ring, const int32_t* conv_phase, const i
     a.head_map = p->head_map;
     a.conv_dim = 2 * p->n_qk * p->dk + p->n_v * p->dv;
     a.eps_l2 = p->eps_l2;
+    a.early = g_gdn_early && rl::g_step_overlap && !rl::g_step_first ? 1 : 0;
     rl::launch_gdn_decode(a, step_sms(d->sms), as_stream(stream), kGdnStreamMin, kGdnGrid);
     RL_CUDA(cudaGetLastError());
     return RL_OK;

@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
     // written (the kernel in front belongs to another layer, or to the end of the previous step), so its first
     // copies are on their way while that kernel finishes.  Everything else -- the step's inputs, the conv
     // rings, every write -- waits for the kernel in front.
-    if (warp != kWarpProducer) griddep_wait();
+    if (warp != kWarpProducer && !a.early) griddep_wait();
     auto slot_of = [&](int b) {
         int slot = a.slot_ids ? a.slot_ids[b] : b;
         if (slot < 0 || slot >= a.n_slots) {
@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
                 bulk_g2s(s.S[st], src, kHeadBytes, &s.full[st]);
             }
         }
+        if (a.early) griddep_wait();
         return;
     }
     if (warp >= kWarpConv0) {
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.vec_ready[buf]);
         }
+        if (a.early) griddep_wait();
         return;
     }
     // ------------------------------ consumers ------------------------------
@@ -270,6 +272,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gdn_decode_stream_kernel(Gd
             mbar_arrive(&s.vec_free[buf]);
         }
     }
+    if (a.early) griddep_wait();      // completes after the kernel in front, as every kernel of a step does
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -302,7 +305,7 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeArgs a) {
     float4 s[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) s[r] = *reinterpret_cast<const float4*>(Sp + (4 * rg + r) * kDv + col0);
-    griddep_wait();
+    if (!a.early) griddep_wait();
 
     if (warp < 2 || (warp == 2 && lane < kSliceCols / 4)) {
         // warp 0: q, warp 1: k (128 channels each), warp 2 lanes 0..7: this slice's 32 v channels
@@ -375,6 +378,7 @@ __global__ void __launch_bounds__(256) gdn_decode_kernel(GdnDecodeArgs a) {
         for (int w = 0; w < 8; ++w) t += red2[w][tid];
         a.o[(size_t(b) * a.n_v + h) * kDv + slice * kSliceCols + tid] = t;
     }
+    if (a.early) griddep_wait();
 }
 
 // phase[l][slot_ids[b]] += n_tok (mod 4): thread = (layer, sequence)

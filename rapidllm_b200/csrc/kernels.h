@@ -182,6 +182,10 @@ struct GdnDecodeArgs {
     int* err;
     int batch, n_v, n_qk, n_slots, head_map, conv_dim;
     float eps_l2;
+    // 1 (inside a step whose DeltaNet inputs are the caller's): nothing the kernel touches belongs to a kernel in
+    // front of it in the step, so it works at once -- filling the SMs the previous layer's last round leaves idle --
+    // and waits for the kernel in front only before it ends
+    int early;
 };
 // heads (items) from which the streaming form is used instead of one CTA per column slice
 void launch_gdn_decode(const GdnDecodeArgs& a, int sms, cudaStream_t st, int stream_min_items, int grid_override = 0);
