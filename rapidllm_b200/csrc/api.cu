@@ -587,7 +587,10 @@ int stack_decode_layers(rl_cache* c, const rl_stack_io* io, cudaStream_t run, bo
             ++di;
         }
         if (host_mode && ((L + 1) % kHostGroup == 0 || L + 1 == f.n_layers)) RL_CUDA(cudaEventRecord(c->ev_out[L], run));
-        if (comm && ((L + 1) % per_x == 0 || L + 1 == f.n_layers))
+        // one layer before each multiple of the group size, so that the last call of the step, the only one whose
+        // time the step waits for in full, carries the last layer alone (in qwen3_5's period of three DeltaNet layers
+        // and an attention layer: one tensor instead of four)
+        if (comm && ((L + 2) % per_x == 0 || L + 1 == f.n_layers))
             if (int st = exchange()) return st;
     }
     // every layer's window has taken this step's token: move the rings on
