@@ -54,7 +54,7 @@ PAGE = 64
 # tolerances of the sharded-step check (those of the tests: fp16-KV attention / FP32 DeltaNet)
 ATTN_MAX_ABS, ATTN_REL_L2, DELTA_MAX_ABS = 2e-2, 1e-3, 1e-4
 OPERATORS = ["f16_decode", "f16_decode_long", "delta_step", "compact_decode", "compact_decode_wht256",
-             "attn_prefill", "attn_prefill_chunk1024", "delta_prefill", "stack_prefill", "stack_long_compact", "stack_long_f16"]
+             "attn_prefill", "attn_prefill_chunk1024", "delta_prefill", "stack_prefill", "stack_prefill_chunk4096", "stack_long_compact", "stack_long_f16"]
 
 
 def parse():
@@ -562,14 +562,15 @@ def op_delta_prefill(args, sampler, peaks, gen):
         "clocks": clocks}
 
 
-def op_stack_prefill(args, sampler, peaks, gen):
-    """A prompt of T tokens through the mixers of all 64 layers in chunks of 1024 (the reference's chunk cap)."""
+def op_stack_prefill(args, sampler, peaks, gen, chunk=1024):
+    """A prompt of T tokens through the mixers of all 64 layers in chunks of 1024 (the reference's chunk cap) or of
+    4096 (what the memory of this part allows: fewer, longer calls of every kernel)."""
     import torch
 
     from rapidllm_b200 import _lib
     from rapidllm_b200.cache import QWEN35_LAYER_TYPES, HybridCache
     T = args.op_ctx or 8192
-    chunk = min(args.chunk or 1024, T)
+    chunk = min(args.chunk or chunk, T)
     types = (QWEN35_LAYER_TYPES * ((args.layers + 3) // 4))[:args.layers]
     pages = (T + PAGE - 1) // PAGE
     cache = HybridCache(types, n_pages=pages, n_slots=1, max_batch=1, max_pages_per_seq=pages)
@@ -711,8 +712,8 @@ def run_one_operator(name, args, sampler, peaks):
         return op_attn_prefill(name, args, sampler, peaks, gen)
     if name == "delta_prefill":
         return op_delta_prefill(args, sampler, peaks, gen)
-    if name == "stack_prefill":
-        return op_stack_prefill(args, sampler, peaks, gen)
+    if name in ("stack_prefill", "stack_prefill_chunk4096"):
+        return op_stack_prefill(args, sampler, peaks, gen, chunk=4096 if name.endswith("4096") else 1024)
     if name in ("stack_long_compact", "stack_long_f16"):
         return op_stack_long(args, sampler, peaks, gen, compact=name == "stack_long_compact")
     raise SystemExit("unknown operator %s" % name)
