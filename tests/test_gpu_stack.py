@@ -386,3 +386,54 @@ def test_stack_decode_with_the_element_wise_steps_inside(oracle):
                 assert np.abs(delta_o[d, b] - ref).max() <= 2e-4, (step, d, b, np.abs(delta_o[d, b] - ref).max())
             assert rel_l2(cache.state(d).cpu().numpy(), Sr[d]) < 1e-6
     cache.close()
+
+
+@pytest.mark.parametrize("B", [1, 40])
+def test_overlapped_step_equals_plain_per_layer_launches(B):
+    """Inside rl_stack_decode the kernels of a step are launched for programmatic dependent launch and some of
+    them work before they wait for the kernel in front (the DeltaNet step, the KV append, the decode kernel's
+    page stream).  A short stack makes consecutive kernels and consecutive steps overlap as far as they ever
+    can; thirty replayed steps must leave exactly the bits that plain launches, one operator after the other,
+    leave (B 1: one CTA per column slice; B 40: persistent CTAs streaming whole heads)."""
+    from rapidllm_b200 import _lib, ops
+    from rapidllm_b200.cache import HybridCache
+    lin, att = _lib.RL_LAYER_LINEAR_ATTENTION, _lib.RL_LAYER_FULL_ATTENTION
+    types = [lin, lin, att, lin]
+    gen = torch.Generator().manual_seed(70 + B)
+    n_steps, max_pages = 30, 2
+    cache = HybridCache(types, n_pages=B * max_pages, n_slots=B, max_batch=B, max_pages_per_seq=max_pages)
+    lens = [int(x) for x in torch.randint(1, 60, (B,), generator=gen)]
+    t = _inputs(cache, B, gen, lens)
+    t["page_table"] = torch.randperm(B * max_pages, generator=gen).int().view(B, max_pages)
+    dev = {n: x.cuda() for n, x in t.items()}
+    # the plain side: its own copies of state, rings, phases and pages
+    S = [cache.state(d).normal_(0, 0.02, generator=None).clone() for d in range(cache.n_delta)]
+    for d in range(cache.n_delta):
+        cache.set_conv_windows(d, torch.randn(cache.conv(d).shape, generator=gen))
+    ring = [cache.conv(d).clone() for d in range(cache.n_delta)]
+    phase = [torch.zeros(B, dtype=torch.int32, device="cuda") for _ in range(cache.n_delta)]
+    kp, vp = cache.k_pool(0).normal_().clone(), cache.v_pool(0).normal_().clone()
+    for d in range(cache.n_delta):
+        cache.state(d).copy_(S[d])
+    cache.k_pool(0).copy_(kp)
+    cache.v_pool(0).copy_(vp)
+    for step in range(n_steps):
+        if step:
+            fresh = _inputs(cache, B, gen, lens)
+            for n in ("attn_q", "attn_gate", "attn_k", "attn_v", "delta_qkv", "delta_beta", "delta_g"):
+                dev[n].copy_(fresh[n])
+            dev["pos"] += 1
+        cache.decode(dev, B)
+        for d in range(cache.n_delta):
+            o = ops.gdn_decode(S[d], ring[d], phase[d], dev["delta_qkv"][d], dev["conv_w"][d], dev["delta_beta"][d],
+                               dev["delta_g"][d], n_qk=cache.n_k)
+            assert torch.equal(o, dev["delta_o"][d]), (step, d)
+        ops.kv_append(kp, vp, dev["page_table"], dev["attn_k"][0].unsqueeze(1), dev["attn_v"][0].unsqueeze(1), pos=dev["pos"])
+        o = ops.attn_decode(dev["attn_q"][0], kp, vp, dev["page_table"], dev["pos"] + 1, dev["attn_gate"][0])
+        assert torch.equal(o, dev["attn_o"][0]), step
+    _lib.check_device()
+    for d in range(cache.n_delta):
+        assert torch.equal(cache.state(d), S[d])
+        assert torch.equal(cache.conv(d), ring[d])
+    assert torch.equal(cache.k_pool(0), kp) and torch.equal(cache.v_pool(0), vp)
+    cache.close()
